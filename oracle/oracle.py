@@ -1,0 +1,251 @@
+"""TEST INFRASTRUCTURE ONLY -- numpy front end of the CPU oracle.
+
+Imported by tests/, by the smoke test and by the benchmark's CPU-baseline leg; never by the package.
+The arithmetic lives in oracle.cpp (built by `make -C oracle`); this file restates the reference's
+host-side shape rules on numpy arrays, each function citing the reference file it follows (paths
+relative to the reference project root):
+
+  matmult / batched matmult   nt/functional/cpu/matmult_cpu.cpp:51-121,654-750,863-1005
+  linear                      nt/functional/cpu/matmult_cpu.cpp:1624-1714
+  unfold2d / conv2d           nt/functional/tensor_files/colim_transform.cpp:565-588, conv.cpp:69-96
+  conv backward               nt/functional/tensor_files/conv.cpp:318-346,444-471
+  matmult / linear backward   nt/nn/functional/matmult.cpp:37-63,253-273
+  relu (clamp) / MSE          nt/nn/functional/min_max.cpp:40-63, nt/nn/Loss.cpp:49-55
+
+Parity status: Float32 is pinned by the reference's committed golden vectors (tests/golden/);
+Float16 / integer / BFloat16 are "parity unpinned" by tests and follow the source semantics.
+"""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "_build", "liboracle.so")
+
+# dtype codes shared with include/ntb200.h
+F32, F16, BF16, I8, I16, I32, I64, F64, U8, U16, U32 = range(11)
+
+_NP_TO_CODE = {
+    np.dtype(np.float32): F32, np.dtype(np.float16): F16, np.dtype(np.int8): I8, np.dtype(np.int16): I16,
+    np.dtype(np.int32): I32, np.dtype(np.int64): I64, np.dtype(np.float64): F64, np.dtype(np.uint8): U8,
+    np.dtype(np.uint16): U16, np.dtype(np.uint32): U32,
+}
+
+
+def build(force=False):
+    """Compile liboracle.so with the committed Makefile (no-op when it is already there)."""
+    if force or not os.path.exists(_LIB_PATH):
+        subprocess.check_call(["make", "-C", _HERE] + (["-B"] if force else []))
+    return _LIB_PATH
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        _lib = ctypes.CDLL(build())
+        i64, vp, ci = ctypes.c_int64, ctypes.c_void_p, ctypes.c_int
+        _lib.oracle_matmult.argtypes = [ci, vp, vp, vp, i64, i64, i64, i64, ci, ci, ci]
+        _lib.oracle_matmult.restype = ci
+        _lib.oracle_im2col.argtypes = [ci, vp, vp] + [i64] * 12
+        _lib.oracle_im2col.restype = ci
+        _lib.oracle_col2im_f32.argtypes = [vp, vp] + [i64] * 12
+        _lib.oracle_col2im_f32.restype = ci
+        _lib.oracle_hardware_threads.restype = ci
+    return _lib
+
+
+def hardware_threads():
+    return int(lib().oracle_hardware_threads())
+
+
+def default_threads():
+    """The reference caps its GEMM at 21 TBB threads (nt_matmult_macros.h:42)."""
+    return max(1, min(21, hardware_threads()))
+
+
+def bf16_round(x32):
+    """float32 -> bfloat16 bit pattern (uint16), round to nearest even."""
+    u = np.ascontiguousarray(x32, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    r = (u + 0x7FFF + ((u >> 16) & 1)) >> 16
+    return r.astype(np.uint16)
+
+
+def bf16_widen(bits):
+    """bfloat16 bit pattern (uint16) -> float32, exact."""
+    return (np.ascontiguousarray(bits, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def _code(arr, bf16):
+    if bf16:
+        assert arr.dtype == np.uint16, "bf16 operands are passed as uint16 bit patterns"
+        return BF16
+    return _NP_TO_CODE[arr.dtype]
+
+
+def matmult_into(a, b, c, transpose_a=False, transpose_b=False, bf16=False, threads=None):
+    """C += op(A).op(B) on 2-D contiguous arrays: the raw nt_matmult<T> contract."""
+    assert a.ndim == 2 and b.ndim == 2 and c.ndim == 2
+    a = np.ascontiguousarray(a)
+    b = np.ascontiguousarray(b)
+    assert c.flags.c_contiguous and a.dtype == b.dtype == c.dtype
+    m, k = (a.shape[1], a.shape[0]) if transpose_a else a.shape
+    k2, n = (b.shape[1], b.shape[0]) if transpose_b else b.shape
+    if k != k2:
+        raise ValueError(f"matmult shape mismatch {a.shape} {b.shape} ta={transpose_a} tb={transpose_b}")
+    assert c.shape == (m, n)
+    rc = lib().oracle_matmult(_code(a, bf16), a.ctypes.data, b.ctypes.data, c.ctypes.data, m, k, k2, n,
+                              int(transpose_a), int(transpose_b), threads or default_threads())
+    if rc:
+        raise RuntimeError(f"oracle_matmult failed rc={rc}")
+    return c
+
+
+def matmult(a, b, transpose_a=False, transpose_b=False, bf16=False, threads=None):
+    """functional::matmult: 2-D x 2-D, N-D x N-D with equal leading dims, or one operand of lower
+    rank repeated over the other's batch (matmult_cpu.cpp:863-1005).  Result starts from zeros."""
+    if a.ndim < 2 or b.ndim < 2:
+        raise ValueError("matmult needs tensors of at least 2 dims")
+    if a.dtype != b.dtype:
+        raise ValueError("matmult operands must share a dtype")
+    am, ak = (a.shape[-1], a.shape[-2]) if transpose_a else a.shape[-2:]
+    bk, bn = (b.shape[-1], b.shape[-2]) if transpose_b else b.shape[-2:]
+    if ak != bk:
+        raise ValueError(f"matmult shape mismatch {a.shape} {b.shape}")
+    lead_a, lead_b = a.shape[:-2], b.shape[:-2]
+    if len(lead_a) >= len(lead_b):
+        lead = lead_a
+        if lead_b and lead_a[len(lead_a) - len(lead_b):] != lead_b:
+            raise ValueError("batch dims must match on the shared suffix")
+    else:
+        lead = lead_b
+        if lead_a and lead_b[len(lead_b) - len(lead_a):] != lead_a:
+            raise ValueError("batch dims must match on the shared suffix")
+    nb = int(np.prod(lead)) if lead else 1
+    a3 = np.ascontiguousarray(np.broadcast_to(a, lead + a.shape[-2:])).reshape((nb,) + a.shape[-2:])
+    b3 = np.ascontiguousarray(np.broadcast_to(b, lead + b.shape[-2:])).reshape((nb,) + b.shape[-2:])
+    out = np.zeros((nb, am, bn), dtype=a.dtype)
+    for i in range(nb):
+        matmult_into(a3[i], b3[i], out[i], transpose_a, transpose_b, bf16, threads)
+    return out.reshape(lead + (am, bn))
+
+
+def linear(x, w, bias=None, transpose_a=False, transpose_b=False, bf16=False, threads=None):
+    """functional::linear: C starts as the broadcast bias, then C += op(x).op(w)."""
+    if bias is None:
+        return matmult(x, w, transpose_a, transpose_b, bf16, threads)
+    m = x.shape[-1] if transpose_a else x.shape[-2]
+    n = w.shape[-2] if transpose_b else w.shape[-1]
+    lead = x.shape[:-2] if x.ndim >= w.ndim else w.shape[:-2]
+    nb = int(np.prod(lead)) if lead else 1
+    out = np.ascontiguousarray(np.broadcast_to(bias, lead + (m, n))).reshape(nb, m, n).copy()
+    x3 = np.ascontiguousarray(np.broadcast_to(x, lead + x.shape[-2:])).reshape((nb,) + x.shape[-2:])
+    w3 = np.ascontiguousarray(np.broadcast_to(w, lead + w.shape[-2:])).reshape((nb,) + w.shape[-2:])
+    for i in range(nb):
+        matmult_into(x3[i], w3[i], out[i], transpose_a, transpose_b, bf16, threads)
+    return out.reshape(lead + (m, n))
+
+
+def _pair(v):
+    return (int(v), int(v)) if np.isscalar(v) else (int(v[0]), int(v[1]))
+
+
+def conv_out_size(size, k, s, p, d):
+    return (size + 2 * p - d * (k - 1) - 1) // s + 1
+
+
+def unfold2d(x, kernel_size, dilation=1, padding=0, stride=1, bf16=False):
+    """functional::unfold2d(..., transpose_out=true): [B, C*kh*kw, L]."""
+    kh, kw = _pair(kernel_size)
+    dh, dw = _pair(dilation)
+    ph, pw = _pair(padding)
+    sh, sw = _pair(stride)
+    x4 = np.ascontiguousarray(x.reshape((-1,) + x.shape[-3:]))
+    bsz, ch, h, w = x4.shape
+    hc, wc = conv_out_size(h, kh, sh, ph, dh), conv_out_size(w, kw, sw, pw, dw)
+    col = np.zeros((bsz, ch * kh * kw, hc * wc), dtype=x.dtype)
+    rc = lib().oracle_im2col(_code(x4, bf16), x4.ctypes.data, col.ctypes.data, bsz, ch, h, w, kh, kw, sh, sw, ph, pw,
+                             dh, dw)
+    assert rc == 0
+    return col
+
+
+def unfold2d_backward(dcol, out_hw, kernel_size, dilation=1, padding=0, stride=1):
+    kh, kw = _pair(kernel_size)
+    dh, dw = _pair(dilation)
+    ph, pw = _pair(padding)
+    sh, sw = _pair(stride)
+    h, w = out_hw
+    dcol = np.ascontiguousarray(dcol, dtype=np.float32)
+    bsz = dcol.shape[0]
+    ch = dcol.shape[1] // (kh * kw)
+    im = np.zeros((bsz, ch, h, w), dtype=np.float32)
+    rc = lib().oracle_col2im_f32(dcol.ctypes.data, im.ctypes.data, bsz, ch, h, w, kh, kw, sh, sw, ph, pw, dh, dw)
+    assert rc == 0
+    return im
+
+
+def conv2d(x, w, stride=1, padding=0, dilation=1, bf16=False, threads=None):
+    """functional::conv2d, groups == 1: matmult(col, w2d, true, true) -> [B, L, Cout], then the
+    row/col swap and the view to [B, Cout, Ho, Wo] (conv.cpp:94-95)."""
+    kh, kw = w.shape[-2:]
+    dh, dw = _pair(dilation)
+    ph, pw = _pair(padding)
+    sh, sw = _pair(stride)
+    x4 = x.reshape((-1,) + x.shape[-3:])
+    ho = conv_out_size(x4.shape[-2], kh, sh, ph, dh)
+    wo = conv_out_size(x4.shape[-1], kw, sw, pw, dw)
+    col = unfold2d(x4, (kh, kw), dilation, padding, stride, bf16)
+    w2d = np.ascontiguousarray(w.reshape(w.shape[0], -1))
+    out = matmult(col, w2d, True, True, bf16, threads)            # [B, L, Cout]
+    return np.ascontiguousarray(out.transpose(0, 2, 1)).reshape(x4.shape[0], w.shape[0], ho, wo)
+
+
+def conv2d_backward(x, w, grad, stride=1, padding=0, dilation=1, threads=None):
+    """conv_dimage (conv.cpp:318-346) and conv_dkernel (conv.cpp:444-471), Float32, groups == 1."""
+    kh, kw = w.shape[-2:]
+    x4 = x.reshape((-1,) + x.shape[-3:])
+    bsz, cout = x4.shape[0], w.shape[0]
+    col = unfold2d(x4, (kh, kw), dilation, padding, stride)
+    w2d = np.ascontiguousarray(w.reshape(cout, -1))
+    g = np.ascontiguousarray(grad.reshape(bsz, cout, -1))
+    dcol = matmult(w2d, g, True, False, threads=threads)          # [B, C*kh*kw, L]
+    dx = unfold2d_backward(dcol, x4.shape[-2:], (kh, kw), dilation, padding, stride).reshape(x.shape)
+    dw = matmult(g, col, False, True, threads=threads).sum(axis=0, dtype=np.float32).reshape(w.shape)
+    return dx, dw
+
+
+def matmult_backward(a, b, grad, transpose_a=False, transpose_b=False, bf16=False, threads=None):
+    """nn/functional/matmult.cpp:37-63: the two transposed GEMMs, flags only."""
+    if transpose_a:
+        da = matmult(b, grad, transpose_b, True, bf16, threads)
+    else:
+        da = matmult(grad, b, False, not transpose_b, bf16, threads)
+    if transpose_b:
+        db = matmult(grad, a, True, transpose_a, bf16, threads)
+    else:
+        db = matmult(a, grad, not transpose_a, False, bf16, threads)
+    return da, db
+
+
+def relu(x):
+    """clamp(x, 0, none) (nn/functional/min_max.cpp:40-63); the mask is where the value changed."""
+    y = np.maximum(x, 0)
+    return y, (y != x)
+
+
+def mse(out, target):
+    """loss::MSE (nn/Loss.cpp:49-55): loss = sum((o-t)^2)/numel, dx = 2(o-t)/numel."""
+    d = out.astype(np.float32) - target.astype(np.float32)
+    return float((d * d).sum(dtype=np.float64) / d.size), (2.0 * d / d.size).astype(np.float32)
+
+
+def rel_fro(x, ref):
+    x = np.asarray(x, dtype=np.float64)
+    ref = np.asarray(ref, dtype=np.float64)
+    den = np.linalg.norm(ref.ravel())
+    return float(np.linalg.norm((x - ref).ravel()) / (den if den > 0 else 1.0))
