@@ -1,0 +1,178 @@
+/* ntb200 -- C ABI of the B200 (sm_100a) dense-contraction engine behind NeuroTensor's matmult path.
+ *
+ * Plain C, plain pointers and sizes: this is the boundary a NeuroTensor build binds instead of its CPU
+ * GEMM templates.  Every entry point returns an ntb200_status (0 = ok) and never throws; the text of the
+ * last failure on the calling thread is available from ntb200_last_error_string().
+ *
+ * Unless a function says "host", pointers are DEVICE pointers valid on the current CUDA device, `stream`
+ * is a cudaStream_t passed as void* (NULL = the legacy default stream) and calls are asynchronous on it.
+ * There is no CPU fallback anywhere: without a usable CUDA device every compute entry point fails with
+ * NTB200_ERR_NO_DEVICE / NTB200_ERR_CUDA.
+ *
+ * File:line citations name the reference interface (NeuroTensor, paths relative to its project root)
+ * that each entry point replaces.
+ */
+#ifndef NTB200_H_
+#define NTB200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Element types.  Output and accumulation follow the reference: the result has the operands' dtype;
+ * integers wrap modulo 2^bits (signed and unsigned share kernels); F16/BF16 accumulate in fp32. */
+typedef enum ntb200_dtype {
+    NTB200_F32 = 0,
+    NTB200_F16 = 1,
+    NTB200_BF16 = 2, /* not a dtype of the reference; added for this engine */
+    NTB200_I8 = 3,
+    NTB200_I16 = 4,
+    NTB200_I32 = 5,
+    NTB200_I64 = 6,
+    NTB200_F64 = 7,
+    NTB200_U8 = 8,
+    NTB200_U16 = 9,
+    NTB200_U32 = 10
+} ntb200_dtype;
+
+typedef enum ntb200_status {
+    NTB200_OK = 0,
+    NTB200_ERR_INVALID_ARG = 1,  /* what the reference reports as std::invalid_argument */
+    NTB200_ERR_UNSUPPORTED = 2,  /* dtype / layout this engine does not cover */
+    NTB200_ERR_ALLOC = 3,
+    NTB200_ERR_CUDA = 4,
+    NTB200_ERR_TIMEOUT = 5,      /* a bounded device-side wait ran out (see ntb200_check_device_status) */
+    NTB200_ERR_NO_DEVICE = 6
+} ntb200_status;
+
+/* Which kernel family a GEMM is routed to.  AUTO picks tcgen05 tensor cores for F16/BF16/I8/U8 when the
+ * operands can be described by a TMA tensor map (unit stride along rows or columns, 16-byte aligned base
+ * and other strides) and the CUDA-core kernel otherwise. */
+typedef enum ntb200_route {
+    NTB200_ROUTE_AUTO = 0,
+    NTB200_ROUTE_TENSOR = 1,  /* fail with NTB200_ERR_UNSUPPORTED if tcgen05 cannot take it */
+    NTB200_ROUTE_SIMT = 2     /* CUDA-core kernel: one ascending-k chain per output element */
+} ntb200_route;
+
+/* F16 rounding on the CUDA-core route.  The reference rounds the running sum to fp16 after every 16
+ * k-steps (nt/mp/simde_traits/simde_traits_avx2.h:1133-1165 with nt/functional/cpu/matmult/nt_matmult.hpp:196);
+ * NTB200_F16_ROUND_PER_KTILE reproduces that bit for bit, NTB200_F16_ROUND_ONCE keeps fp32 to the end. */
+typedef enum ntb200_f16_rounding { NTB200_F16_ROUND_ONCE = 0, NTB200_F16_ROUND_PER_KTILE = 1 } ntb200_f16_rounding;
+
+/* General strided, batched GEMM:  C[b] = (accumulate ? C[b] : 0) + bias + A[b] . B[b]
+ * A is m x k, B is k x n, C is m x n (column stride 1).  Strides are in ELEMENTS; a transposed view is a
+ * pair of swapped strides, never a copy.  A batch stride of 0 repeats the operand over the batch. */
+typedef struct ntb200_gemm_desc {
+    int32_t dtype;      /* ntb200_dtype */
+    int32_t route;      /* ntb200_route */
+    int32_t accumulate; /* 0: overwrite C, 1: C += (the reference's raw-pointer contract) */
+    int32_t f16_rounding;
+    int64_t m, n, k, batch;
+    const void* a; int64_t a_row_stride, a_col_stride, a_batch_stride;
+    const void* b; int64_t b_row_stride, b_col_stride, b_batch_stride;
+    void* c;       int64_t c_row_stride, c_batch_stride;
+    const void* bias; /* optional (NULL = none); same dtype */
+    int64_t bias_row_stride, bias_col_stride, bias_batch_stride;
+} ntb200_gemm_desc;
+
+/* ---- library / device ---------------------------------------------------------------------------- */
+const char* ntb200_version(void);
+const char* ntb200_last_error_string(void);
+int ntb200_device_count(int* count);
+int ntb200_set_device(int device);
+int ntb200_get_device(int* device);
+/* Number of this library's kernels launched by the process so far (all threads, all devices). */
+uint64_t ntb200_kernel_launch_count(void);
+/* Name of the kernel family the most recent GEMM on this thread was routed to ("umma_f16", "simt", ...). */
+const char* ntb200_last_gemm_route(void);
+/* Synchronises `stream` and reports NTB200_ERR_TIMEOUT if any kernel since the last check gave up a wait. */
+int ntb200_check_device_status(void* stream);
+
+/* ---- storage: replaces DeviceCPU::allocate / release (nt/memory/device.cpp:46-92) with a stream-ordered
+ * pool (cudaMallocAsync) on the current device. ---------------------------------------------------------- */
+int ntb200_malloc_async(void** ptr, size_t bytes, void* stream);
+int ntb200_free_async(void* ptr, void* stream);
+int ntb200_memset_async(void* ptr, int value, size_t bytes, void* stream);
+int ntb200_memcpy_h2d_async(void* dst_device, const void* src_host, size_t bytes, void* stream);
+int ntb200_memcpy_d2h_async(void* dst_host, const void* src_device, size_t bytes, void* stream);
+int ntb200_memcpy_d2d_async(void* dst_device, const void* src_device, size_t bytes, void* stream);
+int ntb200_stream_synchronize(void* stream);
+/* Bytes currently held / high-water mark of the pool: the device counterpart of
+ * nt::utils::getAllocatedMemory (nt/memory/track_memory.h:23-35). */
+int ntb200_pool_stats(uint64_t* bytes_in_use, uint64_t* high_water);
+
+/* ---- GEMM ----------------------------------------------------------------------------------------- */
+int ntb200_gemm(const ntb200_gemm_desc* desc, void* stream);
+
+/* Replaces nt_matmult<T> (nt/functional/cpu/matmult/nt_matmult.h:6-7; call sites
+ * nt/functional/cpu/matmult_cpu.cpp:118,150): C += op(A).op(B), row-major contiguous, a_rows/a_cols and
+ * b_rows/b_cols are the logical dims AFTER the transposes (a_cols == b_rows); with transpose_a the
+ * buffer holds A as [a_cols][a_rows].  Device pointers. */
+int ntb200_matmult(int dtype, const void* A, const void* B, void* C, int64_t a_rows, int64_t a_cols, int64_t b_rows,
+                   int64_t b_cols, int transpose_a, int transpose_b, void* stream);
+
+/* Replaces nt_matmult_batch<T> (nt_matmult.h:9-10; call sites matmult_cpu.cpp:740,851): host arrays of
+ * `batches` device pointers, same dims and flags for every item.  Equally spaced pointers run as one
+ * strided launch; anything else runs through a device pointer table. */
+int ntb200_matmult_batch(int dtype, const void* const* A, const void* const* B, void* const* C, int64_t batches,
+                         int64_t a_rows, int64_t a_cols, int64_t b_rows, int64_t b_cols, int transpose_a,
+                         int transpose_b, void* stream);
+
+/* The same two contracts with HOST buffers, exactly the pointers the reference's CPU templates receive:
+ * operands are staged to the device through pinned memory, multiplied there and C is copied back.
+ * `batches` contiguous items (A: batches x a-matrix, ...); synchronous.  accumulate = 1 is the templates'
+ * C += contract (C is uploaded first); accumulate = 0 overwrites C without uploading it, for the call sites
+ * that have just zero-filled C (matmult_cpu.cpp:110,707).  Copies and compute of successive chunks overlap
+ * on separate streams; pinned host buffers make the copies asynchronous. */
+int ntb200_matmult_host(int dtype, const void* A, const void* B, void* C, int64_t batches, int64_t a_rows,
+                        int64_t a_cols, int64_t b_rows, int64_t b_cols, int transpose_a, int transpose_b,
+                        int accumulate);
+
+/* ---- linear: replaces cpu::linear (nt/functional/cpu/matmult_cpu.cpp:1624-1714), which preloads C with
+ * the broadcast bias and then accumulates the GEMM.  Expressed through ntb200_gemm with `bias` set. ----- */
+
+/* ---- conv2d path -------------------------------------------------------------------------------------
+ * Replaces cpu::unfold2d_ / im2col_cpu (nt/functional/cpu/unfold2d.cpp:12-165,219-235):
+ * col[b][(c*kh + i)*kw + j][h*Wc + w] = im[b][c][h*sh - ph + i*dh][w*sw - pw + j*dw] (0 in the padding). */
+int ntb200_im2col(int dtype, const void* im, void* col, int64_t batch, int64_t channels, int64_t height,
+                  int64_t width, int64_t kh, int64_t kw, int64_t sh, int64_t sw, int64_t ph, int64_t pw, int64_t dh,
+                  int64_t dw, void* stream);
+/* Replaces unfold2d_backward / col2im (nt/functional/tensor_files/colim_transform.cpp:592-653): the
+ * adjoint of ntb200_im2col; `im` is overwritten.  F32, F16, BF16. */
+int ntb200_col2im(int dtype, const void* col, void* im, int64_t batch, int64_t channels, int64_t height,
+                  int64_t width, int64_t kh, int64_t kw, int64_t sh, int64_t sw, int64_t ph, int64_t pw, int64_t dh,
+                  int64_t dw, void* stream);
+/* Replaces functional::conv2d for groups == 1 (nt/functional/tensor_files/conv.cpp:69-96):
+ * out[B, Cout, Ho, Wo] = unfold2d(x) contracted with w[Cout, C*kh*kw].  `workspace` must hold
+ * ntb200_conv2d_workspace_bytes(...) bytes (the column matrix). */
+size_t ntb200_conv2d_workspace_bytes(int dtype, int64_t batch, int64_t channels, int64_t height, int64_t width,
+                                     int64_t kh, int64_t kw, int64_t sh, int64_t sw, int64_t ph, int64_t pw,
+                                     int64_t dh, int64_t dw);
+int ntb200_conv2d(int dtype, const void* x, const void* w, void* out, void* workspace, int64_t batch,
+                  int64_t channels, int64_t height, int64_t width, int64_t cout, int64_t kh, int64_t kw, int64_t sh,
+                  int64_t sw, int64_t ph, int64_t pw, int64_t dh, int64_t dw, void* stream);
+
+/* ---- elementwise neighbours of the GEMM in Linear forward/backward ----------------------------------
+ * relu = clamp(x, 0, none) and its mask backward (nt/nn/functional/min_max.cpp:40-63). */
+int ntb200_relu(int dtype, const void* x, void* y, int64_t n, void* stream);
+int ntb200_relu_backward(int dtype, const void* x, const void* grad_out, void* grad_in, int64_t n, void* stream);
+/* loss::MSE (nt/nn/Loss.cpp:49-55): *loss (float, device) = sum((o-t)^2)/n ; grad = 2(o-t)/n in `dtype`. */
+int ntb200_mse(int dtype, const void* out, const void* target, void* grad, float* loss, int64_t n, void* stream);
+/* Bias gradient: column sums of grad[rows, cols] -> out[cols], the broadcast-reduce that
+ * Tensor::operator+= / sum_as performs for dBias (nt/functional/tensor_files/operators.cpp:178-186). */
+int ntb200_column_sum(int dtype, const void* grad, void* out, int64_t rows, int64_t cols, void* stream);
+/* y += x elementwise: GraphNode::accumulate_gradient (nt/nn/AutoGrad.cpp:7-25). */
+int ntb200_add_inplace(int dtype, void* y, const void* x, int64_t n, void* stream);
+/* dst[rows, cols] (contiguous) = src viewed with the given element strides: Tensor::contiguous(). */
+int ntb200_copy_strided_2d(int dtype, void* dst, const void* src, int64_t batch, int64_t rows, int64_t cols,
+                           int64_t src_batch_stride, int64_t src_row_stride, int64_t src_col_stride, void* stream);
+/* dst = convert(src) between F32, F16, BF16: Tensor::to(DType). */
+int ntb200_convert(int dst_dtype, void* dst, int src_dtype, const void* src, int64_t n, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NTB200_H_ */

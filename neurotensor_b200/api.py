@@ -1,0 +1,308 @@
+"""Python mirror of the reference's functional interface for the matmult path, on CUDA tensors.
+
+Names, argument meaning and error behaviour follow the reference (paths relative to its project root):
+
+  matmult, matmult_cT, linear   nt/functional/tensor_files/matmult.h:10-13, matmult.cpp:14-38
+  shape rules                   nt/functional/cpu/matmult_cpu.cpp:51-93 (determine_transposes), :863-1005 (batches)
+  unfold2d / conv2d             nt/functional/tensor_files/colim_transform.cpp:565-588, conv.cpp:69-96
+  relu / MSE                    nt/nn/functional/min_max.cpp:40-63, nt/nn/Loss.cpp:49-55
+  matmult / linear backward     nt/nn/functional/matmult.cpp:37-63,253-273
+
+A torch.Tensor is used only as a typed handle on device memory (pointer, shape, strides); every operation
+is a call through the C ABI of libntb200.so on the current CUDA stream.  Transposed / strided views are
+passed as strides and are never copied when one of the last two strides is 1.  Shape and dtype problems
+raise ValueError (the reference throws std::invalid_argument) before anything is launched.
+"""
+import ctypes
+
+import torch
+
+from . import _lib
+from ._lib import GemmDesc, check, lib
+
+_TORCH_TO_CODE = {
+    torch.float32: _lib.F32, torch.float16: _lib.F16, torch.bfloat16: _lib.BF16, torch.int8: _lib.I8,
+    torch.int16: _lib.I16, torch.int32: _lib.I32, torch.int64: _lib.I64, torch.float64: _lib.F64,
+    torch.uint8: _lib.U8,
+}
+
+
+def dtype_code(t):
+    try:
+        return _TORCH_TO_CODE[t.dtype]
+    except KeyError:
+        raise ValueError("Expected a number type for matmult but got %s" % t.dtype)
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _require_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise ValueError("neurotensor_b200 operates on CUDA tensors only (there is no CPU path)")
+
+
+def _batch_view(t):
+    """(tensor, batch, batch_stride, row_stride, col_stride): leading dims folded into one batch stride.
+    A layout whose leading dims cannot be folded is made contiguous first."""
+    if t.dim() == 2:
+        return t, 1, 0, t.stride(0), t.stride(1)
+    lead = t.shape[:-2]
+    nb = 1
+    for s in lead:
+        nb *= s
+    # foldable iff stride[i] == stride[i+1] * shape[i+1] over the leading dims
+    ok = all(t.stride(i) == t.stride(i + 1) * t.shape[i + 1] for i in range(len(lead) - 1))
+    if not ok:
+        t = t.contiguous()
+    return t, nb, (t.stride(len(lead) - 1) if nb > 1 else 0), t.stride(-2), t.stride(-1)
+
+
+def _matmult_shapes(a, b, transpose_a, transpose_b):
+    if a.dim() < 2 or b.dim() < 2:
+        raise ValueError("Expected tensors of at least 2 dims for matmult but got %dD and %dD" % (a.dim(), b.dim()))
+    if a.dtype != b.dtype:
+        raise ValueError("Expected both tensors to have the same dtype for matmult but got %s and %s"
+                         % (a.dtype, b.dtype))
+    m, k = (a.shape[-1], a.shape[-2]) if transpose_a else (a.shape[-2], a.shape[-1])
+    k2, n = (b.shape[-1], b.shape[-2]) if transpose_b else (b.shape[-2], b.shape[-1])
+    if k != k2:
+        raise ValueError("Expected second tensor rows to be %d when it was %d (shapes %s and %s, transpose_a=%s, "
+                         "transpose_b=%s)" % (k, k2, tuple(a.shape), tuple(b.shape), transpose_a, transpose_b))
+    la, lb = tuple(a.shape[:-2]), tuple(b.shape[:-2])
+    longer, shorter = (la, lb) if len(la) >= len(lb) else (lb, la)
+    if shorter and longer[len(longer) - len(shorter):] != shorter:
+        raise ValueError("Expected batch dims to match on the shared suffix but got %s and %s" % (la, lb))
+    if shorter and len(shorter) != len(longer):
+        raise ValueError("A lower-rank batched operand is not supported; pass a 2-D tensor to repeat it")
+    return m, k, n, longer
+
+
+def gemm(a, b, out, transpose_a=False, transpose_b=False, accumulate=False, bias=None, route=_lib.ROUTE_AUTO,
+         f16_rounding=_lib.F16_ROUND_ONCE):
+    """out = (accumulate ? out : 0) + bias + op(a).op(b); `out` contiguous in its last dim."""
+    _require_cuda(a, b, out, bias)
+    m, k, n, lead = _matmult_shapes(a, b, transpose_a, transpose_b)
+    if out.dtype != a.dtype:
+        raise ValueError("Expected out to have dtype %s but got %s" % (a.dtype, out.dtype))
+    if tuple(out.shape) != tuple(lead) + (m, n):
+        raise ValueError("Expected out to have shape %s but got %s" % (tuple(lead) + (m, n), tuple(out.shape)))
+    if not out.is_contiguous():
+        raise ValueError("Expected out to be contiguous")
+    av, ab, a_bs, a_rs, a_cs = _batch_view(a)
+    bv, bb, b_bs, b_rs, b_cs = _batch_view(b)
+    if transpose_a:
+        a_rs, a_cs = a_cs, a_rs
+    if transpose_b:
+        b_rs, b_cs = b_cs, b_rs
+    nb = 1
+    for s in lead:
+        nb *= s
+    d = GemmDesc()
+    d.dtype, d.route, d.accumulate, d.f16_rounding = dtype_code(a), route, int(bool(accumulate)), f16_rounding
+    d.m, d.n, d.k, d.batch = m, n, k, nb
+    d.a, d.a_row_stride, d.a_col_stride, d.a_batch_stride = av.data_ptr(), a_rs, a_cs, (a_bs if ab > 1 else 0)
+    d.b, d.b_row_stride, d.b_col_stride, d.b_batch_stride = bv.data_ptr(), b_rs, b_cs, (b_bs if bb > 1 else 0)
+    d.c, d.c_row_stride, d.c_batch_stride = out.data_ptr(), n, m * n
+    if bias is not None:
+        if bias.dtype != a.dtype:
+            raise ValueError("Expected bias to have dtype %s but got %s" % (a.dtype, bias.dtype))
+        try:
+            bx = bias.expand(tuple(lead) + (m, n))
+        except RuntimeError:
+            raise ValueError("bias of shape %s cannot be broadcast to the output %s"
+                             % (tuple(bias.shape), tuple(lead) + (m, n)))
+        st = bx.stride()
+        lead_strides = st[:-2]
+        foldable = all(lead_strides[i] == lead_strides[i + 1] * bx.shape[i + 1]
+                       for i in range(len(lead_strides) - 1))
+        if nb > 1 and any(lead_strides) and not foldable:
+            bx = bx.contiguous()
+            st = bx.stride()
+            lead_strides = st[:-2]
+        d.bias = bx.data_ptr()
+        d.bias_row_stride, d.bias_col_stride = st[-2], st[-1]
+        d.bias_batch_stride = lead_strides[-1] if (nb > 1 and lead_strides) else 0
+    check(lib().ntb200_gemm(ctypes.byref(d), _stream()))
+    return out
+
+
+def matmult(a, b, transpose_a=False, transpose_b=False, out=None, route=_lib.ROUTE_AUTO,
+            f16_rounding=_lib.F16_ROUND_ONCE):
+    """functional::matmult.  Without `out` returns a new tensor op(a).op(b); with `out` computes
+    out += op(a).op(b) into the caller's contiguous tensor and returns it (matmult_cpu.cpp:137-153)."""
+    m, k, n, lead = _matmult_shapes(a, b, transpose_a, transpose_b)
+    if out is None:
+        res = torch.empty(tuple(lead) + (m, n), dtype=a.dtype, device=a.device)
+        return gemm(a, b, res, transpose_a, transpose_b, accumulate=False, route=route, f16_rounding=f16_rounding)
+    return gemm(a, b, out, transpose_a, transpose_b, accumulate=True, route=route, f16_rounding=f16_rounding)
+
+
+def matmult_cT(a, b):
+    return matmult(a, b, False, True)
+
+
+def linear(x, w, bias=None, transpose_a=False, transpose_b=False, route=_lib.ROUTE_AUTO):
+    """functional::linear: op(x).op(w) + bias, the bias broadcast over rows and batch."""
+    if bias is None:
+        return matmult(x, w, transpose_a, transpose_b, route=route)
+    m, k, n, lead = _matmult_shapes(x, w, transpose_a, transpose_b)
+    res = torch.empty(tuple(lead) + (m, n), dtype=x.dtype, device=x.device)
+    return gemm(x, w, res, transpose_a, transpose_b, accumulate=False, bias=bias, route=route)
+
+
+def _pair(v):
+    return (int(v), int(v)) if isinstance(v, int) else (int(v[0]), int(v[1]))
+
+
+def _conv_geom(x, kernel_size, dilation, padding, stride):
+    kh, kw = _pair(kernel_size)
+    dh, dw = _pair(dilation)
+    ph, pw = _pair(padding)
+    sh, sw = _pair(stride)
+    if sh < 1 or sw < 1:
+        raise ValueError("Conv2d stride cannot be less than 1 but got %s" % (stride,))
+    if dh < 1 or dw < 1:
+        raise ValueError("Conv2d dilation cannot be less than 1 but got %s" % (dilation,))
+    if ph < 0 or pw < 0:
+        raise ValueError("Conv2d padding cannot be less than 0 but got %s" % (padding,))
+    if x.dim() < 3:
+        raise ValueError("Expected input tensor to have dims greater than or equal to 3 but got %dD" % x.dim())
+    x4 = x.reshape((-1,) + tuple(x.shape[-3:])).contiguous()
+    ho = (x4.shape[-2] + 2 * ph - dh * (kh - 1) - 1) // sh + 1
+    wo = (x4.shape[-1] + 2 * pw - dw * (kw - 1) - 1) // sw + 1
+    if ho <= 0 or wo <= 0:
+        raise ValueError("calculated shape of the array of sliding blocks as (%d, %d), but its components must be "
+                         "at least one" % (ho, wo))
+    return x4, (kh, kw, sh, sw, ph, pw, dh, dw), ho, wo
+
+
+def unfold2d(x, kernel_size, dilation=1, padding=0, stride=1):
+    """functional::unfold2d(..., transpose_out=true) -> [B, C*kh*kw, L]."""
+    _require_cuda(x)
+    x4, (kh, kw, sh, sw, ph, pw, dh, dw), ho, wo = _conv_geom(x, kernel_size, dilation, padding, stride)
+    bsz, ch, h, w = x4.shape
+    col = torch.empty((bsz, ch * kh * kw, ho * wo), dtype=x.dtype, device=x.device)
+    check(lib().ntb200_im2col(dtype_code(x), x4.data_ptr(), col.data_ptr(), bsz, ch, h, w, kh, kw, sh, sw, ph, pw,
+                              dh, dw, _stream()))
+    return col
+
+
+def unfold2d_backward(dcol, out_hw, kernel_size, dilation=1, padding=0, stride=1):
+    _require_cuda(dcol)
+    kh, kw = _pair(kernel_size)
+    dh, dw = _pair(dilation)
+    ph, pw = _pair(padding)
+    sh, sw = _pair(stride)
+    h, w = out_hw
+    dcol = dcol.contiguous()
+    bsz, ch = dcol.shape[0], dcol.shape[1] // (kh * kw)
+    im = torch.empty((bsz, ch, h, w), dtype=dcol.dtype, device=dcol.device)
+    check(lib().ntb200_col2im(dtype_code(dcol), dcol.data_ptr(), im.data_ptr(), bsz, ch, h, w, kh, kw, sh, sw, ph, pw,
+                              dh, dw, _stream()))
+    return im
+
+
+def conv2d(x, w, stride=1, padding=0, dilation=1, groups=1, workspace=None):
+    """functional::conv2d for groups == 1 -> [B, Cout, Ho, Wo]."""
+    _require_cuda(x, w)
+    if groups != 1:
+        raise ValueError("conv2d: groups > 1 is outside this engine's scope")
+    if w.dim() not in (3, 4):
+        raise ValueError("Expected to get a 4D or 3D tensor as the kernel for a 2d convolution, but got %dD" % w.dim())
+    if x.dtype != w.dtype:
+        raise ValueError("Expected both kernel and image to have the same dtype for conv2d but got %s and %s"
+                         % (w.dtype, x.dtype))
+    w4 = (w.unsqueeze(0) if w.dim() == 3 else w).contiguous()
+    x4, (kh, kw, sh, sw, ph, pw, dh, dw), ho, wo = _conv_geom(x, w4.shape[-2:], dilation, padding, stride)
+    bsz, ch, h, wd = x4.shape
+    if w4.shape[1] != ch:
+        raise ValueError("Expected kernel channels %d to equal image channels %d" % (w4.shape[1], ch))
+    cout = w4.shape[0]
+    code = dtype_code(x)
+    need = lib().ntb200_conv2d_workspace_bytes(code, bsz, ch, h, wd, kh, kw, sh, sw, ph, pw, dh, dw)
+    if workspace is None or workspace.numel() * workspace.element_size() < need:
+        workspace = torch.empty(need, dtype=torch.uint8, device=x.device)
+    out = torch.empty((bsz, cout, ho, wo), dtype=x.dtype, device=x.device)
+    check(lib().ntb200_conv2d(code, x4.data_ptr(), w4.data_ptr(), out.data_ptr(), workspace.data_ptr(), bsz, ch, h,
+                              wd, cout, kh, kw, sh, sw, ph, pw, dh, dw, _stream()))
+    return out
+
+
+def relu(x):
+    _require_cuda(x)
+    x = x.contiguous()
+    y = torch.empty_like(x)
+    check(lib().ntb200_relu(dtype_code(x), x.data_ptr(), y.data_ptr(), x.numel(), _stream()))
+    return y
+
+
+def relu_backward(x, grad_out):
+    x, grad_out = x.contiguous(), grad_out.contiguous()
+    gi = torch.empty_like(grad_out)
+    check(lib().ntb200_relu_backward(dtype_code(x), x.data_ptr(), grad_out.data_ptr(), gi.data_ptr(), x.numel(),
+                                     _stream()))
+    return gi
+
+
+def mse(out, target, want_grad=True):
+    """loss::MSE -> (loss as a 1-element float32 device tensor, dx or None)."""
+    out, target = out.contiguous(), target.contiguous()
+    loss = torch.empty(1, dtype=torch.float32, device=out.device)
+    grad = torch.empty_like(out) if want_grad else None
+    check(lib().ntb200_mse(dtype_code(out), out.data_ptr(), target.data_ptr(), grad.data_ptr() if want_grad else None,
+                           loss.data_ptr(), out.numel(), _stream()))
+    return loss, grad
+
+
+def column_sum(grad):
+    g2 = grad.reshape(-1, grad.shape[-1]).contiguous()
+    out = torch.empty(g2.shape[1], dtype=grad.dtype, device=grad.device)
+    check(lib().ntb200_column_sum(dtype_code(g2), g2.data_ptr(), out.data_ptr(), g2.shape[0], g2.shape[1], _stream()))
+    return out
+
+
+def matmult_backward(a, b, grad, transpose_a=False, transpose_b=False):
+    """The two transposed GEMMs of nn/functional/matmult.cpp:37-63 (flags only, nothing is materialised)."""
+    if transpose_a:
+        da = matmult(b, grad, transpose_b, True)
+    else:
+        da = matmult(grad, b, False, not transpose_b)
+    if transpose_b:
+        db = matmult(grad, a, True, transpose_a)
+    else:
+        db = matmult(a, grad, not transpose_a, False)
+    return da, db
+
+
+def matmult_host(a, b, c, transpose_a=False, transpose_b=False, accumulate=True):
+    """The raw nt_matmult / nt_matmult_batch contract on HOST arrays (torch CPU tensors or numpy arrays, ideally
+    pinned): c += op(a).op(b) (or c = op(a).op(b) with accumulate=False), staged through the device by the
+    library.  a, b, c are 2-D or 3-D and contiguous."""
+    import numpy as np
+
+    np_codes = {"float32": _lib.F32, "float16": _lib.F16, "int8": _lib.I8, "int16": _lib.I16, "int32": _lib.I32,
+                "int64": _lib.I64, "float64": _lib.F64, "uint8": _lib.U8, "uint16": _lib.U16, "uint32": _lib.U32}
+
+    def info(t):
+        if isinstance(t, torch.Tensor):
+            if t.is_cuda or not t.is_contiguous():
+                raise ValueError("matmult_host expects contiguous host tensors")
+            return t.data_ptr(), tuple(t.shape), dtype_code(t)
+        if not isinstance(t, np.ndarray) or not t.flags.c_contiguous:
+            raise ValueError("matmult_host expects contiguous host arrays")
+        return t.ctypes.data, t.shape, np_codes[t.dtype.name]
+
+    pa, sa, ca = info(a)
+    pb, sb, cb = info(b)
+    pc, sc, cc = info(c)
+    if not (ca == cb == cc):
+        raise ValueError("matmult_host operands must share a dtype")
+    batches = sa[0] if len(sa) == 3 else 1
+    am, ak = (sa[-1], sa[-2]) if transpose_a else (sa[-2], sa[-1])
+    bk, bn = (sb[-1], sb[-2]) if transpose_b else (sb[-2], sb[-1])
+    check(lib().ntb200_matmult_host(ca, pa, pb, pc, batches, am, ak, bk, bn, int(transpose_a), int(transpose_b),
+                                    int(bool(accumulate))))
+    return c

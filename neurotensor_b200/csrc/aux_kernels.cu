@@ -1,0 +1,354 @@
+// Memory-bound neighbours of the GEMM on the Linear / conv2d path: im2col and its adjoint, ReLU and its
+// mask backward, MSE, the bias-gradient column sum, gradient accumulation, strided copy and dtype
+// conversion.  All are HBM-bound byte movers: coalesced along the innermost dimension, grid-stride loops
+// sized in multiples of the SM count.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <algorithm>
+
+#include "internal.h"
+
+namespace ntb200 {
+namespace {
+
+inline int grid_for(long long n, int per_block) {
+    const long long want = (n + per_block - 1) / per_block;
+    return int(std::max<long long>(1, std::min<long long>(want, (long long)sm_count() * 16)));
+}
+
+template <class T> struct F;
+template <> struct F<float> {
+    static __device__ __forceinline__ float ld(float v) { return v; }
+    static __device__ __forceinline__ float st(float v) { return v; }
+};
+template <> struct F<__half> {
+    static __device__ __forceinline__ float ld(__half v) { return __half2float(v); }
+    static __device__ __forceinline__ __half st(float v) { return __float2half_rn(v); }
+};
+template <> struct F<__nv_bfloat16> {
+    static __device__ __forceinline__ float ld(__nv_bfloat16 v) { return __bfloat162float(v); }
+    static __device__ __forceinline__ __nv_bfloat16 st(float v) { return __float2bfloat16_rn(v); }
+};
+
+struct ConvGeom {
+    long long batch, channels, height, width, kh, kw, sh, sw, ph, pw, dh, dw, hc, wc;
+};
+
+// One thread per column-matrix element; consecutive threads walk the output pixels (coalesced stores, and
+// for unit stride near-contiguous loads).  T is an unsigned integer of the element's size: pure byte moves.
+template <class T>
+__global__ void im2col_kernel(const T* __restrict__ im, T* __restrict__ col, const ConvGeom g) {
+    const long long L = g.hc * g.wc, ccol = g.channels * g.kh * g.kw;
+    const long long total = g.batch * ccol * L;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long l = i % L, c = (i / L) % ccol, b = i / (L * ccol);
+        const long long w = l % g.wc, h = l / g.wc;
+        const long long w_off = c % g.kw, h_off = (c / g.kw) % g.kh, c_im = c / (g.kh * g.kw);
+        const long long hp = h * g.sh - g.ph + h_off * g.dh, wp = w * g.sw - g.pw + w_off * g.dw;
+        T v = T(0);
+        if (hp >= 0 && hp < g.height && wp >= 0 && wp < g.width)
+            v = im[((b * g.channels + c_im) * g.height + hp) * g.width + wp];
+        col[i] = v;
+    }
+}
+
+// Gather form of col2im: each image element sums the taps that read it (no atomics, deterministic).
+template <class T>
+__global__ void col2im_kernel(const T* __restrict__ col, T* __restrict__ im, const ConvGeom g) {
+    const long long total = g.batch * g.channels * g.height * g.width;
+    const long long L = g.hc * g.wc, ccol = g.channels * g.kh * g.kw;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long w = i % g.width, h = (i / g.width) % g.height;
+        const long long c_im = (i / (g.width * g.height)) % g.channels, b = i / (g.width * g.height * g.channels);
+        float acc = 0.f;
+        for (long long ki = 0; ki < g.kh; ++ki) {
+            const long long hn = h + g.ph - ki * g.dh;
+            if (hn < 0 || hn % g.sh) continue;
+            const long long hc = hn / g.sh;
+            if (hc >= g.hc) continue;
+            for (long long kj = 0; kj < g.kw; ++kj) {
+                const long long wn = w + g.pw - kj * g.dw;
+                if (wn < 0 || wn % g.sw) continue;
+                const long long wc = wn / g.sw;
+                if (wc >= g.wc) continue;
+                const long long c = (c_im * g.kh + ki) * g.kw + kj;
+                acc += F<T>::ld(col[(b * ccol + c) * L + hc * g.wc + wc]);
+            }
+        }
+        im[i] = F<T>::st(acc);
+    }
+}
+
+template <class T>
+__global__ void relu_kernel(const T* __restrict__ x, T* __restrict__ y, long long n) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const float v = F<T>::ld(x[i]);
+        y[i] = v < 0.f ? F<T>::st(0.f) : x[i];
+    }
+}
+// grad_in = grad_out where clamp left x unchanged (x >= 0), else 0 (the "before != after" mask).
+template <class T>
+__global__ void relu_backward_kernel(const T* __restrict__ x, const T* __restrict__ go, T* __restrict__ gi, long long n) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        gi[i] = F<T>::ld(x[i]) < 0.f ? F<T>::st(0.f) : go[i];
+}
+
+template <class T>
+__global__ void mse_kernel(const T* __restrict__ o, const T* __restrict__ t, T* __restrict__ grad, float* __restrict__ loss,
+                           long long n, float inv_n) {
+    float local = 0.f;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const float d = F<T>::ld(o[i]) - F<T>::ld(t[i]);
+        local += d * d;
+        if (grad) grad[i] = F<T>::st(2.f * d * inv_n);
+    }
+    __shared__ float red[32];
+    for (int off = 16; off; off >>= 1) local += __shfl_xor_sync(0xffffffffu, local, off);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = local;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+        for (int off = 16; off; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+        if (threadIdx.x == 0) atomicAdd(loss, v * inv_n);
+    }
+}
+
+// out[c] = sum_r grad[r][c]; block = 32 columns x 32 row lanes, one block per 32 columns.
+template <class T>
+__global__ void column_sum_kernel(const T* __restrict__ g, T* __restrict__ out, long long rows, long long cols) {
+    __shared__ float red[32][33];
+    const long long c = (long long)blockIdx.x * 32 + threadIdx.x;
+    float acc = 0.f;
+    if (c < cols)
+        for (long long r = threadIdx.y; r < rows; r += 32) acc += F<T>::ld(g[r * cols + c]);
+    red[threadIdx.y][threadIdx.x] = acc;
+    __syncthreads();
+    if (threadIdx.y == 0 && c < cols) {
+        float s = 0.f;
+        for (int r = 0; r < 32; ++r) s += red[r][threadIdx.x];
+        out[c] = F<T>::st(s);
+    }
+}
+
+template <class T>
+__global__ void add_inplace_kernel(T* __restrict__ y, const T* __restrict__ x, long long n) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        y[i] = F<T>::st(F<T>::ld(y[i]) + F<T>::ld(x[i]));
+}
+__global__ void add_inplace_i32_kernel(unsigned int* __restrict__ y, const unsigned int* __restrict__ x, long long n) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        y[i] += x[i];
+}
+
+// 32 x 32 tiled strided copy through shared memory: coalesced on both sides whichever stride is the unit one.
+template <class T>
+__global__ void copy_strided_kernel(T* __restrict__ dst, const T* __restrict__ src, long long rows, long long cols,
+                                    long long sbs, long long srs, long long scs) {
+    __shared__ T tile[32][33];
+    const long long b = blockIdx.z;
+    const long long r0 = (long long)blockIdx.y * 32, c0 = (long long)blockIdx.x * 32;
+    const T* s = src + b * sbs;
+    T* d = dst + b * rows * cols;
+    if (scs == 1 || srs != 1) {
+        for (int j = threadIdx.y; j < 32; j += 8) {
+            const long long r = r0 + j, c = c0 + threadIdx.x;
+            if (r < rows && c < cols) tile[j][threadIdx.x] = s[r * srs + c * scs];
+        }
+    } else {  // rows are the unit-stride direction of the source: read along rows
+        for (int j = threadIdx.y; j < 32; j += 8) {
+            const long long r = r0 + threadIdx.x, c = c0 + j;
+            if (r < rows && c < cols) tile[threadIdx.x][j] = s[r * srs + c * scs];
+        }
+    }
+    __syncthreads();
+    for (int j = threadIdx.y; j < 32; j += 8) {
+        const long long r = r0 + j, c = c0 + threadIdx.x;
+        if (r < rows && c < cols) d[r * cols + c] = tile[j][threadIdx.x];
+    }
+}
+
+template <class D, class S>
+__global__ void convert_kernel(D* __restrict__ dst, const S* __restrict__ src, long long n) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        dst[i] = F<D>::st(F<S>::ld(src[i]));
+}
+
+bool geom(ConvGeom* g, int64_t batch, int64_t channels, int64_t height, int64_t width, int64_t kh, int64_t kw, int64_t sh,
+          int64_t sw, int64_t ph, int64_t pw, int64_t dh, int64_t dw) {
+    if (batch < 0 || channels < 0 || height <= 0 || width <= 0 || kh <= 0 || kw <= 0 || sh < 1 || sw < 1 || ph < 0 ||
+        pw < 0 || dh < 1 || dw < 1)
+        return false;
+    *g = ConvGeom{batch, channels, height, width, kh, kw, sh, sw, ph, pw, dh, dw, 0, 0};
+    g->hc = (height + 2 * ph - dh * (kh - 1) - 1) / sh + 1;
+    g->wc = (width + 2 * pw - dw * (kw - 1) - 1) / sw + 1;
+    return g->hc > 0 && g->wc > 0;
+}
+
+#define NTB200_FLOAT_SWITCH(dtype, CALL)                                   \
+    switch (dtype) {                                                       \
+        case NTB200_F32: { using T = float; CALL; break; }                 \
+        case NTB200_F16: { using T = __half; CALL; break; }                \
+        case NTB200_BF16: { using T = __nv_bfloat16; CALL; break; }        \
+        default: return fail(NTB200_ERR_UNSUPPORTED, "%s: dtype %s is not a float type of this engine", __func__, dtype_name(dtype)); \
+    }
+
+}  // namespace
+}  // namespace ntb200
+
+using namespace ntb200;
+
+extern "C" {
+
+int ntb200_im2col(int dtype, const void* im, void* col, int64_t batch, int64_t channels, int64_t height, int64_t width,
+                  int64_t kh, int64_t kw, int64_t sh, int64_t sw, int64_t ph, int64_t pw, int64_t dh, int64_t dw,
+                  void* stream) {
+    ConvGeom g;
+    if (!geom(&g, batch, channels, height, width, kh, kw, sh, sw, ph, pw, dh, dw))
+        return fail(NTB200_ERR_INVALID_ARG, "im2col: bad geometry (calculated sliding-block shape must be at least one)");
+    const long long total = g.batch * g.channels * g.kh * g.kw * g.hc * g.wc;
+    if (total == 0) return NTB200_OK;
+    if (!im || !col) return fail(NTB200_ERR_INVALID_ARG, "im2col: null pointer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int blocks = grid_for(total, 256);
+    switch (dtype_size(dtype)) {
+        case 1: im2col_kernel<uint8_t><<<blocks, 256, 0, s>>>((const uint8_t*)im, (uint8_t*)col, g); break;
+        case 2: im2col_kernel<uint16_t><<<blocks, 256, 0, s>>>((const uint16_t*)im, (uint16_t*)col, g); break;
+        case 4: im2col_kernel<uint32_t><<<blocks, 256, 0, s>>>((const uint32_t*)im, (uint32_t*)col, g); break;
+        case 8: im2col_kernel<unsigned long long><<<blocks, 256, 0, s>>>((const unsigned long long*)im, (unsigned long long*)col, g); break;
+        default: return fail(NTB200_ERR_UNSUPPORTED, "im2col: unknown dtype %d", dtype);
+    }
+    count_launch();
+    NTB200_CUDA(cudaGetLastError());
+    return NTB200_OK;
+}
+
+int ntb200_col2im(int dtype, const void* col, void* im, int64_t batch, int64_t channels, int64_t height, int64_t width,
+                  int64_t kh, int64_t kw, int64_t sh, int64_t sw, int64_t ph, int64_t pw, int64_t dh, int64_t dw,
+                  void* stream) {
+    ConvGeom g;
+    if (!geom(&g, batch, channels, height, width, kh, kw, sh, sw, ph, pw, dh, dw))
+        return fail(NTB200_ERR_INVALID_ARG, "col2im: bad geometry");
+    const long long total = g.batch * g.channels * g.height * g.width;
+    if (total == 0) return NTB200_OK;
+    if (!im || !col) return fail(NTB200_ERR_INVALID_ARG, "col2im: null pointer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int blocks = grid_for(total, 256);
+    NTB200_FLOAT_SWITCH(dtype, (col2im_kernel<T><<<blocks, 256, 0, s>>>((const T*)col, (T*)im, g)));
+    count_launch();
+    NTB200_CUDA(cudaGetLastError());
+    return NTB200_OK;
+}
+
+int ntb200_relu(int dtype, const void* x, void* y, int64_t n, void* stream) {
+    if (n < 0) return fail(NTB200_ERR_INVALID_ARG, "relu: negative size");
+    if (n == 0) return NTB200_OK;
+    if (!x || !y) return fail(NTB200_ERR_INVALID_ARG, "relu: null pointer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int blocks = grid_for(n, 1024);
+    NTB200_FLOAT_SWITCH(dtype, (relu_kernel<T><<<blocks, 256, 0, s>>>((const T*)x, (T*)y, n)));
+    count_launch();
+    NTB200_CUDA(cudaGetLastError());
+    return NTB200_OK;
+}
+
+int ntb200_relu_backward(int dtype, const void* x, const void* grad_out, void* grad_in, int64_t n, void* stream) {
+    if (n < 0) return fail(NTB200_ERR_INVALID_ARG, "relu_backward: negative size");
+    if (n == 0) return NTB200_OK;
+    if (!x || !grad_out || !grad_in) return fail(NTB200_ERR_INVALID_ARG, "relu_backward: null pointer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int blocks = grid_for(n, 1024);
+    NTB200_FLOAT_SWITCH(dtype, (relu_backward_kernel<T><<<blocks, 256, 0, s>>>((const T*)x, (const T*)grad_out, (T*)grad_in, n)));
+    count_launch();
+    NTB200_CUDA(cudaGetLastError());
+    return NTB200_OK;
+}
+
+int ntb200_mse(int dtype, const void* out, const void* target, void* grad, float* loss, int64_t n, void* stream) {
+    if (n <= 0) return fail(NTB200_ERR_INVALID_ARG, "mse: size must be positive");
+    if (!out || !target || !loss) return fail(NTB200_ERR_INVALID_ARG, "mse: null pointer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    NTB200_CUDA(cudaMemsetAsync(loss, 0, sizeof(float), s));
+    const int blocks = grid_for(n, 2048);
+    const float inv_n = 1.0f / float(n);
+    NTB200_FLOAT_SWITCH(dtype, (mse_kernel<T><<<blocks, 256, 0, s>>>((const T*)out, (const T*)target, (T*)grad, loss, n, inv_n)));
+    count_launch();
+    NTB200_CUDA(cudaGetLastError());
+    return NTB200_OK;
+}
+
+int ntb200_column_sum(int dtype, const void* grad, void* out, int64_t rows, int64_t cols, void* stream) {
+    if (rows < 0 || cols < 0) return fail(NTB200_ERR_INVALID_ARG, "column_sum: negative size");
+    if (cols == 0) return NTB200_OK;
+    if (!grad || !out) return fail(NTB200_ERR_INVALID_ARG, "column_sum: null pointer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const dim3 block(32, 32);
+    const unsigned blocks = unsigned((cols + 31) / 32);
+    NTB200_FLOAT_SWITCH(dtype, (column_sum_kernel<T><<<blocks, block, 0, s>>>((const T*)grad, (T*)out, rows, cols)));
+    count_launch();
+    NTB200_CUDA(cudaGetLastError());
+    return NTB200_OK;
+}
+
+int ntb200_add_inplace(int dtype, void* y, const void* x, int64_t n, void* stream) {
+    if (n < 0) return fail(NTB200_ERR_INVALID_ARG, "add_inplace: negative size");
+    if (n == 0) return NTB200_OK;
+    if (!x || !y) return fail(NTB200_ERR_INVALID_ARG, "add_inplace: null pointer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int blocks = grid_for(n, 1024);
+    if (dtype == NTB200_I32 || dtype == NTB200_U32) {
+        add_inplace_i32_kernel<<<blocks, 256, 0, s>>>((unsigned int*)y, (const unsigned int*)x, n);
+    } else {
+        NTB200_FLOAT_SWITCH(dtype, (add_inplace_kernel<T><<<blocks, 256, 0, s>>>((T*)y, (const T*)x, n)));
+    }
+    count_launch();
+    NTB200_CUDA(cudaGetLastError());
+    return NTB200_OK;
+}
+
+int ntb200_copy_strided_2d(int dtype, void* dst, const void* src, int64_t batch, int64_t rows, int64_t cols,
+                           int64_t src_batch_stride, int64_t src_row_stride, int64_t src_col_stride, void* stream) {
+    if (batch < 0 || rows < 0 || cols < 0) return fail(NTB200_ERR_INVALID_ARG, "copy_strided_2d: negative size");
+    if (batch == 0 || rows == 0 || cols == 0) return NTB200_OK;
+    if (!dst || !src) return fail(NTB200_ERR_INVALID_ARG, "copy_strided_2d: null pointer");
+    if (batch > 65535 || (rows + 31) / 32 > 65535) return fail(NTB200_ERR_UNSUPPORTED, "copy_strided_2d: too many tiles");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const dim3 grid(unsigned((cols + 31) / 32), unsigned((rows + 31) / 32), unsigned(batch));
+    const dim3 block(32, 8);
+    switch (dtype_size(dtype)) {
+        case 1: copy_strided_kernel<uint8_t><<<grid, block, 0, s>>>((uint8_t*)dst, (const uint8_t*)src, rows, cols, src_batch_stride, src_row_stride, src_col_stride); break;
+        case 2: copy_strided_kernel<uint16_t><<<grid, block, 0, s>>>((uint16_t*)dst, (const uint16_t*)src, rows, cols, src_batch_stride, src_row_stride, src_col_stride); break;
+        case 4: copy_strided_kernel<uint32_t><<<grid, block, 0, s>>>((uint32_t*)dst, (const uint32_t*)src, rows, cols, src_batch_stride, src_row_stride, src_col_stride); break;
+        case 8: copy_strided_kernel<unsigned long long><<<grid, block, 0, s>>>((unsigned long long*)dst, (const unsigned long long*)src, rows, cols, src_batch_stride, src_row_stride, src_col_stride); break;
+        default: return fail(NTB200_ERR_UNSUPPORTED, "copy_strided_2d: unknown dtype %d", dtype);
+    }
+    count_launch();
+    NTB200_CUDA(cudaGetLastError());
+    return NTB200_OK;
+}
+
+int ntb200_convert(int dst_dtype, void* dst, int src_dtype, const void* src, int64_t n, void* stream) {
+    if (n < 0) return fail(NTB200_ERR_INVALID_ARG, "convert: negative size");
+    if (n == 0) return NTB200_OK;
+    if (!dst || !src) return fail(NTB200_ERR_INVALID_ARG, "convert: null pointer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int blocks = grid_for(n, 1024);
+#define NTB200_CVT(DT, ST, D, S) \
+    if (dst_dtype == DT && src_dtype == ST) { convert_kernel<D, S><<<blocks, 256, 0, s>>>((D*)dst, (const S*)src, n); } else
+    NTB200_CVT(NTB200_F32, NTB200_F16, float, __half)
+    NTB200_CVT(NTB200_F32, NTB200_BF16, float, __nv_bfloat16)
+    NTB200_CVT(NTB200_F16, NTB200_F32, __half, float)
+    NTB200_CVT(NTB200_BF16, NTB200_F32, __nv_bfloat16, float)
+    NTB200_CVT(NTB200_F16, NTB200_BF16, __half, __nv_bfloat16)
+    NTB200_CVT(NTB200_BF16, NTB200_F16, __nv_bfloat16, __half)
+    NTB200_CVT(NTB200_F32, NTB200_F32, float, float)
+    NTB200_CVT(NTB200_F16, NTB200_F16, __half, __half)
+    NTB200_CVT(NTB200_BF16, NTB200_BF16, __nv_bfloat16, __nv_bfloat16)
+    { return fail(NTB200_ERR_UNSUPPORTED, "convert: %s -> %s is not supported", dtype_name(src_dtype), dtype_name(dst_dtype)); }
+#undef NTB200_CVT
+    count_launch();
+    NTB200_CUDA(cudaGetLastError());
+    return NTB200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,421 @@
+// extern "C" surface of libntb200: argument validation in the order the reference performs it, routing
+// between the tcgen05 and CUDA-core GEMMs, the stream-ordered storage pool and the host-buffer variants.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <vector>
+
+#include "internal.h"
+
+namespace ntb200 {
+
+namespace {
+thread_local char t_error[512] = "";
+thread_local const char* t_route = "none";
+std::atomic<uint64_t> g_launches{0};
+std::atomic<uint64_t> g_pool_in_use{0}, g_pool_high{0};
+std::mutex g_pool_mu;
+struct Block { void* ptr; size_t bytes; };
+std::vector<Block> g_blocks;  // live pool allocations (for byte accounting)
+}  // namespace
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(t_error, sizeof(t_error), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int cuda_fail(cudaError_t err, const char* what) {
+    const int code = (err == cudaErrorNoDevice || err == cudaErrorInsufficientDriver) ? NTB200_ERR_NO_DEVICE
+                     : (err == cudaErrorMemoryAllocation)                              ? NTB200_ERR_ALLOC
+                                                                                       : NTB200_ERR_CUDA;
+    return fail(code, "%s: %s", what, cudaGetErrorString(err));
+}
+
+size_t dtype_size(int dtype) {
+    switch (dtype) {
+        case NTB200_F32: case NTB200_I32: case NTB200_U32: return 4;
+        case NTB200_F16: case NTB200_BF16: case NTB200_I16: case NTB200_U16: return 2;
+        case NTB200_I8: case NTB200_U8: return 1;
+        case NTB200_I64: case NTB200_F64: return 8;
+    }
+    return 0;
+}
+
+const char* dtype_name(int dtype) {
+    static const char* names[] = {"Float32", "Float16", "BFloat16", "int8", "int16", "int32",
+                                  "int64",   "Float64", "uint8",    "uint16", "uint32"};
+    return (dtype >= 0 && dtype <= NTB200_U32) ? names[dtype] : "unknown";
+}
+
+void count_launch(int n) { g_launches.fetch_add(uint64_t(n), std::memory_order_relaxed); }
+void note_route(const char* name) { t_route = name; }
+
+int sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+namespace {
+
+// Validation shared by every GEMM entry point, then routing.
+int run_gemm(GemmArgs g, int route, cudaStream_t stream) {
+    if (dtype_size(g.dtype) == 0) return fail(NTB200_ERR_UNSUPPORTED, "matmult: unknown dtype %d", g.dtype);
+    if (g.m < 0 || g.n < 0 || g.k < 0 || g.batch < 0) return fail(NTB200_ERR_INVALID_ARG, "matmult: negative extent");
+    if (g.m == 0 || g.n == 0 || g.batch == 0) return NTB200_OK;
+    const bool tables = g.a_ptrs || g.b_ptrs || g.c_ptrs;
+    if (tables && !(g.a_ptrs && g.b_ptrs && g.c_ptrs)) return fail(NTB200_ERR_INVALID_ARG, "matmult: incomplete pointer tables");
+    if (!tables && (!g.c || (g.k > 0 && (!g.a || !g.b)))) return fail(NTB200_ERR_INVALID_ARG, "matmult: null operand");
+    if (g.k == 0) {
+        if (g.accumulate && !g.bias) return NTB200_OK;  // C += 0
+        return launch_fill_c(g, stream);
+    }
+    if (route != NTB200_ROUTE_SIMT) {
+        const char* why = nullptr;
+        if (umma_supported(g, &why)) {
+            const int rc = launch_umma_gemm(g, stream);
+            if (rc != NTB200_ERR_UNSUPPORTED || route == NTB200_ROUTE_TENSOR) return rc;
+        } else if (route == NTB200_ROUTE_TENSOR) {
+            return fail(NTB200_ERR_UNSUPPORTED, "matmult: tcgen05 route refused (%s)", why ? why : "?");
+        }
+    }
+    return launch_simt_gemm(g, stream);
+}
+
+// The reference's raw-pointer contract (nt_matmult.h:6-10) as strides.
+GemmArgs raw_contract(int dtype, const void* A, const void* B, void* C, int64_t a_rows, int64_t a_cols, int64_t b_cols,
+                      bool ta, bool tb, int accumulate) {
+    GemmArgs g{};
+    g.dtype = dtype;
+    g.accumulate = accumulate;
+    g.f16_rounding = NTB200_F16_ROUND_ONCE;
+    g.m = a_rows; g.k = a_cols; g.n = b_cols; g.batch = 1;
+    g.a = A; g.a_rs = ta ? 1 : a_cols; g.a_cs = ta ? a_rows : 1; g.a_bs = a_rows * a_cols;
+    g.b = B; g.b_rs = tb ? 1 : b_cols; g.b_cs = tb ? a_cols : 1; g.b_bs = a_cols * b_cols;
+    g.c = C; g.c_rs = b_cols; g.c_bs = a_rows * b_cols;
+    return g;
+}
+
+int check_raw_dims(int64_t a_rows, int64_t a_cols, int64_t b_rows, int64_t b_cols) {
+    if (a_rows < 0 || a_cols < 0 || b_rows < 0 || b_cols < 0) return fail(NTB200_ERR_INVALID_ARG, "matmult: negative extent");
+    if (a_cols != b_rows)
+        return fail(NTB200_ERR_INVALID_ARG, "Expected second tensor rows to be %lld when it was %lld", (long long)a_cols,
+                    (long long)b_rows);
+    return NTB200_OK;
+}
+
+// ---- host-buffer pipeline ------------------------------------------------------------------------
+struct Lane {
+    cudaStream_t stream = nullptr;
+    void* buf[3] = {nullptr, nullptr, nullptr};
+    size_t cap[3] = {0, 0, 0};
+};
+constexpr int kLanes = 3;
+struct HostCtx {
+    Lane lanes[kLanes];
+    void* shared_b = nullptr;  // an operand every chunk reuses
+    size_t shared_cap = 0;
+};
+std::mutex g_host_mu;
+HostCtx g_host_ctx[64];
+
+int ensure(void** p, size_t* cap, size_t bytes) {
+    if (*cap >= bytes) return NTB200_OK;
+    if (*p) NTB200_CUDA(cudaFree(*p));
+    *p = nullptr; *cap = 0;
+    NTB200_CUDA(cudaMalloc(p, bytes));
+    *cap = bytes;
+    return NTB200_OK;
+}
+
+}  // namespace
+}  // namespace ntb200
+
+using namespace ntb200;
+
+extern "C" {
+
+const char* ntb200_version(void) { return "ntb200 0.1 (sm_100a)"; }
+const char* ntb200_last_error_string(void) { return t_error; }
+uint64_t ntb200_kernel_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+const char* ntb200_last_gemm_route(void) { return t_route; }
+
+int ntb200_device_count(int* count) {
+    if (!count) return fail(NTB200_ERR_INVALID_ARG, "device_count: null pointer");
+    *count = 0;
+    cudaError_t e = cudaGetDeviceCount(count);
+    if (e != cudaSuccess) { *count = 0; return cuda_fail(e, "cudaGetDeviceCount"); }
+    return NTB200_OK;
+}
+int ntb200_set_device(int device) { NTB200_CUDA(cudaSetDevice(device)); return NTB200_OK; }
+int ntb200_get_device(int* device) {
+    if (!device) return fail(NTB200_ERR_INVALID_ARG, "get_device: null pointer");
+    NTB200_CUDA(cudaGetDevice(device));
+    return NTB200_OK;
+}
+int ntb200_check_device_status(void* stream) { return read_device_status(static_cast<cudaStream_t>(stream)); }
+
+int ntb200_malloc_async(void** ptr, size_t bytes, void* stream) {
+    if (!ptr) return fail(NTB200_ERR_INVALID_ARG, "malloc_async: null pointer");
+    *ptr = nullptr;
+    if (bytes == 0) return NTB200_OK;
+    NTB200_CUDA(cudaMallocAsync(ptr, bytes, static_cast<cudaStream_t>(stream)));
+    {
+        std::lock_guard<std::mutex> lk(g_pool_mu);
+        g_blocks.push_back({*ptr, bytes});
+    }
+    const uint64_t now = g_pool_in_use.fetch_add(bytes) + bytes;
+    uint64_t hw = g_pool_high.load();
+    while (now > hw && !g_pool_high.compare_exchange_weak(hw, now)) {}
+    return NTB200_OK;
+}
+int ntb200_free_async(void* ptr, void* stream) {
+    if (!ptr) return NTB200_OK;
+    {
+        std::lock_guard<std::mutex> lk(g_pool_mu);
+        for (size_t i = 0; i < g_blocks.size(); ++i)
+            if (g_blocks[i].ptr == ptr) {
+                g_pool_in_use.fetch_sub(g_blocks[i].bytes);
+                g_blocks[i] = g_blocks.back();
+                g_blocks.pop_back();
+                break;
+            }
+    }
+    NTB200_CUDA(cudaFreeAsync(ptr, static_cast<cudaStream_t>(stream)));
+    return NTB200_OK;
+}
+int ntb200_pool_stats(uint64_t* bytes_in_use, uint64_t* high_water) {
+    if (bytes_in_use) *bytes_in_use = g_pool_in_use.load();
+    if (high_water) *high_water = g_pool_high.load();
+    return NTB200_OK;
+}
+int ntb200_memset_async(void* ptr, int value, size_t bytes, void* stream) {
+    if (bytes == 0) return NTB200_OK;
+    NTB200_CUDA(cudaMemsetAsync(ptr, value, bytes, static_cast<cudaStream_t>(stream)));
+    return NTB200_OK;
+}
+int ntb200_memcpy_h2d_async(void* dst, const void* src, size_t bytes, void* stream) {
+    if (bytes == 0) return NTB200_OK;
+    NTB200_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream)));
+    return NTB200_OK;
+}
+int ntb200_memcpy_d2h_async(void* dst, const void* src, size_t bytes, void* stream) {
+    if (bytes == 0) return NTB200_OK;
+    NTB200_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)));
+    return NTB200_OK;
+}
+int ntb200_memcpy_d2d_async(void* dst, const void* src, size_t bytes, void* stream) {
+    if (bytes == 0) return NTB200_OK;
+    NTB200_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream)));
+    return NTB200_OK;
+}
+int ntb200_stream_synchronize(void* stream) {
+    NTB200_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    return NTB200_OK;
+}
+
+int ntb200_gemm(const ntb200_gemm_desc* d, void* stream) {
+    if (!d) return fail(NTB200_ERR_INVALID_ARG, "gemm: null descriptor");
+    GemmArgs g{};
+    g.dtype = d->dtype; g.accumulate = d->accumulate ? 1 : 0; g.f16_rounding = d->f16_rounding;
+    g.m = d->m; g.n = d->n; g.k = d->k; g.batch = d->batch;
+    g.a = d->a; g.a_rs = d->a_row_stride; g.a_cs = d->a_col_stride; g.a_bs = d->a_batch_stride;
+    g.b = d->b; g.b_rs = d->b_row_stride; g.b_cs = d->b_col_stride; g.b_bs = d->b_batch_stride;
+    g.c = d->c; g.c_rs = d->c_row_stride; g.c_bs = d->c_batch_stride;
+    g.bias = d->bias; g.bias_rs = d->bias_row_stride; g.bias_cs = d->bias_col_stride; g.bias_bs = d->bias_batch_stride;
+    if (g.c_rs < g.n && g.m > 1) return fail(NTB200_ERR_INVALID_ARG, "gemm: C row stride %lld is smaller than n %lld", (long long)g.c_rs, (long long)g.n);
+    int route = d->route;
+    // per-K-tile fp16 rounding only exists on the CUDA-core route
+    if (g.dtype == NTB200_F16 && g.f16_rounding == NTB200_F16_ROUND_PER_KTILE) {
+        if (route == NTB200_ROUTE_TENSOR) return fail(NTB200_ERR_UNSUPPORTED, "gemm: per-K-tile fp16 rounding needs the CUDA-core route");
+        route = NTB200_ROUTE_SIMT;
+    }
+    return run_gemm(g, route, static_cast<cudaStream_t>(stream));
+}
+
+int ntb200_matmult(int dtype, const void* A, const void* B, void* C, int64_t a_rows, int64_t a_cols, int64_t b_rows,
+                   int64_t b_cols, int transpose_a, int transpose_b, void* stream) {
+    if (int rc = check_raw_dims(a_rows, a_cols, b_rows, b_cols)) return rc;
+    GemmArgs g = raw_contract(dtype, A, B, C, a_rows, a_cols, b_cols, transpose_a != 0, transpose_b != 0, 1);
+    return run_gemm(g, NTB200_ROUTE_AUTO, static_cast<cudaStream_t>(stream));
+}
+
+int ntb200_matmult_batch(int dtype, const void* const* A, const void* const* B, void* const* C, int64_t batches,
+                         int64_t a_rows, int64_t a_cols, int64_t b_rows, int64_t b_cols, int transpose_a,
+                         int transpose_b, void* stream) {
+    if (int rc = check_raw_dims(a_rows, a_cols, b_rows, b_cols)) return rc;
+    if (batches < 0) return fail(NTB200_ERR_INVALID_ARG, "matmult_batch: negative batch count");
+    if (batches == 0) return NTB200_OK;
+    if (!A || !B || !C) return fail(NTB200_ERR_INVALID_ARG, "matmult_batch: null pointer table");
+    const size_t es = dtype_size(dtype);
+    if (!es) return fail(NTB200_ERR_UNSUPPORTED, "matmult_batch: unknown dtype %d", dtype);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    GemmArgs g = raw_contract(dtype, A[0], B[0], C[0], a_rows, a_cols, b_cols, transpose_a != 0, transpose_b != 0, 1);
+    g.batch = batches;
+    // Equally spaced pointers (the common case: one tensor split along its batch axis) -> one strided launch.
+    auto spacing = [&](const void* const* p, int64_t* stride) {
+        if (batches == 1) { *stride = 0; return true; }
+        const ptrdiff_t d = static_cast<const char*>(p[1]) - static_cast<const char*>(p[0]);
+        if (d < 0 || d % ptrdiff_t(es)) return false;
+        for (int64_t i = 2; i < batches; ++i)
+            if (static_cast<const char*>(p[i]) - static_cast<const char*>(p[i - 1]) != d) return false;
+        *stride = d / ptrdiff_t(es);
+        return true;
+    };
+    int64_t sa, sb, sc;
+    if (spacing(A, &sa) && spacing(B, &sb) && spacing(reinterpret_cast<const void* const*>(C), &sc) &&
+        (batches == 1 || sc >= a_rows * b_cols)) {
+        g.a_bs = sa; g.b_bs = sb; g.c_bs = sc;
+        return run_gemm(g, NTB200_ROUTE_AUTO, s);
+    }
+    // Irregular pointers: device pointer tables, CUDA-core route.
+    void* table = nullptr;
+    const size_t tbytes = size_t(batches) * sizeof(void*);
+    NTB200_CUDA(cudaMallocAsync(&table, 3 * tbytes, s));
+    char* t = static_cast<char*>(table);
+    cudaError_t e = cudaMemcpyAsync(t, A, tbytes, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(t + tbytes, B, tbytes, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(t + 2 * tbytes, C, tbytes, cudaMemcpyHostToDevice, s);
+    if (e != cudaSuccess) { cudaFreeAsync(table, s); return cuda_fail(e, "pointer table upload"); }
+    // the host arrays may be reused by the caller as soon as we return
+    e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) { cudaFreeAsync(table, s); return cuda_fail(e, "pointer table upload"); }
+    g.a_ptrs = reinterpret_cast<const void* const*>(t);
+    g.b_ptrs = reinterpret_cast<const void* const*>(t + tbytes);
+    g.c_ptrs = reinterpret_cast<void* const*>(t + 2 * tbytes);
+    int rc = run_gemm(g, NTB200_ROUTE_SIMT, s);
+    cudaFreeAsync(table, s);
+    return rc;
+}
+
+int ntb200_matmult_host(int dtype, const void* A, const void* B, void* C, int64_t batches, int64_t a_rows,
+                        int64_t a_cols, int64_t b_rows, int64_t b_cols, int transpose_a, int transpose_b,
+                        int accumulate) {
+    if (int rc = check_raw_dims(a_rows, a_cols, b_rows, b_cols)) return rc;
+    if (batches < 0) return fail(NTB200_ERR_INVALID_ARG, "matmult_host: negative batch count");
+    accumulate = accumulate ? 1 : 0;
+    const size_t es = dtype_size(dtype);
+    if (!es) return fail(NTB200_ERR_UNSUPPORTED, "matmult_host: unknown dtype %d", dtype);
+    if (batches == 0 || a_rows == 0 || b_cols == 0) return NTB200_OK;
+    if (!A || !B || !C) return fail(NTB200_ERR_INVALID_ARG, "matmult_host: null pointer");
+    int dev = 0;
+    NTB200_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(NTB200_ERR_UNSUPPORTED, "matmult_host: device index out of range");
+    std::lock_guard<std::mutex> lk(g_host_mu);
+    HostCtx& ctx = g_host_ctx[dev];
+    for (auto& l : ctx.lanes)
+        if (!l.stream) NTB200_CUDA(cudaStreamCreateWithFlags(&l.stream, cudaStreamNonBlocking));
+
+    const size_t a_item = size_t(a_rows) * a_cols * es, b_item = size_t(a_cols) * b_cols * es,
+                 c_item = size_t(a_rows) * b_cols * es;
+    int rc = NTB200_OK;
+    if (batches > 1) {
+        // chunks of whole batch items; each lane: upload A,B,C -> multiply -> download C
+        const int64_t per = std::max<int64_t>(1, (batches + 7) / 8);
+        int lane_i = 0;
+        for (int64_t b0 = 0; b0 < batches && rc == NTB200_OK; b0 += per, lane_i = (lane_i + 1) % kLanes) {
+            const int64_t nb = std::min(per, batches - b0);
+            Lane& l = ctx.lanes[lane_i];
+            if ((rc = ensure(&l.buf[0], &l.cap[0], a_item * per))) break;
+            if ((rc = ensure(&l.buf[1], &l.cap[1], b_item * per))) break;
+            if ((rc = ensure(&l.buf[2], &l.cap[2], c_item * per))) break;
+            const char* ha = static_cast<const char*>(A) + b0 * a_item;
+            const char* hb = static_cast<const char*>(B) + b0 * b_item;
+            char* hc = static_cast<char*>(C) + b0 * c_item;
+            NTB200_CUDA(cudaMemcpyAsync(l.buf[0], ha, a_item * nb, cudaMemcpyHostToDevice, l.stream));
+            NTB200_CUDA(cudaMemcpyAsync(l.buf[1], hb, b_item * nb, cudaMemcpyHostToDevice, l.stream));
+            if (accumulate) NTB200_CUDA(cudaMemcpyAsync(l.buf[2], hc, c_item * nb, cudaMemcpyHostToDevice, l.stream));
+            GemmArgs g = raw_contract(dtype, l.buf[0], l.buf[1], l.buf[2], a_rows, a_cols, b_cols, transpose_a != 0,
+                                      transpose_b != 0, accumulate);
+            g.batch = nb;
+            rc = run_gemm(g, NTB200_ROUTE_AUTO, l.stream);
+            if (rc) break;
+            NTB200_CUDA(cudaMemcpyAsync(hc, l.buf[2], c_item * nb, cudaMemcpyDeviceToHost, l.stream));
+        }
+    } else {
+        // one matrix: B is uploaded once; A and C travel in row slabs when A's rows are contiguous
+        if ((rc = ensure(&ctx.shared_b, &ctx.shared_cap, b_item))) return rc;
+        cudaStream_t s0 = ctx.lanes[0].stream;
+        NTB200_CUDA(cudaMemcpyAsync(ctx.shared_b, B, b_item, cudaMemcpyHostToDevice, s0));
+        NTB200_CUDA(cudaStreamSynchronize(s0));
+        const bool slab = !transpose_a && a_rows >= 1024;
+        const int64_t rows_per = slab ? ((a_rows + 7) / 8 + 127) / 128 * 128 : a_rows;
+        int lane_i = 0;
+        for (int64_t r0 = 0; r0 < a_rows && rc == NTB200_OK; r0 += rows_per, lane_i = (lane_i + 1) % kLanes) {
+            const int64_t nr = std::min(rows_per, a_rows - r0);
+            Lane& l = ctx.lanes[lane_i];
+            if ((rc = ensure(&l.buf[0], &l.cap[0], size_t(rows_per) * a_cols * es))) break;
+            if ((rc = ensure(&l.buf[2], &l.cap[2], size_t(rows_per) * b_cols * es))) break;
+            const char* ha = static_cast<const char*>(A) + size_t(r0) * a_cols * es;
+            char* hc = static_cast<char*>(C) + size_t(r0) * b_cols * es;
+            NTB200_CUDA(cudaMemcpyAsync(l.buf[0], ha, size_t(nr) * a_cols * es, cudaMemcpyHostToDevice, l.stream));
+            if (accumulate)
+                NTB200_CUDA(cudaMemcpyAsync(l.buf[2], hc, size_t(nr) * b_cols * es, cudaMemcpyHostToDevice, l.stream));
+            GemmArgs g = raw_contract(dtype, l.buf[0], ctx.shared_b, l.buf[2], nr, a_cols, b_cols, transpose_a != 0,
+                                      transpose_b != 0, accumulate);
+            rc = run_gemm(g, NTB200_ROUTE_AUTO, l.stream);
+            if (rc) break;
+            NTB200_CUDA(cudaMemcpyAsync(hc, l.buf[2], size_t(nr) * b_cols * es, cudaMemcpyDeviceToHost, l.stream));
+        }
+    }
+    for (auto& l : ctx.lanes) {
+        cudaError_t e = cudaStreamSynchronize(l.stream);
+        if (e != cudaSuccess && rc == NTB200_OK) rc = cuda_fail(e, "matmult_host: stream synchronize");
+    }
+    return rc;
+}
+
+size_t ntb200_conv2d_workspace_bytes(int dtype, int64_t batch, int64_t channels, int64_t height, int64_t width,
+                                     int64_t kh, int64_t kw, int64_t sh, int64_t sw, int64_t ph, int64_t pw,
+                                     int64_t dh, int64_t dw) {
+    if (sh < 1 || sw < 1) return 0;
+    const int64_t hc = (height + 2 * ph - dh * (kh - 1) - 1) / sh + 1;
+    const int64_t wc = (width + 2 * pw - dw * (kw - 1) - 1) / sw + 1;
+    if (hc <= 0 || wc <= 0 || batch <= 0 || channels <= 0) return 0;
+    const int64_t L = hc * wc;
+    return size_t(batch) * size_t(channels * kh * kw) * size_t(L) * dtype_size(dtype);
+}
+
+int ntb200_conv2d(int dtype, const void* x, const void* w, void* out, void* workspace, int64_t batch, int64_t channels,
+                  int64_t height, int64_t width, int64_t cout, int64_t kh, int64_t kw, int64_t sh, int64_t sw,
+                  int64_t ph, int64_t pw, int64_t dh, int64_t dw, void* stream) {
+    if (dtype_size(dtype) == 0) return fail(NTB200_ERR_UNSUPPORTED, "conv2d: unknown dtype %d", dtype);
+    if (sh < 1 || sw < 1) return fail(NTB200_ERR_INVALID_ARG, "Conv2d stride cannot be less than 1");
+    if (dh < 1 || dw < 1) return fail(NTB200_ERR_INVALID_ARG, "Conv2d dilation cannot be less than 1");
+    if (ph < 0 || pw < 0) return fail(NTB200_ERR_INVALID_ARG, "Conv2d padding cannot be less than 0");
+    if (batch < 0 || channels <= 0 || cout <= 0 || height <= 0 || width <= 0 || kh <= 0 || kw <= 0)
+        return fail(NTB200_ERR_INVALID_ARG, "conv2d: bad extent");
+    const int64_t hc = (height + 2 * ph - dh * (kh - 1) - 1) / sh + 1;
+    const int64_t wc = (width + 2 * pw - dw * (kw - 1) - 1) / sw + 1;
+    if (hc <= 0 || wc <= 0) return fail(NTB200_ERR_INVALID_ARG, "conv2d: calculated output size (%lld, %lld) must be at least one", (long long)hc, (long long)wc);
+    if (batch == 0) return NTB200_OK;
+    if (!x || !w || !out || !workspace) return fail(NTB200_ERR_INVALID_ARG, "conv2d: null pointer");
+    const int64_t L = hc * wc, ck = channels * kh * kw;
+    // The column matrix is written densely ([B][ck][L]); out[b] (cout x L) = w2d (cout x ck) . col[b] (ck x L),
+    // which is the reference's matmult(col, w2d, true, true) followed by its row/col swap, with the same
+    // ascending-ck order for every output element.
+    int rc = ntb200_im2col(dtype, x, workspace, batch, channels, height, width, kh, kw, sh, sw, ph, pw, dh, dw, stream);
+    if (rc) return rc;
+    GemmArgs g{};
+    g.dtype = dtype; g.accumulate = 0; g.f16_rounding = NTB200_F16_ROUND_ONCE;
+    g.m = cout; g.n = L; g.k = ck; g.batch = batch;
+    g.a = w; g.a_rs = ck; g.a_cs = 1; g.a_bs = 0;
+    g.b = workspace; g.b_rs = L; g.b_cs = 1; g.b_bs = ck * L;
+    g.c = out; g.c_rs = L; g.c_bs = cout * L;
+    return run_gemm(g, NTB200_ROUTE_AUTO, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,556 @@
+// tcgen05 GEMM for Float16 / BFloat16 (fp32 accumulate in tensor memory) and Int8 / UInt8 (s32 accumulate,
+// truncated to 8 bits, i.e. arithmetic mod 2^8).  Replaces the packed simde/TBB kernels of
+// nt/functional/cpu/matmult/nt_matmult.hpp:124-235 for those dtypes.
+//
+// One persistent CTA per SM, 192 threads:
+//   warp 0      TMA producer   - one lane issues cp.async.bulk.tensor loads of the A and B tiles of a K block
+//                                into a ring of shared-memory stages (128-byte swizzle), signalling `full`
+//   warp 1      MMA issuer     - allocates tensor memory; one lane issues tcgen05.mma per 32 bytes of K,
+//                                tcgen05.commit releases the stage (`empty`) and, after the last K block,
+//                                publishes the accumulator (`tmem_full`)
+//   warps 2..5  epilogue       - tcgen05.ld the 128 x BN accumulator (each warp owns a 32-lane quadrant),
+//                                add bias / previous C, convert, store; then hand the accumulator back
+// Two accumulators (2 x BN columns of TMEM) let the epilogue of tile i overlap the main loop of tile i+1.
+//
+// Transposed and strided views never get copied: an operand whose unit stride runs along K is staged
+// K-major, one whose unit stride runs along M (or N) is staged MN-major in 128-byte-wide chunks; the
+// difference is carried by the TMA tensor map, the shared-memory descriptor and one bit of the
+// instruction descriptor.  Tails in M, N and K are zero-filled by TMA and masked at the store.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <mutex>
+
+#include "internal.h"
+#include "sm100_ptx.cuh"
+
+namespace ntb200 {
+
+// Raised (never cleared by kernels) when a bounded wait ran out.  Low byte = which wait.
+__device__ unsigned int g_device_status = 0;
+
+namespace {
+
+constexpr int kBM = 128;
+constexpr int kThreads = 192;
+constexpr int kTmemCols = 512;
+
+enum OutKind : int { kOutF16 = 0, kOutBF16 = 1, kOutI8 = 2 };
+
+struct UmmaParams {
+    int m, n, k, batch;
+    int tiles_m, tiles_n, k_blocks, group_m;
+    int total_tiles;
+    int block_k;             // elements per K block (128 bytes of K)
+    uint32_t idesc;
+    int a_mn_major, b_mn_major;
+    int a_chunks, b_chunks;  // TMA loads per stage for an MN-major operand
+    int chunk_mn;            // MN extent of one such load (128 bytes)
+    uint32_t chunk_bytes;    // block_k * 128
+    uint32_t a_lbo, b_lbo;   // leading byte offset of the shared-memory descriptor
+    uint32_t a_kstep, b_kstep;  // start-address increment (16-byte units) per 32 bytes of K
+    int a_batch_mul, b_batch_mul;  // 0 when the operand is shared by the whole batch
+    void* c;
+    long long c_rs, c_bs;
+    const void* bias;
+    long long bias_rs, bias_cs, bias_bs;
+    int accumulate, out_kind, c_vec_ok;
+};
+
+template <int BN>
+struct Tile {
+    static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+    static constexpr uint32_t kABytes = kBM * 128;
+    static constexpr uint32_t kBBytes = BN * 128;
+    static constexpr uint32_t kStageBytes = kABytes + kBBytes;
+    static constexpr uint32_t kBarrierBytes = 256;
+    static constexpr uint32_t kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;
+};
+
+__device__ __forceinline__ void raise_timeout(volatile uint32_t* abort_flag, unsigned int where) {
+    *abort_flag = 1;
+    atomicExch(&g_device_status, 0x100u | where);
+}
+
+__device__ __forceinline__ void tile_coords(const UmmaParams& p, int t, int& b, int& mi, int& ni) {
+    const int per_batch = p.tiles_m * p.tiles_n;
+    b = t / per_batch;
+    const int r = t - b * per_batch;
+    const int group = p.group_m * p.tiles_n;
+    const int g = r / group;
+    const int first_m = g * p.group_m;
+    const int gm = min(p.group_m, p.tiles_m - first_m);
+    const int w = r - g * group;
+    mi = first_m + w % gm;
+    ni = w / gm;
+}
+
+__device__ __forceinline__ float to_float_bits16(uint32_t bits, int out_kind) {
+    return out_kind == kOutF16 ? __half2float(__ushort_as_half((unsigned short)bits))
+                               : __bfloat162float(__ushort_as_bfloat16((unsigned short)bits));
+}
+__device__ __forceinline__ uint32_t from_float_bits16(float v, int out_kind) {
+    return out_kind == kOutF16 ? (uint32_t)__half_as_ushort(__float2half_rn(v))
+                               : (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v));
+}
+
+template <MmaKind kKind, int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                 const UmmaParams p) {
+    using T = Tile<BN>;
+    constexpr int kStages = T::kStages;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    uint8_t* bar_gen = smem_gen + kStages * T::kStageBytes;
+    const uint32_t bar_base = smem_base + kStages * T::kStageBytes;
+    // barrier layout (8 bytes each): full[kStages], empty[kStages], tmem_full[2], tmem_empty[2]
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+    auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
+    auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_gen + 8 * (2 * kStages + 4));
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(tfull_bar(a), 1);
+            mbar_init(tempty_bar(a), 4);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+        fence_proxy_async_smem();
+        tma_prefetch_desc(&tma_a);
+        tma_prefetch_desc(&tma_b);
+    }
+    if (warp == 1) {
+        tmem_alloc<1>(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
+        tmem_relinquish<1>();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x) {
+                int b, mi, ni;
+                tile_coords(p, t, b, mi, ni);
+                const int m0 = mi * kBM, n0 = ni * BN;
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
+                        raise_timeout(abort_flag, 1);
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t a_dst = smem_base + stage * T::kStageBytes;
+                    const uint32_t b_dst = a_dst + T::kABytes;
+                    const uint32_t bar = full_bar(stage);
+                    mbar_expect_tx(bar, T::kStageBytes);
+                    const int k0 = kb * p.block_k;
+                    if (!p.a_mn_major) {
+                        tma_load_3d(a_dst, &tma_a, bar, k0, m0, b * p.a_batch_mul);
+                    } else {
+                        for (int c = 0; c < p.a_chunks; ++c)
+                            tma_load_3d(a_dst + c * p.chunk_bytes, &tma_a, bar, m0 + c * p.chunk_mn, k0,
+                                        b * p.a_batch_mul);
+                    }
+                    if (!p.b_mn_major) {
+                        tma_load_3d(b_dst, &tma_b, bar, k0, n0, b * p.b_batch_mul);
+                    } else {
+                        for (int c = 0; c < p.b_chunks; ++c)
+                            tma_load_3d(b_dst + c * p.chunk_bytes, &tma_b, bar, n0 + c * p.chunk_mn, k0,
+                                        b * p.b_batch_mul);
+                    }
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                }
+            }
+            // Leave no copy in flight behind us: wait (bounded) until the consumer has released every stage,
+            // which implies every load issued above has landed.
+            if (ok) {
+                for (int s = 0; s < kStages; ++s) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { raise_timeout(abort_flag, 2); break; }
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x) {
+                if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
+                    raise_timeout(abort_flag, 3);
+                    break;
+                }
+                tcgen05_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
+                        raise_timeout(abort_flag, 4);
+                        ok = false;
+                        break;
+                    }
+                    tcgen05_fence_after();
+                    const uint32_t a_addr = smem_base + stage * T::kStageBytes;
+                    const uint64_t a_desc = make_smem_desc_sw128(a_addr, p.a_lbo, 1024);
+                    const uint64_t b_desc = make_smem_desc_sw128(a_addr + T::kABytes, p.b_lbo, 1024);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        umma<kKind, 1>(d_tmem, a_desc + uint64_t(k * p.a_kstep), b_desc + uint64_t(k * p.b_kstep),
+                                       p.idesc, (kb | k) != 0);
+                    umma_commit<1>(empty_bar(stage));  // stage is free once these MMAs have read it
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                umma_commit<1>(tfull_bar(acc));        // accumulator complete
+                if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue
+        const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+        const int row_in_tile = quad * 32 + lane;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        const int es = (p.out_kind == kOutI8) ? 1 : 2;
+        for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x) {
+            int b, mi, ni;
+            tile_coords(p, t, b, mi, ni);
+            bool ok = mbar_wait(tfull_bar(acc), acc_phase, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) {
+                if (lane == 0) raise_timeout(abort_flag, 5);
+                break;
+            }
+            tcgen05_fence_after();
+            const int row = mi * kBM + row_in_tile;
+            const bool row_ok = row < p.m;
+            uint8_t* c_row = static_cast<uint8_t*>(p.c) + ((long long)b * p.c_bs + (long long)row * p.c_rs) * es;
+#pragma unroll 1
+            for (int cc = 0; cc < BN / 32; ++cc) {
+                const int col0 = ni * BN + cc * 32;
+                if (col0 >= p.n) break;  // uniform across the CTA
+                uint32_t v[32];
+                tmem_ld_32x32b_x32(tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN + cc * 32), v);
+                tmem_ld_wait();
+                if (!row_ok) continue;
+                const bool full_chunk = (col0 + 32 <= p.n);
+                if (p.out_kind == kOutI8) {
+                    // s32 accumulators; keep the low 8 bits (wrap), adding bias / previous C first
+                    if (p.bias) {
+                        const int8_t* bias = static_cast<const int8_t*>(p.bias) + (long long)b * p.bias_bs +
+                                             (long long)row * p.bias_rs;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col0 + j < p.n) v[j] += (uint32_t)(int)bias[(long long)(col0 + j) * p.bias_cs];
+                    }
+                    uint8_t* dst = c_row + col0;
+                    if (full_chunk && p.c_vec_ok) {
+                        uint32_t packed[8];
+                        if (p.accumulate) {
+                            const uint4 o0 = *reinterpret_cast<const uint4*>(dst);
+                            const uint4 o1 = *reinterpret_cast<const uint4*>(dst + 16);
+                            const uint32_t old[8] = {o0.x, o0.y, o0.z, o0.w, o1.x, o1.y, o1.z, o1.w};
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] += (old[j >> 2] >> (8 * (j & 3))) & 0xffu;
+                        }
+#pragma unroll
+                        for (int q = 0; q < 8; ++q)
+                            packed[q] = (v[4 * q] & 0xffu) | ((v[4 * q + 1] & 0xffu) << 8) |
+                                        ((v[4 * q + 2] & 0xffu) << 16) | ((v[4 * q + 3] & 0xffu) << 24);
+                        *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                        *reinterpret_cast<uint4*>(dst + 16) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col0 + j < p.n) {
+                                uint32_t x = v[j];
+                                if (p.accumulate) x += dst[j];
+                                dst[j] = (uint8_t)x;
+                            }
+                    }
+                } else {
+                    float f[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+                    if (p.bias) {
+                        const uint16_t* bias = static_cast<const uint16_t*>(p.bias) + (long long)b * p.bias_bs +
+                                               (long long)row * p.bias_rs;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col0 + j < p.n) f[j] += to_float_bits16(bias[(long long)(col0 + j) * p.bias_cs], p.out_kind);
+                    }
+                    uint16_t* dst = reinterpret_cast<uint16_t*>(c_row) + col0;
+                    if (full_chunk && p.c_vec_ok) {
+                        if (p.accumulate) {
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                const uint4 o = *reinterpret_cast<const uint4*>(dst + 8 * q);
+                                const uint32_t w[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    f[8 * q + 2 * j] += to_float_bits16(w[j] & 0xffffu, p.out_kind);
+                                    f[8 * q + 2 * j + 1] += to_float_bits16(w[j] >> 16, p.out_kind);
+                                }
+                            }
+                        }
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                w[j] = from_float_bits16(f[8 * q + 2 * j], p.out_kind) |
+                                       (from_float_bits16(f[8 * q + 2 * j + 1], p.out_kind) << 16);
+                            *reinterpret_cast<uint4*>(dst + 8 * q) = make_uint4(w[0], w[1], w[2], w[3]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col0 + j < p.n) {
+                                float x = f[j];
+                                if (p.accumulate) x += to_float_bits16(dst[j], p.out_kind);
+                                dst[j] = (uint16_t)from_float_bits16(x, p.out_kind);
+                            }
+                    }
+                }
+            }
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(acc));
+            if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tmem_dealloc<1>(tmem_base, kTmemCols);
+    }
+}
+
+// ---- host side ---------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+struct OperandPlan {
+    bool mn_major = false;
+    int batch_mul = 1;
+    CUtensorMap map;
+};
+
+inline uint64_t round16(uint64_t v) { return (v + 15u) & ~uint64_t(15); }
+
+// An operand is logically [mn_extent, k_extent] with element strides (mn_stride, k_stride) and a batch stride.
+// Returns nullptr on success, else the reason the operand cannot be staged by TMA.
+const char* plan_operand(const void* ptr, int es, CUtensorMapDataType dt, int64_t mn, int64_t k, int64_t mn_stride,
+                         int64_t k_stride, int64_t batch, int64_t batch_stride, int tile_mn, int block_k,
+                         OperandPlan* out) {
+    if (reinterpret_cast<uintptr_t>(ptr) % 16) return "operand base is not 16-byte aligned";
+    if (mn_stride < 0 || k_stride < 0 || batch_stride < 0) return "negative stride";
+    const bool k_unit = (k_stride == 1 || k == 1);
+    const bool mn_unit = (mn_stride == 1 || mn == 1);
+    auto aligned = [&](int64_t stride) { return (stride * es) % 16 == 0; };
+    bool k_major_ok = k_unit && (mn == 1 || aligned(mn_stride));
+    bool mn_major_ok = mn_unit && (k == 1 || aligned(k_stride));
+    if (!k_major_ok && !mn_major_ok) return "no unit stride with a 16-byte aligned other stride";
+    if (batch > 1 && batch_stride != 0 && !aligned(batch_stride)) return "batch stride is not 16-byte aligned";
+    out->mn_major = !k_major_ok;
+    const bool batched = batch > 1 && batch_stride != 0;
+    out->batch_mul = batched ? 1 : 0;
+    const int64_t inner = out->mn_major ? mn : k;
+    const int64_t outer = out->mn_major ? k : mn;
+    int64_t outer_stride = out->mn_major ? k_stride : mn_stride;
+    if (outer == 1) outer_stride = int64_t(round16(uint64_t(inner) * es)) / es;
+    if (inner > (int64_t(1) << 31) || outer > (int64_t(1) << 31)) return "extent too large for a tensor map";
+    cuuint64_t dims[3] = {cuuint64_t(inner), cuuint64_t(outer), cuuint64_t(batched ? batch : 1)};
+    cuuint64_t strides[2] = {cuuint64_t(outer_stride) * es,
+                             batched ? cuuint64_t(batch_stride) * es
+                                     : round16(cuuint64_t(outer_stride) * es * cuuint64_t(outer))};
+    if (strides[0] % 16 || strides[1] % 16) return "stride is not 16-byte aligned";
+    if (strides[0] >= (cuuint64_t(1) << 40) || strides[1] >= (cuuint64_t(1) << 40)) return "stride too large";
+    cuuint32_t box[3];
+    if (out->mn_major) {
+        box[0] = cuuint32_t(128 / es);
+        box[1] = cuuint32_t(block_k);
+    } else {
+        box[0] = cuuint32_t(block_k);
+        box[1] = cuuint32_t(tile_mn);
+    }
+    box[2] = 1;
+    cuuint32_t elem_strides[3] = {1, 1, 1};
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return "cuTensorMapEncodeTiled is not available from the driver";
+    CUresult r = enc(&out->map, dt, 3, const_cast<void*>(ptr), dims, strides, box, elem_strides,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return "cuTensorMapEncodeTiled rejected the operand";
+    return nullptr;
+}
+
+bool dtype_on_tensor_cores(int dtype) {
+    return dtype == NTB200_F16 || dtype == NTB200_BF16 || dtype == NTB200_I8 || dtype == NTB200_U8;
+}
+
+// Cheap structural test (no driver call): can both operands be staged?
+const char* operands_stageable(const GemmArgs& g) {
+    if (!dtype_on_tensor_cores(g.dtype)) return "dtype has no tensor-core kernel";
+    if (g.a_ptrs || g.b_ptrs || g.c_ptrs) return "pointer-table batches run on the CUDA-core route";
+    if (g.m <= 0 || g.n <= 0 || g.k <= 0 || g.batch <= 0) return "empty problem";
+    const int es = int(dtype_size(g.dtype));
+    // s32 accumulation is exact (no overflow) while k * 2^14 < 2^31
+    if (es == 1 && g.k > 131071) return "int8 K too large for exact s32 accumulation";
+    if (g.m > (int64_t(1) << 30) || g.n > (int64_t(1) << 30) || g.k > (int64_t(1) << 30)) return "extent too large";
+    auto check = [&](const void* ptr, int64_t mn, int64_t k, int64_t mn_s, int64_t k_s, int64_t bs) -> const char* {
+        if (reinterpret_cast<uintptr_t>(ptr) % 16) return "operand base is not 16-byte aligned";
+        if (mn_s < 0 || k_s < 0 || bs < 0) return "negative stride";
+        const bool k_major_ok = (k_s == 1 || k == 1) && (mn == 1 || (mn_s * es) % 16 == 0);
+        const bool mn_major_ok = (mn_s == 1 || mn == 1) && (k == 1 || (k_s * es) % 16 == 0);
+        if (!k_major_ok && !mn_major_ok) return "no unit stride with a 16-byte aligned other stride";
+        if (g.batch > 1 && bs != 0 && (bs * es) % 16) return "batch stride is not 16-byte aligned";
+        return nullptr;
+    };
+    if (const char* w = check(g.a, g.m, g.k, g.a_rs, g.a_cs, g.a_bs)) return w;
+    if (const char* w = check(g.b, g.n, g.k, g.b_cs, g.b_rs, g.b_bs)) return w;
+    const int64_t tiles = ((g.m + kBM - 1) / kBM) * ((g.n + 63) / 64) * g.batch;
+    if (tiles > (int64_t(1) << 30)) return "too many tiles";
+    return nullptr;
+}
+
+template <MmaKind kKind, int BN>
+int launch_instance(const OperandPlan& pa, const OperandPlan& pb, const UmmaParams& p, int grid, cudaStream_t stream) {
+    using T = Tile<BN>;
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    // the attribute is per device; set it on every call (cheap) rather than caching per device
+    attr_err = cudaFuncSetAttribute(umma_gemm_kernel<kKind, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    int(T::kSmemBytes));
+    (void)once;
+    if (attr_err != cudaSuccess) return cuda_fail(attr_err, "cudaFuncSetAttribute(umma_gemm_kernel)");
+    umma_gemm_kernel<kKind, BN><<<grid, kThreads, T::kSmemBytes, stream>>>(pa.map, pb.map, p);
+    count_launch();
+    NTB200_CUDA(cudaGetLastError());
+    return NTB200_OK;
+}
+
+}  // namespace
+
+bool umma_supported(const GemmArgs& g, const char** why) {
+    const char* w = operands_stageable(g);
+    if (why) *why = w;
+    return w == nullptr;
+}
+
+int launch_umma_gemm(const GemmArgs& g, cudaStream_t stream) {
+    if (const char* w = operands_stageable(g)) return fail(NTB200_ERR_UNSUPPORTED, "tcgen05 route: %s", w);
+    const int es = int(dtype_size(g.dtype));
+    const bool is_i8 = es == 1;
+    const int block_k = 128 / es;
+    const CUtensorMapDataType dt = g.dtype == NTB200_F16    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                   : g.dtype == NTB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                            : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    // Tile width: the widest one that still gives every SM a tile.
+    const int sms = sm_count();
+    const int64_t tiles_m = (g.m + kBM - 1) / kBM;
+    int bn = 64;
+    for (int cand : {256, 128, 64}) {
+        bn = cand;
+        if (g.n > cand / 2 && tiles_m * ((g.n + cand - 1) / cand) * g.batch >= sms) break;
+    }
+    if (g.n <= 64) bn = 64;
+    else if (g.n <= 128 && bn > 128) bn = 128;
+
+    OperandPlan pa, pb;
+    if (const char* w = plan_operand(g.a, es, dt, g.m, g.k, g.a_rs, g.a_cs, g.batch, g.a_bs, kBM, block_k, &pa))
+        return fail(NTB200_ERR_UNSUPPORTED, "tcgen05 route, A: %s", w);
+    if (const char* w = plan_operand(g.b, es, dt, g.n, g.k, g.b_cs, g.b_rs, g.batch, g.b_bs, bn, block_k, &pb))
+        return fail(NTB200_ERR_UNSUPPORTED, "tcgen05 route, B: %s", w);
+
+    UmmaParams p{};
+    p.m = int(g.m); p.n = int(g.n); p.k = int(g.k); p.batch = int(g.batch);
+    p.tiles_m = int(tiles_m);
+    p.tiles_n = int((g.n + bn - 1) / bn);
+    p.k_blocks = int((g.k + block_k - 1) / block_k);
+    p.group_m = 8;
+    p.total_tiles = int(int64_t(p.tiles_m) * p.tiles_n * g.batch);
+    p.block_k = block_k;
+    const uint32_t in_fmt = g.dtype == NTB200_BF16 ? 1u : (g.dtype == NTB200_I8 ? 1u : 0u);
+    p.idesc = make_instr_desc(is_i8 ? 2u : 1u, in_fmt, in_fmt, pa.mn_major, pb.mn_major, kBM, uint32_t(bn));
+    p.a_mn_major = pa.mn_major; p.b_mn_major = pb.mn_major;
+    p.chunk_mn = 128 / es;
+    p.chunk_bytes = uint32_t(block_k) * 128u;
+    p.a_chunks = kBM / p.chunk_mn;
+    p.b_chunks = bn / p.chunk_mn;
+    // K-major: rows are 128 bytes, 8-row groups 1024 bytes apart, +32 bytes per MMA along K.
+    // MN-major: each K row of a chunk is 128 bytes of MN, 8-row groups 1024 bytes apart (SBO), chunks
+    // `chunk_bytes` apart (LBO), and one MMA consumes 32/es K rows.
+    p.a_lbo = pa.mn_major ? p.chunk_bytes : 16u;
+    p.b_lbo = pb.mn_major ? p.chunk_bytes : 16u;
+    const uint32_t mn_kstep = uint32_t(32 / es) * 128u / 16u;
+    p.a_kstep = pa.mn_major ? mn_kstep : 2u;
+    p.b_kstep = pb.mn_major ? mn_kstep : 2u;
+    p.a_batch_mul = pa.batch_mul; p.b_batch_mul = pb.batch_mul;
+    p.c = g.c; p.c_rs = g.c_rs; p.c_bs = g.c_bs;
+    p.bias = g.bias; p.bias_rs = g.bias_rs; p.bias_cs = g.bias_cs; p.bias_bs = g.bias_bs;
+    p.accumulate = g.accumulate;
+    p.out_kind = is_i8 ? kOutI8 : (g.dtype == NTB200_F16 ? kOutF16 : kOutBF16);
+    p.c_vec_ok = (reinterpret_cast<uintptr_t>(g.c) % 16 == 0) && ((g.c_rs * es) % 16 == 0) &&
+                 (g.batch == 1 || (g.c_bs * es) % 16 == 0);
+    const int grid = int(std::min<int64_t>(p.total_tiles, sms));
+    note_route(is_i8 ? "umma_i8" : (g.dtype == NTB200_F16 ? "umma_f16" : "umma_bf16"));
+    if (is_i8) {
+        if (bn == 256) return launch_instance<MmaKind::i8, 256>(pa, pb, p, grid, stream);
+        if (bn == 128) return launch_instance<MmaKind::i8, 128>(pa, pb, p, grid, stream);
+        return launch_instance<MmaKind::i8, 64>(pa, pb, p, grid, stream);
+    }
+    if (bn == 256) return launch_instance<MmaKind::f16, 256>(pa, pb, p, grid, stream);
+    if (bn == 128) return launch_instance<MmaKind::f16, 128>(pa, pb, p, grid, stream);
+    return launch_instance<MmaKind::f16, 64>(pa, pb, p, grid, stream);
+}
+
+int read_device_status(cudaStream_t stream) {
+    NTB200_CUDA(cudaStreamSynchronize(stream));
+    unsigned int st = 0;
+    NTB200_CUDA(cudaMemcpyFromSymbol(&st, g_device_status, sizeof(st)));
+    if (st) {
+        unsigned int zero = 0;
+        NTB200_CUDA(cudaMemcpyToSymbol(g_device_status, &zero, sizeof(zero)));
+        return fail(NTB200_ERR_TIMEOUT, "a device-side wait ran out (code 0x%x)", st);
+    }
+    return NTB200_OK;
+}
+
+}  // namespace ntb200

@@ -1,0 +1,55 @@
+// Internal declarations shared by the translation units of libntb200.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdint>
+
+#include "../../include/ntb200.h"
+
+namespace ntb200 {
+
+// Error text of the calling thread; returns `code` so call sites can `return fail(...)`.
+int fail(int code, const char* fmt, ...) __attribute__((format(printf, 2, 3)));
+int cuda_fail(cudaError_t err, const char* what);
+#define NTB200_CUDA(expr)                                            \
+    do {                                                             \
+        cudaError_t e__ = (expr);                                    \
+        if (e__ != cudaSuccess) return ::ntb200::cuda_fail(e__, #expr); \
+    } while (0)
+
+size_t dtype_size(int dtype);
+const char* dtype_name(int dtype);
+void count_launch(int n = 1);
+void note_route(const char* name);
+int sm_count();  // multiprocessors of the current device (cached per device)
+
+// A GEMM after validation: C[b] = (accumulate ? C[b] : 0) + bias + A[b].B[b]; strides in elements.
+struct GemmArgs {
+    int dtype;
+    int accumulate;
+    int f16_rounding;
+    int64_t m, n, k, batch;
+    const void* a; int64_t a_rs, a_cs, a_bs;
+    const void* b; int64_t b_rs, b_cs, b_bs;
+    void* c; int64_t c_rs, c_bs;
+    const void* bias; int64_t bias_rs, bias_cs, bias_bs;
+    // optional device pointer tables (batch entries each); when set they replace a/b/c + batch strides
+    const void* const* a_ptrs = nullptr;
+    const void* const* b_ptrs = nullptr;
+    void* const* c_ptrs = nullptr;
+};
+
+// tcgen05 route.  Returns NTB200_ERR_UNSUPPORTED (without touching the error text) when the operands
+// cannot be expressed as TMA tensor maps, so the caller can route elsewhere.
+bool umma_supported(const GemmArgs& g, const char** why);
+int launch_umma_gemm(const GemmArgs& g, cudaStream_t stream);
+int read_device_status(cudaStream_t stream);
+
+// CUDA-core route: every dtype, every stride pattern.
+int launch_simt_gemm(const GemmArgs& g, cudaStream_t stream);
+
+// K == 0 or pure bias/zero fill of C.
+int launch_fill_c(const GemmArgs& g, cudaStream_t stream);
+
+}  // namespace ntb200

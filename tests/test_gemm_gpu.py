@@ -1,0 +1,245 @@
+"""GPU parity of matmult against the CPU oracle, through the C ABI (ctypes -> libntb200.so).
+
+Bars: integers bit-exact; Float32 bit-exact on the CUDA-core route (one ascending-k FMA chain, like the
+reference) and in any case within 1e-5 relative Frobenius error; Float16 / BFloat16 within 2e-3 relative
+Frobenius error of the reference-faithful oracle (fp32 accumulate on tensor cores), and bit-exact on the
+CUDA-core route with per-K-tile rounding."""
+import numpy as np
+import pytest
+import torch
+
+from gpu_util import dev, host, integers, normal
+
+pytestmark = pytest.mark.gpu
+
+F32_TOL = 1e-5
+F16_TOL = 2e-3
+
+
+@pytest.fixture(scope="module")
+def api():
+    from neurotensor_b200 import api as a
+    return a
+
+
+@pytest.fixture(scope="module")
+def L():
+    from neurotensor_b200 import _lib
+    return _lib
+
+
+FLAGS = [(False, False), (True, False), (False, True), (True, True)]
+
+
+def operands(rng, m, k, n, ta, tb, dtype, scale=1.0, ints=None):
+    sa = (k, m) if ta else (m, k)
+    sb = (n, k) if tb else (k, n)
+    if ints:
+        return integers(rng, sa, dtype, *ints), integers(rng, sb, dtype, *ints)
+    return normal(rng, sa, dtype, scale), normal(rng, sb, dtype, scale)
+
+
+@pytest.mark.parametrize("ta,tb", FLAGS)
+@pytest.mark.parametrize("m,k,n", [(1, 1, 1), (7, 5, 3), (64, 64, 64), (130, 47, 129), (257, 130, 255), (512, 300, 384)])
+def test_f32_bit_exact(api, oracle, ta, tb, m, k, n):
+    rng = np.random.default_rng(m * 1000 + k)
+    a, b = operands(rng, m, k, n, ta, tb, np.float32)
+    got = host(api.matmult(dev(a), dev(b), ta, tb))
+    exp = oracle.matmult(a, b, ta, tb)
+    assert np.array_equal(got, exp)
+
+
+def test_f32_config_1024(api, oracle, L):
+    """BASELINE config 0: Float32 1024^3, contiguous row-major, N(0,1)."""
+    rng = np.random.default_rng(1)
+    a, b = normal(rng, (1024, 1024), np.float32), normal(rng, (1024, 1024), np.float32)
+    got = host(api.matmult(dev(a), dev(b)))
+    assert L.last_route() == "simt"
+    exp = oracle.matmult(a, b)
+    assert oracle.rel_fro(got, exp) <= F32_TOL
+    assert np.array_equal(got, exp)
+
+
+@pytest.mark.parametrize("ta,tb", FLAGS)
+@pytest.mark.parametrize("m,k,n", [(128, 64, 256), (128, 128, 64), (256, 192, 512), (130, 200, 72), (384, 1024, 640)])
+def test_f16_tensor_core_route(api, oracle, L, ta, tb, m, k, n):
+    rng = np.random.default_rng(7 + m + k + n)
+    a, b = operands(rng, m, k, n, ta, tb, np.float16, 0.5)
+    got = host(api.matmult(dev(a), dev(b), ta, tb, route=L.ROUTE_TENSOR))
+    assert L.last_route() == "umma_f16"
+    exp = oracle.matmult(a, b, ta, tb)
+    wide = (a.T if ta else a).astype(np.float32) @ (b.T if tb else b).astype(np.float32)
+    assert oracle.rel_fro(got, wide) <= 5e-4, "vs fp32-accumulate"
+    assert oracle.rel_fro(got, exp) <= F16_TOL, "vs the reference-faithful oracle"
+
+
+@pytest.mark.parametrize("ta,tb", FLAGS)
+def test_f16_per_ktile_rounding_is_bit_exact(api, oracle, L, ta, tb):
+    rng = np.random.default_rng(11)
+    a, b = operands(rng, 70, 150, 90, ta, tb, np.float16, 0.5)
+    got = host(api.matmult(dev(a), dev(b), ta, tb, f16_rounding=L.F16_ROUND_PER_KTILE))
+    assert L.last_route() == "simt"
+    exp = oracle.matmult(a, b, ta, tb)
+    assert np.array_equal(got.view(np.uint16), exp.view(np.uint16))
+
+
+@pytest.mark.parametrize("ta,tb", FLAGS)
+@pytest.mark.parametrize("m,k,n", [(128, 64, 128), (200, 328, 136), (256, 512, 256)])
+def test_bf16_tensor_core_route(api, oracle, L, ta, tb, m, k, n):
+    rng = np.random.default_rng(13 + m)
+    a32, b32 = operands(rng, m, k, n, ta, tb, np.float32)
+    a, b = oracle.bf16_round(a32), oracle.bf16_round(b32)
+    got = host(api.matmult(dev(a, True), dev(b, True), ta, tb, route=L.ROUTE_TENSOR))
+    assert L.last_route() == "umma_bf16"
+    exp = oracle.matmult(a, b, ta, tb, bf16=True)
+    assert oracle.rel_fro(oracle.bf16_widen(got), oracle.bf16_widen(exp)) <= F16_TOL
+
+
+@pytest.mark.parametrize("ta,tb", FLAGS)
+@pytest.mark.parametrize("m,k,n", [(128, 128, 128), (144, 400, 272), (256, 1024, 512)])
+@pytest.mark.parametrize("dt", [np.int8, np.uint8])
+def test_int8_tensor_core_route_bit_exact(api, oracle, L, ta, tb, m, k, n, dt):
+    rng = np.random.default_rng(17 + k)
+    info = np.iinfo(dt)
+    a, b = operands(rng, m, k, n, ta, tb, dt, ints=(info.min, info.max))
+    got = host(api.matmult(dev(a), dev(b), ta, tb, route=L.ROUTE_TENSOR))
+    assert L.last_route() == "umma_i8"
+    assert np.array_equal(got, oracle.matmult(a, b, ta, tb))
+
+
+@pytest.mark.parametrize("ta,tb", FLAGS)
+@pytest.mark.parametrize("dt", [np.int8, np.int16, np.int32, np.int64, np.uint8])
+def test_integers_cuda_core_route_bit_exact(api, oracle, L, ta, tb, dt):
+    rng = np.random.default_rng(19)
+    info = np.iinfo(dt)
+    a, b = operands(rng, 131, 77, 65, ta, tb, dt, ints=(info.min, info.max))
+    got = host(api.matmult(dev(a), dev(b), ta, tb, route=L.ROUTE_SIMT))
+    assert np.array_equal(got, oracle.matmult(a, b, ta, tb))
+
+
+def test_f64(api, oracle):
+    rng = np.random.default_rng(23)
+    a, b = normal(rng, (90, 70), np.float64), normal(rng, (70, 50), np.float64)
+    assert np.array_equal(host(api.matmult(dev(a), dev(b))), oracle.matmult(a, b))
+
+
+def test_unaligned_fp16_falls_to_cuda_cores_not_cpu(api, oracle, L):
+    """Row stride 2*67 bytes is not 16-byte aligned: TMA cannot stage it, the CUDA-core kernel runs."""
+    rng = np.random.default_rng(29)
+    a, b = normal(rng, (40, 67), np.float16, 0.5), normal(rng, (67, 33), np.float16, 0.5)
+    got = host(api.matmult(dev(a), dev(b)))
+    assert L.last_route() == "simt"
+    assert oracle.rel_fro(got, oracle.matmult(a, b)) <= F16_TOL
+    with pytest.raises(L.Ntb200Error):
+        api.matmult(dev(a), dev(b), route=L.ROUTE_TENSOR)
+
+
+def test_transposed_view_is_not_copied(api, oracle, L):
+    """b.transpose(-1,-2) is a stride swap (the reference flips the flag, matmult_cpu.cpp:268-273)."""
+    rng = np.random.default_rng(31)
+    a, bs = normal(rng, (4, 128, 192), np.float16, 0.3), normal(rng, (4, 256, 192), np.float16, 0.3)
+    bview = dev(bs).transpose(-1, -2)
+    assert not bview.is_contiguous()
+    got = host(api.matmult(dev(a), bview, route=L.ROUTE_TENSOR))
+    exp = oracle.matmult(a, bs, False, True)
+    assert oracle.rel_fro(got, exp) <= F16_TOL
+    # the same through flags
+    got2 = host(api.matmult(dev(a), dev(bs), False, True, route=L.ROUTE_TENSOR))
+    assert np.array_equal(got, got2)
+
+
+def test_batched_and_repeated_operand(api, oracle):
+    rng = np.random.default_rng(37)
+    a = normal(rng, (3, 2, 33, 20), np.float32)
+    b = normal(rng, (3, 2, 20, 17), np.float32)
+    assert np.array_equal(host(api.matmult(dev(a), dev(b))), oracle.matmult(a, b))
+    w = normal(rng, (20, 9), np.float32)     # 2-D operand repeated over the batch
+    assert np.array_equal(host(api.matmult(dev(a), dev(w))), oracle.matmult(a, w))
+    x = normal(rng, (33, 20), np.float32)
+    assert np.array_equal(host(api.matmult(dev(x), dev(b))), oracle.matmult(x, b))
+
+
+@pytest.mark.parametrize("dt,route", [(np.float32, "auto"), (np.int32, "auto"), (np.float16, "tensor"), (np.int8, "tensor")])
+def test_out_variant_accumulates(api, oracle, L, dt, route):
+    """matmult(a, b, out): out += a.b, the raw-pointer contract of nt_matmult."""
+    rng = np.random.default_rng(41)
+    if np.issubdtype(dt, np.integer):
+        a, b, c = (integers(rng, s, dt, -9, 9) for s in ((128, 96), (96, 160), (128, 160)))
+    else:
+        a, b, c = (normal(rng, s, dt, 0.5) for s in ((128, 96), (96, 160), (128, 160)))
+    out = dev(c)
+    r = api.matmult(dev(a), dev(b), out=out, route=L.ROUTE_TENSOR if route == "tensor" else L.ROUTE_AUTO)
+    assert r.data_ptr() == out.data_ptr()
+    exp = c.copy()
+    oracle.matmult_into(a, b, exp)
+    if dt == np.float16:
+        assert oracle.rel_fro(host(out), exp) <= F16_TOL
+    else:
+        assert np.array_equal(host(out), exp)
+
+
+def test_raw_contract_and_pointer_tables(api, oracle, L):
+    """ntb200_matmult / ntb200_matmult_batch with the reference's raw-pointer signature."""
+    import ctypes
+    rng = np.random.default_rng(43)
+    a, b = normal(rng, (5, 40, 24), np.float32), normal(rng, (5, 24, 56), np.float32)
+    da, db = dev(a), dev(b)
+    dc = torch.zeros((5, 40, 56), dtype=torch.float32, device="cuda")
+    lib = L.lib()
+    s = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    L.check(lib.ntb200_matmult(L.F32, da[0].data_ptr(), db[0].data_ptr(), dc[0].data_ptr(), 40, 24, 24, 56, 0, 0, s))
+    exp = oracle.matmult(a, b)
+    assert np.array_equal(host(dc[0]), exp[0])
+    # equally spaced pointers -> one strided launch
+    dc.zero_()
+    arr = lambda t, order: (ctypes.c_void_p * 5)(*[t[i].data_ptr() for i in order])
+    order = list(range(5))
+    L.check(lib.ntb200_matmult_batch(L.F32, arr(da, order), arr(db, order), arr(dc, order), 5, 40, 24, 24, 56, 0, 0, s))
+    assert np.array_equal(host(dc), exp)
+    # shuffled pointers -> device pointer tables
+    dc.zero_()
+    order = [3, 0, 4, 1, 2]
+    L.check(lib.ntb200_matmult_batch(L.F32, arr(da, order), arr(db, order), arr(dc, order), 5, 40, 24, 24, 56, 0, 0, s))
+    assert np.array_equal(host(dc), exp)
+
+
+def test_host_buffer_entry_point(api, oracle):
+    """ntb200_matmult_host: the reference's CPU-pointer contract, staged through the device."""
+    rng = np.random.default_rng(47)
+    a, b = normal(rng, (9, 64, 48), np.float16, 0.5), normal(rng, (9, 80, 48), np.float16, 0.5)
+    c = np.zeros((9, 64, 80), np.float16)
+    api.matmult_host(a, b, c, False, True)
+    assert oracle.rel_fro(c, oracle.matmult(a, b, False, True)) <= F16_TOL
+    a2, b2 = normal(rng, (1500, 70), np.float32), normal(rng, (70, 90), np.float32)
+    c2 = normal(rng, (1500, 90), np.float32)
+    exp = c2.copy()
+    oracle.matmult_into(a2, b2, exp)
+    api.matmult_host(a2, b2, c2)
+    assert np.array_equal(c2, exp)
+
+
+def test_empty_and_k_zero(api):
+    z = api.matmult(torch.zeros((0, 5), device="cuda"), torch.ones((5, 3), device="cuda"))
+    assert z.shape == (0, 3)
+    r = api.matmult(torch.ones((4, 0), device="cuda"), torch.ones((0, 3), device="cuda"))
+    assert torch.equal(r, torch.zeros((4, 3), device="cuda"))
+
+
+def test_errors_match_the_reference(api):
+    a = torch.zeros((4, 5), device="cuda")
+    with pytest.raises(ValueError, match="Expected second tensor rows"):
+        api.matmult(a, torch.zeros((4, 5), device="cuda"))
+    with pytest.raises(ValueError, match="same dtype"):
+        api.matmult(a, torch.zeros((5, 5), device="cuda", dtype=torch.float16))
+    with pytest.raises(ValueError, match="number type"):
+        api.matmult(a.bool(), a.bool().t())
+    with pytest.raises(ValueError, match="contiguous"):
+        api.matmult(a, a.t(), out=torch.zeros((4, 8), device="cuda")[:, ::2])
+
+
+def test_launches_are_counted_and_status_is_clean(api, L):
+    before = L.launch_count()
+    api.matmult(torch.ones((128, 64), device="cuda", dtype=torch.float16),
+                torch.ones((64, 128), device="cuda", dtype=torch.float16))
+    assert L.launch_count() == before + 1
+    L.check(L.lib().ntb200_check_device_status(None))

@@ -1,0 +1,171 @@
+"""GPU parity of linear, conv2d / unfold2d and the Linear+ReLU+MSE forward/backward chain, against the
+reference's golden vectors (Float32) and the CPU oracle."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import REF_GOLDEN
+from gpu_util import dev, host, normal
+
+pytestmark = pytest.mark.gpu
+RTOL, ATOL = 1e-5, 1e-8   # nt::allclose defaults (nt/functional/tensor_files/compare.h:34)
+
+
+def g(name):
+    return np.load(os.path.join(REF_GOLDEN, name + ".npy"))
+
+
+@pytest.fixture(scope="module")
+def api():
+    from neurotensor_b200 import api as a
+    return a
+
+
+def test_linear_golden(api):
+    """tests/src/linear_autograd_test.cpp:128-149 on the device."""
+    x, w, b, grad = (dev(g("linear_" + n)) for n in ("input", "weight", "bias", "grad"))
+    out = api.linear(x, w, b, transpose_b=True)
+    assert np.allclose(host(out), g("linear_input") @ g("linear_weight").T + g("linear_bias"), rtol=RTOL, atol=1e-6)
+    dx, dw = api.matmult_backward(x, w, grad, False, True)
+    assert np.allclose(host(dx), g("linear_xgrad"), rtol=RTOL, atol=ATOL)
+    assert np.allclose(host(dw).sum(axis=0), g("linear_wgrad"), rtol=RTOL, atol=1e-6)
+    assert np.allclose(host(api.column_sum(grad)), g("linear_bgrad"), rtol=RTOL, atol=1e-6)
+
+
+@pytest.mark.parametrize("ext", ["", "_batched"])
+def test_conv2d_golden(api, ext):
+    """tests/src/conv_autograd_test.cpp:249-279,313-341 (forward) on the device."""
+    x, w = dev(g("conv2d_input" + ext)), dev(g("conv2d_weight" + ext))
+    out = api.conv2d(x, w, stride=1, padding=1)
+    exp = g("conv2d_output" + ext)
+    assert tuple(out.shape) == exp.shape
+    assert np.allclose(host(out), exp, rtol=RTOL, atol=1e-6)
+
+
+def test_unfold2d_golden(api):
+    """tests/src/col_im_autograd_test.cpp:77-116 on the device."""
+    x = dev(g("unfold_input"))
+    col = api.unfold2d(x, (3, 2), dilation=(1, 2), padding=1, stride=(2, 2))
+    assert np.array_equal(host(col), g("unfold_output"))
+    dx = api.unfold2d_backward(dev(g("unfold_grad")), x.shape[-2:], (3, 2), dilation=(1, 2), padding=1, stride=(2, 2))
+    assert np.allclose(host(dx).reshape(g("unfold_input_grad").shape), g("unfold_input_grad"), rtol=RTOL, atol=1e-6)
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float16, np.int32, np.int8])
+def test_unfold2d_matches_oracle(api, oracle, dt):
+    rng = np.random.default_rng(3)
+    x = (rng.integers(-50, 50, (3, 5, 13, 11))).astype(dt)
+    for ks, dil, pad, st in [((3, 3), 1, 1, 1), ((2, 4), (2, 1), (0, 2), (2, 1)), ((5, 1), 1, 2, 3)]:
+        got = host(api.unfold2d(dev(x), ks, dil, pad, st))
+        assert np.array_equal(got, oracle.unfold2d(x, ks, dil, pad, st))
+
+
+def test_conv2d_f32_bit_exact_vs_oracle(api, oracle):
+    rng = np.random.default_rng(5)
+    x, w = normal(rng, (3, 7, 19, 23), np.float32), normal(rng, (10, 7, 3, 5), np.float32, 0.2)
+    got = host(api.conv2d(dev(x), dev(w), stride=(2, 1), padding=(1, 2), dilation=(1, 2)))
+    assert np.array_equal(got, oracle.conv2d(x, w, stride=(2, 1), padding=(1, 2), dilation=(1, 2)))
+
+
+def test_conv2d_f16_tensor_cores(api, oracle):
+    """A scaled-down BASELINE config 4: fp16, 3x3, stride 1, pad 1; L = 28*28 keeps rows 16-byte aligned."""
+    from neurotensor_b200 import _lib
+    rng = np.random.default_rng(7)
+    x = normal(rng, (4, 64, 28, 28), np.float16)
+    w = normal(rng, (96, 64, 3, 3), np.float16, (1.0 / (64 * 9)) ** 0.5)
+    got = host(api.conv2d(dev(x), dev(w), stride=1, padding=1))
+    assert _lib.last_route() == "umma_f16"
+    exp = oracle.conv2d(x, w, stride=1, padding=1)
+    assert oracle.rel_fro(got, exp) <= 2e-3
+
+
+def test_conv2d_errors(api):
+    x = torch.zeros((1, 3, 8, 8), device="cuda")
+    w = torch.zeros((4, 3, 3, 3), device="cuda")
+    with pytest.raises(ValueError, match="stride"):
+        api.conv2d(x, w, stride=0)
+    with pytest.raises(ValueError, match="same dtype"):
+        api.conv2d(x, w.half())
+    with pytest.raises(ValueError, match="at least one"):
+        api.conv2d(x, torch.zeros((4, 3, 9, 9), device="cuda"))
+
+
+@pytest.mark.parametrize("dt", ["f32", "f16", "bf16"])
+def test_relu_mse_column_sum(api, oracle, dt):
+    rng = np.random.default_rng(11)
+    x32, t32 = normal(rng, (37, 130), np.float32), normal(rng, (37, 130), np.float32)
+    if dt == "bf16":
+        x, t = oracle.bf16_round(x32), oracle.bf16_round(t32)
+        xw, tw = oracle.bf16_widen(x), oracle.bf16_widen(t)
+        dx, dt_ = dev(x, True), dev(t, True)
+        widen = oracle.bf16_widen
+    else:
+        npdt = np.float32 if dt == "f32" else np.float16
+        x, t = x32.astype(npdt), t32.astype(npdt)
+        xw, tw = x.astype(np.float32), t.astype(np.float32)
+        dx, dt_ = dev(x), dev(t)
+        widen = lambda v: v.astype(np.float32)
+    y = api.relu(dx)
+    assert np.array_equal(widen(host(y)), np.maximum(xw, 0))
+    gi = api.relu_backward(dx, dt_)
+    assert np.array_equal(widen(host(gi)), np.where(xw < 0, 0, tw).astype(np.float32))
+    loss, grad = api.mse(dx, dt_)
+    eloss, egrad = oracle.mse(xw, tw)
+    assert abs(float(loss.item()) - eloss) <= 1e-5 * max(1.0, abs(eloss))
+    tol = 1e-6 if dt == "f32" else 1e-2
+    assert np.allclose(widen(host(grad)), egrad, rtol=tol, atol=1e-6)
+    cs = api.column_sum(dx)
+    assert np.allclose(widen(host(cs)), xw.sum(axis=0), rtol=2e-2 if dt != "f32" else 1e-5, atol=1e-1 if dt != "f32" else 1e-4)
+
+
+def mlp_reference(oracle, x, w1, b1, w2, b2, target, bf16):
+    """Linear -> ReLU -> Linear -> MSE forward and backward on the oracle (nt/nn/layers/Linear.cpp:22-24,
+    nt/nn/functional/matmult.cpp:253-273, nt/nn/Loss.cpp:49-55)."""
+    wid = oracle.bf16_widen if bf16 else (lambda v: v.astype(np.float32))
+    nar = oracle.bf16_round if bf16 else (lambda v: v.astype(np.float16))
+    h = oracle.linear(x, w1, b1, bf16=bf16)
+    a, mask = oracle.relu(wid(h))
+    a16 = nar(a)
+    y = oracle.linear(a16, w2, b2, bf16=bf16)
+    loss, dy = oracle.mse(wid(y), wid(target))
+    dy16 = nar(dy)
+    da, dw2 = oracle.matmult_backward(a16, w2, dy16, bf16=bf16)
+    dh16 = nar(np.where(mask, 0, wid(da)))
+    dx, dw1 = oracle.matmult_backward(x, w1, dh16, bf16=bf16)
+    return dict(h=h, y=y, loss=loss, dw2=dw2, dw1=dw1, dx=dx, db2=wid(dy16).sum(0), db1=wid(dh16).sum(0))
+
+
+@pytest.mark.parametrize("bf16", [True, False])
+def test_mlp_forward_backward(api, oracle, bf16):
+    """BASELINE config 3 scaled down (batch 256, 512 -> 1024 -> 512), same initialisation rule."""
+    rng = np.random.default_rng(13)
+    B, D, H = 256, 512, 1024
+    mk = (lambda v: oracle.bf16_round(v)) if bf16 else (lambda v: v.astype(np.float16))
+    wid = oracle.bf16_widen if bf16 else (lambda v: v.astype(np.float32))
+    x = mk(normal(rng, (B, D), np.float32))
+    w1 = mk(normal(rng, (D, H), np.float32, D ** -0.5))
+    w2 = mk(normal(rng, (H, D), np.float32, H ** -0.5))
+    b1 = mk(normal(rng, (H,), np.float32, 0.01))
+    b2 = mk(normal(rng, (D,), np.float32, 0.01))
+    t = mk(normal(rng, (B, D), np.float32))
+    ref = mlp_reference(oracle, x, w1, b1, w2, b2, t, bf16)
+    d = lambda v: dev(v, bf16)
+    dx_, dw1_, dw2_, db1_, db2_, dt_ = d(x), d(w1), d(w2), d(b1), d(b2), d(t)
+    h = api.linear(dx_, dw1_, db1_)
+    a = api.relu(h)
+    y = api.linear(a, dw2_, db2_)
+    loss, dy = api.mse(y, dt_)
+    da, gw2 = api.matmult_backward(a, dw2_, dy)
+    dh = api.relu_backward(h, da)
+    gx, gw1 = api.matmult_backward(dx_, dw1_, dh)
+    gb2, gb1 = api.column_sum(dy), api.column_sum(dh)
+    rel = lambda got, exp: oracle.rel_fro(wid(host(got)), wid(exp) if exp.dtype in (np.uint16, np.float16) else exp)
+    tol = 2e-3
+    assert rel(h, ref["h"]) <= tol and rel(y, ref["y"]) <= tol
+    assert abs(float(loss.item()) - ref["loss"]) <= 5e-3 * ref["loss"]
+    for got, key in ((gw2, "dw2"), (gw1, "dw1"), (gx, "dx")):
+        assert rel(got, ref[key]) <= 2e-2, key
+    assert oracle.rel_fro(wid(host(gb2)), ref["db2"]) <= 2e-2
+    assert oracle.rel_fro(wid(host(gb1)), ref["db1"]) <= 2e-2
