@@ -161,6 +161,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--items", type=int, default=BATCH,
+                    help="batch items per GPU (default: the full 64); smaller values are for profiler captures only")
     args = ap.parse_args()
     rank, world, local_rank = env_int("RANK", 0), env_int("WORLD_SIZE", 1), env_int("LOCAL_RANK", 0)
     if args.impl == "reference":
@@ -179,7 +181,7 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     # this rank's slice of the global batch (weak scaling: 64 items per rank)
-    start, count = partition.shard_range(BATCH * world, world, rank)
+    start, count = partition.shard_range(args.items * world, world, rank)
     gen = torch.Generator(device="cuda").manual_seed(3 + rank)
     a = (torch.randn((count, M, K), generator=gen, device="cuda") * 0.1).half()
     bs = (torch.randn((count, N, K), generator=gen, device="cuda") * 0.1).half()
@@ -215,7 +217,7 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     ms_per_step = ms / args.steps
-    total_items = BATCH * world
+    total_items = args.items * world
     value = total_items * FLOPS_PER_ITEM / (ms_per_step * 1e-3) / 1e12
     route = _lib.last_route()
 
@@ -260,7 +262,7 @@ def main():
         "metric": "matmult TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "global_batch": total_items, "per_gpu_batch": count,
+        "config": {"workload": WORKLOAD, "global_batch": total_items, "per_gpu_batch": count, "full_size": args.items == BATCH,
                    "parallelism": "batch-sharded x%d, no collective" % world,
                    "l2": "inputs (1.6 GB per step) exceed the 126 MB L2; no flush needed", "kernel": route},
         "roofline": {"bound": "tensor", "achieved": per_gpu_tflops, "peak": peak, "unit": "TFLOP/s",

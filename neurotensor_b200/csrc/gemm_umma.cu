@@ -498,6 +498,9 @@ int launch_umma_gemm(const GemmArgs& g, cudaStream_t stream) {
         return fail(NTB200_ERR_UNSUPPORTED, "tcgen05 route, A: %s", w);
     if (const char* w = plan_operand(g.b, es, dt, g.n, g.k, g.b_cs, g.b_rs, g.batch, g.b_bs, bn, block_k, &pb))
         return fail(NTB200_ERR_UNSUPPORTED, "tcgen05 route, B: %s", w);
+    // An N-major operand is staged in chunks of 128 bytes of N: 8-bit tiles cannot be narrower than one chunk.
+    // (The tensor map of an N-major operand does not depend on the tile width, so `pb` stays valid.)
+    if (pb.mn_major && bn < 128 / es) bn = 128 / es;
 
     UmmaParams p{};
     p.m = int(g.m); p.n = int(g.n); p.k = int(g.k); p.batch = int(g.batch);

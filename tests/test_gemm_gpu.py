@@ -61,7 +61,7 @@ def test_f32_config_1024(api, oracle, L):
 
 
 @pytest.mark.parametrize("ta,tb", FLAGS)
-@pytest.mark.parametrize("m,k,n", [(128, 64, 256), (128, 128, 64), (256, 192, 512), (130, 200, 72), (384, 1024, 640)])
+@pytest.mark.parametrize("m,k,n", [(128, 64, 256), (128, 128, 64), (256, 192, 512), (136, 200, 72), (384, 1024, 640)])
 def test_f16_tensor_core_route(api, oracle, L, ta, tb, m, k, n):
     rng = np.random.default_rng(7 + m + k + n)
     a, b = operands(rng, m, k, n, ta, tb, np.float16, 0.5)
