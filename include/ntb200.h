@@ -155,6 +155,26 @@ int ntb200_conv2d(int dtype, const void* x, const void* w, void* out, void* work
                   int64_t channels, int64_t height, int64_t width, int64_t cout, int64_t kh, int64_t kw, int64_t sh,
                   int64_t sw, int64_t ph, int64_t pw, int64_t dh, int64_t dw, void* stream);
 
+/* ntb200_conv2d for callers that cannot allocate device memory.  No counterpart in the reference, which
+ * allocates its column matrix on the CPU heap as it goes.  Some users of this library cannot do the
+ * device-side equivalent: their application has given the whole device heap to its own allocator, so a
+ * cudaMalloc from anywhere else fails, or they are in a phase in which they do not allow themselves
+ * cudaMalloc because it synchronises the device.  This variant takes the same inputs and output as
+ * ntb200_conv2d but no workspace: the column matrix lives in a fixed array of
+ * NTB200_CONV2D_STATIC_SCRATCH_BYTES inside the library, which every GPU that loads the library holds until
+ * the process exits.  The call (and everything under it) uses no cudaMalloc / cudaFree / pool allocation.
+ *   - A problem whose column matrix (ntb200_conv2d_workspace_bytes) is larger than the array is refused with
+ *     NTB200_ERR_INVALID_ARG and a message naming both sizes; nothing is launched.
+ *   - The first call on each device looks up the array's device address (one cudaGetSymbolAddress with that
+ *     device current); make that first call before starting any stream capture.
+ *   - All calls on a device share the one array, and it keeps the previous call's contents.  Each call rewrites
+ *     every element it reads, so stale contents never reach a result, but two calls that overlap on the GPU
+ *     (different streams, no ordering between them) race on it: order them. */
+#define NTB200_CONV2D_STATIC_SCRATCH_BYTES (32u * 1024u * 1024u)
+int ntb200_conv2d_static_scratch(int dtype, const void* x, const void* w, void* out, int64_t batch, int64_t channels,
+                                 int64_t height, int64_t width, int64_t cout, int64_t kh, int64_t kw, int64_t sh,
+                                 int64_t sw, int64_t ph, int64_t pw, int64_t dh, int64_t dw, void* stream);
+
 /* ---- elementwise neighbours of the GEMM in Linear forward/backward ----------------------------------
  * relu = clamp(x, 0, none) and its mask backward (nt/nn/functional/min_max.cpp:40-63). */
 int ntb200_relu(int dtype, const void* x, void* y, int64_t n, void* stream);

@@ -13,6 +13,7 @@ F32, F16, BF16, I8, I16, I32, I64, F64, U8, U16, U32 = range(11)
 ROUTE_AUTO, ROUTE_TENSOR, ROUTE_SIMT = 0, 1, 2
 F16_ROUND_ONCE, F16_ROUND_PER_KTILE = 0, 1
 OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_ALLOC, ERR_CUDA, ERR_TIMEOUT, ERR_NO_DEVICE = range(7)
+CONV2D_STATIC_SCRATCH_BYTES = 32 * 1024 * 1024
 
 _i64, _vp, _ci, _sz = ctypes.c_int64, ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
 
@@ -56,6 +57,7 @@ SIGNATURES = {
     "ntb200_col2im": (_ci, [_ci, _vp, _vp] + [_i64] * 12 + [_vp]),
     "ntb200_conv2d_workspace_bytes": (_sz, [_ci] + [_i64] * 12),
     "ntb200_conv2d": (_ci, [_ci, _vp, _vp, _vp, _vp] + [_i64] * 13 + [_vp]),
+    "ntb200_conv2d_static_scratch": (_ci, [_ci, _vp, _vp, _vp] + [_i64] * 13 + [_vp]),
     "ntb200_relu": (_ci, [_ci, _vp, _vp, _i64, _vp]),
     "ntb200_relu_backward": (_ci, [_ci, _vp, _vp, _vp, _i64, _vp]),
     "ntb200_mse": (_ci, [_ci, _vp, _vp, _vp, _vp, _i64, _vp]),
