@@ -20,6 +20,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <algorithm>
+#include <cstdlib>
 #include <mutex>
 
 #include "internal.h"
@@ -93,6 +95,104 @@ __device__ __forceinline__ float to_float_bits16(uint32_t bits, int out_kind) {
 __device__ __forceinline__ uint32_t from_float_bits16(float v, int out_kind) {
     return out_kind == kOutF16 ? (uint32_t)__half_as_ushort(__float2half_rn(v))
                                : (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v));
+}
+
+// Epilogue of one 128-row accumulator slice: thread `row` of the tile reads its TMEM lane 32 columns at a time,
+// adds the bias and / or the previous C, converts and stores.  `tmem_acc` already carries the warp's lane quadrant
+// and the accumulator's first column.  Executed by whole warps (tcgen05.ld is warp-collective).
+template <int BN>
+__device__ __forceinline__ void epilogue_tile(const UmmaParams& p, uint32_t tmem_acc, int b, int row, int n0) {
+    const int es = (p.out_kind == kOutI8) ? 1 : 2;
+    const bool row_ok = row < p.m;
+    uint8_t* c_row = static_cast<uint8_t*>(p.c) + ((long long)b * p.c_bs + (long long)row * p.c_rs) * es;
+#pragma unroll 1
+    for (int cc = 0; cc < BN / 32; ++cc) {
+        const int col0 = n0 + cc * 32;
+        if (col0 >= p.n) break;  // uniform across the CTA
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tmem_acc + uint32_t(cc * 32), v);
+        tmem_ld_wait();
+        if (!row_ok) continue;
+        const bool full_chunk = (col0 + 32 <= p.n);
+        if (p.out_kind == kOutI8) {
+            // s32 accumulators; keep the low 8 bits (wrap), adding bias / previous C first
+            if (p.bias) {
+                const int8_t* bias = static_cast<const int8_t*>(p.bias) + (long long)b * p.bias_bs +
+                                     (long long)row * p.bias_rs;
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (col0 + j < p.n) v[j] += (uint32_t)(int)bias[(long long)(col0 + j) * p.bias_cs];
+            }
+            uint8_t* dst = c_row + col0;
+            if (full_chunk && p.c_vec_ok) {
+                uint32_t packed[8];
+                if (p.accumulate) {
+                    const uint4 o0 = *reinterpret_cast<const uint4*>(dst);
+                    const uint4 o1 = *reinterpret_cast<const uint4*>(dst + 16);
+                    const uint32_t old[8] = {o0.x, o0.y, o0.z, o0.w, o1.x, o1.y, o1.z, o1.w};
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] += (old[j >> 2] >> (8 * (j & 3))) & 0xffu;
+                }
+#pragma unroll
+                for (int q = 0; q < 8; ++q)
+                    packed[q] = (v[4 * q] & 0xffu) | ((v[4 * q + 1] & 0xffu) << 8) |
+                                ((v[4 * q + 2] & 0xffu) << 16) | ((v[4 * q + 3] & 0xffu) << 24);
+                *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                *reinterpret_cast<uint4*>(dst + 16) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (col0 + j < p.n) {
+                        uint32_t x = v[j];
+                        if (p.accumulate) x += dst[j];
+                        dst[j] = (uint8_t)x;
+                    }
+            }
+        } else {
+            float f[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+            if (p.bias) {
+                const uint16_t* bias = static_cast<const uint16_t*>(p.bias) + (long long)b * p.bias_bs +
+                                       (long long)row * p.bias_rs;
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (col0 + j < p.n) f[j] += to_float_bits16(bias[(long long)(col0 + j) * p.bias_cs], p.out_kind);
+            }
+            uint16_t* dst = reinterpret_cast<uint16_t*>(c_row) + col0;
+            if (full_chunk && p.c_vec_ok) {
+                if (p.accumulate) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const uint4 o = *reinterpret_cast<const uint4*>(dst + 8 * q);
+                        const uint32_t w[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            f[8 * q + 2 * j] += to_float_bits16(w[j] & 0xffffu, p.out_kind);
+                            f[8 * q + 2 * j + 1] += to_float_bits16(w[j] >> 16, p.out_kind);
+                        }
+                    }
+                }
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        w[j] = from_float_bits16(f[8 * q + 2 * j], p.out_kind) |
+                               (from_float_bits16(f[8 * q + 2 * j + 1], p.out_kind) << 16);
+                    *reinterpret_cast<uint4*>(dst + 8 * q) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (col0 + j < p.n) {
+                        float x = f[j];
+                        if (p.accumulate) x += to_float_bits16(dst[j], p.out_kind);
+                        dst[j] = (uint16_t)from_float_bits16(x, p.out_kind);
+                    }
+            }
+        }
+    }
 }
 
 template <MmaKind kKind, int BN>
@@ -230,7 +330,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         const int row_in_tile = quad * 32 + lane;
         int acc = 0;
         uint32_t acc_phase = 0;
-        const int es = (p.out_kind == kOutI8) ? 1 : 2;
         for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x) {
             int b, mi, ni;
             tile_coords(p, t, b, mi, ni);
@@ -241,97 +340,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                 break;
             }
             tcgen05_fence_after();
-            const int row = mi * kBM + row_in_tile;
-            const bool row_ok = row < p.m;
-            uint8_t* c_row = static_cast<uint8_t*>(p.c) + ((long long)b * p.c_bs + (long long)row * p.c_rs) * es;
-#pragma unroll 1
-            for (int cc = 0; cc < BN / 32; ++cc) {
-                const int col0 = ni * BN + cc * 32;
-                if (col0 >= p.n) break;  // uniform across the CTA
-                uint32_t v[32];
-                tmem_ld_32x32b_x32(tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN + cc * 32), v);
-                tmem_ld_wait();
-                if (!row_ok) continue;
-                const bool full_chunk = (col0 + 32 <= p.n);
-                if (p.out_kind == kOutI8) {
-                    // s32 accumulators; keep the low 8 bits (wrap), adding bias / previous C first
-                    if (p.bias) {
-                        const int8_t* bias = static_cast<const int8_t*>(p.bias) + (long long)b * p.bias_bs +
-                                             (long long)row * p.bias_rs;
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (col0 + j < p.n) v[j] += (uint32_t)(int)bias[(long long)(col0 + j) * p.bias_cs];
-                    }
-                    uint8_t* dst = c_row + col0;
-                    if (full_chunk && p.c_vec_ok) {
-                        uint32_t packed[8];
-                        if (p.accumulate) {
-                            const uint4 o0 = *reinterpret_cast<const uint4*>(dst);
-                            const uint4 o1 = *reinterpret_cast<const uint4*>(dst + 16);
-                            const uint32_t old[8] = {o0.x, o0.y, o0.z, o0.w, o1.x, o1.y, o1.z, o1.w};
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) v[j] += (old[j >> 2] >> (8 * (j & 3))) & 0xffu;
-                        }
-#pragma unroll
-                        for (int q = 0; q < 8; ++q)
-                            packed[q] = (v[4 * q] & 0xffu) | ((v[4 * q + 1] & 0xffu) << 8) |
-                                        ((v[4 * q + 2] & 0xffu) << 16) | ((v[4 * q + 3] & 0xffu) << 24);
-                        *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                        *reinterpret_cast<uint4*>(dst + 16) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (col0 + j < p.n) {
-                                uint32_t x = v[j];
-                                if (p.accumulate) x += dst[j];
-                                dst[j] = (uint8_t)x;
-                            }
-                    }
-                } else {
-                    float f[32];
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
-                    if (p.bias) {
-                        const uint16_t* bias = static_cast<const uint16_t*>(p.bias) + (long long)b * p.bias_bs +
-                                               (long long)row * p.bias_rs;
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (col0 + j < p.n) f[j] += to_float_bits16(bias[(long long)(col0 + j) * p.bias_cs], p.out_kind);
-                    }
-                    uint16_t* dst = reinterpret_cast<uint16_t*>(c_row) + col0;
-                    if (full_chunk && p.c_vec_ok) {
-                        if (p.accumulate) {
-#pragma unroll
-                            for (int q = 0; q < 4; ++q) {
-                                const uint4 o = *reinterpret_cast<const uint4*>(dst + 8 * q);
-                                const uint32_t w[4] = {o.x, o.y, o.z, o.w};
-#pragma unroll
-                                for (int j = 0; j < 4; ++j) {
-                                    f[8 * q + 2 * j] += to_float_bits16(w[j] & 0xffffu, p.out_kind);
-                                    f[8 * q + 2 * j + 1] += to_float_bits16(w[j] >> 16, p.out_kind);
-                                }
-                            }
-                        }
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            uint32_t w[4];
-#pragma unroll
-                            for (int j = 0; j < 4; ++j)
-                                w[j] = from_float_bits16(f[8 * q + 2 * j], p.out_kind) |
-                                       (from_float_bits16(f[8 * q + 2 * j + 1], p.out_kind) << 16);
-                            *reinterpret_cast<uint4*>(dst + 8 * q) = make_uint4(w[0], w[1], w[2], w[3]);
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (col0 + j < p.n) {
-                                float x = f[j];
-                                if (p.accumulate) x += to_float_bits16(dst[j], p.out_kind);
-                                dst[j] = (uint16_t)from_float_bits16(x, p.out_kind);
-                            }
-                    }
-                }
-            }
+            epilogue_tile<BN>(p, tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN), b,
+                              mi * kBM + row_in_tile, ni * BN);
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty_bar(acc));
@@ -345,6 +355,185 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     if (warp == 1) {
         tcgen05_fence_after();
         tmem_dealloc<1>(tmem_base, kTmemCols);
+    }
+}
+
+// ---- pair kernel: two CTAs (the two SMs of a TPC, one cluster) share a 256 x 256 tile ------------------------
+// tcgen05.mma.cta_group::2 computes rows [0,128) of the tile in the even CTA's tensor memory and rows [128,256)
+// in the odd CTA's; each CTA stages only its own 128 rows of A and its own 128 of the tile's 256 B columns, so a
+// K block costs each SM 32 KB of L2 traffic instead of 48 KB and the ring holds 6 stages instead of 4.
+//   * both CTAs run a producer; every load credits the EVEN CTA's `full` barrier, whose producer posts the byte
+//     count of both halves;
+//   * only the even CTA issues MMAs; its commits are delivered to `empty` / `tmem_full` in BOTH CTAs;
+//   * both CTAs run the epilogue on their own TMEM lanes and hand the accumulator back by arriving on the even
+//     CTA's `tmem_empty` (8 arrivals: 4 warps x 2 CTAs).
+// The loads are per-CTA copies of this GPU's own memory (no multicast).
+constexpr int kPairStages = 6;
+constexpr uint32_t kPairOperandBytes = 128 * 128;                 // 128 rows (or 128 bytes of MN x block_k rows)
+constexpr uint32_t kPairStageBytes = 2 * kPairOperandBytes;       // per CTA
+constexpr uint32_t kPairSmemBytes = kPairStages * kPairStageBytes + 256 + 1024;
+
+template <MmaKind kKind>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                      const UmmaParams p) {
+    constexpr int BN = 256;
+    constexpr int kStages = kPairStages;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    uint8_t* bar_gen = smem_gen + kStages * kPairStageBytes;
+    const uint32_t bar_base = smem_base + kStages * kPairStageBytes;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+    auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
+    auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_gen + 8 * (2 * kStages + 4));
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_cta_rank();
+    const bool leader = rank == 0;
+    const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(tfull_bar(a), 1);
+            mbar_init(tempty_bar(a), 8);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+        fence_proxy_async_smem();
+        tma_prefetch_desc(&tma_a);
+        tma_prefetch_desc(&tma_b);
+    }
+    if (warp == 1) {
+        tmem_alloc<2>(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
+        tmem_relinquish<2>();
+    }
+    tcgen05_fence_before();
+    cluster_sync_all();  // barriers of both CTAs are initialised before anything signals them remotely
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer (both CTAs)
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = pair; ok && t < p.total_tiles; t += npairs) {
+                int b, mi, ni;
+                tile_coords(p, t, b, mi, ni);
+                const int m0 = mi * 256 + int(rank) * 128, n0 = ni * BN + int(rank) * 128;
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
+                        raise_timeout(abort_flag, 0x11);
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t a_dst = smem_base + stage * kPairStageBytes;
+                    const uint32_t b_dst = a_dst + kPairOperandBytes;
+                    const uint32_t bar = full_bar(stage);
+                    if (leader) mbar_expect_tx(bar, 2 * kPairStageBytes);
+                    const int k0 = kb * p.block_k;
+                    if (!p.a_mn_major) {
+                        tma_load_3d_pair(a_dst, &tma_a, bar, k0, m0, b * p.a_batch_mul);
+                    } else {
+                        for (int c = 0; c < p.a_chunks; ++c)
+                            tma_load_3d_pair(a_dst + c * p.chunk_bytes, &tma_a, bar, m0 + c * p.chunk_mn, k0,
+                                             b * p.a_batch_mul);
+                    }
+                    if (!p.b_mn_major) {
+                        tma_load_3d_pair(b_dst, &tma_b, bar, k0, n0, b * p.b_batch_mul);
+                    } else {
+                        for (int c = 0; c < p.b_chunks; ++c)
+                            tma_load_3d_pair(b_dst + c * p.chunk_bytes, &tma_b, bar, n0 + c * p.chunk_mn, k0,
+                                             b * p.b_batch_mul);
+                    }
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                }
+            }
+            if (ok) {  // drain: every stage released means every load of this CTA has landed and been consumed
+                for (int s = 0; s < kStages; ++s) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { raise_timeout(abort_flag, 0x12); break; }
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer (even CTA only)
+        if (leader && lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int t = pair; ok && t < p.total_tiles; t += npairs) {
+                if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
+                    raise_timeout(abort_flag, 0x13);
+                    break;
+                }
+                tcgen05_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
+                        raise_timeout(abort_flag, 0x14);
+                        ok = false;
+                        break;
+                    }
+                    tcgen05_fence_after();
+                    const uint32_t a_addr = smem_base + stage * kPairStageBytes;
+                    const uint64_t a_desc = make_smem_desc_sw128(a_addr, p.a_lbo, 1024);
+                    const uint64_t b_desc = make_smem_desc_sw128(a_addr + kPairOperandBytes, p.b_lbo, 1024);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        umma<kKind, 2>(d_tmem, a_desc + uint64_t(k * p.a_kstep), b_desc + uint64_t(k * p.b_kstep),
+                                       p.idesc, (kb | k) != 0);
+                    umma_commit_pair(empty_bar(stage), 3);
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                umma_commit_pair(tfull_bar(acc), 3);
+                if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (both CTAs)
+        const int quad = warp & 3;
+        const int row_in_tile = int(rank) * 128 + quad * 32 + lane;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        for (int t = pair; t < p.total_tiles; t += npairs) {
+            int b, mi, ni;
+            tile_coords(p, t, b, mi, ni);
+            bool ok = mbar_wait(tfull_bar(acc), acc_phase, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) {
+                if (lane == 0) raise_timeout(abort_flag, 0x15);
+                break;
+            }
+            tcgen05_fence_after();
+            epilogue_tile<BN>(p, tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN), b,
+                              mi * 256 + row_in_tile, ni * BN);
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_leader(tempty_bar(acc));
+            if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    // Neither CTA may leave while the other can still signal its barriers or read its shared memory.
+    tcgen05_fence_before();
+    cluster_sync_all();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tmem_dealloc<2>(tmem_base, kTmemCols);
     }
 }
 
@@ -421,6 +610,9 @@ const char* plan_operand(const void* ptr, int es, CUtensorMapDataType dt, int64_
     return nullptr;
 }
 
+// NTB200_NO_PAIR=1 keeps every GEMM on the single-CTA kernel (for A/B measurements).
+const bool g_disable_pair = [] { const char* e = getenv("NTB200_NO_PAIR"); return e && e[0] == '1'; }();
+
 bool dtype_on_tensor_cores(int dtype) {
     return dtype == NTB200_F16 || dtype == NTB200_BF16 || dtype == NTB200_I8 || dtype == NTB200_U8;
 }
@@ -466,6 +658,45 @@ int launch_instance(const OperandPlan& pa, const OperandPlan& pb, const UmmaPara
     return NTB200_OK;
 }
 
+// Number of CTA pairs that can be resident at once (one pair per TPC).
+int max_resident_pairs(const void* kernel) {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return sm_count() / 2;
+    if (cached[dev] == 0) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(unsigned(sm_count() & ~1), 1, 1);
+        cfg.blockDim = dim3(kThreads, 1, 1);
+        cfg.dynamicSmemBytes = kPairSmemBytes;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2;
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n <= 0) {
+            (void)cudaGetLastError();
+            n = sm_count() / 2;
+        }
+        cached[dev] = std::min(n, sm_count() / 2);
+    }
+    return cached[dev];
+}
+
+template <MmaKind kKind>
+int launch_pair_instance(const OperandPlan& pa, const OperandPlan& pb, const UmmaParams& p, cudaStream_t stream) {
+    cudaError_t e = cudaFuncSetAttribute(umma_gemm_pair_kernel<kKind>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         int(kPairSmemBytes));
+    if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(umma_gemm_pair_kernel)");
+    const int pairs = std::min(p.total_tiles, max_resident_pairs(reinterpret_cast<const void*>(umma_gemm_pair_kernel<kKind>)));
+    umma_gemm_pair_kernel<kKind><<<2 * pairs, kThreads, kPairSmemBytes, stream>>>(pa.map, pb.map, p);
+    count_launch();
+    NTB200_CUDA(cudaGetLastError());
+    return NTB200_OK;
+}
+
 }  // namespace
 
 bool umma_supported(const GemmArgs& g, const char** why) {
@@ -493,10 +724,17 @@ int launch_umma_gemm(const GemmArgs& g, cudaStream_t stream) {
     if (g.n <= 64) bn = 64;
     else if (g.n <= 128 && bn > 128) bn = 128;
 
+    // Large problems run on CTA pairs (256 x 256 tiles); anything with fewer pair tiles than TPCs keeps the
+    // single-CTA kernel, whose narrower tiles spread small problems over more SMs.
+    const int64_t pair_tiles = ((g.m + 255) / 256) * ((g.n + 255) / 256) * g.batch;
+    const bool use_pair = !g_disable_pair && g.m > 128 && g.n > 128 && pair_tiles >= sms / 2;
+    if (use_pair) bn = 256;
+
     OperandPlan pa, pb;
     if (const char* w = plan_operand(g.a, es, dt, g.m, g.k, g.a_rs, g.a_cs, g.batch, g.a_bs, kBM, block_k, &pa))
         return fail(NTB200_ERR_UNSUPPORTED, "tcgen05 route, A: %s", w);
-    if (const char* w = plan_operand(g.b, es, dt, g.n, g.k, g.b_cs, g.b_rs, g.batch, g.b_bs, bn, block_k, &pb))
+    if (const char* w = plan_operand(g.b, es, dt, g.n, g.k, g.b_cs, g.b_rs, g.batch, g.b_bs, use_pair ? 128 : bn,
+                                     block_k, &pb))
         return fail(NTB200_ERR_UNSUPPORTED, "tcgen05 route, B: %s", w);
     // An N-major operand is staged in chunks of 128 bytes of N: 8-bit tiles cannot be narrower than one chunk.
     // (The tensor map of an N-major operand does not depend on the tile width, so `pb` stays valid.)
@@ -504,19 +742,20 @@ int launch_umma_gemm(const GemmArgs& g, cudaStream_t stream) {
 
     UmmaParams p{};
     p.m = int(g.m); p.n = int(g.n); p.k = int(g.k); p.batch = int(g.batch);
-    p.tiles_m = int(tiles_m);
+    p.tiles_m = use_pair ? int((g.m + 255) / 256) : int(tiles_m);
     p.tiles_n = int((g.n + bn - 1) / bn);
     p.k_blocks = int((g.k + block_k - 1) / block_k);
     p.group_m = 8;
     p.total_tiles = int(int64_t(p.tiles_m) * p.tiles_n * g.batch);
     p.block_k = block_k;
     const uint32_t in_fmt = g.dtype == NTB200_BF16 ? 1u : (g.dtype == NTB200_I8 ? 1u : 0u);
-    p.idesc = make_instr_desc(is_i8 ? 2u : 1u, in_fmt, in_fmt, pa.mn_major, pb.mn_major, kBM, uint32_t(bn));
+    p.idesc = make_instr_desc(is_i8 ? 2u : 1u, in_fmt, in_fmt, pa.mn_major, pb.mn_major, use_pair ? 256u : uint32_t(kBM),
+                              uint32_t(bn));
     p.a_mn_major = pa.mn_major; p.b_mn_major = pb.mn_major;
     p.chunk_mn = 128 / es;
     p.chunk_bytes = uint32_t(block_k) * 128u;
     p.a_chunks = kBM / p.chunk_mn;
-    p.b_chunks = bn / p.chunk_mn;
+    p.b_chunks = (use_pair ? 128 : bn) / p.chunk_mn;
     // K-major: rows are 128 bytes, 8-row groups 1024 bytes apart, +32 bytes per MMA along K.
     // MN-major: each K row of a chunk is 128 bytes of MN, 8-row groups 1024 bytes apart (SBO), chunks
     // `chunk_bytes` apart (LBO), and one MMA consumes 32/es K rows.
@@ -534,6 +773,9 @@ int launch_umma_gemm(const GemmArgs& g, cudaStream_t stream) {
                  (g.batch == 1 || (g.c_bs * es) % 16 == 0);
     const int grid = int(std::min<int64_t>(p.total_tiles, sms));
     note_route(is_i8 ? "umma_i8" : (g.dtype == NTB200_F16 ? "umma_f16" : "umma_bf16"));
+    if (use_pair)
+        return is_i8 ? launch_pair_instance<MmaKind::i8>(pa, pb, p, stream)
+                     : launch_pair_instance<MmaKind::f16>(pa, pb, p, stream);
     if (is_i8) {
         if (bn == 256) return launch_instance<MmaKind::i8, 256>(pa, pb, p, grid, stream);
         if (bn == 128) return launch_instance<MmaKind::i8, 128>(pa, pb, p, grid, stream);

@@ -92,6 +92,32 @@ __device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const void* tmap,
         : "memory");
 }
 
+// The same load issued by either CTA of a pair working as one cta_group::2 MMA: the data lands in the issuing CTA's
+// shared memory, the byte count is credited to the barrier at `bar` in the pair's EVEN CTA (the MMA leader).
+constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;  // clears the bit that selects the odd CTA of a pair in a shared::cluster address
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t smem_dst, const void* tmap, uint32_t bar, int c0, int c1,
+                                                 int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(c2), "r"(bar & kPeerBitMask)
+        : "memory");
+}
+
+// ---- cluster -------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Arrive on the barrier at this offset in the pair's even CTA, from either CTA.
+__device__ __forceinline__ void mbar_arrive_leader(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar & kPeerBitMask) : "memory");
+}
+
 // ---- tensor memory -------------------------------------------------------------------------------
 template <int kCtaGroup>
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_result, uint32_t ncols) {
@@ -154,6 +180,14 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
     else
         asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
+// cta_group::2 form whose arrive is delivered to the barrier at this offset in every CTA of `cta_mask`
+// (a commit signal, not a data copy).
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t cta_mask) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+        ::"r"(bar), "h"(cta_mask) : "memory");
+}
+
 // 32 lanes x 32 columns of 32-bit accumulators -> 32 registers per thread (thread i of the warp owns
 // lane base+i; the warp may only touch the TMEM lane quadrant (warp_id % 4)).
 __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
