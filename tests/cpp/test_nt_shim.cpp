@@ -1,0 +1,246 @@
+// C++ tests of the nt:: host surface, written the way the reference writes its own tests
+// (tests/src/test_macros.h:68-93: named cases that must not throw).  Cases mirror tests/src/matmult_test.cpp:10-307,
+// tests/src/linear_autograd_test.cpp:128-149, tests/src/conv_autograd_test.cpp:249-374 and
+// tests/src/col_im_autograd_test.cpp:77-116, reading the reference's committed golden .npy vectors.
+//   usage: test_nt_shim <dir with the golden .npy files>
+#include <nt/nt.h>
+
+#include <cstdio>
+#include <iostream>
+
+static int g_failed = 0, g_run = 0;
+template <class F>
+void run_test(const char* name, F&& f) {
+    ++g_run;
+    try {
+        f();
+        std::printf("PASS %s\n", name);
+    } catch (const std::exception& e) {
+        ++g_failed;
+        std::printf("FAIL %s: %s\n", name, e.what());
+    }
+    // the reference's harness also fails a case that leaks tracked memory (test_macros.h:72-85)
+    uint64_t in_use = 0;
+    ntb200_pool_stats(&in_use, nullptr);
+    if (in_use != 0) {
+        ++g_failed;
+        std::printf("FAIL %s: %llu bytes still allocated from the pool\n", name, (unsigned long long)in_use);
+    }
+}
+#define REQUIRE(cond) nt::utils::throw_exception((cond), "requirement failed: " #cond " (line ", __LINE__, ")")
+template <class F>
+bool throws_invalid_argument(F&& f) {
+    try { f(); } catch (const std::invalid_argument&) { return true; }
+    return false;
+}
+
+using nt::DType;
+using nt::DeviceType;
+using nt::SizeRef;
+using nt::Tensor;
+using nt::TensorGrad;
+namespace fn = nt::functional;
+
+int main(int argc, char** argv) {
+    const std::string gold = argc > 1 ? std::string(argv[1]) + "/" : "tests/golden/reference_autograd_data/";
+
+    run_test("matmult shapes, 2-D and batched, all flag combinations", [] {
+        Tensor a = nt::randn_seeded({3, 4, 5}, DType::Float32, 1), b = nt::randn_seeded({3, 5, 2}, DType::Float32, 2);
+        REQUIRE(fn::matmult(a, b).shape() == SizeRef({3, 4, 2}));
+        REQUIRE(fn::matmult(a[0], b[0]).shape() == SizeRef({4, 2}));
+        Tensor at = nt::randn_seeded({3, 5, 4}, DType::Float32, 3), bt = nt::randn_seeded({3, 2, 5}, DType::Float32, 4);
+        REQUIRE(fn::matmult(at, b, true, false).shape() == SizeRef({3, 4, 2}));
+        REQUIRE(fn::matmult(a, bt, false, true).shape() == SizeRef({3, 4, 2}));
+        REQUIRE(fn::matmult(at, bt, true, true).shape() == SizeRef({3, 4, 2}));
+        REQUIRE(fn::matmult_cT(a, bt).shape() == SizeRef({3, 4, 2}));
+        // bigger a / bigger b: the 2-D operand is repeated over the batch
+        REQUIRE(fn::matmult(a, b[0]).shape() == SizeRef({3, 4, 2}));
+        REQUIRE(fn::matmult(a[0], b).shape() == SizeRef({3, 4, 2}));
+    });
+
+    run_test("batched matmult equals per-item matmult", [] {
+        Tensor a = nt::randn_seeded({4, 33, 20}, DType::Float32, 5), b = nt::randn_seeded({4, 20, 17}, DType::Float32, 6);
+        Tensor o = fn::matmult(a, b);
+        for (int64_t i = 0; i < 4; ++i) {
+            std::vector<float> whole = o[i].to_vector<float>(), single = fn::matmult(a[i], b[i]).to_vector<float>();
+            REQUIRE(whole == single);  // bit for bit
+        }
+    });
+
+    run_test("transpose is an O(1) view and matmult reads it in place", [] {
+        Tensor a = nt::randn_seeded({2, 128, 192}, DType::Float32, 7).to(DType::Float16);
+        Tensor bs = nt::randn_seeded({2, 256, 192}, DType::Float32, 8).to(DType::Float16);
+        Tensor bview = bs.transpose(-1, -2);
+        REQUIRE(bview.shares_storage_with(bs) && !bview.is_contiguous() && bview.shape() == SizeRef({2, 192, 256}));
+        uint64_t before = ntb200_kernel_launch_count();
+        Tensor c1 = fn::matmult(a, bview);
+        REQUIRE(ntb200_kernel_launch_count() == before + 1);  // one GEMM, no copy kernel
+        REQUIRE(std::string(ntb200_last_gemm_route()) == "umma_f16");
+        Tensor c2 = fn::matmult(a, bs, false, true);
+        REQUIRE(c1.to_vector<uint16_t>() == c2.to_vector<uint16_t>());
+        REQUIRE(bview.contiguous().is_contiguous() && !bview.contiguous().shares_storage_with(bs));
+    });
+
+    run_test("matmult with an out tensor accumulates and validates it", [] {
+        Tensor a = nt::randn_seeded({6, 8}, DType::Float32, 9), b = nt::randn_seeded({8, 4}, DType::Float32, 10);
+        Tensor c = fn::matmult(a, b);
+        Tensor twice = c.clone();
+        Tensor& r = fn::matmult(a, b, twice);
+        REQUIRE(&r == &twice);
+        std::vector<float> v1 = c.to_vector<float>(), v2 = twice.to_vector<float>();
+        for (size_t i = 0; i < v1.size(); ++i) REQUIRE(std::fabs(v2[i] - 2 * v1[i]) <= 1e-5f * std::fabs(v1[i]) + 1e-6f);
+        Tensor wrong = fn::zeros({6, 5});
+        REQUIRE(throws_invalid_argument([&] { fn::matmult(a, b, wrong); }));
+        Tensor frozen = fn::zeros({6, 4});
+        frozen.set_mutability(false);
+        REQUIRE(throws_invalid_argument([&] { fn::matmult(a, b, frozen); }));
+        Tensor strided = fn::zeros({4, 6}).transpose(0, 1);
+        REQUIRE(throws_invalid_argument([&] { fn::matmult(a, b, strided); }));
+    });
+
+    run_test("errors are std::invalid_argument raised before any launch", [] {
+        Tensor a = fn::zeros({4, 5}), b = fn::zeros({4, 5});
+        uint64_t before = ntb200_kernel_launch_count();
+        REQUIRE(throws_invalid_argument([&] { fn::matmult(a, b); }));
+        REQUIRE(throws_invalid_argument([&] { fn::matmult(a, fn::zeros({5, 3}, DType::Float16)); }));
+        REQUIRE(throws_invalid_argument([&] { fn::matmult(a, Tensor::Null()); }));
+        REQUIRE(throws_invalid_argument([&] { fn::matmult(fn::zeros({4, 5}, DType::Bool), fn::zeros({5, 4}, DType::Bool)); }));
+        REQUIRE(throws_invalid_argument([&] { fn::matmult(fn::zeros({2, 4, 5}), fn::zeros({3, 5, 4})); }));
+        REQUIRE(ntb200_kernel_launch_count() == before);
+    });
+
+    run_test("int8 matmult wraps modulo 256 and returns int8", [] {
+        std::vector<int8_t> ha(16 * 32), hb(32 * 8);
+        for (size_t i = 0; i < ha.size(); ++i) ha[i] = int8_t((i * 37 + 11) % 251 - 125);
+        for (size_t i = 0; i < hb.size(); ++i) hb[i] = int8_t((i * 53 + 7) % 241 - 120);
+        Tensor a = Tensor::from_host(ha.data(), {16, 32}, DType::int8), b = Tensor::from_host(hb.data(), {32, 8}, DType::int8);
+        Tensor c = fn::matmult(a, b);
+        REQUIRE(c.dtype() == DType::int8);
+        std::vector<int8_t> got = c.to_vector<int8_t>();
+        for (int i = 0; i < 16; ++i)
+            for (int j = 0; j < 8; ++j) {
+                int acc = 0;
+                for (int k = 0; k < 32; ++k) acc += int(ha[i * 32 + k]) * int(hb[k * 8 + j]);
+                REQUIRE(got[i * 8 + j] == int8_t(uint8_t(acc)));
+            }
+    });
+
+    run_test("host tensors go through the raw-pointer contract", [] {
+        Tensor a = nt::randn_seeded({5, 40, 24}, DType::Float32, 11), b = nt::randn_seeded({5, 24, 56}, DType::Float32, 12);
+        Tensor dev = fn::matmult(a, b);
+        Tensor host = fn::matmult(a.to(DeviceType::CPU), b.to(DeviceType::CPU));
+        REQUIRE(host.device() == DeviceType::CPU);
+        REQUIRE(host.to_vector<float>() == dev.to_vector<float>());
+    });
+
+    run_test("Linear Autograd test (golden)", [&] {
+        TensorGrad x(fn::from_numpy(gold + "linear_input.npy"), true);
+        Tensor grad = fn::from_numpy(gold + "linear_grad.npy");
+        TensorGrad w(fn::from_numpy(gold + "linear_weight.npy"), true), b(fn::from_numpy(gold + "linear_bias.npy"), true);
+        TensorGrad o = fn::linear(x, w, b, false, true);
+        REQUIRE(o.shape() == SizeRef({3, 4, 3}));
+        o.backward(grad);
+        REQUIRE(fn::allclose(x.grad(), fn::from_numpy(gold + "linear_xgrad.npy")));
+        REQUIRE(fn::allclose(w.grad(), fn::from_numpy(gold + "linear_wgrad.npy"), 1e-5, 1e-6));
+        REQUIRE(fn::allclose(b.grad(), fn::from_numpy(gold + "linear_bgrad.npy"), 1e-5, 1e-6));
+    });
+
+    for (const char* ext : {"", "_batched"}) {
+        const std::string e = ext;
+        run_test(("Conv2d Autograd test (golden)" + e).c_str(), [&] {
+            TensorGrad x(fn::from_numpy(gold + "conv2d_input" + e + ".npy"), true);
+            TensorGrad w(fn::from_numpy(gold + "conv2d_weight" + e + ".npy"), true);
+            fn::ConvArgs args;
+            args.ph = args.pw = 1;
+            TensorGrad o = fn::conv2d(x, w, args);
+            REQUIRE(fn::allclose(o.detach(), fn::from_numpy(gold + "conv2d_output" + e + ".npy"), 1e-5, 1e-6));
+            o.backward(fn::from_numpy(gold + "conv2d_grad" + e + ".npy"));
+            REQUIRE(fn::allclose(x.grad(), fn::from_numpy(gold + "conv2d_xgrad" + e + ".npy"), 1e-4, 1e-6));
+            REQUIRE(fn::allclose(w.grad(), fn::from_numpy(gold + "conv2d_wgrad" + e + ".npy"), 1e-4, 1e-5));
+        });
+    }
+
+    run_test("unfold2d (golden)", [&] {
+        Tensor x = fn::from_numpy(gold + "unfold_input.npy");
+        fn::ConvArgs args;
+        args.ph = args.pw = 1; args.sh = args.sw = 2; args.dh = 1; args.dw = 2;
+        Tensor col = fn::unfold2d(x, 3, 2, args);
+        REQUIRE(fn::allclose(col, fn::from_numpy(gold + "unfold_output.npy"), 0, 0));
+        Tensor dx = fn::unfold2d_backward(fn::from_numpy(gold + "unfold_grad.npy"), 8, 8, 3, 2, args);
+        REQUIRE(fn::allclose(dx, fn::from_numpy(gold + "unfold_input_grad.npy"), 1e-5, 1e-6));
+    });
+
+    run_test("MLP through layers::Linear, relu and loss::MSE: forward + backward", [] {
+        const int64_t B = 64, D = 48, H = 96;
+        nt::layers::Linear l1(D, H, true, DType::Float32, 1), l2(H, D, true, DType::Float32, 2);
+        REQUIRE(l1.Weight.shape() == SizeRef({D, H}) && !l1.Weight.detach().is_mutable());
+        Tensor xt = nt::randn_seeded({B, D}, DType::Float32, 3), target = nt::randn_seeded({B, D}, DType::Float32, 4);
+        TensorGrad x(xt, true);
+        TensorGrad y = l2(fn::relu(l1(x)));
+        nt::ScalarGrad loss = nt::loss::MSE(y, target);
+        loss.backward();
+        // plain fp64 restatement on the host
+        auto X = xt.to_vector<float>(), T = target.to_vector<float>();
+        auto W1 = l1.Weight.detach().to_vector<float>(), B1 = l1.Bias.detach().to_vector<float>();
+        auto W2 = l2.Weight.detach().to_vector<float>(), B2 = l2.Bias.detach().to_vector<float>();
+        std::vector<double> Hh(B * H), A(B * H), Y(B * D), dY(B * D), dA(B * H, 0.0), dW2(H * D, 0.0), dW1(D * H, 0.0), dX(B * D, 0.0);
+        double lossv = 0;
+        for (int64_t i = 0; i < B; ++i)
+            for (int64_t j = 0; j < H; ++j) {
+                double s = B1[j];
+                for (int64_t k = 0; k < D; ++k) s += double(X[i * D + k]) * W1[k * H + j];
+                Hh[i * H + j] = s;
+                A[i * H + j] = s > 0 ? s : 0;
+            }
+        for (int64_t i = 0; i < B; ++i)
+            for (int64_t j = 0; j < D; ++j) {
+                double s = B2[j];
+                for (int64_t k = 0; k < H; ++k) s += A[i * H + k] * W2[k * D + j];
+                Y[i * D + j] = s;
+                const double d = s - T[i * D + j];
+                lossv += d * d;
+                dY[i * D + j] = 2 * d / double(B * D);
+            }
+        lossv /= double(B * D);
+        for (int64_t i = 0; i < B; ++i)
+            for (int64_t k = 0; k < H; ++k) {
+                double s = 0;
+                for (int64_t j = 0; j < D; ++j) { s += dY[i * D + j] * W2[k * D + j]; dW2[k * D + j] += A[i * H + k] * dY[i * D + j]; }
+                dA[i * H + k] = Hh[i * H + k] < 0 ? 0 : s;
+            }
+        for (int64_t i = 0; i < B; ++i)
+            for (int64_t k = 0; k < D; ++k) {
+                double s = 0;
+                for (int64_t j = 0; j < H; ++j) { s += dA[i * H + j] * W1[k * H + j]; dW1[k * H + j] += double(X[i * D + k]) * dA[i * H + j]; }
+                dX[i * D + k] = s;
+            }
+        auto close = [](const std::vector<float>& got, const std::vector<double>& exp) {
+            double num = 0, den = 0;
+            for (size_t i = 0; i < got.size(); ++i) { num += (got[i] - exp[i]) * (got[i] - exp[i]); den += exp[i] * exp[i]; }
+            return std::sqrt(num / (den > 0 ? den : 1)) <= 1e-5;
+        };
+        REQUIRE(std::fabs(loss.item() - lossv) <= 1e-5 * lossv);
+        REQUIRE(close(y.detach().to_vector<float>(), Y));
+        REQUIRE(close(l2.Weight.grad().to_vector<float>(), dW2));
+        REQUIRE(close(l1.Weight.grad().to_vector<float>(), dW1));
+        REQUIRE(close(x.grad().to_vector<float>(), dX));
+        REQUIRE(l1.Bias.grad().shape() == SizeRef({H}) && l2.Bias.grad().shape() == SizeRef({D}));
+    });
+
+    run_test("BFloat16 MLP step runs on tensor cores", [] {
+        nt::layers::Linear l1(256, 512, true, DType::BFloat16, 5), l2(512, 256, true, DType::BFloat16, 6);
+        TensorGrad x(nt::randn_seeded({256, 256}, DType::BFloat16, 7), false);
+        Tensor target = nt::randn_seeded({256, 256}, DType::BFloat16, 8);
+        TensorGrad y = l2(fn::relu(l1(x)));
+        REQUIRE(std::string(ntb200_last_gemm_route()) == "umma_bf16");
+        nt::ScalarGrad loss = nt::loss::MSE(y, target);
+        REQUIRE(std::isfinite(loss.item()) && loss.item() > 0);
+        loss.backward();
+        REQUIRE(l1.Weight.grad().shape() == SizeRef({256, 512}) && l2.Weight.grad().shape() == SizeRef({512, 256}));
+        REQUIRE(!x.has_grad());  // the input does not track a gradient
+    });
+
+    nt::utils::check(ntb200_check_device_status(nullptr));
+    std::printf("%d of %d cases failed\n", g_failed, g_run);
+    return g_failed ? 1 : 0;
+}
