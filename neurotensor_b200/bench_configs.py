@@ -1,0 +1,195 @@
+"""Times every BASELINE configuration of the matmult path on one GPU and prints one JSON line per row.
+
+    python -m neurotensor_b200.bench_configs [--steps K] [--cpu] [--only c1,c3i8,...]
+
+Rows: c1 (Float32 1024^3), c2 (batched Float16 64x2048^3, transposed-view B), c3i8 (Int8 4096x8192x4096),
+c3i32 (Int32 2048^3), c4 (BFloat16 MLP 8192 x 4096->16384->4096: forward + backward step), c5 (Float16 conv2d
+[32,256,56,56] * [256,256,3,3]), sweepN (Float32 N^3).  Inputs are seeded synthetic tensors of the stated shapes
+and distributions, resident on the device; time is CUDA events over K launches after 3 warm-ups.  `--cpu` also
+times the CPU oracle on a bounded sub-problem of each row (test infrastructure, scaled linearly, stated per row).
+"""
+import argparse
+import json
+import os
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from neurotensor_b200 import _lib, api  # noqa: E402
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return float(d["bf16_tflops"]), float(d["hbm_gbs"]), "measured"
+    return 1590.0, 6650.0, "fallback"
+
+
+def timed(fn, steps, warm=3):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    l0 = _lib.launch_count()
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps * 1e-3, (_lib.launch_count() - l0) // steps
+
+
+def randn(gen, shape, dtype, scale=1.0):
+    return (torch.randn(shape, generator=gen, device="cuda") * scale).to(dtype)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--cpu", action="store_true")
+    ap.add_argument("--only", default="")
+    args = ap.parse_args()
+    only = set(filter(None, args.only.split(",")))
+    tensor_peak, hbm_peak, src = peaks()
+    sm_clock_ghz = 1.965
+    ffma_peak = 148 * 128 * 2 * sm_clock_ghz / 1e3  # TFLOP/s at the maximum SM clock
+    rows = []
+
+    def emit(name, seconds, flops, alg_bytes, bound, launches, note="", cpu=None):
+        tf = flops / seconds / 1e12
+        gbs = alg_bytes / seconds / 1e9
+        peak = {"tensor": tensor_peak, "tensor_i8": 2 * tensor_peak, "ffma": ffma_peak, "imad": ffma_peak / 2}.get(bound)
+        row = {"config": name, "ms": seconds * 1e3, "tflops_or_tops": tf, "algorithmic_GBps": gbs, "bound": bound,
+               "frac_of_peak": (tf / peak) if peak else gbs / hbm_peak, "peak": peak if peak else hbm_peak,
+               "peak_source": src if bound.startswith("tensor") or bound == "hbm" else "derived: SMs x lanes x 2 x max clock",
+               "launches_per_step": launches, "route": _lib.last_route(), "note": note}
+        if cpu:
+            row["cpu_oracle"] = cpu
+        rows.append(row)
+        print(json.dumps(row), flush=True)
+
+    def cpu_time(fn, scale, what):
+        if not args.cpu:
+            return None
+        from oracle import oracle
+        fn(oracle)  # warm-up
+        t0 = time.perf_counter()
+        fn(oracle)
+        dt = time.perf_counter() - t0
+        return {"seconds_scaled": dt * scale, "sample": what, "threads": oracle.default_threads()}
+
+    gen = torch.Generator(device="cuda").manual_seed(1)
+    want = lambda n: not only or n in only
+
+    if want("c1"):
+        a, b = randn(gen, (1024, 1024), torch.float32), randn(gen, (1024, 1024), torch.float32)
+        c = torch.empty((1024, 1024), device="cuda")
+        s, l = timed(lambda: api.gemm(a, b, c), args.steps * 5)
+        an, bn = a.cpu().numpy(), b.cpu().numpy()
+        emit("c1 Float32 1024^3", s, 2 * 1024 ** 3, 3 * 4 * 1024 ** 2, "ffma", l, "latency-sized problem: 64 CTAs",
+             cpu_time(lambda o: o.matmult(an, bn), 1, "full problem"))
+
+    if want("c2"):
+        a, bs = randn(gen, (64, 2048, 2048), torch.float16, 0.1), randn(gen, (64, 2048, 2048), torch.float16, 0.1)
+        c = torch.empty((64, 2048, 2048), dtype=torch.float16, device="cuda")
+        s, l = timed(lambda: api.gemm(a, bs.transpose(-1, -2), c), args.steps)
+        an, bn = a[:1].cpu().numpy(), bs[:1].cpu().numpy()
+        emit("c2 batched Float16 64x2048^3, B transposed view", s, 64 * 2 * 2048 ** 3, 3 * 64 * 2048 ** 2 * 2, "tensor", l, "",
+             cpu_time(lambda o: o.matmult(an, bn, False, True), 64, "1 of 64 items, scaled x64"))
+        del a, bs, c
+
+    if want("c3i8"):
+        a = torch.randint(-8, 8, (4096, 8192), generator=gen, device="cuda", dtype=torch.int8)
+        b = torch.randint(-8, 8, (8192, 4096), generator=gen, device="cuda", dtype=torch.int8)
+        c = torch.empty((4096, 4096), dtype=torch.int8, device="cuda")
+        s, l = timed(lambda: api.gemm(a, b, c), args.steps)
+        an, bn = a[:512].cpu().numpy(), b.cpu().numpy()
+        emit("c3 Int8 4096x8192x4096 (int8 out, wrap)", s, 2 * 4096 * 8192 * 4096, 2 * 4096 * 8192 + 4096 * 4096, "tensor_i8", l,
+             "peak taken as 2x the measured bf16 figure (nominal ratio), not measured",
+             cpu_time(lambda o: o.matmult(an, bn), 8, "512 of 4096 rows, scaled x8"))
+
+    if want("c3i32"):
+        a = torch.randint(-1000, 1001, (2048, 2048), generator=gen, device="cuda", dtype=torch.int32)
+        b = torch.randint(-1000, 1001, (2048, 2048), generator=gen, device="cuda", dtype=torch.int32)
+        c = torch.empty((2048, 2048), dtype=torch.int32, device="cuda")
+        s, l = timed(lambda: api.gemm(a, b, c), args.steps)
+        an, bn = a.cpu().numpy(), b.cpu().numpy()
+        emit("c3 Int32 2048^3 (wrap)", s, 2 * 2048 ** 3, 3 * 4 * 2048 ** 2, "imad", l, "IMAD at half the FFMA rate",
+             cpu_time(lambda o: o.matmult(an, bn), 1, "full problem"))
+
+    if want("c4"):
+        B, D, H = 8192, 4096, 16384
+        dt = torch.bfloat16
+        x, t = randn(gen, (B, D), dt), randn(gen, (B, D), dt)
+        w1, w2 = randn(gen, (D, H), dt, D ** -0.5), randn(gen, (H, D), dt, H ** -0.5)
+        b1, b2 = randn(gen, (H,), dt, 0.01), randn(gen, (D,), dt, 0.01)
+
+        def step():
+            h = api.linear(x, w1, b1)
+            a = api.relu(h)
+            y = api.linear(a, w2, b2)
+            loss, dy = api.mse(y, t)
+            da, gw2 = api.matmult_backward(a, w2, dy)
+            dh = api.relu_backward(h, da)
+            gw1 = api.matmult(x, dh, True, False)          # the input does not track a gradient: no dX GEMM
+            api.column_sum(dy), api.column_sum(dh)
+            return loss
+
+        s, l = timed(step, max(3, args.steps // 4))
+        flops = 5 * 2 * B * D * H
+        xn, wn = x[:256].view(torch.int16).cpu().numpy().view("uint16"), w1.view(torch.int16).cpu().numpy().view("uint16")
+        emit("c4 BFloat16 MLP 8192x(4096->16384->4096) fwd+bwd step (5 GEMMs + elementwise)", s, flops,
+             0, "tensor", l, "GEMM flops only (5 x 1.0995e12); elementwise kernels are inside the time",
+             cpu_time(lambda o: o.matmult(xn, wn, bf16=True), 32 * 5, "256 of 8192 rows of one GEMM, scaled x32 x5 GEMMs"))
+        # GEMM-only time of the same five contractions
+        h = api.linear(x, w1, b1); a = api.relu(h); y = api.linear(a, w2, b2); _, dy = api.mse(y, t)
+        da = api.matmult(dy, w2, False, True); dh = api.relu_backward(h, da)
+
+        def gemms():
+            api.linear(x, w1, b1); api.linear(a, w2, b2)
+            api.matmult(dy, w2, False, True); api.matmult(a, dy, True, False); api.matmult(x, dh, True, False)
+
+        s, l = timed(gemms, max(3, args.steps // 4))
+        emit("c4 the five GEMMs alone", s, flops, 0, "tensor", l)
+        del x, t, w1, w2, h, a, y, dy, da, dh
+
+    if want("c5"):
+        x = randn(gen, (32, 256, 56, 56), torch.float16)
+        w = randn(gen, (256, 256, 3, 3), torch.float16, (256 * 9) ** -0.5)
+        ws = torch.empty(32 * 2304 * 3136 * 2, dtype=torch.uint8, device="cuda")
+        s, l = timed(lambda: api.conv2d(x, w, 1, 1, workspace=ws), args.steps)
+        flops = 2 * 256 * 2304 * 32 * 3136
+        xn, wn = x[:1].cpu().numpy(), w.cpu().numpy()
+        emit("c5 Float16 conv2d [32,256,56,56]*[256,256,3,3] s1 p1 (im2col + GEMM)", s, flops, (51.4e6 + 1.18e6 + 51.4e6), "tensor", l,
+             "", cpu_time(lambda o: o.conv2d(xn, wn, 1, 1), 32, "1 of 32 images, scaled x32"))
+        s2, l2 = timed(lambda: api.unfold2d(x, (3, 3), 1, 1, 1), args.steps)
+        emit("c5 im2col alone (writes the 462 MB column matrix)", s2, 0, 51.4e6 + 462.4e6, "hbm", l2)
+        col = api.unfold2d(x, (3, 3), 1, 1, 1)
+        out = torch.empty((32, 256, 3136), dtype=torch.float16, device="cuda")
+        w2d = w.reshape(256, 2304)
+        s3, l3 = timed(lambda: api.gemm(w2d, col, out), args.steps)
+        emit("c5 GEMM alone: w[256,2304] x col[32,2304,3136]", s3, flops, 0, "tensor", l3)
+        del col, out
+        del x, w, ws
+
+    for n in (512, 1024, 2048, 4096, 8192, 16384):
+        if not want("sweep%d" % n) and not (not only):
+            continue
+        if only and "sweep%d" % n not in only:
+            continue
+        a, b = randn(gen, (n, n), torch.float32), randn(gen, (n, n), torch.float32)
+        c = torch.empty((n, n), device="cuda")
+        s, l = timed(lambda: api.gemm(a, b, c), max(2, args.steps // (1 if n <= 4096 else 5)))
+        emit("sweep Float32 %d^3" % n, s, 2 * n ** 3, 12 * n * n, "ffma", l)
+        del a, b, c
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -35,22 +35,117 @@ struct ConvGeom {
     long long batch, channels, height, width, kh, kw, sh, sw, ph, pw, dh, dw, hc, wc;
 };
 
-// One thread per column-matrix element; consecutive threads walk the output pixels (coalesced stores, and
-// for unit stride near-contiguous loads).  T is an unsigned integer of the element's size: pure byte moves.
-template <class T>
+// Column-matrix writer.  Each thread produces V = 16 / sizeof(T) consecutive output pixels of one column-matrix row
+// (one (channel, tap) pair of one image) and writes them with a single 16-byte store; consecutive threads write
+// consecutive 16-byte segments, so stores are fully coalesced, and for unit stride the loads of a warp cover a
+// contiguous run of the image.  The (batch, row, pixel) decomposition is done once per vector in index type I
+// (32-bit whenever the element counts allow it).  T is an unsigned integer of the element's size: pure byte moves.
+template <class T, class I, int V>
 __global__ void im2col_kernel(const T* __restrict__ im, T* __restrict__ col, const ConvGeom g) {
-    const long long L = g.hc * g.wc, ccol = g.channels * g.kh * g.kw;
-    const long long total = g.batch * ccol * L;
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-        const long long l = i % L, c = (i / L) % ccol, b = i / (L * ccol);
-        const long long w = l % g.wc, h = l / g.wc;
-        const long long w_off = c % g.kw, h_off = (c / g.kw) % g.kh, c_im = c / (g.kh * g.kw);
-        const long long hp = h * g.sh - g.ph + h_off * g.dh, wp = w * g.sw - g.pw + w_off * g.dw;
-        T v = T(0);
-        if (hp >= 0 && hp < g.height && wp >= 0 && wp < g.width)
-            v = im[((b * g.channels + c_im) * g.height + hp) * g.width + wp];
-        col[i] = v;
+    const I L = I(g.hc * g.wc), ccol = I(g.channels * g.kh * g.kw), wc = I(g.wc), kw = I(g.kw), kh = I(g.kh);
+    const I vec_per_row = L / V;  // V divides L on this path (V == 1 otherwise)
+    const I total_vec = I(g.batch) * ccol * vec_per_row;
+    const I height = I(g.height), width = I(g.width);
+    const I sh = I(g.sh), sw = I(g.sw), ph = I(g.ph), pw = I(g.pw), dh = I(g.dh), dw = I(g.dw);
+    for (I v = I(blockIdx.x) * I(blockDim.x) + I(threadIdx.x); v < total_vec; v += I(gridDim.x) * I(blockDim.x)) {
+        const I lv = v % vec_per_row, row = v / vec_per_row;   // row = b * ccol + c
+        const I c = row % ccol, b = row / ccol;
+        const I w_off = c % kw, h_off = (c / kw) % kh, c_im = c / (kh * kw);
+        const I l0 = lv * V;
+        I h = l0 / wc, w = l0 - h * wc;
+        const T* plane = im + (I(b) * I(g.channels) + c_im) * height * width;
+        __align__(16) T out[V];
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+            const I hp = h * sh - ph + h_off * dh, wp = w * sw - pw + w_off * dw;
+            T val = T(0);
+            if (hp >= 0 && hp < height && wp >= 0 && wp < width) val = plane[hp * width + wp];
+            out[j] = val;
+            if (++w == wc) { w = 0; ++h; }
+        }
+        T* dst = col + row * L + l0;
+        if constexpr (V * sizeof(T) == 16) {
+            *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(out);
+        } else {
+#pragma unroll
+            for (int j = 0; j < V; ++j) dst[j] = out[j];
+        }
     }
+}
+
+// Same result, staged through shared memory: one CTA owns one (image, channel) plane, reads it from HBM once with
+// coalesced loads, and writes the kh*kw column-matrix rows that are built from it (each a shifted, zero-padded
+// copy of the plane) with 16-byte stores.  Global loads drop by kh*kw and the kernel is bound by the column-matrix
+// write.  Requires the output width to be a multiple of the vector width V, so a vector never straddles two output
+// rows: a thread keeps one vector column and walks down the output rows, so the inner loop has no division and a
+// single row test per vector.
+template <class T, int V>
+__global__ void im2col_plane_kernel(const T* __restrict__ im, T* __restrict__ col, const ConvGeom g) {
+    extern __shared__ __align__(16) unsigned char plane_raw[];
+    T* plane = reinterpret_cast<T*>(plane_raw);
+    const int c_im = blockIdx.x, b = blockIdx.y;
+    const int height = int(g.height), width = int(g.width), wc = int(g.wc), hc = int(g.hc), L = hc * wc;
+    const int kh = int(g.kh), kw = int(g.kw);
+    const int sh = int(g.sh), sw = int(g.sw), ph = int(g.ph), pw = int(g.pw), dh = int(g.dh), dw = int(g.dw);
+    const int plane_elems = height * width;
+    const T* src = im + ((long long)b * g.channels + c_im) * plane_elems;
+    if ((reinterpret_cast<uintptr_t>(src) % 16 == 0) && (plane_elems % V == 0)) {
+        for (int i = threadIdx.x; i < plane_elems / V; i += blockDim.x)
+            reinterpret_cast<uint4*>(plane)[i] = reinterpret_cast<const uint4*>(src)[i];
+    } else {
+        for (int i = threadIdx.x; i < plane_elems; i += blockDim.x) plane[i] = src[i];
+    }
+    __syncthreads();
+    const int vec_per_wrow = wc / V;                       // vectors per output row
+    const int rows_per_pass = blockDim.x / vec_per_wrow;   // >= 1 (checked by the launcher)
+    const int hv = threadIdx.x / vec_per_wrow, wv = threadIdx.x - hv * vec_per_wrow;
+    if (hv >= rows_per_pass) return;
+    const int w0 = wv * V;
+    T* dst_base = col + ((long long)b * g.channels + c_im) * (kh * kw) * (long long)L + w0;
+    for (int h_off = 0; h_off < kh; ++h_off) {
+        for (int w_off = 0; w_off < kw; ++w_off) {
+            T* dst_tap = dst_base + (long long)(h_off * kw + w_off) * L;
+            const int wp0 = w0 * sw - pw + w_off * dw;
+            for (int h = hv; h < hc; h += rows_per_pass) {
+                const int hp = h * sh - ph + h_off * dh;
+                __align__(16) T out[V];
+                if (hp >= 0 && hp < height) {
+                    const T* row = plane + hp * width;
+#pragma unroll
+                    for (int j = 0; j < V; ++j) {
+                        const int wp = wp0 + j * sw;
+                        out[j] = (unsigned(wp) < unsigned(width)) ? row[wp] : T(0);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < V; ++j) out[j] = T(0);
+                }
+                *reinterpret_cast<uint4*>(dst_tap + h * wc) = *reinterpret_cast<const uint4*>(out);
+            }
+        }
+    }
+}
+
+template <class T>
+void launch_im2col(const void* im, void* col, const ConvGeom& g, cudaStream_t s) {
+    constexpr int V = 16 / int(sizeof(T));
+    const long long L = g.hc * g.wc, total = g.batch * g.channels * g.kh * g.kw * L;
+    const long long im_elems = g.batch * g.channels * g.height * g.width;
+    const bool small = total < (1ll << 31) && im_elems < (1ll << 31);
+    const bool vec = (L % V == 0) && (reinterpret_cast<uintptr_t>(col) % 16 == 0);
+    const long long work = vec ? total / V : total;
+    const int blocks = grid_for(work, 256);
+    const T* src = static_cast<const T*>(im);
+    T* dst = static_cast<T*>(col);
+    const long long plane_bytes = g.height * g.width * (long long)sizeof(T);
+    if (vec && small && plane_bytes <= 40 * 1024 && g.batch <= 65535 && g.kh * g.kw > 1 && g.wc % V == 0 && g.wc / V <= 256) {
+        im2col_plane_kernel<T, V><<<dim3(unsigned(g.channels), unsigned(g.batch)), 256, size_t((plane_bytes + 15) / 16 * 16), s>>>(src, dst, g);
+        return;
+    }
+    if (vec && small) im2col_kernel<T, int, V><<<blocks, 256, 0, s>>>(src, dst, g);
+    else if (vec) im2col_kernel<T, long long, V><<<blocks, 256, 0, s>>>(src, dst, g);
+    else if (small) im2col_kernel<T, int, 1><<<blocks, 256, 0, s>>>(src, dst, g);
+    else im2col_kernel<T, long long, 1><<<blocks, 256, 0, s>>>(src, dst, g);
 }
 
 // Gather form of col2im: each image element sums the taps that read it (no atomics, deterministic).
@@ -78,6 +173,52 @@ __global__ void col2im_kernel(const T* __restrict__ col, T* __restrict__ im, con
         }
         im[i] = F<T>::st(acc);
     }
+}
+
+// 16-byte vector forms of the elementwise kernels (n a multiple of the vector width, pointers 16-byte aligned).
+template <class T> struct Vec16 { static constexpr int N = 16 / int(sizeof(T)); T v[N]; };
+
+template <class T>
+__global__ void relu_vec_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, long long nvec) {
+    using VT = Vec16<T>;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+        uint4 raw = x[i];
+        VT& a = *reinterpret_cast<VT*>(&raw);
+#pragma unroll
+        for (int j = 0; j < VT::N; ++j)
+            if (F<T>::ld(a.v[j]) < 0.f) a.v[j] = F<T>::st(0.f);
+        y[i] = raw;
+    }
+}
+template <class T>
+__global__ void relu_backward_vec_kernel(const uint4* __restrict__ x, const uint4* __restrict__ go, uint4* __restrict__ gi,
+                                         long long nvec) {
+    using VT = Vec16<T>;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+        uint4 rx = x[i], rg = go[i];
+        const VT& a = *reinterpret_cast<const VT*>(&rx);
+        VT& g = *reinterpret_cast<VT*>(&rg);
+#pragma unroll
+        for (int j = 0; j < VT::N; ++j)
+            if (F<T>::ld(a.v[j]) < 0.f) g.v[j] = F<T>::st(0.f);
+        gi[i] = rg;
+    }
+}
+template <class T>
+__global__ void add_inplace_vec_kernel(uint4* __restrict__ y, const uint4* __restrict__ x, long long nvec) {
+    using VT = Vec16<T>;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+        uint4 ry = y[i], rx = x[i];
+        VT& a = *reinterpret_cast<VT*>(&ry);
+        const VT& b = *reinterpret_cast<const VT*>(&rx);
+#pragma unroll
+        for (int j = 0; j < VT::N; ++j) a.v[j] = F<T>::st(F<T>::ld(a.v[j]) + F<T>::ld(b.v[j]));
+        y[i] = ry;
+    }
+}
+inline bool vec_ok(long long n, int elem_size, const void* a, const void* b = nullptr, const void* c = nullptr) {
+    auto al = [](const void* p) { return p == nullptr || reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+    return n % (16 / elem_size) == 0 && al(a) && al(b) && al(c);
 }
 
 template <class T>
@@ -210,12 +351,11 @@ int ntb200_im2col(int dtype, const void* im, void* col, int64_t batch, int64_t c
     if (total == 0) return NTB200_OK;
     if (!im || !col) return fail(NTB200_ERR_INVALID_ARG, "im2col: null pointer");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const int blocks = grid_for(total, 256);
     switch (dtype_size(dtype)) {
-        case 1: im2col_kernel<uint8_t><<<blocks, 256, 0, s>>>((const uint8_t*)im, (uint8_t*)col, g); break;
-        case 2: im2col_kernel<uint16_t><<<blocks, 256, 0, s>>>((const uint16_t*)im, (uint16_t*)col, g); break;
-        case 4: im2col_kernel<uint32_t><<<blocks, 256, 0, s>>>((const uint32_t*)im, (uint32_t*)col, g); break;
-        case 8: im2col_kernel<unsigned long long><<<blocks, 256, 0, s>>>((const unsigned long long*)im, (unsigned long long*)col, g); break;
+        case 1: launch_im2col<uint8_t>(im, col, g, s); break;
+        case 2: launch_im2col<uint16_t>(im, col, g, s); break;
+        case 4: launch_im2col<uint32_t>(im, col, g, s); break;
+        case 8: launch_im2col<unsigned long long>(im, col, g, s); break;
         default: return fail(NTB200_ERR_UNSUPPORTED, "im2col: unknown dtype %d", dtype);
     }
     count_launch();
@@ -246,7 +386,13 @@ int ntb200_relu(int dtype, const void* x, void* y, int64_t n, void* stream) {
     if (!x || !y) return fail(NTB200_ERR_INVALID_ARG, "relu: null pointer");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const int blocks = grid_for(n, 1024);
-    NTB200_FLOAT_SWITCH(dtype, (relu_kernel<T><<<blocks, 256, 0, s>>>((const T*)x, (T*)y, n)));
+    if (vec_ok(n, int(dtype_size(dtype)), x, y)) {
+        const long long nvec = n / (16 / (long long)dtype_size(dtype));
+        const int vb = grid_for(nvec, 256);
+        NTB200_FLOAT_SWITCH(dtype, (relu_vec_kernel<T><<<vb, 256, 0, s>>>((const uint4*)x, (uint4*)y, nvec)));
+    } else {
+        NTB200_FLOAT_SWITCH(dtype, (relu_kernel<T><<<blocks, 256, 0, s>>>((const T*)x, (T*)y, n)));
+    }
     count_launch();
     NTB200_CUDA(cudaGetLastError());
     return NTB200_OK;
@@ -258,7 +404,13 @@ int ntb200_relu_backward(int dtype, const void* x, const void* grad_out, void* g
     if (!x || !grad_out || !grad_in) return fail(NTB200_ERR_INVALID_ARG, "relu_backward: null pointer");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const int blocks = grid_for(n, 1024);
-    NTB200_FLOAT_SWITCH(dtype, (relu_backward_kernel<T><<<blocks, 256, 0, s>>>((const T*)x, (const T*)grad_out, (T*)grad_in, n)));
+    if (vec_ok(n, int(dtype_size(dtype)), x, grad_out, grad_in)) {
+        const long long nvec = n / (16 / (long long)dtype_size(dtype));
+        const int vb = grid_for(nvec, 256);
+        NTB200_FLOAT_SWITCH(dtype, (relu_backward_vec_kernel<T><<<vb, 256, 0, s>>>((const uint4*)x, (const uint4*)grad_out, (uint4*)grad_in, nvec)));
+    } else {
+        NTB200_FLOAT_SWITCH(dtype, (relu_backward_kernel<T><<<blocks, 256, 0, s>>>((const T*)x, (const T*)grad_out, (T*)grad_in, n)));
+    }
     count_launch();
     NTB200_CUDA(cudaGetLastError());
     return NTB200_OK;
@@ -299,7 +451,13 @@ int ntb200_add_inplace(int dtype, void* y, const void* x, int64_t n, void* strea
     if (dtype == NTB200_I32 || dtype == NTB200_U32) {
         add_inplace_i32_kernel<<<blocks, 256, 0, s>>>((unsigned int*)y, (const unsigned int*)x, n);
     } else {
-        NTB200_FLOAT_SWITCH(dtype, (add_inplace_kernel<T><<<blocks, 256, 0, s>>>((T*)y, (const T*)x, n)));
+        if (vec_ok(n, int(dtype_size(dtype)), x, y)) {
+            const long long nvec = n / (16 / (long long)dtype_size(dtype));
+            const int vb = grid_for(nvec, 256);
+            NTB200_FLOAT_SWITCH(dtype, (add_inplace_vec_kernel<T><<<vb, 256, 0, s>>>((uint4*)y, (const uint4*)x, nvec)));
+        } else {
+            NTB200_FLOAT_SWITCH(dtype, (add_inplace_kernel<T><<<blocks, 256, 0, s>>>((T*)y, (const T*)x, n)));
+        }
     }
     count_launch();
     NTB200_CUDA(cudaGetLastError());
