@@ -5,6 +5,7 @@
 #include <algorithm>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <vector>
@@ -57,6 +58,21 @@ const char* dtype_name(int dtype) {
 void count_launch(int n) { g_launches.fetch_add(uint64_t(n), std::memory_order_relaxed); }
 void note_route(const char* name) { t_route = name; }
 
+// The stream-ordered pool keeps freed blocks instead of returning them to the driver at every synchronisation
+// (the default release threshold of 0 turns each allocate/free pair into a real cudaMalloc/cudaFree).
+void keep_pool_memory() {
+    static bool done[64] = {false};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || done[dev]) return;
+    cudaMemPool_t pool;
+    if (cudaDeviceGetDefaultMemPool(&pool, dev) == cudaSuccess) {
+        unsigned long long keep = ~0ull;
+        (void)cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+    }
+    (void)cudaGetLastError();
+    done[dev] = true;
+}
+
 int sm_count() {
     static int cached[64] = {0};
     int dev = 0;
@@ -82,6 +98,13 @@ int run_gemm(GemmArgs g, int route, cudaStream_t stream) {
     if (g.k == 0) {
         if (g.accumulate && !g.bias) return NTB200_OK;  // C += 0
         return launch_fill_c(g, stream);
+    }
+    // Float32: the exact one-chain CUDA-core kernel for small problems (and always with NTB200_FP32_MODE=ffma);
+    // three-TF32-product tensor-core kernel (within 1e-5 relative Frobenius error) once the problem is large
+    // enough to pay for the split pass.
+    if (g.dtype == NTB200_F32 && route == NTB200_ROUTE_AUTO) {
+        static const bool ffma_only = [] { const char* e = getenv("NTB200_FP32_MODE"); return e && std::strcmp(e, "ffma") == 0; }();
+        if (ffma_only || double(g.m) * double(g.n) * double(g.k) * double(g.batch) < 6.0e7) route = NTB200_ROUTE_SIMT;
     }
     if (route != NTB200_ROUTE_SIMT) {
         const char* why = nullptr;
@@ -172,6 +195,7 @@ int ntb200_malloc_async(void** ptr, size_t bytes, void* stream) {
     if (!ptr) return fail(NTB200_ERR_INVALID_ARG, "malloc_async: null pointer");
     *ptr = nullptr;
     if (bytes == 0) return NTB200_OK;
+    keep_pool_memory();
     NTB200_CUDA(cudaMallocAsync(ptr, bytes, static_cast<cudaStream_t>(stream)));
     {
         std::lock_guard<std::mutex> lk(g_pool_mu);

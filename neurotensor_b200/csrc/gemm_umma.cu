@@ -36,13 +36,15 @@ namespace {
 
 constexpr int kBM = 128;
 constexpr int kThreads = 192;
+constexpr int kThreadsSplit = 320;  // Float32 split kernels: 8 epilogue warps hold the running sums in registers
 constexpr int kTmemCols = 512;
 
-enum OutKind : int { kOutF16 = 0, kOutBF16 = 1, kOutI8 = 2 };
+enum OutKind : int { kOutF16 = 0, kOutBF16 = 1, kOutI8 = 2, kOutF32 = 3 };
 
 struct UmmaParams {
     int m, n, k, batch;
     int tiles_m, tiles_n, k_blocks, group_m;
+    int chunk_blocks;        // K blocks accumulated in tensor memory before the epilogue takes the partial sum
     int total_tiles;
     int block_k;             // elements per K block (128 bytes of K)
     uint32_t idesc;
@@ -60,12 +62,13 @@ struct UmmaParams {
     int accumulate, out_kind, c_vec_ok;
 };
 
-template <int BN>
+// kSplit: every operand is staged twice (high and low part of a Float32 split into two TF32 values).
+template <int BN, bool kSplit = false>
 struct Tile {
-    static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
     static constexpr uint32_t kABytes = kBM * 128;
     static constexpr uint32_t kBBytes = BN * 128;
-    static constexpr uint32_t kStageBytes = kABytes + kBBytes;
+    static constexpr uint32_t kStageBytes = (kSplit ? 2u : 1u) * (kABytes + kBBytes);
+    static constexpr int kStages = int(196608u / kStageBytes);   // 4 / 6 / 8 stages, half of that when split
     static constexpr uint32_t kBarrierBytes = 256;
     static constexpr uint32_t kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;
 };
@@ -97,12 +100,64 @@ __device__ __forceinline__ uint32_t from_float_bits16(float v, int out_kind) {
                                : (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v));
 }
 
+// Stores 32 consecutive Float32 results of one row (bias and previous C added first).
+__device__ __forceinline__ void store_chunk_f32(const UmmaParams& p, int b, int row, int col0, const float* f_in) {
+    float f[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) f[j] = f_in[j];
+    if (p.bias) {
+        const float* bias = static_cast<const float*>(p.bias) + (long long)b * p.bias_bs + (long long)row * p.bias_rs;
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (col0 + j < p.n) f[j] += bias[(long long)(col0 + j) * p.bias_cs];
+    }
+    float* dst = static_cast<float*>(p.c) + (long long)b * p.c_bs + (long long)row * p.c_rs + col0;
+    if (col0 + 32 <= p.n && p.c_vec_ok) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            float4 o = make_float4(f[4 * q], f[4 * q + 1], f[4 * q + 2], f[4 * q + 3]);
+            if (p.accumulate) {
+                const float4 old = *reinterpret_cast<const float4*>(dst + 4 * q);
+                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+            }
+            *reinterpret_cast<float4*>(dst + 4 * q) = o;
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (col0 + j < p.n) dst[j] = p.accumulate ? dst[j] + f[j] : f[j];
+    }
+}
+
+// Two-level accumulation for the Float32 split kernels.  The tensor core adds into its fp32 accumulator with
+// truncation, so a long chain drifts (about 2e-8 of the sum per MMA); the MMA warp therefore hands over a partial sum
+// every `chunk_blocks` K blocks and the epilogue threads add the partial sums in registers with round-to-nearest.
+template <int HC>
+__device__ __forceinline__ void drain_partial(uint32_t taddr, float (&run)[HC], bool first) {
+#pragma unroll
+    for (int cc = 0; cc < HC / 32; ++cc) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(taddr + uint32_t(cc * 32), v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            run[cc * 32 + j] = first ? __uint_as_float(v[j]) : run[cc * 32 + j] + __uint_as_float(v[j]);
+    }
+}
+template <int HC>
+__device__ __forceinline__ void store_running(const UmmaParams& p, const float (&run)[HC], int b, int row, int col_base) {
+    if (row >= p.m) return;
+#pragma unroll
+    for (int cc = 0; cc < HC / 32; ++cc)
+        if (col_base + cc * 32 < p.n) store_chunk_f32(p, b, row, col_base + cc * 32, &run[cc * 32]);
+}
+
 // Epilogue of one 128-row accumulator slice: thread `row` of the tile reads its TMEM lane 32 columns at a time,
 // adds the bias and / or the previous C, converts and stores.  `tmem_acc` already carries the warp's lane quadrant
 // and the accumulator's first column.  Executed by whole warps (tcgen05.ld is warp-collective).
 template <int BN>
 __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, uint32_t tmem_acc, int b, int row, int n0) {
-    const int es = (p.out_kind == kOutI8) ? 1 : 2;
+    const int es = (p.out_kind == kOutI8) ? 1 : (p.out_kind == kOutF32 ? 4 : 2);
     const bool row_ok = row < p.m;
     uint8_t* c_row = static_cast<uint8_t*>(p.c) + ((long long)b * p.c_bs + (long long)row * p.c_rs) * es;
 #pragma unroll 1
@@ -148,6 +203,11 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, uint32_t tmem
                         dst[j] = (uint8_t)x;
                     }
             }
+        } else if (p.out_kind == kOutF32) {
+            float f[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+            store_chunk_f32(p, b, row, col0, f);
         } else {
             float f[32];
 #pragma unroll
@@ -195,11 +255,12 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, uint32_t tmem
     }
 }
 
-template <MmaKind kKind, int BN>
-__global__ void __launch_bounds__(kThreads, 1)
+template <MmaKind kKind, int BN, bool kSplit>
+__global__ void __launch_bounds__(kSplit ? kThreadsSplit : kThreads, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                 const __grid_constant__ CUtensorMap tma_a_lo, const __grid_constant__ CUtensorMap tma_b_lo,
                  const UmmaParams p) {
-    using T = Tile<BN>;
+    using T = Tile<BN, kSplit>;
     constexpr int kStages = T::kStages;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -223,7 +284,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(tfull_bar(a), 1);
-            mbar_init(tempty_bar(a), 4);
+            mbar_init(tempty_bar(a), kSplit ? 8 : 4);   // one arrival per epilogue warp
         }
         *abort_flag = 0;
         fence_barrier_init();
@@ -257,10 +318,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                         break;
                     }
                     const uint32_t a_dst = smem_base + stage * T::kStageBytes;
-                    const uint32_t b_dst = a_dst + T::kABytes;
+                    const uint32_t b_dst = a_dst + (kSplit ? 2u : 1u) * T::kABytes;
                     const uint32_t bar = full_bar(stage);
                     mbar_expect_tx(bar, T::kStageBytes);
                     const int k0 = kb * p.block_k;
+                    if constexpr (kSplit) {  // the split copies are dense and K-major
+                        tma_load_3d(a_dst + T::kABytes, &tma_a_lo, bar, k0, m0, b * p.a_batch_mul);
+                        tma_load_3d(b_dst + T::kBBytes, &tma_b_lo, bar, k0, n0, b * p.b_batch_mul);
+                    }
                     if (!p.a_mn_major) {
                         tma_load_3d(a_dst, &tma_a, bar, k0, m0, b * p.a_batch_mul);
                     } else {
@@ -295,14 +360,17 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             int acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
-            for (int t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x) {
+            for (int t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x)
+            for (int kb0 = 0; ok && kb0 < p.k_blocks; kb0 += p.chunk_blocks) {   // one accumulator per K chunk
+                const int kb_end = min(p.k_blocks, kb0 + p.chunk_blocks);
                 if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
                     raise_timeout(abort_flag, 3);
+                    ok = false;
                     break;
                 }
                 tcgen05_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
-                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                for (int kb = kb0; kb < kb_end; ++kb) {
                     if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
                         raise_timeout(abort_flag, 4);
                         ok = false;
@@ -310,12 +378,26 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                     }
                     tcgen05_fence_after();
                     const uint32_t a_addr = smem_base + stage * T::kStageBytes;
+                    const uint32_t b_addr = a_addr + (kSplit ? 2u : 1u) * T::kABytes;
                     const uint64_t a_desc = make_smem_desc_sw128(a_addr, p.a_lbo, 1024);
-                    const uint64_t b_desc = make_smem_desc_sw128(a_addr + T::kABytes, p.b_lbo, 1024);
+                    const uint64_t b_desc = make_smem_desc_sw128(b_addr, p.b_lbo, 1024);
+                    if constexpr (kSplit) {
+                        // a.b ~ a_lo.b_hi + a_hi.b_lo + a_hi.b_hi, all into the same fp32 accumulator
+                        const uint64_t a_lo = make_smem_desc_sw128(a_addr + T::kABytes, p.a_lbo, 1024);
+                        const uint64_t b_lo = make_smem_desc_sw128(b_addr + T::kBBytes, p.b_lbo, 1024);
 #pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        umma<kKind, 1>(d_tmem, a_desc + uint64_t(k * p.a_kstep), b_desc + uint64_t(k * p.b_kstep),
-                                       p.idesc, (kb | k) != 0);
+                        for (int k = 0; k < 4; ++k) {
+                            const uint64_t ka = uint64_t(k * p.a_kstep), kbs = uint64_t(k * p.b_kstep);
+                            umma<kKind, 1>(d_tmem, a_lo + ka, b_desc + kbs, p.idesc, ((kb - kb0) | k) != 0);
+                            umma<kKind, 1>(d_tmem, a_desc + ka, b_lo + kbs, p.idesc, 1);
+                            umma<kKind, 1>(d_tmem, a_desc + ka, b_desc + kbs, p.idesc, 1);
+                        }
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            umma<kKind, 1>(d_tmem, a_desc + uint64_t(k * p.a_kstep), b_desc + uint64_t(k * p.b_kstep),
+                                           p.idesc, ((kb - kb0) | k) != 0);
+                    }
                     umma_commit<1>(empty_bar(stage));  // stage is free once these MMAs have read it
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
@@ -323,6 +405,36 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                 umma_commit<1>(tfull_bar(acc));        // accumulator complete
                 if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
             }
+        }
+    } else if constexpr (kSplit) {
+        // ------------------------------------------------------------------ epilogue, Float32 split: 8 warps, each
+        // thread keeps the running sums of one row x BN/2 columns in registers
+        constexpr int HC = BN / 2;
+        const int quad = warp & 3, half = (warp - 2) >> 2;
+        const int row_in_tile = quad * 32 + lane;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        float run[HC];
+        bool alive = true;
+        for (int t = blockIdx.x; alive && t < p.total_tiles; t += gridDim.x) {
+            int b, mi, ni;
+            tile_coords(p, t, b, mi, ni);
+            for (int kb0 = 0; kb0 < p.k_blocks; kb0 += p.chunk_blocks) {
+                bool ok = mbar_wait(tfull_bar(acc), acc_phase, abort_flag);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) {
+                    if (lane == 0) raise_timeout(abort_flag, 6);
+                    alive = false;
+                    break;
+                }
+                tcgen05_fence_after();
+                drain_partial<HC>(tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN + half * HC), run, kb0 == 0);
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tempty_bar(acc));
+                if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+            }
+            if (alive) store_running<HC>(p, run, b, mi * kBM + row_in_tile, ni * BN + half * HC);
         }
     } else {
         // ------------------------------------------------------------------ epilogue
@@ -368,17 +480,22 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 //   * both CTAs run the epilogue on their own TMEM lanes and hand the accumulator back by arriving on the even
 //     CTA's `tmem_empty` (8 arrivals: 4 warps x 2 CTAs).
 // The loads are per-CTA copies of this GPU's own memory (no multicast).
-constexpr int kPairStages = 6;
 constexpr uint32_t kPairOperandBytes = 128 * 128;                 // 128 rows (or 128 bytes of MN x block_k rows)
-constexpr uint32_t kPairStageBytes = 2 * kPairOperandBytes;       // per CTA
-constexpr uint32_t kPairSmemBytes = kPairStages * kPairStageBytes + 256 + 1024;
+template <bool kSplit>
+struct PairTile {
+    static constexpr uint32_t kStageBytes = (kSplit ? 4u : 2u) * kPairOperandBytes;   // per CTA
+    static constexpr int kStages = int(196608u / kStageBytes);                        // 6, or 3 when split
+    static constexpr uint32_t kSmemBytes = kStages * kStageBytes + 256 + 1024;
+};
 
-template <MmaKind kKind>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+template <MmaKind kKind, bool kSplit>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kSplit ? kThreadsSplit : kThreads, 1)
 umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                      const __grid_constant__ CUtensorMap tma_a_lo, const __grid_constant__ CUtensorMap tma_b_lo,
                       const UmmaParams p) {
     constexpr int BN = 256;
-    constexpr int kStages = kPairStages;
+    constexpr int kStages = PairTile<kSplit>::kStages;
+    constexpr uint32_t kPairStageBytes = PairTile<kSplit>::kStageBytes;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -403,7 +520,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(tfull_bar(a), 1);
-            mbar_init(tempty_bar(a), 8);
+            mbar_init(tempty_bar(a), kSplit ? 16 : 8);   // one arrival per epilogue warp of both CTAs
         }
         *abort_flag = 0;
         fence_barrier_init();
@@ -437,10 +554,14 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
                         break;
                     }
                     const uint32_t a_dst = smem_base + stage * kPairStageBytes;
-                    const uint32_t b_dst = a_dst + kPairOperandBytes;
+                    const uint32_t b_dst = a_dst + (kSplit ? 2u : 1u) * kPairOperandBytes;
                     const uint32_t bar = full_bar(stage);
                     if (leader) mbar_expect_tx(bar, 2 * kPairStageBytes);
                     const int k0 = kb * p.block_k;
+                    if constexpr (kSplit) {
+                        tma_load_3d_pair(a_dst + kPairOperandBytes, &tma_a_lo, bar, k0, m0, b * p.a_batch_mul);
+                        tma_load_3d_pair(b_dst + kPairOperandBytes, &tma_b_lo, bar, k0, n0, b * p.b_batch_mul);
+                    }
                     if (!p.a_mn_major) {
                         tma_load_3d_pair(a_dst, &tma_a, bar, k0, m0, b * p.a_batch_mul);
                     } else {
@@ -473,14 +594,17 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
             int acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
-            for (int t = pair; ok && t < p.total_tiles; t += npairs) {
+            for (int t = pair; ok && t < p.total_tiles; t += npairs)
+            for (int kb0 = 0; ok && kb0 < p.k_blocks; kb0 += p.chunk_blocks) {
+                const int kb_end = min(p.k_blocks, kb0 + p.chunk_blocks);
                 if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
                     raise_timeout(abort_flag, 0x13);
+                    ok = false;
                     break;
                 }
                 tcgen05_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
-                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                for (int kb = kb0; kb < kb_end; ++kb) {
                     if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
                         raise_timeout(abort_flag, 0x14);
                         ok = false;
@@ -488,12 +612,25 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
                     }
                     tcgen05_fence_after();
                     const uint32_t a_addr = smem_base + stage * kPairStageBytes;
+                    const uint32_t b_addr = a_addr + (kSplit ? 2u : 1u) * kPairOperandBytes;
                     const uint64_t a_desc = make_smem_desc_sw128(a_addr, p.a_lbo, 1024);
-                    const uint64_t b_desc = make_smem_desc_sw128(a_addr + kPairOperandBytes, p.b_lbo, 1024);
+                    const uint64_t b_desc = make_smem_desc_sw128(b_addr, p.b_lbo, 1024);
+                    if constexpr (kSplit) {
+                        const uint64_t a_lo = make_smem_desc_sw128(a_addr + kPairOperandBytes, p.a_lbo, 1024);
+                        const uint64_t b_lo = make_smem_desc_sw128(b_addr + kPairOperandBytes, p.b_lbo, 1024);
 #pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        umma<kKind, 2>(d_tmem, a_desc + uint64_t(k * p.a_kstep), b_desc + uint64_t(k * p.b_kstep),
-                                       p.idesc, (kb | k) != 0);
+                        for (int k = 0; k < 4; ++k) {
+                            const uint64_t ka = uint64_t(k * p.a_kstep), kbs = uint64_t(k * p.b_kstep);
+                            umma<kKind, 2>(d_tmem, a_lo + ka, b_desc + kbs, p.idesc, ((kb - kb0) | k) != 0);
+                            umma<kKind, 2>(d_tmem, a_desc + ka, b_lo + kbs, p.idesc, 1);
+                            umma<kKind, 2>(d_tmem, a_desc + ka, b_desc + kbs, p.idesc, 1);
+                        }
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            umma<kKind, 2>(d_tmem, a_desc + uint64_t(k * p.a_kstep), b_desc + uint64_t(k * p.b_kstep),
+                                           p.idesc, ((kb - kb0) | k) != 0);
+                    }
                     umma_commit_pair(empty_bar(stage), 3);
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
@@ -501,6 +638,35 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
                 umma_commit_pair(tfull_bar(acc), 3);
                 if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
             }
+        }
+    } else if constexpr (kSplit) {
+        // ------------------------------------------------------------------ epilogue, Float32 split (both CTAs)
+        constexpr int HC = BN / 2;
+        const int quad = warp & 3, half = (warp - 2) >> 2;
+        const int row_in_tile = int(rank) * 128 + quad * 32 + lane;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        float run[HC];
+        bool alive = true;
+        for (int t = pair; alive && t < p.total_tiles; t += npairs) {
+            int b, mi, ni;
+            tile_coords(p, t, b, mi, ni);
+            for (int kb0 = 0; kb0 < p.k_blocks; kb0 += p.chunk_blocks) {
+                bool ok = mbar_wait(tfull_bar(acc), acc_phase, abort_flag);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) {
+                    if (lane == 0) raise_timeout(abort_flag, 0x16);
+                    alive = false;
+                    break;
+                }
+                tcgen05_fence_after();
+                drain_partial<HC>(tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN + half * HC), run, kb0 == 0);
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_leader(tempty_bar(acc));
+                if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+            }
+            if (alive) store_running<HC>(p, run, b, mi * 256 + row_in_tile, ni * BN + half * HC);
         }
     } else {
         // ------------------------------------------------------------------ epilogue (both CTAs)
@@ -613,8 +779,15 @@ const char* plan_operand(const void* ptr, int es, CUtensorMapDataType dt, int64_
 // NTB200_NO_PAIR=1 keeps every GEMM on the single-CTA kernel (for A/B measurements).
 const bool g_disable_pair = [] { const char* e = getenv("NTB200_NO_PAIR"); return e && e[0] == '1'; }();
 
+// K blocks per partial sum of the Float32 split kernels (NTB200_TF32_CHUNK overrides it for measurements).
+const int g_split_chunk_blocks = [] {
+    const char* e = getenv("NTB200_TF32_CHUNK");
+    const int v = e ? atoi(e) : 0;
+    return v > 0 ? v : 8;
+}();
+
 bool dtype_on_tensor_cores(int dtype) {
-    return dtype == NTB200_F16 || dtype == NTB200_BF16 || dtype == NTB200_I8 || dtype == NTB200_U8;
+    return dtype == NTB200_F16 || dtype == NTB200_BF16 || dtype == NTB200_I8 || dtype == NTB200_U8 || dtype == NTB200_F32;
 }
 
 // Cheap structural test (no driver call): can both operands be staged?
@@ -622,6 +795,11 @@ const char* operands_stageable(const GemmArgs& g) {
     if (!dtype_on_tensor_cores(g.dtype)) return "dtype has no tensor-core kernel";
     if (g.a_ptrs || g.b_ptrs || g.c_ptrs) return "pointer-table batches run on the CUDA-core route";
     if (g.m <= 0 || g.n <= 0 || g.k <= 0 || g.batch <= 0) return "empty problem";
+    if (g.dtype == NTB200_F32) {  // operands are copied (split) first, so any strides do
+        if (g.m > (int64_t(1) << 30) || g.n > (int64_t(1) << 30) || g.k > (int64_t(1) << 30)) return "extent too large";
+        if (g.a_rs < 0 || g.a_cs < 0 || g.a_bs < 0 || g.b_rs < 0 || g.b_cs < 0 || g.b_bs < 0) return "negative stride";
+        return nullptr;
+    }
     const int es = int(dtype_size(g.dtype));
     // s32 accumulation is exact (no overflow) while k * 2^14 < 2^31
     if (es == 1 && g.k > 131071) return "int8 K too large for exact s32 accumulation";
@@ -642,77 +820,121 @@ const char* operands_stageable(const GemmArgs& g) {
     return nullptr;
 }
 
-template <MmaKind kKind, int BN>
-int launch_instance(const OperandPlan& pa, const OperandPlan& pb, const UmmaParams& p, int grid, cudaStream_t stream) {
-    using T = Tile<BN>;
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    // the attribute is per device; set it on every call (cheap) rather than caching per device
-    attr_err = cudaFuncSetAttribute(umma_gemm_kernel<kKind, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    int(T::kSmemBytes));
-    (void)once;
-    if (attr_err != cudaSuccess) return cuda_fail(attr_err, "cudaFuncSetAttribute(umma_gemm_kernel)");
-    umma_gemm_kernel<kKind, BN><<<grid, kThreads, T::kSmemBytes, stream>>>(pa.map, pb.map, p);
+struct Maps {
+    OperandPlan a, b, a_lo, b_lo;
+};
+
+template <MmaKind kKind, int BN, bool kSplit>
+int launch_instance(const Maps& m, const UmmaParams& p, int grid, cudaStream_t stream) {
+    using T = Tile<BN, kSplit>;
+    // the attribute is per device; setting it on every call is cheap
+    cudaError_t e = cudaFuncSetAttribute(umma_gemm_kernel<kKind, BN, kSplit>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         int(T::kSmemBytes));
+    if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(umma_gemm_kernel)");
+    umma_gemm_kernel<kKind, BN, kSplit><<<grid, kSplit ? kThreadsSplit : kThreads, T::kSmemBytes, stream>>>(m.a.map, m.b.map, m.a_lo.map, m.b_lo.map, p);
     count_launch();
     NTB200_CUDA(cudaGetLastError());
     return NTB200_OK;
 }
 
 // Number of CTA pairs that can be resident at once (one pair per TPC).
-int max_resident_pairs(const void* kernel) {
-    static int cached[64] = {0};
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return sm_count() / 2;
-    if (cached[dev] == 0) {
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(unsigned(sm_count() & ~1), 1, 1);
-        cfg.blockDim = dim3(kThreads, 1, 1);
-        cfg.dynamicSmemBytes = kPairSmemBytes;
-        cudaLaunchAttribute attr;
-        attr.id = cudaLaunchAttributeClusterDimension;
-        attr.val.clusterDim.x = 2;
-        attr.val.clusterDim.y = 1;
-        attr.val.clusterDim.z = 1;
-        cfg.attrs = &attr;
-        cfg.numAttrs = 1;
-        int n = 0;
-        if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n <= 0) {
-            (void)cudaGetLastError();
-            n = sm_count() / 2;
-        }
-        cached[dev] = std::min(n, sm_count() / 2);
+int max_resident_pairs(const void* kernel, uint32_t smem_bytes) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(unsigned(sm_count() & ~1), 1, 1);
+    cfg.blockDim = dim3(kThreadsSplit, 1, 1);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n <= 0) {
+        (void)cudaGetLastError();
+        n = sm_count() / 2;
     }
-    return cached[dev];
+    return std::min(n, sm_count() / 2);
 }
 
-template <MmaKind kKind>
-int launch_pair_instance(const OperandPlan& pa, const OperandPlan& pb, const UmmaParams& p, cudaStream_t stream) {
-    cudaError_t e = cudaFuncSetAttribute(umma_gemm_pair_kernel<kKind>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         int(kPairSmemBytes));
+template <MmaKind kKind, bool kSplit>
+int launch_pair_instance(const Maps& m, const UmmaParams& p, cudaStream_t stream) {
+    constexpr uint32_t smem = PairTile<kSplit>::kSmemBytes;
+    cudaError_t e = cudaFuncSetAttribute(umma_gemm_pair_kernel<kKind, kSplit>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
     if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(umma_gemm_pair_kernel)");
-    const int pairs = std::min(p.total_tiles, max_resident_pairs(reinterpret_cast<const void*>(umma_gemm_pair_kernel<kKind>)));
-    umma_gemm_pair_kernel<kKind><<<2 * pairs, kThreads, kPairSmemBytes, stream>>>(pa.map, pb.map, p);
+    static int cached[64] = {0};  // per instantiation, per device
+    int dev = 0;
+    (void)cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    if (cached[dev] == 0)
+        cached[dev] = max_resident_pairs(reinterpret_cast<const void*>(umma_gemm_pair_kernel<kKind, kSplit>), smem);
+    const int pairs = std::min(p.total_tiles, cached[dev]);
+    umma_gemm_pair_kernel<kKind, kSplit><<<2 * pairs, kSplit ? kThreadsSplit : kThreads, smem, stream>>>(m.a.map, m.b.map, m.a_lo.map, m.b_lo.map, p);
     count_launch();
     NTB200_CUDA(cudaGetLastError());
     return NTB200_OK;
 }
 
-}  // namespace
-
-bool umma_supported(const GemmArgs& g, const char** why) {
-    const char* w = operands_stageable(g);
-    if (why) *why = w;
-    return w == nullptr;
+// ---- Float32 as three TF32 products ------------------------------------------------------------------
+// x = hi + lo with hi = x rounded to TF32 (10 explicit mantissa bits) and lo = x - hi (exact in fp32), so that
+// a.b = a_hi.b_hi + a_hi.b_lo + a_lo.b_hi + O(2^-21 |a||b|).  The pre-pass writes hi and lo as dense K-major
+// matrices [batch][rows][k_padded], whatever the strides of the source view, so the GEMM only ever sees one layout.
+__global__ void split_tf32_kernel(const float* __restrict__ src, float* __restrict__ hi, float* __restrict__ lo,
+                                  long long rows, long long cols, long long cols_padded, long long sbs, long long srs,
+                                  long long scs) {
+    __shared__ float tile[32][33];
+    const long long b = blockIdx.z;
+    const long long r0 = (long long)blockIdx.y * 32, c0 = (long long)blockIdx.x * 32;
+    const float* s = src + b * sbs;
+    const bool read_along_cols = (scs == 1 || srs != 1);
+    if (read_along_cols) {
+        for (int j = threadIdx.y; j < 32; j += 8) {
+            const long long r = r0 + j, c = c0 + threadIdx.x;
+            tile[j][threadIdx.x] = (r < rows && c < cols) ? s[r * srs + c * scs] : 0.f;
+        }
+    } else {  // rows are the unit-stride direction of the source
+        for (int j = threadIdx.y; j < 32; j += 8) {
+            const long long r = r0 + threadIdx.x, c = c0 + j;
+            tile[threadIdx.x][j] = (r < rows && c < cols) ? s[r * srs + c * scs] : 0.f;
+        }
+    }
+    __syncthreads();
+    for (int j = threadIdx.y; j < 32; j += 8) {
+        const long long r = r0 + j, c = c0 + threadIdx.x;
+        if (r < rows && c < cols_padded) {
+            const float x = tile[j][threadIdx.x];
+            uint32_t h;
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(x));
+            const float hf = __uint_as_float(h);
+            const float l = (isfinite(x) && isfinite(hf)) ? x - hf : 0.f;
+            const long long o = (b * rows + r) * cols_padded + c;
+            hi[o] = hf;
+            lo[o] = l;
+        }
+    }
 }
 
-int launch_umma_gemm(const GemmArgs& g, cudaStream_t stream) {
-    if (const char* w = operands_stageable(g)) return fail(NTB200_ERR_UNSUPPORTED, "tcgen05 route: %s", w);
-    const int es = int(dtype_size(g.dtype));
-    const bool is_i8 = es == 1;
+struct Planned {
+    int es;
+    CUtensorMapDataType dt;
+    MmaKind kind;
+    int out_kind;
+    uint32_t d_fmt, in_fmt;
+    bool split;
+    const char* route;
+};
+
+// Operands as the tensor-map planner sees them: logical [mn, k] with element strides and a batch stride.
+struct Side {
+    const void* ptr;
+    int64_t mn_stride, k_stride, bs;
+};
+
+int launch_planned(const GemmArgs& g, const Planned& pl, const Side& a, const Side& b, const Side* a_lo, const Side* b_lo,
+                   cudaStream_t stream) {
+    const int es = pl.es;
     const int block_k = 128 / es;
-    const CUtensorMapDataType dt = g.dtype == NTB200_F16    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
-                                   : g.dtype == NTB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
-                                                            : CU_TENSOR_MAP_DATA_TYPE_UINT8;
     // Tile width: the widest one that still gives every SM a tile.
     const int sms = sm_count();
     const int64_t tiles_m = (g.m + kBM - 1) / kBM;
@@ -730,28 +952,42 @@ int launch_umma_gemm(const GemmArgs& g, cudaStream_t stream) {
     const bool use_pair = !g_disable_pair && g.m > 128 && g.n > 128 && pair_tiles >= sms / 2;
     if (use_pair) bn = 256;
 
-    OperandPlan pa, pb;
-    if (const char* w = plan_operand(g.a, es, dt, g.m, g.k, g.a_rs, g.a_cs, g.batch, g.a_bs, kBM, block_k, &pa))
+    Maps maps;
+    if (const char* w = plan_operand(a.ptr, es, pl.dt, g.m, g.k, a.mn_stride, a.k_stride, g.batch, a.bs, kBM, block_k, &maps.a))
         return fail(NTB200_ERR_UNSUPPORTED, "tcgen05 route, A: %s", w);
-    if (const char* w = plan_operand(g.b, es, dt, g.n, g.k, g.b_cs, g.b_rs, g.batch, g.b_bs, use_pair ? 128 : bn,
-                                     block_k, &pb))
+    if (const char* w = plan_operand(b.ptr, es, pl.dt, g.n, g.k, b.mn_stride, b.k_stride, g.batch, b.bs, use_pair ? 128 : bn,
+                                     block_k, &maps.b))
         return fail(NTB200_ERR_UNSUPPORTED, "tcgen05 route, B: %s", w);
     // An N-major operand is staged in chunks of 128 bytes of N: 8-bit tiles cannot be narrower than one chunk.
-    // (The tensor map of an N-major operand does not depend on the tile width, so `pb` stays valid.)
-    if (pb.mn_major && bn < 128 / es) bn = 128 / es;
+    // (The tensor map of an N-major operand does not depend on the tile width, so the plan stays valid.)
+    if (maps.b.mn_major && bn < 128 / es) bn = 128 / es;
+    if (pl.split) {
+        if (const char* w = plan_operand(a_lo->ptr, es, pl.dt, g.m, g.k, a_lo->mn_stride, a_lo->k_stride, g.batch, a_lo->bs, kBM,
+                                         block_k, &maps.a_lo))
+            return fail(NTB200_ERR_UNSUPPORTED, "tcgen05 route, A (low part): %s", w);
+        if (const char* w = plan_operand(b_lo->ptr, es, pl.dt, g.n, g.k, b_lo->mn_stride, b_lo->k_stride, g.batch, b_lo->bs,
+                                         use_pair ? 128 : bn, block_k, &maps.b_lo))
+            return fail(NTB200_ERR_UNSUPPORTED, "tcgen05 route, B (low part): %s", w);
+        if (maps.a.mn_major || maps.b.mn_major || maps.a_lo.mn_major || maps.b_lo.mn_major)
+            return fail(NTB200_ERR_UNSUPPORTED, "tcgen05 route: split operands must be K-major");
+    } else {
+        maps.a_lo = maps.a;
+        maps.b_lo = maps.b;
+    }
 
     UmmaParams p{};
     p.m = int(g.m); p.n = int(g.n); p.k = int(g.k); p.batch = int(g.batch);
     p.tiles_m = use_pair ? int((g.m + 255) / 256) : int(tiles_m);
     p.tiles_n = int((g.n + bn - 1) / bn);
     p.k_blocks = int((g.k + block_k - 1) / block_k);
+    // Float32 split: hand over a partial sum every `g_split_chunk_blocks` K blocks (32 k each)
+    p.chunk_blocks = pl.split ? g_split_chunk_blocks : p.k_blocks;
     p.group_m = 8;
     p.total_tiles = int(int64_t(p.tiles_m) * p.tiles_n * g.batch);
     p.block_k = block_k;
-    const uint32_t in_fmt = g.dtype == NTB200_BF16 ? 1u : (g.dtype == NTB200_I8 ? 1u : 0u);
-    p.idesc = make_instr_desc(is_i8 ? 2u : 1u, in_fmt, in_fmt, pa.mn_major, pb.mn_major, use_pair ? 256u : uint32_t(kBM),
+    p.idesc = make_instr_desc(pl.d_fmt, pl.in_fmt, pl.in_fmt, maps.a.mn_major, maps.b.mn_major, use_pair ? 256u : uint32_t(kBM),
                               uint32_t(bn));
-    p.a_mn_major = pa.mn_major; p.b_mn_major = pb.mn_major;
+    p.a_mn_major = maps.a.mn_major; p.b_mn_major = maps.b.mn_major;
     p.chunk_mn = 128 / es;
     p.chunk_bytes = uint32_t(block_k) * 128u;
     p.a_chunks = kBM / p.chunk_mn;
@@ -759,31 +995,100 @@ int launch_umma_gemm(const GemmArgs& g, cudaStream_t stream) {
     // K-major: rows are 128 bytes, 8-row groups 1024 bytes apart, +32 bytes per MMA along K.
     // MN-major: each K row of a chunk is 128 bytes of MN, 8-row groups 1024 bytes apart (SBO), chunks
     // `chunk_bytes` apart (LBO), and one MMA consumes 32/es K rows.
-    p.a_lbo = pa.mn_major ? p.chunk_bytes : 16u;
-    p.b_lbo = pb.mn_major ? p.chunk_bytes : 16u;
+    p.a_lbo = maps.a.mn_major ? p.chunk_bytes : 16u;
+    p.b_lbo = maps.b.mn_major ? p.chunk_bytes : 16u;
     const uint32_t mn_kstep = uint32_t(32 / es) * 128u / 16u;
-    p.a_kstep = pa.mn_major ? mn_kstep : 2u;
-    p.b_kstep = pb.mn_major ? mn_kstep : 2u;
-    p.a_batch_mul = pa.batch_mul; p.b_batch_mul = pb.batch_mul;
+    p.a_kstep = maps.a.mn_major ? mn_kstep : 2u;
+    p.b_kstep = maps.b.mn_major ? mn_kstep : 2u;
+    p.a_batch_mul = maps.a.batch_mul; p.b_batch_mul = maps.b.batch_mul;
     p.c = g.c; p.c_rs = g.c_rs; p.c_bs = g.c_bs;
     p.bias = g.bias; p.bias_rs = g.bias_rs; p.bias_cs = g.bias_cs; p.bias_bs = g.bias_bs;
     p.accumulate = g.accumulate;
-    p.out_kind = is_i8 ? kOutI8 : (g.dtype == NTB200_F16 ? kOutF16 : kOutBF16);
-    p.c_vec_ok = (reinterpret_cast<uintptr_t>(g.c) % 16 == 0) && ((g.c_rs * es) % 16 == 0) &&
-                 (g.batch == 1 || (g.c_bs * es) % 16 == 0);
+    p.out_kind = pl.out_kind;
+    const int ces = int(dtype_size(g.dtype));
+    p.c_vec_ok = (reinterpret_cast<uintptr_t>(g.c) % 16 == 0) && ((g.c_rs * ces) % 16 == 0) &&
+                 (g.batch == 1 || (g.c_bs * ces) % 16 == 0);
     const int grid = int(std::min<int64_t>(p.total_tiles, sms));
-    note_route(is_i8 ? "umma_i8" : (g.dtype == NTB200_F16 ? "umma_f16" : "umma_bf16"));
-    if (use_pair)
-        return is_i8 ? launch_pair_instance<MmaKind::i8>(pa, pb, p, stream)
-                     : launch_pair_instance<MmaKind::f16>(pa, pb, p, stream);
-    if (is_i8) {
-        if (bn == 256) return launch_instance<MmaKind::i8, 256>(pa, pb, p, grid, stream);
-        if (bn == 128) return launch_instance<MmaKind::i8, 128>(pa, pb, p, grid, stream);
-        return launch_instance<MmaKind::i8, 64>(pa, pb, p, grid, stream);
+    note_route(pl.route);
+    if (pl.kind == MmaKind::tf32) {
+        if (use_pair) return launch_pair_instance<MmaKind::tf32, true>(maps, p, stream);
+        if (bn == 256) return launch_instance<MmaKind::tf32, 256, true>(maps, p, grid, stream);
+        if (bn == 128) return launch_instance<MmaKind::tf32, 128, true>(maps, p, grid, stream);
+        return launch_instance<MmaKind::tf32, 64, true>(maps, p, grid, stream);
     }
-    if (bn == 256) return launch_instance<MmaKind::f16, 256>(pa, pb, p, grid, stream);
-    if (bn == 128) return launch_instance<MmaKind::f16, 128>(pa, pb, p, grid, stream);
-    return launch_instance<MmaKind::f16, 64>(pa, pb, p, grid, stream);
+    if (pl.kind == MmaKind::i8) {
+        if (use_pair) return launch_pair_instance<MmaKind::i8, false>(maps, p, stream);
+        if (bn == 256) return launch_instance<MmaKind::i8, 256, false>(maps, p, grid, stream);
+        if (bn == 128) return launch_instance<MmaKind::i8, 128, false>(maps, p, grid, stream);
+        return launch_instance<MmaKind::i8, 64, false>(maps, p, grid, stream);
+    }
+    if (use_pair) return launch_pair_instance<MmaKind::f16, false>(maps, p, stream);
+    if (bn == 256) return launch_instance<MmaKind::f16, 256, false>(maps, p, grid, stream);
+    if (bn == 128) return launch_instance<MmaKind::f16, 128, false>(maps, p, grid, stream);
+    return launch_instance<MmaKind::f16, 64, false>(maps, p, grid, stream);
+}
+
+// Float32: split both operands into dense K-major hi/lo copies in pool scratch, then one GEMM with three TF32
+// products per K step.  The scratch is returned to the pool in stream order.
+int launch_f32_split(const GemmArgs& g, cudaStream_t stream) {
+    const int64_t kp = (g.k + 3) & ~int64_t(3);  // rows of the copies stay 16-byte aligned
+    const int64_t a_batch = (g.batch > 1 && g.a_bs != 0) ? g.batch : 1;
+    const int64_t b_batch = (g.batch > 1 && g.b_bs != 0) ? g.batch : 1;
+    if (a_batch > 65535 || b_batch > 65535) return fail(NTB200_ERR_UNSUPPORTED, "tcgen05 route: batch too large for the Float32 split pass");
+    const size_t a_elems = size_t(a_batch) * size_t(g.m) * size_t(kp), b_elems = size_t(b_batch) * size_t(g.n) * size_t(kp);
+    float* scratch = nullptr;
+    keep_pool_memory();
+    NTB200_CUDA(cudaMallocAsync(reinterpret_cast<void**>(&scratch), 2 * (a_elems + b_elems) * sizeof(float), stream));
+    float* a_hi = scratch;
+    float* a_lo = a_hi + a_elems;
+    float* b_hi = a_lo + a_elems;
+    float* b_lo = b_hi + b_elems;
+    const dim3 block(32, 8);
+    split_tf32_kernel<<<dim3(unsigned((kp + 31) / 32), unsigned((g.m + 31) / 32), unsigned(a_batch)), block, 0, stream>>>(
+        static_cast<const float*>(g.a), a_hi, a_lo, g.m, g.k, kp, g.a_bs, g.a_rs, g.a_cs);
+    // B is logically [k, n]; its copy is [n][k]: rows = n (source stride b_cs), columns = k (source stride b_rs)
+    split_tf32_kernel<<<dim3(unsigned((kp + 31) / 32), unsigned((g.n + 31) / 32), unsigned(b_batch)), block, 0, stream>>>(
+        static_cast<const float*>(g.b), b_hi, b_lo, g.n, g.k, kp, g.b_bs, g.b_cs, g.b_rs);
+    count_launch(2);
+    cudaError_t e = cudaGetLastError();
+    int rc = NTB200_OK;
+    if (e != cudaSuccess) {
+        rc = cuda_fail(e, "split_tf32_kernel");
+    } else {
+        const Planned pl{4, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, MmaKind::tf32, kOutF32, 1u, 2u, true, "umma_3xtf32"};
+        const Side sa{a_hi, kp, 1, a_batch > 1 ? g.m * kp : 0}, sal{a_lo, kp, 1, a_batch > 1 ? g.m * kp : 0};
+        const Side sb{b_hi, kp, 1, b_batch > 1 ? g.n * kp : 0}, sbl{b_lo, kp, 1, b_batch > 1 ? g.n * kp : 0};
+        rc = launch_planned(g, pl, sa, sb, &sal, &sbl, stream);
+    }
+    cudaFreeAsync(scratch, stream);
+    return rc;
+}
+
+}  // namespace
+
+bool umma_supported(const GemmArgs& g, const char** why) {
+    const char* w = operands_stageable(g);
+    if (why) *why = w;
+    return w == nullptr;
+}
+
+int launch_umma_gemm(const GemmArgs& g, cudaStream_t stream) {
+    if (const char* w = operands_stageable(g)) return fail(NTB200_ERR_UNSUPPORTED, "tcgen05 route: %s", w);
+    if (g.dtype == NTB200_F32) return launch_f32_split(g, stream);
+    const int es = int(dtype_size(g.dtype));
+    const bool is_i8 = es == 1;
+    Planned pl;
+    pl.es = es;
+    pl.dt = g.dtype == NTB200_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+            : g.dtype == NTB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    pl.kind = is_i8 ? MmaKind::i8 : MmaKind::f16;
+    pl.out_kind = is_i8 ? kOutI8 : (g.dtype == NTB200_F16 ? kOutF16 : kOutBF16);
+    pl.d_fmt = is_i8 ? 2u : 1u;
+    pl.in_fmt = g.dtype == NTB200_BF16 ? 1u : (g.dtype == NTB200_I8 ? 1u : 0u);
+    pl.split = false;
+    pl.route = is_i8 ? "umma_i8" : (g.dtype == NTB200_F16 ? "umma_f16" : "umma_bf16");
+    const Side a{g.a, g.a_rs, g.a_cs, g.a_bs}, b{g.b, g.b_cs, g.b_rs, g.b_bs};
+    return launch_planned(g, pl, a, b, nullptr, nullptr, stream);
 }
 
 int read_device_status(cudaStream_t stream) {

@@ -23,6 +23,7 @@ const char* dtype_name(int dtype);
 void count_launch(int n = 1);
 void note_route(const char* name);
 int sm_count();  // multiprocessors of the current device (cached per device)
+void keep_pool_memory();  // once per device: the stream-ordered pool retains freed blocks
 
 // A GEMM after validation: C[b] = (accumulate ? C[b] : 0) + bias + A[b].B[b]; strides in elements.
 struct GemmArgs {

@@ -90,6 +90,10 @@ def test_config5_conv2d_full_size(api, oracle):
 
 @pytest.mark.parametrize("n", [512, 2048])
 def test_config5_f32_sweep_points(api, oracle, n):
+    from neurotensor_b200 import _lib
     rng = np.random.default_rng(16 + n)
     a, b = normal(rng, (n, n), np.float32), normal(rng, (n, n), np.float32)
-    assert np.array_equal(host(api.matmult(dev(a), dev(b))), oracle.matmult(a, b))
+    exp = oracle.matmult(a, b)
+    assert oracle.rel_fro(host(api.matmult(dev(a), dev(b))), exp) <= 1e-5          # tensor cores, 3 x TF32
+    assert _lib.last_route() == "umma_3xtf32"
+    assert np.array_equal(host(api.matmult(dev(a), dev(b), route=_lib.ROUTE_SIMT)), exp)   # CUDA cores: bit-exact

@@ -50,14 +50,55 @@ def test_f32_bit_exact(api, oracle, ta, tb, m, k, n):
 
 
 def test_f32_config_1024(api, oracle, L):
-    """BASELINE config 0: Float32 1024^3, contiguous row-major, N(0,1)."""
+    """BASELINE config 0: Float32 1024^3, contiguous row-major, N(0,1).  The default route is the tensor-core
+    kernel with three TF32 products per multiply (within the 1e-5 bar); the CUDA-core route is bit-exact."""
     rng = np.random.default_rng(1)
     a, b = normal(rng, (1024, 1024), np.float32), normal(rng, (1024, 1024), np.float32)
-    got = host(api.matmult(dev(a), dev(b)))
-    assert L.last_route() == "simt"
     exp = oracle.matmult(a, b)
+    got = host(api.matmult(dev(a), dev(b)))
+    assert L.last_route() == "umma_3xtf32"
+    err = oracle.rel_fro(got, exp)
+    assert err <= F32_TOL, err
+    exact = host(api.matmult(dev(a), dev(b), route=L.ROUTE_SIMT))
+    assert L.last_route() == "simt"
+    assert np.array_equal(exact, exp)
+
+
+@pytest.mark.parametrize("ta,tb", FLAGS)
+@pytest.mark.parametrize("m,k,n", [(128, 32, 64), (257, 130, 255), (384, 1023, 640), (2048, 512, 2304)])
+def test_f32_three_tf32_route(api, oracle, L, ta, tb, m, k, n):
+    """Float32 on tensor cores: any strides (the split pass copies), K not a multiple of 4, M/N tails, pair tiles."""
+    rng = np.random.default_rng(53 + m + k)
+    a, b = operands(rng, m, k, n, ta, tb, np.float32)
+    got = host(api.matmult(dev(a), dev(b), ta, tb, route=L.ROUTE_TENSOR))
+    assert L.last_route() == "umma_3xtf32"
+    err = oracle.rel_fro(got, oracle.matmult(a, b, ta, tb))
+    assert err <= F32_TOL, err
+
+
+def test_f32_three_tf32_bias_accumulate_and_shared_operand(api, oracle, L):
+    rng = np.random.default_rng(59)
+    x, w = normal(rng, (3, 200, 96), np.float32), normal(rng, (96, 136), np.float32)
+    bias, c0 = normal(rng, (136,), np.float32), normal(rng, (3, 200, 136), np.float32)
+    got = host(api.linear(dev(x), dev(w), dev(bias), route=L.ROUTE_TENSOR))
+    assert L.last_route() == "umma_3xtf32"
+    assert oracle.rel_fro(got, oracle.linear(x, w, bias)) <= F32_TOL
+    out = dev(c0)
+    api.matmult(dev(x), dev(w), out=out, route=L.ROUTE_TENSOR)
+    assert oracle.rel_fro(host(out), c0 + oracle.matmult(x, w)) <= F32_TOL
+    # values spanning many binades and exact zero rows keep their accuracy
+    big = (normal(rng, (130, 64), np.float32) * np.exp2(rng.integers(-20, 20, (130, 64)))).astype(np.float32)
+    big[1, :] = 0
+    small = normal(rng, (64, 70), np.float32)
+    got = host(api.matmult(dev(big), dev(small), route=L.ROUTE_TENSOR))
+    exp = oracle.matmult(big, small)
+    assert np.all(got[1] == 0) and np.isfinite(got).all()
     assert oracle.rel_fro(got, exp) <= F32_TOL
-    assert np.array_equal(got, exp)
+    # an infinite input stays non-finite (inf or NaN: inf x (hi + lo) may meet inf - inf); the CUDA-core route is exact
+    big[0, 0] = np.inf
+    got = host(api.matmult(dev(big), dev(small), route=L.ROUTE_TENSOR))
+    assert not np.isfinite(got[0]).any() and np.isfinite(got[1:]).all()
+    assert np.array_equal(host(api.matmult(dev(big), dev(small), route=L.ROUTE_SIMT)), oracle.matmult(big, small), equal_nan=True)
 
 
 @pytest.mark.parametrize("ta,tb", FLAGS)
