@@ -1,0 +1,92 @@
+"""N-sharded MLP step (BASELINE config 3: BFloat16, batch 8192, 4096 -> 16384 -> 4096, ReLU, MSE) on the GPUs of one box.
+
+    python -m neurotensor_b200.bench_mlp_sharded                       # 1 GPU
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        -m neurotensor_b200.bench_mlp_sharded [--steps K] [--check]
+
+Strong scaling: the problem is fixed, every large GEMM is split over its output columns across the ranks, and the
+hidden activations and the output are all-gathered with NCCL (partition.ShardedMLP).  Time is CUDA events around K
+steps between barriers, maximum over ranks.  `--check` compares rank 0's loss and gradient shards with the same step
+run unsharded on rank 0.  Prints one JSON line on rank 0.
+"""
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from neurotensor_b200 import _lib, partition  # noqa: E402
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--batch", type=int, default=8192)
+    ap.add_argument("--din", type=int, default=4096)
+    ap.add_argument("--hidden", type=int, default=16384)
+    ap.add_argument("--check", action="store_true")
+    args = ap.parse_args()
+    rank, world, local = (int(os.environ.get(k, d)) for k, d in (("RANK", 0), ("WORLD_SIZE", 1), ("LOCAL_RANK", 0)))
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    B, D, H = args.batch, args.din, args.hidden
+    dt = torch.bfloat16
+    gen = torch.Generator(device="cuda").manual_seed(9)          # same seed on every rank: replicated tensors agree
+    rn = lambda shape, s=1.0: (torch.randn(shape, generator=gen, device="cuda") * s).to(dt)
+    x, t = rn((B, D)), rn((B, D))
+    w1, w2 = rn((D, H), D ** -0.5), rn((H, D), H ** -0.5)
+    b1, b2 = rn((H,), 0.01), rn((D,), 0.01)
+    h0, hn = partition.column_shard(H, world, rank)
+    mlp = partition.ShardedMLP(w1[:, h0:h0 + hn].contiguous(), b1[h0:h0 + hn].contiguous(), w2, b2, rank, world)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(3):
+        loss, grads = mlp.step(x, t)
+    barrier()
+    l0 = _lib.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        loss, grads = mlp.step(x, t)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / args.steps
+    launches = (_lib.launch_count() - l0) // args.steps
+    if dist is not None:
+        tt = torch.tensor([ms], device="cuda")
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms = float(tt.item())
+    check = None
+    if args.check and rank == 0:
+        ref = partition.ShardedMLP(w1, b1, w2, b2, 0, 1)
+        rloss, rg = ref.step(x, t)
+        d0, dn = partition.column_shard(D, world, rank)
+        rel = lambda a, b: float(((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-30)).item())
+        check = {"loss": [float(loss.item()), float(rloss.item())],
+                 "dw1": rel(grads["w1"], rg["w1"][:, h0:h0 + hn]), "dw2": rel(grads["w2"], rg["w2"][:, d0:d0 + dn]),
+                 "y": rel(grads["y"], rg["y"])}
+    if rank == 0:
+        flops = 5 * 2.0 * B * D * H
+        print(json.dumps({"config": "BFloat16 MLP %dx(%d->%d->%d) fwd+bwd step, N-sharded" % (B, D, H, D), "n_gpus": world,
+                          "ms_per_step": ms, "tflops": flops / (ms * 1e-3) / 1e12, "scaling": "strong",
+                          "kernels_per_step_rank0": int(launches), "collectives_per_step": 0 if world == 1 else 2,
+                          "check": check}), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -309,6 +309,17 @@ __global__ void copy_strided_kernel(T* __restrict__ dst, const T* __restrict__ s
     }
 }
 
+// Rows that are contiguous in the source (unit column stride): plain 16-byte row copies, coalesced on both sides.
+// dst is dense [batch][rows][cols]; one grid-stride loop over all 16-byte vectors.
+__global__ void copy_rows_kernel(uint4* __restrict__ dst, const unsigned char* __restrict__ src, long long total_vec,
+                                 long long rows, long long vec_per_row, long long batch_stride_bytes, long long row_stride_bytes) {
+    for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < total_vec; v += (long long)gridDim.x * blockDim.x) {
+        const long long c = v % vec_per_row, t = v / vec_per_row;
+        const long long r = t % rows, b = t / rows;
+        dst[v] = *reinterpret_cast<const uint4*>(src + b * batch_stride_bytes + r * row_stride_bytes + c * 16);
+    }
+}
+
 template <class D, class S>
 __global__ void convert_kernel(D* __restrict__ dst, const S* __restrict__ src, long long n) {
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
@@ -469,8 +480,18 @@ int ntb200_copy_strided_2d(int dtype, void* dst, const void* src, int64_t batch,
     if (batch < 0 || rows < 0 || cols < 0) return fail(NTB200_ERR_INVALID_ARG, "copy_strided_2d: negative size");
     if (batch == 0 || rows == 0 || cols == 0) return NTB200_OK;
     if (!dst || !src) return fail(NTB200_ERR_INVALID_ARG, "copy_strided_2d: null pointer");
-    if (batch > 65535 || (rows + 31) / 32 > 65535) return fail(NTB200_ERR_UNSUPPORTED, "copy_strided_2d: too many tiles");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const long long es = (long long)dtype_size(dtype);
+    if (es && src_col_stride == 1 && (cols * es) % 16 == 0 && (src_row_stride * es) % 16 == 0 && (src_batch_stride * es) % 16 == 0 &&
+        reinterpret_cast<uintptr_t>(dst) % 16 == 0 && reinterpret_cast<uintptr_t>(src) % 16 == 0) {
+        const long long vpr = cols * es / 16, total_vec = batch * rows * vpr;
+        copy_rows_kernel<<<grid_for(total_vec, 256), 256, 0, s>>>(static_cast<uint4*>(dst), static_cast<const unsigned char*>(src),
+                                                                 total_vec, rows, vpr, src_batch_stride * es, src_row_stride * es);
+        count_launch();
+        NTB200_CUDA(cudaGetLastError());
+        return NTB200_OK;
+    }
+    if (batch > 65535 || (rows + 31) / 32 > 65535) return fail(NTB200_ERR_UNSUPPORTED, "copy_strided_2d: too many tiles");
     const dim3 grid(unsigned((cols + 31) / 32), unsigned((rows + 31) / 32), unsigned(batch));
     const dim3 block(32, 8);
     switch (dtype_size(dtype)) {

@@ -54,10 +54,65 @@ def n_sharded_linear(x, w_local, bias_local=None, group=None, gather=True):
 
 
 def all_gather_columns(y_local, group=None):
-    """All-gather equal-width column blocks [M, n_r] of every rank into row-major [M, world * n_r]."""
+    """All-gather equal-width column blocks [M, n_r] of every rank into row-major [M, world * n_r].
+
+    The collective gathers whole blocks ([world, M, n_r]); one strided-copy kernel of this library re-tiles them
+    into rows (on CPU tensors, used by the host-logic tests, torch does the re-tiling)."""
     import torch.distributed as dist
     world = dist.get_world_size(group)
     m, n_r = y_local.shape
     parts = torch.empty((world, m, n_r), dtype=y_local.dtype, device=y_local.device)
-    dist.all_gather_into_tensor(parts, y_local.contiguous(), group=group)
-    return parts.permute(1, 0, 2).reshape(m, world * n_r)
+    dist.all_gather_into_tensor(parts.view(world * m, n_r), y_local.contiguous(), group=group)   # rank-major blocks
+    if not y_local.is_cuda:
+        return parts.permute(1, 0, 2).reshape(m, world * n_r)
+    import ctypes
+    from . import _lib, api
+    out = torch.empty((m, world * n_r), dtype=y_local.dtype, device=y_local.device)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    for m0 in range(0, m, 65535):      # the copy kernel batches over rows: dst[row][rank][:] = parts[rank][row][:]
+        mb = min(65535, m - m0)
+        _lib.check(_lib.lib().ntb200_copy_strided_2d(api.dtype_code(y_local), out[m0:].data_ptr(), parts[:, m0:].data_ptr(),
+                                                     mb, world, n_r, n_r, m * n_r, 1, stream))
+    return out
+
+
+class ShardedMLP:
+    """Linear -> ReLU -> Linear -> MSE, forward and backward, with every large GEMM split over the output columns
+    (N) across the ranks of a process group.
+
+    Every rank holds x, the target, this rank's columns of W1 / b1, and all of W2 / b2 (its column block is read as a
+    strided view for the forward pass, its row block for the backward pass; nothing is copied).  Communication per
+    step: one all-gather of the hidden activations and one of the output, both only because the next operation
+    needs full rows.  Gradients come out sharded the same way as the parameters they belong to
+    (dW1, db1: this rank's columns; dW2, db2: this rank's columns)."""
+
+    def __init__(self, w1_local, b1_local, w2_full, b2_full, rank, world, group=None):
+        self.w1, self.b1, self.w2, self.b2 = w1_local, b1_local, w2_full, b2_full
+        self.rank, self.world, self.group = rank, world, group
+        self.h0, self.hn = column_shard(w2_full.shape[0], world, rank)       # hidden units owned by this rank
+        self.d0, self.dn = column_shard(w2_full.shape[1], world, rank)       # output columns owned by this rank
+        assert w1_local.shape[1] == self.hn, "W1 shard does not match the hidden partition"
+
+    def gather(self, t):
+        if self.world == 1:
+            return t
+        return all_gather_columns(t, self.group)
+
+    def step(self, x, target):
+        from . import api
+        h_loc = api.linear(x, self.w1, self.b1)                               # [B, hn]
+        a_loc = api.relu(h_loc)
+        a = self.gather(a_loc)                                                # [B, H]   all-gather 1
+        w2_cols = self.w2[:, self.d0:self.d0 + self.dn]                       # strided view
+        y_loc = api.linear(a, w2_cols, self.b2[self.d0:self.d0 + self.dn])    # [B, dn]
+        y = self.gather(y_loc)                                                # [B, D]   all-gather 2
+        loss, dy = api.mse(y, target)
+        dy_loc = dy[:, self.d0:self.d0 + self.dn]                             # strided view
+        gw2_loc = api.matmult(a, dy_loc, True, False)                         # [H, dn]
+        gb2_loc = api.column_sum(dy_loc.contiguous())
+        w2_rows = self.w2[self.h0:self.h0 + self.hn]                          # [hn, D]
+        da_loc = api.matmult(dy, w2_rows, False, True)                        # [B, hn]
+        dh_loc = api.relu_backward(h_loc, da_loc)
+        gw1_loc = api.matmult(x, dh_loc, True, False)                         # [Din, hn]
+        gb1_loc = api.column_sum(dh_loc)
+        return loss, dict(w1=gw1_loc, b1=gb1_loc, w2=gw2_loc, b2=gb2_loc, y=y)
