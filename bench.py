@@ -23,9 +23,10 @@ sys.path.insert(0, ROOT)
 BATCH, M, K, N = 64, 2048, 2048, 2048
 FLOPS_PER_ITEM = 2.0 * M * K * N
 WORKLOAD = "batched matmult Float16 A[64,2048,2048] x B[64,2048,2048]^T-view, fp32 accumulate (BASELINE config 1)"
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the GEMM kernel, from the ncu capture
-# summarised under profiles/; None until a capture exists.
-NCU_DRAM_TRAFFIC_BYTES_PER_LAUNCH = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the GEMM kernel, from the ncu capture summarised in
+# profiles/umma_pair_f16_batched_2048.md: 174.6 MB for 8 items, scaled to the 64 items of a full launch (traffic
+# grows in proportion to the items).  Per batch item; multiplied by the items of the run below.
+NCU_DRAM_TRAFFIC_BYTES_PER_ITEM = (134.312192e6 + 40.332544e6) / 8
 
 
 def env_int(name, default):
@@ -266,7 +267,7 @@ def main():
                    "parallelism": "batch-sharded x%d, no collective" % world,
                    "l2": "inputs (1.6 GB per step) exceed the 126 MB L2; no flush needed", "kernel": route},
         "roofline": {"bound": "tensor", "achieved": per_gpu_tflops, "peak": peak, "unit": "TFLOP/s",
-                     "frac": per_gpu_tflops / peak, "traffic": NCU_DRAM_TRAFFIC_BYTES_PER_LAUNCH,
+                     "frac": per_gpu_tflops / peak, "traffic": NCU_DRAM_TRAFFIC_BYTES_PER_ITEM * count,
                      "peak_source": "%s (%s bf16 cuBLAS figure)" % (peaks["source"], peak_kind),
                      "algorithmic_flops_per_launch": count * FLOPS_PER_ITEM,
                      "algorithmic_bytes_per_launch": 3 * count * M * N * 2},
