@@ -484,7 +484,7 @@ constexpr uint32_t kPairOperandBytes = 128 * 128;                 // 128 rows (o
 template <bool kSplit>
 struct PairTile {
     static constexpr uint32_t kStageBytes = (kSplit ? 4u : 2u) * kPairOperandBytes;   // per CTA
-    static constexpr int kStages = int(196608u / kStageBytes);                        // 6, or 3 when split
+    static constexpr int kStages = int(229376u / kStageBytes);                        // 7 (224 KB), or 3 when split
     static constexpr uint32_t kSmemBytes = kStages * kStageBytes + 256 + 1024;
 };
 
