@@ -107,6 +107,21 @@ int ntb200_pool_stats(uint64_t* bytes_in_use, uint64_t* high_water);
 /* ---- GEMM ----------------------------------------------------------------------------------------- */
 int ntb200_gemm(const ntb200_gemm_desc* desc, void* stream);
 
+/* Multi-GPU (no counterpart in the reference, which has a single CPU device).  ntb200_gemm_push is ntb200_gemm
+ * whose epilogue stores every finished tile of C into this GPU's C AND into up to 7 peer-mapped copies of C on
+ * other GPUs (same layout, plain stores over NVLink): the all-gather of an N-sharded GEMM fused into the GEMM.
+ * F16 / BF16, tcgen05 route only.  The kernel does not wait for anybody; the caller orders the ranks with one
+ * collective (a barrier) before any rank reads its gathered buffer, and must not let a rank overwrite a buffer
+ * that a slower peer may still be reading (alternate two buffers).
+ * The peer_* helpers allocate buffers that can be mapped into other processes (cudaMalloc + CUDA IPC): export
+ * gives a 64-byte handle to send to the peers, import maps a peer's buffer here and enables peer access. */
+int ntb200_gemm_push(const ntb200_gemm_desc* desc, void* const* peer_c, int n_peers, void* stream);
+int ntb200_peer_alloc(void** ptr, size_t bytes);
+int ntb200_peer_free(void* ptr);
+int ntb200_peer_export(const void* ptr, unsigned char handle[64]);
+int ntb200_peer_import(const unsigned char handle[64], void** ptr);
+int ntb200_peer_release(void* ptr);
+
 /* Replaces nt_matmult<T> (nt/functional/cpu/matmult/nt_matmult.h:6-7; call sites
  * nt/functional/cpu/matmult_cpu.cpp:118,150): C += op(A).op(B), row-major contiguous, a_rows/a_cols and
  * b_rows/b_cols are the logical dims AFTER the transposes (a_cols == b_rows); with transpose_a the

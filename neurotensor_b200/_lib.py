@@ -49,6 +49,12 @@ SIGNATURES = {
     "ntb200_stream_synchronize": (_ci, [_vp]),
     "ntb200_pool_stats": (_ci, [ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_uint64)]),
     "ntb200_gemm": (_ci, [ctypes.POINTER(GemmDesc), _vp]),
+    "ntb200_gemm_push": (_ci, [ctypes.POINTER(GemmDesc), ctypes.POINTER(_vp), _ci, _vp]),
+    "ntb200_peer_alloc": (_ci, [ctypes.POINTER(_vp), _sz]),
+    "ntb200_peer_free": (_ci, [_vp]),
+    "ntb200_peer_export": (_ci, [_vp, ctypes.c_char_p]),
+    "ntb200_peer_import": (_ci, [ctypes.c_char_p, ctypes.POINTER(_vp)]),
+    "ntb200_peer_release": (_ci, [_vp]),
     "ntb200_matmult": (_ci, [_ci, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _ci, _ci, _vp]),
     "ntb200_matmult_batch": (_ci, [_ci, ctypes.POINTER(_vp), ctypes.POINTER(_vp), ctypes.POINTER(_vp), _i64, _i64,
                                    _i64, _i64, _i64, _ci, _ci, _vp]),

@@ -129,6 +129,34 @@ def gemm(a, b, out, transpose_a=False, transpose_b=False, accumulate=False, bias
     return out
 
 
+def gemm_push(a, b, full_out, col0, bias=None, transpose_a=False, transpose_b=False, peer_bases=()):
+    """full_out[:, col0:col0+n] = bias + op(a).op(b), and the same block into the buffers at `peer_bases` (raw device
+    pointers of peer-mapped tensors shaped like `full_out` on other GPUs): the column all-gather of an N-sharded GEMM
+    done by the GEMM's own epilogue.  2-D, Float16 / BFloat16, tensor-core route."""
+    _require_cuda(a, b, full_out, bias)
+    m, k, n, lead = _matmult_shapes(a, b, transpose_a, transpose_b)
+    if lead or full_out.dim() != 2 or not full_out.is_contiguous():
+        raise ValueError("gemm_push takes 2-D operands and a contiguous 2-D output buffer")
+    if full_out.shape[0] != m or col0 < 0 or col0 + n > full_out.shape[1] or full_out.dtype != a.dtype:
+        raise ValueError("gemm_push: column block [%d, %d) does not fit an output of shape %s" % (col0, col0 + n, tuple(full_out.shape)))
+    es = full_out.element_size()
+    a_rs, a_cs = (a.stride(1), a.stride(0)) if transpose_a else (a.stride(0), a.stride(1))
+    b_rs, b_cs = (b.stride(1), b.stride(0)) if transpose_b else (b.stride(0), b.stride(1))
+    d = GemmDesc()
+    d.dtype, d.route, d.accumulate, d.f16_rounding = dtype_code(a), _lib.ROUTE_TENSOR, 0, _lib.F16_ROUND_ONCE
+    d.m, d.n, d.k, d.batch = m, n, k, 1
+    d.a, d.a_row_stride, d.a_col_stride, d.a_batch_stride = a.data_ptr(), a_rs, a_cs, 0
+    d.b, d.b_row_stride, d.b_col_stride, d.b_batch_stride = b.data_ptr(), b_rs, b_cs, 0
+    d.c, d.c_row_stride, d.c_batch_stride = full_out.data_ptr() + col0 * es, full_out.shape[1], 0
+    if bias is not None:
+        if bias.dim() != 1 or bias.shape[0] != n or bias.dtype != a.dtype:
+            raise ValueError("gemm_push: bias must be a vector of the block's %d columns" % n)
+        d.bias, d.bias_row_stride, d.bias_col_stride, d.bias_batch_stride = bias.data_ptr(), 0, bias.stride(0), 0
+    peers = (ctypes.c_void_p * max(1, len(peer_bases)))(*[int(p) + col0 * es for p in peer_bases])
+    check(lib().ntb200_gemm_push(ctypes.byref(d), peers, len(peer_bases), _stream()))
+    return full_out
+
+
 def matmult(a, b, transpose_a=False, transpose_b=False, out=None, route=_lib.ROUTE_AUTO,
             f16_rounding=_lib.F16_ROUND_ONCE):
     """functional::matmult.  Without `out` returns a new tensor op(a).op(b); with `out` computes

@@ -30,6 +30,7 @@ def main():
     ap.add_argument("--din", type=int, default=4096)
     ap.add_argument("--hidden", type=int, default=16384)
     ap.add_argument("--check", action="store_true")
+    ap.add_argument("--fused", action="store_true", help="all-gathers fused into the GEMM epilogues (peer stores)")
     args = ap.parse_args()
     rank, world, local = (int(os.environ.get(k, d)) for k, d in (("RANK", 0), ("WORLD_SIZE", 1), ("LOCAL_RANK", 0)))
     torch.cuda.set_device(local)
@@ -52,14 +53,18 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    fused = args.fused and world > 1
+    if fused:
+        mlp.enable_fused_gather(B)
+    step = mlp.step_fused if fused else mlp.step
     for _ in range(3):
-        loss, grads = mlp.step(x, t)
+        loss, grads = step(x, t)
     barrier()
     l0 = _lib.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
-        loss, grads = mlp.step(x, t)
+        loss, grads = step(x, t)
     e1.record()
     barrier()
     ms = e0.elapsed_time(e1) / args.steps
@@ -81,8 +86,11 @@ def main():
         flops = 5 * 2.0 * B * D * H
         print(json.dumps({"config": "BFloat16 MLP %dx(%d->%d->%d) fwd+bwd step, N-sharded" % (B, D, H, D), "n_gpus": world,
                           "ms_per_step": ms, "tflops": flops / (ms * 1e-3) / 1e12, "scaling": "strong",
-                          "kernels_per_step_rank0": int(launches), "collectives_per_step": 0 if world == 1 else 2,
+                          "kernels_per_step_rank0": int(launches), "collectives_per_step": 0 if world == 1 else 2, "gather": "fused peer stores + barrier" if fused else "NCCL all-gather + re-tile",
                           "check": check}), flush=True)
+    if fused:
+        barrier()
+        mlp.close()
     if dist is not None:
         dist.destroy_process_group()
     return 0

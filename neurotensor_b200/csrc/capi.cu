@@ -251,9 +251,16 @@ int ntb200_stream_synchronize(void* stream) {
     return NTB200_OK;
 }
 
-int ntb200_gemm(const ntb200_gemm_desc* d, void* stream) {
+static int gemm_from_desc(const ntb200_gemm_desc* d, void* const* peer_c, int n_peers, void* stream) {
     if (!d) return fail(NTB200_ERR_INVALID_ARG, "gemm: null descriptor");
     GemmArgs g{};
+    if (n_peers < 0 || n_peers > 7) return fail(NTB200_ERR_INVALID_ARG, "gemm_push: between 0 and 7 peers");
+    if (n_peers > 0 && !peer_c) return fail(NTB200_ERR_INVALID_ARG, "gemm_push: null peer table");
+    g.n_peers = n_peers;
+    for (int t = 0; t < n_peers; ++t) {
+        if (!peer_c[t]) return fail(NTB200_ERR_INVALID_ARG, "gemm_push: null peer pointer");
+        g.peer_c[t] = peer_c[t];
+    }
     g.dtype = d->dtype; g.accumulate = d->accumulate ? 1 : 0; g.f16_rounding = d->f16_rounding;
     g.m = d->m; g.n = d->n; g.k = d->k; g.batch = d->batch;
     g.a = d->a; g.a_rs = d->a_row_stride; g.a_cs = d->a_col_stride; g.a_bs = d->a_batch_stride;
@@ -267,7 +274,49 @@ int ntb200_gemm(const ntb200_gemm_desc* d, void* stream) {
         if (route == NTB200_ROUTE_TENSOR) return fail(NTB200_ERR_UNSUPPORTED, "gemm: per-K-tile fp16 rounding needs the CUDA-core route");
         route = NTB200_ROUTE_SIMT;
     }
+    if (n_peers > 0) {
+        if (route == NTB200_ROUTE_SIMT) return fail(NTB200_ERR_UNSUPPORTED, "gemm_push needs the tcgen05 route");
+        route = NTB200_ROUTE_TENSOR;
+    }
     return run_gemm(g, route, static_cast<cudaStream_t>(stream));
+}
+
+int ntb200_gemm(const ntb200_gemm_desc* d, void* stream) { return gemm_from_desc(d, nullptr, 0, stream); }
+
+int ntb200_gemm_push(const ntb200_gemm_desc* d, void* const* peer_c, int n_peers, void* stream) {
+    return gemm_from_desc(d, peer_c, n_peers, stream);
+}
+
+int ntb200_peer_alloc(void** ptr, size_t bytes) {
+    if (!ptr) return fail(NTB200_ERR_INVALID_ARG, "peer_alloc: null pointer");
+    *ptr = nullptr;
+    if (bytes == 0) return fail(NTB200_ERR_INVALID_ARG, "peer_alloc: zero bytes");
+    NTB200_CUDA(cudaMalloc(ptr, bytes));
+    NTB200_CUDA(cudaMemset(*ptr, 0, bytes));
+    return NTB200_OK;
+}
+int ntb200_peer_free(void* ptr) {
+    if (ptr) NTB200_CUDA(cudaFree(ptr));
+    return NTB200_OK;
+}
+int ntb200_peer_export(const void* ptr, unsigned char handle[64]) {
+    if (!ptr || !handle) return fail(NTB200_ERR_INVALID_ARG, "peer_export: null pointer");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    cudaIpcMemHandle_t h;
+    NTB200_CUDA(cudaIpcGetMemHandle(&h, const_cast<void*>(ptr)));
+    std::memcpy(handle, &h, 64);
+    return NTB200_OK;
+}
+int ntb200_peer_import(const unsigned char handle[64], void** ptr) {
+    if (!ptr || !handle) return fail(NTB200_ERR_INVALID_ARG, "peer_import: null pointer");
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handle, 64);
+    NTB200_CUDA(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    return NTB200_OK;
+}
+int ntb200_peer_release(void* ptr) {
+    if (ptr) NTB200_CUDA(cudaIpcCloseMemHandle(ptr));
+    return NTB200_OK;
 }
 
 int ntb200_matmult(int dtype, const void* A, const void* B, void* C, int64_t a_rows, int64_t a_cols, int64_t b_rows,

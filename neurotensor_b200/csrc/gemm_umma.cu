@@ -60,6 +60,9 @@ struct UmmaParams {
     const void* bias;
     long long bias_rs, bias_cs, bias_bs;
     int accumulate, out_kind, c_vec_ok;
+    // Copies of C in other GPUs' memory (peer-mapped): the epilogue stores every finished tile there too.
+    int n_peers;
+    long long peer_offset[7];   // byte distance from this GPU's C to peer i's C (same layout)
 };
 
 // kSplit: every operand is staged twice (high and low part of a Float32 split into two TF32 values).
@@ -240,7 +243,11 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, uint32_t tmem
                     for (int j = 0; j < 4; ++j)
                         w[j] = from_float_bits16(f[8 * q + 2 * j], p.out_kind) |
                                (from_float_bits16(f[8 * q + 2 * j + 1], p.out_kind) << 16);
-                    *reinterpret_cast<uint4*>(dst + 8 * q) = make_uint4(w[0], w[1], w[2], w[3]);
+                    const uint4 packed = make_uint4(w[0], w[1], w[2], w[3]);
+                    *reinterpret_cast<uint4*>(dst + 8 * q) = packed;
+                    // the same 16 bytes into every peer's copy of C (plain stores over NVLink)
+                    for (int t = 0; t < p.n_peers; ++t)
+                        *reinterpret_cast<uint4*>(reinterpret_cast<char*>(dst + 8 * q) + p.peer_offset[t]) = packed;
                 }
             } else {
 #pragma unroll
@@ -248,7 +255,10 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, uint32_t tmem
                     if (col0 + j < p.n) {
                         float x = f[j];
                         if (p.accumulate) x += to_float_bits16(dst[j], p.out_kind);
-                        dst[j] = (uint16_t)from_float_bits16(x, p.out_kind);
+                        const uint16_t r16 = (uint16_t)from_float_bits16(x, p.out_kind);
+                        dst[j] = r16;
+                        for (int t = 0; t < p.n_peers; ++t)
+                            *reinterpret_cast<uint16_t*>(reinterpret_cast<char*>(dst + j) + p.peer_offset[t]) = r16;
                     }
             }
         }
@@ -1005,6 +1015,11 @@ int launch_planned(const GemmArgs& g, const Planned& pl, const Side& a, const Si
     p.bias = g.bias; p.bias_rs = g.bias_rs; p.bias_cs = g.bias_cs; p.bias_bs = g.bias_bs;
     p.accumulate = g.accumulate;
     p.out_kind = pl.out_kind;
+    p.n_peers = g.n_peers;
+    for (int t = 0; t < g.n_peers; ++t)
+        p.peer_offset[t] = static_cast<const char*>(g.peer_c[t]) - static_cast<const char*>(g.c);
+    if (g.n_peers > 0 && pl.out_kind != kOutF16 && pl.out_kind != kOutBF16)
+        return fail(NTB200_ERR_UNSUPPORTED, "peer stores are implemented for Float16 / BFloat16 outputs");
     const int ces = int(dtype_size(g.dtype));
     p.c_vec_ok = (reinterpret_cast<uintptr_t>(g.c) % 16 == 0) && ((g.c_rs * ces) % 16 == 0) &&
                  (g.batch == 1 || (g.c_bs * ces) % 16 == 0);

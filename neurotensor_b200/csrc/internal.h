@@ -39,6 +39,9 @@ struct GemmArgs {
     const void* const* a_ptrs = nullptr;
     const void* const* b_ptrs = nullptr;
     void* const* c_ptrs = nullptr;
+    // peer-mapped copies of C on other GPUs that receive every finished tile as well (tcgen05 route only)
+    int n_peers = 0;
+    void* peer_c[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
 };
 
 // tcgen05 route.  Returns NTB200_ERR_UNSUPPORTED (without touching the error text) when the operands

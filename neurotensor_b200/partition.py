@@ -76,6 +76,57 @@ def all_gather_columns(y_local, group=None):
     return out
 
 
+class _RawCuda:
+    """A device pointer dressed up for torch.as_tensor (CUDA array interface)."""
+
+    def __init__(self, ptr, shape, typestr):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (int(ptr), False), "version": 3}
+
+
+class PeerBuffer:
+    """A [rows, cols] buffer of a 2-byte dtype that exists on every rank and is mapped into every other rank
+    (cudaMalloc + CUDA IPC through the library's peer_* entry points).  `local` is this rank's tensor; `peer_bases`
+    are raw device pointers of the other ranks' copies, valid for this library's kernels only (they are never handed
+    to torch or NCCL)."""
+
+    def __init__(self, rows, cols, dtype, group=None):
+        import ctypes
+        import torch.distributed as dist
+        from . import _lib
+        assert dtype in (torch.float16, torch.bfloat16)
+        self.rows, self.cols, self.dtype = rows, cols, dtype
+        L = _lib.lib()
+        ptr = ctypes.c_void_p()
+        _lib.check(L.ntb200_peer_alloc(ctypes.byref(ptr), rows * cols * 2))
+        self._ptr = ptr
+        self.local = torch.as_tensor(_RawCuda(ptr.value, (rows, cols), "<i2"), device="cuda").view(dtype)
+        handle = ctypes.create_string_buffer(64)
+        _lib.check(L.ntb200_peer_export(ptr, handle))
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        handles = [None] * world
+        dist.all_gather_object(handles, bytes(handle.raw), group=group)
+        self._imported = []
+        self.peer_bases = []
+        for r in range(world):
+            if r == rank:
+                continue
+            p = ctypes.c_void_p()
+            _lib.check(L.ntb200_peer_import(ctypes.create_string_buffer(handles[r], 64), ctypes.byref(p)))
+            self._imported.append(p)
+            self.peer_bases.append(p.value)
+
+    def close(self):
+        from . import _lib
+        L = _lib.lib()
+        for p in self._imported:
+            L.ntb200_peer_release(p)
+        self._imported, self.peer_bases = [], []
+        if self._ptr is not None:
+            self.local = None
+            L.ntb200_peer_free(self._ptr)
+            self._ptr = None
+
+
 class ShardedMLP:
     """Linear -> ReLU -> Linear -> MSE, forward and backward, with every large GEMM split over the output columns
     (N) across the ranks of a process group.
@@ -97,6 +148,56 @@ class ShardedMLP:
         if self.world == 1:
             return t
         return all_gather_columns(t, self.group)
+
+    def enable_fused_gather(self, batch):
+        """Switch the two all-gathers to the fused form: the GEMM epilogue stores its column block straight into every
+        rank's full buffer (peer stores), and one tiny NCCL all-reduce orders the ranks.  Two buffers alternate per
+        step so a fast rank never overwrites what a slower rank is still reading."""
+        dt = self.w2.dtype
+        hidden, dout = self.w2.shape
+        self._fused = {"a": [PeerBuffer(batch, hidden, dt, self.group) for _ in range(2)],
+                       "y": [PeerBuffer(batch, dout, dt, self.group) for _ in range(2)],
+                       "flag": torch.zeros(1, device="cuda"), "parity": 0}
+
+    def close(self):
+        for bufs in (getattr(self, "_fused", None) or {}).values():
+            if isinstance(bufs, list):
+                for b in bufs:
+                    b.close()
+        self._fused = None
+
+    def _rank_barrier(self):
+        import torch.distributed as dist
+        dist.all_reduce(self._fused["flag"], group=self.group)   # stream-ordered: every rank's GEMM is behind it
+
+    def step_fused(self, x, target):
+        """Same step with the all-gathers fused into the GEMM epilogues.  The hidden buffer holds the pre-activation
+        h (the ReLU is applied to the gathered buffer locally: cheaper than a second pass on every shard's owner and
+        it keeps h for the mask)."""
+        from . import api
+        f = self._fused
+        par = f["parity"]
+        f["parity"] ^= 1
+        hbuf, ybuf = f["a"][par], f["y"][par]
+        api.gemm_push(x, self.w1, hbuf.local, self.h0, bias=self.b1, peer_bases=hbuf.peer_bases)     # h, all ranks
+        self._rank_barrier()
+        h_full = hbuf.local
+        a = api.relu(h_full)                                                                          # [B, H]
+        w2_cols = self.w2[:, self.d0:self.d0 + self.dn]
+        api.gemm_push(a, w2_cols, ybuf.local, self.d0, bias=self.b2[self.d0:self.d0 + self.dn], peer_bases=ybuf.peer_bases)
+        self._rank_barrier()
+        y = ybuf.local
+        loss, dy = api.mse(y, target)
+        dy_loc = dy[:, self.d0:self.d0 + self.dn]
+        gw2_loc = api.matmult(a, dy_loc, True, False)
+        gb2_loc = api.column_sum(dy_loc.contiguous())
+        w2_rows = self.w2[self.h0:self.h0 + self.hn]
+        da_loc = api.matmult(dy, w2_rows, False, True)
+        h_loc = h_full[:, self.h0:self.h0 + self.hn].contiguous()
+        dh_loc = api.relu_backward(h_loc, da_loc)
+        gw1_loc = api.matmult(x, dh_loc, True, False)
+        gb1_loc = api.column_sum(dh_loc)
+        return loss, dict(w1=gw1_loc, b1=gb1_loc, w2=gw2_loc, b2=gb2_loc, y=y)
 
     def step(self, x, target):
         from . import api

@@ -169,3 +169,40 @@ def test_mlp_forward_backward(api, oracle, bf16):
         assert rel(got, ref[key]) <= 2e-2, key
     assert oracle.rel_fro(wid(host(gb2)), ref["db2"]) <= 2e-2
     assert oracle.rel_fro(wid(host(gb1)), ref["db1"]) <= 2e-2
+
+
+def test_gemm_push_writes_every_copy(api, oracle):
+    """ntb200_gemm_push: the epilogue stores the column block into this buffer and into every peer copy.  On one GPU
+    the "peers" are two more local buffers; across GPUs they are IPC-mapped (bench_mlp_sharded --fused)."""
+    rng = np.random.default_rng(17)
+    x, w, b = normal(rng, (200, 96), np.float16, 0.5), normal(rng, (96, 136), np.float16, 0.5), normal(rng, (136,), np.float16)
+    full = [torch.full((200, 400), 7.0, dtype=torch.float16, device="cuda") for _ in range(3)]
+    api.gemm_push(dev(x), dev(w), full[0], 128, bias=dev(b), peer_bases=[full[1].data_ptr(), full[2].data_ptr()])
+    exp = oracle.linear(x, w, b)
+    for f in full:
+        got = host(f)
+        assert oracle.rel_fro(got[:, 128:264], exp) <= 2e-3
+        assert np.all(got[:, :128] == 7) and np.all(got[:, 264:] == 7)      # nothing outside the block is touched
+    assert torch.equal(full[0], full[1]) and torch.equal(full[0], full[2])
+    with pytest.raises(ValueError):
+        api.gemm_push(dev(x), dev(w), full[0], 300)                           # block does not fit
+
+
+def test_sharded_mlp_matches_unsharded(api, oracle):
+    """partition.ShardedMLP with one rank is the plain step; two simulated shards reproduce its gradients exactly."""
+    from neurotensor_b200 import partition
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    rn = lambda s, sc=1.0: (torch.randn(s, generator=gen, device="cuda") * sc).bfloat16()
+    B, D, H = 256, 128, 512
+    x, t, w1, w2, b1, b2 = rn((B, D)), rn((B, D)), rn((D, H), D ** -0.5), rn((H, D), H ** -0.5), rn((H,), 0.01), rn((D,), 0.01)
+    full = partition.ShardedMLP(w1, b1, w2, b2, 0, 1)
+    loss, g = full.step(x, t)
+    # shard 1 of 2, with the gathers replaced by the known full activations
+    h0, hn = partition.column_shard(H, 2, 1)
+    d0, dn = partition.column_shard(D, 2, 1)
+    shard = partition.ShardedMLP(w1[:, h0:h0 + hn].contiguous(), b1[h0:h0 + hn].contiguous(), w2, b2, 1, 2)
+    a_full = api.relu(api.linear(x, w1, b1))
+    shard.gather = lambda part: a_full if part.shape[1] == hn else g["y"]
+    loss2, g2 = shard.step(x, t)
+    assert torch.equal(g2["w1"], g["w1"][:, h0:h0 + hn]) and torch.equal(g2["w2"], g["w2"][:, d0:d0 + dn])
+    assert abs(float(loss.item()) - float(loss2.item())) < 1e-6
