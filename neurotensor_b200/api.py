@@ -259,6 +259,23 @@ def conv2d(x, w, stride=1, padding=0, dilation=1, groups=1, workspace=None):
     return out
 
 
+def conv2d_backward(x, w, grad, stride=1, padding=0, dilation=1):
+    """conv_dimage (conv.cpp:318-346) and conv_dkernel (conv.cpp:444-471) for groups == 1 -> (d_image, d_kernel):
+    d_image = col2im(matmult(w2d, grad, true, false)); d_kernel = sum over the batch of matmult(grad, col, false, true)."""
+    _require_cuda(x, w, grad)
+    w4 = (w.unsqueeze(0) if w.dim() == 3 else w).contiguous()
+    x4, (kh, kw, sh, sw, ph, pw, dh, dw), ho, wo = _conv_geom(x, w4.shape[-2:], dilation, padding, stride)
+    bsz, cout = x4.shape[0], w4.shape[0]
+    w2d = w4.reshape(cout, -1)
+    g = grad.contiguous().reshape(bsz, cout, ho * wo)
+    dcol = matmult(w2d, g, True, False)                                   # [B, C*kh*kw, L]
+    dx = unfold2d_backward(dcol, x4.shape[-2:], (kh, kw), (dh, dw), (ph, pw), (sh, sw)).reshape(x.shape)
+    col = unfold2d(x4, (kh, kw), (dh, dw), (ph, pw), (sh, sw))
+    per_image = matmult(g, col, False, True)                              # [B, Cout, C*kh*kw]
+    dw_ = column_sum(per_image.reshape(bsz, -1)).reshape(w.shape)         # reduce over the batch
+    return dx, dw_
+
+
 def relu(x):
     _require_cuda(x)
     x = x.contiguous()

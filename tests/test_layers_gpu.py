@@ -206,3 +206,12 @@ def test_sharded_mlp_matches_unsharded(api, oracle):
     loss2, g2 = shard.step(x, t)
     assert torch.equal(g2["w1"], g["w1"][:, h0:h0 + hn]) and torch.equal(g2["w2"], g["w2"][:, d0:d0 + dn])
     assert abs(float(loss.item()) - float(loss2.item())) < 1e-6
+
+
+@pytest.mark.parametrize("ext", ["", "_batched"])
+def test_conv2d_backward_golden(api, ext):
+    """tests/src/conv_autograd_test.cpp:249-279,313-341 (backward) on the device."""
+    x, w, grad = dev(g("conv2d_input" + ext)), dev(g("conv2d_weight" + ext)), dev(g("conv2d_grad" + ext))
+    dx, dw = api.conv2d_backward(x, w, grad, stride=1, padding=1)
+    assert np.allclose(host(dx), g("conv2d_xgrad" + ext), rtol=1e-4, atol=1e-6)
+    assert np.allclose(host(dw), g("conv2d_wgrad" + ext), rtol=1e-4, atol=1e-5)
