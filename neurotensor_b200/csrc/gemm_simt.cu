@@ -26,6 +26,7 @@ struct SimtParams {
     const void* bias; long long bias_rs, bias_cs, bias_bs;
     const void* const* a_ptrs; const void* const* b_ptrs; void* const* c_ptrs;
     int accumulate, round_per_ktile;
+    int vec_ok;  // 4-byte dtype, 16-byte aligned bases, every non-unit stride a multiple of 4 elements
 };
 
 template <class T> struct Num;
@@ -76,8 +77,11 @@ simt_gemm_kernel(const SimtParams p) {
     using Acc = typename N::Acc;
     constexpr int BK = sizeof(Acc) == 8 ? 8 : 16;
     constexpr int kLoads = kBM * BK / kThreads;  // elements of each operand tile per thread
-    __shared__ __align__(16) Acc As[2][BK][kBM];
-    __shared__ __align__(16) Acc Bs[2][BK][kBN];
+    // +4 elements of padding per row: rows stay 16-byte aligned for vector reads, and the transposing stores of a
+    // K-contiguous operand (16 consecutive k of one row per half-warp) spread over the banks instead of hitting one
+    constexpr int kPad = 4;
+    __shared__ __align__(16) Acc As[2][BK][kBM + kPad];
+    __shared__ __align__(16) Acc Bs[2][BK][kBN + kPad];
 
     const int tid = threadIdx.x;
     const int tx = tid & 15, ty = tid >> 4;
@@ -91,8 +95,32 @@ simt_gemm_kernel(const SimtParams p) {
     const bool a_k_fast = (p.a_cs == 1 && p.a_rs != 1);
     const bool b_k_fast = (p.b_rs == 1 && p.b_cs != 1);
 
+    // Interior tiles of 4-byte dtypes with 16-byte aligned operands take 16-byte global loads (two per operand per
+    // thread and K block instead of eight scalar ones); edge tiles and everything else take the scalar path.  The
+    // values and their k order are the same either way.
+    constexpr bool kVecCapable = sizeof(T) == 4 && sizeof(Acc) == 4 && BK == 16;
+    const bool vec_tile = kVecCapable && p.vec_ok && m0 + kBM <= p.m && n0 + kBN <= p.n;
+
     Acc ra[kLoads], rb[kLoads];
     auto fetch = [&](long long k0) {
+        if constexpr (kVecCapable) {
+            if (vec_tile && k0 + BK <= p.k) {
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const int v = tid + i * kThreads;   // 0..511: one float4 each
+                    float4 qa, qb;
+                    if (a_k_fast) qa = *reinterpret_cast<const float4*>(A + (m0 + (v >> 2)) * p.a_rs + k0 + (v & 3) * 4);
+                    else qa = *reinterpret_cast<const float4*>(A + (k0 + (v >> 5)) * p.a_cs + m0 + (v & 31) * 4);
+                    if (b_k_fast) qb = *reinterpret_cast<const float4*>(B + (n0 + (v >> 2)) * p.b_cs + k0 + (v & 3) * 4);
+                    else qb = *reinterpret_cast<const float4*>(B + (k0 + (v >> 5)) * p.b_rs + n0 + (v & 31) * 4);
+                    const Acc* pa = reinterpret_cast<const Acc*>(&qa);
+                    const Acc* pb = reinterpret_cast<const Acc*>(&qb);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) { ra[i * 4 + j] = pa[j]; rb[i * 4 + j] = pb[j]; }
+                }
+                return true;
+            }
+        }
 #pragma unroll
         for (int i = 0; i < kLoads; ++i) {
             const int e = tid + i * kThreads;
@@ -105,8 +133,30 @@ simt_gemm_kernel(const SimtParams p) {
             const long long gn = n0 + nn, gkb = k0 + kb;
             rb[i] = (gn < p.n && gkb < p.k) ? N::widen(B[gkb * p.b_rs + gn * p.b_cs]) : Acc(0);
         }
+        return false;
     };
-    auto stash = [&](int buf) {
+    auto stash = [&](int buf, bool vec) {
+        if constexpr (kVecCapable) {
+            if (vec) {
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const int v = tid + i * kThreads;
+                    if (a_k_fast) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) As[buf][(v & 3) * 4 + j][v >> 2] = ra[i * 4 + j];
+                    } else {
+                        *reinterpret_cast<float4*>(&As[buf][v >> 5][(v & 31) * 4]) = *reinterpret_cast<const float4*>(&ra[i * 4]);
+                    }
+                    if (b_k_fast) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) Bs[buf][(v & 3) * 4 + j][v >> 2] = rb[i * 4 + j];
+                    } else {
+                        *reinterpret_cast<float4*>(&Bs[buf][v >> 5][(v & 31) * 4]) = *reinterpret_cast<const float4*>(&rb[i * 4]);
+                    }
+                }
+                return;
+            }
+        }
 #pragma unroll
         for (int i = 0; i < kLoads; ++i) {
             const int e = tid + i * kThreads;
@@ -141,14 +191,15 @@ simt_gemm_kernel(const SimtParams p) {
     }
 
     const long long kblocks = (p.k + BK - 1) / BK;
+    bool fetched_vec = false;
     if (kblocks > 0) {
-        fetch(0);
-        stash(0);
+        fetched_vec = fetch(0);
+        stash(0, fetched_vec);
     }
     __syncthreads();
     for (long long kb = 0; kb < kblocks; ++kb) {
         const int buf = int(kb & 1);
-        if (kb + 1 < kblocks) fetch((kb + 1) * BK);
+        if (kb + 1 < kblocks) fetched_vec = fetch((kb + 1) * BK);
 #pragma unroll
         for (int kk = 0; kk < BK; ++kk) {
             Acc af[8], bf[8];
@@ -170,7 +221,7 @@ simt_gemm_kernel(const SimtParams p) {
 #pragma unroll
                 for (int j = 0; j < 8; ++j) acc[i][j] = N::round_tile(acc[i][j]);
         }
-        if (kb + 1 < kblocks) stash(buf ^ 1);
+        if (kb + 1 < kblocks) stash(buf ^ 1, fetched_vec);
         __syncthreads();
     }
 
@@ -214,6 +265,11 @@ SimtParams to_params(const GemmArgs& g) {
     p.bias = g.bias; p.bias_rs = g.bias_rs; p.bias_cs = g.bias_cs; p.bias_bs = g.bias_bs;
     p.a_ptrs = g.a_ptrs; p.b_ptrs = g.b_ptrs; p.c_ptrs = g.c_ptrs;
     p.accumulate = g.accumulate;
+    auto al16 = [](const void* q) { return reinterpret_cast<uintptr_t>(q) % 16 == 0; };
+    auto m4 = [](long long v) { return v % 4 == 0; };
+    const bool a_ok = (g.a_cs == 1 && g.a_rs != 1) ? m4(g.a_rs) : (g.a_rs == 1 && m4(g.a_cs));
+    const bool b_ok = (g.b_rs == 1 && g.b_cs != 1) ? m4(g.b_cs) : (g.b_cs == 1 && m4(g.b_rs));
+    p.vec_ok = (dtype_size(g.dtype) == 4 && !g.a_ptrs && al16(g.a) && al16(g.b) && a_ok && b_ok && m4(g.a_bs) && m4(g.b_bs)) ? 1 : 0;
     p.round_per_ktile = (g.dtype == NTB200_F16 && g.f16_rounding == NTB200_F16_ROUND_PER_KTILE) ? 1 : 0;
     return p;
 }
