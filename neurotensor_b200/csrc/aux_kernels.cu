@@ -109,6 +109,27 @@ __global__ void im2col_plane_kernel(const T* __restrict__ im, T* __restrict__ co
             for (int h = hv; h < hc; h += rows_per_pass) {
                 const int hp = h * sh - ph + h_off * dh;
                 __align__(16) T out[V];
+                if constexpr (sizeof(T) == 2) {
+                    // unit stride, the whole vector inside the row: 8 consecutive 2-byte pixels come from 4 aligned
+                    // 32-bit shared loads, or from 5 of them and a funnel shift when the run starts on an odd pixel
+                    if (sw == 1 && hp >= 0 && hp < height && wp0 >= 0 && wp0 + V <= width) {
+                        const int e0 = hp * width + wp0;
+                        const uint32_t* words = reinterpret_cast<const uint32_t*>(plane) + (e0 >> 1);
+                        uint32_t o[4];
+                        if ((e0 & 1) == 0) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) o[j] = words[j];
+                        } else {
+                            uint32_t w5[5];
+#pragma unroll
+                            for (int j = 0; j < 5; ++j) w5[j] = words[j];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) o[j] = __funnelshift_r(w5[j], w5[j + 1], 16);
+                        }
+                        *reinterpret_cast<uint4*>(dst_tap + h * wc) = make_uint4(o[0], o[1], o[2], o[3]);
+                        continue;
+                    }
+                }
                 if (hp >= 0 && hp < height) {
                     const T* row = plane + hp * width;
 #pragma unroll
@@ -139,7 +160,7 @@ void launch_im2col(const void* im, void* col, const ConvGeom& g, cudaStream_t s)
     T* dst = static_cast<T*>(col);
     const long long plane_bytes = g.height * g.width * (long long)sizeof(T);
     if (vec && small && plane_bytes <= 40 * 1024 && g.batch <= 65535 && g.kh * g.kw > 1 && g.wc % V == 0 && g.wc / V <= 256) {
-        im2col_plane_kernel<T, V><<<dim3(unsigned(g.channels), unsigned(g.batch)), 256, size_t((plane_bytes + 15) / 16 * 16), s>>>(src, dst, g);
+        im2col_plane_kernel<T, V><<<dim3(unsigned(g.channels), unsigned(g.batch)), 256, size_t((plane_bytes + 15) / 16 * 16 + 16), s>>>(src, dst, g);
         return;
     }
     if (vec && small) im2col_kernel<T, int, V><<<blocks, 256, 0, s>>>(src, dst, g);
