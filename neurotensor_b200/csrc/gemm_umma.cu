@@ -713,189 +713,6 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
     }
 }
 
-// ---- wide pair kernel: 256 x 512 tiles ---------------------------------------------------------------------
-// Same pair scheme, but the tile is 512 columns wide: every K block issues two N = 256 MMA groups that share the A
-// operand already in shared memory, one into each half of tensor memory.  A CTA then pulls 16 KB of A and 32 KB of B
-// per 2 x 4 MMAs, i.e. 24 KB of L2 traffic per 256 x 256 x 64 of work instead of 32 KB -- the saving a 2-pair cluster
-// would get from a multicast load, obtained here with plain per-CTA loads.  The price: both accumulators belong to
-// the same tile, so the epilogue of a tile overlaps only the tail/head of the neighbouring main loops (half 0 is
-// drained while half 1's last MMAs run; the next tile's half-0 MMAs run while half 1 is drained).
-constexpr int kWideStages = 4;
-constexpr uint32_t kWideStageBytes = 3 * kPairOperandBytes;          // A 16 KB + two 16 KB blocks of B, per CTA
-constexpr uint32_t kWideSmemBytes = kWideStages * kWideStageBytes + 256 + 1024;
-
-template <MmaKind kKind>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
-umma_gemm_pair_wide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                           const UmmaParams p) {
-    constexpr int BN = 512, HN = 256;
-    constexpr int kStages = kWideStages;
-    extern __shared__ uint8_t smem_raw[];
-    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    uint8_t* bar_gen = smem_gen + kStages * kWideStageBytes;
-    const uint32_t bar_base = smem_base + kStages * kWideStageBytes;
-    auto full_bar = [&](int s) { return bar_base + 8u * s; };
-    auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
-    auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
-    auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_gen + 8 * (2 * kStages + 4));
-    volatile uint32_t* abort_flag = tmem_slot + 1;
-
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t rank = cluster_cta_rank();
-    const bool leader = rank == 0;
-    const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
-
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) {
-            mbar_init(full_bar(s), 1);
-            mbar_init(empty_bar(s), 1);
-        }
-        for (int a = 0; a < 2; ++a) {
-            mbar_init(tfull_bar(a), 1);
-            mbar_init(tempty_bar(a), 8);
-        }
-        *abort_flag = 0;
-        fence_barrier_init();
-        fence_proxy_async_smem();
-        tma_prefetch_desc(&tma_a);
-        tma_prefetch_desc(&tma_b);
-    }
-    if (warp == 1) {
-        tmem_alloc<2>(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
-        tmem_relinquish<2>();
-    }
-    tcgen05_fence_before();
-    cluster_sync_all();
-    tcgen05_fence_after();
-    const uint32_t tmem_base = *tmem_slot;
-
-    if (warp == 0) {
-        // ------------------------------------------------------------------ TMA producer (both CTAs)
-        if (lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0;
-            bool ok = true;
-            for (int t = pair; ok && t < p.total_tiles; t += npairs) {
-                int b, mi, ni;
-                tile_coords(p, t, b, mi, ni);
-                const int m0 = mi * 256 + int(rank) * 128, n0 = ni * BN + int(rank) * 128;
-                for (int kb = 0; kb < p.k_blocks; ++kb) {
-                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
-                        raise_timeout(abort_flag, 0x21);
-                        ok = false;
-                        break;
-                    }
-                    const uint32_t a_dst = smem_base + stage * kWideStageBytes;
-                    const uint32_t bar = full_bar(stage);
-                    if (leader) mbar_expect_tx(bar, 2 * kWideStageBytes);
-                    const int k0 = kb * p.block_k;
-                    if (!p.a_mn_major) {
-                        tma_load_3d_pair(a_dst, &tma_a, bar, k0, m0, b * p.a_batch_mul);
-                    } else {
-                        for (int c = 0; c < p.a_chunks; ++c)
-                            tma_load_3d_pair(a_dst + c * p.chunk_bytes, &tma_a, bar, m0 + c * p.chunk_mn, k0,
-                                             b * p.a_batch_mul);
-                    }
-#pragma unroll
-                    for (int h = 0; h < 2; ++h) {   // this CTA's 128 columns of each 256-column half
-                        const uint32_t b_dst = a_dst + (1 + h) * kPairOperandBytes;
-                        const int nh = n0 + h * HN;
-                        if (!p.b_mn_major) {
-                            tma_load_3d_pair(b_dst, &tma_b, bar, k0, nh, b * p.b_batch_mul);
-                        } else {
-                            for (int c = 0; c < p.b_chunks; ++c)
-                                tma_load_3d_pair(b_dst + c * p.chunk_bytes, &tma_b, bar, nh + c * p.chunk_mn, k0,
-                                                 b * p.b_batch_mul);
-                        }
-                    }
-                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
-                }
-            }
-            if (ok) {
-                for (int s = 0; s < kStages; ++s) {
-                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { raise_timeout(abort_flag, 0x22); break; }
-                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
-                }
-            }
-        }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer (even CTA only)
-        if (leader && lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0, tile_phase = 0;
-            bool ok = true;
-            for (int t = pair; ok && t < p.total_tiles; t += npairs) {
-                for (int kb = 0; kb < p.k_blocks; ++kb) {
-                    if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
-                        raise_timeout(abort_flag, 0x24);
-                        ok = false;
-                        break;
-                    }
-                    tcgen05_fence_after();
-                    const uint32_t a_addr = smem_base + stage * kWideStageBytes;
-                    const uint64_t a_desc = make_smem_desc_sw128(a_addr, p.a_lbo, 1024);
-#pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        if (kb == 0) {   // this half of tensor memory must have been drained by both epilogues
-                            if (!mbar_wait(tempty_bar(h), tile_phase ^ 1u, abort_flag)) {
-                                raise_timeout(abort_flag, 0x23);
-                                ok = false;
-                                break;
-                            }
-                            tcgen05_fence_after();
-                        }
-                        const uint64_t b_desc = make_smem_desc_sw128(a_addr + (1 + h) * kPairOperandBytes, p.b_lbo, 1024);
-#pragma unroll
-                        for (int k = 0; k < 4; ++k)
-                            umma<kKind, 2>(tmem_base + h * HN, a_desc + uint64_t(k * p.a_kstep),
-                                           b_desc + uint64_t(k * p.b_kstep), p.idesc, (kb | k) != 0);
-                        if (kb == p.k_blocks - 1) umma_commit_pair(tfull_bar(h), 3);   // half h complete
-                    }
-                    if (!ok) break;
-                    umma_commit_pair(empty_bar(stage), 3);
-                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
-                }
-                tile_phase ^= 1u;
-            }
-        }
-    } else {
-        // ------------------------------------------------------------------ epilogue (both CTAs)
-        const int quad = warp & 3;
-        const int row_in_tile = int(rank) * 128 + quad * 32 + lane;
-        uint32_t tile_phase = 0;
-        bool alive = true;
-        for (int t = pair; alive && t < p.total_tiles; t += npairs) {
-            int b, mi, ni;
-            tile_coords(p, t, b, mi, ni);
-            for (int h = 0; h < 2; ++h) {
-                bool ok = mbar_wait(tfull_bar(h), tile_phase, abort_flag);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) {
-                    if (lane == 0) raise_timeout(abort_flag, 0x25);
-                    alive = false;
-                    break;
-                }
-                tcgen05_fence_after();
-                epilogue_tile<HN>(p, tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(h * HN), b, mi * 256 + row_in_tile,
-                                  ni * BN + h * HN);
-                tcgen05_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_leader(tempty_bar(h));
-            }
-            tile_phase ^= 1u;
-        }
-    }
-
-    tcgen05_fence_before();
-    cluster_sync_all();
-    if (warp == 1) {
-        tcgen05_fence_after();
-        tmem_dealloc<2>(tmem_base, kTmemCols);
-    }
-}
-
 // ---- host side ---------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -971,9 +788,6 @@ const char* plan_operand(const void* ptr, int es, CUtensorMapDataType dt, int64_
 
 // NTB200_NO_PAIR=1 keeps every GEMM on the single-CTA kernel (for A/B measurements).
 const bool g_disable_pair = [] { const char* e = getenv("NTB200_NO_PAIR"); return e && e[0] == '1'; }();
-
-// NTB200_WIDE=0 disables the 512-wide pair tiles, 2 forces them wherever a pair kernel runs (measurements).
-const int g_wide_mode = [] { const char* e = getenv("NTB200_WIDE"); return e ? atoi(e) : 1; }();
 
 // K blocks per partial sum of the Float32 split kernels (NTB200_TF32_CHUNK overrides it for measurements).
 const int g_split_chunk_blocks = [] {
@@ -1072,24 +886,6 @@ int launch_pair_instance(const Maps& m, const UmmaParams& p, cudaStream_t stream
     return NTB200_OK;
 }
 
-template <MmaKind kKind>
-int launch_pair_wide_instance(const Maps& m, const UmmaParams& p, cudaStream_t stream) {
-    cudaError_t e = cudaFuncSetAttribute(umma_gemm_pair_wide_kernel<kKind>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         int(kWideSmemBytes));
-    if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(umma_gemm_pair_wide_kernel)");
-    static int cached[64] = {0};
-    int dev = 0;
-    (void)cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64) dev = 0;
-    if (cached[dev] == 0)
-        cached[dev] = max_resident_pairs(reinterpret_cast<const void*>(umma_gemm_pair_wide_kernel<kKind>), kWideSmemBytes);
-    const int pairs = std::min(p.total_tiles, cached[dev]);
-    umma_gemm_pair_wide_kernel<kKind><<<2 * pairs, kThreads, kWideSmemBytes, stream>>>(m.a.map, m.b.map, p);
-    count_launch();
-    NTB200_CUDA(cudaGetLastError());
-    return NTB200_OK;
-}
-
 // ---- Float32 as three TF32 products ------------------------------------------------------------------
 // x = hi + lo with hi = x rounded to TF32 (10 explicit mantissa bits) and lo = x - hi (exact in fp32), so that
 // a.b = a_hi.b_hi + a_hi.b_lo + a_lo.b_hi + O(2^-21 |a||b|).  The pre-pass writes hi and lo as dense K-major
@@ -1165,11 +961,6 @@ int launch_planned(const GemmArgs& g, const Planned& pl, const Side& a, const Si
     const int64_t pair_tiles = ((g.m + 255) / 256) * ((g.n + 255) / 256) * g.batch;
     const bool use_pair = !g_disable_pair && g.m > 128 && g.n > 128 && pair_tiles >= sms / 2;
     if (use_pair) bn = 256;
-    // 512-wide pair tiles when the problem still fills the machine twice over with them and N divides evenly enough.
-    const int64_t wide_tiles = ((g.m + 255) / 256) * ((g.n + 511) / 512) * g.batch;
-    const bool use_wide = use_pair && !pl.split && g_wide_mode != 0 && g.n >= 512 &&
-                          (g_wide_mode == 2 || (wide_tiles >= sms && ((g.n + 511) / 512) * 512 - g.n <= g.n / 16));
-    if (use_wide) bn = 512;
 
     Maps maps;
     if (const char* w = plan_operand(a.ptr, es, pl.dt, g.m, g.k, a.mn_stride, a.k_stride, g.batch, a.bs, kBM, block_k, &maps.a))
@@ -1205,7 +996,7 @@ int launch_planned(const GemmArgs& g, const Planned& pl, const Side& a, const Si
     p.total_tiles = int(int64_t(p.tiles_m) * p.tiles_n * g.batch);
     p.block_k = block_k;
     p.idesc = make_instr_desc(pl.d_fmt, pl.in_fmt, pl.in_fmt, maps.a.mn_major, maps.b.mn_major, use_pair ? 256u : uint32_t(kBM),
-                              uint32_t(use_wide ? 256 : bn));
+                              uint32_t(bn));
     p.a_mn_major = maps.a.mn_major; p.b_mn_major = maps.b.mn_major;
     p.chunk_mn = 128 / es;
     p.chunk_bytes = uint32_t(block_k) * 128u;
@@ -1240,9 +1031,6 @@ int launch_planned(const GemmArgs& g, const Planned& pl, const Side& a, const Si
         if (bn == 128) return launch_instance<MmaKind::tf32, 128, true>(maps, p, grid, stream);
         return launch_instance<MmaKind::tf32, 64, true>(maps, p, grid, stream);
     }
-    if (use_wide)
-        return pl.kind == MmaKind::i8 ? launch_pair_wide_instance<MmaKind::i8>(maps, p, stream)
-                                      : launch_pair_wide_instance<MmaKind::f16>(maps, p, stream);
     if (pl.kind == MmaKind::i8) {
         if (use_pair) return launch_pair_instance<MmaKind::i8, false>(maps, p, stream);
         if (bn == 256) return launch_instance<MmaKind::i8, 256, false>(maps, p, grid, stream);
