@@ -91,6 +91,12 @@ const char* ntb200_last_gemm_route(void);
 /* Synchronises `stream` and reports NTB200_ERR_TIMEOUT if any kernel since the last check gave up a wait. */
 int ntb200_check_device_status(void* stream);
 
+/* Failure-path self-test (no counterpart in the reference): launches a one-thread kernel that waits, for at most
+ * `limit_ms` (1..1000), on a barrier nothing signals.  The wait gives up, the kernel returns normally, and the next
+ * ntb200_check_device_status reports NTB200_ERR_TIMEOUT once; the context stays usable.  Exercises the same bounded
+ * wait every GEMM role uses, without faulting or hanging anything. */
+int ntb200_selftest_wait_timeout(unsigned int limit_ms, void* stream);
+
 /* ---- storage: replaces DeviceCPU::allocate / release (nt/memory/device.cpp:46-92) with a stream-ordered
  * pool (cudaMallocAsync) on the current device. ---------------------------------------------------------- */
 int ntb200_malloc_async(void** ptr, size_t bytes, void* stream);

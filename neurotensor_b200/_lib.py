@@ -40,6 +40,7 @@ SIGNATURES = {
     "ntb200_kernel_launch_count": (ctypes.c_uint64, []),
     "ntb200_last_gemm_route": (ctypes.c_char_p, []),
     "ntb200_check_device_status": (_ci, [_vp]),
+    "ntb200_selftest_wait_timeout": (_ci, [ctypes.c_uint, _vp]),
     "ntb200_malloc_async": (_ci, [ctypes.POINTER(_vp), _sz, _vp]),
     "ntb200_free_async": (_ci, [_vp, _vp]),
     "ntb200_memset_async": (_ci, [_vp, _ci, _sz, _vp]),

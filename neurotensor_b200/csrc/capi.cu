@@ -189,6 +189,10 @@ int ntb200_get_device(int* device) {
     NTB200_CUDA(cudaGetDevice(device));
     return NTB200_OK;
 }
+int ntb200_selftest_wait_timeout(unsigned int limit_ms, void* stream) {
+    if (limit_ms == 0 || limit_ms > 1000) return fail(NTB200_ERR_INVALID_ARG, "selftest_wait_timeout: limit must be 1..1000 ms");
+    return launch_wait_timeout_selftest(1000000ull * limit_ms, static_cast<cudaStream_t>(stream));
+}
 int ntb200_check_device_status(void* stream) { return read_device_status(static_cast<cudaStream_t>(stream)); }
 
 int ntb200_malloc_async(void** ptr, size_t bytes, void* stream) {

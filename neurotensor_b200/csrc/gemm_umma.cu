@@ -1106,6 +1106,26 @@ int launch_umma_gemm(const GemmArgs& g, cudaStream_t stream) {
     return launch_planned(g, pl, a, b, nullptr, nullptr, stream);
 }
 
+// Self-test of the bounded-wait plumbing: one thread waits on an mbarrier that nothing ever signals, with a short
+// limit; the wait must give up, raise the device status word and let the kernel return normally.
+__global__ void wait_timeout_selftest_kernel(unsigned long long limit_ns) {
+    __shared__ __align__(8) unsigned long long bar;
+    __shared__ uint32_t abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(smem_u32(&bar), 1);
+        fence_barrier_init();
+        if (!mbar_wait(smem_u32(&bar), 0, &abort_flag, limit_ns)) raise_timeout(&abort_flag, 0x7f);
+    }
+}
+
+int launch_wait_timeout_selftest(unsigned long long limit_ns, cudaStream_t stream) {
+    wait_timeout_selftest_kernel<<<1, 32, 0, stream>>>(limit_ns);
+    count_launch();
+    NTB200_CUDA(cudaGetLastError());
+    return NTB200_OK;
+}
+
 int read_device_status(cudaStream_t stream) {
     NTB200_CUDA(cudaStreamSynchronize(stream));
     unsigned int st = 0;

@@ -49,6 +49,7 @@ struct GemmArgs {
 bool umma_supported(const GemmArgs& g, const char** why);
 int launch_umma_gemm(const GemmArgs& g, cudaStream_t stream);
 int read_device_status(cudaStream_t stream);
+int launch_wait_timeout_selftest(unsigned long long limit_ns, cudaStream_t stream);
 
 // CUDA-core route: every dtype, every stride pattern.
 int launch_simt_gemm(const GemmArgs& g, cudaStream_t stream);

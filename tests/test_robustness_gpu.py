@@ -1,0 +1,100 @@
+"""Failure paths and concurrency on the GPU, without faulting or hanging it: a bounded wait that runs out is reported
+as a status and leaves the context usable; concurrent host threads on separate streams get independent, correct
+results; a randomised sweep of shapes, strides and dtypes agrees with the CPU oracle on whichever route is chosen."""
+import ctypes
+import threading
+
+import numpy as np
+import pytest
+import torch
+
+from gpu_util import dev, host, integers, normal
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def api():
+    from neurotensor_b200 import api as a
+    return a
+
+
+def test_bounded_wait_runs_out_and_is_reported(api):
+    from neurotensor_b200 import _lib as L
+    lib = L.lib()
+    L.check(lib.ntb200_check_device_status(None))                      # clean before
+    L.check(lib.ntb200_selftest_wait_timeout(20, None))                # 20 ms on a barrier nobody signals
+    rc = lib.ntb200_check_device_status(None)
+    assert rc == L.ERR_TIMEOUT and b"0x17f" in lib.ntb200_last_error_string()
+    assert lib.ntb200_check_device_status(None) == L.OK                # reported once, then clean
+    # the context is still usable and correct
+    a = torch.ones((128, 64), device="cuda", dtype=torch.float16)
+    c = api.matmult(a, a.t().contiguous())
+    assert torch.all(c == 64)
+    assert lib.ntb200_selftest_wait_timeout(0, None) == L.ERR_INVALID_ARG
+
+
+def test_concurrent_host_threads_on_their_own_streams(api, oracle):
+    rng = np.random.default_rng(3)
+    cases = [(normal(rng, (256, 320), np.float16, 0.3), normal(rng, (320, 384), np.float16, 0.3)) for _ in range(4)]
+    out, err = [None] * 4, []
+
+    def work(i):
+        try:
+            s = torch.cuda.Stream()
+            with torch.cuda.stream(s):
+                a, b = dev(cases[i][0]), dev(cases[i][1])
+                for _ in range(20):
+                    c = api.matmult(a, b)
+                s.synchronize()
+                out[i] = c.cpu().numpy()
+        except Exception as e:  # pragma: no cover
+            err.append(e)
+
+    threads = [threading.Thread(target=work, args=(i,)) for i in range(4)]
+    [t.start() for t in threads]
+    [t.join() for t in threads]
+    assert not err
+    for i in range(4):
+        assert oracle.rel_fro(out[i], oracle.matmult(*cases[i])) <= 2e-3
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_random_shapes_strides_and_dtypes(api, oracle, seed):
+    """Random M, N, K (1..700), all transpose flags, optional batch and repeated operand, sliced (offset, padded-stride)
+    views: whichever kernel the router picks must agree with the oracle."""
+    from neurotensor_b200 import _lib as L
+    rng = np.random.default_rng(1000 + seed)
+    for _ in range(6):
+        m, k, n = (int(rng.integers(1, 700)) for _ in range(3))
+        if rng.random() < 0.5:      # make the tensor-core route reachable: 16-byte friendly extents
+            m, k, n = (max(8, v // 8 * 8) for v in (m, k, n))
+        ta, tb = bool(rng.integers(2)), bool(rng.integers(2))
+        batch = int(rng.choice([0, 0, 2, 3]))
+        kind = rng.choice(["f16", "bf16", "i8", "f32", "i32"])
+        sa = ((k, m) if ta else (m, k))
+        sb = ((n, k) if tb else (k, n))
+        pad = int(rng.choice([0, 8, 16]))
+        shape_a = ((batch,) if batch else ()) + (sa[0], sa[1] + pad)
+        shape_b = (() if (batch and rng.random() < 0.3) else ((batch,) if batch else ())) + (sb[0], sb[1] + pad)
+        if kind in ("i8", "i32"):
+            dt = np.int8 if kind == "i8" else np.int32
+            A, B = integers(rng, shape_a, dt, -100, 100), integers(rng, shape_b, dt, -100, 100)
+        elif kind == "bf16":
+            A, B = oracle.bf16_round(normal(rng, shape_a, np.float32)), oracle.bf16_round(normal(rng, shape_b, np.float32))
+        else:
+            dt = np.float16 if kind == "f16" else np.float32
+            A, B = normal(rng, shape_a, dt, 0.5), normal(rng, shape_b, dt, 0.5)
+        dA, dB = dev(A, kind == "bf16"), dev(B, kind == "bf16")
+        va, vb = dA[..., :sa[1]], dB[..., :sb[1]]                    # strided views (row stride = width + pad)
+        got = host(api.matmult(va, vb, ta, tb))
+        exp = oracle.matmult(np.ascontiguousarray(A[..., :sa[1]]), np.ascontiguousarray(B[..., :sb[1]]), ta, tb, bf16=(kind == "bf16"))
+        tag = (kind, m, k, n, ta, tb, batch, pad, L.last_route())
+        if kind in ("i8", "i32"):
+            assert np.array_equal(got, exp), tag
+        elif kind == "f32":
+            assert oracle.rel_fro(got, exp) <= 1e-5, tag
+        elif kind == "bf16":
+            assert oracle.rel_fro(oracle.bf16_widen(got), oracle.bf16_widen(exp)) <= 3e-3, tag
+        else:
+            assert oracle.rel_fro(got, exp) <= 2e-3, tag
