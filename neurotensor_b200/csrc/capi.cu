@@ -401,7 +401,7 @@ int ntb200_matmult_host(int dtype, const void* A, const void* B, void* C, int64_
     int rc = NTB200_OK;
     if (batches > 1) {
         // chunks of whole batch items; each lane: upload A,B,C -> multiply -> download C
-        const int64_t per = std::max<int64_t>(1, (batches + 7) / 8);
+        const int64_t per = std::max<int64_t>(1, (batches + 31) / 32);   // short pipeline fill and drain
         int lane_i = 0;
         for (int64_t b0 = 0; b0 < batches && rc == NTB200_OK; b0 += per, lane_i = (lane_i + 1) % kLanes) {
             const int64_t nb = std::min(per, batches - b0);
