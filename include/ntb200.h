@@ -76,6 +76,14 @@ typedef struct ntb200_gemm_desc {
     void* c;       int64_t c_row_stride, c_batch_stride;
     const void* bias; /* optional (NULL = none); same dtype */
     int64_t bias_row_stride, bias_col_stride, bias_batch_stride;
+    /* Optional fused neighbours of Linear (F16 / BF16 on the tensor-core route, accumulate = 0; leave NULL otherwise).
+     * Both tensors have exactly C's layout (same row and batch strides).
+     * relu_out: a second output, relu(C) = clamp(C, 0, none) of the rounded result (nn/functional/min_max.cpp:40-63),
+     *           so one launch yields the pre-activation C and the activation;
+     * relu_mask_src: the forward input h of a ReLU; the result is zeroed where h < 0, which is the clamp backward
+     *           applied to the gradient this GEMM produces (dH = mask(dA)). */
+    void* relu_out;
+    const void* relu_mask_src;
 } ntb200_gemm_desc;
 
 /* ---- library / device ---------------------------------------------------------------------------- */

@@ -27,6 +27,7 @@ class GemmDesc(ctypes.Structure):
         ("b", _vp), ("b_row_stride", _i64), ("b_col_stride", _i64), ("b_batch_stride", _i64),
         ("c", _vp), ("c_row_stride", _i64), ("c_batch_stride", _i64),
         ("bias", _vp), ("bias_row_stride", _i64), ("bias_col_stride", _i64), ("bias_batch_stride", _i64),
+        ("relu_out", _vp), ("relu_mask_src", _vp),
     ]
 
 

@@ -81,7 +81,7 @@ def _matmult_shapes(a, b, transpose_a, transpose_b):
 
 
 def gemm(a, b, out, transpose_a=False, transpose_b=False, accumulate=False, bias=None, route=_lib.ROUTE_AUTO,
-         f16_rounding=_lib.F16_ROUND_ONCE):
+         f16_rounding=_lib.F16_ROUND_ONCE, relu_out=None, relu_mask=None):
     """out = (accumulate ? out : 0) + bias + op(a).op(b); `out` contiguous in its last dim."""
     _require_cuda(a, b, out, bias)
     m, k, n, lead = _matmult_shapes(a, b, transpose_a, transpose_b)
@@ -125,8 +125,46 @@ def gemm(a, b, out, transpose_a=False, transpose_b=False, accumulate=False, bias
         d.bias = bx.data_ptr()
         d.bias_row_stride, d.bias_col_stride = st[-2], st[-1]
         d.bias_batch_stride = lead_strides[-1] if (nb > 1 and lead_strides) else 0
+    for t, name in ((relu_out, "relu_out"), (relu_mask, "relu_mask")):
+        if t is not None and (tuple(t.shape) != tuple(out.shape) or t.dtype != out.dtype or not t.is_contiguous() or not t.is_cuda):
+            raise ValueError("%s must be a contiguous CUDA tensor shaped and typed like the output" % name)
+    if relu_out is not None:
+        d.relu_out = relu_out.data_ptr()
+    if relu_mask is not None:
+        d.relu_mask_src = relu_mask.data_ptr()
     check(lib().ntb200_gemm(ctypes.byref(d), _stream()))
     return out
+
+
+def linear_relu(x, w, bias=None):
+    """h = x.w + bias and a = relu(h) from ONE launch (the ReLU is a second output of the GEMM epilogue).  Falls back
+    to two launches when the tensor-core route cannot take the operands."""
+    m, k, n, lead = _matmult_shapes(x, w, False, False)
+    h = torch.empty(tuple(lead) + (m, n), dtype=x.dtype, device=x.device)
+    if x.dtype in (torch.float16, torch.bfloat16):
+        a = torch.empty_like(h)
+        try:
+            gemm(x, w, h, bias=bias, relu_out=a)
+            return h, a
+        except _lib.Ntb200Error as e:
+            if e.code != _lib.ERR_UNSUPPORTED:
+                raise
+    gemm(x, w, h, bias=bias)
+    return h, relu(h)
+
+
+def matmult_relu_backward(grad, w, h, transpose_b=True):
+    """dH = relu_backward(h, grad . op(w)) from ONE launch: the clamp mask is applied in the GEMM epilogue."""
+    m, k, n, lead = _matmult_shapes(grad, w, False, transpose_b)
+    out = torch.empty(tuple(lead) + (m, n), dtype=grad.dtype, device=grad.device)
+    if grad.dtype in (torch.float16, torch.bfloat16) and h.is_contiguous():
+        try:
+            return gemm(grad, w, out, False, transpose_b, relu_mask=h)
+        except _lib.Ntb200Error as e:
+            if e.code != _lib.ERR_UNSUPPORTED:
+                raise
+    gemm(grad, w, out, False, transpose_b)
+    return relu_backward(h, out)
 
 
 def gemm_push(a, b, full_out, col0, bias=None, transpose_a=False, transpose_b=False, peer_bases=()):

@@ -141,12 +141,11 @@ def main():
         b1, b2 = randn(gen, (H,), dt, 0.01), randn(gen, (D,), dt, 0.01)
 
         def step():
-            h = api.linear(x, w1, b1)
-            a = api.relu(h)
+            h, a = api.linear_relu(x, w1, b1)                  # ReLU as a second output of the GEMM epilogue
             y = api.linear(a, w2, b2)
             loss, dy = api.mse(y, t)
-            da, gw2 = api.matmult_backward(a, w2, dy)
-            dh = api.relu_backward(h, da)
+            gw2 = api.matmult(a, dy, True, False)
+            dh = api.matmult_relu_backward(dy, w2, h, True)    # ReLU mask applied in the GEMM epilogue
             gw1 = api.matmult(x, dh, True, False)          # the input does not track a gradient: no dX GEMM
             api.column_sum(dy), api.column_sum(dh)
             return loss
@@ -154,7 +153,7 @@ def main():
         s, l = timed(step, max(3, args.steps // 4))
         flops = 5 * 2 * B * D * H
         xn, wn = x[:256].view(torch.int16).cpu().numpy().view("uint16"), w1.view(torch.int16).cpu().numpy().view("uint16")
-        emit("c4 BFloat16 MLP 8192x(4096->16384->4096) fwd+bwd step (5 GEMMs + elementwise)", s, flops,
+        emit("c4 BFloat16 MLP 8192x(4096->16384->4096) fwd+bwd step (5 GEMMs, fused ReLU epilogues, + elementwise)", s, flops,
              0, "tensor", l, "GEMM flops only (5 x 1.0995e12); elementwise kernels are inside the time",
              cpu_time(lambda o: o.matmult(xn, wn, bf16=True), 32 * 5, "256 of 8192 rows of one GEMM, scaled x32 x5 GEMMs"))
         # GEMM-only time of the same five contractions

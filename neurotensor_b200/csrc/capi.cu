@@ -271,6 +271,9 @@ static int gemm_from_desc(const ntb200_gemm_desc* d, void* const* peer_c, int n_
     g.b = d->b; g.b_rs = d->b_row_stride; g.b_cs = d->b_col_stride; g.b_bs = d->b_batch_stride;
     g.c = d->c; g.c_rs = d->c_row_stride; g.c_bs = d->c_batch_stride;
     g.bias = d->bias; g.bias_rs = d->bias_row_stride; g.bias_cs = d->bias_col_stride; g.bias_bs = d->bias_batch_stride;
+    g.relu_out = d->relu_out; g.mask_src = d->relu_mask_src;
+    if ((g.relu_out || g.mask_src) && d->route == NTB200_ROUTE_SIMT)
+        return fail(NTB200_ERR_UNSUPPORTED, "gemm: fused ReLU epilogues need the tcgen05 route");
     if (g.c_rs < g.n && g.m > 1) return fail(NTB200_ERR_INVALID_ARG, "gemm: C row stride %lld is smaller than n %lld", (long long)g.c_rs, (long long)g.n);
     int route = d->route;
     // per-K-tile fp16 rounding only exists on the CUDA-core route
@@ -278,6 +281,7 @@ static int gemm_from_desc(const ntb200_gemm_desc* d, void* const* peer_c, int n_
         if (route == NTB200_ROUTE_TENSOR) return fail(NTB200_ERR_UNSUPPORTED, "gemm: per-K-tile fp16 rounding needs the CUDA-core route");
         route = NTB200_ROUTE_SIMT;
     }
+    if (g.relu_out || g.mask_src) route = NTB200_ROUTE_TENSOR;
     if (n_peers > 0) {
         if (route == NTB200_ROUTE_SIMT) return fail(NTB200_ERR_UNSUPPORTED, "gemm_push needs the tcgen05 route");
         route = NTB200_ROUTE_TENSOR;

@@ -63,6 +63,10 @@ struct UmmaParams {
     // Copies of C in other GPUs' memory (peer-mapped): the epilogue stores every finished tile there too.
     int n_peers;
     long long peer_offset[7];   // byte distance from this GPU's C to peer i's C (same layout)
+    // Fused elementwise neighbours (16-bit outputs): tensors laid out exactly like C, given as byte offsets from C.
+    int has_relu_out, has_mask;
+    long long relu_out_offset;   // second output: max(C, 0)
+    long long mask_offset;       // input h: the result is zeroed where h < 0 (ReLU backward)
 };
 
 // kSplit: every operand is staged twice (high and low part of a Float32 split into two TF32 values).
@@ -236,6 +240,18 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, uint32_t tmem
                         }
                     }
                 }
+                if (p.has_mask) {   // ReLU backward: no gradient where the forward input was negative
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const uint4 hq = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(dst + 8 * q) + p.mask_offset);
+                        const uint32_t hw[4] = {hq.x, hq.y, hq.z, hq.w};
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            if (to_float_bits16(hw[j] & 0xffffu, p.out_kind) < 0.f) f[8 * q + 2 * j] = 0.f;
+                            if (to_float_bits16(hw[j] >> 16, p.out_kind) < 0.f) f[8 * q + 2 * j + 1] = 0.f;
+                        }
+                    }
+                }
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                     uint32_t w[4];
@@ -245,6 +261,17 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, uint32_t tmem
                                (from_float_bits16(f[8 * q + 2 * j + 1], p.out_kind) << 16);
                     const uint4 packed = make_uint4(w[0], w[1], w[2], w[3]);
                     *reinterpret_cast<uint4*>(dst + 8 * q) = packed;
+                    if (p.has_relu_out) {   // second output: the activation, negatives (of the ROUNDED value) cleared
+                        uint32_t r[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const uint32_t lo = w[j] & 0xffffu, hi = w[j] >> 16;
+                            r[j] = (to_float_bits16(lo, p.out_kind) < 0.f ? 0u : lo) |
+                                   ((to_float_bits16(hi, p.out_kind) < 0.f ? 0u : hi) << 16);
+                        }
+                        *reinterpret_cast<uint4*>(reinterpret_cast<char*>(dst + 8 * q) + p.relu_out_offset) =
+                            make_uint4(r[0], r[1], r[2], r[3]);
+                    }
                     // the same 16 bytes into every peer's copy of C (plain stores over NVLink)
                     for (int t = 0; t < p.n_peers; ++t)
                         *reinterpret_cast<uint4*>(reinterpret_cast<char*>(dst + 8 * q) + p.peer_offset[t]) = packed;
@@ -255,8 +282,15 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, uint32_t tmem
                     if (col0 + j < p.n) {
                         float x = f[j];
                         if (p.accumulate) x += to_float_bits16(dst[j], p.out_kind);
+                        if (p.has_mask &&
+                            to_float_bits16(*reinterpret_cast<const uint16_t*>(reinterpret_cast<const char*>(dst + j) + p.mask_offset),
+                                            p.out_kind) < 0.f)
+                            x = 0.f;
                         const uint16_t r16 = (uint16_t)from_float_bits16(x, p.out_kind);
                         dst[j] = r16;
+                        if (p.has_relu_out)
+                            *reinterpret_cast<uint16_t*>(reinterpret_cast<char*>(dst + j) + p.relu_out_offset) =
+                                to_float_bits16(r16, p.out_kind) < 0.f ? uint16_t(0) : r16;
                         for (int t = 0; t < p.n_peers; ++t)
                             *reinterpret_cast<uint16_t*>(reinterpret_cast<char*>(dst + j) + p.peer_offset[t]) = r16;
                     }
@@ -1015,6 +1049,14 @@ int launch_planned(const GemmArgs& g, const Planned& pl, const Side& a, const Si
     p.bias = g.bias; p.bias_rs = g.bias_rs; p.bias_cs = g.bias_cs; p.bias_bs = g.bias_bs;
     p.accumulate = g.accumulate;
     p.out_kind = pl.out_kind;
+    p.has_relu_out = g.relu_out != nullptr;
+    p.has_mask = g.mask_src != nullptr;
+    p.relu_out_offset = g.relu_out ? static_cast<const char*>(g.relu_out) - static_cast<const char*>(g.c) : 0;
+    p.mask_offset = g.mask_src ? static_cast<const char*>(g.mask_src) - static_cast<const char*>(g.c) : 0;
+    if ((g.relu_out || g.mask_src) && pl.out_kind != kOutF16 && pl.out_kind != kOutBF16)
+        return fail(NTB200_ERR_UNSUPPORTED, "fused ReLU epilogues are implemented for Float16 / BFloat16 outputs");
+    if ((g.relu_out || g.mask_src) && g.accumulate)
+        return fail(NTB200_ERR_UNSUPPORTED, "fused ReLU epilogues do not combine with accumulate");
     p.n_peers = g.n_peers;
     for (int t = 0; t < g.n_peers; ++t)
         p.peer_offset[t] = static_cast<const char*>(g.peer_c[t]) - static_cast<const char*>(g.c);

@@ -39,6 +39,9 @@ struct GemmArgs {
     const void* const* a_ptrs = nullptr;
     const void* const* b_ptrs = nullptr;
     void* const* c_ptrs = nullptr;
+    // fused elementwise neighbours (tcgen05 route, 16-bit): tensors with exactly C's layout
+    void* relu_out = nullptr;        // also write max(C, 0) here
+    const void* mask_src = nullptr;  // zero the result where this tensor is negative
     // peer-mapped copies of C on other GPUs that receive every finished tile as well (tcgen05 route only)
     int n_peers = 0;
     void* peer_c[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};

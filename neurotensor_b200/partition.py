@@ -201,8 +201,7 @@ class ShardedMLP:
 
     def step(self, x, target):
         from . import api
-        h_loc = api.linear(x, self.w1, self.b1)                               # [B, hn]
-        a_loc = api.relu(h_loc)
+        h_loc, a_loc = api.linear_relu(x, self.w1, self.b1)                   # [B, hn] twice, one launch
         a = self.gather(a_loc)                                                # [B, H]   all-gather 1
         w2_cols = self.w2[:, self.d0:self.d0 + self.dn]                       # strided view
         y_loc = api.linear(a, w2_cols, self.b2[self.d0:self.d0 + self.dn])    # [B, dn]
@@ -212,8 +211,7 @@ class ShardedMLP:
         gw2_loc = api.matmult(a, dy_loc, True, False)                         # [H, dn]
         gb2_loc = api.column_sum(dy_loc.contiguous())
         w2_rows = self.w2[self.h0:self.h0 + self.hn]                          # [hn, D]
-        da_loc = api.matmult(dy, w2_rows, False, True)                        # [B, hn]
-        dh_loc = api.relu_backward(h_loc, da_loc)
+        dh_loc = api.matmult_relu_backward(dy, w2_rows, h_loc, True)           # [B, hn], ReLU mask in the epilogue
         gw1_loc = api.matmult(x, dh_loc, True, False)                         # [Din, hn]
         gb1_loc = api.column_sum(dh_loc)
         return loss, dict(w1=gw1_loc, b1=gb1_loc, w2=gw2_loc, b2=gb2_loc, y=y)

@@ -215,3 +215,25 @@ def test_conv2d_backward_golden(api, ext):
     dx, dw = api.conv2d_backward(x, w, grad, stride=1, padding=1)
     assert np.allclose(host(dx), g("conv2d_xgrad" + ext), rtol=1e-4, atol=1e-6)
     assert np.allclose(host(dw), g("conv2d_wgrad" + ext), rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("m,k,n", [(256, 128, 512), (200, 96, 136), (130, 64, 72)])
+@pytest.mark.parametrize("bf16", [False, True])
+def test_fused_relu_epilogues_equal_the_separate_kernels(api, m, k, n, bf16):
+    """linear+ReLU as a second GEMM output, and the ReLU mask applied to the gradient GEMM: same bits as separate launches."""
+    from neurotensor_b200 import _lib
+    gen = torch.Generator(device="cuda").manual_seed(m + n)
+    dt = torch.bfloat16 if bf16 else torch.float16
+    rn = lambda s, sc=1.0: (torch.randn(s, generator=gen, device="cuda") * sc).to(dt)
+    x, w, b, g = rn((m, k)), rn((k, n), k ** -0.5), rn((n,), 0.1), rn((m, k))
+    before = _lib.launch_count()
+    h, a = api.linear_relu(x, w, b)
+    assert _lib.launch_count() == before + 1
+    h_ref = api.linear(x, w, b)
+    assert torch.equal(h, h_ref) and torch.equal(a, api.relu(h_ref))
+    # backward through the ReLU: dX = mask(h) applied to ... here on a gradient of h's shape: dH = mask(g2 . w2^T)
+    g2, w2 = rn((m, k)), rn((n, k), k ** -0.5)           # g2 [m,k] . w2^T [k,n] -> [m,n], masked by h [m,n]
+    before = _lib.launch_count()
+    dh = api.matmult_relu_backward(g2, w2, h, transpose_b=True)
+    assert _lib.launch_count() == before + 1
+    assert torch.equal(dh, api.relu_backward(h, api.matmult(g2, w2, False, True)))
