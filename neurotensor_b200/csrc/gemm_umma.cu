@@ -39,7 +39,7 @@ constexpr int kThreads = 192;
 constexpr int kThreadsSplit = 320;  // Float32 split kernels: 8 epilogue warps hold the running sums in registers
 constexpr int kTmemCols = 512;
 
-enum OutKind : int { kOutF16 = 0, kOutBF16 = 1, kOutI8 = 2, kOutF32 = 3 };
+enum OutKind : int { kOutF16 = 0, kOutBF16 = 1, kOutI8 = 2, kOutF32 = 3, kOutU32 = 4 };
 
 struct UmmaParams {
     int m, n, k, batch;
@@ -65,6 +65,7 @@ struct UmmaParams {
     long long peer_offset[7];   // byte distance from this GPU's C to peer i's C (same layout)
     // Fused elementwise neighbours (16-bit outputs): tensors laid out exactly like C, given as byte offsets from C.
     int has_relu_out, has_mask;
+    int shift;                   // kOutU32: the s32 accumulator is shifted left by this much before it is added
     long long relu_out_offset;   // second output: max(C, 0)
     long long mask_offset;       // input h: the result is zeroed where h < 0 (ReLU backward)
 };
@@ -164,7 +165,7 @@ __device__ __forceinline__ void store_running(const UmmaParams& p, const float (
 // and the accumulator's first column.  Executed by whole warps (tcgen05.ld is warp-collective).
 template <int BN>
 __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, uint32_t tmem_acc, int b, int row, int n0) {
-    const int es = (p.out_kind == kOutI8) ? 1 : (p.out_kind == kOutF32 ? 4 : 2);
+    const int es = (p.out_kind == kOutI8) ? 1 : ((p.out_kind == kOutF32 || p.out_kind == kOutU32) ? 4 : 2);
     const bool row_ok = row < p.m;
     uint8_t* c_row = static_cast<uint8_t*>(p.c) + ((long long)b * p.c_bs + (long long)row * p.c_rs) * es;
 #pragma unroll 1
@@ -209,6 +210,32 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, uint32_t tmem
                         if (p.accumulate) x += dst[j];
                         dst[j] = (uint8_t)x;
                     }
+            }
+        } else if (p.out_kind == kOutU32) {
+            // one limb product of a 32-bit integer GEMM: (acc << shift) joins C modulo 2^32
+            uint32_t* dst = reinterpret_cast<uint32_t*>(c_row) + col0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] <<= p.shift;
+            if (p.bias) {
+                const uint32_t* bias = static_cast<const uint32_t*>(p.bias) + (long long)b * p.bias_bs + (long long)row * p.bias_rs;
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (col0 + j < p.n) v[j] += bias[(long long)(col0 + j) * p.bias_cs];
+            }
+            if (full_chunk && p.c_vec_ok) {
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    uint4 o = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                    if (p.accumulate) {
+                        const uint4 old = *reinterpret_cast<const uint4*>(dst + 4 * q);
+                        o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                    }
+                    *reinterpret_cast<uint4*>(dst + 4 * q) = o;
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (col0 + j < p.n) dst[j] = p.accumulate ? dst[j] + v[j] : v[j];
             }
         } else if (p.out_kind == kOutF32) {
             float f[32];
@@ -831,7 +858,8 @@ const int g_split_chunk_blocks = [] {
 }();
 
 bool dtype_on_tensor_cores(int dtype) {
-    return dtype == NTB200_F16 || dtype == NTB200_BF16 || dtype == NTB200_I8 || dtype == NTB200_U8 || dtype == NTB200_F32;
+    return dtype == NTB200_F16 || dtype == NTB200_BF16 || dtype == NTB200_I8 || dtype == NTB200_U8 || dtype == NTB200_F32 ||
+           dtype == NTB200_I32 || dtype == NTB200_U32;
 }
 
 // Cheap structural test (no driver call): can both operands be staged?
@@ -839,6 +867,11 @@ const char* operands_stageable(const GemmArgs& g) {
     if (!dtype_on_tensor_cores(g.dtype)) return "dtype has no tensor-core kernel";
     if (g.a_ptrs || g.b_ptrs || g.c_ptrs) return "pointer-table batches run on the CUDA-core route";
     if (g.m <= 0 || g.n <= 0 || g.k <= 0 || g.batch <= 0) return "empty problem";
+    if (g.dtype == NTB200_I32 || g.dtype == NTB200_U32) {   // limb planes are copies too; each limb GEMM must be exact in s32
+        if (g.m > (int64_t(1) << 30) || g.n > (int64_t(1) << 30)) return "extent too large";
+        if (g.a_rs < 0 || g.a_cs < 0 || g.a_bs < 0 || g.b_rs < 0 || g.b_cs < 0 || g.b_bs < 0) return "negative stride";
+        return nullptr;
+    }
     if (g.dtype == NTB200_F32) {  // operands are copied (split) first, so any strides do
         if (g.m > (int64_t(1) << 30) || g.n > (int64_t(1) << 30) || g.k > (int64_t(1) << 30)) return "extent too large";
         if (g.a_rs < 0 || g.a_cs < 0 || g.a_bs < 0 || g.b_rs < 0 || g.b_cs < 0 || g.b_bs < 0) return "negative stride";
@@ -967,6 +1000,7 @@ struct Planned {
     uint32_t d_fmt, in_fmt;
     bool split;
     const char* route;
+    int shift = 0;
 };
 
 // Operands as the tensor-map planner sees them: logical [mn, k] with element strides and a batch stride.
@@ -993,7 +1027,7 @@ int launch_planned(const GemmArgs& g, const Planned& pl, const Side& a, const Si
     // Large problems run on CTA pairs (256 x 256 tiles); anything with fewer pair tiles than TPCs keeps the
     // single-CTA kernel, whose narrower tiles spread small problems over more SMs.
     const int64_t pair_tiles = ((g.m + 255) / 256) * ((g.n + 255) / 256) * g.batch;
-    const bool use_pair = !g_disable_pair && g.m > 128 && g.n > 128 && pair_tiles >= sms / 2;
+    const bool use_pair = !g_disable_pair && g.m > 128 && g.n > 128 && pair_tiles * 5 >= (sms / 2) * 4;   // >= 80 % of one wave
     if (use_pair) bn = 256;
 
     Maps maps;
@@ -1049,6 +1083,7 @@ int launch_planned(const GemmArgs& g, const Planned& pl, const Side& a, const Si
     p.bias = g.bias; p.bias_rs = g.bias_rs; p.bias_cs = g.bias_cs; p.bias_bs = g.bias_bs;
     p.accumulate = g.accumulate;
     p.out_kind = pl.out_kind;
+    p.shift = pl.shift;
     p.has_relu_out = g.relu_out != nullptr;
     p.has_mask = g.mask_src != nullptr;
     p.relu_out_offset = g.relu_out ? static_cast<const char*>(g.relu_out) - static_cast<const char*>(g.c) : 0;
@@ -1121,6 +1156,86 @@ int launch_f32_split(const GemmArgs& g, cudaStream_t stream) {
     return rc;
 }
 
+// ---- Int32 / UInt32 as products of 8-bit limbs ----------------------------------------------------------
+// x = x0 + x1 2^8 + x2 2^16 + x3 2^24 with unsigned 8-bit limbs (the top limb's sign does not matter modulo 2^32), so
+// a.b mod 2^32 = sum over s = 0..3 of 2^(8s) * sum over i + j = s of (a_i . b_j)  mod 2^32.
+// The pre-pass writes, per K chunk of Kc columns, the four limb planes of a row side by side:
+//     A row: [a_0 | a_1 | a_2 | a_3],   B^T row: [b_3 | b_2 | b_1 | b_0]        (each Kc bytes, K-major)
+// so that sum_{i+j=s} a_i . b_j is ONE 8-bit GEMM of depth (s+1) Kc: the first s+1 planes of the A row against the
+// last s+1 planes of the B row.  Four kind::i8 GEMMs per K chunk, whose exact s32 sums ((s+1) Kc 255^2 < 2^31) are
+// shifted and added into C by the epilogue.  Bit-exact with the reference's mullo_epi32 / add_epi32
+// (nt/mp/simde_traits/simde_traits_avx2.h:444-485) by construction.
+constexpr int64_t kLimbChunkK = 8192;
+
+__global__ void split_limbs_kernel(const uint32_t* __restrict__ src, uint8_t* __restrict__ limbs, long long rows, long long cols,
+                                   long long kc, long long nchunks, int reverse, long long sbs, long long srs, long long scs) {
+    __shared__ uint32_t tile[32][33];
+    const long long b = blockIdx.z;
+    const long long r0 = (long long)blockIdx.y * 32, c0 = (long long)blockIdx.x * 32;
+    const uint32_t* s = src + b * sbs;
+    if (scs == 1 || srs != 1) {
+        for (int j = threadIdx.y; j < 32; j += 8) {
+            const long long r = r0 + j, c = c0 + threadIdx.x;
+            tile[j][threadIdx.x] = (r < rows && c < cols) ? s[r * srs + c * scs] : 0u;
+        }
+    } else {
+        for (int j = threadIdx.y; j < 32; j += 8) {
+            const long long r = r0 + threadIdx.x, c = c0 + j;
+            tile[threadIdx.x][j] = (r < rows && c < cols) ? s[r * srs + c * scs] : 0u;
+        }
+    }
+    __syncthreads();
+    const long long row_bytes = nchunks * 4 * kc;
+    for (int j = threadIdx.y; j < 32; j += 8) {
+        const long long r = r0 + j, c = c0 + threadIdx.x;
+        if (r < rows && c < nchunks * kc) {
+            const uint32_t x = tile[j][threadIdx.x];   // zero beyond `cols`: the padding columns contribute nothing
+            uint8_t* row = limbs + (b * rows + r) * row_bytes + (c / kc) * 4 * kc + (c % kc);
+#pragma unroll
+            for (int l = 0; l < 4; ++l) row[(reverse ? 3 - l : l) * kc] = uint8_t(x >> (8 * l));
+        }
+    }
+}
+
+int launch_i32_limbs(const GemmArgs& g, cudaStream_t stream) {
+    const int64_t kp = (g.k + 15) & ~int64_t(15);
+    const int64_t kc = std::min(kp, kLimbChunkK), nchunks = (kp + kc - 1) / kc;
+    const int64_t row_bytes = nchunks * 4 * kc;
+    const int64_t a_batch = (g.batch > 1 && g.a_bs != 0) ? g.batch : 1;
+    const int64_t b_batch = (g.batch > 1 && g.b_bs != 0) ? g.batch : 1;
+    if (a_batch > 65535 || b_batch > 65535) return fail(NTB200_ERR_UNSUPPORTED, "tcgen05 route: batch too large for the limb split pass");
+    const size_t a_bytes = size_t(a_batch) * size_t(g.m) * size_t(row_bytes), b_bytes = size_t(b_batch) * size_t(g.n) * size_t(row_bytes);
+    uint8_t* scratch = nullptr;
+    keep_pool_memory();
+    NTB200_CUDA(cudaMallocAsync(reinterpret_cast<void**>(&scratch), a_bytes + b_bytes, stream));
+    uint8_t* a_limbs = scratch;
+    uint8_t* b_limbs = scratch + a_bytes;
+    const dim3 block(32, 8);
+    const unsigned gx = unsigned((nchunks * kc + 31) / 32);
+    split_limbs_kernel<<<dim3(gx, unsigned((g.m + 31) / 32), unsigned(a_batch)), block, 0, stream>>>(
+        static_cast<const uint32_t*>(g.a), a_limbs, g.m, g.k, kc, nchunks, 0, g.a_bs, g.a_rs, g.a_cs);
+    split_limbs_kernel<<<dim3(gx, unsigned((g.n + 31) / 32), unsigned(b_batch)), block, 0, stream>>>(
+        static_cast<const uint32_t*>(g.b), b_limbs, g.n, g.k, kc, nchunks, 1, g.b_bs, g.b_cs, g.b_rs);
+    count_launch(2);
+    cudaError_t e = cudaGetLastError();
+    int rc = e == cudaSuccess ? NTB200_OK : cuda_fail(e, "split_limbs_kernel");
+    bool first = true;
+    for (int64_t ch = 0; ch < nchunks && rc == NTB200_OK; ++ch)
+        for (int sh = 0; sh <= 3 && rc == NTB200_OK; ++sh) {
+            Planned pl{1, CU_TENSOR_MAP_DATA_TYPE_UINT8, MmaKind::i8, kOutU32, 2u, 0u, false, "umma_i32_limbs"};
+            pl.shift = 8 * sh;
+            GemmArgs part = g;
+            part.k = (sh + 1) * kc;                         // planes 0..sh of A against planes sh..0 of B
+            if (!first) { part.accumulate = 1; part.bias = nullptr; }
+            const Side sa{a_limbs + ch * 4 * kc, row_bytes, 1, a_batch > 1 ? g.m * row_bytes : 0};
+            const Side sb{b_limbs + ch * 4 * kc + (3 - sh) * kc, row_bytes, 1, b_batch > 1 ? g.n * row_bytes : 0};
+            rc = launch_planned(part, pl, sa, sb, nullptr, nullptr, stream);
+            first = false;
+        }
+    cudaFreeAsync(scratch, stream);
+    return rc;
+}
+
 }  // namespace
 
 bool umma_supported(const GemmArgs& g, const char** why) {
@@ -1132,6 +1247,7 @@ bool umma_supported(const GemmArgs& g, const char** why) {
 int launch_umma_gemm(const GemmArgs& g, cudaStream_t stream) {
     if (const char* w = operands_stageable(g)) return fail(NTB200_ERR_UNSUPPORTED, "tcgen05 route: %s", w);
     if (g.dtype == NTB200_F32) return launch_f32_split(g, stream);
+    if (g.dtype == NTB200_I32 || g.dtype == NTB200_U32) return launch_i32_limbs(g, stream);
     const int es = int(dtype_size(g.dtype));
     const bool is_i8 = es == 1;
     Planned pl;

@@ -284,3 +284,30 @@ def test_launches_are_counted_and_status_is_clean(api, L):
                 torch.ones((64, 128), device="cuda", dtype=torch.float16))
     assert L.launch_count() == before + 1
     L.check(L.lib().ntb200_check_device_status(None))
+
+
+@pytest.mark.parametrize("ta,tb", FLAGS)
+@pytest.mark.parametrize("m,k,n", [(131, 77, 65), (256, 512, 384), (1024, 2048, 1280)])
+def test_int32_on_tensor_cores_bit_exact(api, oracle, L, ta, tb, m, k, n):
+    """Int32 as ten products of 8-bit limbs on kind::i8: full-range operands, wrap modulo 2^32, any strides."""
+    rng = np.random.default_rng(61 + m)
+    info = np.iinfo(np.int32)
+    a, b = operands(rng, m, k, n, ta, tb, np.int32, ints=(info.min, info.max))
+    got = host(api.matmult(dev(a), dev(b), ta, tb, route=L.ROUTE_TENSOR))
+    assert L.last_route() == "umma_i32_limbs"
+    assert np.array_equal(got, oracle.matmult(a, b, ta, tb))
+
+
+def test_int32_tensor_route_accumulate_bias_batch(api, oracle, L):
+    rng = np.random.default_rng(67)
+    a, w = integers(rng, (3, 200, 96), np.int32, -10 ** 9, 10 ** 9), integers(rng, (96, 136), np.int32, -10 ** 9, 10 ** 9)
+    bias, c0 = integers(rng, (136,), np.int32, -10 ** 9, 10 ** 9), integers(rng, (3, 200, 136), np.int32, -10 ** 9, 10 ** 9)
+    got = host(api.linear(dev(a), dev(w), dev(bias), route=L.ROUTE_TENSOR))
+    assert L.last_route() == "umma_i32_limbs"
+    assert np.array_equal(got, oracle.linear(a, w, bias))
+    out = dev(c0)
+    api.matmult(dev(a), dev(w), out=out, route=L.ROUTE_TENSOR)
+    exp = c0.copy()
+    for i in range(3):
+        oracle.matmult_into(a[i], w, exp[i])
+    assert np.array_equal(host(out), exp)
