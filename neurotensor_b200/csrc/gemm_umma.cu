@@ -1,21 +1,28 @@
-// tcgen05 GEMM for Float16 / BFloat16 (fp32 accumulate in tensor memory) and Int8 / UInt8 (s32 accumulate,
-// truncated to 8 bits, i.e. arithmetic mod 2^8).  Replaces the packed simde/TBB kernels of
-// nt/functional/cpu/matmult/nt_matmult.hpp:124-235 for those dtypes.
+// tcgen05 GEMMs.  Replace the packed simde/TBB kernels of nt/functional/cpu/matmult/nt_matmult.hpp:124-235 for
+//   Float16 / BFloat16   fp32 accumulation in tensor memory, one rounding at the end
+//   Int8 / UInt8         s32 accumulation, truncated to 8 bits (arithmetic mod 2^8)
+//   Float32              three TF32 products per multiply on hi/lo split copies, two-level accumulation
+//   Int32 / UInt32       products of 8-bit limbs, shifted and added modulo 2^32 by the epilogue
 //
-// One persistent CTA per SM, 192 threads:
+// Two kernels with the same roles.  `umma_gemm_pair_kernel`: a cluster of two CTAs (the two SMs of a TPC) computes a
+// 256 x 256 tile with tcgen05.mma.cta_group::2; `umma_gemm_kernel<BN>`: one CTA per 128 x BN tile, for problems too
+// small to fill the machine with pair tiles.  Both are persistent (one CTA per SM) with 192 threads:
 //   warp 0      TMA producer   - one lane issues cp.async.bulk.tensor loads of the A and B tiles of a K block
 //                                into a ring of shared-memory stages (128-byte swizzle), signalling `full`
 //   warp 1      MMA issuer     - allocates tensor memory; one lane issues tcgen05.mma per 32 bytes of K,
 //                                tcgen05.commit releases the stage (`empty`) and, after the last K block,
 //                                publishes the accumulator (`tmem_full`)
-//   warps 2..5  epilogue       - tcgen05.ld the 128 x BN accumulator (each warp owns a 32-lane quadrant),
-//                                add bias / previous C, convert, store; then hand the accumulator back
-// Two accumulators (2 x BN columns of TMEM) let the epilogue of tile i overlap the main loop of tile i+1.
+//   warps 2..5  epilogue       - tcgen05.ld the accumulator (each warp owns a 32-lane quadrant), add bias /
+//                                previous C, apply the optional ReLU outputs, convert, store (also into peer GPUs'
+//                                copies of C when asked); then hand the accumulator back
+// (the Float32 split kernels run 8 epilogue warps that keep running sums in registers).
+// Two accumulators (2 x 256 columns of TMEM) let the epilogue of tile i overlap the main loop of tile i+1.
 //
 // Transposed and strided views never get copied: an operand whose unit stride runs along K is staged
 // K-major, one whose unit stride runs along M (or N) is staged MN-major in 128-byte-wide chunks; the
 // difference is carried by the TMA tensor map, the shared-memory descriptor and one bit of the
 // instruction descriptor.  Tails in M, N and K are zero-filled by TMA and masked at the store.
+// Every wait is bounded; a wait that runs out raises the device status word and the kernel returns.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
