@@ -76,14 +76,6 @@ typedef struct ntb200_gemm_desc {
     void* c;       int64_t c_row_stride, c_batch_stride;
     const void* bias; /* optional (NULL = none); same dtype */
     int64_t bias_row_stride, bias_col_stride, bias_batch_stride;
-    /* Optional fused neighbours of Linear (F16 / BF16 on the tensor-core route, accumulate = 0; leave NULL otherwise).
-     * Both tensors have exactly C's layout (same row and batch strides).
-     * relu_out: a second output, relu(C) = clamp(C, 0, none) of the rounded result (nn/functional/min_max.cpp:40-63),
-     *           so one launch yields the pre-activation C and the activation;
-     * relu_mask_src: the forward input h of a ReLU; the result is zeroed where h < 0, which is the clamp backward
-     *           applied to the gradient this GEMM produces (dH = mask(dA)). */
-    void* relu_out;
-    const void* relu_mask_src;
 } ntb200_gemm_desc;
 
 /* ---- library / device ---------------------------------------------------------------------------- */
@@ -118,8 +110,21 @@ int ntb200_stream_synchronize(void* stream);
  * nt::utils::getAllocatedMemory (nt/memory/track_memory.h:23-35). */
 int ntb200_pool_stats(uint64_t* bytes_in_use, uint64_t* high_water);
 
+/* Optional fused neighbours of Linear for ntb200_gemm_fused (F16 / BF16 on the tensor-core route, accumulate = 0).
+ * Both tensors have exactly C's layout (same row and batch strides); a NULL member is simply not used.
+ * relu_out:      a second output, relu(C) = clamp(C, 0, none) of the rounded result (nn/functional/min_max.cpp:40-63),
+ *                so one launch yields the pre-activation C and the activation;
+ * relu_mask_src: the forward input h of a ReLU; the result is zeroed where h < 0, which is the clamp backward
+ *                applied to the gradient this GEMM produces (dH = mask(dA)). */
+typedef struct ntb200_gemm_epilogue {
+    void* relu_out;
+    const void* relu_mask_src;
+} ntb200_gemm_epilogue;
+
 /* ---- GEMM ----------------------------------------------------------------------------------------- */
 int ntb200_gemm(const ntb200_gemm_desc* desc, void* stream);
+/* ntb200_gemm with the fused epilogue members above (`epilogue` may be NULL: then identical to ntb200_gemm). */
+int ntb200_gemm_fused(const ntb200_gemm_desc* desc, const ntb200_gemm_epilogue* epilogue, void* stream);
 
 /* Multi-GPU (no counterpart in the reference, which has a single CPU device).  ntb200_gemm_push is ntb200_gemm
  * whose epilogue stores every finished tile of C into this GPU's C AND into up to 7 peer-mapped copies of C on

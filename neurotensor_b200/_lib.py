@@ -27,8 +27,11 @@ class GemmDesc(ctypes.Structure):
         ("b", _vp), ("b_row_stride", _i64), ("b_col_stride", _i64), ("b_batch_stride", _i64),
         ("c", _vp), ("c_row_stride", _i64), ("c_batch_stride", _i64),
         ("bias", _vp), ("bias_row_stride", _i64), ("bias_col_stride", _i64), ("bias_batch_stride", _i64),
-        ("relu_out", _vp), ("relu_mask_src", _vp),
     ]
+
+
+class GemmEpilogue(ctypes.Structure):
+    _fields_ = [("relu_out", _vp), ("relu_mask_src", _vp)]
 
 
 # name -> (restype, argtypes); every symbol include/ntb200.h declares
@@ -51,6 +54,7 @@ SIGNATURES = {
     "ntb200_stream_synchronize": (_ci, [_vp]),
     "ntb200_pool_stats": (_ci, [ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_uint64)]),
     "ntb200_gemm": (_ci, [ctypes.POINTER(GemmDesc), _vp]),
+    "ntb200_gemm_fused": (_ci, [ctypes.POINTER(GemmDesc), ctypes.POINTER(GemmEpilogue), _vp]),
     "ntb200_gemm_push": (_ci, [ctypes.POINTER(GemmDesc), ctypes.POINTER(_vp), _ci, _vp]),
     "ntb200_peer_alloc": (_ci, [ctypes.POINTER(_vp), _sz]),
     "ntb200_peer_free": (_ci, [_vp]),

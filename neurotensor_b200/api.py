@@ -128,11 +128,13 @@ def gemm(a, b, out, transpose_a=False, transpose_b=False, accumulate=False, bias
     for t, name in ((relu_out, "relu_out"), (relu_mask, "relu_mask")):
         if t is not None and (tuple(t.shape) != tuple(out.shape) or t.dtype != out.dtype or not t.is_contiguous() or not t.is_cuda):
             raise ValueError("%s must be a contiguous CUDA tensor shaped and typed like the output" % name)
-    if relu_out is not None:
-        d.relu_out = relu_out.data_ptr()
-    if relu_mask is not None:
-        d.relu_mask_src = relu_mask.data_ptr()
-    check(lib().ntb200_gemm(ctypes.byref(d), _stream()))
+    if relu_out is not None or relu_mask is not None:
+        ep = _lib.GemmEpilogue()
+        ep.relu_out = relu_out.data_ptr() if relu_out is not None else None
+        ep.relu_mask_src = relu_mask.data_ptr() if relu_mask is not None else None
+        check(lib().ntb200_gemm_fused(ctypes.byref(d), ctypes.byref(ep), _stream()))
+    else:
+        check(lib().ntb200_gemm(ctypes.byref(d), _stream()))
     return out
 
 

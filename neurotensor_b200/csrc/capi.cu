@@ -258,7 +258,7 @@ int ntb200_stream_synchronize(void* stream) {
     return NTB200_OK;
 }
 
-static int gemm_from_desc(const ntb200_gemm_desc* d, void* const* peer_c, int n_peers, void* stream) {
+static int gemm_from_desc(const ntb200_gemm_desc* d, const ntb200_gemm_epilogue* ep, void* const* peer_c, int n_peers, void* stream) {
     if (!d) return fail(NTB200_ERR_INVALID_ARG, "gemm: null descriptor");
     GemmArgs g{};
     if (n_peers < 0 || n_peers > 7) return fail(NTB200_ERR_INVALID_ARG, "gemm_push: between 0 and 7 peers");
@@ -274,7 +274,7 @@ static int gemm_from_desc(const ntb200_gemm_desc* d, void* const* peer_c, int n_
     g.b = d->b; g.b_rs = d->b_row_stride; g.b_cs = d->b_col_stride; g.b_bs = d->b_batch_stride;
     g.c = d->c; g.c_rs = d->c_row_stride; g.c_bs = d->c_batch_stride;
     g.bias = d->bias; g.bias_rs = d->bias_row_stride; g.bias_cs = d->bias_col_stride; g.bias_bs = d->bias_batch_stride;
-    g.relu_out = d->relu_out; g.mask_src = d->relu_mask_src;
+    if (ep) { g.relu_out = ep->relu_out; g.mask_src = ep->relu_mask_src; }
     if ((g.relu_out || g.mask_src) && d->route == NTB200_ROUTE_SIMT)
         return fail(NTB200_ERR_UNSUPPORTED, "gemm: fused ReLU epilogues need the tcgen05 route");
     if (g.c_rs < g.n && g.m > 1) return fail(NTB200_ERR_INVALID_ARG, "gemm: C row stride %lld is smaller than n %lld", (long long)g.c_rs, (long long)g.n);
@@ -292,10 +292,14 @@ static int gemm_from_desc(const ntb200_gemm_desc* d, void* const* peer_c, int n_
     return run_gemm(g, route, static_cast<cudaStream_t>(stream));
 }
 
-int ntb200_gemm(const ntb200_gemm_desc* d, void* stream) { return gemm_from_desc(d, nullptr, 0, stream); }
+int ntb200_gemm(const ntb200_gemm_desc* d, void* stream) { return gemm_from_desc(d, nullptr, nullptr, 0, stream); }
+
+int ntb200_gemm_fused(const ntb200_gemm_desc* d, const ntb200_gemm_epilogue* ep, void* stream) {
+    return gemm_from_desc(d, ep, nullptr, 0, stream);
+}
 
 int ntb200_gemm_push(const ntb200_gemm_desc* d, void* const* peer_c, int n_peers, void* stream) {
-    return gemm_from_desc(d, peer_c, n_peers, stream);
+    return gemm_from_desc(d, nullptr, peer_c, n_peers, stream);
 }
 
 int ntb200_peer_alloc(void** ptr, size_t bytes) {

@@ -28,8 +28,7 @@ def test_cpp_shim_compiles_and_links():
 
 @pytest.mark.gpu
 def test_cpp_shim_cases_pass_on_gpu():
-    if not os.path.exists(BIN):
-        build_binary()
+    build_binary()   # always against the current header and library: a stale binary would speak an old ABI
     r = subprocess.run([BIN, REF_GOLDEN], capture_output=True, text=True, timeout=600)
     print(r.stdout[-4000:], r.stderr[-2000:])
     assert r.returncode == 0, r.stdout[-4000:] + r.stderr[-2000:]
