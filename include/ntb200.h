@@ -106,6 +106,13 @@ int ntb200_memcpy_h2d_async(void* dst_device, const void* src_host, size_t bytes
 int ntb200_memcpy_d2h_async(void* dst_host, const void* src_device, size_t bytes, void* stream);
 int ntb200_memcpy_d2d_async(void* dst_device, const void* src_device, size_t bytes, void* stream);
 int ntb200_stream_synchronize(void* stream);
+/* Page-locked host memory for tensors that stay on the CPU side of the boundary: what DeviceCPU::allocate /
+ * release (nt/memory/device.cpp:46-92, 64-byte aligned_alloc) should call so that ntb200_matmult_host copies
+ * run asynchronously at full PCIe speed.  ntb200_host_register pins memory the application already owns. */
+int ntb200_host_alloc(void** ptr, size_t bytes);
+int ntb200_host_free(void* ptr);
+int ntb200_host_register(void* ptr, size_t bytes);
+int ntb200_host_unregister(void* ptr);
 /* Bytes currently held / high-water mark of the pool: the device counterpart of
  * nt::utils::getAllocatedMemory (nt/memory/track_memory.h:23-35). */
 int ntb200_pool_stats(uint64_t* bytes_in_use, uint64_t* high_water);

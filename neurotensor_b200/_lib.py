@@ -52,6 +52,10 @@ SIGNATURES = {
     "ntb200_memcpy_d2h_async": (_ci, [_vp, _vp, _sz, _vp]),
     "ntb200_memcpy_d2d_async": (_ci, [_vp, _vp, _sz, _vp]),
     "ntb200_stream_synchronize": (_ci, [_vp]),
+    "ntb200_host_alloc": (_ci, [ctypes.POINTER(_vp), _sz]),
+    "ntb200_host_free": (_ci, [_vp]),
+    "ntb200_host_register": (_ci, [_vp, _sz]),
+    "ntb200_host_unregister": (_ci, [_vp]),
     "ntb200_pool_stats": (_ci, [ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_uint64)]),
     "ntb200_gemm": (_ci, [ctypes.POINTER(GemmDesc), _vp]),
     "ntb200_gemm_fused": (_ci, [ctypes.POINTER(GemmDesc), ctypes.POINTER(GemmEpilogue), _vp]),

@@ -292,6 +292,27 @@ static int gemm_from_desc(const ntb200_gemm_desc* d, const ntb200_gemm_epilogue*
     return run_gemm(g, route, static_cast<cudaStream_t>(stream));
 }
 
+int ntb200_host_alloc(void** ptr, size_t bytes) {
+    if (!ptr) return fail(NTB200_ERR_INVALID_ARG, "host_alloc: null pointer");
+    *ptr = nullptr;
+    if (bytes == 0) return NTB200_OK;
+    NTB200_CUDA(cudaHostAlloc(ptr, bytes, cudaHostAllocPortable));
+    return NTB200_OK;
+}
+int ntb200_host_free(void* ptr) {
+    if (ptr) NTB200_CUDA(cudaFreeHost(ptr));
+    return NTB200_OK;
+}
+int ntb200_host_register(void* ptr, size_t bytes) {
+    if (!ptr || bytes == 0) return fail(NTB200_ERR_INVALID_ARG, "host_register: null pointer or zero size");
+    NTB200_CUDA(cudaHostRegister(ptr, bytes, cudaHostRegisterPortable));
+    return NTB200_OK;
+}
+int ntb200_host_unregister(void* ptr) {
+    if (ptr) NTB200_CUDA(cudaHostUnregister(ptr));
+    return NTB200_OK;
+}
+
 int ntb200_gemm(const ntb200_gemm_desc* d, void* stream) { return gemm_from_desc(d, nullptr, nullptr, 0, stream); }
 
 int ntb200_gemm_fused(const ntb200_gemm_desc* d, const ntb200_gemm_epilogue* ep, void* stream) {

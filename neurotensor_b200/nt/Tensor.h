@@ -125,14 +125,15 @@ struct Storage {
         if (dev == DeviceType::CUDA) {
             utils::check(ntb200_malloc_async(&ptr, n, nullptr));
         } else {
-            ptr = std::aligned_alloc(64, (n + 63) / 64 * 64);  // 64-byte aligned like DeviceCPU (device.cpp:39-41)
-            if (!ptr) throw std::bad_alloc();
+            // page-locked (and therefore at least 64-byte aligned like DeviceCPU, device.cpp:39-41): host tensors feed
+            // ntb200_matmult_host, whose copies are asynchronous only from pinned memory
+            utils::check(ntb200_host_alloc(&ptr, n));
         }
     }
     ~Storage() {
         if (!ptr) return;
         if (device == DeviceType::CUDA) ntb200_free_async(ptr, nullptr);
-        else std::free(ptr);
+        else ntb200_host_free(ptr);
     }
     Storage(const Storage&) = delete;
     Storage& operator=(const Storage&) = delete;

@@ -311,3 +311,28 @@ def test_int32_tensor_route_accumulate_bias_batch(api, oracle, L):
     for i in range(3):
         oracle.matmult_into(a[i], w, exp[i])
     assert np.array_equal(host(out), exp)
+
+
+def test_pinned_host_buffers_from_the_library(api, oracle, L):
+    """ntb200_host_alloc / ntb200_host_register give page-locked host memory for ntb200_matmult_host."""
+    import ctypes
+    lib = L.lib()
+    rng = np.random.default_rng(71)
+    shape_a, shape_b, shape_c = (4, 96, 64), (4, 64, 80), (4, 96, 80)
+    bufs = []
+    for shape in (shape_a, shape_b, shape_c):
+        p = ctypes.c_void_p()
+        L.check(lib.ntb200_host_alloc(ctypes.byref(p), int(np.prod(shape)) * 4))
+        arr = np.ctypeslib.as_array(ctypes.cast(p, ctypes.POINTER(ctypes.c_float)), shape=shape)
+        bufs.append((p, arr))
+    (pa, a), (pb, b), (pc, c) = bufs
+    a[...] = normal(rng, shape_a, np.float32)
+    b[...] = normal(rng, shape_b, np.float32)
+    c[...] = 0
+    api.matmult_host(a, b, c, accumulate=False)
+    assert np.array_equal(c, oracle.matmult(a.copy(), b.copy()))
+    for p, _ in bufs:
+        L.check(lib.ntb200_host_free(p))
+    own = np.zeros((64, 64), np.float32)
+    L.check(lib.ntb200_host_register(own.ctypes.data, own.nbytes))
+    L.check(lib.ntb200_host_unregister(own.ctypes.data))
