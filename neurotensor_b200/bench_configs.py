@@ -175,8 +175,8 @@ def main():
         s, l = timed(lambda: api.conv2d(x, w, 1, 1, workspace=ws), args.steps)
         flops = 2 * 256 * 2304 * 32 * 3136
         xn, wn = x[:1].cpu().numpy(), w.cpu().numpy()
-        emit("c5 Float16 conv2d [32,256,56,56]*[256,256,3,3] s1 p1 (im2col + GEMM)", s, flops, (51.4e6 + 1.18e6 + 51.4e6), "tensor", l,
-             "", cpu_time(lambda o: o.conv2d(xn, wn, 1, 1), 32, "1 of 32 images, scaled x32"))
+        emit("c5 Float16 conv2d [32,256,56,56]*[256,256,3,3] s1 p1", s, flops, (51.4e6 + 1.18e6 + 51.4e6), "tensor", l,
+             "channels-last copy + weights reorder + implicit GEMM; NTB200_CONV_EXPLICIT=1 gives im2col + GEMM", cpu_time(lambda o: o.conv2d(xn, wn, 1, 1), 32, "1 of 32 images, scaled x32"))
         s2, l2 = timed(lambda: api.unfold2d(x, (3, 3), 1, 1, 1), args.steps)
         emit("c5 im2col alone (writes the 462 MB column matrix)", s2, 0, 51.4e6 + 462.4e6, "hbm", l2)
         col = api.unfold2d(x, (3, 3), 1, 1, 1)

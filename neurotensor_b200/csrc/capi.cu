@@ -513,6 +513,14 @@ int ntb200_conv2d(int dtype, const void* x, const void* w, void* out, void* work
     if (batch == 0) return NTB200_OK;
     if (!x || !w || !out || !workspace) return fail(NTB200_ERR_INVALID_ARG, "conv2d: null pointer");
     const int64_t L = hc * wc, ck = channels * kh * kw;
+    // 16-bit floats with stride 1 and whole 64-channel blocks: gather the GEMM's operand from a channels-last copy of
+    // the input instead of writing the column matrix (the workspace holds that copy and the reordered weights).
+    const Conv2dShape shape{dtype, batch, channels, height, width, cout, kh, kw, sh, sw, ph, pw, dh, dw, hc, wc};
+    if (conv2d_implicit_supported(shape, ntb200_conv2d_workspace_bytes(dtype, batch, channels, height, width, kh, kw, sh,
+                                                                       sw, ph, pw, dh, dw))) {
+        const int rc_implicit = launch_conv2d_implicit(shape, x, w, out, workspace, static_cast<cudaStream_t>(stream));
+        if (rc_implicit != NTB200_ERR_UNSUPPORTED) return rc_implicit;
+    }
     // The column matrix is written densely ([B][ck][L]); out[b] (cout x L) = w2d (cout x ck) . col[b] (ck x L),
     // which is the reference's matmult(col, w2d, true, true) followed by its row/col swap, with the same
     // ascending-ck order for every output element.

@@ -922,7 +922,7 @@ int launch_instance(const Maps& m, const UmmaParams& p, int grid, cudaStream_t s
 }
 
 // Number of CTA pairs that can be resident at once (one pair per TPC).
-int max_resident_pairs(const void* kernel, uint32_t smem_bytes) {
+int resident_pairs_query(const void* kernel, uint32_t smem_bytes) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(unsigned(sm_count() & ~1), 1, 1);
     cfg.blockDim = dim3(kThreadsSplit, 1, 1);
@@ -952,7 +952,7 @@ int launch_pair_instance(const Maps& m, const UmmaParams& p, cudaStream_t stream
     (void)cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) dev = 0;
     if (cached[dev] == 0)
-        cached[dev] = max_resident_pairs(reinterpret_cast<const void*>(umma_gemm_pair_kernel<kKind, kSplit>), smem);
+        cached[dev] = resident_pairs_query(reinterpret_cast<const void*>(umma_gemm_pair_kernel<kKind, kSplit>), smem);
     const int pairs = std::min(p.total_tiles, cached[dev]);
     umma_gemm_pair_kernel<kKind, kSplit><<<2 * pairs, kSplit ? kThreadsSplit : kThreads, smem, stream>>>(m.a.map, m.b.map, m.a_lo.map, m.b_lo.map, p);
     count_launch();
@@ -1290,6 +1290,19 @@ int launch_wait_timeout_selftest(unsigned long long limit_ns, cudaStream_t strea
     NTB200_CUDA(cudaGetLastError());
     return NTB200_OK;
 }
+
+unsigned int* device_status_word() {
+    void* addr = nullptr;
+    if (cudaGetSymbolAddress(&addr, g_device_status) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return nullptr;
+    }
+    return static_cast<unsigned int*>(addr);
+}
+
+void* tensor_map_encoder() { return reinterpret_cast<void*>(encode_fn()); }
+
+int max_resident_pairs(const void* kernel, uint32_t smem_bytes) { return resident_pairs_query(kernel, smem_bytes); }
 
 int read_device_status(cudaStream_t stream) {
     NTB200_CUDA(cudaStreamSynchronize(stream));

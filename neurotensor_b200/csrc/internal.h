@@ -54,6 +54,22 @@ int launch_umma_gemm(const GemmArgs& g, cudaStream_t stream);
 int read_device_status(cudaStream_t stream);
 int launch_wait_timeout_selftest(unsigned long long limit_ns, cudaStream_t stream);
 
+// Pieces of the tcgen05 GEMM translation unit that the implicit convolution shares.
+unsigned int* device_status_word();   // device address of the status word raised by bounded waits (nullptr on error)
+int max_resident_pairs(const void* kernel, uint32_t smem_bytes);   // CTA pairs of `kernel` resident at once
+void* tensor_map_encoder();           // cuTensorMapEncodeTiled from the driver, or nullptr
+
+// conv2d geometry after validation (ho, wo = output extent).
+struct Conv2dShape {
+    int dtype;
+    int64_t batch, channels, height, width, cout, kh, kw, sh, sw, ph, pw, dh, dw, ho, wo;
+};
+// Convolution straight from a channels-last copy of the input (16-bit floats, stride 1, channels % 64 == 0).
+// `launch` returns NTB200_ERR_UNSUPPORTED before launching anything when the tensor maps cannot be built.
+bool conv2d_implicit_supported(const Conv2dShape& s, size_t workspace_bytes);
+int launch_conv2d_implicit(const Conv2dShape& s, const void* x, const void* w, void* out, void* workspace,
+                           cudaStream_t stream);
+
 // CUDA-core route: every dtype, every stride pattern.
 int launch_simt_gemm(const GemmArgs& g, cudaStream_t stream);
 

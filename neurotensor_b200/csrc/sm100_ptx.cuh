@@ -103,6 +103,15 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t smem_dst, const void* 
         : "memory");
 }
 
+// 4-D form of the pair load (channels-last image boxes: channel, x, y, image).
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t smem_dst, const void* tmap, uint32_t bar, int c0, int c1,
+                                                 int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+        ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar & kPeerBitMask)
+        : "memory");
+}
+
 // ---- cluster -------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t cluster_cta_rank() {
     uint32_t r;

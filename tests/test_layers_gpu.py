@@ -76,9 +76,63 @@ def test_conv2d_f16_tensor_cores(api, oracle):
     x = normal(rng, (4, 64, 28, 28), np.float16)
     w = normal(rng, (96, 64, 3, 3), np.float16, (1.0 / (64 * 9)) ** 0.5)
     got = host(api.conv2d(dev(x), dev(w), stride=1, padding=1))
-    assert _lib.last_route() == "umma_f16"
+    assert _lib.last_route() == "conv2d-implicit-umma-pair"
     exp = oracle.conv2d(x, w, stride=1, padding=1)
     assert oracle.rel_fro(got, exp) <= 2e-3
+
+
+IMPLICIT_CASES = [
+    # batch, channels, height, width, cout, kernel, padding, dilation
+    (3, 64, 28, 28, 96, (3, 3), (1, 1), (1, 1)),      # 4 output rows per CTA, 224-pixel tiles
+    (2, 128, 20, 24, 300, (3, 5), (2, 1), (2, 1)),    # two M tiles, dilation, Wo = 22: 176-pixel tiles
+    (2, 128, 9, 22, 40, (3, 3), (0, 0), (1, 1)),      # Wo = 20: 6 rows per CTA, 240-pixel tiles, last tile ragged
+    (3, 64, 7, 20, 130, (3, 1), (1, 0), (1, 1)),      # L = 140: rows of the output not 16-byte aligned
+    (2, 64, 12, 130, 64, (1, 3), (0, 0), (1, 1)),     # Wo = 128: one output row per CTA
+    (5, 192, 14, 14, 256, (3, 3), (1, 1), (1, 1)),    # 8 rows per CTA, K = 27 blocks
+    (1, 64, 6, 10, 32, (5, 5), (4, 4), (1, 1)),       # padding wider than the kernel's reach: Wo = 14 > W
+    (2, 64, 7, 15, 48, (3, 3), (1, 1), (1, 1)),       # odd image size: element-wise channels-last copy
+    (1, 64, 6, 27, 16, (3, 3), (1, 0), (1, 1)),       # Wo = 25: no whole groups of eight pixels -> column path
+]
+
+
+@pytest.mark.parametrize("case", IMPLICIT_CASES)
+def test_conv2d_without_column_matrix_matches_oracle_and_column_path(api, oracle, case):
+    """Stride-1 16-bit convolutions read the input through a channels-last copy (no column matrix).  They must
+    agree with the oracle and with the column-matrix path (NTB200_CONV_EXPLICIT=1), which orders K differently."""
+    from neurotensor_b200 import _lib
+    bsz, ch, h, wd, cout, kernel, padding, dilation = case
+    rng = np.random.default_rng(hash(case) % (2 ** 31))
+    x = normal(rng, (bsz, ch, h, wd), np.float16)
+    w = normal(rng, (cout, ch) + kernel, np.float16, (1.0 / (ch * kernel[0] * kernel[1])) ** 0.5)
+    got = host(api.conv2d(dev(x), dev(w), stride=1, padding=padding, dilation=dilation))
+    route = _lib.last_route()
+    wo = wd + 2 * padding[1] - dilation[1] * (kernel[1] - 1)
+    has_rows = any((r * wo) % 8 == 0 for r in range(1, 128 // wo + 1))
+    assert route == "conv2d-implicit-umma-pair" if has_rows else route in ("umma_f16", "simt")
+    exp = oracle.conv2d(x, w, stride=1, padding=padding, dilation=dilation)
+    assert got.shape == exp.shape
+    assert oracle.rel_fro(got, exp) <= 2e-3
+    os.environ["NTB200_CONV_EXPLICIT"] = "1"
+    try:
+        col = host(api.conv2d(dev(x), dev(w), stride=1, padding=padding, dilation=dilation))
+        assert _lib.last_route() in ("umma_f16", "simt")
+    finally:
+        del os.environ["NTB200_CONV_EXPLICIT"]
+    assert oracle.rel_fro(got, col) <= 2e-3
+    # every element, not just the norm: a misplaced tile would show as a large single error
+    assert np.max(np.abs(got.astype(np.float32) - exp.astype(np.float32))) <= 0.02 * max(1.0, float(np.max(np.abs(exp))))
+
+
+def test_conv2d_without_column_matrix_bf16(api, oracle):
+    from neurotensor_b200 import _lib
+    rng = np.random.default_rng(23)
+    xb = oracle.bf16_round(normal(rng, (2, 64, 16, 16), np.float32))
+    wb = oracle.bf16_round(normal(rng, (72, 64, 3, 3), np.float32, (1.0 / (64 * 9)) ** 0.5))
+    got = api.conv2d(dev(xb, bf16=True), dev(wb, bf16=True), stride=1, padding=1)
+    assert _lib.last_route() == "conv2d-implicit-umma-pair"
+    # the oracle convolves the exact float32 values of the bf16 inputs; the kernel rounds its fp32 sums to bf16 once
+    exp = oracle.conv2d(oracle.bf16_widen(xb), oracle.bf16_widen(wb), stride=1, padding=1)
+    assert oracle.rel_fro(got.float().cpu().numpy(), exp) <= 6e-3
 
 
 def test_conv2d_errors(api):

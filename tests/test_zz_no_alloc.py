@@ -39,15 +39,16 @@ def _both(L, code, x, w, geom):
 def test_static_scratch_conv2d_matches_workspace_conv2d_twice():
     from neurotensor_b200 import _lib as L
     gen = torch.Generator(device="cuda").manual_seed(123)
-    # call 1: Float16 on the tensor-core route, padded 3x3, fills ~7 MB of the scratch
+    # call 1: Float16 on the tensor cores, padded 3x3; the scratch receives the channels-last copy of the input and
+    # the reordered weights
     x1 = torch.randn((4, 64, 28, 28), generator=gen, device="cuda").half()
     w1 = (torch.randn((96, 64, 3, 3), generator=gen, device="cuda") / 24).half()
     ref1, got1 = _both(L, L.F16, x1, w1, (1, 1, 1, 1, 1, 1))
-    assert L.last_route() == "umma_f16"
+    assert L.last_route() == "conv2d-implicit-umma-pair"
     assert not torch.isnan(got1).any()
     assert torch.equal(got1, ref1)          # same kernels on the same data: identical bits
     # call 2 straight after, a smaller Float32 problem with different geometry: the scratch still holds call 1's
-    # column matrix, none of which may show up in the result
+    # data, none of which may show up in the result
     x2 = torch.randn((2, 5, 17, 13), generator=gen, device="cuda")
     w2 = torch.randn((7, 5, 2, 4), generator=gen, device="cuda")
     ref2, got2 = _both(L, L.F32, x2, w2, (2, 1, 0, 3, 1, 2))
