@@ -188,7 +188,9 @@ int ntb200_col2im(int dtype, const void* col, void* im, int64_t batch, int64_t c
                   int64_t dw, void* stream);
 /* Replaces functional::conv2d for groups == 1 (nt/functional/tensor_files/conv.cpp:69-96):
  * out[B, Cout, Ho, Wo] = unfold2d(x) contracted with w[Cout, C*kh*kw].  `workspace` must hold
- * ntb200_conv2d_workspace_bytes(...) bytes (the column matrix). */
+ * ntb200_conv2d_workspace_bytes(...) bytes (the column matrix).  F16 / BF16 with stride 1 and channels a
+ * multiple of 64 skip the column matrix: the workspace then holds a channels-last copy of x and the
+ * reordered weights, and the fp32 sums run tap-major before the single rounding. */
 size_t ntb200_conv2d_workspace_bytes(int dtype, int64_t batch, int64_t channels, int64_t height, int64_t width,
                                      int64_t kh, int64_t kw, int64_t sh, int64_t sw, int64_t ph, int64_t pw,
                                      int64_t dh, int64_t dw);
