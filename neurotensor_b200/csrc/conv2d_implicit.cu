@@ -263,7 +263,7 @@ conv2d_implicit_pair_kernel(const __grid_constant__ CUtensorMap tma_w, const __g
 //     is kept in tile row (c >> 1) + 32 * (c & 1): the two halves of an output word then sit in rows that differ by
 //     32, and with a row stride of 33 words the 32 lanes of a warp read 32 different banks.
 //   the remaining blocks: w[cout][c][tap] -> wp[cout][tap][c].
-template <bool kVec>
+template <int kVec>
 __global__ void __launch_bounds__(256)
 conv_prepare_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ xt, int channels, int hw, int tiles_p,
                     int tiles_c, int tr_blocks, const uint16_t* __restrict__ w, uint16_t* __restrict__ wp, int taps,
@@ -278,13 +278,45 @@ conv_prepare_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ xt, i
         wp[idx] = w[(co * channels + c) * taps + t];
         return;
     }
-    __shared__ uint32_t tile[64][33];
+    __shared__ __align__(16) uint32_t tile[64][33];
     const int pt = int(blockIdx.x) % tiles_p;
     const int rest = int(blockIdx.x) / tiles_p;
     const int ct = rest % tiles_c, b = rest / tiles_c;
     const size_t image = size_t(b) * size_t(channels) * size_t(hw);
     const int c0 = ct * 64, p0 = pt * 64;
-    if constexpr (kVec) {
+    if constexpr (kVec == 8) {
+        // hw is a multiple of 8 and the bases are 16-byte aligned: 16-byte loads (8 pixels of one channel) and
+        // 16-byte stores (8 channels of one pixel).  The tile keeps 128-byte rows [channel][64 pixels] whose
+        // 16-byte chunks are XOR-ed with bits 3..5 of the channel, so the eight channels one output vector needs
+        // (same pixel, channels 8*cw .. 8*cw+7 for the eight cw of a quarter warp) come from different banks.
+        uint4* t128 = reinterpret_cast<uint4*>(&tile[0][0]);          // [64 rows][8 chunks]
+        const uint16_t* t16 = reinterpret_cast<const uint16_t*>(&tile[0][0]);
+#pragma unroll
+        for (int it = 0; it < 2; ++it) {
+            const int idx = it * 256 + int(threadIdx.x);
+            const int c = idx >> 3, chunk = idx & 7;
+            if (p0 + 8 * chunk < hw)
+                t128[c * 8 + (chunk ^ ((c >> 3) & 7))] =
+                    *reinterpret_cast<const uint4*>(x + image + size_t(c0 + c) * hw + p0 + 8 * chunk);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int it = 0; it < 2; ++it) {
+            const int idx = it * 256 + int(threadIdx.x);
+            const int pp = idx >> 3, cw = idx & 7;
+            if (p0 + pp < hw) {
+                uint32_t v[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int ce = 8 * cw + 2 * q;   // channels ce, ce + 1: same (c >> 3), so the same chunk swizzle
+                    const int at = (((pp >> 3) ^ cw) << 3) + (pp & 7);
+                    v[q] = uint32_t(t16[ce * 64 + at]) | (uint32_t(t16[(ce + 1) * 64 + at]) << 16);
+                }
+                *reinterpret_cast<uint4*>(xt + image + size_t(p0 + pp) * channels + c0 + 8 * cw) =
+                    make_uint4(v[0], v[1], v[2], v[3]);
+            }
+        }
+    } else if constexpr (kVec == 2) {
 #pragma unroll
         for (int it = 0; it < 8; ++it) {
             const int idx = it * 256 + int(threadIdx.x);
@@ -428,8 +460,10 @@ int launch_conv2d_implicit(const Conv2dShape& s, const void* x, const void* w, v
     const long long w_total = (long long)s.cout * ck;
     const long long blocks = tr_blocks + (w_total + 255) / 256;
     if (blocks >= (int64_t(1) << 31)) return NTB200_ERR_UNSUPPORTED;
-    const bool vec = hw % 2 == 0 && reinterpret_cast<uintptr_t>(x) % 4 == 0;
-    auto prepare = vec ? conv_prepare_kernel<true> : conv_prepare_kernel<false>;
+    const uintptr_t x_addr = reinterpret_cast<uintptr_t>(x);
+    auto prepare = (hw % 8 == 0 && x_addr % 16 == 0) ? conv_prepare_kernel<8>
+                   : (hw % 2 == 0 && x_addr % 4 == 0) ? conv_prepare_kernel<2>
+                                                       : conv_prepare_kernel<0>;
     prepare<<<unsigned(blocks), 256, 0, stream>>>(static_cast<const uint16_t*>(x), xt, int(s.channels), hw, tiles_p,
                                                   tiles_c, int(tr_blocks), static_cast<const uint16_t*>(w), wp,
                                                   int(taps), w_total);
