@@ -198,6 +198,26 @@ int ntb200_conv2d(int dtype, const void* x, const void* w, void* out, void* work
                   int64_t channels, int64_t height, int64_t width, int64_t cout, int64_t kh, int64_t kw, int64_t sh,
                   int64_t sw, int64_t ph, int64_t pw, int64_t dh, int64_t dw, void* stream);
 
+/* conv2d backward, groups == 1.  Replaces conv_dimage (nt/functional/tensor_files/conv.cpp:318-346):
+ *   d_image[B, C, H, W] = col2im( w2d^T . grad )       grad is [B, Cout, Ho, Wo]; d_image is overwritten
+ * and conv_dkernel (conv.cpp:444-471):
+ *   d_kernel[Cout, C, kh, kw] (+)= sum over the batch of grad[b] . unfold2d(x)[b]^T
+ * (`accumulate` != 0 adds to d_kernel as the reference's `d_kernel +=` does).  F32, F16, BF16.  `workspace` must
+ * hold ntb200_conv2d_backward_workspace_bytes(...) bytes; one size serves both calls.  For F16 / BF16 with
+ * stride 1 the image gradient is evaluated as a convolution of grad with the flipped kernel (no gradient
+ * column matrix), which sums in a different order than col2im. */
+size_t ntb200_conv2d_backward_workspace_bytes(int dtype, int64_t batch, int64_t channels, int64_t height,
+                                              int64_t width, int64_t cout, int64_t kh, int64_t kw, int64_t sh,
+                                              int64_t sw, int64_t ph, int64_t pw, int64_t dh, int64_t dw);
+int ntb200_conv2d_backward_image(int dtype, const void* grad, const void* w, void* d_image, void* workspace,
+                                 int64_t batch, int64_t channels, int64_t height, int64_t width, int64_t cout,
+                                 int64_t kh, int64_t kw, int64_t sh, int64_t sw, int64_t ph, int64_t pw, int64_t dh,
+                                 int64_t dw, void* stream);
+int ntb200_conv2d_backward_kernel(int dtype, const void* x, const void* grad, void* d_kernel, void* workspace,
+                                  int accumulate, int64_t batch, int64_t channels, int64_t height, int64_t width,
+                                  int64_t cout, int64_t kh, int64_t kw, int64_t sh, int64_t sw, int64_t ph,
+                                  int64_t pw, int64_t dh, int64_t dw, void* stream);
+
 /* ntb200_conv2d for callers that cannot allocate device memory.  No counterpart in the reference, which
  * allocates its column matrix on the CPU heap as it goes.  Some users of this library cannot do the
  * device-side equivalent: their application has given the whole device heap to its own allocator, so a

@@ -299,21 +299,33 @@ def conv2d(x, w, stride=1, padding=0, dilation=1, groups=1, workspace=None):
     return out
 
 
-def conv2d_backward(x, w, grad, stride=1, padding=0, dilation=1):
+def conv2d_backward(x, w, grad, stride=1, padding=0, dilation=1, workspace=None):
     """conv_dimage (conv.cpp:318-346) and conv_dkernel (conv.cpp:444-471) for groups == 1 -> (d_image, d_kernel):
-    d_image = col2im(matmult(w2d, grad, true, false)); d_kernel = sum over the batch of matmult(grad, col, false, true)."""
+    d_image = col2im(matmult(w2d, grad, true, false)); d_kernel = sum over the batch of matmult(grad, col, false, true).
+    Both run inside the library (ntb200_conv2d_backward_image / _kernel) on one shared workspace."""
     _require_cuda(x, w, grad)
+    if not (x.dtype == w.dtype == grad.dtype):
+        raise ValueError("conv2d_backward: image, kernel and gradient must share a dtype")
     w4 = (w.unsqueeze(0) if w.dim() == 3 else w).contiguous()
     x4, (kh, kw, sh, sw, ph, pw, dh, dw), ho, wo = _conv_geom(x, w4.shape[-2:], dilation, padding, stride)
-    bsz, cout = x4.shape[0], w4.shape[0]
-    w2d = w4.reshape(cout, -1)
-    g = grad.contiguous().reshape(bsz, cout, ho * wo)
-    dcol = matmult(w2d, g, True, False)                                   # [B, C*kh*kw, L]
-    dx = unfold2d_backward(dcol, x4.shape[-2:], (kh, kw), (dh, dw), (ph, pw), (sh, sw)).reshape(x.shape)
-    col = unfold2d(x4, (kh, kw), (dh, dw), (ph, pw), (sh, sw))
-    per_image = matmult(g, col, False, True)                              # [B, Cout, C*kh*kw]
-    dw_ = column_sum(per_image.reshape(bsz, -1)).reshape(w.shape)         # reduce over the batch
-    return dx, dw_
+    x4 = x4.contiguous()
+    bsz, ch, h, wd = x4.shape
+    cout = w4.shape[0]
+    g = grad.contiguous()
+    if g.numel() != bsz * cout * ho * wo:
+        raise ValueError("conv2d_backward: gradient has %d elements, expected [%d, %d, %d, %d]"
+                         % (g.numel(), bsz, cout, ho, wo))
+    code = dtype_code(x)
+    need = lib().ntb200_conv2d_backward_workspace_bytes(code, bsz, ch, h, wd, cout, kh, kw, sh, sw, ph, pw, dh, dw)
+    if workspace is None or workspace.numel() * workspace.element_size() < need:
+        workspace = torch.empty(need, dtype=torch.uint8, device=x.device)
+    dx = torch.empty_like(x4)
+    dw_ = torch.empty_like(w4)
+    check(lib().ntb200_conv2d_backward_image(code, g.data_ptr(), w4.data_ptr(), dx.data_ptr(), workspace.data_ptr(), bsz,
+                                             ch, h, wd, cout, kh, kw, sh, sw, ph, pw, dh, dw, _stream()))
+    check(lib().ntb200_conv2d_backward_kernel(code, x4.data_ptr(), g.data_ptr(), dw_.data_ptr(), workspace.data_ptr(), 0,
+                                              bsz, ch, h, wd, cout, kh, kw, sh, sw, ph, pw, dh, dw, _stream()))
+    return dx.reshape(x.shape), dw_.reshape(w.shape)
 
 
 def relu(x):

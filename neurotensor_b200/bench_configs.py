@@ -185,6 +185,25 @@ def main():
         s3, l3 = timed(lambda: api.gemm(w2d, col, out), args.steps)
         emit("c5 GEMM alone: w[256,2304] x col[32,2304,3136]", s3, flops, 0, "tensor", l3)
         del col, out
+        # backward of the same convolution (the step after the C5 forward): image and kernel gradients
+        g = randn(gen, (32, 256, 56, 56), torch.float16)
+        need = api.lib().ntb200_conv2d_backward_workspace_bytes(api.dtype_code(x), 32, 256, 56, 56, 256, 3, 3, 1, 1, 1, 1, 1, 1)
+        wsb = torch.empty(need, dtype=torch.uint8, device="cuda")
+        dxb, dwb = torch.empty_like(x), torch.empty_like(w)
+
+        def bwd_image():
+            api.check(api.lib().ntb200_conv2d_backward_image(api.dtype_code(x), g.data_ptr(), w.data_ptr(), dxb.data_ptr(),
+                                                             wsb.data_ptr(), 32, 256, 56, 56, 256, 3, 3, 1, 1, 1, 1, 1, 1, None))
+
+        def bwd_kernel():
+            api.check(api.lib().ntb200_conv2d_backward_kernel(api.dtype_code(x), x.data_ptr(), g.data_ptr(), dwb.data_ptr(),
+                                                              wsb.data_ptr(), 0, 32, 256, 56, 56, 256, 3, 3, 1, 1, 1, 1, 1, 1, None))
+
+        s4, l4 = timed(bwd_image, args.steps)
+        emit("c5 backward, image gradient [32,256,56,56]", s4, flops, 0, "tensor", l4)
+        s5, l5 = timed(bwd_kernel, args.steps)
+        emit("c5 backward, kernel gradient [256,256,3,3]", s5, flops, 0, "tensor", l5)
+        del g, wsb, dxb, dwb
         del x, w, ws
 
     for n in (512, 1024, 2048, 4096, 8192, 16384):

@@ -168,6 +168,9 @@ int ensure(void** p, size_t* cap, size_t bytes) {
 }
 
 }  // namespace
+
+int route_gemm(const GemmArgs& g, int route, cudaStream_t stream) { return run_gemm(g, route, stream); }
+
 }  // namespace ntb200
 
 using namespace ntb200;

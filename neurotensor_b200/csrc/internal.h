@@ -73,6 +73,9 @@ int launch_conv2d_implicit(const Conv2dShape& s, const void* x, const void* w, v
 // CUDA-core route: every dtype, every stride pattern.
 int launch_simt_gemm(const GemmArgs& g, cudaStream_t stream);
 
+// The route decision every GEMM of the library goes through (tcgen05, CUDA cores or a plain fill of C).
+int route_gemm(const GemmArgs& g, int route, cudaStream_t stream);
+
 // K == 0 or pure bias/zero fill of C.
 int launch_fill_c(const GemmArgs& g, cudaStream_t stream);
 

@@ -291,3 +291,60 @@ def test_fused_relu_epilogues_equal_the_separate_kernels(api, m, k, n, bf16):
     dh = api.matmult_relu_backward(g2, w2, h, transpose_b=True)
     assert _lib.launch_count() == before + 1
     assert torch.equal(dh, api.relu_backward(h, api.matmult(g2, w2, False, True)))
+
+
+BACKWARD_CASES = [
+    # batch, channels, height, width, cout, kernel, stride, padding, dilation
+    (3, 64, 14, 14, 128, (3, 3), (1, 1), (1, 1), (1, 1)),    # image gradient = implicit convolution of grad
+    (2, 32, 12, 16, 64, (3, 3), (1, 1), (1, 1), (1, 1)),     # grad has 64 channels: implicit; the image has 32
+    (2, 64, 13, 16, 48, (3, 2), (2, 1), (1, 0), (1, 2)),     # stride 2: GEMM + col2im
+    (1, 16, 10, 10, 8, (5, 5), (1, 1), (0, 0), (1, 1)),      # one image: the product is the kernel gradient
+]
+
+
+@pytest.mark.parametrize("case", BACKWARD_CASES)
+def test_conv2d_backward_f16_matches_oracle(api, oracle, case):
+    """ntb200_conv2d_backward_image / _kernel on Float16 against the oracle evaluated in Float32 on the same values,
+    and the image gradient's two routes (convolution of grad with the flipped kernel; GEMM + col2im) against each
+    other."""
+    bsz, ch, h, wd, cout, kernel, stride, padding, dilation = case
+    rng = np.random.default_rng(hash(case) % (2 ** 31))
+    x = normal(rng, (bsz, ch, h, wd), np.float16)
+    w = normal(rng, (cout, ch) + kernel, np.float16, (1.0 / (ch * kernel[0] * kernel[1])) ** 0.5)
+    ho = (h + 2 * padding[0] - dilation[0] * (kernel[0] - 1) - 1) // stride[0] + 1
+    wo = (wd + 2 * padding[1] - dilation[1] * (kernel[1] - 1) - 1) // stride[1] + 1
+    g = normal(rng, (bsz, cout, ho, wo), np.float16)
+    dx, dw = api.conv2d_backward(dev(x), dev(w), dev(g), stride=stride, padding=padding, dilation=dilation)
+    exp_dx, exp_dw = oracle.conv2d_backward(x.astype(np.float32), w.astype(np.float32), g.astype(np.float32),
+                                            stride=stride, padding=padding, dilation=dilation)
+    assert oracle.rel_fro(host(dx), exp_dx) <= 2e-3
+    assert oracle.rel_fro(host(dw), exp_dw) <= 4e-3     # rounded per image, then once more by the sum over the batch
+    os.environ["NTB200_CONV_EXPLICIT"] = "1"
+    try:
+        dx2, dw2 = api.conv2d_backward(dev(x), dev(w), dev(g), stride=stride, padding=padding, dilation=dilation)
+    finally:
+        del os.environ["NTB200_CONV_EXPLICIT"]
+    assert oracle.rel_fro(host(dx2), exp_dx) <= 2e-3
+    assert oracle.rel_fro(host(dx), host(dx2)) <= 2e-3
+    assert torch.equal(dw, dw2)
+
+
+def test_conv2d_backward_kernel_accumulates_and_rejects_integers(api):
+    from neurotensor_b200 import _lib
+    lib = _lib.lib()
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn((3, 8, 9, 9), generator=gen, device="cuda")
+    w = torch.randn((6, 8, 3, 3), generator=gen, device="cuda")
+    g = torch.randn((3, 6, 9, 9), generator=gen, device="cuda")
+    _, dw = api.conv2d_backward(x, w, g, stride=1, padding=1)
+    need = lib.ntb200_conv2d_backward_workspace_bytes(_lib.F32, 3, 8, 9, 9, 6, 3, 3, 1, 1, 1, 1, 1, 1)
+    ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+    acc = torch.ones_like(w)
+    _lib.check(lib.ntb200_conv2d_backward_kernel(_lib.F32, x.data_ptr(), g.data_ptr(), acc.data_ptr(), ws.data_ptr(), 1,
+                                                 3, 8, 9, 9, 6, 3, 3, 1, 1, 1, 1, 1, 1, None))
+    assert torch.equal(acc, dw + 1.0)      # d_kernel += ..., as the reference does
+    xi = torch.zeros((1, 8, 9, 9), dtype=torch.int32, device="cuda")
+    rc = lib.ntb200_conv2d_backward_image(_lib.I32, xi.data_ptr(), xi.data_ptr(), xi.data_ptr(), ws.data_ptr(), 1, 8, 9, 9,
+                                          6, 3, 3, 1, 1, 1, 1, 1, 1, None)
+    assert rc == _lib.ERR_UNSUPPORTED
+    assert "Float32" in lib.ntb200_last_error_string().decode()
