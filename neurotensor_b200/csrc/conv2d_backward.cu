@@ -89,6 +89,8 @@ size_t ntb200_conv2d_backward_workspace_bytes(int dtype, int64_t batch, int64_t 
                                                              dw * (kw - 1) - pw, dh, dw);
         need = std::max(need, round256(conv_ws) + size_t(cout) * size_t(channels * kh * kw) * es);
     }
+    const Conv2dShape shape{dtype, batch, channels, height, width, cout, kh, kw, sh, sw, ph, pw, dh, dw, ho, wo};
+    need = std::max(need, conv2d_dkernel_implicit_bytes(shape));
     return need;
 }
 
@@ -142,6 +144,11 @@ int ntb200_conv2d_backward_kernel(int dtype, const void* x, const void* grad, vo
     if (!x || !grad || !d_kernel || !workspace) return fail(NTB200_ERR_INVALID_ARG, "conv2d_backward_kernel: null pointer");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const size_t es = dtype_size(dtype);
+    {   // 16-bit floats, stride 1: the implicit GEMM over channels-last copies (no column matrix)
+        const Conv2dShape shape{dtype, batch, channels, height, width, cout, kh, kw, sh, sw, ph, pw, dh, dw, g.ho, g.wo};
+        const int rc = launch_conv2d_dkernel_implicit(shape, x, grad, d_kernel, workspace, accumulate, s);
+        if (rc != NTB200_ERR_UNSUPPORTED) return rc;
+    }
     void* col = workspace;
     void* per_image = static_cast<char*>(workspace) + round256(size_t(batch) * size_t(g.ck) * size_t(g.L) * es);
     if (int rc = ntb200_im2col(dtype, x, col, batch, channels, height, width, kh, kw, sh, sw, ph, pw, dh, dw, stream)) return rc;

@@ -487,4 +487,365 @@ int launch_conv2d_implicit(const Conv2dShape& s, const void* x, const void* w, v
     return NTB200_OK;
 }
 
+// ---- kernel gradient -----------------------------------------------------------------------------------
+// d_kernel[co][c][i][j] = sum over images b and output pixels (y, x) of
+//     grad[b][co][y][x] * image[b][c][y + i*dh - ph][x + j*dw - pw]          (conv.cpp:444-471 without the column matrix)
+// As a GEMM: M = co, N = (tap, c), K = (b, y, x).  With channels-last copies of grad and of the image, both
+// operands have their M / N index contiguous and the pixels as rows, i.e. they are MN-major operand tiles:
+//   A chunk = gt[b][y0 .. +r][0 .. Wo][co0 .. +64]                      r*Wo pixel rows of 128 bytes
+//   B chunk = xt[b][y0 + i*dh - ph .. +r][j*dw - pw .. +Wo][c0 .. +64]  the same pixels, shifted by the tap
+// each fetched by one 4-D TMA box (zero-filled outside the image).  One stage holds r*Wo pixels of K for the
+// 2 x 64 output channels and 2 x 64 (tap, c) columns of one CTA; the pair's UMMA is 256 x 256 x 16.  There are only
+// (Cout/256) x (taps*C/256) output tiles, so K is also split over groups of images: every (group, tile) is one work
+// item with its own fp32 partial result, and dkernel_reduce_kernel adds the groups, restores the [co][c][tap]
+// order and rounds once.
+namespace {
+
+constexpr uint32_t kDkSmemLimit = 232448 - 2048;   // dynamic shared memory per CTA minus barriers and alignment slack
+
+struct DkParams {
+    int cout, channels, taps, n_total;   // n_total = taps * channels
+    int tiles_m, tiles_n, groups, images_per_group, batch, total_items;
+    int row_blocks;                       // ceil(Ho / rows)
+    int rows, ksteps;                     // output rows per stage; rows * Wo / 16
+    uint32_t chunk_bytes;                 // rows * Wo * 128
+    uint32_t stage_bytes;                 // 4 chunks
+    int stages;
+    int kw, dh, dw, ph, pw;
+    uint32_t idesc;
+    float* partial;                       // [groups][cout][n_total]
+    unsigned int* status;
+};
+
+__device__ __forceinline__ void dk_timeout(const DkParams& p, volatile uint32_t* abort_flag, unsigned int where) {
+    *abort_flag = 1;
+    atomicExch(p.status, 0x100u | where);
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kConvThreads, 1)
+conv2d_dkernel_pair_kernel(const __grid_constant__ CUtensorMap tma_g, const __grid_constant__ CUtensorMap tma_x,
+                           const DkParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const int stages = p.stages;
+    uint8_t* bar_gen = smem_gen + stages * p.stage_bytes;
+    const uint32_t bar_base = smem_base + stages * p.stage_bytes;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (stages + s); };
+    auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * stages + a); };
+    auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * stages + 2 + a); };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_gen + 8 * (2 * stages + 4));
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_cta_rank();
+    const bool leader = rank == 0;
+    const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+    const int tiles = p.tiles_m * p.tiles_n;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(tfull_bar(a), 1);
+            mbar_init(tempty_bar(a), 8);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+        fence_proxy_async_smem();
+        tma_prefetch_desc(&tma_g);
+        tma_prefetch_desc(&tma_x);
+    }
+    if (warp == 1) {
+        tmem_alloc<2>(smem_u32(const_cast<uint32_t*>(tmem_slot)), kConvTmemCols);
+        tmem_relinquish<2>();
+    }
+    tcgen05_fence_before();
+    cluster_sync_all();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer (both CTAs)
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = pair; ok && t < p.total_items; t += npairs) {
+                const int g = t / tiles, r = t - g * tiles;
+                const int mi = r / p.tiles_n, ni = r - mi * p.tiles_n;
+                const int co0 = mi * 256 + int(rank) * 128;
+                int c0[2], sh_y[2], sh_x[2];
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {   // the two 64-wide (tap, c) chunks this CTA stages
+                    const int nidx = ((ni * 2 + int(rank)) * 2 + q) * 64;
+                    const int tap = nidx / p.channels;
+                    c0[q] = nidx - tap * p.channels;
+                    const int ti = tap / p.kw, tj = tap - ti * p.kw;
+                    sh_y[q] = ti * p.dh - p.ph;
+                    sh_x[q] = tj * p.dw - p.pw;
+                }
+                const int img_end = min(p.batch, (g + 1) * p.images_per_group);
+                for (int img = g * p.images_per_group; ok && img < img_end; ++img) {
+                    for (int rb = 0; rb < p.row_blocks; ++rb) {
+                        if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
+                            dk_timeout(p, abort_flag, 0x31);
+                            ok = false;
+                            break;
+                        }
+                        const uint32_t a_dst = smem_base + stage * p.stage_bytes;
+                        const uint32_t b_dst = a_dst + 2 * p.chunk_bytes;
+                        const uint32_t bar = full_bar(stage);
+                        if (leader) mbar_expect_tx(bar, 2 * p.stage_bytes);
+                        const int y0 = rb * p.rows;
+                        tma_load_4d_pair(a_dst, &tma_g, bar, co0, 0, y0, img);
+                        tma_load_4d_pair(a_dst + p.chunk_bytes, &tma_g, bar, co0 + 64, 0, y0, img);
+                        tma_load_4d_pair(b_dst, &tma_x, bar, c0[0], sh_x[0], y0 + sh_y[0], img);
+                        tma_load_4d_pair(b_dst + p.chunk_bytes, &tma_x, bar, c0[1], sh_x[1], y0 + sh_y[1], img);
+                        if (++stage == stages) { stage = 0; phase ^= 1u; }
+                    }
+                }
+            }
+            if (ok) {
+                for (int s = 0; s < stages; ++s) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { dk_timeout(p, abort_flag, 0x32); break; }
+                    if (++stage == stages) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer (even CTA only)
+        if (leader && lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int t = pair; ok && t < p.total_items; t += npairs) {
+                const int g = t / tiles;
+                const int n_img = min(p.batch, (g + 1) * p.images_per_group) - g * p.images_per_group;
+                const int n_stages = n_img * p.row_blocks;
+                if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
+                    dk_timeout(p, abort_flag, 0x33);
+                    break;
+                }
+                tcgen05_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * 256;
+                for (int it = 0; it < n_stages; ++it) {
+                    if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
+                        dk_timeout(p, abort_flag, 0x34);
+                        ok = false;
+                        break;
+                    }
+                    tcgen05_fence_after();
+                    const uint32_t a_addr = smem_base + stage * p.stage_bytes;
+                    const uint64_t a_desc = make_smem_desc_sw128(a_addr, p.chunk_bytes, 1024);
+                    const uint64_t b_desc = make_smem_desc_sw128(a_addr + 2 * p.chunk_bytes, p.chunk_bytes, 1024);
+                    for (int k = 0; k < p.ksteps; ++k)   // 16 pixel rows (2048 bytes) per instruction
+                        umma<MmaKind::f16, 2>(d_tmem, a_desc + uint64_t(k * 128), b_desc + uint64_t(k * 128), p.idesc,
+                                              (it | k) != 0);
+                    umma_commit_pair(empty_bar(stage), 3);
+                    if (++stage == stages) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                umma_commit_pair(tfull_bar(acc), 3);
+                if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (both CTAs): fp32 partials
+        const int quad = warp & 3;
+        const int row_in_tile = int(rank) * 128 + quad * 32 + lane;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        for (int t = pair; t < p.total_items; t += npairs) {
+            const int g = t / tiles, r = t - g * tiles;
+            const int mi = r / p.tiles_n, ni = r - mi * p.tiles_n;
+            bool ok = mbar_wait(tfull_bar(acc), acc_phase, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) {
+                if (lane == 0) dk_timeout(p, abort_flag, 0x35);
+                break;
+            }
+            tcgen05_fence_after();
+            const int row = mi * 256 + row_in_tile;
+            const int n0 = ni * 256;
+            const uint32_t taddr = tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * 256);
+            float* out_row = p.partial + ((long long)g * p.cout + row) * (long long)p.n_total;
+#pragma unroll 1
+            for (int cc = 0; cc < 8; ++cc) {
+                const int col0 = n0 + cc * 32;
+                if (col0 >= p.n_total) break;   // n_total is a multiple of 64: chunks are whole
+                uint32_t v[32];
+                tmem_ld_32x32b_x32(taddr + uint32_t(cc * 32), v);
+                tmem_ld_wait();
+                if (row >= p.cout) continue;
+                float4* dst = reinterpret_cast<float4*>(out_row + col0);
+#pragma unroll
+                for (int q = 0; q < 8; ++q)
+                    dst[q] = make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]),
+                                         __uint_as_float(v[4 * q + 2]), __uint_as_float(v[4 * q + 3]));
+            }
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_leader(tempty_bar(acc));
+            if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+        }
+    }
+
+    tcgen05_fence_before();
+    cluster_sync_all();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tmem_dealloc<2>(tmem_base, kConvTmemCols);
+    }
+}
+
+// d_kernel[co][c][tap] (+)= sum over groups of partial[g][co][tap * C + c], rounded once.
+__global__ void dkernel_reduce_kernel(const float* __restrict__ partial, uint16_t* __restrict__ dk, int groups,
+                                      long long per_group, int n_total, int channels, int taps, int bf16, int accumulate) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= per_group) return;
+    float sum = 0.f;
+    for (int g = 0; g < groups; ++g) sum += partial[(long long)g * per_group + idx];
+    const long long co = idx / n_total;
+    const int n = int(idx - co * n_total);
+    const int tap = n / channels, c = n - tap * channels;
+    uint16_t* dst = dk + (co * channels + c) * taps + tap;
+    if (accumulate)
+        sum += bf16 ? __bfloat162float(__ushort_as_bfloat16(*dst)) : __half2float(__ushort_as_half(*dst));
+    *dst = uint16_t(pack16(sum, 0.f, bf16));
+}
+
+// Output rows per stage for the kernel gradient: the most rows whose pixels are at most 128 and a multiple of 16.
+int dk_rows_per_stage(int64_t wo) {
+    for (int64_t r = 128 / wo; r >= 1; --r)
+        if ((r * wo) % 16 == 0) return int(r);
+    return 0;
+}
+
+struct DkPlan {
+    int rows, groups, images_per_group, tiles_m, tiles_n;
+    size_t xt_bytes, gt_bytes, partial_bytes;
+};
+
+bool dk_plan(const Conv2dShape& s, DkPlan* out) {
+    if (s.dtype != NTB200_F16 && s.dtype != NTB200_BF16) return false;
+    if (s.sh != 1 || s.sw != 1) return false;
+    if (s.channels % 64 != 0 || s.cout % 64 != 0) return false;
+    if (s.wo < 1 || s.wo > 128) return false;
+    const int rows = dk_rows_per_stage(s.wo);
+    if (rows == 0) return false;
+    const int64_t lim = int64_t(1) << 30;
+    if (s.batch >= lim || s.channels * s.kh * s.kw >= lim || s.height >= lim || s.width >= lim || s.cout >= lim ||
+        s.ho * s.wo >= lim || s.ph >= lim || s.pw >= lim || s.dh * s.kh >= lim || s.dw * s.kw >= lim)
+        return false;
+    out->rows = rows;
+    out->tiles_m = int((s.cout + 255) / 256);
+    out->tiles_n = int((s.channels * s.kh * s.kw + 255) / 256);
+    const int64_t tiles = int64_t(out->tiles_m) * out->tiles_n;
+    if (tiles >= lim) return false;
+    const int pairs = std::max(1, sm_count() / 2);
+    int64_t groups = std::max<int64_t>(1, std::min<int64_t>(s.batch, pairs / tiles));
+    out->images_per_group = int((s.batch + groups - 1) / groups);
+    out->groups = int((s.batch + out->images_per_group - 1) / out->images_per_group);
+    out->xt_bytes = round256(size_t(s.batch) * s.channels * s.height * s.width * 2);
+    out->gt_bytes = round256(size_t(s.batch) * s.cout * s.ho * s.wo * 2);
+    out->partial_bytes = size_t(out->groups) * s.cout * s.channels * s.kh * s.kw * 4;
+    return true;
+}
+
+}  // namespace
+
+size_t conv2d_dkernel_implicit_bytes(const Conv2dShape& s) {
+    DkPlan pl;
+    if (!dk_plan(s, &pl)) return 0;
+    return pl.xt_bytes + pl.gt_bytes + pl.partial_bytes;
+}
+
+int launch_conv2d_dkernel_implicit(const Conv2dShape& s, const void* x, const void* grad, void* d_kernel,
+                                   void* workspace, int accumulate, cudaStream_t stream) {
+    DkPlan pl;
+    if (force_explicit() || !dk_plan(s, &pl)) return NTB200_ERR_UNSUPPORTED;
+    if (reinterpret_cast<uintptr_t>(workspace) % 256) return NTB200_ERR_UNSUPPORTED;
+    EncodeTiledFn enc = reinterpret_cast<EncodeTiledFn>(tensor_map_encoder());
+    if (!enc) return NTB200_ERR_UNSUPPORTED;
+    const size_t es = 2;
+    uint16_t* xt = static_cast<uint16_t*>(workspace);
+    uint16_t* gt = reinterpret_cast<uint16_t*>(static_cast<char*>(workspace) + pl.xt_bytes);
+    float* partial = reinterpret_cast<float*>(static_cast<char*>(workspace) + pl.xt_bytes + pl.gt_bytes);
+    const CUtensorMapDataType dt = s.dtype == NTB200_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+
+    auto encode4 = [&](CUtensorMap* map, void* base, int64_t ch, int64_t wd, int64_t ht) {
+        cuuint64_t dims[4] = {cuuint64_t(ch), cuuint64_t(wd), cuuint64_t(ht), cuuint64_t(s.batch)};
+        cuuint64_t strides[3] = {cuuint64_t(ch) * es, cuuint64_t(ch) * es * cuuint64_t(wd),
+                                 cuuint64_t(ch) * es * cuuint64_t(wd) * cuuint64_t(ht)};
+        cuuint32_t box[4] = {64, cuuint32_t(s.wo), cuuint32_t(pl.rows), 1};
+        cuuint32_t estr[4] = {1, 1, 1, 1};
+        return enc(map, dt, 4, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    };
+    CUtensorMap map_g, map_x;
+    if (!encode4(&map_g, gt, s.cout, s.wo, s.ho) || !encode4(&map_x, xt, s.channels, s.width, s.height))
+        return NTB200_ERR_UNSUPPORTED;
+
+    DkParams p{};
+    p.cout = int(s.cout); p.channels = int(s.channels); p.taps = int(s.kh * s.kw);
+    p.n_total = p.taps * p.channels;
+    p.tiles_m = pl.tiles_m; p.tiles_n = pl.tiles_n;
+    p.groups = pl.groups; p.images_per_group = pl.images_per_group; p.batch = int(s.batch);
+    p.total_items = pl.groups * pl.tiles_m * pl.tiles_n;
+    p.rows = pl.rows;
+    p.row_blocks = int((s.ho + pl.rows - 1) / pl.rows);
+    p.ksteps = int(pl.rows * s.wo / 16);
+    p.chunk_bytes = uint32_t(pl.rows * s.wo) * 128u;
+    p.stage_bytes = 4 * p.chunk_bytes;
+    p.stages = int(std::min<uint32_t>(8, kDkSmemLimit / p.stage_bytes));
+    p.kw = int(s.kw); p.dh = int(s.dh); p.dw = int(s.dw); p.ph = int(s.ph); p.pw = int(s.pw);
+    const uint32_t fmt = s.dtype == NTB200_F16 ? 0u : 1u;
+    p.idesc = make_instr_desc(1, fmt, fmt, true, true, 256, 256);
+    p.partial = partial;
+    p.status = device_status_word();
+    if (!p.status || p.stages < 2) return NTB200_ERR_UNSUPPORTED;
+
+    // channels-last copies of the image and of the gradient (nothing was launched before this point)
+    auto copy_channels_last = [&](const void* src, uint16_t* dst, int64_t ch, int64_t hw64) -> int {
+        const int hw = int(hw64);
+        const int tiles_p = (hw + 63) / 64, tiles_c = int(ch / 64);
+        const long long blocks = (long long)tiles_p * tiles_c * s.batch;
+        if (blocks >= (int64_t(1) << 31)) return fail(NTB200_ERR_INVALID_ARG, "conv2d_backward_kernel: too many tiles");
+        const uintptr_t addr = reinterpret_cast<uintptr_t>(src);
+        auto prepare = (hw % 8 == 0 && addr % 16 == 0) ? conv_prepare_kernel<8>
+                       : (hw % 2 == 0 && addr % 4 == 0) ? conv_prepare_kernel<2>
+                                                        : conv_prepare_kernel<0>;
+        prepare<<<unsigned(blocks), 256, 0, stream>>>(static_cast<const uint16_t*>(src), dst, int(ch), hw, tiles_p, tiles_c,
+                                                      int(blocks), nullptr, nullptr, 1, 0);
+        count_launch();
+        NTB200_CUDA(cudaGetLastError());
+        return NTB200_OK;
+    };
+    if (int rc = copy_channels_last(x, xt, s.channels, s.height * s.width)) return rc;
+    if (int rc = copy_channels_last(grad, gt, s.cout, s.ho * s.wo)) return rc;
+
+    const uint32_t smem = uint32_t(p.stages) * p.stage_bytes + 256 + 1024;
+    cudaError_t e = cudaFuncSetAttribute(conv2d_dkernel_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(conv2d_dkernel_pair_kernel)");
+    const int pairs = std::min(p.total_items, std::max(1, sm_count() / 2));
+    conv2d_dkernel_pair_kernel<<<2 * pairs, kConvThreads, smem, stream>>>(map_g, map_x, p);
+    count_launch();
+    NTB200_CUDA(cudaGetLastError());
+
+    const long long per_group = (long long)s.cout * p.n_total;
+    dkernel_reduce_kernel<<<unsigned((per_group + 255) / 256), 256, 0, stream>>>(
+        partial, static_cast<uint16_t*>(d_kernel), p.groups, per_group, p.n_total, p.channels, p.taps,
+        s.dtype == NTB200_BF16, accumulate != 0);
+    count_launch();
+    NTB200_CUDA(cudaGetLastError());
+    note_route("conv2d-dkernel-implicit-umma-pair");
+    return NTB200_OK;
+}
+
 }  // namespace ntb200

@@ -69,6 +69,12 @@ struct Conv2dShape {
 bool conv2d_implicit_supported(const Conv2dShape& s, size_t workspace_bytes);
 int launch_conv2d_implicit(const Conv2dShape& s, const void* x, const void* w, void* out, void* workspace,
                            cudaStream_t stream);
+// Kernel gradient of the same convolution without a column matrix (16-bit floats, stride 1, channels and output
+// channels multiples of 64).  `bytes` is the workspace it needs (0: shape not supported); `launch` returns
+// NTB200_ERR_UNSUPPORTED before launching anything when it cannot run.
+size_t conv2d_dkernel_implicit_bytes(const Conv2dShape& s);
+int launch_conv2d_dkernel_implicit(const Conv2dShape& s, const void* x, const void* grad, void* d_kernel,
+                                   void* workspace, int accumulate, cudaStream_t stream);
 
 // CUDA-core route: every dtype, every stride pattern.
 int launch_simt_gemm(const GemmArgs& g, cudaStream_t stream);

@@ -182,28 +182,34 @@ inline TensorGrad relu(const TensorGrad& x) {
 }
 
 // conv2d with gradient tracking, groups == 1.  d_image = col2im(matmult(w2d, g, true, false)) (conv.cpp:343-345);
-// d_kernel = sum over the batch of matmult(g, col, false, true) (conv.cpp:467).
+// d_kernel = sum over the batch of matmult(g, col, false, true) (conv.cpp:467).  Both gradients are computed by the
+// library's conv2d backward entry points on one shared workspace.
 inline TensorGrad conv2d(const TensorGrad& image, const TensorGrad& kernel, const ConvArgs& args = {}) {
     Tensor X = image.detach(), W = kernel.detach();
     Tensor out = conv2d(X, W, args);
     return TensorGrad::make_result(out, {image.node(), kernel.node()},
         [X, W, args](const Tensor& g_in, GraphParents& parents) {
-            Tensor im = detail::as_batched_image(X);
+            Tensor im = detail::as_batched_image(X).contiguous();
             Tensor w4 = W.contiguous();
             if (w4.dims() == 3) w4 = w4.view({1, w4.shape()[0], w4.shape()[1], w4.shape()[2]});
-            const int64_t B = im.shape()[0], cout = w4.shape()[0], kh = w4.shape()[2], kw = w4.shape()[3];
-            Tensor w2d = w4.view({cout, -1});
-            Tensor g = g_in.contiguous().view({B, cout, -1});
+            const int64_t B = im.shape()[0], C = im.shape()[1], H = im.shape()[2], Wd = im.shape()[3];
+            const int64_t cout = w4.shape()[0], kh = w4.shape()[2], kw = w4.shape()[3];
+            Tensor g = g_in.contiguous();
+            const int code = dtype_code(X.dtype());
+            const size_t need = ntb200_conv2d_backward_workspace_bytes(code, B, C, H, Wd, cout, kh, kw, args.sh, args.sw, args.ph,
+                                                                       args.pw, args.dh, args.dw);
+            Tensor ws({int64_t(need)}, DType::uint8, DeviceType::CUDA);
             if (parents[0]->requires_grad) {
-                Tensor dcol = matmult(w2d, g, true, false);  // [B, C*kh*kw, L]
-                Tensor dx = unfold2d_backward(dcol, im.shape()[2], im.shape()[3], kh, kw, args);
+                Tensor dx({B, C, H, Wd}, X.dtype(), DeviceType::CUDA);
+                utils::check(ntb200_conv2d_backward_image(code, g.data_ptr(), w4.data_ptr(), dx.data_ptr(), ws.data_ptr(), B, C, H, Wd,
+                                                          cout, kh, kw, args.sh, args.sw, args.ph, args.pw, args.dh, args.dw, nullptr));
                 parents[0]->accumulate_gradient(dx.view(X.shape().Vec()));
             }
             if (parents[1]->requires_grad) {
-                Tensor col = unfold2d(im, kh, kw, args);                 // [B, CK, L]
-                Tensor per_image = matmult(g, col, false, true);          // [B, cout, CK]
-                Tensor dw(SizeRef({cout * w2d.shape()[1]}), W.dtype(), DeviceType::CUDA);
-                dw += per_image.view({B, -1});                            // reduce over the batch
+                Tensor dw(w4.shape(), W.dtype(), DeviceType::CUDA);
+                utils::check(ntb200_conv2d_backward_kernel(code, im.data_ptr(), g.data_ptr(), dw.data_ptr(), ws.data_ptr(), 0, B, C, H,
+                                                           Wd, cout, kh, kw, args.sh, args.sw, args.ph, args.pw, args.dh, args.dw,
+                                                           nullptr));
                 parents[1]->accumulate_gradient(dw.view(W.shape().Vec()));
             }
         });
