@@ -249,6 +249,16 @@ int ntb200_mse(int dtype, const void* out, const void* target, void* grad, float
 int ntb200_column_sum(int dtype, const void* grad, void* out, int64_t rows, int64_t cols, void* stream);
 /* y += x elementwise: GraphNode::accumulate_gradient (nt/nn/AutoGrad.cpp:7-25). */
 int ntb200_add_inplace(int dtype, void* y, const void* x, int64_t n, void* stream);
+/* Parameter updates of the reference's optimizers, one launch per parameter tensor; F32, F16, BF16.
+ * Every intermediate is rounded to the tensor's dtype, as the reference's whole-tensor operations do.
+ *   optimizers::SGD::step (nt/nn/Optimizers.cpp:8-17):  param -= clip(grad, -10, 10) * learning_rate
+ *   optimizers::Adam::step (nt/nn/Optimizers.cpp:68-98), exactly as written there:
+ *     m = (m*beta1 + (1-beta1)) * grad;  v = (v*beta2 + (1-beta2)) * grad^2;
+ *     param -= clip(learning_rate * (m / (1-beta1)^t) / (sqrt(v / (1-beta2)^t) + epsilon), -10, 10)
+ *   `t` is the optimizer's step counter (the reference never advances it from 0).  grad is not modified. */
+int ntb200_sgd_step(int dtype, void* param, const void* grad, int64_t n, double learning_rate, void* stream);
+int ntb200_adam_step(int dtype, void* param, const void* grad, void* m, void* v, int64_t n, double learning_rate,
+                     double beta1, double beta2, double epsilon, int64_t t, void* stream);
 /* dst[rows, cols] (contiguous) = src viewed with the given element strides: Tensor::contiguous(). */
 int ntb200_copy_strided_2d(int dtype, void* dst, const void* src, int64_t batch, int64_t rows, int64_t cols,
                            int64_t src_batch_stride, int64_t src_row_stride, int64_t src_col_stride, void* stream);

@@ -344,6 +344,29 @@ def relu_backward(x, grad_out):
     return gi
 
 
+def sgd_step(param, grad, lr=0.01):
+    """optimizers::SGD::step for one parameter (Optimizers.cpp:8-17): param -= clip(grad, -10, 10) * lr, in place."""
+    _require_cuda(param, grad)
+    if not param.is_contiguous():
+        raise ValueError("sgd_step: the parameter must be contiguous (it is updated in place)")
+    g = grad.contiguous()
+    check(lib().ntb200_sgd_step(dtype_code(param), param.data_ptr(), g.data_ptr(), param.numel(), float(lr), _stream()))
+    return param
+
+
+def adam_step(param, grad, m, v, lr=0.001, beta1=0.9, beta2=0.999, epsilon=1e-8, t=0):
+    """optimizers::Adam::step for one parameter (Optimizers.cpp:68-98), with the reference's own update rule and its
+    step counter `t` (which the reference leaves at 0); param, m and v are updated in place."""
+    _require_cuda(param, grad, m, v)
+    for name, x in (("param", param), ("m", m), ("v", v)):
+        if not x.is_contiguous():
+            raise ValueError("adam_step: %s must be contiguous (it is updated in place)" % name)
+    g = grad.contiguous()
+    check(lib().ntb200_adam_step(dtype_code(param), param.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr(),
+                                 param.numel(), float(lr), float(beta1), float(beta2), float(epsilon), int(t), _stream()))
+    return param
+
+
 def mse(out, target, want_grad=True):
     """loss::MSE -> (loss as a 1-element float32 device tensor, dx or None)."""
     out, target = out.contiguous(), target.contiguous()

@@ -166,6 +166,21 @@ def main():
 
         s, l = timed(gemms, max(3, args.steps // 4))
         emit("c4 the five GEMMs alone", s, flops, 0, "tensor", l)
+        # the parameter update that turns the step into a train step: Adam over W1, b1, W2, b2 (134 M parameters)
+        gw1, gw2 = api.matmult(x, dh, True, False), api.matmult(a, dy, True, False)
+        gb1, gb2 = api.column_sum(dh), api.column_sum(dy)
+        params = [(w1, gw1), (b1, gb1.to(dt)), (w2, gw2), (b2, gb2.to(dt))]
+        state = [(torch.zeros_like(p), torch.zeros_like(p)) for p, _ in params]
+
+        def adam():
+            for (p, g), (m, v) in zip(params, state):
+                api.adam_step(p, g, m, v, lr=1e-3)
+
+        s, l = timed(adam, args.steps)
+        n_par = sum(p.numel() for p, _ in params)
+        emit("c4 optimizers::Adam::step over W1, b1, W2, b2 (%d parameters, BFloat16)" % n_par, s, 0, 7 * 2 * n_par, "hbm", l,
+             "reads param, grad, m, v and writes param, m, v once each")
+        del gw1, gw2, gb1, gb2, params, state
         del x, t, w1, w2, h, a, y, dy, da, dh
 
     if want("c5"):

@@ -1,0 +1,146 @@
+// Parameter updates of nt::optimizers::SGD and nt::optimizers::Adam (nt/nn/Optimizers.cpp:8-17 and :68-98) as one
+// elementwise kernel each.
+//
+// The reference builds every update from whole-tensor operations in the parameter's dtype, so each intermediate is
+// rounded to that dtype.  The kernels follow the same operation sequence and round after every operation (the
+// __f*_rn intrinsics are never contracted into FMAs; 16-bit types are rounded to their format after each step), so
+// a Float32 or Float16 update is bit-identical to the reference's arithmetic.  BFloat16 is not a dtype of the
+// reference; it gets the same sequence with bf16 roundings.
+//
+//   SGD::step    g' = clip(g, -10, 10) * lr ;  p -= g'
+//   Adam::step   m = (m * beta1 + (1 - beta1)) * g          (as written in the reference: the moment estimate is
+//                v = (v * beta2 + (1 - beta2)) * g^2         scaled by the gradient, not blended with it)
+//                m_hat = m / (1 - beta1)^t ;  v_hat = v / (1 - beta2)^t      t is the optimizer's step counter,
+//                u = clip(lr * m_hat / (sqrt(v_hat) + eps), -10, 10) ;  p -= u   which the reference leaves at 0
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <cmath>
+
+#include "internal.h"
+
+namespace ntb200 {
+namespace {
+
+template <typename T> struct Fmt;
+template <> struct Fmt<float> {
+    static __device__ __forceinline__ float round(float x) { return x; }
+    static __device__ __forceinline__ float load(const float* p) { return *p; }
+    static __device__ __forceinline__ void store(float* p, float x) { *p = x; }
+    static float from_double(double x) { return float(x); }
+};
+template <> struct Fmt<__half> {
+    static __device__ __forceinline__ float round(float x) { return __half2float(__float2half_rn(x)); }
+    static __device__ __forceinline__ float load(const __half* p) { return __half2float(*p); }
+    static __device__ __forceinline__ void store(__half* p, float x) { *p = __float2half_rn(x); }
+    static float from_double(double x) { return __half2float(__double2half(x)); }
+};
+template <> struct Fmt<__nv_bfloat16> {
+    static __device__ __forceinline__ float round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+    static __device__ __forceinline__ float load(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, float x) { *p = __float2bfloat16_rn(x); }
+    static float from_double(double x) { return __bfloat162float(__double2bfloat16(x)); }
+};
+
+// std::clamp as the reference's clamp_ applies it (nt/functional/cpu/min_max.cpp:66-101): a NaN stays a NaN
+__device__ __forceinline__ float clip10(float x) { return x < -10.f ? -10.f : (10.f < x ? 10.f : x); }
+
+template <typename T>
+__global__ void sgd_step_kernel(T* __restrict__ param, const T* __restrict__ grad, long long n, float lr) {
+    using F = Fmt<T>;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const float g = F::round(__fmul_rn(clip10(F::load(grad + i)), lr));
+        F::store(param + i, __fsub_rn(F::load(param + i), g));
+    }
+}
+
+struct AdamScalars {   // every scalar already rounded to the tensor's dtype, as Scalar -> T conversion does
+    float lr, beta1, beta2, one_minus_beta1, one_minus_beta2, eps, corr1, corr2;
+};
+
+template <typename T>
+__global__ void adam_step_kernel(T* __restrict__ param, const T* __restrict__ grad, T* __restrict__ m, T* __restrict__ v,
+                                 long long n, AdamScalars k) {
+    using F = Fmt<T>;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const float g = F::load(grad + i);
+        float mi = F::round(__fmul_rn(F::load(m + i), k.beta1));
+        mi = F::round(__fadd_rn(mi, k.one_minus_beta1));
+        mi = F::round(__fmul_rn(mi, g));
+        const float g2 = F::round(__fmul_rn(g, g));
+        float vi = F::round(__fmul_rn(F::load(v + i), k.beta2));
+        vi = F::round(__fadd_rn(vi, k.one_minus_beta2));
+        vi = F::round(__fmul_rn(vi, g2));
+        F::store(m + i, mi);
+        F::store(v + i, vi);
+        const float m_hat = F::round(__fdiv_rn(mi, k.corr1));
+        const float v_hat = F::round(__fdiv_rn(vi, k.corr2));
+        const float num = F::round(__fmul_rn(k.lr, m_hat));
+        const float den = F::round(__fadd_rn(F::round(__fsqrt_rn(v_hat)), k.eps));
+        const float u = clip10(F::round(__fdiv_rn(num, den)));
+        F::store(param + i, __fsub_rn(F::load(param + i), u));
+    }
+}
+
+template <typename T>
+void launch_adam(void* param, const void* grad, void* m, void* v, int64_t n, double learning_rate, double beta1,
+                 double beta2, double epsilon, int64_t t, int grid, cudaStream_t s) {
+    AdamScalars k;
+    k.lr = Fmt<T>::from_double(learning_rate);
+    k.beta1 = Fmt<T>::from_double(beta1);
+    k.beta2 = Fmt<T>::from_double(beta2);
+    k.one_minus_beta1 = Fmt<T>::from_double(1 - beta1);
+    k.one_minus_beta2 = Fmt<T>::from_double(1 - beta2);
+    k.eps = Fmt<T>::from_double(epsilon);
+    k.corr1 = Fmt<T>::from_double(std::pow(1 - beta1, double(t)));
+    k.corr2 = Fmt<T>::from_double(std::pow(1 - beta2, double(t)));
+    adam_step_kernel<T><<<grid, 256, 0, s>>>(static_cast<T*>(param), static_cast<const T*>(grad), static_cast<T*>(m),
+                                             static_cast<T*>(v), n, k);
+}
+
+int grid_for_elements(int64_t n) {
+    const int64_t blocks = (n + 1023) / 1024;
+    return int(blocks < 1 ? 1 : (blocks > 148 * 16 ? 148 * 16 : blocks));
+}
+
+}  // namespace
+}  // namespace ntb200
+
+using namespace ntb200;
+
+#define NTB200_OPT_SWITCH(dtype, CALL)                                                                            \
+    switch (dtype) {                                                                                              \
+        case NTB200_F32: { using T = float; CALL; break; }                                                        \
+        case NTB200_F16: { using T = __half; CALL; break; }                                                       \
+        case NTB200_BF16: { using T = __nv_bfloat16; CALL; break; }                                               \
+        default: return fail(NTB200_ERR_UNSUPPORTED, "%s: dtype %s is not a float type of this engine", __func__, \
+                             dtype_name(dtype));                                                                  \
+    }
+
+extern "C" {
+
+int ntb200_sgd_step(int dtype, void* param, const void* grad, int64_t n, double learning_rate, void* stream) {
+    if (n < 0) return fail(NTB200_ERR_INVALID_ARG, "sgd_step: negative size");
+    if (n == 0) return NTB200_OK;
+    if (!param || !grad) return fail(NTB200_ERR_INVALID_ARG, "sgd_step: null pointer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    NTB200_OPT_SWITCH(dtype, (sgd_step_kernel<T><<<grid_for_elements(n), 256, 0, s>>>(
+                                 static_cast<T*>(param), static_cast<const T*>(grad), n, Fmt<T>::from_double(learning_rate))));
+    count_launch();
+    NTB200_CUDA(cudaGetLastError());
+    return NTB200_OK;
+}
+
+int ntb200_adam_step(int dtype, void* param, const void* grad, void* m, void* v, int64_t n, double learning_rate,
+                     double beta1, double beta2, double epsilon, int64_t t, void* stream) {
+    if (n < 0) return fail(NTB200_ERR_INVALID_ARG, "adam_step: negative size");
+    if (n == 0) return NTB200_OK;
+    if (!param || !grad || !m || !v) return fail(NTB200_ERR_INVALID_ARG, "adam_step: null pointer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    NTB200_OPT_SWITCH(dtype, (launch_adam<T>(param, grad, m, v, n, learning_rate, beta1, beta2, epsilon, t, grid_for_elements(n), s)));
+    count_launch();
+    NTB200_CUDA(cudaGetLastError());
+    return NTB200_OK;
+}
+
+}  // extern "C"

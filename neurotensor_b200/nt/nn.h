@@ -247,6 +247,62 @@ class Linear {
 };
 }  // namespace layers
 
+namespace optimizers {
+// optimizers::SGD and optimizers::Adam (nn/Optimizers.h:12-62, Optimizers.cpp:8-98) over an explicit parameter list
+// (the reference collects the list by reflection over a Module).  step() updates every parameter that tracks a
+// gradient and has one, with one kernel per parameter, then drops the gradients as erase_grad_tracking does.
+class SGD {
+    std::vector<TensorGrad> parameters_;
+    double learning_rate_;
+
+   public:
+    explicit SGD(std::vector<TensorGrad> params, double lr = 0.01) : parameters_(std::move(params)), learning_rate_(lr) {}
+    void step() {
+        for (auto& p : parameters_) {
+            if (p.is_null() || !p.track_grad() || !p.has_grad()) continue;
+            Tensor g = p.grad().contiguous();
+            utils::check(ntb200_sgd_step(dtype_code(p.dtype()), p.detach().data_ptr(), g.data_ptr(), p.detach().numel(),
+                                         learning_rate_, nullptr));
+        }
+        zero_grad();
+    }
+    void zero_grad() {
+        for (auto& p : parameters_)
+            if (!p.is_null()) p.zero_grad();
+    }
+};
+
+class Adam {
+    std::vector<TensorGrad> parameters_;
+    double learning_rate_, beta1_, beta2_, epsilon_;
+    std::vector<Tensor> m_, v_;
+    int64_t t_ = 0;   // never advanced, as in the reference
+
+   public:
+    explicit Adam(std::vector<TensorGrad> params, double lr = 0.001, double beta1 = 0.9, double beta2 = 0.999,
+                  double epsilon = 1e-8)
+        : parameters_(std::move(params)), learning_rate_(lr), beta1_(beta1), beta2_(beta2), epsilon_(epsilon),
+          m_(parameters_.size()), v_(parameters_.size()) {}
+    void step() {
+        for (size_t i = 0; i < parameters_.size(); ++i) {
+            TensorGrad& p = parameters_[i];
+            if (p.is_null() || !p.track_grad() || !p.has_grad()) continue;
+            if (m_[i].is_null()) m_[i] = functional::zeros(p.shape(), p.dtype());
+            if (v_[i].is_null()) v_[i] = functional::zeros(p.shape(), p.dtype());
+            Tensor g = p.grad().contiguous();
+            utils::check(ntb200_adam_step(dtype_code(p.dtype()), p.detach().data_ptr(), g.data_ptr(), m_[i].data_ptr(),
+                                          v_[i].data_ptr(), p.detach().numel(), learning_rate_, beta1_, beta2_, epsilon_, t_,
+                                          nullptr));
+        }
+        zero_grad();
+    }
+    void zero_grad() {
+        for (auto& p : parameters_)
+            if (!p.is_null()) p.zero_grad();
+    }
+};
+}  // namespace optimizers
+
 // A scalar loss that remembers the gradient to send back (ScalarGrad.h:18-40).
 class ScalarGrad {
     double item_;

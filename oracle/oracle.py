@@ -249,3 +249,46 @@ def rel_fro(x, ref):
     ref = np.asarray(ref, dtype=np.float64)
     den = np.linalg.norm(ref.ravel())
     return float(np.linalg.norm((x - ref).ravel()) / (den if den > 0 else 1.0))
+
+
+def _typed_ops(dtype, bf16):
+    """(round-to-dtype, scalar-in-dtype) for the optimizers.  bf16 values travel as float32 arrays holding bf16
+    numbers; every operation is done in float32 and rounded to bf16, which is how the device computes them."""
+    if bf16:
+        rnd = lambda x: bf16_widen(bf16_round(np.asarray(x, dtype=np.float32)))
+        return rnd, (lambda s: rnd(np.float32(s))[()])
+    return (lambda x: np.asarray(x).astype(dtype)), dtype.type
+
+
+def _clamp10(x, c):
+    """std::clamp as clamp_ applies it (nt/functional/cpu/min_max.cpp:66-101): a NaN stays a NaN."""
+    return np.where(x < c(-10), c(-10), np.where(c(10) < x, c(10), x))
+
+
+def sgd_step(param, grad, lr=0.01, bf16=False):
+    """optimizers::SGD::step (nt/nn/Optimizers.cpp:8-17) on one parameter: every whole-tensor operation of the
+    reference rounds to the tensor's dtype, which numpy's typed arithmetic reproduces.  Returns the new parameter."""
+    rnd, c = _typed_ops(param.dtype, bf16)
+    g = rnd(_clamp10(grad, c) * c(lr))
+    return rnd(param - g)
+
+
+def adam_step(param, grad, m, v, lr=0.001, beta1=0.9, beta2=0.999, epsilon=1e-8, t=0, bf16=False):
+    """optimizers::Adam::step (nt/nn/Optimizers.cpp:68-98), operation by operation as written there (the moment
+    estimates are scaled by the gradient; the step counter t stays where the caller has it, 0 in the reference).
+    Returns (param, m, v)."""
+    rnd, c = _typed_ops(param.dtype, bf16)
+    with np.errstate(divide="ignore", invalid="ignore", over="ignore"):
+        m1 = rnd(m * c(beta1))
+        m1 = rnd(m1 + c(1 - beta1))
+        m1 = rnd(m1 * grad)
+        g2 = rnd(grad * grad)
+        v1 = rnd(v * c(beta2))
+        v1 = rnd(v1 + c(1 - beta2))
+        v1 = rnd(v1 * g2)
+        m_hat = rnd(m1 / c((1 - beta1) ** t))
+        v_hat = rnd(v1 / c((1 - beta2) ** t))
+        num = rnd(c(lr) * m_hat)
+        den = rnd(rnd(np.sqrt(v_hat)) + c(epsilon))
+        u = _clamp10(rnd(num / den), c)
+        return rnd(param - u), m1, v1

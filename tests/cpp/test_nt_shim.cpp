@@ -240,6 +240,50 @@ int main(int argc, char** argv) {
         REQUIRE(!x.has_grad());  // the input does not track a gradient
     });
 
+    run_test("optimizers::SGD and optimizers::Adam make a train step: the loss goes down and the updates are the reference's", [] {
+        const int64_t B = 32, D = 16, H = 24;
+        nt::layers::Linear l1(D, H, true, DType::Float32, 11), l2(H, D, true, DType::Float32, 12);
+        Tensor xt = nt::randn_seeded({B, D}, DType::Float32, 13), target = nt::randn_seeded({B, D}, DType::Float32, 14);
+        TensorGrad x(xt, false);
+        nt::optimizers::SGD sgd({l1.Weight, l1.Bias, l2.Weight, l2.Bias}, 0.05);
+        double first = 0, last = 0;
+        for (int it = 0; it < 20; ++it) {
+            nt::ScalarGrad loss = nt::loss::MSE(l2(fn::relu(l1(x))), target);
+            if (it == 0) first = loss.item();
+            last = loss.item();
+            loss.backward();
+            if (it == 0) {   // one SGD update by hand, in float like the reference: w -= clip(g, -10, 10) * lr
+                auto w = l2.Weight.detach().to_vector<float>(), g = l2.Weight.grad().to_vector<float>();
+                sgd.step();
+                auto w_new = l2.Weight.detach().to_vector<float>();
+                bool same = true;
+                for (size_t i = 0; i < w.size(); ++i) {
+                    const float gi = std::fmin(std::fmax(g[i], -10.f), 10.f) * 0.05f;
+                    same = same && (w_new[i] == w[i] - gi);
+                }
+                REQUIRE(same);
+                REQUIRE(!l2.Weight.has_grad());   // step() drops the gradients
+            } else {
+                sgd.step();
+            }
+        }
+        REQUIRE(last < first);
+        // Adam, first step from zero moments: m = (1-b1) g, v = (1-b2) g^2, update = lr m / (sqrt(v) + eps)
+        nt::optimizers::Adam adam({l1.Weight, l1.Bias, l2.Weight, l2.Bias}, 0.001);
+        nt::ScalarGrad loss = nt::loss::MSE(l2(fn::relu(l1(x))), target);
+        loss.backward();
+        auto w = l1.Weight.detach().to_vector<float>(), g = l1.Weight.grad().to_vector<float>();
+        adam.step();
+        auto w_new = l1.Weight.detach().to_vector<float>();
+        double worst = 0;
+        for (size_t i = 0; i < w.size(); ++i) {
+            const double m = (1 - 0.9) * g[i], v = (1 - 0.999) * double(g[i]) * g[i];
+            const double u = 0.001 * m / (std::sqrt(v) + 1e-8);
+            worst = std::fmax(worst, std::fabs((double(w[i]) - u) - w_new[i]));
+        }
+        REQUIRE(worst <= 1e-6);
+    });
+
     nt::utils::check(ntb200_check_device_status(nullptr));
     std::printf("%d of %d cases failed\n", g_failed, g_run);
     return g_failed ? 1 : 0;
