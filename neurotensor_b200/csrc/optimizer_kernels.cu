@@ -45,41 +45,99 @@ template <> struct Fmt<__nv_bfloat16> {
 // std::clamp as the reference's clamp_ applies it (nt/functional/cpu/min_max.cpp:66-101): a NaN stays a NaN
 __device__ __forceinline__ float clip10(float x) { return x < -10.f ? -10.f : (10.f < x ? 10.f : x); }
 
+// Elements per 16-byte vector, and a register view of one vector.
+template <typename T> struct Vec {
+    static constexpr int kN = 16 / int(sizeof(T));
+    union { uint4 raw; T e[16 / sizeof(T)]; };
+};
+
 template <typename T>
-__global__ void sgd_step_kernel(T* __restrict__ param, const T* __restrict__ grad, long long n, float lr) {
+__device__ __forceinline__ float sgd_one(float p, float g, float lr) {
     using F = Fmt<T>;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
-        const float g = F::round(__fmul_rn(clip10(F::load(grad + i)), lr));
-        F::store(param + i, __fsub_rn(F::load(param + i), g));
+    return F::round(__fsub_rn(p, F::round(__fmul_rn(clip10(g), lr))));
+}
+
+// One 16-byte vector per thread and pass; the last n % kN elements are done one by one by the first threads.
+template <typename T>
+__global__ void sgd_step_kernel(T* __restrict__ param, const T* __restrict__ grad, long long n, float lr, int vec) {
+    using F = Fmt<T>;
+    constexpr int kN = Vec<T>::kN;
+    const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, nthreads = (long long)gridDim.x * blockDim.x;
+    const long long nvec = vec ? n / kN : 0;
+    for (long long i = tid; i < nvec; i += nthreads) {
+        Vec<T> p, g;
+        p.raw = reinterpret_cast<const uint4*>(param)[i];
+        g.raw = reinterpret_cast<const uint4*>(grad)[i];
+#pragma unroll
+        for (int j = 0; j < kN; ++j) F::store(&p.e[j], sgd_one<T>(F::load(&p.e[j]), F::load(&g.e[j]), lr));
+        reinterpret_cast<uint4*>(param)[i] = p.raw;
     }
+    for (long long i = nvec * kN + tid; i < n; i += nthreads)
+        F::store(param + i, sgd_one<T>(F::load(param + i), F::load(grad + i), lr));
 }
 
 struct AdamScalars {   // every scalar already rounded to the tensor's dtype, as Scalar -> T conversion does
     float lr, beta1, beta2, one_minus_beta1, one_minus_beta2, eps, corr1, corr2;
 };
 
+// Division by exactly 1 (the reference's bias correction while its step counter is 0) leaves every value as it is.
+template <typename T>
+__device__ __forceinline__ void adam_one(float& p, float g, float& m, float& v, const AdamScalars& k) {
+    using F = Fmt<T>;
+    float mi = F::round(__fmul_rn(m, k.beta1));
+    mi = F::round(__fadd_rn(mi, k.one_minus_beta1));
+    mi = F::round(__fmul_rn(mi, g));
+    const float g2 = F::round(__fmul_rn(g, g));
+    float vi = F::round(__fmul_rn(v, k.beta2));
+    vi = F::round(__fadd_rn(vi, k.one_minus_beta2));
+    vi = F::round(__fmul_rn(vi, g2));
+    m = mi;
+    v = vi;
+    const float m_hat = k.corr1 == 1.f ? mi : F::round(__fdiv_rn(mi, k.corr1));
+    const float v_hat = k.corr2 == 1.f ? vi : F::round(__fdiv_rn(vi, k.corr2));
+    const float num = F::round(__fmul_rn(k.lr, m_hat));
+    const float den = F::round(__fadd_rn(F::round(__fsqrt_rn(v_hat)), k.eps));
+    const float u = clip10(F::round(__fdiv_rn(num, den)));
+    p = F::round(__fsub_rn(p, u));
+}
+
 template <typename T>
 __global__ void adam_step_kernel(T* __restrict__ param, const T* __restrict__ grad, T* __restrict__ m, T* __restrict__ v,
-                                 long long n, AdamScalars k) {
+                                 long long n, AdamScalars k, int vec) {
     using F = Fmt<T>;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
-        const float g = F::load(grad + i);
-        float mi = F::round(__fmul_rn(F::load(m + i), k.beta1));
-        mi = F::round(__fadd_rn(mi, k.one_minus_beta1));
-        mi = F::round(__fmul_rn(mi, g));
-        const float g2 = F::round(__fmul_rn(g, g));
-        float vi = F::round(__fmul_rn(F::load(v + i), k.beta2));
-        vi = F::round(__fadd_rn(vi, k.one_minus_beta2));
-        vi = F::round(__fmul_rn(vi, g2));
-        F::store(m + i, mi);
-        F::store(v + i, vi);
-        const float m_hat = F::round(__fdiv_rn(mi, k.corr1));
-        const float v_hat = F::round(__fdiv_rn(vi, k.corr2));
-        const float num = F::round(__fmul_rn(k.lr, m_hat));
-        const float den = F::round(__fadd_rn(F::round(__fsqrt_rn(v_hat)), k.eps));
-        const float u = clip10(F::round(__fdiv_rn(num, den)));
-        F::store(param + i, __fsub_rn(F::load(param + i), u));
+    constexpr int kN = Vec<T>::kN;
+    const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, nthreads = (long long)gridDim.x * blockDim.x;
+    const long long nvec = vec ? n / kN : 0;
+    for (long long i = tid; i < nvec; i += nthreads) {
+        Vec<T> p, g, mm, vv;
+        p.raw = reinterpret_cast<const uint4*>(param)[i];
+        g.raw = reinterpret_cast<const uint4*>(grad)[i];
+        mm.raw = reinterpret_cast<const uint4*>(m)[i];
+        vv.raw = reinterpret_cast<const uint4*>(v)[i];
+#pragma unroll
+        for (int j = 0; j < kN; ++j) {
+            float pj = F::load(&p.e[j]), mj = F::load(&mm.e[j]), vj = F::load(&vv.e[j]);
+            adam_one<T>(pj, F::load(&g.e[j]), mj, vj, k);
+            F::store(&p.e[j], pj);
+            F::store(&mm.e[j], mj);
+            F::store(&vv.e[j], vj);
+        }
+        reinterpret_cast<uint4*>(param)[i] = p.raw;
+        reinterpret_cast<uint4*>(m)[i] = mm.raw;
+        reinterpret_cast<uint4*>(v)[i] = vv.raw;
     }
+    for (long long i = nvec * kN + tid; i < n; i += nthreads) {
+        float pj = F::load(param + i), mj = F::load(m + i), vj = F::load(v + i);
+        adam_one<T>(pj, F::load(grad + i), mj, vj, k);
+        F::store(param + i, pj);
+        F::store(m + i, mj);
+        F::store(v + i, vj);
+    }
+}
+
+inline int all_aligned16(const void* a, const void* b, const void* c = nullptr, const void* d = nullptr) {
+    return ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c) |
+             reinterpret_cast<uintptr_t>(d)) % 16) == 0;
 }
 
 template <typename T>
@@ -95,12 +153,13 @@ void launch_adam(void* param, const void* grad, void* m, void* v, int64_t n, dou
     k.corr1 = Fmt<T>::from_double(std::pow(1 - beta1, double(t)));
     k.corr2 = Fmt<T>::from_double(std::pow(1 - beta2, double(t)));
     adam_step_kernel<T><<<grid, 256, 0, s>>>(static_cast<T*>(param), static_cast<const T*>(grad), static_cast<T*>(m),
-                                             static_cast<T*>(v), n, k);
+                                             static_cast<T*>(v), n, k, all_aligned16(param, grad, m, v));
 }
 
 int grid_for_elements(int64_t n) {
-    const int64_t blocks = (n + 1023) / 1024;
-    return int(blocks < 1 ? 1 : (blocks > 148 * 16 ? 148 * 16 : blocks));
+    const int64_t blocks = (n + 2047) / 2048;   // about one 16-byte vector per thread, capped at 16 blocks per SM
+    const int64_t cap = int64_t(sm_count()) * 16;
+    return int(blocks < 1 ? 1 : (blocks > cap ? cap : blocks));
 }
 
 }  // namespace
@@ -125,7 +184,8 @@ int ntb200_sgd_step(int dtype, void* param, const void* grad, int64_t n, double 
     if (!param || !grad) return fail(NTB200_ERR_INVALID_ARG, "sgd_step: null pointer");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     NTB200_OPT_SWITCH(dtype, (sgd_step_kernel<T><<<grid_for_elements(n), 256, 0, s>>>(
-                                 static_cast<T*>(param), static_cast<const T*>(grad), n, Fmt<T>::from_double(learning_rate))));
+                                 static_cast<T*>(param), static_cast<const T*>(grad), n, Fmt<T>::from_double(learning_rate),
+                                 all_aligned16(param, grad))));
     count_launch();
     NTB200_CUDA(cudaGetLastError());
     return NTB200_OK;
