@@ -218,6 +218,31 @@ int ntb200_conv2d_backward_kernel(int dtype, const void* x, const void* grad, vo
                                   int64_t cout, int64_t kh, int64_t kw, int64_t sh, int64_t sw, int64_t ph,
                                   int64_t pw, int64_t dh, int64_t dw, void* stream);
 
+/* conv2d with groups, forward and backward (conv.cpp:97-118, 328-337, 453-461): w is [Cout, C/groups, kh, kw];
+ * group g maps input channels [g*C/groups, (g+1)*C/groups) to filters [g*Cout/groups, (g+1)*Cout/groups).
+ * Same arguments as the ungrouped calls plus `groups`; groups == 1 forwards to them.  One workspace size
+ * (ntb200_conv2d_grouped_workspace_bytes) serves the three calls.  conv1d is the H == 1, kh == 1 case;
+ * conv_transpose2d(x, w) is ntb200_conv2d_grouped_backward_image with x in the place of grad, and its own
+ * gradients are ntb200_conv2d_grouped (for x) and ntb200_conv2d_grouped_backward_kernel with the roles of
+ * image and gradient exchanged (for w). */
+size_t ntb200_conv2d_grouped_workspace_bytes(int dtype, int64_t batch, int64_t channels, int64_t height,
+                                             int64_t width, int64_t cout, int64_t kh, int64_t kw, int64_t sh,
+                                             int64_t sw, int64_t ph, int64_t pw, int64_t dh, int64_t dw,
+                                             int64_t groups);
+int ntb200_conv2d_grouped(int dtype, const void* x, const void* w, void* out, void* workspace, int64_t batch,
+                          int64_t channels, int64_t height, int64_t width, int64_t cout, int64_t kh, int64_t kw,
+                          int64_t sh, int64_t sw, int64_t ph, int64_t pw, int64_t dh, int64_t dw, int64_t groups,
+                          void* stream);
+int ntb200_conv2d_grouped_backward_image(int dtype, const void* grad, const void* w, void* d_image, void* workspace,
+                                         int64_t batch, int64_t channels, int64_t height, int64_t width,
+                                         int64_t cout, int64_t kh, int64_t kw, int64_t sh, int64_t sw, int64_t ph,
+                                         int64_t pw, int64_t dh, int64_t dw, int64_t groups, void* stream);
+int ntb200_conv2d_grouped_backward_kernel(int dtype, const void* x, const void* grad, void* d_kernel,
+                                          void* workspace, int accumulate, int64_t batch, int64_t channels,
+                                          int64_t height, int64_t width, int64_t cout, int64_t kh, int64_t kw,
+                                          int64_t sh, int64_t sw, int64_t ph, int64_t pw, int64_t dh, int64_t dw,
+                                          int64_t groups, void* stream);
+
 /* ntb200_conv2d for callers that cannot allocate device memory.  No counterpart in the reference, which
  * allocates its column matrix on the CPU heap as it goes.  Some users of this library cannot do the
  * device-side equivalent: their application has given the whole device heap to its own allocator, so a

@@ -76,6 +76,10 @@ SIGNATURES = {
     "ntb200_conv2d_backward_workspace_bytes": (_sz, [_ci] + [_i64] * 13),
     "ntb200_conv2d_backward_image": (_ci, [_ci, _vp, _vp, _vp, _vp] + [_i64] * 13 + [_vp]),
     "ntb200_conv2d_backward_kernel": (_ci, [_ci, _vp, _vp, _vp, _vp, _ci] + [_i64] * 13 + [_vp]),
+    "ntb200_conv2d_grouped_workspace_bytes": (_sz, [_ci] + [_i64] * 14),
+    "ntb200_conv2d_grouped": (_ci, [_ci, _vp, _vp, _vp, _vp] + [_i64] * 14 + [_vp]),
+    "ntb200_conv2d_grouped_backward_image": (_ci, [_ci, _vp, _vp, _vp, _vp] + [_i64] * 14 + [_vp]),
+    "ntb200_conv2d_grouped_backward_kernel": (_ci, [_ci, _vp, _vp, _vp, _vp, _ci] + [_i64] * 14 + [_vp]),
     "ntb200_conv2d_static_scratch": (_ci, [_ci, _vp, _vp, _vp] + [_i64] * 13 + [_vp]),
     "ntb200_relu": (_ci, [_ci, _vp, _vp, _i64, _vp]),
     "ntb200_relu_backward": (_ci, [_ci, _vp, _vp, _vp, _i64, _vp]),

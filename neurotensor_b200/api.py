@@ -273,41 +273,62 @@ def unfold2d_backward(dcol, out_hw, kernel_size, dilation=1, padding=0, stride=1
     return im
 
 
-def conv2d(x, w, stride=1, padding=0, dilation=1, groups=1, workspace=None):
-    """functional::conv2d for groups == 1 -> [B, Cout, Ho, Wo]."""
-    _require_cuda(x, w)
-    if groups != 1:
-        raise ValueError("conv2d: groups > 1 is outside this engine's scope")
+def _conv_weights(x, w, groups, what="conv2d"):
     if w.dim() not in (3, 4):
         raise ValueError("Expected to get a 4D or 3D tensor as the kernel for a 2d convolution, but got %dD" % w.dim())
     if x.dtype != w.dtype:
-        raise ValueError("Expected both kernel and image to have the same dtype for conv2d but got %s and %s"
-                         % (w.dtype, x.dtype))
-    w4 = (w.unsqueeze(0) if w.dim() == 3 else w).contiguous()
-    x4, (kh, kw, sh, sw, ph, pw, dh, dw), ho, wo = _conv_geom(x, w4.shape[-2:], dilation, padding, stride)
+        raise ValueError("Expected both kernel and image to have the same dtype for %s but got %s and %s"
+                         % (what, w.dtype, x.dtype))
+    if groups < 1:
+        raise ValueError("Expected groups for a convolution to be greater than 0 but got %d" % groups)
+    return (w.unsqueeze(0) if w.dim() == 3 else w).contiguous()
+
+
+def _grouped_workspace(code, bsz, ch, h, wd, cout, geom, groups, workspace, device):
+    kh, kw, sh, sw, ph, pw, dh, dw = geom
+    need = lib().ntb200_conv2d_grouped_workspace_bytes(code, bsz, ch, h, wd, cout, kh, kw, sh, sw, ph, pw, dh, dw, groups)
+    if workspace is None or workspace.numel() * workspace.element_size() < need:
+        workspace = torch.empty(max(need, 1), dtype=torch.uint8, device=device)
+    return workspace
+
+
+def conv2d(x, w, stride=1, padding=0, dilation=1, groups=1, workspace=None):
+    """functional::conv2d (conv.cpp:69-119) -> [B, Cout, Ho, Wo]; w is [Cout, C/groups, kh, kw]."""
+    _require_cuda(x, w)
+    w4 = _conv_weights(x, w, groups)
+    x4, geom, ho, wo = _conv_geom(x, w4.shape[-2:], dilation, padding, stride)
+    kh, kw, sh, sw, ph, pw, dh, dw = geom
     bsz, ch, h, wd = x4.shape
-    if w4.shape[1] != ch:
-        raise ValueError("Expected kernel channels %d to equal image channels %d" % (w4.shape[1], ch))
+    if ch % groups:
+        raise ValueError("Expected image channels to be divisible by groups in Conv2d but got %d %% %d != 0" % (ch, groups))
+    if w4.shape[1] * groups != ch:
+        raise ValueError("Expected kernel channels %d times groups %d to equal image channels %d" % (w4.shape[1], groups, ch))
     cout = w4.shape[0]
     code = dtype_code(x)
-    need = lib().ntb200_conv2d_workspace_bytes(code, bsz, ch, h, wd, kh, kw, sh, sw, ph, pw, dh, dw)
-    if workspace is None or workspace.numel() * workspace.element_size() < need:
-        workspace = torch.empty(need, dtype=torch.uint8, device=x.device)
     out = torch.empty((bsz, cout, ho, wo), dtype=x.dtype, device=x.device)
-    check(lib().ntb200_conv2d(code, x4.data_ptr(), w4.data_ptr(), out.data_ptr(), workspace.data_ptr(), bsz, ch, h,
-                              wd, cout, kh, kw, sh, sw, ph, pw, dh, dw, _stream()))
+    if groups == 1:
+        need = lib().ntb200_conv2d_workspace_bytes(code, bsz, ch, h, wd, kh, kw, sh, sw, ph, pw, dh, dw)
+        if workspace is None or workspace.numel() * workspace.element_size() < need:
+            workspace = torch.empty(need, dtype=torch.uint8, device=x.device)
+        check(lib().ntb200_conv2d(code, x4.data_ptr(), w4.data_ptr(), out.data_ptr(), workspace.data_ptr(), bsz, ch, h,
+                                  wd, cout, kh, kw, sh, sw, ph, pw, dh, dw, _stream()))
+        return out
+    workspace = _grouped_workspace(code, bsz, ch, h, wd, cout, geom, groups, workspace, x.device)
+    check(lib().ntb200_conv2d_grouped(code, x4.data_ptr(), w4.data_ptr(), out.data_ptr(), workspace.data_ptr(), bsz, ch, h,
+                                      wd, cout, kh, kw, sh, sw, ph, pw, dh, dw, groups, _stream()))
     return out
 
 
-def conv2d_backward(x, w, grad, stride=1, padding=0, dilation=1, workspace=None):
-    """conv_dimage (conv.cpp:318-346) and conv_dkernel (conv.cpp:444-471) for groups == 1 -> (d_image, d_kernel):
-    d_image = col2im(matmult(w2d, grad, true, false)); d_kernel = sum over the batch of matmult(grad, col, false, true).
-    Both run inside the library (ntb200_conv2d_backward_image / _kernel) on one shared workspace."""
+def conv2d_backward(x, w, grad, stride=1, padding=0, dilation=1, groups=1, workspace=None):
+    """conv_dimage (conv.cpp:318-346) and conv_dkernel (conv.cpp:444-471) -> (d_image, d_kernel):
+    d_image = col2im(matmult(w2d, grad, true, false)); d_kernel = sum over the batch of matmult(grad, col, false, true),
+    group by group when groups > 1.  Both run inside the library on one shared workspace."""
     _require_cuda(x, w, grad)
     if not (x.dtype == w.dtype == grad.dtype):
         raise ValueError("conv2d_backward: image, kernel and gradient must share a dtype")
-    w4 = (w.unsqueeze(0) if w.dim() == 3 else w).contiguous()
-    x4, (kh, kw, sh, sw, ph, pw, dh, dw), ho, wo = _conv_geom(x, w4.shape[-2:], dilation, padding, stride)
+    w4 = _conv_weights(x, w, groups)
+    x4, geom, ho, wo = _conv_geom(x, w4.shape[-2:], dilation, padding, stride)
+    kh, kw, sh, sw, ph, pw, dh, dw = geom
     x4 = x4.contiguous()
     bsz, ch, h, wd = x4.shape
     cout = w4.shape[0]
@@ -316,15 +337,112 @@ def conv2d_backward(x, w, grad, stride=1, padding=0, dilation=1, workspace=None)
         raise ValueError("conv2d_backward: gradient has %d elements, expected [%d, %d, %d, %d]"
                          % (g.numel(), bsz, cout, ho, wo))
     code = dtype_code(x)
-    need = lib().ntb200_conv2d_backward_workspace_bytes(code, bsz, ch, h, wd, cout, kh, kw, sh, sw, ph, pw, dh, dw)
-    if workspace is None or workspace.numel() * workspace.element_size() < need:
-        workspace = torch.empty(need, dtype=torch.uint8, device=x.device)
+    workspace = _grouped_workspace(code, bsz, ch, h, wd, cout, geom, groups, workspace, x.device)
     dx = torch.empty_like(x4)
     dw_ = torch.empty_like(w4)
-    check(lib().ntb200_conv2d_backward_image(code, g.data_ptr(), w4.data_ptr(), dx.data_ptr(), workspace.data_ptr(), bsz,
-                                             ch, h, wd, cout, kh, kw, sh, sw, ph, pw, dh, dw, _stream()))
-    check(lib().ntb200_conv2d_backward_kernel(code, x4.data_ptr(), g.data_ptr(), dw_.data_ptr(), workspace.data_ptr(), 0,
-                                              bsz, ch, h, wd, cout, kh, kw, sh, sw, ph, pw, dh, dw, _stream()))
+    check(lib().ntb200_conv2d_grouped_backward_image(code, g.data_ptr(), w4.data_ptr(), dx.data_ptr(), workspace.data_ptr(),
+                                                     bsz, ch, h, wd, cout, kh, kw, sh, sw, ph, pw, dh, dw, groups, _stream()))
+    check(lib().ntb200_conv2d_grouped_backward_kernel(code, x4.data_ptr(), g.data_ptr(), dw_.data_ptr(), workspace.data_ptr(),
+                                                      0, bsz, ch, h, wd, cout, kh, kw, sh, sw, ph, pw, dh, dw, groups, _stream()))
+    return dx.reshape(x.shape), dw_.reshape(w.shape)
+
+
+def conv1d(x, w, stride=1, padding=0, dilation=1, groups=1):
+    """functional::conv1d (conv.cpp:13-67): [B, C, W] * [Cout, C/groups, k] as the one-row case of conv2d."""
+    if x.dim() < 2 or w.dim() not in (2, 3):
+        raise ValueError("Expected a 2D or greater input and a 2D or 3D kernel for a 1d convolution")
+    w3 = w.unsqueeze(0) if w.dim() == 2 else w
+    x3 = x.reshape((-1,) + tuple(x.shape[-2:]))
+    out = conv2d(x3.unsqueeze(-2), w3.unsqueeze(-2), (1, stride), (0, padding), (1, dilation), groups)
+    return out.squeeze(-2)
+
+
+def conv1d_backward(x, w, grad, stride=1, padding=0, dilation=1, groups=1):
+    w3 = w.unsqueeze(0) if w.dim() == 2 else w
+    x3 = x.reshape((-1,) + tuple(x.shape[-2:]))
+    g3 = grad.reshape((x3.shape[0], w3.shape[0], -1))
+    dx, dw_ = conv2d_backward(x3.unsqueeze(-2), w3.unsqueeze(-2), g3.unsqueeze(-2), (1, stride), (0, padding), (1, dilation),
+                              groups)
+    return dx.reshape(x.shape), dw_.reshape(w.shape)
+
+
+def _transpose_geom(x, w4, stride, padding, output_padding, dilation, groups):
+    sh, sw = _pair(stride)
+    ph, pw = _pair(padding)
+    oh, ow = _pair(output_padding)
+    dh, dw = _pair(dilation)
+    if sh < 1 or sw < 1:
+        raise ValueError("Conv2d Transpose stride cannot be less than 1 but got %s" % (stride,))
+    if dh < 1 or dw < 1:
+        raise ValueError("Conv2d Transpose dilation cannot be less than 1 but got %s" % (dilation,))
+    if ph < 0 or pw < 0 or oh < 0 or ow < 0:
+        raise ValueError("Conv2d Transpose padding and output_padding cannot be less than 0")
+    if oh >= sh or ow >= sw:
+        raise ValueError("conv_transpose2d: output_padding must be smaller than the stride")
+    x4 = x.reshape((-1,) + tuple(x.shape[-3:])).contiguous()
+    if x4.shape[1] != w4.shape[0]:
+        raise ValueError("Expected image channels to be the same as the kernel batches for conv_transpose2d but got %s and %s"
+                         % (tuple(x4.shape), tuple(w4.shape)))
+    kh, kw = w4.shape[-2:]
+    ho = (x4.shape[-2] - 1) * sh - 2 * ph + dh * (kh - 1) + 1 + oh
+    wo = (x4.shape[-1] - 1) * sw - 2 * pw + dw * (kw - 1) + 1 + ow
+    return x4, (kh, kw, sh, sw, ph, pw, dh, dw), ho, wo
+
+
+def conv_transpose2d(x, w, stride=1, padding=0, output_padding=0, dilation=1, groups=1):
+    """functional::conv_transpose2d (conv.cpp:614-672): x [B, Cin, Hi, Wi], w [Cin, Cout/groups, kh, kw] ->
+    [B, Cout, Ho, Wo].  It is the image gradient of the convolution that maps [B, Cout, Ho, Wo] to x's shape with
+    the same kernel, so it runs as ntb200_conv2d_grouped_backward_image with x in the place of the gradient."""
+    _require_cuda(x, w)
+    w4 = _conv_weights(x, w, groups, "conv2d transpose")
+    x4, geom, ho, wo = _transpose_geom(x, w4, stride, padding, output_padding, dilation, groups)
+    kh, kw, sh, sw, ph, pw, dh, dw = geom
+    bsz, cin, hi, wi = x4.shape
+    cout = w4.shape[1] * groups
+    code = dtype_code(x)
+    workspace = _grouped_workspace(code, bsz, cout, ho, wo, cin, geom, groups, None, x.device)
+    out = torch.empty((bsz, cout, ho, wo), dtype=x.dtype, device=x.device)
+    check(lib().ntb200_conv2d_grouped_backward_image(code, x4.data_ptr(), w4.data_ptr(), out.data_ptr(), workspace.data_ptr(),
+                                                     bsz, cout, ho, wo, cin, kh, kw, sh, sw, ph, pw, dh, dw, groups, _stream()))
+    return out
+
+
+def conv_transpose2d_backward(x, w, grad, stride=1, padding=0, output_padding=0, dilation=1, groups=1):
+    """Gradients of conv_transpose2d -> (d_x, d_w): d_x is the forward convolution of grad with w; d_w is the kernel
+    gradient of that convolution with the roles of image (grad) and gradient (x) exchanged."""
+    _require_cuda(x, w, grad)
+    w4 = _conv_weights(x, w, groups, "conv2d transpose")
+    x4, geom, ho, wo = _transpose_geom(x, w4, stride, padding, output_padding, dilation, groups)
+    kh, kw, sh, sw, ph, pw, dh, dw = geom
+    bsz, cin, hi, wi = x4.shape
+    cout = w4.shape[1] * groups
+    g = grad.contiguous().reshape(bsz, cout, ho, wo)
+    code = dtype_code(x)
+    workspace = _grouped_workspace(code, bsz, cout, ho, wo, cin, geom, groups, None, x.device)
+    dx = torch.empty_like(x4)
+    dw_ = torch.empty_like(w4)
+    check(lib().ntb200_conv2d_grouped(code, g.data_ptr(), w4.data_ptr(), dx.data_ptr(), workspace.data_ptr(), bsz, cout, ho,
+                                      wo, cin, kh, kw, sh, sw, ph, pw, dh, dw, groups, _stream()))
+    check(lib().ntb200_conv2d_grouped_backward_kernel(code, g.data_ptr(), x4.data_ptr(), dw_.data_ptr(), workspace.data_ptr(),
+                                                      0, bsz, cout, ho, wo, cin, kh, kw, sh, sw, ph, pw, dh, dw, groups, _stream()))
+    return dx.reshape(x.shape), dw_.reshape(w.shape)
+
+
+def conv_transpose1d(x, w, stride=1, padding=0, output_padding=0, dilation=1, groups=1):
+    """functional::conv_transpose1d (conv.cpp:538-612) as the one-row case of conv_transpose2d."""
+    w3 = w.unsqueeze(0) if w.dim() == 2 else w
+    x3 = x.reshape((-1,) + tuple(x.shape[-2:]))
+    out = conv_transpose2d(x3.unsqueeze(-2), w3.unsqueeze(-2), (1, stride), (0, padding), (0, output_padding), (1, dilation),
+                           groups)
+    return out.squeeze(-2)
+
+
+def conv_transpose1d_backward(x, w, grad, stride=1, padding=0, output_padding=0, dilation=1, groups=1):
+    w3 = w.unsqueeze(0) if w.dim() == 2 else w
+    x3 = x.reshape((-1,) + tuple(x.shape[-2:]))
+    g3 = grad.reshape((x3.shape[0], -1, grad.shape[-1]))
+    dx, dw_ = conv_transpose2d_backward(x3.unsqueeze(-2), w3.unsqueeze(-2), g3.unsqueeze(-2), (1, stride), (0, padding),
+                                        (0, output_padding), (1, dilation), groups)
     return dx.reshape(x.shape), dw_.reshape(w.shape)
 
 

@@ -189,9 +189,10 @@ def unfold2d_backward(dcol, out_hw, kernel_size, dilation=1, padding=0, stride=1
     return im
 
 
-def conv2d(x, w, stride=1, padding=0, dilation=1, bf16=False, threads=None):
-    """functional::conv2d, groups == 1: matmult(col, w2d, true, true) -> [B, L, Cout], then the
-    row/col swap and the view to [B, Cout, Ho, Wo] (conv.cpp:94-95)."""
+def conv2d(x, w, stride=1, padding=0, dilation=1, bf16=False, threads=None, groups=1):
+    """functional::conv2d: matmult(col, w2d, true, true) -> [B, L, Cout], then the row/col swap and the view to
+    [B, Cout, Ho, Wo] (conv.cpp:94-95); with groups the column matrix is split into `groups` row blocks and the
+    kernel into `groups` filter blocks, multiplied pairwise and interleaved back (conv.cpp:97-118)."""
     kh, kw = w.shape[-2:]
     dh, dw = _pair(dilation)
     ph, pw = _pair(padding)
@@ -200,23 +201,75 @@ def conv2d(x, w, stride=1, padding=0, dilation=1, bf16=False, threads=None):
     ho = conv_out_size(x4.shape[-2], kh, sh, ph, dh)
     wo = conv_out_size(x4.shape[-1], kw, sw, pw, dw)
     col = unfold2d(x4, (kh, kw), dilation, padding, stride, bf16)
-    w2d = np.ascontiguousarray(w.reshape(w.shape[0], -1))
-    out = matmult(col, w2d, True, True, bf16, threads)            # [B, L, Cout]
-    return np.ascontiguousarray(out.transpose(0, 2, 1)).reshape(x4.shape[0], w.shape[0], ho, wo)
+    cout = w.shape[0]
+    ckg, coutg = col.shape[1] // groups, cout // groups
+    outs = []
+    for g in range(groups):
+        col_g = np.ascontiguousarray(col[:, g * ckg:(g + 1) * ckg])
+        w2d = np.ascontiguousarray(w[g * coutg:(g + 1) * coutg].reshape(coutg, -1))
+        out = matmult(col_g, w2d, True, True, bf16, threads)        # [B, L, Cout/groups]
+        outs.append(out.transpose(0, 2, 1))
+    return np.ascontiguousarray(np.concatenate(outs, axis=1)).reshape(x4.shape[0], cout, ho, wo)
 
 
-def conv2d_backward(x, w, grad, stride=1, padding=0, dilation=1, threads=None):
-    """conv_dimage (conv.cpp:318-346) and conv_dkernel (conv.cpp:444-471), Float32, groups == 1."""
+def conv2d_backward(x, w, grad, stride=1, padding=0, dilation=1, threads=None, groups=1):
+    """conv_dimage (conv.cpp:318-346) and conv_dkernel (conv.cpp:444-471), Float32, group by group."""
     kh, kw = w.shape[-2:]
     x4 = x.reshape((-1,) + x.shape[-3:])
     bsz, cout = x4.shape[0], w.shape[0]
     col = unfold2d(x4, (kh, kw), dilation, padding, stride)
-    w2d = np.ascontiguousarray(w.reshape(cout, -1))
-    g = np.ascontiguousarray(grad.reshape(bsz, cout, -1))
-    dcol = matmult(w2d, g, True, False, threads=threads)          # [B, C*kh*kw, L]
+    g3 = np.ascontiguousarray(grad.reshape(bsz, cout, -1))
+    ckg, coutg = col.shape[1] // groups, cout // groups
+    dcol = np.empty_like(col)
+    dw = np.empty((cout, ckg), dtype=np.float32)
+    for g in range(groups):
+        w2d = np.ascontiguousarray(w[g * coutg:(g + 1) * coutg].reshape(coutg, -1))
+        gg = np.ascontiguousarray(g3[:, g * coutg:(g + 1) * coutg])
+        dcol[:, g * ckg:(g + 1) * ckg] = matmult(w2d, gg, True, False, threads=threads)      # [B, ckg, L]
+        col_g = np.ascontiguousarray(col[:, g * ckg:(g + 1) * ckg])
+        dw[g * coutg:(g + 1) * coutg] = matmult(gg, col_g, False, True, threads=threads).sum(axis=0, dtype=np.float32)
     dx = unfold2d_backward(dcol, x4.shape[-2:], (kh, kw), dilation, padding, stride).reshape(x.shape)
-    dw = matmult(g, col, False, True, threads=threads).sum(axis=0, dtype=np.float32).reshape(w.shape)
+    return dx, dw.reshape(w.shape)
+
+
+def conv_transpose2d(x, w, stride=1, padding=0, output_padding=0, dilation=1, groups=1, threads=None):
+    """functional::conv_transpose2d (conv.cpp:614-672): the input is dilated by the stride (zeros between its
+    elements), padded at the end by output_padding, and convolved with stride 1 and padding d*(k-1) - p by the
+    kernel with its two channel axes swapped (within each group) and both spatial axes flipped."""
+    sh, sw = _pair(stride)
+    ph, pw = _pair(padding)
+    oh, ow = _pair(output_padding)
+    dh, dw = _pair(dilation)
+    x4 = x.reshape((-1,) + x.shape[-3:])
+    bsz, cin, hi, wi = x4.shape
+    kh, kw = w.shape[-2:]
+    xd = np.zeros((bsz, cin, (hi - 1) * sh + 1 + oh, (wi - 1) * sw + 1 + ow), dtype=x.dtype)
+    xd[:, :, :(hi - 1) * sh + 1:sh, :(wi - 1) * sw + 1:sw] = x4
+    cing, coutg = cin // groups, w.shape[1]
+    wf = np.empty((coutg * groups, cing, kh, kw), dtype=w.dtype)
+    for g in range(groups):     # w.transpose(0, 1).flip({-1, -2}), group by group
+        blk = w[g * cing:(g + 1) * cing]                                    # [cin/g, cout/g, kh, kw]
+        wf[g * coutg:(g + 1) * coutg] = blk.transpose(1, 0, 2, 3)[:, :, ::-1, ::-1]
+    return conv2d(xd, np.ascontiguousarray(wf), 1, (dh * (kh - 1) - ph, dw * (kw - 1) - pw), (dh, dw), threads=threads,
+                  groups=groups)
+
+
+def conv_transpose2d_backward(x, w, grad, stride=1, padding=0, output_padding=0, dilation=1, groups=1, threads=None):
+    """Gradients of conv_transpose2d: it is the image-gradient operator of the convolution with the same kernel,
+    so d_x is that convolution applied to grad, and d_w is its kernel gradient with grad as the image and x as
+    the gradient (nn/functional/conv.cpp, conv_transpose2d backward)."""
+    x4 = x.reshape((-1,) + x.shape[-3:])
+    g4 = grad.reshape((x4.shape[0], -1) + grad.shape[-2:])
+    dx = conv2d(g4, w, stride, padding, dilation, threads=threads, groups=groups).reshape(x.shape)
+    _, dw = conv2d_backward(g4, w, x4, stride, padding, dilation, threads=threads, groups=groups)
     return dx, dw
+
+
+def conv1d(x, w, stride=1, padding=0, dilation=1, groups=1, threads=None):
+    """functional::conv1d (conv.cpp:13-67): unfold1d + matmult, i.e. the one-row case of conv2d."""
+    x3 = x.reshape((-1,) + x.shape[-2:])
+    out = conv2d(x3[:, :, None, :], w[:, :, None, :], (1, stride), (0, padding), (1, dilation), threads=threads, groups=groups)
+    return out[:, :, 0, :]
 
 
 def matmult_backward(a, b, grad, transpose_a=False, transpose_b=False, bf16=False, threads=None):

@@ -1,4 +1,4 @@
-"""Copies the reference's own committed golden vectors for the matmult / linear / conv2d / unfold2d path
+"""Copies the reference's own committed golden vectors for the matmult / linear / conv / unfold2d path
 into tests/golden/reference_autograd_data/.
 
 The reference's tests (tests/src/linear_autograd_test.cpp:24-59,128-196, tests/src/conv_autograd_test.cpp:249-374,
@@ -18,6 +18,13 @@ NAMES = (
     + ["conv2d_%s%s.npy" % (s, e) for s in ("input", "weight", "output", "grad", "xgrad", "wgrad")
        for e in ("", "_batched")]
     + ["unfold_%s.npy" % s for s in ("input", "output", "grad", "input_grad")]
+    # grouped conv2d, conv1d and the transposed convolutions (tests/src/conv_autograd_test.cpp:126-240, 284-360, 556-835)
+    + ["conv2d_%s%s.npy" % (s, e) for s in ("input", "weight", "output", "grad", "xgrad", "wgrad")
+       for e in ("_grouped", "_grouped_batched")]
+    + ["%s_%s%s.npy" % (f, s, e) for f in ("conv1d", "conv_transpose1d", "conv_transpose2d")
+       for s in ("input", "weight", "output", "grad", "xgrad", "wgrad")
+       for e in ("", "_batched", "_grouped", "_grouped_batched")]
+    + ["conv_transpose1d_%s_grouped_bigger.npy" % s for s in ("input", "weight", "output", "grad", "xgrad", "wgrad")]
 )
 
 
