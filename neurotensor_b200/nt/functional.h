@@ -211,7 +211,7 @@ inline Tensor unfold2d_backward(const Tensor& dcol, int64_t H, int64_t W, int64_
     return im;
 }
 
-// conv2d, groups == 1 (conv.cpp:69-96) -> [B, Cout, Ho, Wo].
+// conv2d (conv.cpp:69-119) -> [B, Cout, Ho, Wo]; kernel is [Cout, C/groups, kh, kw].
 inline Tensor conv2d(const Tensor& image, const Tensor& kernel, const ConvArgs& g = {}, int64_t groups = 1) {
     utils::throw_exception(!image.is_null() && !kernel.is_null(), "conv2d got a null tensor");
     utils::throw_exception(image.dims() >= 3, "Expected to get a 3D or greater tensor as the input for a 2d convolution, but got ",
@@ -221,20 +221,77 @@ inline Tensor conv2d(const Tensor& image, const Tensor& kernel, const ConvArgs& 
     utils::throw_exception(image.dtype() == kernel.dtype(), "Expected both kernel and image to have the same dtype for conv2d but got ",
                            dtype_name(kernel.dtype()), " and ", dtype_name(image.dtype()));
     detail::check_conv_args(g);
-    utils::throw_exception(groups == 1, "conv2d: groups > 1 is outside this engine's scope");
+    utils::throw_exception(groups >= 1, "Expected groups for a convolution to be greater than 0 but got ", groups);
     Tensor im = detail::as_batched_image(image);
     Tensor w = kernel.contiguous();
     if (w.dims() == 3) w = w.view({1, w.shape()[0], w.shape()[1], w.shape()[2]});
     const int64_t B = im.shape()[0], C = im.shape()[1], H = im.shape()[2], W = im.shape()[3];
     const int64_t cout = w.shape()[0], kh = w.shape()[2], kw = w.shape()[3];
-    utils::throw_exception(w.shape()[1] == C, "Expected kernel channels ", w.shape()[1], " to equal image channels ", C);
+    utils::throw_exception(C % groups == 0, "Expected image channels to be divisible by groups in Conv2d but got ", C, " % ", groups,
+                           " != 0");
+    utils::throw_exception(w.shape()[1] * groups == C, "Expected kernel rows times groups to be equal to rows of image Conv2d but got ",
+                           w.shape()[1], " * ", groups, " != ", C);
     const int64_t ho = detail::out_size(H, kh, g.sh, g.ph, g.dh), wo = detail::out_size(W, kw, g.sw, g.pw, g.dw);
     utils::throw_exception(ho > 0 && wo > 0, "conv2d: calculated output size must be at least one");
-    const size_t need = ntb200_conv2d_workspace_bytes(dtype_code(image.dtype()), B, C, H, W, kh, kw, g.sh, g.sw, g.ph, g.pw, g.dh, g.dw);
+    const int code = dtype_code(image.dtype());
+    const size_t need = ntb200_conv2d_grouped_workspace_bytes(code, B, C, H, W, cout, kh, kw, g.sh, g.sw, g.ph, g.pw, g.dh, g.dw, groups);
     Tensor ws({int64_t(need)}, DType::uint8, DeviceType::CUDA);
     Tensor out({B, cout, ho, wo}, image.dtype(), DeviceType::CUDA);
-    utils::check(ntb200_conv2d(dtype_code(image.dtype()), im.data_ptr(), w.data_ptr(), out.data_ptr(), ws.data_ptr(), B, C, H, W, cout, kh,
-                               kw, g.sh, g.sw, g.ph, g.pw, g.dh, g.dw, nullptr));
+    utils::check(ntb200_conv2d_grouped(code, im.data_ptr(), w.data_ptr(), out.data_ptr(), ws.data_ptr(), B, C, H, W, cout, kh, kw, g.sh,
+                                       g.sw, g.ph, g.pw, g.dh, g.dw, groups, nullptr));
+    return out;
+}
+
+// conv1d (conv.cpp:13-67): [B, C, W] with a [Cout, C/groups, k] kernel, the one-row case of conv2d.
+inline Tensor conv1d(const Tensor& image, const Tensor& kernel, int64_t stride = 1, int64_t padding = 0, int64_t dilation = 1,
+                     int64_t groups = 1) {
+    utils::throw_exception(image.dims() >= 2, "Expected to get a 2D or greater tensor as the input for a 1d convolution, but got ",
+                           image.dims(), "D");
+    utils::throw_exception(kernel.dims() == 2 || kernel.dims() == 3,
+                           "Expected to get a 3D or 2D tensor as the kernel for a 1d convolution, but got ", kernel.dims(), "D");
+    Tensor im = image.contiguous().view({-1, image.shape()[-2], 1, image.shape()[-1]});
+    Tensor w = kernel.contiguous();
+    w = w.dims() == 2 ? w.view({1, w.shape()[0], 1, w.shape()[1]}) : w.view({w.shape()[0], w.shape()[1], 1, w.shape()[2]});
+    ConvArgs a;
+    a.sw = stride; a.pw = padding; a.dw = dilation;
+    Tensor out = conv2d(im, w, a, groups);
+    return out.view({out.shape()[0], out.shape()[1], out.shape()[3]});
+}
+
+// conv_transpose2d (conv.cpp:614-672): x [B, Cin, Hi, Wi], kernel [Cin, Cout/groups, kh, kw] -> [B, Cout, Ho, Wo].  It is
+// the image gradient of the convolution with the same kernel, evaluated with x in the place of the gradient.
+inline Tensor conv_transpose2d(const Tensor& image, const Tensor& kernel, const ConvArgs& g = {}, int64_t out_pad_h = 0,
+                               int64_t out_pad_w = 0, int64_t groups = 1) {
+    utils::throw_exception(!image.is_null() && !kernel.is_null(), "conv_transpose2d got a null tensor");
+    utils::throw_exception(image.dims() >= 3, "Expected to get a 3D or greater tensor as the input for a conv2d transpose, but got ",
+                           image.dims(), "D");
+    utils::throw_exception(kernel.dims() == 3 || kernel.dims() == 4,
+                           "Expected to get a 3D or 4D tensor as the kernel for a conv2d transpose, but got ", kernel.dims(), "D");
+    utils::throw_exception(image.dtype() == kernel.dtype(),
+                           "Expected both kernel and image to have the same dtype for conv2d transpose but got ", dtype_name(kernel.dtype()),
+                           " and ", dtype_name(image.dtype()));
+    detail::check_conv_args(g);
+    utils::throw_exception(out_pad_h >= 0 && out_pad_w >= 0, "Conv2d Transpose output_padding cannot be less than 0");
+    utils::throw_exception(out_pad_h < g.sh && out_pad_w < g.sw, "conv_transpose2d: output_padding must be smaller than the stride");
+    utils::throw_exception(groups >= 1, "Expected groups for a convolution to be greater than 0 but got ", groups);
+    Tensor im = detail::as_batched_image(image);
+    Tensor w = kernel.contiguous();
+    if (w.dims() == 3) w = w.view({1, w.shape()[0], w.shape()[1], w.shape()[2]});
+    const int64_t B = im.shape()[0], cin = im.shape()[1], hi = im.shape()[2], wi = im.shape()[3];
+    utils::throw_exception(cin == w.shape()[0], "Expected image channels to be the same as the kernel batches for conv_transpose2d but got ",
+                           im.shape(), " and ", w.shape());
+    utils::throw_exception(cin % groups == 0, "Expected image channels to be divisible by groups in Conv2d Transpose but got ", cin, " % ",
+                           groups, " != 0");
+    const int64_t cout = w.shape()[1] * groups, kh = w.shape()[2], kw = w.shape()[3];
+    const int64_t ho = (hi - 1) * g.sh - 2 * g.ph + g.dh * (kh - 1) + 1 + out_pad_h;
+    const int64_t wo = (wi - 1) * g.sw - 2 * g.pw + g.dw * (kw - 1) + 1 + out_pad_w;
+    utils::throw_exception(ho > 0 && wo > 0, "conv_transpose2d: calculated output size must be at least one");
+    const int code = dtype_code(image.dtype());
+    const size_t need = ntb200_conv2d_grouped_workspace_bytes(code, B, cout, ho, wo, cin, kh, kw, g.sh, g.sw, g.ph, g.pw, g.dh, g.dw, groups);
+    Tensor ws({int64_t(need)}, DType::uint8, DeviceType::CUDA);
+    Tensor out({B, cout, ho, wo}, image.dtype(), DeviceType::CUDA);
+    utils::check(ntb200_conv2d_grouped_backward_image(code, im.data_ptr(), w.data_ptr(), out.data_ptr(), ws.data_ptr(), B, cout, ho, wo, cin,
+                                                      kh, kw, g.sh, g.sw, g.ph, g.pw, g.dh, g.dw, groups, nullptr));
     return out;
 }
 

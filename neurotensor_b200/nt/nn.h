@@ -184,11 +184,11 @@ inline TensorGrad relu(const TensorGrad& x) {
 // conv2d with gradient tracking, groups == 1.  d_image = col2im(matmult(w2d, g, true, false)) (conv.cpp:343-345);
 // d_kernel = sum over the batch of matmult(g, col, false, true) (conv.cpp:467).  Both gradients are computed by the
 // library's conv2d backward entry points on one shared workspace.
-inline TensorGrad conv2d(const TensorGrad& image, const TensorGrad& kernel, const ConvArgs& args = {}) {
+inline TensorGrad conv2d(const TensorGrad& image, const TensorGrad& kernel, const ConvArgs& args = {}, int64_t groups = 1) {
     Tensor X = image.detach(), W = kernel.detach();
-    Tensor out = conv2d(X, W, args);
+    Tensor out = conv2d(X, W, args, groups);
     return TensorGrad::make_result(out, {image.node(), kernel.node()},
-        [X, W, args](const Tensor& g_in, GraphParents& parents) {
+        [X, W, args, groups](const Tensor& g_in, GraphParents& parents) {
             Tensor im = detail::as_batched_image(X).contiguous();
             Tensor w4 = W.contiguous();
             if (w4.dims() == 3) w4 = w4.view({1, w4.shape()[0], w4.shape()[1], w4.shape()[2]});
@@ -196,20 +196,21 @@ inline TensorGrad conv2d(const TensorGrad& image, const TensorGrad& kernel, cons
             const int64_t cout = w4.shape()[0], kh = w4.shape()[2], kw = w4.shape()[3];
             Tensor g = g_in.contiguous();
             const int code = dtype_code(X.dtype());
-            const size_t need = ntb200_conv2d_backward_workspace_bytes(code, B, C, H, Wd, cout, kh, kw, args.sh, args.sw, args.ph,
-                                                                       args.pw, args.dh, args.dw);
+            const size_t need = ntb200_conv2d_grouped_workspace_bytes(code, B, C, H, Wd, cout, kh, kw, args.sh, args.sw, args.ph,
+                                                                      args.pw, args.dh, args.dw, groups);
             Tensor ws({int64_t(need)}, DType::uint8, DeviceType::CUDA);
             if (parents[0]->requires_grad) {
                 Tensor dx({B, C, H, Wd}, X.dtype(), DeviceType::CUDA);
-                utils::check(ntb200_conv2d_backward_image(code, g.data_ptr(), w4.data_ptr(), dx.data_ptr(), ws.data_ptr(), B, C, H, Wd,
-                                                          cout, kh, kw, args.sh, args.sw, args.ph, args.pw, args.dh, args.dw, nullptr));
+                utils::check(ntb200_conv2d_grouped_backward_image(code, g.data_ptr(), w4.data_ptr(), dx.data_ptr(), ws.data_ptr(), B, C,
+                                                                  H, Wd, cout, kh, kw, args.sh, args.sw, args.ph, args.pw, args.dh,
+                                                                  args.dw, groups, nullptr));
                 parents[0]->accumulate_gradient(dx.view(X.shape().Vec()));
             }
             if (parents[1]->requires_grad) {
                 Tensor dw(w4.shape(), W.dtype(), DeviceType::CUDA);
-                utils::check(ntb200_conv2d_backward_kernel(code, im.data_ptr(), g.data_ptr(), dw.data_ptr(), ws.data_ptr(), 0, B, C, H,
-                                                           Wd, cout, kh, kw, args.sh, args.sw, args.ph, args.pw, args.dh, args.dw,
-                                                           nullptr));
+                utils::check(ntb200_conv2d_grouped_backward_kernel(code, im.data_ptr(), g.data_ptr(), dw.data_ptr(), ws.data_ptr(), 0, B,
+                                                                   C, H, Wd, cout, kh, kw, args.sh, args.sw, args.ph, args.pw, args.dh,
+                                                                   args.dw, groups, nullptr));
                 parents[1]->accumulate_gradient(dw.view(W.shape().Vec()));
             }
         });

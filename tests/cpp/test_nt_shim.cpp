@@ -160,6 +160,31 @@ int main(int argc, char** argv) {
         });
     }
 
+    for (const std::string e : {"_grouped", "_grouped_batched"}) {
+        run_test(("Conv2d Autograd test, groups = 2 (golden)" + e).c_str(), [&] {
+            TensorGrad x(fn::from_numpy(gold + "conv2d_input" + e + ".npy"), true), w(fn::from_numpy(gold + "conv2d_weight" + e + ".npy"), true);
+            TensorGrad o = fn::conv2d(x, w, fn::ConvArgs{}, 2);
+            REQUIRE(fn::allclose(o.detach(), fn::from_numpy(gold + "conv2d_output" + e + ".npy"), 1e-4, 1e-5));
+            o.backward(fn::from_numpy(gold + "conv2d_grad" + e + ".npy"));
+            REQUIRE(fn::allclose(x.grad(), fn::from_numpy(gold + "conv2d_xgrad" + e + ".npy"), 1e-4, 1e-5));
+            REQUIRE(fn::allclose(w.grad(), fn::from_numpy(gold + "conv2d_wgrad" + e + ".npy"), 1e-4, 1e-5));
+        });
+    }
+    run_test("conv1d and conv_transpose2d (golden)", [&] {
+        Tensor o1 = fn::conv1d(fn::from_numpy(gold + "conv1d_input_batched.npy"), fn::from_numpy(gold + "conv1d_weight_batched.npy"), 1, 1);
+        REQUIRE(fn::allclose(o1, fn::from_numpy(gold + "conv1d_output_batched.npy"), 1e-4, 1e-5));
+        fn::ConvArgs a;
+        a.sh = a.sw = 2; a.ph = a.pw = 1;
+        Tensor o2 = fn::conv_transpose2d(fn::from_numpy(gold + "conv_transpose2d_input_batched.npy"),
+                                         fn::from_numpy(gold + "conv_transpose2d_weight_batched.npy"), a, 1, 1);
+        REQUIRE(fn::allclose(o2, fn::from_numpy(gold + "conv_transpose2d_output_batched.npy"), 1e-4, 1e-5));
+        fn::ConvArgs b;
+        b.ph = b.pw = 1;
+        Tensor o3 = fn::conv_transpose2d(fn::from_numpy(gold + "conv_transpose2d_input_grouped.npy"),
+                                         fn::from_numpy(gold + "conv_transpose2d_weight_grouped.npy"), b, 0, 0, 5);
+        REQUIRE(fn::allclose(o3, fn::from_numpy(gold + "conv_transpose2d_output_grouped.npy"), 1e-4, 1e-5));
+    });
+
     run_test("unfold2d (golden)", [&] {
         Tensor x = fn::from_numpy(gold + "unfold_input.npy");
         fn::ConvArgs args;
