@@ -73,6 +73,7 @@ struct UmmaParams {
     // Fused elementwise neighbours (16-bit outputs): tensors laid out exactly like C, given as byte offsets from C.
     int has_relu_out, has_mask;
     int shift;                   // kOutU32: the s32 accumulator is shifted left by this much before it is added
+    int tma_store;               // pair kernel, 16-bit outputs: tiles leave through shared memory and TMA stores
     long long relu_out_offset;   // second output: max(C, 0)
     long long mask_offset;       // input h: the result is zeroed where h < 0 (ReLU backward)
 };
@@ -333,6 +334,56 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, uint32_t tmem
     }
 }
 
+// Epilogue of one warp's 32 x BN slice for 16-bit outputs, leaving through shared memory: every thread converts its
+// row 32 columns at a time and writes them into the warp's staging buffer, laid out as 64-column sub-tiles of
+// 32 rows x 128 bytes with the 128-byte swizzle (conflict-free for the 16-byte writes of 32 different rows); each
+// finished sub-tile is handed to one TMA store, which writes whole 128-byte row segments and clips at the edges
+// of C.  `staging` is this warp's 16 KB; the stores of the previous tile must have read it before it is reused.
+template <int BN>
+__device__ __forceinline__ void epilogue_tile_tma(const UmmaParams& p, const CUtensorMap* tma_c, uint32_t tmem_acc,
+                                                  uint32_t staging, int b, int row0, int lane, int n0) {
+    const int row = row0 + lane;
+    if (lane == 0) tma_store_wait_read();
+    __syncwarp();
+#pragma unroll 1
+    for (int cc = 0; cc < BN / 32; ++cc) {
+        const int col0 = n0 + cc * 32;
+        if (col0 >= p.n) break;  // uniform across the CTA
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tmem_acc + uint32_t(cc * 32), v);
+        tmem_ld_wait();
+        float f[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+        if (p.bias && row < p.m) {
+            const uint16_t* bias = static_cast<const uint16_t*>(p.bias) + (long long)b * p.bias_bs + (long long)row * p.bias_rs;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.n) f[j] += to_float_bits16(bias[(long long)(col0 + j) * p.bias_cs], p.out_kind);
+        }
+        const int sub = cc >> 1;
+        const uint32_t row_base = staging + uint32_t(sub) * 4096u + uint32_t(lane) * 128u;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                w[j] = from_float_bits16(f[8 * q + 2 * j], p.out_kind) | (from_float_bits16(f[8 * q + 2 * j + 1], p.out_kind) << 16);
+            const uint32_t chunk = uint32_t((cc & 1) * 4 + q) ^ uint32_t(lane & 7);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_base + (chunk << 4)), "r"(w[0]), "r"(w[1]),
+                         "r"(w[2]), "r"(w[3]) : "memory");
+        }
+        if ((cc & 1) || col0 + 32 >= p.n) {   // the 64-column sub-tile is complete (or C ends inside it)
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                tma_store_3d(tma_c, staging + uint32_t(sub) * 4096u, n0 + sub * 64, row0, b);
+                tma_store_commit();
+            }
+        }
+    }
+}
+
 template <MmaKind kKind, int BN, bool kSplit>
 __global__ void __launch_bounds__(kSplit ? kThreadsSplit : kThreads, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
@@ -562,23 +613,28 @@ constexpr uint32_t kPairOperandBytes = 128 * 128;                 // 128 rows (o
 template <bool kSplit>
 struct PairTile {
     static constexpr uint32_t kStageBytes = (kSplit ? 4u : 2u) * kPairOperandBytes;   // per CTA
-    static constexpr int kStages = int(229376u / kStageBytes);                        // 7 (224 KB), or 3 when split
-    static constexpr uint32_t kSmemBytes = kStages * kStageBytes + 256 + 1024;
+    // Four to seven stages run at the same speed (the loads are not latency bound), so the plain kernel keeps five and
+    // gives 64 KB to the output staging buffer of the TMA-store epilogue; the split kernel has three 64 KB stages.
+    static constexpr int kStages = kSplit ? 3 : 5;
+    static constexpr uint32_t kStagingBytes = kSplit ? 0u : 65536u;                   // 4 warps x 32 rows x 256 x 2 bytes
+    static constexpr uint32_t kSmemBytes = kStages * kStageBytes + kStagingBytes + 256 + 1024;
 };
 
 template <MmaKind kKind, bool kSplit>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kSplit ? kThreadsSplit : kThreads, 1)
 umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                       const __grid_constant__ CUtensorMap tma_a_lo, const __grid_constant__ CUtensorMap tma_b_lo,
-                      const UmmaParams p) {
+                      const __grid_constant__ CUtensorMap tma_c, const UmmaParams p) {
     constexpr int BN = 256;
     constexpr int kStages = PairTile<kSplit>::kStages;
     constexpr uint32_t kPairStageBytes = PairTile<kSplit>::kStageBytes;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    uint8_t* bar_gen = smem_gen + kStages * kPairStageBytes;
-    const uint32_t bar_base = smem_base + kStages * kPairStageBytes;
+    constexpr uint32_t kStagingBytes = PairTile<kSplit>::kStagingBytes;
+    const uint32_t staging_base = smem_base + kStages * kPairStageBytes;   // 1024-byte aligned
+    uint8_t* bar_gen = smem_gen + kStages * kPairStageBytes + kStagingBytes;
+    const uint32_t bar_base = staging_base + kStagingBytes;
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
     auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
@@ -605,6 +661,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
         fence_proxy_async_smem();
         tma_prefetch_desc(&tma_a);
         tma_prefetch_desc(&tma_b);
+        if (p.tma_store) tma_prefetch_desc(&tma_c);
     }
     if (warp == 1) {
         tmem_alloc<2>(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
@@ -762,13 +819,24 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
                 break;
             }
             tcgen05_fence_after();
-            epilogue_tile<BN>(p, tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN), b,
-                              mi * 256 + row_in_tile, ni * BN);
+            if constexpr (!kSplit) {
+                if (p.tma_store)
+                    epilogue_tile_tma<BN>(p, &tma_c, tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN),
+                                          staging_base + uint32_t(quad) * 16384u, b, mi * 256 + int(rank) * 128 + quad * 32,
+                                          lane, ni * BN);
+                else
+                    epilogue_tile<BN>(p, tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN), b,
+                                      mi * 256 + row_in_tile, ni * BN);
+            } else {
+                epilogue_tile<BN>(p, tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN), b,
+                                  mi * 256 + row_in_tile, ni * BN);
+            }
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_leader(tempty_bar(acc));
             if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
         }
+        if (p.tma_store && lane == 0) tma_store_wait_all();   // the last tiles' stores are complete before the CTA leaves
     }
 
     // ---------------------------------------------------------------------- teardown
@@ -857,6 +925,9 @@ const char* plan_operand(const void* ptr, int es, CUtensorMapDataType dt, int64_
 // NTB200_NO_PAIR=1 keeps every GEMM on the single-CTA kernel (for A/B measurements).
 const bool g_disable_pair = [] { const char* e = getenv("NTB200_NO_PAIR"); return e && e[0] == '1'; }();
 
+// NTB200_DIRECT_STORES=1 keeps the per-thread global stores in every epilogue (for A/B measurements).
+const bool g_direct_stores = [] { const char* e = getenv("NTB200_DIRECT_STORES"); return e && e[0] == '1'; }();
+
 // K blocks per partial sum of the Float32 split kernels (NTB200_TF32_CHUNK overrides it for measurements).
 const int g_split_chunk_blocks = [] {
     const char* e = getenv("NTB200_TF32_CHUNK");
@@ -906,7 +977,26 @@ const char* operands_stageable(const GemmArgs& g) {
 
 struct Maps {
     OperandPlan a, b, a_lo, b_lo;
+    CUtensorMap c;   // output tiles of the TMA-store epilogue (valid when UmmaParams::tma_store is set)
 };
+
+// Tensor map of a 16-bit C [batch][m][n] for 64-column x 32-row store boxes with the 128-byte swizzle.
+bool plan_store(void* c, CUtensorMapDataType dt, int64_t m, int64_t n, int64_t batch, int64_t c_rs, int64_t c_bs,
+                CUtensorMap* out) {
+    const uint64_t es = 2;
+    if (reinterpret_cast<uintptr_t>(c) % 16 || (uint64_t(c_rs) * es) % 16) return false;
+    if (batch > 1 && (uint64_t(c_bs) * es) % 16) return false;
+    if (c_rs < n || c_rs <= 0 || (batch > 1 && c_bs <= 0)) return false;
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return false;
+    cuuint64_t dims[3] = {cuuint64_t(n), cuuint64_t(m), cuuint64_t(batch > 1 ? batch : 1)};
+    cuuint64_t strides[2] = {cuuint64_t(c_rs) * es, batch > 1 ? cuuint64_t(c_bs) * es : round16(cuuint64_t(c_rs) * es * cuuint64_t(m))};
+    if (strides[0] >= (cuuint64_t(1) << 40) || strides[1] >= (cuuint64_t(1) << 40)) return false;
+    cuuint32_t box[3] = {64, 32, 1};
+    cuuint32_t elem_strides[3] = {1, 1, 1};
+    return enc(out, dt, 3, c, dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
 
 template <MmaKind kKind, int BN, bool kSplit>
 int launch_instance(const Maps& m, const UmmaParams& p, int grid, cudaStream_t stream) {
@@ -954,7 +1044,7 @@ int launch_pair_instance(const Maps& m, const UmmaParams& p, cudaStream_t stream
     if (cached[dev] == 0)
         cached[dev] = resident_pairs_query(reinterpret_cast<const void*>(umma_gemm_pair_kernel<kKind, kSplit>), smem);
     const int pairs = std::min(p.total_tiles, cached[dev]);
-    umma_gemm_pair_kernel<kKind, kSplit><<<2 * pairs, kSplit ? kThreadsSplit : kThreads, smem, stream>>>(m.a.map, m.b.map, m.a_lo.map, m.b_lo.map, p);
+    umma_gemm_pair_kernel<kKind, kSplit><<<2 * pairs, kSplit ? kThreadsSplit : kThreads, smem, stream>>>(m.a.map, m.b.map, m.a_lo.map, m.b_lo.map, m.c, p);
     count_launch();
     NTB200_CUDA(cudaGetLastError());
     return NTB200_OK;
@@ -1107,6 +1197,13 @@ int launch_planned(const GemmArgs& g, const Planned& pl, const Side& a, const Si
     const int ces = int(dtype_size(g.dtype));
     p.c_vec_ok = (reinterpret_cast<uintptr_t>(g.c) % 16 == 0) && ((g.c_rs * ces) % 16 == 0) &&
                  (g.batch == 1 || (g.c_bs * ces) % 16 == 0);
+    // Pair kernel, plain 16-bit output (optionally with a bias): finished tiles leave through shared memory and TMA
+    // stores.  Accumulation, the fused ReLU outputs and peer copies keep the direct stores.
+    maps.c = maps.a.map;
+    p.tma_store = 0;
+    if (use_pair && !pl.split && (pl.out_kind == kOutF16 || pl.out_kind == kOutBF16) && !g.accumulate && !g.relu_out &&
+        !g.mask_src && g.n_peers == 0 && !g_direct_stores)
+        p.tma_store = plan_store(g.c, pl.dt, g.m, g.n, g.batch, g.c_rs, g.c_bs, &maps.c) ? 1 : 0;
     const int grid = int(std::min<int64_t>(p.total_tiles, sms));
     note_route(pl.route);
     if (pl.kind == MmaKind::tf32) {

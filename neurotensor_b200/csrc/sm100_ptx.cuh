@@ -112,6 +112,18 @@ __device__ __forceinline__ void tma_load_4d_pair(uint32_t smem_dst, const void* 
         : "memory");
 }
 
+// Tiled store shared -> global of one box (bulk async-group completion), and the group bookkeeping around it.
+// The shared-memory source must have been made visible to the async proxy (fence_proxy_async_smem) by its writers.
+__device__ __forceinline__ void tma_store_3d(const void* tmap, uint32_t smem_src, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_src), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Every store group of this thread has finished READING its shared-memory source (the buffer may be rewritten).
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// Every store group of this thread has completed.
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 // ---- cluster -------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t cluster_cta_rank() {
     uint32_t r;
