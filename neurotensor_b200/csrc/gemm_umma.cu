@@ -334,51 +334,139 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, uint32_t tmem
     }
 }
 
-// Epilogue of one warp's 32 x BN slice for 16-bit outputs, leaving through shared memory: every thread converts its
-// row 32 columns at a time and writes them into the warp's staging buffer, laid out as 64-column sub-tiles of
+// Epilogue of one warp's 32 x BN slice leaving through shared memory (16-bit and 8-bit outputs): every thread
+// converts its row 32 columns at a time and writes them into the warp's staging buffer, laid out as sub-tiles of
 // 32 rows x 128 bytes with the 128-byte swizzle (conflict-free for the 16-byte writes of 32 different rows); each
 // finished sub-tile is handed to one TMA store, which writes whole 128-byte row segments and clips at the edges
-// of C.  `staging` is this warp's 16 KB; the stores of the previous tile must have read it before it is reused.
+// of C.  Bias, the previous C (accumulate) and the ReLU-backward mask are applied in registers first (the latter two
+// read with the thread's own 16-byte loads); the fused ReLU output is a second sub-tile and a second store.
+// `staging` is this warp's 16 KB = four 4 KB sub-tile buffers; a buffer is rewritten only after the store that
+// last used it has finished reading it.
 template <int BN>
-__device__ __forceinline__ void epilogue_tile_tma(const UmmaParams& p, const CUtensorMap* tma_c, uint32_t tmem_acc,
-                                                  uint32_t staging, int b, int row0, int lane, int n0) {
+__device__ __forceinline__ void epilogue_tile_tma(const UmmaParams& p, const CUtensorMap* tma_c, const CUtensorMap* tma_relu,
+                                                  uint32_t tmem_acc, uint32_t staging, int b, int row0, int lane, int n0) {
     const int row = row0 + lane;
+    const bool row_ok = row < p.m;
+    const bool i8 = p.out_kind == kOutI8;
+    const int es = i8 ? 1 : 2;
+    const int per_sub = i8 ? 4 : 2;              // 32-column chunks per 128-byte sub-tile row
+    const int pieces = i8 ? 2 : 4;               // 16-byte pieces one chunk contributes to a row
+    const uint8_t* c_row = static_cast<const uint8_t*>(p.c) + ((long long)b * p.c_bs + (long long)row * p.c_rs) * es;
     if (lane == 0) tma_store_wait_read();
     __syncwarp();
 #pragma unroll 1
     for (int cc = 0; cc < BN / 32; ++cc) {
         const int col0 = n0 + cc * 32;
         if (col0 >= p.n) break;  // uniform across the CTA
+        const int sub = cc / per_sub, in_sub = cc - sub * per_sub;
+        const int buf_c = p.has_relu_out ? ((2 * sub) & 3) : sub;
+        if (p.has_relu_out && in_sub == 0 && sub >= 2) {   // buffers of sub-tile (sub - 2) come round again
+            if (lane == 0) tma_store_wait_read_but2();
+            __syncwarp();
+        }
         uint32_t v[32];
         tmem_ld_32x32b_x32(tmem_acc + uint32_t(cc * 32), v);
         tmem_ld_wait();
-        float f[32];
+        const bool full_chunk = col0 + 32 <= p.n;
+        uint32_t w[16];                            // the chunk's 32 outputs, packed (16-bit: 16 words, 8-bit: 8 words)
+        if (i8) {
+            if (p.bias && row_ok) {
+                const int8_t* bias = static_cast<const int8_t*>(p.bias) + (long long)b * p.bias_bs + (long long)row * p.bias_rs;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
-        if (p.bias && row < p.m) {
-            const uint16_t* bias = static_cast<const uint16_t*>(p.bias) + (long long)b * p.bias_bs + (long long)row * p.bias_rs;
+                for (int j = 0; j < 32; ++j)
+                    if (col0 + j < p.n) v[j] += (uint32_t)(int)bias[(long long)(col0 + j) * p.bias_cs];
+            }
+            if (p.accumulate && row_ok) {
+                if (full_chunk) {
+                    const uint4 o0 = *reinterpret_cast<const uint4*>(c_row + col0);
+                    const uint4 o1 = *reinterpret_cast<const uint4*>(c_row + col0 + 16);
+                    const uint32_t old[8] = {o0.x, o0.y, o0.z, o0.w, o1.x, o1.y, o1.z, o1.w};
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-                if (col0 + j < p.n) f[j] += to_float_bits16(bias[(long long)(col0 + j) * p.bias_cs], p.out_kind);
+                    for (int j = 0; j < 32; ++j) v[j] += (old[j >> 2] >> (8 * (j & 3))) & 0xffu;
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (col0 + j < p.n) v[j] += c_row[col0 + j];
+                }
+            }
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+                w[q] = (v[4 * q] & 0xffu) | ((v[4 * q + 1] & 0xffu) << 8) | ((v[4 * q + 2] & 0xffu) << 16) |
+                       ((v[4 * q + 3] & 0xffu) << 24);
+        } else {
+            float f[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+            if (p.bias && row_ok) {
+                const uint16_t* bias = static_cast<const uint16_t*>(p.bias) + (long long)b * p.bias_bs + (long long)row * p.bias_rs;
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (col0 + j < p.n) f[j] += to_float_bits16(bias[(long long)(col0 + j) * p.bias_cs], p.out_kind);
+            }
+            if ((p.accumulate || p.has_mask) && row_ok) {
+                const uint8_t* src = c_row + (long long)col0 * 2 + (p.has_mask ? p.mask_offset : 0);
+                if (full_chunk) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const uint4 o = *reinterpret_cast<const uint4*>(src + 16 * q);
+                        const uint32_t ow[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const float lo = to_float_bits16(ow[j] & 0xffffu, p.out_kind), hi = to_float_bits16(ow[j] >> 16, p.out_kind);
+                            if (p.has_mask) {   // ReLU backward: no gradient where the forward input was negative
+                                if (lo < 0.f) f[8 * q + 2 * j] = 0.f;
+                                if (hi < 0.f) f[8 * q + 2 * j + 1] = 0.f;
+                            } else {
+                                f[8 * q + 2 * j] += lo;
+                                f[8 * q + 2 * j + 1] += hi;
+                            }
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (col0 + j < p.n) {
+                            const float o = to_float_bits16(reinterpret_cast<const uint16_t*>(src)[j], p.out_kind);
+                            if (p.has_mask) { if (o < 0.f) f[j] = 0.f; } else f[j] += o;
+                        }
+                }
+            }
+#pragma unroll
+            for (int q = 0; q < 16; ++q)
+                w[q] = from_float_bits16(f[2 * q], p.out_kind) | (from_float_bits16(f[2 * q + 1], p.out_kind) << 16);
         }
-        const int sub = cc >> 1;
-        const uint32_t row_base = staging + uint32_t(sub) * 4096u + uint32_t(lane) * 128u;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            uint32_t w[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-                w[j] = from_float_bits16(f[8 * q + 2 * j], p.out_kind) | (from_float_bits16(f[8 * q + 2 * j + 1], p.out_kind) << 16);
-            const uint32_t chunk = uint32_t((cc & 1) * 4 + q) ^ uint32_t(lane & 7);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_base + (chunk << 4)), "r"(w[0]), "r"(w[1]),
-                         "r"(w[2]), "r"(w[3]) : "memory");
+        const uint32_t row_c = staging + uint32_t(buf_c) * 4096u + uint32_t(lane) * 128u;
+        for (int q = 0; q < pieces; ++q) {
+            const uint32_t chunk = uint32_t(in_sub * pieces + q) ^ uint32_t(lane & 7);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_c + (chunk << 4)), "r"(w[4 * q]), "r"(w[4 * q + 1]),
+                         "r"(w[4 * q + 2]), "r"(w[4 * q + 3]) : "memory");
         }
-        if ((cc & 1) || col0 + 32 >= p.n) {   // the 64-column sub-tile is complete (or C ends inside it)
+        if (p.has_relu_out) {   // second output: the activation, negatives (of the ROUNDED value) cleared
+            const uint32_t row_r = row_c + 4096u;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                uint32_t r[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint32_t lo = w[4 * q + j] & 0xffffu, hi = w[4 * q + j] >> 16;
+                    r[j] = (to_float_bits16(lo, p.out_kind) < 0.f ? 0u : lo) | ((to_float_bits16(hi, p.out_kind) < 0.f ? 0u : hi) << 16);
+                }
+                const uint32_t chunk = uint32_t(in_sub * 4 + q) ^ uint32_t(lane & 7);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_r + (chunk << 4)), "r"(r[0]), "r"(r[1]), "r"(r[2]),
+                             "r"(r[3]) : "memory");
+            }
+        }
+        if (in_sub == per_sub - 1 || col0 + 32 >= p.n) {   // the sub-tile is complete (or C ends inside it)
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
-                tma_store_3d(tma_c, staging + uint32_t(sub) * 4096u, n0 + sub * 64, row0, b);
+                const int x0 = n0 + sub * per_sub * 32;
+                tma_store_3d(tma_c, staging + uint32_t(buf_c) * 4096u, x0, row0, b);
                 tma_store_commit();
+                if (p.has_relu_out) {
+                    tma_store_3d(tma_relu, staging + uint32_t(buf_c + 1) * 4096u, x0, row0, b);
+                    tma_store_commit();
+                }
             }
         }
     }
@@ -624,7 +712,8 @@ template <MmaKind kKind, bool kSplit>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kSplit ? kThreadsSplit : kThreads, 1)
 umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                       const __grid_constant__ CUtensorMap tma_a_lo, const __grid_constant__ CUtensorMap tma_b_lo,
-                      const __grid_constant__ CUtensorMap tma_c, const UmmaParams p) {
+                      const __grid_constant__ CUtensorMap tma_c, const __grid_constant__ CUtensorMap tma_relu,
+                      const UmmaParams p) {
     constexpr int BN = 256;
     constexpr int kStages = PairTile<kSplit>::kStages;
     constexpr uint32_t kPairStageBytes = PairTile<kSplit>::kStageBytes;
@@ -662,6 +751,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
         tma_prefetch_desc(&tma_a);
         tma_prefetch_desc(&tma_b);
         if (p.tma_store) tma_prefetch_desc(&tma_c);
+        if (p.tma_store && p.has_relu_out) tma_prefetch_desc(&tma_relu);
     }
     if (warp == 1) {
         tmem_alloc<2>(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
@@ -821,7 +911,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
             tcgen05_fence_after();
             if constexpr (!kSplit) {
                 if (p.tma_store)
-                    epilogue_tile_tma<BN>(p, &tma_c, tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN),
+                    epilogue_tile_tma<BN>(p, &tma_c, &tma_relu, tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN),
                                           staging_base + uint32_t(quad) * 16384u, b, mi * 256 + int(rank) * 128 + quad * 32,
                                           lane, ni * BN);
                 else
@@ -977,13 +1067,13 @@ const char* operands_stageable(const GemmArgs& g) {
 
 struct Maps {
     OperandPlan a, b, a_lo, b_lo;
-    CUtensorMap c;   // output tiles of the TMA-store epilogue (valid when UmmaParams::tma_store is set)
+    CUtensorMap c, relu;   // outputs of the TMA-store epilogue (valid when UmmaParams::tma_store is set)
 };
 
-// Tensor map of a 16-bit C [batch][m][n] for 64-column x 32-row store boxes with the 128-byte swizzle.
-bool plan_store(void* c, CUtensorMapDataType dt, int64_t m, int64_t n, int64_t batch, int64_t c_rs, int64_t c_bs,
+// Tensor map of C [batch][m][n] (1- or 2-byte elements) for store boxes of 128 bytes x 32 rows with the 128-byte swizzle.
+bool plan_store(void* c, CUtensorMapDataType dt, int es_bytes, int64_t m, int64_t n, int64_t batch, int64_t c_rs, int64_t c_bs,
                 CUtensorMap* out) {
-    const uint64_t es = 2;
+    const uint64_t es = uint64_t(es_bytes);
     if (reinterpret_cast<uintptr_t>(c) % 16 || (uint64_t(c_rs) * es) % 16) return false;
     if (batch > 1 && (uint64_t(c_bs) * es) % 16) return false;
     if (c_rs < n || c_rs <= 0 || (batch > 1 && c_bs <= 0)) return false;
@@ -992,7 +1082,7 @@ bool plan_store(void* c, CUtensorMapDataType dt, int64_t m, int64_t n, int64_t b
     cuuint64_t dims[3] = {cuuint64_t(n), cuuint64_t(m), cuuint64_t(batch > 1 ? batch : 1)};
     cuuint64_t strides[2] = {cuuint64_t(c_rs) * es, batch > 1 ? cuuint64_t(c_bs) * es : round16(cuuint64_t(c_rs) * es * cuuint64_t(m))};
     if (strides[0] >= (cuuint64_t(1) << 40) || strides[1] >= (cuuint64_t(1) << 40)) return false;
-    cuuint32_t box[3] = {64, 32, 1};
+    cuuint32_t box[3] = {cuuint32_t(128 / es), 32, 1};   // 128 bytes of columns x 32 rows
     cuuint32_t elem_strides[3] = {1, 1, 1};
     return enc(out, dt, 3, c, dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
@@ -1044,7 +1134,7 @@ int launch_pair_instance(const Maps& m, const UmmaParams& p, cudaStream_t stream
     if (cached[dev] == 0)
         cached[dev] = resident_pairs_query(reinterpret_cast<const void*>(umma_gemm_pair_kernel<kKind, kSplit>), smem);
     const int pairs = std::min(p.total_tiles, cached[dev]);
-    umma_gemm_pair_kernel<kKind, kSplit><<<2 * pairs, kSplit ? kThreadsSplit : kThreads, smem, stream>>>(m.a.map, m.b.map, m.a_lo.map, m.b_lo.map, m.c, p);
+    umma_gemm_pair_kernel<kKind, kSplit><<<2 * pairs, kSplit ? kThreadsSplit : kThreads, smem, stream>>>(m.a.map, m.b.map, m.a_lo.map, m.b_lo.map, m.c, m.relu, p);
     count_launch();
     NTB200_CUDA(cudaGetLastError());
     return NTB200_OK;
@@ -1197,13 +1287,18 @@ int launch_planned(const GemmArgs& g, const Planned& pl, const Side& a, const Si
     const int ces = int(dtype_size(g.dtype));
     p.c_vec_ok = (reinterpret_cast<uintptr_t>(g.c) % 16 == 0) && ((g.c_rs * ces) % 16 == 0) &&
                  (g.batch == 1 || (g.c_bs * ces) % 16 == 0);
-    // Pair kernel, plain 16-bit output (optionally with a bias): finished tiles leave through shared memory and TMA
-    // stores.  Accumulation, the fused ReLU outputs and peer copies keep the direct stores.
+    // Pair kernel, 16-bit and 8-bit outputs: finished tiles leave through shared memory and TMA stores.  Peer copies
+    // keep the direct stores.
     maps.c = maps.a.map;
+    maps.relu = maps.a.map;
     p.tma_store = 0;
-    if (use_pair && !pl.split && (pl.out_kind == kOutF16 || pl.out_kind == kOutBF16) && !g.accumulate && !g.relu_out &&
-        !g.mask_src && g.n_peers == 0 && !g_direct_stores)
-        p.tma_store = plan_store(g.c, pl.dt, g.m, g.n, g.batch, g.c_rs, g.c_bs, &maps.c) ? 1 : 0;
+    const bool out16 = pl.out_kind == kOutF16 || pl.out_kind == kOutBF16;
+    if (use_pair && !pl.split && (out16 || pl.out_kind == kOutI8) && g.n_peers == 0 && !g_direct_stores) {
+        bool ok = plan_store(g.c, pl.dt, out16 ? 2 : 1, g.m, g.n, g.batch, g.c_rs, g.c_bs, &maps.c);
+        if (ok && g.relu_out) ok = plan_store(g.relu_out, pl.dt, 2, g.m, g.n, g.batch, g.c_rs, g.c_bs, &maps.relu);
+        if (ok && g.mask_src) ok = reinterpret_cast<uintptr_t>(g.mask_src) % 16 == 0;
+        p.tma_store = ok ? 1 : 0;
+    }
     const int grid = int(std::min<int64_t>(p.total_tiles, sms));
     note_route(pl.route);
     if (pl.kind == MmaKind::tf32) {

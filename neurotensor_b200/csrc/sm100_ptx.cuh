@@ -121,6 +121,8 @@ __device__ __forceinline__ void tma_store_3d(const void* tmap, uint32_t smem_src
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Every store group of this thread has finished READING its shared-memory source (the buffer may be rewritten).
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// All but the two most recent store groups of this thread have finished reading their source.
+__device__ __forceinline__ void tma_store_wait_read_but2() { asm volatile("cp.async.bulk.wait_group.read 2;" ::: "memory"); }
 // Every store group of this thread has completed.
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
