@@ -32,10 +32,11 @@ namespace ntb200 {
 namespace {
 
 constexpr int kConvThreads = 192;                      // warp 0 loads, warp 1 issues MMAs, warps 2-5 store
-constexpr int kConvStages = 7;
+constexpr int kConvStages = 5;                         // the loads are not latency bound: 4 to 7 stages time the same
 constexpr uint32_t kConvOperandBytes = 128 * 128;      // 128 rows of 128 bytes
 constexpr uint32_t kConvStageBytes = 2 * kConvOperandBytes;
-constexpr uint32_t kConvSmemBytes = kConvStages * kConvStageBytes + 256 + 1024;
+constexpr uint32_t kConvStagingBytes = 65536;          // output staging: 4 epilogue warps x 8 chunks of 32 rows x 64 bytes
+constexpr uint32_t kConvSmemBytes = kConvStages * kConvStageBytes + kConvStagingBytes + 256 + 1024;
 constexpr uint32_t kConvTmemCols = 512;                // two accumulators of up to 256 columns
 
 struct ConvParams {
@@ -51,6 +52,7 @@ struct ConvParams {
     uint32_t idesc;
     int out_bf16;
     int vec_ok;            // rows of the output start on 16-byte boundaries
+    int tma_store;         // tiles leave through shared memory and TMA stores (bn a multiple of 32, aligned rows)
     void* out;
     unsigned int* status;  // device status word raised when a bounded wait runs out
 };
@@ -77,12 +79,13 @@ __device__ __forceinline__ uint32_t pack16(float lo, float hi, int bf16) {
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kConvThreads, 1)
 conv2d_implicit_pair_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_constant__ CUtensorMap tma_x,
-                            const ConvParams p) {
+                            const __grid_constant__ CUtensorMap tma_out, const ConvParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    uint8_t* bar_gen = smem_gen + kConvStages * kConvStageBytes;
-    const uint32_t bar_base = smem_base + kConvStages * kConvStageBytes;
+    const uint32_t staging_base = smem_base + kConvStages * kConvStageBytes;
+    uint8_t* bar_gen = smem_gen + kConvStages * kConvStageBytes + kConvStagingBytes;
+    const uint32_t bar_base = staging_base + kConvStagingBytes;
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (kConvStages + s); };
     auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * kConvStages + a); };
@@ -96,6 +99,7 @@ conv2d_implicit_pair_kernel(const __grid_constant__ CUtensorMap tma_w, const __g
     const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
 
     if (threadIdx.x == 0) {
+        if (p.tma_store) tma_prefetch_desc(&tma_out);
         for (int s = 0; s < kConvStages; ++s) {
             mbar_init(full_bar(s), 1);
             mbar_init(empty_bar(s), 1);
@@ -214,6 +218,41 @@ conv2d_implicit_pair_kernel(const __grid_constant__ CUtensorMap tma_w, const __g
             const int n0 = ni * p.bn;
             const int n_end = min(p.L, n0 + p.bn);
             const uint32_t taddr = tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * 256);
+            if (p.tma_store) {
+                // 32-column chunks leave through this warp's staging buffers (32 rows x 64 bytes each, 64-byte swizzle:
+                // the 16-byte piece q of row r sits at piece q ^ ((r >> 1) & 3)) and one TMA store per chunk, which
+                // clips at the end of the image's pixels.  bn is a multiple of 32 here, so no chunk crosses into the
+                // next tile.
+                const uint32_t staging = staging_base + uint32_t(quad) * 16384u;
+                if (lane == 0) tma_store_wait_read();
+                __syncwarp();
+#pragma unroll 1
+                for (int cc = 0; cc * 32 < p.bn; ++cc) {
+                    const int col0 = n0 + cc * 32;
+                    if (col0 >= n_end) break;   // uniform across the CTA
+                    uint32_t v[32];
+                    tmem_ld_32x32b_x32(taddr + uint32_t(cc * 32), v);
+                    tmem_ld_wait();
+                    const uint32_t buf = staging + uint32_t(cc) * 2048u;
+                    const uint32_t row_smem = buf + uint32_t(lane) * 64u;
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const uint32_t w0 = pack16(__uint_as_float(v[8 * q + 0]), __uint_as_float(v[8 * q + 1]), p.out_bf16);
+                        const uint32_t w1 = pack16(__uint_as_float(v[8 * q + 2]), __uint_as_float(v[8 * q + 3]), p.out_bf16);
+                        const uint32_t w2 = pack16(__uint_as_float(v[8 * q + 4]), __uint_as_float(v[8 * q + 5]), p.out_bf16);
+                        const uint32_t w3 = pack16(__uint_as_float(v[8 * q + 6]), __uint_as_float(v[8 * q + 7]), p.out_bf16);
+                        const uint32_t piece = uint32_t(q) ^ uint32_t((lane >> 1) & 3);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_smem + (piece << 4)), "r"(w0), "r"(w1),
+                                     "r"(w2), "r"(w3) : "memory");
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_3d(&tma_out, buf, col0, mi * 256 + int(rank) * 128 + quad * 32, b);
+                        tma_store_commit();
+                    }
+                }
+            } else {
             uint16_t* out_row = static_cast<uint16_t*>(p.out) + ((long long)b * p.cout + row) * (long long)p.L;
 #pragma unroll 1
             for (int cc = 0; cc * 32 < p.bn; ++cc) {
@@ -240,11 +279,13 @@ conv2d_implicit_pair_kernel(const __grid_constant__ CUtensorMap tma_w, const __g
                         if (col0 + j < n_end) dst[j] = uint16_t(pack16(__uint_as_float(v[j]), 0.f, p.out_bf16));
                 }
             }
+            }
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_leader(tempty_bar(acc));
             if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
         }
+        if (p.tma_store && lane == 0) tma_store_wait_all();
     }
 
     // Neither CTA may leave while the other can still signal its barriers or read its shared memory.
@@ -354,6 +395,12 @@ conv_prepare_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ xt, i
     }
 }
 
+// NTB200_DIRECT_STORES=1 keeps the per-thread global stores in the epilogue (for A/B measurements).
+bool direct_stores() {
+    const char* e = getenv("NTB200_DIRECT_STORES");
+    return e && e[0] == '1';
+}
+
 // NTB200_CONV_EXPLICIT=1 keeps every convolution on the column-matrix path (read per call, for A/B comparisons).
 bool force_explicit() {
     const char* e = getenv("NTB200_CONV_EXPLICIT");
@@ -432,6 +479,16 @@ int launch_conv2d_implicit(const Conv2dShape& s, const void* x, const void* w, v
     }
 
     ConvParams p{};
+    CUtensorMap map_out = map_w;
+    p.tma_store = 0;
+    if ((2 * rows * s.wo) % 32 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0 && L % 8 == 0 && !direct_stores()) {
+        cuuint64_t dims[3] = {cuuint64_t(L), cuuint64_t(s.cout), cuuint64_t(s.batch)};
+        cuuint64_t strides[2] = {cuuint64_t(L) * es, cuuint64_t(L) * es * cuuint64_t(s.cout)};
+        cuuint32_t box[3] = {32, 32, 1};
+        cuuint32_t estr[3] = {1, 1, 1};
+        p.tma_store = enc(&map_out, dt, 3, out, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    }
     p.cout = int(s.cout); p.L = int(L); p.batch = int(s.batch);
     p.tiles_m = int((s.cout + 255) / 256);
     p.tiles_n = int((s.ho + 2 * rows - 1) / (2 * rows));
@@ -480,7 +537,7 @@ int launch_conv2d_implicit(const Conv2dShape& s, const void* x, const void* w, v
     if (resident[dev] == 0)
         resident[dev] = max_resident_pairs(reinterpret_cast<const void*>(conv2d_implicit_pair_kernel), kConvSmemBytes);
     const int pairs = std::min(p.total_tiles, resident[dev]);
-    conv2d_implicit_pair_kernel<<<2 * pairs, kConvThreads, kConvSmemBytes, stream>>>(map_w, map_x, p);
+    conv2d_implicit_pair_kernel<<<2 * pairs, kConvThreads, kConvSmemBytes, stream>>>(map_w, map_x, map_out, p);
     count_launch();
     NTB200_CUDA(cudaGetLastError());
     note_route("conv2d-implicit-umma-pair");
