@@ -26,7 +26,7 @@ WORKLOAD = "batched matmult Float16 A[64,2048,2048] x B[64,2048,2048]^T-view, fp
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the GEMM kernel, from the ncu capture summarised in
 # profiles/umma_pair_f16_batched_2048.md: 174.6 MB for 8 items, scaled to the 64 items of a full launch (traffic
 # grows in proportion to the items).  Per batch item; multiplied by the items of the run below.
-NCU_DRAM_TRAFFIC_BYTES_PER_ITEM = (134.312192e6 + 40.332544e6) / 8
+NCU_DRAM_TRAFFIC_BYTES_PER_ITEM = (134.298880e6 + 43.018240e6) / 8
 
 
 def env_int(name, default):
