@@ -142,6 +142,12 @@ int ntb200_gemm_fused(const ntb200_gemm_desc* desc, const ntb200_gemm_epilogue* 
  * The peer_* helpers allocate buffers that can be mapped into other processes (cudaMalloc + CUDA IPC): export
  * gives a 64-byte handle to send to the peers, import maps a peer's buffer here and enables peer access. */
 int ntb200_gemm_push(const ntb200_gemm_desc* desc, void* const* peer_c, int n_peers, void* stream);
+/* Linear + ReLU of an N-sharded layer in one launch: desc->c receives the pre-activation block (kept by its owner
+ * for the backward mask), and max(c, 0) goes to relu_out (row stride relu_row_stride, normally the block's place in
+ * this GPU's full activation buffer) and to the same place in up to 7 peer-mapped activation buffers.  One 2-D
+ * problem, F16 / BF16, at least 74 tiles of 256 x 256, 16-byte aligned rows.  Ordering rules as for ntb200_gemm_push. */
+int ntb200_gemm_push_relu(const ntb200_gemm_desc* desc, void* relu_out, int64_t relu_row_stride, void* const* peer_relu,
+                          int n_peers, void* stream);
 int ntb200_peer_alloc(void** ptr, size_t bytes);
 int ntb200_peer_free(void* ptr);
 int ntb200_peer_export(const void* ptr, unsigned char handle[64]);

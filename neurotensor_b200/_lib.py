@@ -60,6 +60,7 @@ SIGNATURES = {
     "ntb200_gemm": (_ci, [ctypes.POINTER(GemmDesc), _vp]),
     "ntb200_gemm_fused": (_ci, [ctypes.POINTER(GemmDesc), ctypes.POINTER(GemmEpilogue), _vp]),
     "ntb200_gemm_push": (_ci, [ctypes.POINTER(GemmDesc), ctypes.POINTER(_vp), _ci, _vp]),
+    "ntb200_gemm_push_relu": (_ci, [ctypes.POINTER(GemmDesc), _vp, _i64, ctypes.POINTER(_vp), _ci, _vp]),
     "ntb200_peer_alloc": (_ci, [ctypes.POINTER(_vp), _sz]),
     "ntb200_peer_free": (_ci, [_vp]),
     "ntb200_peer_export": (_ci, [_vp, ctypes.c_char_p]),

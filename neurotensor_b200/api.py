@@ -197,6 +197,35 @@ def gemm_push(a, b, full_out, col0, bias=None, transpose_a=False, transpose_b=Fa
     return full_out
 
 
+def gemm_push_relu(a, b, full_act, col0, bias=None, peer_bases=()):
+    """Linear + ReLU of one rank's column block of an N-sharded layer, gathered by the GEMM itself:
+    h = bias + a.b is returned (contiguous [m, n], kept for the backward mask) and max(h, 0) is written to
+    full_act[:, col0:col0+n] here and at the same place in the peer-mapped buffers at `peer_bases`.  One launch."""
+    _require_cuda(a, b, full_act, bias)
+    m, k, n, lead = _matmult_shapes(a, b, False, False)
+    if lead or full_act.dim() != 2 or not full_act.is_contiguous():
+        raise ValueError("gemm_push_relu takes 2-D operands and a contiguous 2-D activation buffer")
+    if full_act.shape[0] != m or col0 < 0 or col0 + n > full_act.shape[1] or full_act.dtype != a.dtype:
+        raise ValueError("gemm_push_relu: column block [%d, %d) does not fit a buffer of shape %s"
+                         % (col0, col0 + n, tuple(full_act.shape)))
+    es = full_act.element_size()
+    h = torch.empty((m, n), dtype=a.dtype, device=a.device)
+    d = GemmDesc()
+    d.dtype, d.route, d.accumulate, d.f16_rounding = dtype_code(a), _lib.ROUTE_TENSOR, 0, _lib.F16_ROUND_ONCE
+    d.m, d.n, d.k, d.batch = m, n, k, 1
+    d.a, d.a_row_stride, d.a_col_stride, d.a_batch_stride = a.data_ptr(), a.stride(0), a.stride(1), 0
+    d.b, d.b_row_stride, d.b_col_stride, d.b_batch_stride = b.data_ptr(), b.stride(0), b.stride(1), 0
+    d.c, d.c_row_stride, d.c_batch_stride = h.data_ptr(), n, 0
+    if bias is not None:
+        if bias.dim() != 1 or bias.shape[0] != n or bias.dtype != a.dtype:
+            raise ValueError("gemm_push_relu: bias must be a vector of the block's %d columns" % n)
+        d.bias, d.bias_row_stride, d.bias_col_stride, d.bias_batch_stride = bias.data_ptr(), 0, bias.stride(0), 0
+    peers = (ctypes.c_void_p * max(1, len(peer_bases)))(*[int(p) + col0 * es for p in peer_bases])
+    check(lib().ntb200_gemm_push_relu(ctypes.byref(d), full_act.data_ptr() + col0 * es, full_act.shape[1], peers,
+                                      len(peer_bases), _stream()))
+    return h
+
+
 def matmult(a, b, transpose_a=False, transpose_b=False, out=None, route=_lib.ROUTE_AUTO,
             f16_rounding=_lib.F16_ROUND_ONCE):
     """functional::matmult.  Without `out` returns a new tensor op(a).op(b); with `out` computes

@@ -261,7 +261,8 @@ int ntb200_stream_synchronize(void* stream) {
     return NTB200_OK;
 }
 
-static int gemm_from_desc(const ntb200_gemm_desc* d, const ntb200_gemm_epilogue* ep, void* const* peer_c, int n_peers, void* stream) {
+static int gemm_from_desc(const ntb200_gemm_desc* d, const ntb200_gemm_epilogue* ep, void* const* peer_c, int n_peers, void* stream,
+                          int64_t relu_row_stride = 0, int peers_get_relu = 0) {
     if (!d) return fail(NTB200_ERR_INVALID_ARG, "gemm: null descriptor");
     GemmArgs g{};
     if (n_peers < 0 || n_peers > 7) return fail(NTB200_ERR_INVALID_ARG, "gemm_push: between 0 and 7 peers");
@@ -278,6 +279,7 @@ static int gemm_from_desc(const ntb200_gemm_desc* d, const ntb200_gemm_epilogue*
     g.c = d->c; g.c_rs = d->c_row_stride; g.c_bs = d->c_batch_stride;
     g.bias = d->bias; g.bias_rs = d->bias_row_stride; g.bias_cs = d->bias_col_stride; g.bias_bs = d->bias_batch_stride;
     if (ep) { g.relu_out = ep->relu_out; g.mask_src = ep->relu_mask_src; }
+    g.relu_rs = relu_row_stride; g.relu_bs = 0; g.peers_get_relu = peers_get_relu;
     if ((g.relu_out || g.mask_src) && d->route == NTB200_ROUTE_SIMT)
         return fail(NTB200_ERR_UNSUPPORTED, "gemm: fused ReLU epilogues need the tcgen05 route");
     if (g.c_rs < g.n && g.m > 1) return fail(NTB200_ERR_INVALID_ARG, "gemm: C row stride %lld is smaller than n %lld", (long long)g.c_rs, (long long)g.n);
@@ -324,6 +326,17 @@ int ntb200_gemm_fused(const ntb200_gemm_desc* d, const ntb200_gemm_epilogue* ep,
 
 int ntb200_gemm_push(const ntb200_gemm_desc* d, void* const* peer_c, int n_peers, void* stream) {
     return gemm_from_desc(d, nullptr, peer_c, n_peers, stream);
+}
+
+int ntb200_gemm_push_relu(const ntb200_gemm_desc* d, void* relu_out, int64_t relu_row_stride, void* const* peer_relu,
+                          int n_peers, void* stream) {
+    if (!d) return fail(NTB200_ERR_INVALID_ARG, "gemm_push_relu: null descriptor");
+    if (!relu_out) return fail(NTB200_ERR_INVALID_ARG, "gemm_push_relu: null ReLU output");
+    if (d->batch != 1) return fail(NTB200_ERR_INVALID_ARG, "gemm_push_relu takes one 2-D problem");
+    if (relu_row_stride < d->n) return fail(NTB200_ERR_INVALID_ARG, "gemm_push_relu: ReLU row stride %lld is smaller than n %lld",
+                                            (long long)relu_row_stride, (long long)d->n);
+    ntb200_gemm_epilogue ep{relu_out, nullptr};
+    return gemm_from_desc(d, &ep, peer_relu, n_peers, stream, relu_row_stride, 1);
 }
 
 int ntb200_peer_alloc(void** ptr, size_t bytes) {

@@ -74,8 +74,14 @@ struct UmmaParams {
     int has_relu_out, has_mask;
     int shift;                   // kOutU32: the s32 accumulator is shifted left by this much before it is added
     int tma_store;               // pair kernel, 16-bit outputs: tiles leave through shared memory and TMA stores
+    int peers_relu;              // TMA-store epilogue: the peer copies receive the fused ReLU output instead of C
     long long relu_out_offset;   // second output: max(C, 0)
     long long mask_offset;       // input h: the result is zeroed where h < 0 (ReLU backward)
+};
+
+// Tensor maps of the peer-mapped copies of C (TMA-store epilogue of ntb200_gemm_push); only the first n_peers are valid.
+struct PeerMaps {
+    CUtensorMap m[7];
 };
 
 // kSplit: every operand is staged twice (high and low part of a Float32 split into two TF32 values).
@@ -344,7 +350,8 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, uint32_t tmem
 // last used it has finished reading it.
 template <int BN>
 __device__ __forceinline__ void epilogue_tile_tma(const UmmaParams& p, const CUtensorMap* tma_c, const CUtensorMap* tma_relu,
-                                                  uint32_t tmem_acc, uint32_t staging, int b, int row0, int lane, int n0) {
+                                                  const PeerMaps* peers, uint32_t tmem_acc, uint32_t staging, int b, int row0,
+                                                  int lane, int n0) {
     const int row = row0 + lane;
     const bool row_ok = row < p.m;
     const bool i8 = p.out_kind == kOutI8;
@@ -462,9 +469,15 @@ __device__ __forceinline__ void epilogue_tile_tma(const UmmaParams& p, const CUt
             if (lane == 0) {
                 const int x0 = n0 + sub * per_sub * 32;
                 tma_store_3d(tma_c, staging + uint32_t(buf_c) * 4096u, x0, row0, b);
+                // the same sub-tile into every peer's copy: whole 128-byte row segments over NVLink
+                if (!p.peers_relu)
+                    for (int t = 0; t < p.n_peers; ++t) tma_store_3d(&peers->m[t], staging + uint32_t(buf_c) * 4096u, x0, row0, b);
                 tma_store_commit();
                 if (p.has_relu_out) {
                     tma_store_3d(tma_relu, staging + uint32_t(buf_c + 1) * 4096u, x0, row0, b);
+                    if (p.peers_relu)
+                        for (int t = 0; t < p.n_peers; ++t)
+                            tma_store_3d(&peers->m[t], staging + uint32_t(buf_c + 1) * 4096u, x0, row0, b);
                     tma_store_commit();
                 }
             }
@@ -713,7 +726,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kSplit ? kThreadsSpl
 umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                       const __grid_constant__ CUtensorMap tma_a_lo, const __grid_constant__ CUtensorMap tma_b_lo,
                       const __grid_constant__ CUtensorMap tma_c, const __grid_constant__ CUtensorMap tma_relu,
-                      const UmmaParams p) {
+                      const __grid_constant__ PeerMaps tma_peers, const UmmaParams p) {
     constexpr int BN = 256;
     constexpr int kStages = PairTile<kSplit>::kStages;
     constexpr uint32_t kPairStageBytes = PairTile<kSplit>::kStageBytes;
@@ -911,7 +924,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
             tcgen05_fence_after();
             if constexpr (!kSplit) {
                 if (p.tma_store)
-                    epilogue_tile_tma<BN>(p, &tma_c, &tma_relu, tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN),
+                    epilogue_tile_tma<BN>(p, &tma_c, &tma_relu, &tma_peers, tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN),
                                           staging_base + uint32_t(quad) * 16384u, b, mi * 256 + int(rank) * 128 + quad * 32,
                                           lane, ni * BN);
                 else
@@ -1068,6 +1081,7 @@ const char* operands_stageable(const GemmArgs& g) {
 struct Maps {
     OperandPlan a, b, a_lo, b_lo;
     CUtensorMap c, relu;   // outputs of the TMA-store epilogue (valid when UmmaParams::tma_store is set)
+    PeerMaps peers;
 };
 
 // Tensor map of C [batch][m][n] (1- or 2-byte elements) for store boxes of 128 bytes x 32 rows with the 128-byte swizzle.
@@ -1134,7 +1148,7 @@ int launch_pair_instance(const Maps& m, const UmmaParams& p, cudaStream_t stream
     if (cached[dev] == 0)
         cached[dev] = resident_pairs_query(reinterpret_cast<const void*>(umma_gemm_pair_kernel<kKind, kSplit>), smem);
     const int pairs = std::min(p.total_tiles, cached[dev]);
-    umma_gemm_pair_kernel<kKind, kSplit><<<2 * pairs, kSplit ? kThreadsSplit : kThreads, smem, stream>>>(m.a.map, m.b.map, m.a_lo.map, m.b_lo.map, m.c, m.relu, p);
+    umma_gemm_pair_kernel<kKind, kSplit><<<2 * pairs, kSplit ? kThreadsSplit : kThreads, smem, stream>>>(m.a.map, m.b.map, m.a_lo.map, m.b_lo.map, m.c, m.relu, m.peers, p);
     count_launch();
     NTB200_CUDA(cudaGetLastError());
     return NTB200_OK;
@@ -1287,18 +1301,28 @@ int launch_planned(const GemmArgs& g, const Planned& pl, const Side& a, const Si
     const int ces = int(dtype_size(g.dtype));
     p.c_vec_ok = (reinterpret_cast<uintptr_t>(g.c) % 16 == 0) && ((g.c_rs * ces) % 16 == 0) &&
                  (g.batch == 1 || (g.c_bs * ces) % 16 == 0);
-    // Pair kernel, 16-bit and 8-bit outputs: finished tiles leave through shared memory and TMA stores.  Peer copies
-    // keep the direct stores.
+    // Pair kernel, 16-bit and 8-bit outputs: finished tiles leave through shared memory and TMA stores, peer copies
+    // of C included (plain TMA stores into peer-mapped memory; no load ever touches a peer).
     maps.c = maps.a.map;
     maps.relu = maps.a.map;
     p.tma_store = 0;
     const bool out16 = pl.out_kind == kOutF16 || pl.out_kind == kOutBF16;
-    if (use_pair && !pl.split && (out16 || pl.out_kind == kOutI8) && g.n_peers == 0 && !g_direct_stores) {
+    if (use_pair && !pl.split && (out16 || pl.out_kind == kOutI8) && !g_direct_stores) {
+        const int64_t relu_rs = g.relu_rs ? g.relu_rs : g.c_rs, relu_bs = g.relu_rs ? g.relu_bs : g.c_bs;
+        const bool peers_relu = g.peers_get_relu && g.relu_out;
         bool ok = plan_store(g.c, pl.dt, out16 ? 2 : 1, g.m, g.n, g.batch, g.c_rs, g.c_bs, &maps.c);
-        if (ok && g.relu_out) ok = plan_store(g.relu_out, pl.dt, 2, g.m, g.n, g.batch, g.c_rs, g.c_bs, &maps.relu);
+        for (int t = 0; ok && t < g.n_peers; ++t)   // peer-mapped copies with the layout of the tensor they mirror
+            ok = plan_store(g.peer_c[t], pl.dt, out16 ? 2 : 1, g.m, g.n, g.batch, peers_relu ? relu_rs : g.c_rs,
+                            peers_relu ? relu_bs : g.c_bs, &maps.peers.m[t]);
+        if (ok && g.relu_out) ok = plan_store(g.relu_out, pl.dt, 2, g.m, g.n, g.batch, relu_rs, relu_bs, &maps.relu);
+        p.peers_relu = peers_relu ? 1 : 0;
         if (ok && g.mask_src) ok = reinterpret_cast<uintptr_t>(g.mask_src) % 16 == 0;
         p.tma_store = ok ? 1 : 0;
     }
+    if (!p.tma_store && g.relu_out && ((g.relu_rs && g.relu_rs != g.c_rs) || g.peers_get_relu))
+        return fail(NTB200_ERR_UNSUPPORTED,
+                    "tcgen05 route: a ReLU output with its own strides (or pushed to peers) needs the TMA-store epilogue "
+                    "(problem of at least 74 tiles of 256 x 256, 16-byte aligned rows)");
     const int grid = int(std::min<int64_t>(p.total_tiles, sms));
     note_route(pl.route);
     if (pl.kind == MmaKind::tf32) {

@@ -41,6 +41,8 @@ struct GemmArgs {
     void* const* c_ptrs = nullptr;
     // fused elementwise neighbours (tcgen05 route, 16-bit): tensors with exactly C's layout
     void* relu_out = nullptr;        // also write max(C, 0) here
+    int64_t relu_rs = 0, relu_bs = 0;  // strides of relu_out when they differ from C's (0: exactly C's layout; TMA-store epilogue only)
+    int peers_get_relu = 0;          // the peer copies receive relu_out's values instead of C's
     const void* mask_src = nullptr;  // zero the result where this tensor is negative
     // peer-mapped copies of C on other GPUs that receive every finished tile as well (tcgen05 route only)
     int n_peers = 0;

@@ -171,18 +171,17 @@ class ShardedMLP:
         dist.all_reduce(self._fused["flag"], group=self.group)   # stream-ordered: every rank's GEMM is behind it
 
     def step_fused(self, x, target):
-        """Same step with the all-gathers fused into the GEMM epilogues.  The hidden buffer holds the pre-activation
-        h (the ReLU is applied to the gathered buffer locally: cheaper than a second pass on every shard's owner and
-        it keeps h for the mask)."""
+        """Same step with the all-gathers fused into the GEMM epilogues: layer 1 keeps its pre-activation block and
+        pushes the activation block into every rank's activation buffer (one launch), layer 2 pushes its output
+        block; one barrier after each before anybody reads a gathered buffer.  The backward is the one of step()."""
         from . import api
         f = self._fused
         par = f["parity"]
         f["parity"] ^= 1
-        hbuf, ybuf = f["a"][par], f["y"][par]
-        api.gemm_push(x, self.w1, hbuf.local, self.h0, bias=self.b1, peer_bases=hbuf.peer_bases)     # h, all ranks
+        abuf, ybuf = f["a"][par], f["y"][par]
+        h_loc = api.gemm_push_relu(x, self.w1, abuf.local, self.h0, bias=self.b1, peer_bases=abuf.peer_bases)
         self._rank_barrier()
-        h_full = hbuf.local
-        a = api.relu(h_full)                                                                          # [B, H]
+        a = abuf.local                                                         # [B, H], every rank's block
         w2_cols = self.w2[:, self.d0:self.d0 + self.dn]
         api.gemm_push(a, w2_cols, ybuf.local, self.d0, bias=self.b2[self.d0:self.d0 + self.dn], peer_bases=ybuf.peer_bases)
         self._rank_barrier()
@@ -192,9 +191,7 @@ class ShardedMLP:
         gw2_loc = api.matmult(a, dy_loc, True, False)
         gb2_loc = api.column_sum(dy_loc.contiguous())
         w2_rows = self.w2[self.h0:self.h0 + self.hn]
-        da_loc = api.matmult(dy, w2_rows, False, True)
-        h_loc = h_full[:, self.h0:self.h0 + self.hn].contiguous()
-        dh_loc = api.relu_backward(h_loc, da_loc)
+        dh_loc = api.matmult_relu_backward(dy, w2_rows, h_loc, True)           # ReLU mask in the epilogue
         gw1_loc = api.matmult(x, dh_loc, True, False)
         gb1_loc = api.column_sum(dh_loc)
         return loss, dict(w1=gw1_loc, b1=gb1_loc, w2=gw2_loc, b2=gb2_loc, y=y)

@@ -242,6 +242,30 @@ def test_gemm_push_writes_every_copy(api, oracle):
         api.gemm_push(dev(x), dev(w), full[0], 300)                           # block does not fit
 
 
+def test_gemm_push_on_the_tma_store_path_and_push_relu(api, oracle):
+    """Problems of at least 74 pair tiles leave through shared memory and TMA stores, also into the peer copies
+    (local stand-ins here).  ntb200_gemm_push_relu keeps the pre-activation block and gathers the activation block."""
+    rng = np.random.default_rng(19)
+    m, k, n, width, col0 = 2304, 128, 2096, 4608, 2048          # 9 x 9 = 81 tiles; the last column tile is ragged
+    x, w, b = normal(rng, (m, k), np.float16, 0.5), normal(rng, (k, n), np.float16, 0.5), normal(rng, (n,), np.float16)
+    xd, wd, bd = dev(x), dev(w), dev(b)
+    full = [torch.full((m, width), 7.0, dtype=torch.float16, device="cuda") for _ in range(3)]
+    api.gemm_push(xd, wd, full[0], col0, bias=bd, peer_bases=[full[1].data_ptr(), full[2].data_ptr()])
+    h_exp = api.linear(xd, wd, bd)                                # same kernel without the peers
+    for f in full:
+        assert torch.equal(f[:, col0:col0 + n], h_exp)
+        assert bool((f[:, :col0] == 7).all()) and bool((f[:, col0 + n:] == 7).all())
+    assert oracle.rel_fro(host(h_exp[:64]), oracle.linear(x[:64], w, b)) <= 2e-3
+    act = [torch.full((m, width), 7.0, dtype=torch.float16, device="cuda") for _ in range(3)]
+    h = api.gemm_push_relu(xd, wd, act[0], col0, bias=bd, peer_bases=[act[1].data_ptr(), act[2].data_ptr()])
+    assert torch.equal(h, h_exp)                                  # the owner keeps the pre-activation
+    for f in act:
+        assert torch.equal(f[:, col0:col0 + n], api.relu(h_exp))
+        assert bool((f[:, :col0] == 7).all()) and bool((f[:, col0 + n:] == 7).all())
+    with pytest.raises(RuntimeError):                             # too small for the pair kernel: refused, not emulated
+        api.gemm_push_relu(xd[:128], wd[:, :128], torch.zeros((128, 256), dtype=torch.float16, device="cuda"), 0, peer_bases=[])
+
+
 def test_sharded_mlp_matches_unsharded(api, oracle):
     """partition.ShardedMLP with one rank is the plain step; two simulated shards reproduce its gradients exactly."""
     from neurotensor_b200 import partition
