@@ -2,10 +2,11 @@
 
     python -m neurotensor_b200.bench_mlp_sharded                       # 1 GPU
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
-        -m neurotensor_b200.bench_mlp_sharded [--steps K] [--check]
+        -m neurotensor_b200.bench_mlp_sharded [--steps K] [--check] [--nccl]
 
 Strong scaling: the problem is fixed, every large GEMM is split over its output columns across the ranks, and the
-hidden activations and the output are all-gathered with NCCL (partition.ShardedMLP).  Time is CUDA events around K
+hidden activations and the output are gathered by the GEMMs' own epilogues (TMA stores into every rank's buffer,
+partition.ShardedMLP.step_fused); `--nccl` gathers them with NCCL all-gathers instead.  Time is CUDA events around K
 steps between barriers, maximum over ranks.  `--check` compares rank 0's loss and gradient shards with the same step
 run unsharded on rank 0.  Prints one JSON line on rank 0.
 """
@@ -30,7 +31,8 @@ def main():
     ap.add_argument("--din", type=int, default=4096)
     ap.add_argument("--hidden", type=int, default=16384)
     ap.add_argument("--check", action="store_true")
-    ap.add_argument("--fused", action="store_true", help="all-gathers fused into the GEMM epilogues (peer stores)")
+    ap.add_argument("--fused", action="store_true", help="(default) all-gathers fused into the GEMM epilogues: TMA stores into peer buffers")
+    ap.add_argument("--nccl", action="store_true", help="baseline: NCCL all-gather + re-tile kernel instead of the fused epilogues")
     args = ap.parse_args()
     rank, world, local = (int(os.environ.get(k, d)) for k, d in (("RANK", 0), ("WORLD_SIZE", 1), ("LOCAL_RANK", 0)))
     torch.cuda.set_device(local)
@@ -53,7 +55,7 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    fused = args.fused and world > 1
+    fused = (not args.nccl) and world > 1
     if fused:
         mlp.enable_fused_gather(B)
     step = mlp.step_fused if fused else mlp.step
