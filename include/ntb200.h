@@ -249,6 +249,27 @@ int ntb200_conv2d_grouped_backward_kernel(int dtype, const void* x, const void* 
                                           int64_t sh, int64_t sw, int64_t ph, int64_t pw, int64_t dh, int64_t dw,
                                           int64_t groups, void* stream);
 
+/* ---- conv3d -------------------------------------------------------------------------------------------
+ * functional::conv3d / unfold3d and their backward (nt/functional/tensor_files/conv.cpp:122-174 and the dim == 3
+ * cases of conv_dimage / conv_dkernel; colim_transform.cpp:661-800).  x is [B, C, D, H, W], w is
+ * [Cout, C/groups, kd, kh, kw]; the three-element arrays are ordered (depth, height, width).  The column matrix
+ * is col[b][((c*kd + kz)*kh + ky)*kw + kx][(z*Ho + y)*Wo + x].  One workspace size serves the three conv3d calls.
+ * conv_transpose3d(x, w) is ntb200_conv3d_backward_image with x in the place of grad (as in the 2-D case).
+ * This struct is frozen: new inputs get new entry points. */
+typedef struct ntb200_conv3d_geom {
+    int64_t batch, channels, depth, height, width, cout, groups;
+    int64_t kernel[3], stride[3], padding[3], dilation[3];
+} ntb200_conv3d_geom;
+int ntb200_im2col3d(int dtype, const void* im, void* col, const ntb200_conv3d_geom* geom, void* stream);
+int ntb200_col2im3d(int dtype, const void* col, void* im, const ntb200_conv3d_geom* geom, void* stream);
+size_t ntb200_conv3d_workspace_bytes(int dtype, const ntb200_conv3d_geom* geom);
+int ntb200_conv3d(int dtype, const void* x, const void* w, void* out, void* workspace, const ntb200_conv3d_geom* geom,
+                  void* stream);
+int ntb200_conv3d_backward_image(int dtype, const void* grad, const void* w, void* d_image, void* workspace,
+                                 const ntb200_conv3d_geom* geom, void* stream);
+int ntb200_conv3d_backward_kernel(int dtype, const void* x, const void* grad, void* d_kernel, void* workspace,
+                                  int accumulate, const ntb200_conv3d_geom* geom, void* stream);
+
 /* ntb200_conv2d for callers that cannot allocate device memory.  No counterpart in the reference, which
  * allocates its column matrix on the CPU heap as it goes.  Some users of this library cannot do the
  * device-side equivalent: their application has given the whole device heap to its own allocator, so a

@@ -30,6 +30,12 @@ class GemmDesc(ctypes.Structure):
     ]
 
 
+class Conv3dGeom(ctypes.Structure):
+    """ntb200_conv3d_geom: three-element arrays are (depth, height, width)."""
+    _fields_ = [(n, ctypes.c_int64) for n in ("batch", "channels", "depth", "height", "width", "cout", "groups")] + \
+               [(n, ctypes.c_int64 * 3) for n in ("kernel", "stride", "padding", "dilation")]
+
+
 class GemmEpilogue(ctypes.Structure):
     _fields_ = [("relu_out", _vp), ("relu_mask_src", _vp)]
 
@@ -81,6 +87,12 @@ SIGNATURES = {
     "ntb200_conv2d_grouped": (_ci, [_ci, _vp, _vp, _vp, _vp] + [_i64] * 14 + [_vp]),
     "ntb200_conv2d_grouped_backward_image": (_ci, [_ci, _vp, _vp, _vp, _vp] + [_i64] * 14 + [_vp]),
     "ntb200_conv2d_grouped_backward_kernel": (_ci, [_ci, _vp, _vp, _vp, _vp, _ci] + [_i64] * 14 + [_vp]),
+    "ntb200_im2col3d": (_ci, [_ci, _vp, _vp, ctypes.POINTER(Conv3dGeom), _vp]),
+    "ntb200_col2im3d": (_ci, [_ci, _vp, _vp, ctypes.POINTER(Conv3dGeom), _vp]),
+    "ntb200_conv3d_workspace_bytes": (_sz, [_ci, ctypes.POINTER(Conv3dGeom)]),
+    "ntb200_conv3d": (_ci, [_ci, _vp, _vp, _vp, _vp, ctypes.POINTER(Conv3dGeom), _vp]),
+    "ntb200_conv3d_backward_image": (_ci, [_ci, _vp, _vp, _vp, _vp, ctypes.POINTER(Conv3dGeom), _vp]),
+    "ntb200_conv3d_backward_kernel": (_ci, [_ci, _vp, _vp, _vp, _vp, _ci, ctypes.POINTER(Conv3dGeom), _vp]),
     "ntb200_conv2d_static_scratch": (_ci, [_ci, _vp, _vp, _vp] + [_i64] * 13 + [_vp]),
     "ntb200_relu": (_ci, [_ci, _vp, _vp, _i64, _vp]),
     "ntb200_relu_backward": (_ci, [_ci, _vp, _vp, _vp, _i64, _vp]),

@@ -475,6 +475,118 @@ def conv_transpose1d_backward(x, w, grad, stride=1, padding=0, output_padding=0,
     return dx.reshape(x.shape), dw_.reshape(w.shape)
 
 
+def _triple(v):
+    if isinstance(v, (tuple, list)):
+        if len(v) != 3:
+            raise ValueError("expected one value or three (depth, height, width), got %r" % (v,))
+        return tuple(int(q) for q in v)
+    return (int(v),) * 3
+
+
+def _geom3(bsz, ch, dhw, cout, groups, kernel, stride, padding, dilation):
+    g = _lib.Conv3dGeom()
+    g.batch, g.channels, (g.depth, g.height, g.width), g.cout, g.groups = bsz, ch, dhw, cout, groups
+    for name, val in (("kernel", kernel), ("stride", stride), ("padding", padding), ("dilation", dilation)):
+        arr = getattr(g, name)
+        for i in range(3):
+            arr[i] = val[i]
+    return g
+
+
+def _conv3d_setup(x, w, stride, padding, dilation, groups, what="conv3d"):
+    _require_cuda(x, w)
+    if x.dim() < 4 or w.dim() not in (4, 5):
+        raise ValueError("Expected a 4D or greater input and a 4D or 5D kernel for a 3d convolution")
+    if x.dtype != w.dtype:
+        raise ValueError("Expected both kernel and image to have the same dtype for %s but got %s and %s" % (what, w.dtype, x.dtype))
+    w5 = (w.unsqueeze(0) if w.dim() == 4 else w).contiguous()
+    x5 = x.reshape((-1,) + tuple(x.shape[-4:])).contiguous()
+    return x5, w5, _triple(stride), _triple(padding), _triple(dilation)
+
+
+def _out3(size, k, s, p, d):
+    return tuple((size[i] + 2 * p[i] - d[i] * (k[i] - 1) - 1) // s[i] + 1 for i in range(3))
+
+
+def conv3d(x, w, stride=1, padding=0, dilation=1, groups=1):
+    """functional::conv3d (conv.cpp:122-174) -> [B, Cout, Do, Ho, Wo]; w is [Cout, C/groups, kd, kh, kw]."""
+    x5, w5, s3, p3, d3 = _conv3d_setup(x, w, stride, padding, dilation, groups)
+    bsz, ch = x5.shape[:2]
+    cout, k3 = w5.shape[0], tuple(w5.shape[-3:])
+    if groups < 1 or ch % groups or w5.shape[1] * groups != ch:
+        raise ValueError("Expected kernel channels %d times groups %d to equal image channels %d" % (w5.shape[1], groups, ch))
+    o3 = _out3(tuple(x5.shape[-3:]), k3, s3, p3, d3)
+    if min(o3) <= 0:
+        raise ValueError("conv3d: calculated output size %s must be at least one" % (o3,))
+    geom = _geom3(bsz, ch, tuple(x5.shape[-3:]), cout, groups, k3, s3, p3, d3)
+    code = dtype_code(x)
+    ws = torch.empty(max(1, lib().ntb200_conv3d_workspace_bytes(code, ctypes.byref(geom))), dtype=torch.uint8, device=x.device)
+    out = torch.empty((bsz, cout) + o3, dtype=x.dtype, device=x.device)
+    check(lib().ntb200_conv3d(code, x5.data_ptr(), w5.data_ptr(), out.data_ptr(), ws.data_ptr(), ctypes.byref(geom), _stream()))
+    return out
+
+
+def conv3d_backward(x, w, grad, stride=1, padding=0, dilation=1, groups=1):
+    """conv_dimage / conv_dkernel for the 3-D case -> (d_image, d_kernel)."""
+    x5, w5, s3, p3, d3 = _conv3d_setup(x, w, stride, padding, dilation, groups)
+    _require_cuda(grad)
+    bsz, ch = x5.shape[:2]
+    cout, k3 = w5.shape[0], tuple(w5.shape[-3:])
+    geom = _geom3(bsz, ch, tuple(x5.shape[-3:]), cout, groups, k3, s3, p3, d3)
+    code = dtype_code(x)
+    g = grad.contiguous()
+    ws = torch.empty(max(1, lib().ntb200_conv3d_workspace_bytes(code, ctypes.byref(geom))), dtype=torch.uint8, device=x.device)
+    dx, dw_ = torch.empty_like(x5), torch.empty_like(w5)
+    check(lib().ntb200_conv3d_backward_image(code, g.data_ptr(), w5.data_ptr(), dx.data_ptr(), ws.data_ptr(), ctypes.byref(geom),
+                                             _stream()))
+    check(lib().ntb200_conv3d_backward_kernel(code, x5.data_ptr(), g.data_ptr(), dw_.data_ptr(), ws.data_ptr(), 0,
+                                              ctypes.byref(geom), _stream()))
+    return dx.reshape(x.shape), dw_.reshape(w.shape)
+
+
+def _transpose3_geom(x5, w5, s3, p3, o3pad, d3, groups):
+    if x5.shape[1] != w5.shape[0]:
+        raise ValueError("Expected image channels to be the same as the kernel batches for conv_transpose3d but got %s and %s"
+                         % (tuple(x5.shape), tuple(w5.shape)))
+    if any(o3pad[i] < 0 or o3pad[i] >= s3[i] for i in range(3)):
+        raise ValueError("conv_transpose3d: output_padding must be at least 0 and smaller than the stride")
+    k3 = tuple(w5.shape[-3:])
+    out3 = tuple((x5.shape[2 + i] - 1) * s3[i] - 2 * p3[i] + d3[i] * (k3[i] - 1) + 1 + o3pad[i] for i in range(3))
+    cout = w5.shape[1] * groups
+    return k3, out3, cout
+
+
+def conv_transpose3d(x, w, stride=1, padding=0, output_padding=0, dilation=1, groups=1):
+    """functional::conv_transpose3d: x [B, Cin, Di, Hi, Wi], w [Cin, Cout/groups, kd, kh, kw] -> [B, Cout, Do, Ho, Wo],
+    evaluated as the image gradient of the convolution with the same kernel."""
+    x5, w5, s3, p3, d3 = _conv3d_setup(x, w, stride, padding, dilation, groups, "conv3d transpose")
+    k3, out3, cout = _transpose3_geom(x5, w5, s3, p3, _triple(output_padding), d3, groups)
+    bsz, cin = x5.shape[:2]
+    geom = _geom3(bsz, cout, out3, cin, groups, k3, s3, p3, d3)
+    code = dtype_code(x)
+    ws = torch.empty(max(1, lib().ntb200_conv3d_workspace_bytes(code, ctypes.byref(geom))), dtype=torch.uint8, device=x.device)
+    out = torch.empty((bsz, cout) + out3, dtype=x.dtype, device=x.device)
+    check(lib().ntb200_conv3d_backward_image(code, x5.data_ptr(), w5.data_ptr(), out.data_ptr(), ws.data_ptr(), ctypes.byref(geom),
+                                             _stream()))
+    return out
+
+
+def conv_transpose3d_backward(x, w, grad, stride=1, padding=0, output_padding=0, dilation=1, groups=1):
+    x5, w5, s3, p3, d3 = _conv3d_setup(x, w, stride, padding, dilation, groups, "conv3d transpose")
+    _require_cuda(grad)
+    k3, out3, cout = _transpose3_geom(x5, w5, s3, p3, _triple(output_padding), d3, groups)
+    bsz, cin = x5.shape[:2]
+    geom = _geom3(bsz, cout, out3, cin, groups, k3, s3, p3, d3)
+    code = dtype_code(x)
+    g = grad.contiguous()
+    ws = torch.empty(max(1, lib().ntb200_conv3d_workspace_bytes(code, ctypes.byref(geom))), dtype=torch.uint8, device=x.device)
+    dx, dw_ = torch.empty_like(x5), torch.empty_like(w5)
+    check(lib().ntb200_conv3d(code, g.data_ptr(), w5.data_ptr(), dx.data_ptr(), ws.data_ptr(), ctypes.byref(geom), _stream()))
+    check(lib().ntb200_conv3d_backward_kernel(code, g.data_ptr(), x5.data_ptr(), dw_.data_ptr(), ws.data_ptr(), 0,
+                                              ctypes.byref(geom), _stream()))
+    return dx.reshape(x.shape), dw_.reshape(w.shape)
+
+
 def relu(x):
     _require_cuda(x)
     x = x.contiguous()

@@ -265,6 +265,116 @@ def conv_transpose2d_backward(x, w, grad, stride=1, padding=0, output_padding=0,
     return dx, dw
 
 
+def _triple(v):
+    return tuple(v) if isinstance(v, (tuple, list)) else (v, v, v)
+
+
+def unfold3d(x, kernel_size, dilation=1, padding=0, stride=1):
+    """unfold3d (colim_transform.cpp:661-696, cpu/unfold3d.cpp): col[b][((c*kd+kz)*kh+ky)*kw+kx][(z*Ho+y)*Wo+x] =
+    x[b][c][z*sd-pd+kz*dd][y*sh-ph+ky*dh][x*sw-pw+kx*dw], zero outside the image."""
+    kd, kh, kw = _triple(kernel_size)
+    dd, dh, dw = _triple(dilation)
+    pd, ph, pw = _triple(padding)
+    sd, sh, sw = _triple(stride)
+    b, c, D, H, W = x.shape
+    od, oh, ow = conv_out_size(D, kd, sd, pd, dd), conv_out_size(H, kh, sh, ph, dh), conv_out_size(W, kw, sw, pw, dw)
+    xp = np.zeros((b, c, D + 2 * pd, H + 2 * ph, W + 2 * pw), dtype=x.dtype)
+    xp[:, :, pd:pd + D, ph:ph + H, pw:pw + W] = x
+    col = np.empty((b, c, kd, kh, kw, od, oh, ow), dtype=x.dtype)
+    for kz in range(kd):
+        for ky in range(kh):
+            for kx in range(kw):
+                col[:, :, kz, ky, kx] = xp[:, :, kz * dd:kz * dd + (od - 1) * sd + 1:sd, ky * dh:ky * dh + (oh - 1) * sh + 1:sh,
+                                           kx * dw:kx * dw + (ow - 1) * sw + 1:sw]
+    return col.reshape(b, c * kd * kh * kw, od * oh * ow)
+
+
+def unfold3d_backward(dcol, out_dhw, kernel_size, dilation=1, padding=0, stride=1):
+    """unfold3d_backward (colim_transform.cpp:698-800): the adjoint of unfold3d, accumulated in Float32."""
+    kd, kh, kw = _triple(kernel_size)
+    dd, dh, dw = _triple(dilation)
+    pd, ph, pw = _triple(padding)
+    sd, sh, sw = _triple(stride)
+    D, H, W = out_dhw
+    b = dcol.shape[0]
+    c = dcol.shape[1] // (kd * kh * kw)
+    od, oh, ow = conv_out_size(D, kd, sd, pd, dd), conv_out_size(H, kh, sh, ph, dh), conv_out_size(W, kw, sw, pw, dw)
+    d8 = dcol.reshape(b, c, kd, kh, kw, od, oh, ow).astype(np.float32)
+    xp = np.zeros((b, c, D + 2 * pd, H + 2 * ph, W + 2 * pw), dtype=np.float32)
+    for kz in range(kd):
+        for ky in range(kh):
+            for kx in range(kw):
+                xp[:, :, kz * dd:kz * dd + (od - 1) * sd + 1:sd, ky * dh:ky * dh + (oh - 1) * sh + 1:sh,
+                   kx * dw:kx * dw + (ow - 1) * sw + 1:sw] += d8[:, :, kz, ky, kx]
+    return xp[:, :, pd:pd + D, ph:ph + H, pw:pw + W].astype(dcol.dtype)
+
+
+def conv3d(x, w, stride=1, padding=0, dilation=1, groups=1, threads=None):
+    """functional::conv3d (conv.cpp:122-174): unfold3d, then matmult(col, w2d, true, true) and the row/col swap,
+    group by group."""
+    x5 = x.reshape((-1,) + x.shape[-4:])
+    k3 = w.shape[-3:]
+    s3, p3, d3 = _triple(stride), _triple(padding), _triple(dilation)
+    o3 = tuple(conv_out_size(x5.shape[2 + i], k3[i], s3[i], p3[i], d3[i]) for i in range(3))
+    col = unfold3d(x5, k3, d3, p3, s3)
+    cout = w.shape[0]
+    ckg, coutg = col.shape[1] // groups, cout // groups
+    outs = []
+    for g in range(groups):
+        col_g = np.ascontiguousarray(col[:, g * ckg:(g + 1) * ckg])
+        w2d = np.ascontiguousarray(w[g * coutg:(g + 1) * coutg].reshape(coutg, -1))
+        outs.append(matmult(col_g, w2d, True, True, threads=threads).transpose(0, 2, 1))
+    return np.ascontiguousarray(np.concatenate(outs, axis=1)).reshape((x5.shape[0], cout) + o3)
+
+
+def conv3d_backward(x, w, grad, stride=1, padding=0, dilation=1, groups=1, threads=None):
+    """conv_dimage / conv_dkernel, dim == 3 (conv.cpp:347-376, 472-500), Float32."""
+    x5 = x.reshape((-1,) + x.shape[-4:])
+    k3 = w.shape[-3:]
+    s3, p3, d3 = _triple(stride), _triple(padding), _triple(dilation)
+    bsz, cout = x5.shape[0], w.shape[0]
+    col = unfold3d(x5, k3, d3, p3, s3)
+    g3 = np.ascontiguousarray(grad.reshape(bsz, cout, -1))
+    ckg, coutg = col.shape[1] // groups, cout // groups
+    dcol = np.empty_like(col)
+    dw = np.empty((cout, ckg), dtype=np.float32)
+    for g in range(groups):
+        w2d = np.ascontiguousarray(w[g * coutg:(g + 1) * coutg].reshape(coutg, -1))
+        gg = np.ascontiguousarray(g3[:, g * coutg:(g + 1) * coutg])
+        dcol[:, g * ckg:(g + 1) * ckg] = matmult(w2d, gg, True, False, threads=threads)
+        col_g = np.ascontiguousarray(col[:, g * ckg:(g + 1) * ckg])
+        dw[g * coutg:(g + 1) * coutg] = matmult(gg, col_g, False, True, threads=threads).sum(axis=0, dtype=np.float32)
+    dx = unfold3d_backward(dcol, x5.shape[-3:], k3, d3, p3, s3).reshape(x.shape)
+    return dx, dw.reshape(w.shape)
+
+
+def conv_transpose3d(x, w, stride=1, padding=0, output_padding=0, dilation=1, groups=1, threads=None):
+    """functional::conv_transpose3d (conv.cpp:674-735): dilate the input by the stride, pad the end by
+    output_padding, convolve with stride 1 and padding d*(k-1) - p by the channel-swapped, flipped kernel."""
+    s3, p3, o3, d3 = _triple(stride), _triple(padding), _triple(output_padding), _triple(dilation)
+    x5 = x.reshape((-1,) + x.shape[-4:])
+    bsz, cin = x5.shape[:2]
+    k3 = w.shape[-3:]
+    ext = tuple((x5.shape[2 + i] - 1) * s3[i] + 1 + o3[i] for i in range(3))
+    xd = np.zeros((bsz, cin) + ext, dtype=x.dtype)
+    xd[:, :, :(x5.shape[2] - 1) * s3[0] + 1:s3[0], :(x5.shape[3] - 1) * s3[1] + 1:s3[1], :(x5.shape[4] - 1) * s3[2] + 1:s3[2]] = x5
+    cing, coutg = cin // groups, w.shape[1]
+    wf = np.empty((coutg * groups, cing) + tuple(k3), dtype=w.dtype)
+    for g in range(groups):
+        blk = w[g * cing:(g + 1) * cing]
+        wf[g * coutg:(g + 1) * coutg] = blk.transpose(1, 0, 2, 3, 4)[:, :, ::-1, ::-1, ::-1]
+    pad = tuple(d3[i] * (k3[i] - 1) - p3[i] for i in range(3))
+    return conv3d(xd, np.ascontiguousarray(wf), 1, pad, d3, groups=groups, threads=threads)
+
+
+def conv_transpose3d_backward(x, w, grad, stride=1, padding=0, output_padding=0, dilation=1, groups=1, threads=None):
+    x5 = x.reshape((-1,) + x.shape[-4:])
+    g5 = grad.reshape((x5.shape[0], -1) + grad.shape[-3:])
+    dx = conv3d(g5, w, stride, padding, dilation, groups=groups, threads=threads).reshape(x.shape)
+    _, dw = conv3d_backward(g5, w, x5, stride, padding, dilation, groups=groups, threads=threads)
+    return dx, dw
+
+
 def conv1d(x, w, stride=1, padding=0, dilation=1, groups=1, threads=None):
     """functional::conv1d (conv.cpp:13-67): unfold1d + matmult, i.e. the one-row case of conv2d."""
     x3 = x.reshape((-1,) + x.shape[-2:])

@@ -25,6 +25,11 @@ NAMES = (
        for s in ("input", "weight", "output", "grad", "xgrad", "wgrad")
        for e in ("", "_batched", "_grouped", "_grouped_batched")]
     + ["conv_transpose1d_%s_grouped_bigger.npy" % s for s in ("input", "weight", "output", "grad", "xgrad", "wgrad")]
+    # conv3d and conv_transpose3d (conv_autograd_test.cpp:376-500, 848-960); the largest sets stay in the reference tree
+    + ["conv3d_%s%s.npy" % (s, e) for s in ("input", "weight", "output", "grad", "xgrad", "wgrad")
+       for e in ("", "_grouped", "_grouped_batched")]
+    + ["conv_transpose3d_%s%s.npy" % (s, e) for s in ("input", "weight", "output", "grad", "xgrad", "wgrad")
+       for e in ("", "_grouped_batched")]
 )
 
 

@@ -1,5 +1,5 @@
-"""Grouped conv2d, conv1d and the transposed convolutions against the reference's own golden vectors
-(tests/src/conv_autograd_test.cpp:126-240 conv1d, :284-360 grouped conv2d, :556-835 conv_transpose1d/2d; the
+"""Grouped conv2d, conv1d, conv3d and the transposed convolutions against the reference's own golden vectors
+(tests/src/conv_autograd_test.cpp:126-240 conv1d, :284-360 grouped conv2d, :376-500 conv3d, :556-960 conv_transpose1d/2d/3d; the
 vectors were generated there with PyTorch and are compared with allclose).  CPU tests pin the oracle; GPU tests
 run the same cases through the library."""
 import os
@@ -26,6 +26,8 @@ CONV1D = [("", dict(stride=1, padding=1)), ("_batched", dict(stride=1, padding=1
 TRANSPOSE1D = [("", dict(stride=2, output_padding=1)), ("_batched", dict(stride=2, output_padding=1, padding=1)),
                ("_grouped", dict(stride=1, groups=2, padding=1)), ("_grouped_batched", dict(stride=1, groups=2, padding=1)),
                ("_grouped_bigger", dict(stride=1, groups=5, padding=1))]
+CONV3D = [("", dict(stride=1, padding=1)), ("_grouped", dict(stride=1, groups=2)), ("_grouped_batched", dict(stride=1, groups=2))]
+TRANSPOSE3D = [("", dict(stride=2, output_padding=1)), ("_grouped_batched", dict(stride=1, groups=2, padding=1))]
 TRANSPOSE2D = [("", dict(stride=2, output_padding=1)), ("_batched", dict(stride=2, output_padding=1, padding=1)),
                ("_grouped", dict(stride=1, groups=5, padding=1)), ("_grouped_batched", dict(stride=1, groups=2, padding=1))]
 
@@ -54,6 +56,22 @@ def test_oracle_conv_transpose2d(oracle, ext, kw):
     x, w, out, grad, xg, wg = family("conv_transpose2d", ext)
     assert close(oracle.conv_transpose2d(x, w, **kw), out)
     dx, dw = oracle.conv_transpose2d_backward(x, w, grad, **kw)
+    assert close(dx, xg) and close(dw, wg)
+
+
+@pytest.mark.parametrize("ext,kw", CONV3D)
+def test_oracle_conv3d(oracle, ext, kw):
+    x, w, out, grad, xg, wg = family("conv3d", ext)
+    assert close(oracle.conv3d(x, w, **kw), out)
+    dx, dw = oracle.conv3d_backward(x, w, grad, **kw)
+    assert close(dx, xg) and close(dw, wg)
+
+
+@pytest.mark.parametrize("ext,kw", TRANSPOSE3D)
+def test_oracle_conv_transpose3d(oracle, ext, kw):
+    x, w, out, grad, xg, wg = family("conv_transpose3d", ext)
+    assert close(oracle.conv_transpose3d(x, w, **kw), out)
+    dx, dw = oracle.conv_transpose3d_backward(x, w, grad, **kw)
     assert close(dx, xg) and close(dw, wg)
 
 
@@ -102,6 +120,52 @@ def test_conv_transpose2d_golden(api, ext, kw):
     assert close(host(api.conv_transpose2d(dev(x), dev(w), **kw)), out)
     dx, dw = api.conv_transpose2d_backward(dev(x), dev(w), dev(grad), **kw)
     assert close(host(dx), xg) and close(host(dw), wg)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("ext,kw", CONV3D)
+def test_conv3d_golden(api, ext, kw):
+    from gpu_util import dev, host
+    x, w, out, grad, xg, wg = family("conv3d", ext)
+    assert close(host(api.conv3d(dev(x), dev(w), **kw)), out)
+    dx, dw = api.conv3d_backward(dev(x), dev(w), dev(grad), **kw)
+    assert close(host(dx), xg) and close(host(dw), wg)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("ext,kw", TRANSPOSE3D)
+def test_conv_transpose3d_golden(api, ext, kw):
+    from gpu_util import dev, host
+    x, w, out, grad, xg, wg = family("conv_transpose3d", ext)
+    assert close(host(api.conv_transpose3d(dev(x), dev(w), **kw)), out)
+    dx, dw = api.conv_transpose3d_backward(dev(x), dev(w), dev(grad), **kw)
+    assert close(host(dx), xg) and close(host(dw), wg)
+
+
+@pytest.mark.gpu
+def test_unfold3d_bit_exact_and_conv3d_f16(api, oracle):
+    """ntb200_im2col3d is a pure gather (bit-exact for any geometry); Float16 conv3d goes to the tensor cores."""
+    import ctypes
+    import torch
+    from gpu_util import dev, host, normal
+    from neurotensor_b200 import _lib
+    rng = np.random.default_rng(37)
+    x = normal(rng, (2, 5, 7, 9, 8), np.float32)
+    k3, s3, p3, d3 = (2, 3, 2), (2, 1, 2), (1, 2, 0), (1, 2, 2)
+    exp = oracle.unfold3d(x, k3, d3, p3, s3)
+    geom = api._geom3(2, 5, (7, 9, 8), 1, 1, k3, s3, p3, d3)
+    col = torch.empty(exp.shape, dtype=torch.float32, device="cuda")
+    xd = dev(x)
+    _lib.check(_lib.lib().ntb200_im2col3d(_lib.F32, xd.data_ptr(), col.data_ptr(), ctypes.byref(geom), None))
+    assert np.array_equal(host(col), exp)
+    back = torch.empty_like(xd)
+    _lib.check(_lib.lib().ntb200_col2im3d(_lib.F32, col.data_ptr(), back.data_ptr(), ctypes.byref(geom), None))
+    assert np.allclose(host(back), oracle.unfold3d_backward(exp, (7, 9, 8), k3, d3, p3, s3), rtol=1e-5, atol=1e-6)
+    xh = normal(rng, (2, 16, 6, 8, 8), np.float16)
+    wh = normal(rng, (24, 16, 3, 3, 3), np.float16, (1.0 / (16 * 27)) ** 0.5)
+    got = host(api.conv3d(dev(xh), dev(wh), stride=1, padding=1))
+    expc = oracle.conv3d(xh.astype(np.float32), wh.astype(np.float32), 1, 1, 1)
+    assert oracle.rel_fro(got, expc) <= 2e-3
 
 
 @pytest.mark.gpu
