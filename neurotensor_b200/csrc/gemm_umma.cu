@@ -14,7 +14,9 @@
 //                                publishes the accumulator (`tmem_full`)
 //   warps 2..5  epilogue       - tcgen05.ld the accumulator (each warp owns a 32-lane quadrant), add bias /
 //                                previous C, apply the optional ReLU outputs, convert, store (also into peer GPUs'
-//                                copies of C when asked); then hand the accumulator back
+//                                copies of C when asked); then hand the accumulator back.  In the pair kernel the
+//                                8- and 16-bit outputs leave through a swizzled shared-memory staging buffer and
+//                                TMA stores of 128-byte row segments instead of per-thread global stores
 // (the Float32 split kernels run 8 epilogue warps that keep running sums in registers).
 // Two accumulators (2 x 256 columns of TMEM) let the epilogue of tile i overlap the main loop of tile i+1.
 //
