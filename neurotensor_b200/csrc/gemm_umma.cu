@@ -1058,6 +1058,7 @@ const char* operands_stageable(const GemmArgs& g) {
     if (g.dtype == NTB200_F32) {  // operands are copied (split) first, so any strides do
         if (g.m > (int64_t(1) << 30) || g.n > (int64_t(1) << 30) || g.k > (int64_t(1) << 30)) return "extent too large";
         if (g.a_rs < 0 || g.a_cs < 0 || g.a_bs < 0 || g.b_rs < 0 || g.b_cs < 0 || g.b_bs < 0) return "negative stride";
+        if ((g.m + 31) / 32 + (g.n + 31) / 32 > 65535) return "operands too tall for the split pass";
         return nullptr;
     }
     const int es = int(dtype_size(g.dtype));
@@ -1160,12 +1161,27 @@ int launch_pair_instance(const Maps& m, const UmmaParams& p, cudaStream_t stream
 // x = hi + lo with hi = x rounded to TF32 (10 explicit mantissa bits) and lo = x - hi (exact in fp32), so that
 // a.b = a_hi.b_hi + a_hi.b_lo + a_lo.b_hi + O(2^-21 |a||b|).  The pre-pass writes hi and lo as dense K-major
 // matrices [batch][rows][k_padded], whatever the strides of the source view, so the GEMM only ever sees one layout.
-__global__ void split_tf32_kernel(const float* __restrict__ src, float* __restrict__ hi, float* __restrict__ lo,
-                                  long long rows, long long cols, long long cols_padded, long long sbs, long long srs,
-                                  long long scs) {
+struct SplitJob {
+    const float* src;
+    float* hi;
+    float* lo;
+    long long rows, batch, sbs, srs, scs;
+    int row_blocks;   // ceil(rows / 32)
+};
+
+// One launch splits both operands: blockIdx.y below a.row_blocks works on A, the rest on B.
+__global__ void split_tf32_kernel(SplitJob ja, SplitJob jb, long long cols, long long cols_padded) {
+    const bool second = int(blockIdx.y) >= ja.row_blocks;
+    const SplitJob& job = second ? jb : ja;
+    if ((long long)blockIdx.z >= job.batch) return;
+    const float* __restrict__ src = job.src;
+    float* __restrict__ hi = job.hi;
+    float* __restrict__ lo = job.lo;
+    const long long rows = job.rows, sbs = job.sbs, srs = job.srs, scs = job.scs;
+    const int by = int(blockIdx.y) - (second ? ja.row_blocks : 0);
     __shared__ float tile[32][33];
     const long long b = blockIdx.z;
-    const long long r0 = (long long)blockIdx.y * 32, c0 = (long long)blockIdx.x * 32;
+    const long long r0 = (long long)by * 32, c0 = (long long)blockIdx.x * 32;
     const float* s = src + b * sbs;
     const bool read_along_cols = (scs == 1 || srs != 1);
     if (read_along_cols) {
@@ -1361,12 +1377,16 @@ int launch_f32_split(const GemmArgs& g, cudaStream_t stream) {
     float* b_hi = a_lo + a_elems;
     float* b_lo = b_hi + b_elems;
     const dim3 block(32, 8);
-    split_tf32_kernel<<<dim3(unsigned((kp + 31) / 32), unsigned((g.m + 31) / 32), unsigned(a_batch)), block, 0, stream>>>(
-        static_cast<const float*>(g.a), a_hi, a_lo, g.m, g.k, kp, g.a_bs, g.a_rs, g.a_cs);
     // B is logically [k, n]; its copy is [n][k]: rows = n (source stride b_cs), columns = k (source stride b_rs)
-    split_tf32_kernel<<<dim3(unsigned((kp + 31) / 32), unsigned((g.n + 31) / 32), unsigned(b_batch)), block, 0, stream>>>(
-        static_cast<const float*>(g.b), b_hi, b_lo, g.n, g.k, kp, g.b_bs, g.b_cs, g.b_rs);
-    count_launch(2);
+    const SplitJob ja{static_cast<const float*>(g.a), a_hi, a_lo, g.m, a_batch, g.a_bs, g.a_rs, g.a_cs, int((g.m + 31) / 32)};
+    const SplitJob jb{static_cast<const float*>(g.b), b_hi, b_lo, g.n, b_batch, g.b_bs, g.b_cs, g.b_rs, int((g.n + 31) / 32)};
+    if (int64_t(ja.row_blocks) + jb.row_blocks > 65535) {
+        cudaFreeAsync(scratch, stream);
+        return fail(NTB200_ERR_UNSUPPORTED, "tcgen05 route: operand too tall for the Float32 split pass");
+    }
+    split_tf32_kernel<<<dim3(unsigned((kp + 31) / 32), unsigned(ja.row_blocks + jb.row_blocks), unsigned(std::max(a_batch, b_batch))),
+                        block, 0, stream>>>(ja, jb, g.k, kp);
+    count_launch();
     cudaError_t e = cudaGetLastError();
     int rc = NTB200_OK;
     if (e != cudaSuccess) {
