@@ -3,7 +3,7 @@
     python -m neurotensor_b200.bench_configs [--steps K] [--cpu] [--only c1,c3i8,...]
 
 Rows: c1 (Float32 1024^3), c2 (batched Float16 64x2048^3, transposed-view B), c3i8 (Int8 4096x8192x4096),
-c3i32 (Int32 2048^3), c4 (BFloat16 MLP 8192 x 4096->16384->4096: forward + backward step), c5 (Float16 conv2d
+c3i32 (Int32 2048^3), t8192 (Float16 / BFloat16 8192^3), c4 (BFloat16 MLP 8192 x 4096->16384->4096: forward + backward step), c5 (Float16 conv2d
 [32,256,56,56] * [256,256,3,3]), sweepN (Float32 N^3).  Inputs are seeded synthetic tensors of the stated shapes
 and distributions, resident on the device; time is CUDA events over K launches after 3 warm-ups.  `--cpu` also
 times the CPU oracle on a bounded sub-problem of each row (test infrastructure, scaled linearly, stated per row).
@@ -103,6 +103,16 @@ def main():
         emit("c2 batched Float16 64x2048^3, B transposed view", s, 64 * 2 * 2048 ** 3, 3 * 64 * 2048 ** 2 * 2, "tensor", l, "",
              cpu_time(lambda o: o.matmult(an, bn, False, True), 64, "1 of 64 items, scaled x64"))
         del a, bs, c
+
+    if want("t8192"):
+        # the north-star target shape: one 8192^3 GEMM on 16-bit inputs (32 x 32 pair tiles, 13.8 waves)
+        for name, dt in (("Float16", torch.float16), ("BFloat16", torch.bfloat16)):
+            a, b = randn(gen, (8192, 8192), dt, 0.1), randn(gen, (8192, 8192), dt, 0.1)
+            c = torch.empty((8192, 8192), dtype=dt, device="cuda")
+            s, l = timed(lambda: api.gemm(a, b, c), max(5, args.steps // 2))
+            emit("target %s 8192^3" % name, s, 2 * 8192 ** 3, 3 * 8192 ** 2 * 2, "tensor", l,
+                 "nominal dense peak 2250 TFLOP/s: %.1f %% of it" % (2 * 8192 ** 3 / s / 1e12 / 2250 * 100))
+            del a, b, c
 
     if want("c3i8"):
         a = torch.randint(-8, 8, (4096, 8192), generator=gen, device="cuda", dtype=torch.int8)
