@@ -3,7 +3,7 @@
     python -m neurotensor_b200.bench_configs [--steps K] [--cpu] [--only c1,c3i8,...]
 
 Rows: c1 (Float32 1024^3), c2 (batched Float16 64x2048^3, transposed-view B), c3i8 (Int8 4096x8192x4096),
-c3i32 (Int32 2048^3), t8192 (Float16 / BFloat16 8192^3), c4 (BFloat16 MLP 8192 x 4096->16384->4096: forward + backward step), c5 (Float16 conv2d
+c3i32 (Int32 2048^3), c3i16 (Int16 4096^3), t8192 (Float16 / BFloat16 8192^3), c4 (BFloat16 MLP 8192 x 4096->16384->4096: forward + backward step), c5 (Float16 conv2d
 [32,256,56,56] * [256,256,3,3]), sweepN (Float32 N^3).  Inputs are seeded synthetic tensors of the stated shapes
 and distributions, resident on the device; time is CUDA events over K launches after 3 warm-ups.  `--cpu` also
 times the CPU oracle on a bounded sub-problem of each row (test infrastructure, scaled linearly, stated per row).
@@ -142,6 +142,17 @@ def main():
         an, bn = a.cpu().numpy(), b.cpu().numpy()
         emit("c3 Int32 2048^3 (wrap)", s, 2 * 2048 ** 3, 3 * 4 * 2048 ** 2, "imad", l, "peak = IMAD at half the FFMA rate; the default route is 8-bit limb products on tensor cores",
              cpu_time(lambda o: o.matmult(an, bn), 1, "full problem"))
+
+    if want("c3i16"):
+        a = torch.randint(-30000, 30001, (4096, 4096), generator=gen, device="cuda", dtype=torch.int16)
+        b = torch.randint(-30000, 30001, (4096, 4096), generator=gen, device="cuda", dtype=torch.int16)
+        c = torch.empty((4096, 4096), dtype=torch.int16, device="cuda")
+        s, l = timed(lambda: api.gemm(a, b, c), args.steps)
+        emit("Int16 4096^3 (wrap) on 8-bit limb products", s, 2 * 4096 ** 3, 3 * 2 * 4096 ** 2, "tensor_i8", l,
+             "three 8-bit GEMM depths per int16 product: the tensor cores do 3x the listed ops")
+        s, l = timed(lambda: api.gemm(a, b, c, route=_lib.ROUTE_SIMT), max(3, args.steps // 4))
+        emit("Int16 4096^3 (wrap) on the CUDA-core route", s, 2 * 4096 ** 3, 3 * 2 * 4096 ** 2, "imad", l)
+        del a, b, c
 
     if want("c4"):
         B, D, H = 8192, 4096, 16384

@@ -102,7 +102,7 @@ int run_gemm(GemmArgs g, int route, cudaStream_t stream) {
     // Float32: the exact one-chain CUDA-core kernel for small problems (and always with NTB200_FP32_MODE=ffma);
     // three-TF32-product tensor-core kernel (within 1e-5 relative Frobenius error) once the problem is large
     // enough to pay for the split pass.
-    if ((g.dtype == NTB200_I32 || g.dtype == NTB200_U32) && route == NTB200_ROUTE_AUTO &&
+    if ((g.dtype == NTB200_I32 || g.dtype == NTB200_U32 || g.dtype == NTB200_I16 || g.dtype == NTB200_U16) && route == NTB200_ROUTE_AUTO &&
         double(g.m) * double(g.n) * double(g.k) * double(g.batch) < 6.0e7)
         route = NTB200_ROUTE_SIMT;   // ten limb GEMMs and a split pass only pay off on large problems
     if (g.dtype == NTB200_F32 && route == NTB200_ROUTE_AUTO) {

@@ -48,7 +48,7 @@ constexpr int kThreads = 192;
 constexpr int kThreadsSplit = 320;  // Float32 split kernels: 8 epilogue warps hold the running sums in registers
 constexpr int kTmemCols = 512;
 
-enum OutKind : int { kOutF16 = 0, kOutBF16 = 1, kOutI8 = 2, kOutF32 = 3, kOutU32 = 4 };
+enum OutKind : int { kOutF16 = 0, kOutBF16 = 1, kOutI8 = 2, kOutF32 = 3, kOutU32 = 4, kOutU16 = 5 };
 
 struct UmmaParams {
     int m, n, k, batch;
@@ -74,7 +74,7 @@ struct UmmaParams {
     long long peer_offset[7];   // byte distance from this GPU's C to peer i's C (same layout)
     // Fused elementwise neighbours (16-bit outputs): tensors laid out exactly like C, given as byte offsets from C.
     int has_relu_out, has_mask;
-    int shift;                   // kOutU32: the s32 accumulator is shifted left by this much before it is added
+    int shift;                   // kOutU32 / kOutU16: the s32 accumulator is shifted left by this much before it is added
     int tma_store;               // pair kernel, 16-bit outputs: tiles leave through shared memory and TMA stores
     int peers_relu;              // TMA-store epilogue: the peer copies receive the fused ReLU output instead of C
     long long relu_out_offset;   // second output: max(C, 0)
@@ -181,7 +181,7 @@ __device__ __forceinline__ void store_running(const UmmaParams& p, const float (
 // and the accumulator's first column.  Executed by whole warps (tcgen05.ld is warp-collective).
 template <int BN>
 __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, uint32_t tmem_acc, int b, int row, int n0) {
-    const int es = (p.out_kind == kOutI8) ? 1 : ((p.out_kind == kOutF32 || p.out_kind == kOutU32) ? 4 : 2);
+    const int es = (p.out_kind == kOutI8) ? 1 : ((p.out_kind == kOutF32 || p.out_kind == kOutU32) ? 4 : 2);   // kOutU16: 2
     const bool row_ok = row < p.m;
     uint8_t* c_row = static_cast<uint8_t*>(p.c) + ((long long)b * p.c_bs + (long long)row * p.c_rs) * es;
 #pragma unroll 1
@@ -252,6 +252,39 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, uint32_t tmem
 #pragma unroll
                 for (int j = 0; j < 32; ++j)
                     if (col0 + j < p.n) dst[j] = p.accumulate ? dst[j] + v[j] : v[j];
+            }
+        } else if (p.out_kind == kOutU16) {
+            // one limb product of a 16-bit integer GEMM: (acc << shift) joins C modulo 2^16
+            uint16_t* dst = reinterpret_cast<uint16_t*>(c_row) + col0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] <<= p.shift;
+            if (p.bias) {
+                const uint16_t* bias = static_cast<const uint16_t*>(p.bias) + (long long)b * p.bias_bs + (long long)row * p.bias_rs;
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (col0 + j < p.n) v[j] += bias[(long long)(col0 + j) * p.bias_cs];
+            }
+            if (full_chunk && p.c_vec_ok) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    uint32_t w[4];
+                    if (p.accumulate) {
+                        const uint4 old = *reinterpret_cast<const uint4*>(dst + 8 * q);
+                        const uint32_t ow[4] = {old.x, old.y, old.z, old.w};
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            v[8 * q + 2 * j] += ow[j] & 0xffffu;
+                            v[8 * q + 2 * j + 1] += ow[j] >> 16;
+                        }
+                    }
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) w[j] = (v[8 * q + 2 * j] & 0xffffu) | (v[8 * q + 2 * j + 1] << 16);
+                    *reinterpret_cast<uint4*>(dst + 8 * q) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (col0 + j < p.n) dst[j] = uint16_t(p.accumulate ? dst[j] + v[j] : v[j]);
             }
         } else if (p.out_kind == kOutF32) {
             float f[32];
@@ -1042,7 +1075,7 @@ const int g_split_chunk_blocks = [] {
 
 bool dtype_on_tensor_cores(int dtype) {
     return dtype == NTB200_F16 || dtype == NTB200_BF16 || dtype == NTB200_I8 || dtype == NTB200_U8 || dtype == NTB200_F32 ||
-           dtype == NTB200_I32 || dtype == NTB200_U32;
+           dtype == NTB200_I32 || dtype == NTB200_U32 || dtype == NTB200_I16 || dtype == NTB200_U16;
 }
 
 // Cheap structural test (no driver call): can both operands be staged?
@@ -1050,7 +1083,7 @@ const char* operands_stageable(const GemmArgs& g) {
     if (!dtype_on_tensor_cores(g.dtype)) return "dtype has no tensor-core kernel";
     if (g.a_ptrs || g.b_ptrs || g.c_ptrs) return "pointer-table batches run on the CUDA-core route";
     if (g.m <= 0 || g.n <= 0 || g.k <= 0 || g.batch <= 0) return "empty problem";
-    if (g.dtype == NTB200_I32 || g.dtype == NTB200_U32) {   // limb planes are copies too; each limb GEMM must be exact in s32
+    if (g.dtype == NTB200_I32 || g.dtype == NTB200_U32 || g.dtype == NTB200_I16 || g.dtype == NTB200_U16) {   // limb planes are copies too; each limb GEMM must be exact in s32
         if (g.m > (int64_t(1) << 30) || g.n > (int64_t(1) << 30)) return "extent too large";
         if (g.a_rs < 0 || g.a_cs < 0 || g.a_bs < 0 || g.b_rs < 0 || g.b_cs < 0 || g.b_bs < 0) return "negative stride";
         return nullptr;
@@ -1412,12 +1445,13 @@ int launch_f32_split(const GemmArgs& g, cudaStream_t stream) {
 // (nt/mp/simde_traits/simde_traits_avx2.h:444-485) by construction.
 constexpr int64_t kLimbChunkK = 8192;
 
-__global__ void split_limbs_kernel(const uint32_t* __restrict__ src, uint8_t* __restrict__ limbs, long long rows, long long cols,
+template <typename Src, int kLimbs>
+__global__ void split_limbs_kernel(const Src* __restrict__ src, uint8_t* __restrict__ limbs, long long rows, long long cols,
                                    long long kc, long long nchunks, int reverse, long long sbs, long long srs, long long scs) {
     __shared__ uint32_t tile[32][33];
     const long long b = blockIdx.z;
     const long long r0 = (long long)blockIdx.y * 32, c0 = (long long)blockIdx.x * 32;
-    const uint32_t* s = src + b * sbs;
+    const Src* s = src + b * sbs;
     if (scs == 1 || srs != 1) {
         for (int j = threadIdx.y; j < 32; j += 8) {
             const long long r = r0 + j, c = c0 + threadIdx.x;
@@ -1430,22 +1464,24 @@ __global__ void split_limbs_kernel(const uint32_t* __restrict__ src, uint8_t* __
         }
     }
     __syncthreads();
-    const long long row_bytes = nchunks * 4 * kc;
+    const long long row_bytes = nchunks * kLimbs * kc;
     for (int j = threadIdx.y; j < 32; j += 8) {
         const long long r = r0 + j, c = c0 + threadIdx.x;
         if (r < rows && c < nchunks * kc) {
             const uint32_t x = tile[j][threadIdx.x];   // zero beyond `cols`: the padding columns contribute nothing
-            uint8_t* row = limbs + (b * rows + r) * row_bytes + (c / kc) * 4 * kc + (c % kc);
+            uint8_t* row = limbs + (b * rows + r) * row_bytes + (c / kc) * kLimbs * kc + (c % kc);
 #pragma unroll
-            for (int l = 0; l < 4; ++l) row[(reverse ? 3 - l : l) * kc] = uint8_t(x >> (8 * l));
+            for (int l = 0; l < kLimbs; ++l) row[(reverse ? kLimbs - 1 - l : l) * kc] = uint8_t(x >> (8 * l));
         }
     }
 }
 
-int launch_i32_limbs(const GemmArgs& g, cudaStream_t stream) {
+// kLimbs = 4: Int32 / UInt32 (four GEMMs per K chunk); kLimbs = 2: Int16 / UInt16 (two), the same scheme modulo 2^16.
+template <typename Src, int kLimbs>
+int launch_int_limbs(const GemmArgs& g, cudaStream_t stream) {
     const int64_t kp = (g.k + 15) & ~int64_t(15);
     const int64_t kc = std::min(kp, kLimbChunkK), nchunks = (kp + kc - 1) / kc;
-    const int64_t row_bytes = nchunks * 4 * kc;
+    const int64_t row_bytes = nchunks * kLimbs * kc;
     const int64_t a_batch = (g.batch > 1 && g.a_bs != 0) ? g.batch : 1;
     const int64_t b_batch = (g.batch > 1 && g.b_bs != 0) ? g.batch : 1;
     if (a_batch > 65535 || b_batch > 65535) return fail(NTB200_ERR_UNSUPPORTED, "tcgen05 route: batch too large for the limb split pass");
@@ -1457,23 +1493,24 @@ int launch_i32_limbs(const GemmArgs& g, cudaStream_t stream) {
     uint8_t* b_limbs = scratch + a_bytes;
     const dim3 block(32, 8);
     const unsigned gx = unsigned((nchunks * kc + 31) / 32);
-    split_limbs_kernel<<<dim3(gx, unsigned((g.m + 31) / 32), unsigned(a_batch)), block, 0, stream>>>(
-        static_cast<const uint32_t*>(g.a), a_limbs, g.m, g.k, kc, nchunks, 0, g.a_bs, g.a_rs, g.a_cs);
-    split_limbs_kernel<<<dim3(gx, unsigned((g.n + 31) / 32), unsigned(b_batch)), block, 0, stream>>>(
-        static_cast<const uint32_t*>(g.b), b_limbs, g.n, g.k, kc, nchunks, 1, g.b_bs, g.b_cs, g.b_rs);
+    split_limbs_kernel<Src, kLimbs><<<dim3(gx, unsigned((g.m + 31) / 32), unsigned(a_batch)), block, 0, stream>>>(
+        static_cast<const Src*>(g.a), a_limbs, g.m, g.k, kc, nchunks, 0, g.a_bs, g.a_rs, g.a_cs);
+    split_limbs_kernel<Src, kLimbs><<<dim3(gx, unsigned((g.n + 31) / 32), unsigned(b_batch)), block, 0, stream>>>(
+        static_cast<const Src*>(g.b), b_limbs, g.n, g.k, kc, nchunks, 1, g.b_bs, g.b_cs, g.b_rs);
     count_launch(2);
     cudaError_t e = cudaGetLastError();
     int rc = e == cudaSuccess ? NTB200_OK : cuda_fail(e, "split_limbs_kernel");
     bool first = true;
     for (int64_t ch = 0; ch < nchunks && rc == NTB200_OK; ++ch)
-        for (int sh = 0; sh <= 3 && rc == NTB200_OK; ++sh) {
-            Planned pl{1, CU_TENSOR_MAP_DATA_TYPE_UINT8, MmaKind::i8, kOutU32, 2u, 0u, false, "umma_i32_limbs"};
+        for (int sh = 0; sh < kLimbs && rc == NTB200_OK; ++sh) {
+            Planned pl{1, CU_TENSOR_MAP_DATA_TYPE_UINT8, MmaKind::i8, kLimbs == 4 ? kOutU32 : kOutU16, 2u, 0u, false,
+                       kLimbs == 4 ? "umma_i32_limbs" : "umma_i16_limbs"};
             pl.shift = 8 * sh;
             GemmArgs part = g;
             part.k = (sh + 1) * kc;                         // planes 0..sh of A against planes sh..0 of B
             if (!first) { part.accumulate = 1; part.bias = nullptr; }
-            const Side sa{a_limbs + ch * 4 * kc, row_bytes, 1, a_batch > 1 ? g.m * row_bytes : 0};
-            const Side sb{b_limbs + ch * 4 * kc + (3 - sh) * kc, row_bytes, 1, b_batch > 1 ? g.n * row_bytes : 0};
+            const Side sa{a_limbs + ch * kLimbs * kc, row_bytes, 1, a_batch > 1 ? g.m * row_bytes : 0};
+            const Side sb{b_limbs + ch * kLimbs * kc + (kLimbs - 1 - sh) * kc, row_bytes, 1, b_batch > 1 ? g.n * row_bytes : 0};
             rc = launch_planned(part, pl, sa, sb, nullptr, nullptr, stream);
             first = false;
         }
@@ -1492,7 +1529,8 @@ bool umma_supported(const GemmArgs& g, const char** why) {
 int launch_umma_gemm(const GemmArgs& g, cudaStream_t stream) {
     if (const char* w = operands_stageable(g)) return fail(NTB200_ERR_UNSUPPORTED, "tcgen05 route: %s", w);
     if (g.dtype == NTB200_F32) return launch_f32_split(g, stream);
-    if (g.dtype == NTB200_I32 || g.dtype == NTB200_U32) return launch_i32_limbs(g, stream);
+    if (g.dtype == NTB200_I32 || g.dtype == NTB200_U32) return launch_int_limbs<uint32_t, 4>(g, stream);
+    if (g.dtype == NTB200_I16 || g.dtype == NTB200_U16) return launch_int_limbs<uint16_t, 2>(g, stream);
     const int es = int(dtype_size(g.dtype));
     const bool is_i8 = es == 1;
     Planned pl;

@@ -313,6 +313,41 @@ def test_int32_tensor_route_accumulate_bias_batch(api, oracle, L):
     assert np.array_equal(host(out), exp)
 
 
+@pytest.mark.parametrize("ta,tb", FLAGS)
+@pytest.mark.parametrize("m,k,n,dtype", [(136, 72, 64, np.int16), (256, 520, 384, np.uint16), (1024, 9000, 1280, np.int16)])
+def test_int16_on_tensor_cores_bit_exact(api, oracle, L, ta, tb, m, k, n, dtype):
+    """Int16 / UInt16 as three products of 8-bit limbs on kind::i8 (two GEMMs per 8192-wide K chunk): full-range
+    operands, wrap modulo 2^16, all transpose combinations; K = 9000 crosses a chunk boundary."""
+    rng = np.random.default_rng(73 + m)
+    info = np.iinfo(dtype)
+    a, b = operands(rng, m, k, n, ta, tb, dtype, ints=(info.min, info.max))
+    # numpy has no 16-bit cuda tensors for uint16 in torch: travel as int16 bit patterns
+    da, db = torch.from_numpy(a.view(np.int16)).cuda(), torch.from_numpy(b.view(np.int16)).cuda()
+    got = host(api.matmult(da, db, ta, tb, route=L.ROUTE_TENSOR)).view(dtype)
+    assert L.last_route() == "umma_i16_limbs"
+    assert np.array_equal(got, oracle.matmult(a.view(np.int16), b.view(np.int16), ta, tb).view(dtype))
+
+
+def test_int16_tensor_route_accumulate_bias_batch(api, oracle, L):
+    rng = np.random.default_rng(79)
+    a, w = integers(rng, (3, 200, 96), np.int16, -32768, 32767), integers(rng, (96, 136), np.int16, -32768, 32767)
+    bias, c0 = integers(rng, (136,), np.int16, -32768, 32767), integers(rng, (3, 200, 136), np.int16, -32768, 32767)
+    got = host(api.linear(dev(a), dev(w), dev(bias), route=L.ROUTE_TENSOR))
+    assert L.last_route() == "umma_i16_limbs"
+    assert np.array_equal(got, oracle.linear(a, w, bias))
+    out = dev(c0)
+    api.matmult(dev(a), dev(w), out=out, route=L.ROUTE_TENSOR)
+    exp = c0.copy()
+    for i in range(3):
+        oracle.matmult_into(a[i], w, exp[i])
+    assert np.array_equal(host(out), exp)
+    # large problems take the limb route by themselves
+    big_a, big_b = integers(rng, (512, 1024), np.int16, -32768, 32767), integers(rng, (1024, 512), np.int16, -32768, 32767)
+    got = host(api.matmult(dev(big_a), dev(big_b)))
+    assert L.last_route() == "umma_i16_limbs"
+    assert np.array_equal(got, oracle.matmult(big_a, big_b))
+
+
 def test_pinned_host_buffers_from_the_library(api, oracle, L):
     """ntb200_host_alloc / ntb200_host_register give page-locked host memory for ntb200_matmult_host."""
     import ctypes
