@@ -293,6 +293,45 @@ __global__ void column_sum_kernel(const T* __restrict__ g, T* __restrict__ out, 
     }
 }
 
+// Column sums of a 16-bit matrix with 16-byte loads: a warp covers 256 columns of one row (512 contiguous bytes),
+// the block's 8 row lanes walk its slab of rows, and every (column block, row slab) leaves one fp32 partial row;
+// column_sum_final_kernel adds the slabs in order and rounds once.
+template <class T>
+__global__ void __launch_bounds__(256)
+column_sum_partial_kernel(const T* __restrict__ g, float* __restrict__ partial, long long rows, long long cols, long long rows_per_slab) {
+    __shared__ float red[8][256 + 8];
+    const long long c0 = ((long long)blockIdx.x * 32 + threadIdx.x) * 8;
+    const long long r_begin = (long long)blockIdx.y * rows_per_slab, r_end = min(rows, r_begin + rows_per_slab);
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (c0 < cols) {
+        for (long long r = r_begin + threadIdx.y; r < r_end; r += 8) {
+            const uint4 v = *reinterpret_cast<const uint4*>(g + r * cols + c0);
+            const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] += F<T>::ld(e[j]);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) red[threadIdx.y][threadIdx.x * 8 + j] = acc[j];
+    __syncthreads();
+    const int t = threadIdx.y * 32 + threadIdx.x;   // 256 threads, one column of the block each
+    const long long c = (long long)blockIdx.x * 256 + t;
+    if (c < cols) {
+        float s = 0.f;
+#pragma unroll
+        for (int y = 0; y < 8; ++y) s += red[y][t];
+        partial[(long long)blockIdx.y * cols + c] = s;
+    }
+}
+template <class T>
+__global__ void column_sum_final_kernel(const float* __restrict__ partial, T* __restrict__ out, int slabs, long long cols) {
+    const long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= cols) return;
+    float s = 0.f;
+    for (int i = 0; i < slabs; ++i) s += partial[(long long)i * cols + c];
+    out[c] = F<T>::st(s);
+}
+
 template <class T>
 __global__ void add_inplace_kernel(T* __restrict__ y, const T* __restrict__ x, long long n) {
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
@@ -466,6 +505,33 @@ int ntb200_column_sum(int dtype, const void* grad, void* out, int64_t rows, int6
     if (cols == 0) return NTB200_OK;
     if (!grad || !out) return fail(NTB200_ERR_INVALID_ARG, "column_sum: null pointer");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // Large 16-bit matrices (bias gradients of wide layers): two passes with 16-byte loads and the rows spread
+    // over enough blocks to fill the GPU.
+    if (dtype_size(dtype) == 2 && cols % 8 == 0 && reinterpret_cast<uintptr_t>(grad) % 16 == 0 && rows * cols >= (int64_t(1) << 22)) {
+        const int64_t col_blocks = (cols + 255) / 256;
+        int64_t slabs = std::max<int64_t>(1, std::min<int64_t>((rows + 63) / 64, (int64_t(sm_count()) * 8 + col_blocks - 1) / col_blocks));
+        slabs = std::min<int64_t>(slabs, 65535);
+        const int64_t rows_per_slab = (rows + slabs - 1) / slabs;
+        slabs = (rows + rows_per_slab - 1) / rows_per_slab;
+        float* partial = nullptr;
+        keep_pool_memory();
+        NTB200_CUDA(cudaMallocAsync(reinterpret_cast<void**>(&partial), size_t(slabs) * size_t(cols) * sizeof(float), s));
+        const dim3 grid(static_cast<unsigned>(col_blocks), static_cast<unsigned>(slabs), 1);
+        const dim3 block(32, 8, 1);
+        cudaError_t e = cudaSuccess;
+        if (dtype == NTB200_F16) {
+            column_sum_partial_kernel<__half><<<grid, block, 0, s>>>((const __half*)grad, partial, rows, cols, rows_per_slab);
+            column_sum_final_kernel<__half><<<unsigned((cols + 255) / 256), 256, 0, s>>>(partial, (__half*)out, int(slabs), cols);
+        } else {
+            column_sum_partial_kernel<__nv_bfloat16><<<grid, block, 0, s>>>((const __nv_bfloat16*)grad, partial, rows, cols, rows_per_slab);
+            column_sum_final_kernel<__nv_bfloat16><<<unsigned((cols + 255) / 256), 256, 0, s>>>(partial, (__nv_bfloat16*)out, int(slabs), cols);
+        }
+        e = cudaGetLastError();
+        cudaFreeAsync(partial, s);
+        count_launch(2);
+        if (e != cudaSuccess) return cuda_fail(e, "column_sum kernels");
+        return NTB200_OK;
+    }
     const dim3 block(32, 32);
     const unsigned blocks = unsigned((cols + 31) / 32);
     NTB200_FLOAT_SWITCH(dtype, (column_sum_kernel<T><<<blocks, block, 0, s>>>((const T*)grad, (T*)out, rows, cols)));
