@@ -311,6 +311,13 @@ int ntb200_add_inplace(int dtype, void* y, const void* x, int64_t n, void* strea
 int ntb200_sgd_step(int dtype, void* param, const void* grad, int64_t n, double learning_rate, void* stream);
 int ntb200_adam_step(int dtype, void* param, const void* grad, void* m, void* v, int64_t n, double learning_rate,
                      double beta1, double beta2, double epsilon, int64_t t, void* stream);
+/* layers::Conv2D adds its bias [C, 1, 1] to the convolution's output as a separate elementwise operation
+ * (nt/nn/layers/Conv2D.cpp:34-44): x[b][c][i] += bias[c] in place, and the bias gradient is the sum of the output
+ * gradient over the batch and the pixels, out[c] = sum_b sum_i grad[b][c][i].  F32, F16, BF16. */
+int ntb200_bias_add_channels(int dtype, void* x, const void* bias, int64_t batch, int64_t channels, int64_t inner,
+                             void* stream);
+int ntb200_sum_channels(int dtype, const void* grad, void* out, int64_t batch, int64_t channels, int64_t inner,
+                        void* stream);
 /* dst[rows, cols] (contiguous) = src viewed with the given element strides: Tensor::contiguous(). */
 int ntb200_copy_strided_2d(int dtype, void* dst, const void* src, int64_t batch, int64_t rows, int64_t cols,
                            int64_t src_batch_stride, int64_t src_row_stride, int64_t src_col_stride, void* stream);

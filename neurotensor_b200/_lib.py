@@ -99,6 +99,8 @@ SIGNATURES = {
     "ntb200_mse": (_ci, [_ci, _vp, _vp, _vp, _vp, _i64, _vp]),
     "ntb200_column_sum": (_ci, [_ci, _vp, _vp, _i64, _i64, _vp]),
     "ntb200_add_inplace": (_ci, [_ci, _vp, _vp, _i64, _vp]),
+    "ntb200_bias_add_channels": (_ci, [_ci, _vp, _vp, _i64, _i64, _i64, _vp]),
+    "ntb200_sum_channels": (_ci, [_ci, _vp, _vp, _i64, _i64, _i64, _vp]),
     "ntb200_sgd_step": (_ci, [_ci, _vp, _vp, _i64, ctypes.c_double, _vp]),
     "ntb200_adam_step": (_ci, [_ci, _vp, _vp, _vp, _vp, _i64] + [ctypes.c_double] * 4 + [_i64, _vp]),
     "ntb200_copy_strided_2d": (_ci, [_ci, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _vp]),

@@ -603,6 +603,29 @@ def relu_backward(x, grad_out):
     return gi
 
 
+def bias_add_channels(x, bias):
+    """layers::Conv2D's `outp + Bias` (Conv2D.cpp:43): x [B, C, ...] += bias [C] (or [C, 1, 1]) in place."""
+    _require_cuda(x, bias)
+    if x.dim() < 2 or not x.is_contiguous() or bias.numel() != x.shape[1] or bias.dtype != x.dtype:
+        raise ValueError("bias_add_channels: x must be contiguous [B, C, ...] and bias must hold C values of x's dtype")
+    inner = x.numel() // max(1, x.shape[0] * x.shape[1])
+    b = bias.contiguous()
+    check(lib().ntb200_bias_add_channels(dtype_code(x), x.data_ptr(), b.data_ptr(), x.shape[0], x.shape[1], inner, _stream()))
+    return x
+
+
+def sum_channels(grad):
+    """Bias gradient of layers::Conv2D: sum of grad [B, C, ...] over the batch and the trailing dims -> [C]."""
+    _require_cuda(grad)
+    if grad.dim() < 2:
+        raise ValueError("sum_channels: expected [B, C, ...]")
+    g = grad.contiguous()
+    out = torch.empty((g.shape[1],), dtype=g.dtype, device=g.device)
+    inner = g.numel() // max(1, g.shape[0] * g.shape[1])
+    check(lib().ntb200_sum_channels(dtype_code(g), g.data_ptr(), out.data_ptr(), g.shape[0], g.shape[1], inner, _stream()))
+    return out
+
+
 def sgd_step(param, grad, lr=0.01):
     """optimizers::SGD::step for one parameter (Optimizers.cpp:8-17): param -= clip(grad, -10, 10) * lr, in place."""
     _require_cuda(param, grad)

@@ -332,6 +332,49 @@ __global__ void column_sum_final_kernel(const float* __restrict__ partial, T* __
     out[c] = F<T>::st(s);
 }
 
+// x[b][c][i] += bias[c] in place: the `outp + Bias` of layers::Conv2D with Bias shaped [C, 1, 1].
+template <class T>
+__global__ void bias_add_channels_kernel(T* __restrict__ x, const T* __restrict__ bias, long long total, long long channels,
+                                         long long inner) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long c = (i / inner) % channels;
+        x[i] = F<T>::st(F<T>::ld(x[i]) + F<T>::ld(bias[c]));
+    }
+}
+// Eight 16-bit elements per thread when a channel's run is a multiple of 8 elements (one channel per vector).
+template <class T>
+__global__ void bias_add_channels_vec_kernel(uint4* __restrict__ x, const T* __restrict__ bias, long long nvec, long long channels,
+                                             long long inner_vec) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+        const float b = F<T>::ld(bias[(i / inner_vec) % channels]);
+        uint4 v = x[i];
+        T* e = reinterpret_cast<T*>(&v);
+#pragma unroll
+        for (int j = 0; j < int(16 / sizeof(T)); ++j) e[j] = F<T>::st(F<T>::ld(e[j]) + b);
+        x[i] = v;
+    }
+}
+// out[c] = sum over b and i of g[b][c][i] (the bias gradient of layers::Conv2D): one block per channel, fp32 sums.
+template <class T>
+__global__ void __launch_bounds__(256)
+sum_channels_kernel(const T* __restrict__ g, T* __restrict__ out, long long batch, long long channels, long long inner) {
+    const long long c = blockIdx.x;
+    float acc = 0.f;
+    for (long long b = 0; b < batch; ++b) {
+        const T* row = g + (b * channels + c) * inner;
+        for (long long i = threadIdx.x; i < inner; i += blockDim.x) acc += F<T>::ld(row[i]);
+    }
+    __shared__ float red[8];
+    for (int off = 16; off; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float s = 0.f;
+        for (int w = 0; w < 8; ++w) s += red[w];
+        out[c] = F<T>::st(s);
+    }
+}
+
 template <class T>
 __global__ void add_inplace_kernel(T* __restrict__ y, const T* __restrict__ x, long long n) {
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
@@ -588,6 +631,35 @@ int ntb200_copy_strided_2d(int dtype, void* dst, const void* src, int64_t batch,
         case 8: copy_strided_kernel<unsigned long long><<<grid, block, 0, s>>>((unsigned long long*)dst, (const unsigned long long*)src, rows, cols, src_batch_stride, src_row_stride, src_col_stride); break;
         default: return fail(NTB200_ERR_UNSUPPORTED, "copy_strided_2d: unknown dtype %d", dtype);
     }
+    count_launch();
+    NTB200_CUDA(cudaGetLastError());
+    return NTB200_OK;
+}
+
+int ntb200_bias_add_channels(int dtype, void* x, const void* bias, int64_t batch, int64_t channels, int64_t inner, void* stream) {
+    if (batch < 0 || channels <= 0 || inner < 0) return fail(NTB200_ERR_INVALID_ARG, "bias_add_channels: bad extent");
+    const int64_t total = batch * channels * inner;
+    if (total == 0) return NTB200_OK;
+    if (!x || !bias) return fail(NTB200_ERR_INVALID_ARG, "bias_add_channels: null pointer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int64_t per = 16 / int64_t(dtype_size(dtype) ? dtype_size(dtype) : 16);
+    if ((dtype == NTB200_F32 || dtype == NTB200_F16 || dtype == NTB200_BF16) && inner % per == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0) {
+        const int64_t nvec = total / per;
+        NTB200_FLOAT_SWITCH(dtype, (bias_add_channels_vec_kernel<T><<<grid_for(nvec, 256), 256, 0, s>>>((uint4*)x, (const T*)bias, nvec, channels, inner / per)));
+    } else {
+        NTB200_FLOAT_SWITCH(dtype, (bias_add_channels_kernel<T><<<grid_for(total, 1024), 256, 0, s>>>((T*)x, (const T*)bias, total, channels, inner)));
+    }
+    count_launch();
+    NTB200_CUDA(cudaGetLastError());
+    return NTB200_OK;
+}
+
+int ntb200_sum_channels(int dtype, const void* grad, void* out, int64_t batch, int64_t channels, int64_t inner, void* stream) {
+    if (batch < 0 || channels <= 0 || inner < 0) return fail(NTB200_ERR_INVALID_ARG, "sum_channels: bad extent");
+    if (!grad || !out) return fail(NTB200_ERR_INVALID_ARG, "sum_channels: null pointer");
+    if (channels > 2147483647) return fail(NTB200_ERR_INVALID_ARG, "sum_channels: too many channels");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    NTB200_FLOAT_SWITCH(dtype, (sum_channels_kernel<T><<<unsigned(channels), 256, 0, s>>>((const T*)grad, (T*)out, batch, channels, inner)));
     count_launch();
     NTB200_CUDA(cudaGetLastError());
     return NTB200_OK;

@@ -246,6 +246,46 @@ class Linear {
     TensorGrad forward(const TensorGrad& x) { return functional::linear(x, Weight, Bias); }
     TensorGrad operator()(const TensorGrad& x) { return forward(x); }
 };
+// Conv2D (nn/layers/Conv2D.cpp:11-44): Weight [out, in / groups, kh, kw], Bias [out, 1, 1]; forward is
+// conv2d(x, Weight, stride, padding, dilation, groups) + Bias, the bias being a separate elementwise step whose
+// gradient is the sum of the output gradient over the batch and the pixels.
+class Conv2D {
+   public:
+    bool use_bias;
+    int64_t groups, in_channels, out_channels;
+    functional::ConvArgs args;
+    TensorGrad Weight, Bias;
+    Conv2D(int64_t in_channels, int64_t out_channels, int64_t kh, int64_t kw, functional::ConvArgs args = {}, int64_t groups = 1,
+           bool use_bias = true, DType dt = DType::Float32, uint64_t seed = 0)
+        : use_bias(use_bias), groups(groups), in_channels(in_channels), out_channels(out_channels), args(args),
+          Weight(randn_seeded({out_channels, in_channels / (groups > 0 ? groups : 1), kh, kw}, dt, seed * 2 + 1,
+                              1.0 / std::sqrt(double(in_channels / (groups > 0 ? groups : 1) * kh * kw)))),
+          Bias(use_bias ? TensorGrad(randn_seeded({out_channels, 1, 1}, dt, seed * 2 + 2, 0.01)) : TensorGrad()) {
+        utils::throw_exception(groups >= 1 && out_channels % groups == 0, "Expected in channels to be divisible by groups");
+        utils::throw_exception(in_channels % groups == 0, "Expected in channels to be divisible by groups");
+        Weight.detach().set_mutability(false);
+        if (use_bias) Bias.detach().set_mutability(false);
+    }
+    TensorGrad forward(const TensorGrad& x) {
+        utils::throw_exception(x.shape()[-3] == in_channels, "Expected input tensor to have channel size of ", in_channels, " but got ",
+                               x.shape());
+        TensorGrad outp = functional::conv2d(x, Weight, args, groups);
+        if (!use_bias) return outp;
+        Tensor y = outp.detach().clone();
+        const int64_t B = y.shape()[0], C = y.shape()[1], inner = y.numel() / (B * C);
+        utils::check(ntb200_bias_add_channels(dtype_code(y.dtype()), y.data_ptr(), Bias.detach().data_ptr(), B, C, inner, nullptr));
+        return TensorGrad::make_result(y, {outp.node(), Bias.node()}, [B, C, inner](const Tensor& g, GraphParents& parents) {
+            if (parents[0]->requires_grad) parents[0]->accumulate_gradient(g);
+            if (parents[1]->requires_grad) {
+                Tensor gc = g.contiguous();
+                Tensor db({C, 1, 1}, g.dtype(), DeviceType::CUDA);
+                utils::check(ntb200_sum_channels(dtype_code(g.dtype()), gc.data_ptr(), db.data_ptr(), B, C, inner, nullptr));
+                parents[1]->accumulate_gradient(db);
+            }
+        });
+    }
+    TensorGrad operator()(const TensorGrad& x) { return forward(x); }
+};
 }  // namespace layers
 
 namespace optimizers {

@@ -185,6 +185,36 @@ int main(int argc, char** argv) {
         REQUIRE(fn::allclose(o3, fn::from_numpy(gold + "conv_transpose2d_output_grouped.npy"), 1e-4, 1e-5));
     });
 
+    run_test("layers::Conv2D: convolution plus per-channel bias, and the three gradients", [] {
+        fn::ConvArgs a;
+        a.ph = a.pw = 1;
+        nt::layers::Conv2D conv(6, 8, 3, 3, a, 2, true, DType::Float32, 21);
+        REQUIRE(conv.Weight.shape() == SizeRef({8, 3, 3, 3}) && conv.Bias.shape() == SizeRef({8, 1, 1}));
+        Tensor xt = nt::randn_seeded({2, 6, 5, 7}, DType::Float32, 22);
+        TensorGrad x(xt, true);
+        TensorGrad y = conv(x);
+        REQUIRE(y.shape() == SizeRef({2, 8, 5, 7}));
+        // forward = conv2d without bias + bias per channel
+        Tensor plain = fn::conv2d(xt, conv.Weight.detach(), a, 2);
+        auto yv = y.detach().to_vector<float>(), pv = plain.to_vector<float>(), bv = conv.Bias.detach().to_vector<float>();
+        bool fwd = true;
+        for (size_t i = 0; i < yv.size(); ++i) fwd = fwd && (yv[i] == pv[i] + bv[(i / 35) % 8]);
+        REQUIRE(fwd);
+        Tensor g = nt::randn_seeded({2, 8, 5, 7}, DType::Float32, 23);
+        y.backward(g);
+        auto gv = g.to_vector<float>(), db = conv.Bias.grad().to_vector<float>();
+        REQUIRE(conv.Bias.grad().shape() == SizeRef({8, 1, 1}));
+        bool bias_ok = true;
+        for (int c = 0; c < 8; ++c) {
+            double s = 0;
+            for (int b = 0; b < 2; ++b)
+                for (int i = 0; i < 35; ++i) s += gv[(b * 8 + c) * 35 + i];
+            bias_ok = bias_ok && std::fabs(db[c] - s) <= 1e-4 * (1.0 + std::fabs(s));
+        }
+        REQUIRE(bias_ok);
+        REQUIRE(conv.Weight.grad().shape() == SizeRef({8, 3, 3, 3}) && x.grad().shape() == SizeRef({2, 6, 5, 7}));
+    });
+
     run_test("unfold2d (golden)", [&] {
         Tensor x = fn::from_numpy(gold + "unfold_input.npy");
         fn::ConvArgs args;

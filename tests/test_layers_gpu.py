@@ -382,3 +382,31 @@ def test_conv2d_backward_kernel_accumulates_and_rejects_integers(api):
                                           6, 3, 3, 1, 1, 1, 1, 1, 1, None)
     assert rc == _lib.ERR_UNSUPPORTED
     assert "Float32" in lib.ntb200_last_error_string().decode()
+
+
+@pytest.mark.parametrize("dt", ["f32", "f16", "bf16"])
+def test_conv2d_layer_bias_and_its_gradient(api, oracle, dt):
+    """layers::Conv2D adds Bias [C, 1, 1] after the convolution (Conv2D.cpp:43); its gradient sums the output
+    gradient over batch and pixels."""
+    rng = np.random.default_rng(83)
+    for shape in ((3, 8, 5, 7), (2, 64, 4, 16), (1, 5, 3, 3)):          # scalar path, 16-byte vector path, tiny
+        x32 = normal(rng, shape, np.float32)
+        b32 = normal(rng, (shape[1],), np.float32)
+        if dt == "bf16":
+            x, b = dev(oracle.bf16_round(x32), bf16=True), dev(oracle.bf16_round(b32), bf16=True)
+            xw, bw = oracle.bf16_widen(oracle.bf16_round(x32)), oracle.bf16_widen(oracle.bf16_round(b32))
+            narrow = lambda v: oracle.bf16_widen(oracle.bf16_round(v))
+            got = lambda t: oracle.bf16_widen(host(t))
+        else:
+            np_dt = np.float32 if dt == "f32" else np.float16
+            x, b = dev(x32.astype(np_dt)), dev(b32.astype(np_dt))
+            xw, bw = x32.astype(np_dt).astype(np.float32), b32.astype(np_dt).astype(np.float32)
+            narrow = lambda v: v.astype(np_dt).astype(np.float32)
+            got = lambda t: host(t).astype(np.float32)
+        sums = api.sum_channels(x)
+        exp_sums = xw.sum(axis=(0, 2, 3), dtype=np.float64)
+        assert np.allclose(got(sums), exp_sums, rtol=2e-2 if dt != "f32" else 1e-5, atol=5e-2 if dt != "f32" else 1e-4)
+        api.bias_add_channels(x, b.reshape(-1, 1, 1))
+        assert np.array_equal(got(x), narrow(xw + bw[None, :, None, None]))     # one rounding per element: exact
+    with pytest.raises(ValueError):
+        api.bias_add_channels(x, b[:2])
