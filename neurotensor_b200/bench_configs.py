@@ -3,7 +3,7 @@
     python -m neurotensor_b200.bench_configs [--steps K] [--cpu] [--only c1,c3i8,...]
 
 Rows: c1 (Float32 1024^3), c2 (batched Float16 64x2048^3, transposed-view B), c3i8 (Int8 4096x8192x4096),
-c3i32 (Int32 2048^3), c3i16 (Int16 4096^3), t8192 (Float16 / BFloat16 8192^3), c4 (BFloat16 MLP 8192 x 4096->16384->4096: forward + backward step), c5 (Float16 conv2d
+c3i32 (Int32 2048^3), c3i16 (Int16 4096^3), t8192 (Float16 / BFloat16 8192^3), skinny (1 / 16 / 128 rows x 8192 x 8192), c4 (BFloat16 MLP 8192 x 4096->16384->4096: forward + backward step), c5 (Float16 conv2d
 [32,256,56,56] * [256,256,3,3]), sweepN (Float32 N^3).  Inputs are seeded synthetic tensors of the stated shapes
 and distributions, resident on the device; time is CUDA events over K launches after 3 warm-ups.  `--cpu` also
 times the CPU oracle on a bounded sub-problem of each row (test infrastructure, scaled linearly, stated per row).
@@ -113,6 +113,21 @@ def main():
             emit("target %s 8192^3" % name, s, 2 * 8192 ** 3, 3 * 8192 ** 2 * 2, "tensor", l,
                  "nominal dense peak 2250 TFLOP/s: %.1f %% of it" % (2 * 8192 ** 3 / s / 1e12 / 2250 * 100))
             del a, b, c
+
+    if want("skinny"):
+        # memory-bound shapes: few rows against a large weight matrix (the weights are read once from HBM)
+        for m in (1, 16, 128):
+            for name, dt in (("Float16", torch.float16),):
+                a, b = randn(gen, (m, 8192), dt, 0.1), randn(gen, (8192, 8192), dt, 0.1)
+                c = torch.empty((m, 8192), dtype=dt, device="cuda")
+                s, l = timed(lambda: api.gemm(a, b, c), args.steps)
+                emit("skinny %s %dx8192x8192" % (name, m), s, 2 * m * 8192 * 8192, (m * 8192 * 2 + 8192 * 8192) * 2, "hbm", l,
+                     "the 134 MB weight matrix is the traffic; it exceeds L2")
+                bt = b.t().contiguous()
+                s, l = timed(lambda: api.gemm(a, bt, c, transpose_b=True), args.steps)
+                emit("skinny %s %dx8192x8192, weights stored [N, K]" % (name, m), s, 2 * m * 8192 * 8192,
+                     (m * 8192 * 2 + 8192 * 8192) * 2, "hbm", l)
+                del a, b, bt, c
 
     if want("c3i8"):
         a = torch.randint(-8, 8, (4096, 8192), generator=gen, device="cuda", dtype=torch.int8)

@@ -77,6 +77,13 @@ struct UmmaParams {
     int shift;                   // kOutU32 / kOutU16: the s32 accumulator is shifted left by this much before it is added
     int tma_store;               // pair kernel, 16-bit outputs: tiles leave through shared memory and TMA stores
     int peers_relu;              // TMA-store epilogue: the peer copies receive the fused ReLU output instead of C
+    // Stage geometry of the single-CTA kernel (run-time: a problem with few rows stages only those rows of A and
+    // spends the shared memory on more stages instead; the unused rows of the 128-row MMA operand alias whatever follows
+    // in shared memory and only feed accumulator rows that are never stored)
+    int s_stages;
+    uint32_t s_a_bytes;          // bytes reserved per copy of the A tile (a multiple of 1024)
+    uint32_t s_stage_bytes;      // A copies + B copies
+    uint32_t s_stage_tx;         // bytes the TMA loads of one stage deliver
     long long relu_out_offset;   // second output: max(C, 0)
     long long mask_offset;       // input h: the result is zeroed where h < 0 (ReLU backward)
 };
@@ -93,8 +100,9 @@ struct Tile {
     static constexpr uint32_t kBBytes = BN * 128;
     static constexpr uint32_t kStageBytes = (kSplit ? 2u : 1u) * (kABytes + kBBytes);
     static constexpr int kStages = int(196608u / kStageBytes);   // 4 / 6 / 8 stages, half of that when split
-    static constexpr uint32_t kBarrierBytes = 256;
-    static constexpr uint32_t kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;
+    static constexpr int kMaxStages = 24;                        // ring length when few rows of A are staged
+    static constexpr uint32_t kBarrierBytes = 512;               // 2 * kMaxStages + 4 barriers, TMEM slot, abort flag
+    static constexpr uint32_t kRingBudget = 196608u + 16384u;    // shared memory the ring (plus one A tile of slack) may take
 };
 
 __device__ __forceinline__ void raise_timeout(volatile uint32_t* abort_flag, unsigned int where) {
@@ -526,12 +534,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                  const __grid_constant__ CUtensorMap tma_a_lo, const __grid_constant__ CUtensorMap tma_b_lo,
                  const UmmaParams p) {
     using T = Tile<BN, kSplit>;
-    constexpr int kStages = T::kStages;
+    const int kStages = p.s_stages;   // run-time ring length (the name is kept from when it was a constant)
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    uint8_t* bar_gen = smem_gen + kStages * T::kStageBytes;
-    const uint32_t bar_base = smem_base + kStages * T::kStageBytes;
+    // the ring, then one A tile of slack (the last stage's 128-row operand view may run past its trimmed A region)
+    const uint32_t ring_bytes = uint32_t(kStages) * p.s_stage_bytes + T::kABytes;
+    uint8_t* bar_gen = smem_gen + ring_bytes;
+    const uint32_t bar_base = smem_base + ring_bytes;
     // barrier layout (8 bytes each): full[kStages], empty[kStages], tmem_full[2], tmem_empty[2]
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
@@ -582,13 +592,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                         ok = false;
                         break;
                     }
-                    const uint32_t a_dst = smem_base + stage * T::kStageBytes;
-                    const uint32_t b_dst = a_dst + (kSplit ? 2u : 1u) * T::kABytes;
+                    const uint32_t a_dst = smem_base + stage * p.s_stage_bytes;
+                    const uint32_t b_dst = a_dst + (kSplit ? 2u : 1u) * p.s_a_bytes;
                     const uint32_t bar = full_bar(stage);
-                    mbar_expect_tx(bar, T::kStageBytes);
+                    mbar_expect_tx(bar, p.s_stage_tx);
                     const int k0 = kb * p.block_k;
                     if constexpr (kSplit) {  // the split copies are dense and K-major
-                        tma_load_3d(a_dst + T::kABytes, &tma_a_lo, bar, k0, m0, b * p.a_batch_mul);
+                        tma_load_3d(a_dst + p.s_a_bytes, &tma_a_lo, bar, k0, m0, b * p.a_batch_mul);
                         tma_load_3d(b_dst + T::kBBytes, &tma_b_lo, bar, k0, n0, b * p.b_batch_mul);
                     }
                     if (!p.a_mn_major) {
@@ -642,13 +652,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                         break;
                     }
                     tcgen05_fence_after();
-                    const uint32_t a_addr = smem_base + stage * T::kStageBytes;
-                    const uint32_t b_addr = a_addr + (kSplit ? 2u : 1u) * T::kABytes;
+                    const uint32_t a_addr = smem_base + stage * p.s_stage_bytes;
+                    const uint32_t b_addr = a_addr + (kSplit ? 2u : 1u) * p.s_a_bytes;
                     const uint64_t a_desc = make_smem_desc_sw128(a_addr, p.a_lbo, 1024);
                     const uint64_t b_desc = make_smem_desc_sw128(b_addr, p.b_lbo, 1024);
                     if constexpr (kSplit) {
                         // a.b ~ a_lo.b_hi + a_hi.b_lo + a_hi.b_hi, all into the same fp32 accumulator
-                        const uint64_t a_lo = make_smem_desc_sw128(a_addr + T::kABytes, p.a_lbo, 1024);
+                        const uint64_t a_lo = make_smem_desc_sw128(a_addr + p.s_a_bytes, p.a_lbo, 1024);
                         const uint64_t b_lo = make_smem_desc_sw128(b_addr + T::kBBytes, p.b_lbo, 1024);
 #pragma unroll
                         for (int k = 0; k < 4; ++k) {
@@ -1063,6 +1073,9 @@ const char* plan_operand(const void* ptr, int es, CUtensorMapDataType dt, int64_
 // NTB200_NO_PAIR=1 keeps every GEMM on the single-CTA kernel (for A/B measurements).
 const bool g_disable_pair = [] { const char* e = getenv("NTB200_NO_PAIR"); return e && e[0] == '1'; }();
 
+// NTB200_FULL_A_TILE=1 always stages all 128 rows of A in the single-CTA kernel (for A/B measurements).
+const bool g_full_a_tile = [] { const char* e = getenv("NTB200_FULL_A_TILE"); return e && e[0] == '1'; }();
+
 // NTB200_DIRECT_STORES=1 keeps the per-thread global stores in every epilogue (for A/B measurements).
 const bool g_direct_stores = [] { const char* e = getenv("NTB200_DIRECT_STORES"); return e && e[0] == '1'; }();
 
@@ -1139,13 +1152,21 @@ bool plan_store(void* c, CUtensorMapDataType dt, int es_bytes, int64_t m, int64_
 }
 
 template <MmaKind kKind, int BN, bool kSplit>
-int launch_instance(const Maps& m, const UmmaParams& p, int grid, cudaStream_t stream) {
+int launch_instance(const Maps& m, const UmmaParams& p_in, int grid, int a_rows_staged, cudaStream_t stream) {
     using T = Tile<BN, kSplit>;
+    UmmaParams p = p_in;
+    // Stage geometry: all 128 rows of A, or only the `a_rows_staged` (8 / 16 / 32 / 64) the problem has, with the
+    // shared memory saved going into a longer ring (more bytes of B in flight for memory-bound, few-row problems).
+    const uint32_t copies = kSplit ? 2u : 1u;
+    p.s_a_bytes = uint32_t(a_rows_staged) * 128u;
+    p.s_stage_bytes = copies * (p.s_a_bytes + T::kBBytes);
+    p.s_stage_tx = p.s_stage_bytes;
+    p.s_stages = int(std::min<uint32_t>(uint32_t(T::kMaxStages), (T::kRingBudget - T::kABytes) / p.s_stage_bytes));
+    const uint32_t smem = uint32_t(p.s_stages) * p.s_stage_bytes + T::kABytes + T::kBarrierBytes + 1024;
     // the attribute is per device; setting it on every call is cheap
-    cudaError_t e = cudaFuncSetAttribute(umma_gemm_kernel<kKind, BN, kSplit>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         int(T::kSmemBytes));
+    cudaError_t e = cudaFuncSetAttribute(umma_gemm_kernel<kKind, BN, kSplit>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
     if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(umma_gemm_kernel)");
-    umma_gemm_kernel<kKind, BN, kSplit><<<grid, kSplit ? kThreadsSplit : kThreads, T::kSmemBytes, stream>>>(m.a.map, m.b.map, m.a_lo.map, m.b_lo.map, p);
+    umma_gemm_kernel<kKind, BN, kSplit><<<grid, kSplit ? kThreadsSplit : kThreads, smem, stream>>>(m.a.map, m.b.map, m.a_lo.map, m.b_lo.map, p);
     count_launch();
     NTB200_CUDA(cudaGetLastError());
     return NTB200_OK;
@@ -1285,6 +1306,14 @@ int launch_planned(const GemmArgs& g, const Planned& pl, const Side& a, const Si
     Maps maps;
     if (const char* w = plan_operand(a.ptr, es, pl.dt, g.m, g.k, a.mn_stride, a.k_stride, g.batch, a.bs, kBM, block_k, &maps.a))
         return fail(NTB200_ERR_UNSUPPORTED, "tcgen05 route, A: %s", w);
+    // Few rows (one M tile of at most 64 rows, K-major A): stage only those rows and run a longer ring, so that a
+    // memory-bound problem keeps more bytes of B in flight.
+    int a_rows_staged = kBM;
+    if (!use_pair && !pl.split && g.m <= 64 && !maps.a.mn_major && !g_full_a_tile) {
+        a_rows_staged = g.m <= 8 ? 8 : (g.m <= 16 ? 16 : (g.m <= 32 ? 32 : 64));
+        if (const char* w = plan_operand(a.ptr, es, pl.dt, g.m, g.k, a.mn_stride, a.k_stride, g.batch, a.bs, a_rows_staged, block_k, &maps.a))
+            return fail(NTB200_ERR_UNSUPPORTED, "tcgen05 route, A: %s", w);
+    }
     if (const char* w = plan_operand(b.ptr, es, pl.dt, g.n, g.k, b.mn_stride, b.k_stride, g.batch, b.bs, use_pair ? 128 : bn,
                                      block_k, &maps.b))
         return fail(NTB200_ERR_UNSUPPORTED, "tcgen05 route, B: %s", w);
@@ -1378,20 +1407,20 @@ int launch_planned(const GemmArgs& g, const Planned& pl, const Side& a, const Si
     note_route(pl.route);
     if (pl.kind == MmaKind::tf32) {
         if (use_pair) return launch_pair_instance<MmaKind::tf32, true>(maps, p, stream);
-        if (bn == 256) return launch_instance<MmaKind::tf32, 256, true>(maps, p, grid, stream);
-        if (bn == 128) return launch_instance<MmaKind::tf32, 128, true>(maps, p, grid, stream);
-        return launch_instance<MmaKind::tf32, 64, true>(maps, p, grid, stream);
+        if (bn == 256) return launch_instance<MmaKind::tf32, 256, true>(maps, p, grid, a_rows_staged, stream);
+        if (bn == 128) return launch_instance<MmaKind::tf32, 128, true>(maps, p, grid, a_rows_staged, stream);
+        return launch_instance<MmaKind::tf32, 64, true>(maps, p, grid, a_rows_staged, stream);
     }
     if (pl.kind == MmaKind::i8) {
         if (use_pair) return launch_pair_instance<MmaKind::i8, false>(maps, p, stream);
-        if (bn == 256) return launch_instance<MmaKind::i8, 256, false>(maps, p, grid, stream);
-        if (bn == 128) return launch_instance<MmaKind::i8, 128, false>(maps, p, grid, stream);
-        return launch_instance<MmaKind::i8, 64, false>(maps, p, grid, stream);
+        if (bn == 256) return launch_instance<MmaKind::i8, 256, false>(maps, p, grid, a_rows_staged, stream);
+        if (bn == 128) return launch_instance<MmaKind::i8, 128, false>(maps, p, grid, a_rows_staged, stream);
+        return launch_instance<MmaKind::i8, 64, false>(maps, p, grid, a_rows_staged, stream);
     }
     if (use_pair) return launch_pair_instance<MmaKind::f16, false>(maps, p, stream);
-    if (bn == 256) return launch_instance<MmaKind::f16, 256, false>(maps, p, grid, stream);
-    if (bn == 128) return launch_instance<MmaKind::f16, 128, false>(maps, p, grid, stream);
-    return launch_instance<MmaKind::f16, 64, false>(maps, p, grid, stream);
+    if (bn == 256) return launch_instance<MmaKind::f16, 256, false>(maps, p, grid, a_rows_staged, stream);
+    if (bn == 128) return launch_instance<MmaKind::f16, 128, false>(maps, p, grid, a_rows_staged, stream);
+    return launch_instance<MmaKind::f16, 64, false>(maps, p, grid, a_rows_staged, stream);
 }
 
 // Float32: split both operands into dense K-major hi/lo copies in pool scratch, then one GEMM with three TF32
