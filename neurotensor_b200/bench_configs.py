@@ -3,7 +3,7 @@
     python -m neurotensor_b200.bench_configs [--steps K] [--cpu] [--only c1,c3i8,...]
 
 Rows: c1 (Float32 1024^3), c2 (batched Float16 64x2048^3, transposed-view B), c3i8 (Int8 4096x8192x4096),
-c3i32 (Int32 2048^3), c3i16 (Int16 4096^3), t8192 (Float16 / BFloat16 8192^3), skinny (1 / 16 / 128 rows x 8192 x 8192), c4 (BFloat16 MLP 8192 x 4096->16384->4096: forward + backward step), c5 (Float16 conv2d
+c3i32 (Int32 2048^3), c3i16 (Int16 4096^3), t8192 (Float16 / BFloat16 8192^3), skinny (1 / 2 / 16 / 128 rows x 8192 x 8192), c4 (BFloat16 MLP 8192 x 4096->16384->4096: forward + backward step), c5 (Float16 conv2d
 [32,256,56,56] * [256,256,3,3]), sweepN (Float32 N^3).  Inputs are seeded synthetic tensors of the stated shapes
 and distributions, resident on the device; time is CUDA events over K launches after 3 warm-ups.  `--cpu` also
 times the CPU oracle on a bounded sub-problem of each row (test infrastructure, scaled linearly, stated per row).
@@ -116,7 +116,7 @@ def main():
 
     if want("skinny"):
         # memory-bound shapes: few rows against a large weight matrix (the weights are read once from HBM)
-        for m in (1, 16, 128):
+        for m in (1, 2, 16, 128):
             for name, dt in (("Float16", torch.float16),):
                 a, b = randn(gen, (m, 8192), dt, 0.1), randn(gen, (8192, 8192), dt, 0.1)
                 c = torch.empty((m, 8192), dtype=dt, device="cuda")

@@ -109,6 +109,8 @@ int run_gemm(GemmArgs g, int route, cudaStream_t stream) {
         static const bool ffma_only = [] { const char* e = getenv("NTB200_FP32_MODE"); return e && std::strcmp(e, "ffma") == 0; }();
         if (ffma_only || double(g.m) * double(g.n) * double(g.k) * double(g.batch) < 6.0e7) route = NTB200_ROUTE_SIMT;
     }
+    // a handful of rows against a large 16-bit weight matrix is bound by reading the weights once: stream them
+    if (route == NTB200_ROUTE_AUTO && gemv_supported(g)) return launch_gemv(g, stream);
     if (route != NTB200_ROUTE_SIMT) {
         const char* why = nullptr;
         if (umma_supported(g, &why)) {

@@ -78,6 +78,10 @@ size_t conv2d_dkernel_implicit_bytes(const Conv2dShape& s);
 int launch_conv2d_dkernel_implicit(const Conv2dShape& s, const void* x, const void* grad, void* d_kernel,
                                    void* workspace, int accumulate, cudaStream_t stream);
 
+// One or two rows of 16-bit floats against a large weight matrix: CUDA-core kernels that stream the weights.
+bool gemv_supported(const GemmArgs& g);
+int launch_gemv(const GemmArgs& g, cudaStream_t stream);
+
 // CUDA-core route: every dtype, every stride pattern.
 int launch_simt_gemm(const GemmArgs& g, cudaStream_t stream);
 

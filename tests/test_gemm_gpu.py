@@ -348,6 +348,41 @@ def test_int16_tensor_route_accumulate_bias_batch(api, oracle, L):
     assert np.array_equal(got, oracle.matmult(big_a, big_b))
 
 
+@pytest.mark.parametrize("bf16", [False, True])
+@pytest.mark.parametrize("m", [1, 2])
+@pytest.mark.parametrize("weights_nk", [False, True])
+def test_few_rows_stream_the_weights(api, oracle, L, m, weights_nk, bf16):
+    """One or two rows of 16-bit floats against a large weight matrix take the CUDA-core streaming kernels
+    (weights [K, N] or a transposed view of weights [N, K]); fp32 accumulation, one rounding, optional bias and C +=."""
+    rng = np.random.default_rng(89 + m)
+    k, n = 1544, 1160                                   # ragged against the 128 / 2048 K slabs and the column blocks
+    x32, w32 = normal(rng, (m, k), np.float32, 0.5), normal(rng, (k, n), np.float32, 0.5)
+    b32, c32 = normal(rng, (n,), np.float32), normal(rng, (m, n), np.float32)
+    if bf16:
+        enc = lambda v: dev(oracle.bf16_round(v), bf16=True)
+        val = lambda v: oracle.bf16_widen(oracle.bf16_round(v))
+        dec = lambda t: oracle.bf16_widen(host(t))
+    else:
+        enc = lambda v: dev(v.astype(np.float16))
+        val = lambda v: v.astype(np.float16).astype(np.float32)
+        dec = lambda t: host(t).astype(np.float32)
+    x, bias = enc(x32), enc(b32)
+    w = enc(np.ascontiguousarray(w32.T)).t() if weights_nk else enc(w32)    # [K, N] view either way
+    exact = val(x32).astype(np.float64) @ val(w32).astype(np.float64)
+    got = api.linear(x, w, bias)
+    assert L.last_route() == "gemv_simt"
+    assert oracle.rel_fro(dec(got), exact + val(b32)) <= 2e-3
+    out = enc(c32)
+    api.matmult(x, w, out=out)                           # C += x . w
+    assert L.last_route() == "gemv_simt"
+    assert oracle.rel_fro(dec(out), exact + val(c32)) <= 2e-3
+    # an explicit route request is honoured, and three rows are the tensor cores' again
+    api.matmult(x, w, route=L.ROUTE_TENSOR)
+    assert L.last_route() in ("umma_f16", "umma_bf16")
+    api.matmult(x[:1].repeat(3, 1), w)
+    assert L.last_route() in ("umma_f16", "umma_bf16")
+
+
 def test_pinned_host_buffers_from_the_library(api, oracle, L):
     """ntb200_host_alloc / ntb200_host_register give page-locked host memory for ntb200_matmult_host."""
     import ctypes
