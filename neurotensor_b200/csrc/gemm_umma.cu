@@ -1547,6 +1547,90 @@ int launch_int_limbs(const GemmArgs& g, cudaStream_t stream) {
     return rc;
 }
 
+// ---- few-row products of 16-bit floats: K split over the "batch" axis of the same kernel -------------------
+// One elected thread issues every TMA load and every MMA of a CTA, and each of those instructions costs it some
+// 50 to 100 cycles, so a CTA turns over one 64-deep K block in about 550 cycles whatever the tile's width: a
+// [16, 8192] x [8192, 8192] product on 128 tiles of 128 x 64 streams its weights at 15 bytes per clock and SM
+// (2.9 TB/s in all), well under what HBM delivers.  Wider tiles move more bytes per instruction but leave SMs idle
+// when there are few of them.  So the K axis is cut into S slices that run as S "batches" of the ordinary kernel
+// (A and B are strided views, nothing is copied), each writing an fp32 partial tile; a small second kernel adds the
+// S partials in order, then the bias and the previous C, and rounds once, like the one-pass epilogue does.
+const bool g_no_splitk = [] { const char* e = getenv("NTB200_NO_SPLITK"); return e && e[0] == '1'; }();
+
+int pick_k_splits(const GemmArgs& g) {
+    if (g_no_splitk || g.batch != 1 || g.m > kBM || g.relu_out || g.mask_src || g.n_peers > 0) return 1;
+    if (g.k % 64 != 0 || g.n % 4 != 0) return 1;
+    // measured: no gain (or a loss, once the partial tiles weigh against the weights) below 4096 deep or 32 MB of weights
+    if (g.k < 4096 || g.n * g.k < (int64_t(1) << 24)) return 1;
+    const int sms = sm_count();
+    const int64_t tiles = (g.n + 127) / 128;               // 128-wide tiles: 16 KB of B per K block
+    if (tiles >= sms) return 1;
+    int best = 1;
+    for (int s = 2; s <= 16; s *= 2) {
+        if (g.k % (64 * s) != 0 || g.k / s < 512) break;
+        best = s;
+        if (tiles * s >= sms) break;
+    }
+    return best;
+}
+
+template <int kOutKind>
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, int splits, long long slab, int m, int n, uint16_t* c,
+                                     long long c_rs, const uint16_t* bias, long long bias_rs, long long bias_cs, int accumulate) {
+    const int n4 = n >> 2;                                  // n is a multiple of 4
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long long)m * n4) return;
+    const int row = int(idx / n4), col = int(idx % n4) * 4;
+    const float* src = partial + (long long)row * n + col;
+    float4 acc = *reinterpret_cast<const float4*>(src);
+    for (int s = 1; s < splits; ++s) {
+        const float4 v = *reinterpret_cast<const float4*>(src + s * slab);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    float f[4] = {acc.x, acc.y, acc.z, acc.w};
+    uint16_t* dst = c + (long long)row * c_rs + col;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        if (bias) f[j] += to_float_bits16(bias[(long long)row * bias_rs + (long long)(col + j) * bias_cs], kOutKind);
+        if (accumulate) f[j] += to_float_bits16(dst[j], kOutKind);
+        dst[j] = uint16_t(from_float_bits16(f[j], kOutKind));
+    }
+}
+
+int launch_f16_split_k(const GemmArgs& g, const Planned& pl16, int splits, cudaStream_t stream) {
+    const int64_t slab = g.m * g.n, kslice = g.k / splits;
+    float* partial = nullptr;
+    keep_pool_memory();
+    NTB200_CUDA(cudaMallocAsync(reinterpret_cast<void**>(&partial), size_t(splits) * size_t(slab) * sizeof(float), stream));
+    GemmArgs part = g;
+    part.batch = splits;
+    part.k = kslice;
+    part.c = partial; part.c_rs = g.n; part.c_bs = slab;
+    part.bias = nullptr; part.accumulate = 0;
+    Planned pl = pl16;
+    pl.out_kind = kOutF32;
+    pl.route = g.dtype == NTB200_F16 ? "umma_f16_splitk" : "umma_bf16_splitk";
+    const Side a{g.a, g.a_rs, g.a_cs, kslice * g.a_cs}, b{g.b, g.b_cs, g.b_rs, kslice * g.b_rs};
+    int rc = launch_planned(part, pl, a, b, nullptr, nullptr, stream);
+    if (rc == NTB200_OK) {
+        const long long work = (long long)g.m * (g.n / 4);
+        const unsigned blocks = unsigned((work + 255) / 256);
+        uint16_t* c = static_cast<uint16_t*>(g.c);
+        const uint16_t* bias = static_cast<const uint16_t*>(g.bias);
+        if (g.dtype == NTB200_F16)
+            splitk_reduce_kernel<kOutF16><<<blocks, 256, 0, stream>>>(partial, splits, slab, int(g.m), int(g.n), c, g.c_rs, bias,
+                                                                     g.bias_rs, g.bias_cs, g.accumulate);
+        else
+            splitk_reduce_kernel<kOutBF16><<<blocks, 256, 0, stream>>>(partial, splits, slab, int(g.m), int(g.n), c, g.c_rs, bias,
+                                                                      g.bias_rs, g.bias_cs, g.accumulate);
+        count_launch();
+        const cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) rc = cuda_fail(e, "splitk_reduce_kernel");
+    }
+    cudaFreeAsync(partial, stream);
+    return rc;
+}
+
 }  // namespace
 
 bool umma_supported(const GemmArgs& g, const char** why) {
@@ -1572,6 +1656,10 @@ int launch_umma_gemm(const GemmArgs& g, cudaStream_t stream) {
     pl.in_fmt = g.dtype == NTB200_BF16 ? 1u : (g.dtype == NTB200_I8 ? 1u : 0u);
     pl.split = false;
     pl.route = is_i8 ? "umma_i8" : (g.dtype == NTB200_F16 ? "umma_f16" : "umma_bf16");
+    if (!is_i8) {
+        const int splits = pick_k_splits(g);
+        if (splits > 1) return launch_f16_split_k(g, pl, splits, stream);
+    }
     const Side a{g.a, g.a_rs, g.a_cs, g.a_bs}, b{g.b, g.b_cs, g.b_rs, g.b_bs};
     return launch_planned(g, pl, a, b, nullptr, nullptr, stream);
 }

@@ -383,6 +383,43 @@ def test_few_rows_stream_the_weights(api, oracle, L, m, weights_nk, bf16):
     assert L.last_route() in ("umma_f16", "umma_bf16")
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("bf16", [False, True])
+@pytest.mark.parametrize("m,n,k,weights_nk", [(3, 4096, 4096, False), (16, 4100, 4096, True), (100, 4096, 8192, False),
+                                              (128, 8192, 4096, True)])
+def test_few_rows_split_the_k_axis(api, oracle, L, m, n, k, weights_nk, bf16):
+    """Up to 128 rows of 16-bit floats against a deep, large weight matrix: K is cut into slices that run side by side
+    as fp32 partial tiles, and a second kernel adds them, the bias and the previous C and rounds once."""
+    rng = np.random.default_rng(97 + m)
+    x32, w32 = normal(rng, (m, k), np.float32, 0.5), normal(rng, (k, n), np.float32, 0.5)
+    b32, c32 = normal(rng, (n,), np.float32), normal(rng, (m, n), np.float32)
+    if bf16:
+        enc = lambda v: dev(oracle.bf16_round(v), bf16=True)
+        val = lambda v: oracle.bf16_widen(oracle.bf16_round(v))
+        dec = lambda t: oracle.bf16_widen(host(t))
+    else:
+        enc = lambda v: dev(v.astype(np.float16))
+        val = lambda v: v.astype(np.float16).astype(np.float32)
+        dec = lambda t: host(t).astype(np.float32)
+    x, bias = enc(x32), enc(b32)
+    w = enc(np.ascontiguousarray(w32.T)).t() if weights_nk else enc(w32)    # [K, N] view either way
+    exact = val(x32).astype(np.float64) @ val(w32).astype(np.float64)
+    split_route = "umma_bf16_splitk" if bf16 else "umma_f16_splitk"
+    got = api.linear(x, w, bias)
+    assert L.last_route() == split_route
+    assert oracle.rel_fro(dec(got), exact + val(b32)) <= 2e-3
+    out = enc(c32)
+    api.matmult(x, w, out=out)                           # C += x . w
+    assert L.last_route() == split_route
+    assert oracle.rel_fro(dec(out), exact + val(c32)) <= 2e-3
+    # the left half of the columns on its own (a strided view, possibly too small to split) gives the same sums up to
+    # the order of the fp32 additions
+    half = api.matmult(x, w[:, : n // 2])
+    both = api.matmult(x, w)
+    assert L.last_route() == split_route
+    assert oracle.rel_fro(dec(both)[:, : n // 2], dec(half)) <= 1e-3
+
+
 def test_pinned_host_buffers_from_the_library(api, oracle, L):
     """ntb200_host_alloc / ntb200_host_register give page-locked host memory for ntb200_matmult_host."""
     import ctypes
