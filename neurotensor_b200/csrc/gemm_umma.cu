@@ -1075,6 +1075,14 @@ const bool g_disable_pair = [] { const char* e = getenv("NTB200_NO_PAIR"); retur
 
 // NTB200_FULL_A_TILE=1 always stages all 128 rows of A in the single-CTA kernel (for A/B measurements).
 const bool g_full_a_tile = [] { const char* e = getenv("NTB200_FULL_A_TILE"); return e && e[0] == '1'; }();
+// NTB200_TUNE=1 at load time makes every launch re-read NTB200_FORCE_BN (64 / 128 / 256), NTB200_FORCE_SPLITS (K slices)
+// and NTB200_NO_PAIR from the environment: the knobs the tile heuristics were fitted with.
+const bool g_tune = [] { const char* e = getenv("NTB200_TUNE"); return e && e[0] == '1'; }();
+int tune_int(const char* name) {
+    if (!g_tune) return 0;
+    const char* e = getenv(name);
+    return e ? atoi(e) : 0;
+}
 
 // NTB200_DIRECT_STORES=1 keeps the per-thread global stores in every epilogue (for A/B measurements).
 const bool g_direct_stores = [] { const char* e = getenv("NTB200_DIRECT_STORES"); return e && e[0] == '1'; }();
@@ -1282,8 +1290,14 @@ struct Side {
     int64_t mn_stride, k_stride, bs;
 };
 
+// A tile shape decided by the caller (the 16-bit cost model below) instead of the heuristics inside launch_planned.
+struct TileChoice {
+    bool pair;
+    int bn;
+};
+
 int launch_planned(const GemmArgs& g, const Planned& pl, const Side& a, const Side& b, const Side* a_lo, const Side* b_lo,
-                   cudaStream_t stream) {
+                   cudaStream_t stream, const TileChoice* choice = nullptr) {
     const int es = pl.es;
     const int block_k = 128 / es;
     // Tile width: the widest one that still gives every SM a tile.
@@ -1300,7 +1314,17 @@ int launch_planned(const GemmArgs& g, const Planned& pl, const Side& a, const Si
     // Large problems run on CTA pairs (256 x 256 tiles); anything with fewer pair tiles than TPCs keeps the
     // single-CTA kernel, whose narrower tiles spread small problems over more SMs.
     const int64_t pair_tiles = ((g.m + 255) / 256) * ((g.n + 255) / 256) * g.batch;
-    const bool use_pair = !g_disable_pair && g.m > 128 && g.n > 128 && pair_tiles * 5 >= (sms / 2) * 4;   // >= 80 % of one wave
+    bool use_pair = !g_disable_pair && g.m > 128 && g.n > 128 && pair_tiles * 5 >= (sms / 2) * 4;   // >= 80 % of one wave
+    if (choice) {
+        use_pair = choice->pair && g.m > 128 && g.n > 128;
+        if (!use_pair) bn = choice->bn;
+    }
+    if (g_tune) {
+        if (tune_int("NTB200_NO_PAIR") == 1) use_pair = false;
+        if (tune_int("NTB200_NO_PAIR") == 2) use_pair = g.m > 128 && g.n > 128;
+        const int f = tune_int("NTB200_FORCE_BN");
+        if (!use_pair && (f == 64 || f == 128 || f == 256)) bn = f;
+    }
     if (use_pair) bn = 256;
 
     Maps maps;
@@ -1574,6 +1598,49 @@ int pick_k_splits(const GemmArgs& g) {
     return best;
 }
 
+// More than 128 rows of 16-bit floats: tile shape and K slices by a small cost model, in microseconds.  One K block
+// of a tile costs its CTA (or CTA pair) a fixed time that hardly depends on the tile's width below 256 columns (the
+// issue cost above), so what matters is the number of waves of tiles, the K blocks each tile runs through, and, with
+// K slices, the fp32 partial tiles that are written and read back.  The constants are fitted to a sweep of
+// m = 129 .. 1536 against weight matrices of 2048 .. 11008 squared-ish shapes (tile kind x slices, CUDA events).
+struct F16Plan {
+    TileChoice tile;
+    int splits;
+    bool valid;
+};
+
+F16Plan plan_f16_tiles(const GemmArgs& g) {
+    F16Plan best{{false, 64}, 1, false};
+    if (g.m <= kBM) return best;   // few rows: pick_k_splits and the heuristics in launch_planned
+    const int sms = sm_count();
+    const double kb = double((g.k + 63) / 64);
+    const bool fused = g.relu_out || g.mask_src || g.n_peers > 0;
+    const bool may_split = !g_no_splitk && g.batch == 1 && !fused && g.n % 4 == 0;
+    const double dram_us = double(g.batch) * (double(g.m) * g.k + double(g.k) * g.n + double(g.m) * g.n) * 2.0 / 4.5e6;
+    struct Cand { bool pair; int bn; double us_per_k_block; };
+    const Cand cands[] = {{true, 256, 0.40}, {false, 256, 0.46}, {false, 128, 0.385}, {false, 64, 0.32}};
+    double best_us = 1e30;
+    for (const Cand& c : cands) {
+        if (c.pair && (g_disable_pair || g.n <= 128)) continue;
+        if (!c.pair && c.bn > 64 && g.n <= c.bn / 2) continue;          // a tile more than twice as wide as C
+        if (fused && !c.pair && g.n > 128) continue;                     // fused epilogues keep the TMA-store kernel
+        const int64_t tiles = (c.pair ? ((g.m + 255) / 256) * ((g.n + 255) / 256)
+                                      : ((g.m + kBM - 1) / kBM) * ((g.n + c.bn - 1) / c.bn)) * g.batch;
+        const int units = c.pair ? sms / 2 : sms;
+        for (int s = 1; s <= 16; s *= 2) {
+            if (s > 1 && (!may_split || g.k % (64 * s) != 0 || g.k / s < 512)) break;
+            const double waves = double((tiles * s + units - 1) / units);
+            double us = 4.0 + std::max(waves * (kb / s) * c.us_per_k_block, dram_us);
+            if (s > 1) us += 3.0 + double(s) * double(g.m) * double(g.n) * 8.0 / 2.0e6;   // partial tiles out and back in
+            if (us < best_us * 0.97) {   // candidates come in order of preference: a later one has to be clearly better
+                best_us = us;
+                best = F16Plan{{c.pair, c.bn}, s, true};
+            }
+        }
+    }
+    return best;
+}
+
 template <int kOutKind>
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int splits, long long slab, int m, int n, uint16_t* c,
                                      long long c_rs, const uint16_t* bias, long long bias_rs, long long bias_cs, int accumulate) {
@@ -1597,7 +1664,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int spli
     }
 }
 
-int launch_f16_split_k(const GemmArgs& g, const Planned& pl16, int splits, cudaStream_t stream) {
+int launch_f16_split_k(const GemmArgs& g, const Planned& pl16, int splits, const TileChoice* choice, cudaStream_t stream) {
     const int64_t slab = g.m * g.n, kslice = g.k / splits;
     float* partial = nullptr;
     keep_pool_memory();
@@ -1611,7 +1678,7 @@ int launch_f16_split_k(const GemmArgs& g, const Planned& pl16, int splits, cudaS
     pl.out_kind = kOutF32;
     pl.route = g.dtype == NTB200_F16 ? "umma_f16_splitk" : "umma_bf16_splitk";
     const Side a{g.a, g.a_rs, g.a_cs, kslice * g.a_cs}, b{g.b, g.b_cs, g.b_rs, kslice * g.b_rs};
-    int rc = launch_planned(part, pl, a, b, nullptr, nullptr, stream);
+    int rc = launch_planned(part, pl, a, b, nullptr, nullptr, stream, choice);
     if (rc == NTB200_OK) {
         const long long work = (long long)g.m * (g.n / 4);
         const unsigned blocks = unsigned((work + 255) / 256);
@@ -1656,12 +1723,23 @@ int launch_umma_gemm(const GemmArgs& g, cudaStream_t stream) {
     pl.in_fmt = g.dtype == NTB200_BF16 ? 1u : (g.dtype == NTB200_I8 ? 1u : 0u);
     pl.split = false;
     pl.route = is_i8 ? "umma_i8" : (g.dtype == NTB200_F16 ? "umma_f16" : "umma_bf16");
+    const TileChoice* choice = nullptr;
+    F16Plan plan{};
     if (!is_i8) {
-        const int splits = pick_k_splits(g);
-        if (splits > 1) return launch_f16_split_k(g, pl, splits, stream);
+        int splits = pick_k_splits(g);
+        plan = plan_f16_tiles(g);
+        if (plan.valid && !tune_int("NTB200_OLD_PLAN")) {
+            choice = &plan.tile;
+            splits = plan.splits;
+        }
+        if (const int f = tune_int("NTB200_FORCE_SPLITS")) {
+            choice = nullptr;
+            splits = (g.batch == 1 && !g.relu_out && !g.mask_src && g.n_peers == 0 && g.n % 4 == 0 && g.k % (64 * f) == 0) ? f : 1;
+        }
+        if (splits > 1) return launch_f16_split_k(g, pl, splits, choice, stream);
     }
     const Side a{g.a, g.a_rs, g.a_cs, g.a_bs}, b{g.b, g.b_cs, g.b_rs, g.b_bs};
-    return launch_planned(g, pl, a, b, nullptr, nullptr, stream);
+    return launch_planned(g, pl, a, b, nullptr, nullptr, stream, choice);
 }
 
 // Self-test of the bounded-wait plumbing: one thread waits on an mbarrier that nothing ever signals, with a short

@@ -386,10 +386,10 @@ def test_few_rows_stream_the_weights(api, oracle, L, m, weights_nk, bf16):
 @pytest.mark.gpu
 @pytest.mark.parametrize("bf16", [False, True])
 @pytest.mark.parametrize("m,n,k,weights_nk", [(3, 4096, 4096, False), (16, 4100, 4096, True), (100, 4096, 8192, False),
-                                              (128, 8192, 4096, True)])
+                                              (128, 8192, 4096, True), (256, 2048, 8192, False), (300, 2048, 8192, True)])
 def test_few_rows_split_the_k_axis(api, oracle, L, m, n, k, weights_nk, bf16):
-    """Up to 128 rows of 16-bit floats against a deep, large weight matrix: K is cut into slices that run side by side
-    as fp32 partial tiles, and a second kernel adds them, the bias and the previous C and rounds once."""
+    """A few rows (or a few hundred against a deep, narrow weight matrix) of 16-bit floats: K is cut into slices that run
+    side by side as fp32 partial tiles, and a second kernel adds them, the bias and the previous C and rounds once."""
     rng = np.random.default_rng(97 + m)
     x32, w32 = normal(rng, (m, k), np.float32, 0.5), normal(rng, (k, n), np.float32, 0.5)
     b32, c32 = normal(rng, (n,), np.float32), normal(rng, (m, n), np.float32)
