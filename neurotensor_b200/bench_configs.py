@@ -3,7 +3,7 @@
     python -m neurotensor_b200.bench_configs [--steps K] [--cpu] [--only c1,c3i8,...]
 
 Rows: c1 (Float32 1024^3), c2 (batched Float16 64x2048^3, transposed-view B), c3i8 (Int8 4096x8192x4096),
-c3i32 (Int32 2048^3), c3i16 (Int16 4096^3), t8192 (Float16 / BFloat16 8192^3), skinny (1 / 2 / 16 / 128 rows x 8192 x 8192), c4 (BFloat16 MLP 8192 x 4096->16384->4096: forward + backward step), c5 (Float16 conv2d
+c3i32 (Int32 2048^3), c3i16 (Int16 4096^3), t8192 (Float16 / BFloat16 8192^3), skinny (1 / 2 / 16 / 128 rows x 8192 x 8192), midrows (256 - 512 rows against 2048 - 11008-wide weights), c4 (BFloat16 MLP 8192 x 4096->16384->4096: forward + backward step), c5 (Float16 conv2d
 [32,256,56,56] * [256,256,3,3]), sweepN (Float32 N^3).  Inputs are seeded synthetic tensors of the stated shapes
 and distributions, resident on the device; time is CUDA events over K launches after 3 warm-ups.  `--cpu` also
 times the CPU oracle on a bounded sub-problem of each row (test infrastructure, scaled linearly, stated per row).
@@ -128,6 +128,16 @@ def main():
                 emit("skinny %s %dx8192x8192, weights stored [N, K]" % (name, m), s, 2 * m * 8192 * 8192,
                      (m * 8192 * 2 + 8192 * 8192) * 2, "hbm", l)
                 del a, b, bt, c
+
+    if want("midrows"):
+        # a few hundred rows through a Linear layer: too few 256 x 256 tiles to fill the GPU, so the planner weighs
+        # CTA pairs against single-CTA tiles and K slices
+        for (m, n, k) in ((256, 8192, 8192), (512, 4096, 4096), (384, 4096, 11008), (256, 2048, 8192)):
+            a, b = randn(gen, (m, k), torch.float16, 0.1), randn(gen, (k, n), torch.float16, 0.1)
+            c = torch.empty((m, n), dtype=torch.float16, device="cuda")
+            s, l = timed(lambda: api.gemm(a, b, c), args.steps)
+            emit("midrows Float16 %dx%dx%d" % (m, k, n), s, 2 * m * n * k, (m * k + k * n + m * n) * 2, "tensor", l)
+            del a, b, c
 
     if want("c3i8"):
         a = torch.randint(-8, 8, (4096, 8192), generator=gen, device="cuda", dtype=torch.int8)

@@ -1643,7 +1643,8 @@ F16Plan plan_f16_tiles(const GemmArgs& g) {
 
 template <int kOutKind>
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int splits, long long slab, int m, int n, uint16_t* c,
-                                     long long c_rs, const uint16_t* bias, long long bias_rs, long long bias_cs, int accumulate) {
+                                     long long c_rs, const uint16_t* bias, long long bias_rs, long long bias_cs, int accumulate,
+                                     int wide_stores) {
     const int n4 = n >> 2;                                  // n is a multiple of 4
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (long long)m * n4) return;
@@ -1656,11 +1657,18 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int spli
     }
     float f[4] = {acc.x, acc.y, acc.z, acc.w};
     uint16_t* dst = c + (long long)row * c_rs + col;
+    uint32_t r[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
         if (bias) f[j] += to_float_bits16(bias[(long long)row * bias_rs + (long long)(col + j) * bias_cs], kOutKind);
         if (accumulate) f[j] += to_float_bits16(dst[j], kOutKind);
-        dst[j] = uint16_t(from_float_bits16(f[j], kOutKind));
+        r[j] = from_float_bits16(f[j], kOutKind);
+    }
+    if (wide_stores) {   // C and its rows are 8-byte aligned
+        *reinterpret_cast<uint2*>(dst) = make_uint2(r[0] | (r[1] << 16), r[2] | (r[3] << 16));
+    } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) dst[j] = uint16_t(r[j]);
     }
 }
 
@@ -1684,12 +1692,13 @@ int launch_f16_split_k(const GemmArgs& g, const Planned& pl16, int splits, const
         const unsigned blocks = unsigned((work + 255) / 256);
         uint16_t* c = static_cast<uint16_t*>(g.c);
         const uint16_t* bias = static_cast<const uint16_t*>(g.bias);
+        const int wide_stores = (reinterpret_cast<uintptr_t>(g.c) % 8 == 0 && g.c_rs % 4 == 0) ? 1 : 0;
         if (g.dtype == NTB200_F16)
             splitk_reduce_kernel<kOutF16><<<blocks, 256, 0, stream>>>(partial, splits, slab, int(g.m), int(g.n), c, g.c_rs, bias,
-                                                                     g.bias_rs, g.bias_cs, g.accumulate);
+                                                                     g.bias_rs, g.bias_cs, g.accumulate, wide_stores);
         else
             splitk_reduce_kernel<kOutBF16><<<blocks, 256, 0, stream>>>(partial, splits, slab, int(g.m), int(g.n), c, g.c_rs, bias,
-                                                                      g.bias_rs, g.bias_cs, g.accumulate);
+                                                                      g.bias_rs, g.bias_cs, g.accumulate, wide_stores);
         count_launch();
         const cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) rc = cuda_fail(e, "splitk_reduce_kernel");
