@@ -1602,23 +1602,25 @@ int pick_k_splits(const GemmArgs& g) {
 // of a tile costs its CTA (or CTA pair) a fixed time that hardly depends on the tile's width below 256 columns (the
 // issue cost above), so what matters is the number of waves of tiles, the K blocks each tile runs through, and, with
 // K slices, the fp32 partial tiles that are written and read back.  The constants are fitted to a sweep of
-// m = 129 .. 1536 against weight matrices of 2048 .. 11008 squared-ish shapes (tile kind x slices, CUDA events).
+// m = 129 .. 1536 against weight matrices 2048 .. 11008 wide and deep (tile kind x slices, CUDA events over
+// back-to-back launches, so the fixed part includes the launch).
 struct F16Plan {
     TileChoice tile;
     int splits;
     bool valid;
 };
 
-F16Plan plan_f16_tiles(const GemmArgs& g) {
+F16Plan plan_f16_tiles(const GemmArgs& g, int es = 2) {
     F16Plan best{{false, 64}, 1, false};
     if (g.m <= kBM) return best;   // few rows: pick_k_splits and the heuristics in launch_planned
     const int sms = sm_count();
-    const double kb = double((g.k + 63) / 64);
+    const int block_k = 128 / es;  // 8-bit operands: 128 deep K blocks, the same four MMAs and the same cycles
+    const double kb = double((g.k + block_k - 1) / block_k);
     const bool fused = g.relu_out || g.mask_src || g.n_peers > 0;
-    const bool may_split = !g_no_splitk && g.batch == 1 && !fused && g.n % 4 == 0;
-    const double dram_us = double(g.batch) * (double(g.m) * g.k + double(g.k) * g.n + double(g.m) * g.n) * 2.0 / 4.5e6;
-    struct Cand { bool pair; int bn; double us_per_k_block; };
-    const Cand cands[] = {{true, 256, 0.40}, {false, 256, 0.46}, {false, 128, 0.385}, {false, 64, 0.32}};
+    const bool may_split = es == 2 && !g_no_splitk && g.batch == 1 && !fused && g.n % 4 == 0;   // the reduce kernel is 16-bit
+    const double dram_us = double(g.batch) * (double(g.m) * g.k + double(g.k) * g.n + double(g.m) * g.n) * es / 4.5e6;
+    struct Cand { bool pair; int bn; double fixed_us, us_per_k_block; };   // launch + fill + last epilogue; main loop
+    const Cand cands[] = {{true, 256, 11.0, 0.35}, {false, 256, 13.0, 0.39}, {false, 128, 10.0, 0.34}, {false, 64, 10.0, 0.30}};
     double best_us = 1e30;
     for (const Cand& c : cands) {
         if (c.pair && (g_disable_pair || g.n <= 128)) continue;
@@ -1630,8 +1632,8 @@ F16Plan plan_f16_tiles(const GemmArgs& g) {
         for (int s = 1; s <= 16; s *= 2) {
             if (s > 1 && (!may_split || g.k % (64 * s) != 0 || g.k / s < 512)) break;
             const double waves = double((tiles * s + units - 1) / units);
-            double us = 4.0 + std::max(waves * (kb / s) * c.us_per_k_block, dram_us);
-            if (s > 1) us += 3.0 + double(s) * double(g.m) * double(g.n) * 8.0 / 2.0e6;   // partial tiles out and back in
+            double us = c.fixed_us + std::max(waves * (kb / s) * c.us_per_k_block, dram_us);
+            if (s > 1) us += 3.0 + double(s) * double(g.m) * double(g.n) * 8.0 / 4.0e6;   // partial tiles out and back in (mostly L2)
             if (us < best_us * 0.97) {   // candidates come in order of preference: a later one has to be clearly better
                 best_us = us;
                 best = F16Plan{{c.pair, c.bn}, s, true};
@@ -1734,7 +1736,10 @@ int launch_umma_gemm(const GemmArgs& g, cudaStream_t stream) {
     pl.route = is_i8 ? "umma_i8" : (g.dtype == NTB200_F16 ? "umma_f16" : "umma_bf16");
     const TileChoice* choice = nullptr;
     F16Plan plan{};
-    if (!is_i8) {
+    if (is_i8) {
+        plan = plan_f16_tiles(g, 1);
+        if (plan.valid && !tune_int("NTB200_OLD_PLAN")) choice = &plan.tile;
+    } else {
         int splits = pick_k_splits(g);
         plan = plan_f16_tiles(g);
         if (plan.valid && !tune_int("NTB200_OLD_PLAN")) {
