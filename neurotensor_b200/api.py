@@ -237,6 +237,87 @@ def matmult(a, b, transpose_a=False, transpose_b=False, out=None, route=_lib.ROU
     return gemm(a, b, out, transpose_a, transpose_b, accumulate=True, route=route, f16_rounding=f16_rounding)
 
 
+def matmult_tensors(a_list, b_list, transpose_a=False, transpose_b=False):
+    """functional::matmult on two tensors of tensors (DType::TensorObj operands, matmult_cpu.cpp:1240-1558): two lists
+    of the same length, every tensor of a list with one shape and dtype; item i of the result is
+    matmult(a_list[i], b_list[i]).  The items may have batch dimensions of their own, and the items of one list may
+    have fewer dimensions than those of the other (they are then reused over the other's batch dimensions, the
+    reference's `n_k` / `k_n` forms).  Every (item, batch) pair becomes one entry of the pointer tables of a single
+    ntb200_matmult_batch call: equally spaced pointers (lists made by splitting one tensor) run as one strided
+    launch, anything else through device pointer tables.  Returns the list of results, views of one allocation.
+    Errors follow subT_check (matmult_cpu.cpp:1486-1513)."""
+    a_list, b_list = list(a_list), list(b_list)
+    if len(a_list) != len(b_list):
+        raise ValueError("Expected both tensors to have the same number of sub-tensors, going to have these multiplied in a "
+                         "list-like fashion, but got %d and %d tensors" % (len(a_list), len(b_list)))
+    if not a_list:
+        return []
+    for name, lst in (("a", a_list), ("b", b_list)):
+        for t in lst[1:]:
+            if t.shape != lst[0].shape:
+                raise ValueError("Expected all tensors in list of tensors to have the same shape, but %s has a tensor of shape "
+                                 "%s and %s" % (name, tuple(lst[0].shape), tuple(t.shape)))
+            if t.dtype != lst[0].dtype:
+                raise ValueError("Expected all tensors in list of tensors to have the same dtype, but %s has a tensor of dtype "
+                                 "%s and %s" % (name, lst[0].dtype, t.dtype))
+    if a_list[0].dtype != b_list[0].dtype:
+        raise ValueError("Expected all tensors in list of tensors to have the same dtype (%s), but b has a tensor of dtype %s"
+                         % (a_list[0].dtype, b_list[0].dtype))
+    _require_cuda(*a_list, *b_list)
+    a0, b0 = a_list[0], b_list[0]
+    if a0.dim() < 2 or b0.dim() < 2:
+        raise ValueError("matmult: the tensors of a tensor of tensors need at least two dimensions")
+    a_rows, a_cols = int(a0.shape[-2]), int(a0.shape[-1])
+    b_rows, b_cols = int(b0.shape[-2]), int(b0.shape[-1])
+    lead_a, lead_b = tuple(a0.shape[:-2]), tuple(b0.shape[:-2])
+    if len(lead_a) >= len(lead_b):
+        lead = lead_a
+        if lead_b and lead_a[len(lead_a) - len(lead_b):] != lead_b:
+            raise ValueError("matmult: batch dimensions %s and %s do not match" % (lead_a, lead_b))
+    else:
+        lead = lead_b
+        if lead_a and lead_b[len(lead_b) - len(lead_a):] != lead_a:
+            raise ValueError("matmult: batch dimensions %s and %s do not match" % (lead_a, lead_b))
+    inner = 1
+    for d in lead:
+        inner *= int(d)
+    m = a_cols if transpose_a else a_rows
+    k = a_rows if transpose_a else a_cols
+    kb = b_cols if transpose_b else b_rows
+    n = b_rows if transpose_b else b_cols
+    if k != kb:
+        raise ValueError("Expected second tensor rows to be %d when it was %d" % (k, kb))
+    a_list = [t.contiguous() for t in a_list]
+    b_list = [t.contiguous() for t in b_list]
+    out = torch.zeros((len(a_list),) + lead + (m, n), dtype=a0.dtype, device=a0.device)   # the raw contract is C +=
+    es = a0.element_size()
+    count = len(a_list) * inner
+    pa, pb, pc = (ctypes.c_void_p * count)(), (ctypes.c_void_p * count)(), (ctypes.c_void_p * count)()
+    a_inner = a0.numel() // (a_rows * a_cols)
+    b_inner = b0.numel() // (b_rows * b_cols)
+    for i, (ta, tb) in enumerate(zip(a_list, b_list)):
+        base_a, base_b, base_c = ta.data_ptr(), tb.data_ptr(), out[i].data_ptr()
+        for j in range(inner):
+            pa[i * inner + j] = base_a + (j % a_inner) * a_rows * a_cols * es
+            pb[i * inner + j] = base_b + (j % b_inner) * b_rows * b_cols * es
+            pc[i * inner + j] = base_c + j * m * n * es
+    check(lib().ntb200_matmult_batch(dtype_code(a0), pa, pb, pc, count, a_rows, a_cols, b_rows, b_cols,
+                                     int(bool(transpose_a)), int(bool(transpose_b)), _stream()))
+    return [out[i] for i in range(len(a_list))]
+
+
+def hodge_laplacian_from_boundaries(boundary_kp1, boundary_k=None):
+    """The matmult calls of the TDA Hodge Laplacian (nt/tda/nn/laplacian.cpp:42-45,61-62,84-86):
+    L = B_{k+1} B_{k+1}^T (+ B_k^T B_k), both products by transpose flags on the boundary matrices, then one
+    elementwise add of the two finished products (not a continued accumulation: the reference adds two tensors)."""
+    up = matmult(boundary_kp1, boundary_kp1, False, True)
+    if boundary_k is None:
+        return up
+    down = matmult(boundary_k, boundary_k, True, False)
+    check(lib().ntb200_add_inplace(dtype_code(up), up.data_ptr(), down.data_ptr(), up.numel(), _stream()))
+    return up
+
+
 def matmult_cT(a, b):
     return matmult(a, b, False, True)
 

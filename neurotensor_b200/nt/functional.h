@@ -154,6 +154,56 @@ inline Tensor& matmult(const Tensor& a, const Tensor& b, Tensor& c, bool trans_a
     return detail::run(a, b, c, trans_a, trans_b, /*accumulate=*/true, nullptr);
 }
 
+// Tensor-of-tensors operands (DType::TensorObj in the reference, matmult_cpu.cpp:1240-1558): two lists of equal
+// length, one shape and dtype per list; result[i] = matmult(a[i], b[i]).  Every (item, batch) pair is one entry of
+// the pointer tables of a single ntb200_matmult_batch call (equally spaced pointers run as one strided launch).
+// Device tensors only.  Checks follow subT_check (matmult_cpu.cpp:1486-1513).
+inline std::vector<Tensor> matmult(const std::vector<Tensor>& a, const std::vector<Tensor>& b, bool trans_a = false,
+                                   bool trans_b = false) {
+    utils::throw_exception(a.size() == b.size(), "Expected both tensors to have the same number of sub-tensors, going to have these "
+                           "multiplied in a list-like fashion, but got ", a.size(), " and ", b.size(), " tensors");
+    std::vector<Tensor> out;
+    if (a.empty()) return out;
+    for (size_t i = 1; i < a.size(); ++i) {
+        utils::throw_exception(a[i].shape() == a[0].shape(), "Expected all tensors in list of tensors to have the same shape, but a has a "
+                               "tensor of shape ", a[0].shape(), " and ", a[i].shape());
+        utils::throw_exception(b[i].shape() == b[0].shape(), "Expected all tensors in list of tensors to have the same shape, but b has a "
+                               "tensor of shape ", b[0].shape(), " and ", b[i].shape());
+        utils::throw_exception(a[i].dtype() == a[0].dtype() && b[i].dtype() == a[0].dtype(),
+                               "Expected all tensors in list of tensors to have the same dtype (", dtype_name(a[0].dtype()), ")");
+    }
+    detail::check_operands(a[0], b[0]);
+    utils::throw_exception(a[0].device() != DeviceType::CPU, "matmult on lists of tensors: move the tensors to DeviceType::CUDA");
+    int64_t m, k, n;
+    detail::check_inner(a[0], b[0], trans_a, trans_b, m, k, n);
+    const SizeRef item_shape = detail::result_shape(a[0], b[0], trans_a, trans_b);
+    const int64_t ar = a[0].shape()[-2], ac = a[0].shape()[-1], br = b[0].shape()[-2], bc = b[0].shape()[-1];
+    const int64_t a_inner = a[0].numel() / (ar * ac), b_inner = b[0].numel() / (br * bc);
+    const int64_t inner = std::max(a_inner, b_inner);
+    const size_t es = dtype_size(a[0].dtype());
+    std::vector<Tensor> keep;   // contiguous copies stay alive until the call returns
+    std::vector<const void*> pa, pb;
+    std::vector<void*> pc;
+    for (size_t i = 0; i < a.size(); ++i) {
+        keep.push_back(a[i].contiguous());
+        const char* base_a = static_cast<const char*>(keep.back().data_ptr());
+        keep.push_back(b[i].contiguous());
+        const char* base_b = static_cast<const char*>(keep.back().data_ptr());
+        Tensor c(item_shape, a[0].dtype(), a[0].device());   // zero-filled: the raw contract accumulates
+        char* base_c = static_cast<char*>(c.data_ptr());
+        for (int64_t j = 0; j < inner; ++j) {
+            pa.push_back(base_a + (j % a_inner) * ar * ac * es);
+            pb.push_back(base_b + (j % b_inner) * br * bc * es);
+            pc.push_back(base_c + j * m * n * es);
+        }
+        out.push_back(c);
+    }
+    utils::check(ntb200_matmult_batch(dtype_code(a[0].dtype()), pa.data(), pb.data(), pc.data(), int64_t(pa.size()), ar, ac, br, bc,
+                                      trans_a, trans_b, nullptr));
+    utils::check(ntb200_stream_synchronize(nullptr));
+    return out;
+}
+
 inline Tensor matmult_cT(const Tensor& a, const Tensor& b) { return matmult(a, b, false, true); }
 
 // op(x).op(w) + bias; a null bias is a plain matmult (matmult.cpp:27-32).  The bias is the value the accumulation

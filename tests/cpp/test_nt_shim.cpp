@@ -67,6 +67,35 @@ int main(int argc, char** argv) {
         }
     });
 
+    run_test("matmult tensors: lists of tensors multiply pairwise (no bigger, Ta, Tb, bigger a)", [] {
+        // the cases of the reference's tests/src/matmult_test.cpp:108-190, with its own check all(o1 == o[i])
+        struct Case { SizeRef a, b; bool ta, tb; };
+        const Case cases[] = {{{5, 2, 3, 4}, {5, 2, 4, 3}, false, false}, {{5, 2, 4, 3}, {5, 2, 4, 3}, true, false},
+                              {{5, 2, 4, 3}, {5, 2, 4, 3}, false, true},  {{5, 2, 4, 3}, {5, 4, 3}, true, false},
+                              {{5, 2, 4, 3}, {5, 4, 3}, false, true}};
+        int seed = 40;
+        for (const Case& c : cases) {
+            Tensor a = nt::randn_seeded(c.a, DType::Float32, ++seed), b = nt::randn_seeded(c.b, DType::Float32, ++seed);
+            std::vector<Tensor> al, bl;
+            for (int64_t i = 0; i < 5; ++i) { al.push_back(a[i]); bl.push_back(b[i]); }
+            std::vector<Tensor> o = fn::matmult(al, bl, c.ta, c.tb);
+            REQUIRE(o.size() == 5);
+            for (int64_t i = 0; i < 5; ++i) {
+                Tensor o1 = fn::matmult(al[size_t(i)], bl[size_t(i)], c.ta, c.tb);
+                REQUIRE(o[size_t(i)].shape() == o1.shape());
+                REQUIRE(o[size_t(i)].to_vector<float>() == o1.to_vector<float>());
+            }
+            // the same lists in another order: pointers no longer equally spaced
+            std::vector<Tensor> as = {al[3], al[0], al[4], al[1], al[2]}, bs = {bl[3], bl[0], bl[4], bl[1], bl[2]};
+            std::vector<Tensor> os = fn::matmult(as, bs, c.ta, c.tb);
+            REQUIRE(os[0].to_vector<float>() == o[3].to_vector<float>());
+            REQUIRE(os[4].to_vector<float>() == o[2].to_vector<float>());
+        }
+        Tensor x = nt::randn_seeded({2, 3, 4}, DType::Float32, 60);
+        REQUIRE(throws_invalid_argument([&] { fn::matmult(std::vector<Tensor>{x, x}, std::vector<Tensor>{x}); }));
+        REQUIRE(throws_invalid_argument([&] { fn::matmult(std::vector<Tensor>{x}, std::vector<Tensor>{x}); }));   // 4 != 3
+    });
+
     run_test("transpose is an O(1) view and matmult reads it in place", [] {
         Tensor a = nt::randn_seeded({2, 128, 192}, DType::Float32, 7).to(DType::Float16);
         Tensor bs = nt::randn_seeded({2, 256, 192}, DType::Float32, 8).to(DType::Float16);

@@ -443,3 +443,64 @@ def test_pinned_host_buffers_from_the_library(api, oracle, L):
     own = np.zeros((64, 64), np.float32)
     L.check(lib.ntb200_host_register(own.ctypes.data, own.nbytes))
     L.check(lib.ntb200_host_unregister(own.ctypes.data))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("a_shape,b_shape,ta,tb", [
+    ((5, 2, 3, 4), (5, 2, 4, 3), False, False),      # "matmult tensors (no bigger)", tests/src/matmult_test.cpp:108-120
+    ((5, 2, 4, 3), (5, 2, 4, 3), True, False),       # "matmult tensors Ta", :142-153
+    ((5, 2, 4, 3), (5, 2, 4, 3), False, True),       # "matmult tensors Tb", :154-165
+    ((5, 2, 4, 3), (5, 4, 3), True, False),          # "Ta (bigger a)", :167-178
+    ((5, 2, 4, 3), (5, 4, 3), False, True),          # "Tb (bigger a)", :179-190
+    ((5, 3, 4), (5, 2, 4, 3), False, False),         # the items of b carry the batch dimension
+])
+@pytest.mark.parametrize("scattered", [False, True])
+def test_tensor_of_tensors_matmult(api, oracle, L, a_shape, b_shape, ta, tb, scattered):
+    """Tensor-of-tensors operands: item i of the result equals matmult(a[i], b[i]), bit for bit (the reference's own
+    check, `all(o1 == o[i])`), for lists split from one tensor (equally spaced pointers, one strided launch) and for
+    lists of separately allocated tensors in shuffled order (device pointer tables)."""
+    rng = np.random.default_rng(101)
+    a = rng.integers(0, 3, a_shape).astype(np.float32) + normal(rng, a_shape, np.float32, 0.25)
+    b = rng.integers(0, 3, b_shape).astype(np.float32) + normal(rng, b_shape, np.float32, 0.25)
+    if scattered:
+        order = [3, 0, 4, 1, 2]
+        a_list = [dev(a[i].copy()) for i in order]
+        b_list = [dev(b[i].copy()) for i in order]
+        a, b = a[order], b[order]
+    else:
+        da, db = dev(a), dev(b)
+        a_list, b_list = [da[i] for i in range(5)], [db[i] for i in range(5)]
+    out = api.matmult_tensors(a_list, b_list, ta, tb)
+    assert len(out) == 5
+    for i in range(5):
+        single = api.matmult(a_list[i], b_list[i], ta, tb)
+        assert torch.equal(out[i], single), "item %d differs from the 2-operand call" % i
+        ai = np.swapaxes(a[i], -1, -2) if ta else a[i]
+        bi = np.swapaxes(b[i], -1, -2) if tb else b[i]
+        assert np.array_equal(host(out[i]), oracle.matmult(ai, bi))
+
+
+@pytest.mark.gpu
+def test_tensor_of_tensors_errors(api):
+    x = torch.zeros((2, 3, 4), device="cuda")
+    with pytest.raises(ValueError, match="same number of sub-tensors"):
+        api.matmult_tensors([x, x], [x])
+    with pytest.raises(ValueError, match="same shape"):
+        api.matmult_tensors([x, x[:, :2]], [x, x])
+    with pytest.raises(ValueError, match="same dtype"):
+        api.matmult_tensors([x, x], [x.half(), x.half()], False, True)
+    with pytest.raises(ValueError, match="Expected second tensor rows to be 4 when it was 3"):
+        api.matmult_tensors([x], [x])
+
+
+@pytest.mark.gpu
+def test_hodge_laplacian_products(api, oracle):
+    """The two matmult calls of the TDA Hodge Laplacian on signed boundary matrices (entries -1, 0, 1 scaled by radii):
+    B_{k+1} B_{k+1}^T + B_k^T B_k, Float32, bit-exact against the oracle's chains and one fp32 add."""
+    rng = np.random.default_rng(103)
+    bk = (rng.integers(-1, 2, (21, 35)) * rng.uniform(0.5, 1.5, (21, 35))).astype(np.float32)      # [k-1 simplices, k simplices]
+    bkp1 = (rng.integers(-1, 2, (35, 40)) * rng.uniform(0.5, 1.5, (35, 40))).astype(np.float32)    # [k simplices, k+1 simplices]
+    got = api.hodge_laplacian_from_boundaries(dev(bkp1), dev(bk))
+    exp = oracle.matmult(bkp1, bkp1.T.copy()) + oracle.matmult(bk.T.copy(), bk)
+    assert np.array_equal(host(got), exp.astype(np.float32))
+    assert np.array_equal(host(api.hodge_laplacian_from_boundaries(dev(bkp1))), oracle.matmult(bkp1, bkp1.T.copy()))
