@@ -301,7 +301,8 @@ def matmult_tensors(a_list, b_list, transpose_a=False, transpose_b=False):
             pa[i * inner + j] = base_a + (j % a_inner) * a_rows * a_cols * es
             pb[i * inner + j] = base_b + (j % b_inner) * b_rows * b_cols * es
             pc[i * inner + j] = base_c + j * m * n * es
-    check(lib().ntb200_matmult_batch(dtype_code(a0), pa, pb, pc, count, a_rows, a_cols, b_rows, b_cols,
+    # the raw contract takes the logical extents of op(a) and op(b); the flags say how they are stored
+    check(lib().ntb200_matmult_batch(dtype_code(a0), pa, pb, pc, count, m, k, k, n,
                                      int(bool(transpose_a)), int(bool(transpose_b)), _stream()))
     return [out[i] for i in range(len(a_list))]
 

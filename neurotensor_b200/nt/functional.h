@@ -198,7 +198,8 @@ inline std::vector<Tensor> matmult(const std::vector<Tensor>& a, const std::vect
         }
         out.push_back(c);
     }
-    utils::check(ntb200_matmult_batch(dtype_code(a[0].dtype()), pa.data(), pb.data(), pc.data(), int64_t(pa.size()), ar, ac, br, bc,
+    // the raw contract takes the logical extents of op(a) and op(b); the flags say how they are stored
+    utils::check(ntb200_matmult_batch(dtype_code(a[0].dtype()), pa.data(), pb.data(), pc.data(), int64_t(pa.size()), m, k, k, n,
                                       trans_a, trans_b, nullptr));
     utils::check(ntb200_stream_synchronize(nullptr));
     return out;
