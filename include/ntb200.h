@@ -35,7 +35,15 @@ typedef enum ntb200_dtype {
     NTB200_F64 = 7,
     NTB200_U8 = 8,
     NTB200_U16 = 9,
-    NTB200_U32 = 10
+    NTB200_U32 = 10,
+    /* Complex64 / Complex128 (interleaved re, im).  The reference's GEMM traits for these types are the plain float /
+     * double vector operations on the interleaved lanes (nt/mp/simde_traits/simde_traits_avx2.h:915-1000,1029-1110:
+     * broadcast = set1 of the pair, fmadd = _mm256_fmadd_ps / _pd), so its matmult multiplies real parts with real
+     * parts and imaginary parts with imaginary parts: C.re = A.re B.re, C.im = A.im B.im, each an exact sequential FMA
+     * chain.  These codes reproduce exactly that (bit for bit), on the CUDA-core route; they are NOT the mathematical
+     * complex product. */
+    NTB200_C64 = 11,
+    NTB200_C128 = 12
 } ntb200_dtype;
 
 typedef enum ntb200_status {

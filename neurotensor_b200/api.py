@@ -24,6 +24,8 @@ _TORCH_TO_CODE = {
     torch.float32: _lib.F32, torch.float16: _lib.F16, torch.bfloat16: _lib.BF16, torch.int8: _lib.I8,
     torch.int16: _lib.I16, torch.int32: _lib.I32, torch.int64: _lib.I64, torch.float64: _lib.F64,
     torch.uint8: _lib.U8,
+    # interleaved (re, im); the reference's componentwise semantics, see NTB200_C64 in include/ntb200.h
+    torch.complex64: _lib.C64, torch.complex128: _lib.C128,
 }
 
 

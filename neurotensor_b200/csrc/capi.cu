@@ -44,15 +44,16 @@ size_t dtype_size(int dtype) {
         case NTB200_F32: case NTB200_I32: case NTB200_U32: return 4;
         case NTB200_F16: case NTB200_BF16: case NTB200_I16: case NTB200_U16: return 2;
         case NTB200_I8: case NTB200_U8: return 1;
-        case NTB200_I64: case NTB200_F64: return 8;
+        case NTB200_I64: case NTB200_F64: case NTB200_C64: return 8;
+        case NTB200_C128: return 16;
     }
     return 0;
 }
 
 const char* dtype_name(int dtype) {
     static const char* names[] = {"Float32", "Float16", "BFloat16", "int8", "int16", "int32",
-                                  "int64",   "Float64", "uint8",    "uint16", "uint32"};
-    return (dtype >= 0 && dtype <= NTB200_U32) ? names[dtype] : "unknown";
+                                  "int64",   "Float64", "uint8",    "uint16", "uint32", "Complex64", "Complex128"};
+    return (dtype >= 0 && dtype <= NTB200_C128) ? names[dtype] : "unknown";
 }
 
 void count_launch(int n) { g_launches.fetch_add(uint64_t(n), std::memory_order_relaxed); }
@@ -98,6 +99,11 @@ int run_gemm(GemmArgs g, int route, cudaStream_t stream) {
     if (g.k == 0) {
         if (g.accumulate && !g.bias) return NTB200_OK;  // C += 0
         return launch_fill_c(g, stream);
+    }
+    // Complex64 / Complex128: the reference's componentwise chains, CUDA-core route only.
+    if (g.dtype == NTB200_C64 || g.dtype == NTB200_C128) {
+        if (route == NTB200_ROUTE_TENSOR) return fail(NTB200_ERR_UNSUPPORTED, "matmult: complex dtypes run on the CUDA-core route only");
+        route = NTB200_ROUTE_SIMT;
     }
     // Float32: the exact one-chain CUDA-core kernel for small problems (and always with NTB200_FP32_MODE=ffma);
     // three-TF32-product tensor-core kernel (within 1e-5 relative Frobenius error) once the problem is large

@@ -58,6 +58,29 @@ template <> struct Num<__nv_bfloat16> {
     static __device__ __forceinline__ Acc fma(Acc a, Acc b, Acc c) { return fmaf(a, b, c); }
     static __device__ __forceinline__ Acc round_tile(Acc v) { return v; }
 };
+// Complex64 / Complex128 as the reference's SIMD traits treat them: a pair of independent lanes.  fmadd on the
+// interleaved vector multiplies re with re and im with im (simde_traits_avx2.h:996-998, 1107-1109).
+template <class F> struct Cplx {
+    F re, im;
+    Cplx() = default;
+    __host__ __device__ explicit Cplx(int) : re(F(0)), im(F(0)) {}
+    __host__ __device__ Cplx(F r, F i) : re(r), im(i) {}
+};
+template <class F> __device__ __forceinline__ Cplx<F> operator+(Cplx<F> a, Cplx<F> b) { return Cplx<F>(a.re + b.re, a.im + b.im); }
+template <> struct Num<Cplx<float>> {
+    using Acc = Cplx<float>;
+    static __device__ __forceinline__ Acc widen(Acc v) { return v; }
+    static __device__ __forceinline__ Acc narrow(Acc v) { return v; }
+    static __device__ __forceinline__ Acc fma(Acc a, Acc b, Acc c) { return Acc(fmaf(a.re, b.re, c.re), fmaf(a.im, b.im, c.im)); }
+    static __device__ __forceinline__ Acc round_tile(Acc v) { return v; }
+};
+template <> struct Num<Cplx<double>> {
+    using Acc = Cplx<double>;
+    static __device__ __forceinline__ Acc widen(Acc v) { return v; }
+    static __device__ __forceinline__ Acc narrow(Acc v) { return v; }
+    static __device__ __forceinline__ Acc fma(Acc a, Acc b, Acc c) { return Acc(::fma(a.re, b.re, c.re), ::fma(a.im, b.im, c.im)); }
+    static __device__ __forceinline__ Acc round_tile(Acc v) { return v; }
+};
 template <class U, class A> struct IntNum {
     using Acc = A;
     static __device__ __forceinline__ Acc widen(U v) { return Acc(v); }
@@ -75,7 +98,7 @@ __global__ void __launch_bounds__(kThreads)
 simt_gemm_kernel(const SimtParams p) {
     using N = Num<T>;
     using Acc = typename N::Acc;
-    constexpr int BK = sizeof(Acc) == 8 ? 8 : 16;
+    constexpr int BK = sizeof(Acc) >= 16 ? 4 : (sizeof(Acc) == 8 ? 8 : 16);
     constexpr int kLoads = kBM * BK / kThreads;  // elements of each operand tile per thread
     // +4 elements of padding per row: rows stay 16-byte aligned for vector reads, and the transposing stores of a
     // K-contiguous operand (16 consecutive k of one row per half-warp) spread over the banks instead of hitting one
@@ -317,6 +340,8 @@ int dispatch(const GemmArgs& g, cudaStream_t stream, bool fill_only) {
         case NTB200_I16: case NTB200_U16: return launch_typed<uint16_t>(g, stream, fill_only);
         case NTB200_I32: case NTB200_U32: return launch_typed<uint32_t>(g, stream, fill_only);
         case NTB200_I64: return launch_typed<unsigned long long>(g, stream, fill_only);
+        case NTB200_C64: return launch_typed<Cplx<float>>(g, stream, fill_only);
+        case NTB200_C128: return launch_typed<Cplx<double>>(g, stream, fill_only);
     }
     return fail(NTB200_ERR_UNSUPPORTED, "unknown dtype %d", g.dtype);
 }

@@ -112,6 +112,16 @@ def matmult(a, b, transpose_a=False, transpose_b=False, bf16=False, threads=None
         raise ValueError("matmult needs tensors of at least 2 dims")
     if a.dtype != b.dtype:
         raise ValueError("matmult operands must share a dtype")
+    if np.iscomplexobj(a):
+        # Complex64 / Complex128: the SIMD traits of these types are the float / double operations on the interleaved
+        # (re, im) lanes (nt/mp/simde_traits/simde_traits_avx2.h:915-1000, 1029-1110: broadcast = set1 of the pair,
+        # fmadd = _mm256_fmadd_ps / _pd), so the microkernel multiplies re with re and im with im: two independent
+        # real matmults, not the mathematical complex product.
+        out_re = matmult(np.ascontiguousarray(a.real), np.ascontiguousarray(b.real), transpose_a, transpose_b, False, threads)
+        out_im = matmult(np.ascontiguousarray(a.imag), np.ascontiguousarray(b.imag), transpose_a, transpose_b, False, threads)
+        out = np.empty(out_re.shape, dtype=a.dtype)
+        out.real, out.imag = out_re, out_im
+        return out
     am, ak = (a.shape[-1], a.shape[-2]) if transpose_a else a.shape[-2:]
     bk, bn = (b.shape[-1], b.shape[-2]) if transpose_b else b.shape[-2:]
     if ak != bk:

@@ -504,3 +504,35 @@ def test_hodge_laplacian_products(api, oracle):
     exp = oracle.matmult(bkp1, bkp1.T.copy()) + oracle.matmult(bk.T.copy(), bk)
     assert np.array_equal(host(got), exp.astype(np.float32))
     assert np.array_equal(host(api.hodge_laplacian_from_boundaries(dev(bkp1))), oracle.matmult(bkp1, bkp1.T.copy()))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("np_dtype", [np.complex64, np.complex128])
+def test_complex_matmult_is_the_references_lanewise_product(api, oracle, L, np_dtype):
+    """Complex64 / Complex128: the reference's SIMD traits multiply the interleaved (re, im) lanes independently, so its
+    matmult gives C.re = A.re B.re and C.im = A.im B.im as two exact FMA chains; the CUDA-core route reproduces that bit
+    for bit (2-D, batched with a lower-rank operand, transposed views, C +=), and a tensor-core request is refused."""
+    rng = np.random.default_rng(107)
+    fdt = np.float32 if np_dtype == np.complex64 else np.float64
+    cplx = lambda shape: (normal(rng, shape, fdt) + 1j * normal(rng, shape, fdt)).astype(np_dtype)
+    a, b = cplx((3, 70, 45)), cplx((45, 133))
+    got = api.matmult(dev(a), dev(b))
+    assert L.last_route() == "simt"
+    exp = oracle.matmult(a, b)
+    assert np.array_equal(host(got), exp)
+    assert not np.allclose(exp, a @ b)                   # not the mathematical product
+    assert np.array_equal(exp.real, oracle.matmult(np.ascontiguousarray(a.real), np.ascontiguousarray(b.real)))
+    bt = cplx((133, 45))
+    got_t = api.matmult(dev(a), dev(bt), transpose_b=True)
+    assert np.array_equal(host(got_t), oracle.matmult(a, bt, transpose_b=True))
+    at = cplx((3, 45, 70))
+    assert np.array_equal(host(api.matmult(dev(at), dev(b), transpose_a=True)), oracle.matmult(at, b, transpose_a=True))
+    # C += : the chains continue from the previous contents, lane by lane
+    c0 = cplx((70, 133))
+    out = dev(c0.copy())
+    api.matmult(dev(a[0]), dev(b), out=out)
+    exp_re = oracle.matmult_into(np.ascontiguousarray(a[0].real), np.ascontiguousarray(b.real), np.ascontiguousarray(c0.real))
+    exp_im = oracle.matmult_into(np.ascontiguousarray(a[0].imag), np.ascontiguousarray(b.imag), np.ascontiguousarray(c0.imag))
+    assert np.array_equal(host(out).real, exp_re) and np.array_equal(host(out).imag, exp_im)
+    with pytest.raises(L.Ntb200Error):
+        api.matmult(dev(a), dev(b), route=L.ROUTE_TENSOR)

@@ -171,3 +171,19 @@ def test_empty_and_ragged(oracle):
         a = rng.integers(-3, 3, (m, k)).astype(np.float32)
         b = rng.integers(-3, 3, (k, n)).astype(np.float32)
         assert np.array_equal(oracle.matmult(a, b), a @ b)
+
+
+def test_complex_matmult_follows_the_simd_traits_lanes():
+    """The reference's complex GEMM traits are the float / double lane operations on interleaved (re, im) data
+    (simde_traits_avx2.h:915-1000, 1029-1110), so matmult gives re x re and im x im as independent real chains."""
+    from oracle import oracle
+    rng = np.random.default_rng(5)
+    for cdt, fdt in ((np.complex64, np.float32), (np.complex128, np.float64)):
+        a = (rng.standard_normal((2, 9, 21)) + 1j * rng.standard_normal((2, 9, 21))).astype(cdt)
+        b = (rng.standard_normal((21, 13)) + 1j * rng.standard_normal((21, 13))).astype(cdt)
+        got = oracle.matmult(a, b)
+        assert got.dtype == cdt and got.shape == (2, 9, 13)
+        assert np.array_equal(got.real, oracle.matmult(np.ascontiguousarray(a.real), np.ascontiguousarray(b.real)))
+        assert np.array_equal(got.imag, oracle.matmult(np.ascontiguousarray(a.imag), np.ascontiguousarray(b.imag)))
+        assert got.real.dtype == fdt
+        assert not np.allclose(got, a @ b)
