@@ -3,7 +3,7 @@
     python -m neurotensor_b200.bench_configs [--steps K] [--cpu] [--only c1,c3i8,...]
 
 Rows: c1 (Float32 1024^3), c2 (batched Float16 64x2048^3, transposed-view B), c3i8 (Int8 4096x8192x4096),
-c3i32 (Int32 2048^3), c3i16 (Int16 4096^3), t8192 (Float16 / BFloat16 8192^3), skinny (1 / 2 / 16 / 128 rows x 8192 x 8192), midrows (256 - 512 rows against 2048 - 11008-wide weights), c4 (BFloat16 MLP 8192 x 4096->16384->4096: forward + backward step), c5 (Float16 conv2d
+c3i32 (Int32 2048^3), c3i16 (Int16 4096^3), f64 (Float64 4096^3 and Complex64 2048^3 on the CUDA-core route), t8192 (Float16 / BFloat16 8192^3), skinny (1 / 2 / 16 / 128 rows x 8192 x 8192), midrows (256 - 512 rows against 2048 - 11008-wide weights), c4 (BFloat16 MLP 8192 x 4096->16384->4096: forward + backward step), c5 (Float16 conv2d
 [32,256,56,56] * [256,256,3,3]), sweepN (Float32 N^3).  Inputs are seeded synthetic tensors of the stated shapes
 and distributions, resident on the device; time is CUDA events over K launches after 3 warm-ups.  `--cpu` also
 times the CPU oracle on a bounded sub-problem of each row (test infrastructure, scaled linearly, stated per row).
@@ -64,7 +64,7 @@ def main():
     def emit(name, seconds, flops, alg_bytes, bound, launches, note="", cpu=None):
         tf = flops / seconds / 1e12
         gbs = alg_bytes / seconds / 1e9
-        peak = {"tensor": tensor_peak, "tensor_i8": 3314.0, "ffma": ffma_peak, "imad": ffma_peak / 2}.get(bound)
+        peak = {"tensor": tensor_peak, "tensor_i8": 3314.0, "ffma": ffma_peak, "imad": ffma_peak / 2, "dfma": ffma_peak / 2}.get(bound)
         row = {"config": name, "ms": seconds * 1e3, "tflops_or_tops": tf, "algorithmic_GBps": gbs, "bound": bound,
                "frac_of_peak": (tf / peak) if peak else gbs / hbm_peak, "peak": peak if peak else hbm_peak,
                "peak_source": src if bound.startswith("tensor") or bound == "hbm" else "derived: SMs x lanes x 2 x max clock",
@@ -158,6 +158,21 @@ def main():
         s, l = timed(lambda: api.gemm(a, bt, c, transpose_b=True, route=_lib.ROUTE_SIMT), args.steps)
         emit("Float32 4096^3 CUDA-core route, B transposed", s, 2 * 4096 ** 3, 12 * 4096 ** 2, "ffma", l)
         del a, b, bt, c
+
+    if want("f64"):
+        # Float64 and Int64 exist on the CUDA-core route only (bit-exact chains); B200's FP64 rate is 1/2 of FP32 per SM
+        a, b = randn(gen, (4096, 4096), torch.float64), randn(gen, (4096, 4096), torch.float64)
+        c = torch.empty((4096, 4096), dtype=torch.float64, device="cuda")
+        s, l = timed(lambda: api.gemm(a, b, c), args.steps)
+        emit("Float64 4096^3 on the CUDA-core route", s, 2 * 4096 ** 3, 3 * 8 * 4096 ** 2, "dfma", l,
+             "peak = DFMA at half the FFMA rate (derived)")
+        ca = torch.view_as_complex(randn(gen, (2048, 2048, 2), torch.float32).contiguous())
+        cb = torch.view_as_complex(randn(gen, (2048, 2048, 2), torch.float32).contiguous())
+        cc = torch.empty((2048, 2048), dtype=torch.complex64, device="cuda")
+        s, l = timed(lambda: api.gemm(ca, cb, cc), args.steps)
+        emit("Complex64 2048^3 (the reference's lane-wise product: two FMA chains per element)", s, 4 * 2048 ** 3,
+             3 * 8 * 2048 ** 2, "ffma", l)
+        del a, b, c, ca, cb, cc
 
     if want("c3i32"):
         a = torch.randint(-1000, 1001, (2048, 2048), generator=gen, device="cuda", dtype=torch.int32)
