@@ -132,6 +132,16 @@ __device__ __forceinline__ uint32_t from_float_bits16(float v, int out_kind) {
                                : (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v));
 }
 
+// Two fp32 values rounded to nearest-even and packed (first value in the low half): one cvt.rn.{f16x2,bf16x2}.f32.
+__device__ __forceinline__ uint32_t pack2_bits16(float lo, float hi, int out_kind) {
+    if (out_kind == kOutF16) {
+        const __half2 h = __floats2half2_rn(lo, hi);
+        return *reinterpret_cast<const uint32_t*>(&h);
+    }
+    const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
 // Stores 32 consecutive Float32 results of one row (bias and previous C added first).
 __device__ __forceinline__ void store_chunk_f32(const UmmaParams& p, int b, int row, int col0, const float* f_in) {
     float f[32];
@@ -404,19 +414,15 @@ __device__ __forceinline__ void epilogue_tile_tma(const UmmaParams& p, const CUt
     const uint8_t* c_row = static_cast<const uint8_t*>(p.c) + ((long long)b * p.c_bs + (long long)row * p.c_rs) * es;
     if (lane == 0) tma_store_wait_read();
     __syncwarp();
-#pragma unroll 1
-    for (int cc = 0; cc < BN / 32; ++cc) {
+    // One 32-column chunk of this thread's row: convert, stage in shared memory, hand finished sub-tiles to TMA.
+    auto process = [&](uint32_t (&v)[32], int cc) {
         const int col0 = n0 + cc * 32;
-        if (col0 >= p.n) break;  // uniform across the CTA
-        const int sub = cc / per_sub, in_sub = cc - sub * per_sub;
+        const int sub = i8 ? (cc >> 2) : (cc >> 1), in_sub = cc - sub * per_sub;
         const int buf_c = p.has_relu_out ? ((2 * sub) & 3) : sub;
         if (p.has_relu_out && in_sub == 0 && sub >= 2) {   // buffers of sub-tile (sub - 2) come round again
             if (lane == 0) tma_store_wait_read_but2();
             __syncwarp();
         }
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(tmem_acc + uint32_t(cc * 32), v);
-        tmem_ld_wait();
         const bool full_chunk = col0 + 32 <= p.n;
         uint32_t w[16];                            // the chunk's 32 outputs, packed (16-bit: 16 words, 8-bit: 8 words)
         if (i8) {
@@ -482,8 +488,7 @@ __device__ __forceinline__ void epilogue_tile_tma(const UmmaParams& p, const CUt
                 }
             }
 #pragma unroll
-            for (int q = 0; q < 16; ++q)
-                w[q] = from_float_bits16(f[2 * q], p.out_kind) | (from_float_bits16(f[2 * q + 1], p.out_kind) << 16);
+            for (int q = 0; q < 16; ++q) w[q] = pack2_bits16(f[2 * q], f[2 * q + 1], p.out_kind);
         }
         const uint32_t row_c = staging + uint32_t(buf_c) * 4096u + uint32_t(lane) * 128u;
         for (int q = 0; q < pieces; ++q) {
@@ -525,7 +530,25 @@ __device__ __forceinline__ void epilogue_tile_tma(const UmmaParams& p, const CUt
                 }
             }
         }
+    };
+    // The tensor-memory load of the next chunk is in flight while the current one is converted and staged (two
+    // register sets, the loop unrolled by two so that both are addressed statically).  Loads past the last column of
+    // C read accumulator columns that are never used; no load is left outstanding on return.
+    constexpr int kChunks = BN / 32;
+    static_assert(kChunks % 2 == 0, "the chunk loop is unrolled by two");
+    uint32_t va[32], vb[32];
+    tmem_ld_32x32b_x32(tmem_acc, va);
+#pragma unroll 1
+    for (int cc = 0; cc < kChunks; cc += 2) {
+        if (n0 + cc * 32 >= p.n) break;  // uniform across the CTA
+        tmem_ld_wait();
+        tmem_ld_32x32b_x32(tmem_acc + uint32_t((cc + 1) * 32), vb);
+        process(va, cc);
+        tmem_ld_wait();
+        if (cc + 2 < kChunks) tmem_ld_32x32b_x32(tmem_acc + uint32_t((cc + 2) * 32), va);
+        if (n0 + (cc + 1) * 32 < p.n) process(vb, cc + 1);
     }
+    tmem_ld_wait();
 }
 
 template <MmaKind kKind, int BN, bool kSplit>
