@@ -789,8 +789,10 @@ struct PairTile {
     static constexpr uint32_t kSmemBytes = kStages * kStageBytes + kStagingBytes + 256 + 1024;
 };
 
-template <MmaKind kKind, bool kSplit>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kSplit ? kThreadsSplit : kThreads, 1)
+// kEpi = 8 (16- and 8-bit outputs through TMA stores, no second output): two epilogue warps per lane quadrant, each
+// taking 128 of the tile's 256 columns, for shallow K where the epilogue, not the main loop, bounds a tile.
+template <MmaKind kKind, bool kSplit, int kEpi = 4>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__((kSplit || kEpi == 8) ? kThreadsSplit : kThreads, 1)
 umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                       const __grid_constant__ CUtensorMap tma_a_lo, const __grid_constant__ CUtensorMap tma_b_lo,
                       const __grid_constant__ CUtensorMap tma_c, const __grid_constant__ CUtensorMap tma_relu,
@@ -824,7 +826,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(tfull_bar(a), 1);
-            mbar_init(tempty_bar(a), kSplit ? 16 : 8);   // one arrival per epilogue warp of both CTAs
+            mbar_init(tempty_bar(a), (kSplit || kEpi == 8) ? 16 : 8);   // one arrival per epilogue warp of both CTAs
         }
         *abort_flag = 0;
         fence_barrier_init();
@@ -990,7 +992,17 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
                 break;
             }
             tcgen05_fence_after();
-            if constexpr (!kSplit) {
+            if constexpr (!kSplit && kEpi == 8) {
+                const int half = (warp - 2) >> 2;   // warps 2-5: columns 0-127, warps 6-9: columns 128-255
+                if (p.tma_store)
+                    epilogue_tile_tma<128>(p, &tma_c, &tma_relu, &tma_peers,
+                                           tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN + half * 128),
+                                           staging_base + uint32_t(warp - 2) * 8192u, b, mi * 256 + int(rank) * 128 + quad * 32,
+                                           lane, ni * BN + half * 128);
+                else
+                    epilogue_tile<128>(p, tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN + half * 128), b,
+                                       mi * 256 + row_in_tile, ni * BN + half * 128);
+            } else if constexpr (!kSplit) {
                 if (p.tma_store)
                     epilogue_tile_tma<BN>(p, &tma_c, &tma_relu, &tma_peers, tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN),
                                           staging_base + uint32_t(quad) * 16384u, b, mi * 256 + int(rank) * 128 + quad * 32,
@@ -1097,6 +1109,7 @@ const char* plan_operand(const void* ptr, int es, CUtensorMapDataType dt, int64_
 const bool g_disable_pair = [] { const char* e = getenv("NTB200_NO_PAIR"); return e && e[0] == '1'; }();
 
 // NTB200_FULL_A_TILE=1 always stages all 128 rows of A in the single-CTA kernel (for A/B measurements).
+const bool g_four_epilogue_warps = [] { const char* e = getenv("NTB200_FOUR_EPILOGUE_WARPS"); return e && e[0] == '1'; }();
 const bool g_full_a_tile = [] { const char* e = getenv("NTB200_FULL_A_TILE"); return e && e[0] == '1'; }();
 // NTB200_TUNE=1 at load time makes every launch re-read NTB200_FORCE_BN (64 / 128 / 256), NTB200_FORCE_SPLITS (K slices)
 // and NTB200_NO_PAIR from the environment: the knobs the tile heuristics were fitted with.
@@ -1224,19 +1237,24 @@ int resident_pairs_query(const void* kernel, uint32_t smem_bytes) {
     return std::min(n, sm_count() / 2);
 }
 
-template <MmaKind kKind, bool kSplit>
+template <MmaKind kKind, bool kSplit, int kEpi = 4>
 int launch_pair_instance(const Maps& m, const UmmaParams& p, cudaStream_t stream) {
+    // Shallow K, plain TMA-store epilogue: the instantiation with eight epilogue warps
+    if constexpr (!kSplit && kEpi == 4) {
+        if (p.tma_store && !p.has_relu_out && p.k_blocks <= 6 && !g_four_epilogue_warps)
+            return launch_pair_instance<kKind, kSplit, 8>(m, p, stream);
+    }
     constexpr uint32_t smem = PairTile<kSplit>::kSmemBytes;
-    cudaError_t e = cudaFuncSetAttribute(umma_gemm_pair_kernel<kKind, kSplit>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    cudaError_t e = cudaFuncSetAttribute(umma_gemm_pair_kernel<kKind, kSplit, kEpi>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
     if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(umma_gemm_pair_kernel)");
     static int cached[64] = {0};  // per instantiation, per device
     int dev = 0;
     (void)cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) dev = 0;
     if (cached[dev] == 0)
-        cached[dev] = resident_pairs_query(reinterpret_cast<const void*>(umma_gemm_pair_kernel<kKind, kSplit>), smem);
+        cached[dev] = resident_pairs_query(reinterpret_cast<const void*>(umma_gemm_pair_kernel<kKind, kSplit, kEpi>), smem);
     const int pairs = std::min(p.total_tiles, cached[dev]);
-    umma_gemm_pair_kernel<kKind, kSplit><<<2 * pairs, kSplit ? kThreadsSplit : kThreads, smem, stream>>>(m.a.map, m.b.map, m.a_lo.map, m.b_lo.map, m.c, m.relu, m.peers, p);
+    umma_gemm_pair_kernel<kKind, kSplit, kEpi><<<2 * pairs, (kSplit || kEpi == 8) ? kThreadsSplit : kThreads, smem, stream>>>(m.a.map, m.b.map, m.a_lo.map, m.b_lo.map, m.c, m.relu, m.peers, p);
     count_launch();
     NTB200_CUDA(cudaGetLastError());
     return NTB200_OK;
