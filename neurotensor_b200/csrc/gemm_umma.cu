@@ -1351,6 +1351,10 @@ int launch_planned(const GemmArgs& g, const Planned& pl, const Side& a, const Si
     }
     if (g.n <= 64) bn = 64;
     else if (g.n <= 128 && bn > 128) bn = 128;
+    // Float32 split kernel: 64-wide tiles only pay while 128-wide ones would leave more than half of the SMs idle
+    // (measured: [512, 4096] x [4096, 4096] 0.211 -> 0.156 ms, [256, 8192] x [8192, 8192] 0.517 -> 0.411 ms on 128-wide
+    // tiles; 1024^3, 64 tiles of 128 columns, stays on 64-wide ones at 0.035 ms)
+    if (pl.split && bn == 64 && g.n > 64 && tiles_m * ((g.n + 127) / 128) * g.batch * 2 >= sms) bn = 128;
 
     // Large problems run on CTA pairs (256 x 256 tiles); anything with fewer pair tiles than TPCs keeps the
     // single-CTA kernel, whose narrower tiles spread small problems over more SMs.
