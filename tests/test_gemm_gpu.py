@@ -536,3 +536,42 @@ def test_complex_matmult_is_the_references_lanewise_product(api, oracle, L, np_d
     assert np.array_equal(host(out).real, exp_re) and np.array_equal(host(out).imag, exp_im)
     with pytest.raises(L.Ntb200Error):
         api.matmult(dev(a), dev(b), route=L.ROUTE_TENSOR)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("kind", ["f16", "bf16", "i8"])
+@pytest.mark.parametrize("m,n,k", [(300, 528, 48), (256, 512, 384), (515, 272, 144)])
+def test_shallow_k_takes_the_wide_epilogue(api, oracle, L, kind, m, n, k):
+    """At most six K blocks on CTA pairs: two epilogue warps per lane quadrant share a tile's 256 columns.  Ragged edges,
+    bias, C += and 8-bit outputs go through the same staging and TMA stores as the four-warp epilogue."""
+    rng = np.random.default_rng(113 + m)
+    if kind == "i8":
+        a, b = integers(rng, (m, k), np.int8, -128, 127), integers(rng, (k, n), np.int8, -128, 127)
+        c0 = integers(rng, (m, n), np.int8, -128, 127)
+        got = api.matmult(dev(a), dev(b))
+        assert L.last_route() == "umma_i8"
+        assert np.array_equal(host(got), oracle.matmult(a, b))
+        out = dev(c0.copy())
+        api.matmult(dev(a), dev(b), out=out)
+        assert np.array_equal(host(out), oracle.matmult_into(a, b, c0.copy()))
+        return
+    bf16 = kind == "bf16"
+    a32, b32 = normal(rng, (m, k), np.float32, 0.5), normal(rng, (k, n), np.float32, 0.5)
+    bias32, c32 = normal(rng, (n,), np.float32), normal(rng, (m, n), np.float32)
+    if bf16:
+        enc = lambda v: dev(oracle.bf16_round(v), bf16=True)
+        val = lambda v: oracle.bf16_widen(oracle.bf16_round(v))
+        dec = lambda t: oracle.bf16_widen(host(t))
+    else:
+        enc = lambda v: dev(v.astype(np.float16))
+        val = lambda v: v.astype(np.float16).astype(np.float32)
+        dec = lambda t: host(t).astype(np.float32)
+    exact = val(a32).astype(np.float64) @ val(b32).astype(np.float64)
+    got = api.linear(enc(a32), enc(b32), enc(bias32))
+    assert L.last_route() in ("umma_f16", "umma_bf16")
+    assert oracle.rel_fro(dec(got), exact + val(bias32)) <= 2e-3
+    out = enc(c32)
+    api.matmult(enc(a32), enc(b32), out=out)
+    assert oracle.rel_fro(dec(out), exact + val(c32)) <= 2e-3
+    bt = enc(np.ascontiguousarray(b32.T)).t()            # K-major B
+    assert oracle.rel_fro(dec(api.matmult(enc(a32), bt)), exact) <= 2e-3
