@@ -3,7 +3,7 @@
     python -m neurotensor_b200.bench_configs [--steps K] [--cpu] [--only c1,c3i8,...]
 
 Rows: c1 (Float32 1024^3), c2 (batched Float16 64x2048^3, transposed-view B), c3i8 (Int8 4096x8192x4096),
-c3i32 (Int32 2048^3), c3i16 (Int16 4096^3), f64 (Float64 4096^3 and Complex64 2048^3 on the CUDA-core route), t8192 (Float16 / BFloat16 8192^3), skinny (1 / 2 / 16 / 128 rows x 8192 x 8192), midrows (256 - 512 rows against 2048 - 11008-wide weights), c4 (BFloat16 MLP 8192 x 4096->16384->4096: forward + backward step), c5 (Float16 conv2d
+c3i32 (Int32 2048^3), c3i16 (Int16 4096^3), f64 (Float64 4096^3 and Complex64 2048^3 on the CUDA-core route), t8192 (Float16 / BFloat16 8192^3), skinny (1 / 2 / 16 / 128 rows x 8192 x 8192), midrows (256 - 512 rows against 2048 - 11008-wide weights), shallowk (8192 x k x 8192 with k = 16 / 256 / 1024), c4 (BFloat16 MLP 8192 x 4096->16384->4096: forward + backward step), c5 (Float16 conv2d
 [32,256,56,56] * [256,256,3,3]), sweepN (Float32 N^3).  Inputs are seeded synthetic tensors of the stated shapes
 and distributions, resident on the device; time is CUDA events over K launches after 3 warm-ups.  `--cpu` also
 times the CPU oracle on a bounded sub-problem of each row (test infrastructure, scaled linearly, stated per row).
@@ -138,6 +138,16 @@ def main():
             s, l = timed(lambda: api.gemm(a, b, c), args.steps)
             emit("midrows Float16 %dx%dx%d" % (m, k, n), s, 2 * m * n * k, (m * k + k * n + m * n) * 2, "tensor", l)
             del a, b, c
+
+    if want("shallowk"):
+        # weight-gradient shapes of a small batch: dW[8192, 8192] = X[k, 8192]^T . G[k, 8192]; writing C is the traffic
+        for k in (16, 256, 1024):
+            x, gr = randn(gen, (k, 8192), torch.float16, 0.1), randn(gen, (k, 8192), torch.float16, 0.1)
+            c = torch.empty((8192, 8192), dtype=torch.float16, device="cuda")
+            s, l = timed(lambda: api.gemm(x, gr, c, transpose_a=True), args.steps)
+            emit("shallowk Float16 8192x%dx8192 (A transposed view)" % k, s, 2 * 8192 * 8192 * k,
+                 (8192 * 8192 + 2 * k * 8192) * 2, "hbm" if k <= 256 else "tensor", l)
+            del x, gr, c
 
     if want("c3i8"):
         a = torch.randint(-8, 8, (4096, 8192), generator=gen, device="cuda", dtype=torch.int8)
