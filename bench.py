@@ -1,14 +1,19 @@
 #!/usr/bin/env python
-"""Benchmark of the matmult hot path on B200: BASELINE config 1 (the configuration the metric is quoted on):
-batched Float16 matmult, A[64,2048,2048] . B[64,2048,2048] with B passed as a transposed view, fp32
-accumulation.  One step = one pass of the whole batch.  With N GPUs every rank owns its own 64-item slice of a
-64*N-item batch (weak scaling, no collective on the data path).
+"""Benchmark of the matmult hot path on B200.  Workload: BASELINE.json's configs[1] (the second of its five
+configurations, the one the metric is quoted on): batched Float16 matmult, A[64,2048,2048] . B[64,2048,2048] with B
+passed as a transposed view, fp32 accumulation.  One step = one pass of the whole batch.  With N GPUs every rank owns
+its own 64-item slice of a 64*N-item batch (weak scaling, no collective on the data path).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python bench.py --configs [--cpu] [--only c1,c3i8,...]      # one JSON line per other configuration
 
 Prints ONE JSON line (rank 0).  `value` is device-resident throughput, `e2e` goes through the C-ABI
 host-buffer entry point with pinned host buffers (copies inside the timed region), `roofline` compares the
 GEMM kernel with the measured tensor-core peak, `cpu_baseline` is the CPU oracle timed on this box's cores.
+Secondary blocks on the same line: `sustained` (the same launch repeated for at least two seconds, against the
+sustained cuBLAS figure), `target_8192` (the 8192^3 Float16 / BFloat16 target shape) and, with more than one GPU,
+`mlp_n_sharded` (configs[3]: the BFloat16 MLP step with every GEMM split over its output columns, strong scaling,
+checked against the unsharded step).
 """
 import argparse
 import json
@@ -22,10 +27,11 @@ sys.path.insert(0, ROOT)
 
 BATCH, M, K, N = 64, 2048, 2048, 2048
 FLOPS_PER_ITEM = 2.0 * M * K * N
-WORKLOAD = "batched matmult Float16 A[64,2048,2048] x B[64,2048,2048]^T-view, fp32 accumulate (BASELINE config 1)"
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the GEMM kernel, from the ncu capture summarised in
-# profiles/umma_pair_f16_batched_2048.md: 174.6 MB for 8 items, scaled to the 64 items of a full launch (traffic
-# grows in proportion to the items).  Per batch item; multiplied by the items of the run below.
+WORKLOAD = ("batched matmult Float16 A[64,2048,2048] x B[64,2048,2048]^T-view, fp32 accumulate "
+            "(BASELINE.json configs[1], the second of the five configurations)")
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the GEMM kernel: not measured by this run (a profiler
+# cannot run inside a timed benchmark) but taken from a stored ncu capture of the same kernel on 8 items (134.3 MB
+# read + 43.0 MB written), scaled to the items of the run: the traffic grows in proportion to the items.
 NCU_DRAM_TRAFFIC_BYTES_PER_ITEM = (134.298880e6 + 43.018240e6) / 8
 
 
@@ -164,7 +170,18 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--items", type=int, default=BATCH,
                     help="batch items per GPU (default: the full 64); smaller values are for profiler captures only")
+    ap.add_argument("--no-extras", action="store_true", help="skip the sustained / target_8192 / mlp_n_sharded blocks")
+    ap.add_argument("--configs", action="store_true", help="time the other configurations instead (one JSON line each)")
+    ap.add_argument("--cpu", action="store_true", help="with --configs: also time the CPU oracle on a bounded sample of each row")
+    ap.add_argument("--only", default="", help="with --configs: comma-separated row names")
     args = ap.parse_args()
+    if args.configs:
+        from neurotensor_b200 import bench_configs
+        cpu_oracle = None
+        if args.cpu:                                  # the oracle is test infrastructure: it is handed in from here
+            from oracle import oracle as cpu_oracle
+            cpu_oracle.build()
+        return bench_configs.run(steps=min(args.steps, 20), only=args.only, oracle=cpu_oracle)
     rank, world, local_rank = env_int("RANK", 0), env_int("WORLD_SIZE", 1), env_int("LOCAL_RANK", 0)
     if args.impl == "reference":
         run_reference(args, rank, world)
@@ -249,12 +266,67 @@ def main():
                "ms_per_step": e_ms, "steps": e_steps, "matches_device_result": ok,
                "api": "ntb200_matmult_host (C ABI, pinned host buffers)"}
 
+    peaks = measured_peaks()
+    extras = {}
+    if not args.no_extras and args.items == BATCH:
+        # ---- the same launch repeated for at least two seconds: what the GPU sustains under its power cap
+        barrier()
+        loop = max(50, int(2.2 / (ms_per_step * 1e-3)))
+        sus_sampler = ClockSampler(local_rank)
+        sus_sampler.start()
+        ev0.record()
+        for _ in range(loop):
+            step()
+        ev1.record()
+        barrier()
+        sus_clocks = sus_sampler.finish()
+        sus_ms = ev0.elapsed_time(ev1)
+        if dist is not None:
+            t = torch.tensor([sus_ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            sus_ms = float(t.item())
+        sus_tflops = count * FLOPS_PER_ITEM * loop / (sus_ms * 1e-3) / 1e12          # per GPU
+        sus_peak = peaks["tflops_sustained"] or peaks["tflops_burst"]
+        extras["sustained"] = {"seconds": sus_ms * 1e-3, "launches": loop, "tflops_per_gpu": sus_tflops,
+                               "peak": sus_peak, "frac": sus_tflops / sus_peak,
+                               "peak_source": "%s (sustained bf16 cuBLAS figure)" % peaks["source"], "clocks": sus_clocks}
+        # ---- the 8192^3 target shape, Float16 and BFloat16 (every rank runs its own copy; rank 0's numbers are reported)
+        target = {}
+        for name, dt in (("f16", torch.float16), ("bf16", torch.bfloat16)):
+            ta = (torch.randn((8192, 8192), generator=gen, device="cuda") * 0.1).to(dt)
+            tb = (torch.randn((8192, 8192), generator=gen, device="cuda") * 0.1).to(dt)
+            tc = torch.empty((8192, 8192), dtype=dt, device="cuda")
+            for _ in range(3):
+                api.gemm(ta, tb, tc)
+            torch.cuda.synchronize()
+            ev0.record()
+            for _ in range(20):
+                api.gemm(ta, tb, tc)
+            ev1.record()
+            torch.cuda.synchronize()
+            t_ms = ev0.elapsed_time(ev1) / 20
+            tf = 2.0 * 8192 ** 3 / (t_ms * 1e-3) / 1e12
+            target[name] = {"ms": t_ms, "tflops": tf, "frac_of_burst_peak": tf / peaks["tflops_burst"], "route": _lib.last_route()}
+            del ta, tb, tc
+        target["peak"] = peaks["tflops_burst"]
+        target["note"] = "20 launches after 3 warm-ups, operands (403 MB) exceed the L2"
+        extras["target_8192"] = target
+        # ---- more than one GPU: the N-sharded MLP step (strong scaling) through the C-ABI partitioner
+        if world > 1:
+            from neurotensor_b200 import bench_mlp_sharded
+            rec = bench_mlp_sharded.measure(rank, world, dist, steps=10, check=True)
+            chk = rec.get("check") or {}
+            extras["mlp_n_sharded"] = {"workload": "BASELINE.json configs[3]: BFloat16 MLP 8192 x (4096 -> 16384 -> 4096), forward + backward, "
+                                                   "every GEMM split over its output columns", "scaling": "strong",
+                                       "ms_per_step": rec["ms_per_step"], "tflops": rec["tflops"], "gather": rec["gather"],
+                                       "kernels_per_step": rec["kernels_per_step_rank0"],
+                                       "matches_unsharded": bool(chk.get("bit_identical", False)), "check": chk}
+
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
         return 0
 
-    peaks = measured_peaks()
     per_gpu_tflops = count * FLOPS_PER_ITEM / (ms_per_step * 1e-3) / 1e12
     timed_s = ms * 1e-3
     peak_kind = "sustained" if (timed_s > 1.0 and peaks["tflops_sustained"] > 0) else "burst"
@@ -268,11 +340,13 @@ def main():
                    "l2": "inputs (1.6 GB per step) exceed the 126 MB L2; no flush needed", "kernel": route},
         "roofline": {"bound": "tensor", "achieved": per_gpu_tflops, "peak": peak, "unit": "TFLOP/s",
                      "frac": per_gpu_tflops / peak, "traffic": NCU_DRAM_TRAFFIC_BYTES_PER_ITEM * count,
+                     "traffic_source": "stored ncu profile of the same kernel on 8 items, scaled by the items per launch",
                      "peak_source": "%s (%s bf16 cuBLAS figure)" % (peaks["source"], peak_kind),
                      "algorithmic_flops_per_launch": count * FLOPS_PER_ITEM,
                      "algorithmic_bytes_per_launch": 3 * count * M * N * 2},
         "clocks": clocks, "gpu_launches": int(launches),
     }
+    line.update(extras)
     if e2e is not None:
         line["e2e"] = e2e
     if world == 1 and not args.no_cpu_baseline:

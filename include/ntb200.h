@@ -122,8 +122,22 @@ int ntb200_host_free(void* ptr);
 int ntb200_host_register(void* ptr, size_t bytes);
 int ntb200_host_unregister(void* ptr);
 /* Bytes currently held / high-water mark of the pool: the device counterpart of
- * nt::utils::getAllocatedMemory (nt/memory/track_memory.h:23-35). */
+ * nt::utils::getAllocatedMemory (nt/memory/track_memory.h:23-35).  Counts ntb200_malloc_async blocks. */
 int ntb200_pool_stats(uint64_t* bytes_in_use, uint64_t* high_water);
+/* Scratch of the library's own kernels (no counterpart in the reference, whose pack buffers are static arrays,
+ * nt/functional/cpu/matmult/nt_matmult_macros.h:60-71).  Routes that copy or slice their operands (Float32 as three
+ * TF32 products, integer limb planes, K slices, weight streaming) take a block from the stream-ordered pool and keep
+ * it for the next call on the same (device, stream), so a GEMM call allocates nothing once its stream is warm.
+ * Blocks above NTB200_SCRATCH_KEEP_MB (environment, default 512) are allocated and freed per call.
+ * scratch_stats: bytes kept right now, blocks handed out so far, and how many of those needed a new allocation.
+ * scratch_release_all: returns every idle kept block to the pool (waits for the kernels still using them). */
+int ntb200_scratch_stats(uint64_t* retained_bytes, uint64_t* acquisitions, uint64_t* allocations);
+int ntb200_scratch_release_all(void);
+/* The current device's default stream-ordered pool as the CUDA runtime accounts for it: bytes handed out now, their
+ * high-water mark (reset_high != 0 first resets the mark to zero) and bytes the pool holds from the driver.  Every
+ * allocation this library makes on a compute path goes through that pool, so a caller can check that a call
+ * allocated nothing. */
+int ntb200_device_pool_usage(uint64_t* used_now, uint64_t* used_high, uint64_t* reserved_now, int reset_high);
 
 /* Optional fused neighbours of Linear for ntb200_gemm_fused (F16 / BF16 on the tensor-core route, accumulate = 0).
  * Both tensors have exactly C's layout (same row and batch strides); a NULL member is simply not used.
@@ -161,6 +175,54 @@ int ntb200_peer_free(void* ptr);
 int ntb200_peer_export(const void* ptr, unsigned char handle[64]);
 int ntb200_peer_import(const unsigned char handle[64], void** ptr);
 int ntb200_peer_release(void* ptr);
+
+/* ---- the multi-GPU partitioner (no counterpart in the reference: its only device is the CPU,
+ * nt/memory/DeviceEnum.h:6-10).  One rank per GPU of one NVLink domain (up to 8): one process per rank, or one host
+ * thread per rank inside one process.  No communication library is linked: ranks exchange 88-byte buffer records at
+ * set-up through the caller's all-gather callback (torch.distributed, MPI, a socket; a shared array between threads),
+ * data crosses NVLink as stores from the GEMM epilogues into peer-mapped buffers, and ranks are ordered by a flag
+ * exchange kernel whose polls are bounded (two seconds, then NTB200_ERR_TIMEOUT from ntb200_check_device_status).
+ *
+ *   ntb200_dist_shard            which units of `total` belong to `rank`: contiguous blocks of `align` units, the first
+ *                                (blocks % world) ranks one block more.  Batched matmult shards its batch with
+ *                                align = 1 and needs nothing else: items are independent
+ *                                (nt/functional/cpu/matmult/nt_matmult.hpp:228-235 is a serial loop over them).
+ *                                A GEMM split over its output columns uses align = 8 (16-byte rows of 2-byte types).
+ *   ntb200_dist_init             collective over all ranks, with the rank's device current; `exchange` gathers
+ *                                `bytes` bytes of every rank, rank-major, into `recv` and returns 0 (may be NULL for one rank).
+ *   ntb200_dist_buffer_create    collective: `bytes` on every rank, each block mapped into every rank (zero-filled).
+ *   ntb200_dist_gemm_allgather   this rank's column block of C = bias + A.B goes to columns [col0, col0 + n) of the
+ *                                gathered [m, gathered_row_stride] matrix in EVERY rank's buffer, stored by the GEMM's
+ *                                epilogue, followed by ntb200_dist_barrier on the same stream: when work queued after
+ *                                the call runs, every rank's block has arrived here.  relu != 0: desc->c keeps the
+ *                                pre-activation block [m, n] and the gathered matrix receives max(C, 0) (Linear + ReLU
+ *                                of a column-sharded layer in one launch).  F16 / BF16; desc->c is ignored when relu == 0.
+ *                                A rank must not start the next gather into the same buffer while a slower rank may
+ *                                still read the previous one: alternate two buffers.
+ *   ntb200_dist_allgather_columns the same gather for a block that already exists (any dtype).
+ *   ntb200_dist_barrier          orders the ranks on `stream` (asynchronous for the host).  A rank whose peer does not
+ *                                arrive within the limit (default 2000 ms, ntb200_dist_set_barrier_limit_ms) gives up:
+ *                                the kernel returns, ntb200_check_device_status reports NTB200_ERR_TIMEOUT, the context
+ *                                stays usable, and the late peer's own barrier call still completes against the count
+ *                                this rank left behind, so the ranks are in step again afterwards. */
+typedef struct ntb200_dist_comm ntb200_dist_comm;
+typedef struct ntb200_dist_buffer ntb200_dist_buffer;
+typedef int (*ntb200_allgather_fn)(void* ctx, const void* send, void* recv, size_t bytes);
+int ntb200_dist_shard(int64_t total, int world, int rank, int64_t align, int64_t* start, int64_t* count);
+int ntb200_dist_init(ntb200_dist_comm** comm, int rank, int world, ntb200_allgather_fn exchange, void* ctx);
+int ntb200_dist_destroy(ntb200_dist_comm* comm);
+int ntb200_dist_rank(const ntb200_dist_comm* comm);
+int ntb200_dist_world(const ntb200_dist_comm* comm);
+int ntb200_dist_buffer_create(ntb200_dist_comm* comm, size_t bytes, ntb200_dist_buffer** buffer);
+int ntb200_dist_buffer_destroy(ntb200_dist_buffer* buffer);
+void* ntb200_dist_buffer_ptr(const ntb200_dist_buffer* buffer);   /* this rank's block (device pointer) */
+int ntb200_dist_barrier(ntb200_dist_comm* comm, void* stream);
+int ntb200_dist_set_barrier_limit_ms(ntb200_dist_comm* comm, unsigned int limit_ms);
+int ntb200_dist_gemm_allgather(ntb200_dist_comm* comm, const ntb200_gemm_desc* desc, ntb200_dist_buffer* gathered,
+                               int64_t gathered_row_stride, int64_t col0, int relu, void* stream);
+int ntb200_dist_allgather_columns(ntb200_dist_comm* comm, int dtype, const void* block, int64_t rows, int64_t cols,
+                                  int64_t block_row_stride, ntb200_dist_buffer* gathered, int64_t gathered_row_stride,
+                                  int64_t col0, void* stream);
 
 /* Replaces nt_matmult<T> (nt/functional/cpu/matmult/nt_matmult.h:6-7; call sites
  * nt/functional/cpu/matmult_cpu.cpp:118,150): C += op(A).op(B), row-major contiguous, a_rows/a_cols and
@@ -285,11 +347,17 @@ int ntb200_conv3d_backward_kernel(int dtype, const void* x, const void* grad, vo
  * cudaMalloc because it synchronises the device.  This variant takes the same inputs and output as
  * ntb200_conv2d but no workspace: the column matrix lives in a fixed array of
  * NTB200_CONV2D_STATIC_SCRATCH_BYTES inside the library, which every GPU that loads the library holds until
- * the process exits.  The call (and everything under it) uses no cudaMalloc / cudaFree / pool allocation.
+ * the process exits.  The call (and everything under it) uses no cudaMalloc / cudaFree / pool allocation: its GEMM
+ * keeps to the routes that need no scratch of their own, so Float32, Int16 and Int32 run on the CUDA-core kernel
+ * whatever their size (bit-exact, slower than ntb200_conv2d on large problems) and 16-bit floats never take K
+ * slices or the weight-streaming kernels.
  *   - A problem whose column matrix (ntb200_conv2d_workspace_bytes) is larger than the array is refused with
  *     NTB200_ERR_INVALID_ARG and a message naming both sizes; nothing is launched.
  *   - The first call on each device looks up the array's device address (one cudaGetSymbolAddress with that
- *     device current); make that first call before starting any stream capture.
+ *     device current); make that first call before starting any stream capture.  With CUDA's lazy module loading
+ *     (the default) the runtime also creates the array's 32 MiB of device storage at that moment, which fails with
+ *     NTB200_ERR_ALLOC if the application has already taken the whole heap: make the first call (any tiny valid
+ *     problem) before that, or run with CUDA_MODULE_LOADING=EAGER so the storage exists from library load on.
  *   - All calls on a device share the one array, and it keeps the previous call's contents.  Each call rewrites
  *     every element it reads, so stale contents never reach a result, but two calls that overlap on the GPU
  *     (different streams, no ordering between them) race on it: order them. */

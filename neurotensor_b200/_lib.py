@@ -40,6 +40,8 @@ class GemmEpilogue(ctypes.Structure):
     _fields_ = [("relu_out", _vp), ("relu_mask_src", _vp)]
 
 
+ALLGATHER_FN = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t)
+
 # name -> (restype, argtypes); every symbol include/ntb200.h declares
 SIGNATURES = {
     "ntb200_version": (ctypes.c_char_p, []),
@@ -63,6 +65,9 @@ SIGNATURES = {
     "ntb200_host_register": (_ci, [_vp, _sz]),
     "ntb200_host_unregister": (_ci, [_vp]),
     "ntb200_pool_stats": (_ci, [ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_uint64)]),
+    "ntb200_scratch_stats": (_ci, [ctypes.POINTER(ctypes.c_uint64)] * 3),
+    "ntb200_scratch_release_all": (_ci, []),
+    "ntb200_device_pool_usage": (_ci, [ctypes.POINTER(ctypes.c_uint64)] * 3 + [_ci]),
     "ntb200_gemm": (_ci, [ctypes.POINTER(GemmDesc), _vp]),
     "ntb200_gemm_fused": (_ci, [ctypes.POINTER(GemmDesc), ctypes.POINTER(GemmEpilogue), _vp]),
     "ntb200_gemm_push": (_ci, [ctypes.POINTER(GemmDesc), ctypes.POINTER(_vp), _ci, _vp]),
@@ -72,6 +77,18 @@ SIGNATURES = {
     "ntb200_peer_export": (_ci, [_vp, ctypes.c_char_p]),
     "ntb200_peer_import": (_ci, [ctypes.c_char_p, ctypes.POINTER(_vp)]),
     "ntb200_peer_release": (_ci, [_vp]),
+    "ntb200_dist_shard": (_ci, [_i64, _ci, _ci, _i64, ctypes.POINTER(_i64), ctypes.POINTER(_i64)]),
+    "ntb200_dist_init": (_ci, [ctypes.POINTER(_vp), _ci, _ci, ALLGATHER_FN, _vp]),
+    "ntb200_dist_destroy": (_ci, [_vp]),
+    "ntb200_dist_rank": (_ci, [_vp]),
+    "ntb200_dist_world": (_ci, [_vp]),
+    "ntb200_dist_buffer_create": (_ci, [_vp, _sz, ctypes.POINTER(_vp)]),
+    "ntb200_dist_buffer_destroy": (_ci, [_vp]),
+    "ntb200_dist_buffer_ptr": (_vp, [_vp]),
+    "ntb200_dist_barrier": (_ci, [_vp, _vp]),
+    "ntb200_dist_set_barrier_limit_ms": (_ci, [_vp, ctypes.c_uint]),
+    "ntb200_dist_gemm_allgather": (_ci, [_vp, ctypes.POINTER(GemmDesc), _vp, _i64, _i64, _ci, _vp]),
+    "ntb200_dist_allgather_columns": (_ci, [_vp, _ci, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _vp]),
     "ntb200_matmult": (_ci, [_ci, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _ci, _ci, _vp]),
     "ntb200_matmult_batch": (_ci, [_ci, ctypes.POINTER(_vp), ctypes.POINTER(_vp), ctypes.POINTER(_vp), _i64, _i64,
                                    _i64, _i64, _i64, _ci, _ci, _vp]),

@@ -1,12 +1,14 @@
 """Times every BASELINE configuration of the matmult path on one GPU and prints one JSON line per row.
 
-    python -m neurotensor_b200.bench_configs [--steps K] [--cpu] [--only c1,c3i8,...]
+    python bench.py --configs [--steps K] [--cpu] [--only c1,c3i8,...]
+    python -m neurotensor_b200.bench_configs [--steps K] [--only c1,c3i8,...]          # GPU rows only
 
 Rows: c1 (Float32 1024^3), c2 (batched Float16 64x2048^3, transposed-view B), c3i8 (Int8 4096x8192x4096),
 c3i32 (Int32 2048^3), c3i16 (Int16 4096^3), f64 (Float64 4096^3 and Complex64 2048^3 on the CUDA-core route), t8192 (Float16 / BFloat16 8192^3), skinny (1 / 2 / 16 / 128 rows x 8192 x 8192), midrows (256 - 512 rows against 2048 - 11008-wide weights), shallowk (8192 x k x 8192 with k = 16 / 256 / 1024), c4 (BFloat16 MLP 8192 x 4096->16384->4096: forward + backward step), c5 (Float16 conv2d
 [32,256,56,56] * [256,256,3,3]), sweepN (Float32 N^3).  Inputs are seeded synthetic tensors of the stated shapes
-and distributions, resident on the device; time is CUDA events over K launches after 3 warm-ups.  `--cpu` also
-times the CPU oracle on a bounded sub-problem of each row (test infrastructure, scaled linearly, stated per row).
+and distributions, resident on the device; time is CUDA events over K launches after 3 warm-ups.  Given a CPU
+oracle by its caller (bench.py --configs --cpu), it also times that on a bounded sub-problem of each row (scaled
+linearly, stated per row); this package itself never imports it.
 """
 import argparse
 import json
@@ -52,10 +54,19 @@ def randn(gen, shape, dtype, scale=1.0):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--cpu", action="store_true")
     ap.add_argument("--only", default="")
     args = ap.parse_args()
-    only = set(filter(None, args.only.split(",")))
+    return run(args.steps, args.only, None)
+
+
+def run(steps=20, only="", oracle=None):
+    """Times the rows named in `only` (all when empty).  `oracle`: the CPU oracle module for the per-row CPU figures, or
+    None for GPU rows only."""
+    class _Args:
+        pass
+    args = _Args()
+    args.steps, args.cpu = steps, oracle is not None
+    only = set(filter(None, only.split(",")))
     tensor_peak, hbm_peak, src = peaks()
     sm_clock_ghz = 1.965
     ffma_peak = 148 * 128 * 2 * sm_clock_ghz / 1e3  # TFLOP/s at the maximum SM clock
@@ -77,7 +88,6 @@ def main():
     def cpu_time(fn, scale, what):
         if not args.cpu:
             return None
-        from oracle import oracle
         fn(oracle)  # warm-up
         t0 = time.perf_counter()
         fn(oracle)

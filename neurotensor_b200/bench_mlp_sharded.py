@@ -1,4 +1,4 @@
-"""N-sharded MLP step (BASELINE config 3: BFloat16, batch 8192, 4096 -> 16384 -> 4096, ReLU, MSE) on the GPUs of one box.
+"""N-sharded MLP step (BASELINE.json configs[3], the fourth config: BFloat16, batch 8192, 4096 -> 16384 -> 4096, ReLU, MSE) on the GPUs of one box.
 
     python -m neurotensor_b200.bench_mlp_sharded                       # 1 GPU
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
@@ -24,23 +24,10 @@ if ROOT not in sys.path:
 from neurotensor_b200 import _lib, partition  # noqa: E402
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--steps", type=int, default=10)
-    ap.add_argument("--batch", type=int, default=8192)
-    ap.add_argument("--din", type=int, default=4096)
-    ap.add_argument("--hidden", type=int, default=16384)
-    ap.add_argument("--check", action="store_true")
-    ap.add_argument("--fused", action="store_true", help="(default) all-gathers fused into the GEMM epilogues: TMA stores into peer buffers")
-    ap.add_argument("--nccl", action="store_true", help="baseline: NCCL all-gather + re-tile kernel instead of the fused epilogues")
-    args = ap.parse_args()
-    rank, world, local = (int(os.environ.get(k, d)) for k, d in (("RANK", 0), ("WORLD_SIZE", 1), ("LOCAL_RANK", 0)))
-    torch.cuda.set_device(local)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    B, D, H = args.batch, args.din, args.hidden
+def measure(rank, world, dist=None, steps=10, batch=8192, din=4096, hidden=16384, check=False, nccl=False, warmup=3):
+    """Times the N-sharded step on the ranks of an initialised process group (dist = torch.distributed, or None for one
+    rank) and returns the result record on every rank (`check` is filled on rank 0 only)."""
+    B, D, H = batch, din, hidden
     dt = torch.bfloat16
     gen = torch.Generator(device="cuda").manual_seed(9)          # same seed on every rank: replicated tensors agree
     rn = lambda shape, s=1.0: (torch.randn(shape, generator=gen, device="cuda") * s).to(dt)
@@ -55,44 +42,71 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    fused = (not args.nccl) and world > 1
+    fused = (not nccl) and world > 1
     if fused:
         mlp.enable_fused_gather(B)
     step = mlp.step_fused if fused else mlp.step
-    for _ in range(3):
+    for _ in range(warmup):
         loss, grads = step(x, t)
     barrier()
     l0 = _lib.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
+    for _ in range(steps):
         loss, grads = step(x, t)
     e1.record()
     barrier()
-    ms = e0.elapsed_time(e1) / args.steps
-    launches = (_lib.launch_count() - l0) // args.steps
+    _lib.check(_lib.lib().ntb200_check_device_status(None))
+    ms = e0.elapsed_time(e1) / steps
+    launches = (_lib.launch_count() - l0) // steps
     if dist is not None:
         tt = torch.tensor([ms], device="cuda")
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         ms = float(tt.item())
-    check = None
-    if args.check and rank == 0:
+    result_check = None
+    if check and rank == 0:
         ref = partition.ShardedMLP(w1, b1, w2, b2, 0, 1)
         rloss, rg = ref.step(x, t)
         d0, dn = partition.column_shard(D, world, rank)
         rel = lambda a, b: float(((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-30)).item())
-        check = {"loss": [float(loss.item()), float(rloss.item())],
-                 "dw1": rel(grads["w1"], rg["w1"][:, h0:h0 + hn]), "dw2": rel(grads["w2"], rg["w2"][:, d0:d0 + dn]),
-                 "y": rel(grads["y"], rg["y"])}
-    if rank == 0:
-        flops = 5 * 2.0 * B * D * H
-        print(json.dumps({"config": "BFloat16 MLP %dx(%d->%d->%d) fwd+bwd step, N-sharded" % (B, D, H, D), "n_gpus": world,
-                          "ms_per_step": ms, "tflops": flops / (ms * 1e-3) / 1e12, "scaling": "strong",
-                          "kernels_per_step_rank0": int(launches), "collectives_per_step": 0 if world == 1 else 2, "gather": "fused peer stores + barrier" if fused else "NCCL all-gather + re-tile",
-                          "check": check}), flush=True)
+        result_check = {"loss": [float(loss.item()), float(rloss.item())],
+                        "dw1": rel(grads["w1"], rg["w1"][:, h0:h0 + hn]), "dw2": rel(grads["w2"], rg["w2"][:, d0:d0 + dn]),
+                        "y": rel(grads["y"], rg["y"]),
+                        "bit_identical": bool(torch.equal(grads["w1"], rg["w1"][:, h0:h0 + hn]) and
+                                              torch.equal(grads["w2"], rg["w2"][:, d0:d0 + dn]) and torch.equal(grads["y"], rg["y"]))}
+        del ref, rg
+    flops = 5 * 2.0 * B * D * H
+    record = {"config": "BFloat16 MLP %dx(%d->%d->%d) fwd+bwd step, N-sharded" % (B, D, H, D), "n_gpus": world,
+              "ms_per_step": ms, "tflops": flops / (ms * 1e-3) / 1e12, "scaling": "strong", "steps": steps,
+              "kernels_per_step_rank0": int(launches), "collectives_per_step": 0 if (world == 1 or fused) else 2,
+              "gather": ("stores from the GEMM epilogues into peer-mapped buffers + flag exchange (ntb200_dist_gemm_allgather)" if fused
+                         else ("none" if world == 1 else "NCCL all-gather + re-tile")),
+              "check": result_check}
     if fused:
         barrier()
         mlp.close()
+    return record
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--batch", type=int, default=8192)
+    ap.add_argument("--din", type=int, default=4096)
+    ap.add_argument("--hidden", type=int, default=16384)
+    ap.add_argument("--check", action="store_true")
+    ap.add_argument("--fused", action="store_true", help="(default) all-gathers fused into the GEMM epilogues: stores into peer buffers")
+    ap.add_argument("--nccl", action="store_true", help="baseline: NCCL all-gather + re-tile kernel instead of the fused epilogues")
+    args = ap.parse_args()
+    rank, world, local = (int(os.environ.get(k, d)) for k, d in (("RANK", 0), ("WORLD_SIZE", 1), ("LOCAL_RANK", 0)))
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    record = measure(rank, world, dist, args.steps, args.batch, args.din, args.hidden, args.check, args.nccl)
+    if rank == 0:
+        print(json.dumps(record), flush=True)
     if dist is not None:
         dist.destroy_process_group()
     return 0

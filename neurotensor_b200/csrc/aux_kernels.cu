@@ -557,8 +557,7 @@ int ntb200_column_sum(int dtype, const void* grad, void* out, int64_t rows, int6
         const int64_t rows_per_slab = (rows + slabs - 1) / slabs;
         slabs = (rows + rows_per_slab - 1) / rows_per_slab;
         float* partial = nullptr;
-        keep_pool_memory();
-        NTB200_CUDA(cudaMallocAsync(reinterpret_cast<void**>(&partial), size_t(slabs) * size_t(cols) * sizeof(float), s));
+        if (int rc = scratch_acquire(reinterpret_cast<void**>(&partial), size_t(slabs) * size_t(cols) * sizeof(float), s)) return rc;
         const dim3 grid(static_cast<unsigned>(col_blocks), static_cast<unsigned>(slabs), 1);
         const dim3 block(32, 8, 1);
         cudaError_t e = cudaSuccess;
@@ -570,7 +569,7 @@ int ntb200_column_sum(int dtype, const void* grad, void* out, int64_t rows, int6
             column_sum_final_kernel<__nv_bfloat16><<<unsigned((cols + 255) / 256), 256, 0, s>>>(partial, (__nv_bfloat16*)out, int(slabs), cols);
         }
         e = cudaGetLastError();
-        cudaFreeAsync(partial, s);
+        scratch_release(partial, s);
         count_launch(2);
         if (e != cudaSuccess) return cuda_fail(e, "column_sum kernels");
         return NTB200_OK;

@@ -62,28 +62,115 @@ void note_route(const char* name) { t_route = name; }
 // The stream-ordered pool keeps freed blocks instead of returning them to the driver at every synchronisation
 // (the default release threshold of 0 turns each allocate/free pair into a real cudaMalloc/cudaFree).
 void keep_pool_memory() {
-    static bool done[64] = {false};
+    static std::atomic<bool> done[64];   // zero-initialised; host threads may race here, setting it twice is harmless
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || done[dev]) return;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || done[dev].load(std::memory_order_acquire)) return;
     cudaMemPool_t pool;
     if (cudaDeviceGetDefaultMemPool(&pool, dev) == cudaSuccess) {
         unsigned long long keep = ~0ull;
         (void)cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
     }
     (void)cudaGetLastError();
-    done[dev] = true;
+    done[dev].store(true, std::memory_order_release);
 }
 
 int sm_count() {
-    static int cached[64] = {0};
+    static std::atomic<int> cached[64];  // zero-initialised
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-    if (cached[dev] == 0) {
-        int n = 0;
+    int n = cached[dev].load(std::memory_order_relaxed);
+    if (n == 0) {
         if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-        cached[dev] = n;
+        cached[dev].store(n, std::memory_order_relaxed);
     }
-    return cached[dev];
+    return n;
+}
+
+// ---- scratch of the library's own kernels ------------------------------------------------------------
+// Hi/lo copies of the Float32 split, limb planes, partial tiles of K slices.  A block is kept per (device, stream)
+// and handed to the next call on that stream: work on one stream runs in order, so the next kernel that writes the
+// block starts after the last one that read it, and a GEMM call makes no cudaMallocAsync / cudaFreeAsync once its
+// stream has a block that is large enough.  Blocks above the keep limit (NTB200_SCRATCH_KEEP_MB, default 512) are
+// allocated and freed in stream order per call, as are blocks for a second host thread launching on the same stream
+// at the same moment.
+namespace {
+struct ScratchBlock { int dev; cudaStream_t stream; void* ptr; size_t bytes; bool busy; uint64_t last_use; };
+std::mutex g_scratch_mu;
+std::vector<ScratchBlock> g_scratch;
+uint64_t g_scratch_tick = 0;
+std::atomic<uint64_t> g_scratch_acquires{0}, g_scratch_allocs{0};
+constexpr size_t kScratchCacheEntries = 16;
+size_t scratch_keep_limit() {
+    static const size_t limit = [] {
+        const char* e = getenv("NTB200_SCRATCH_KEEP_MB");
+        const long v = e ? atol(e) : 512;
+        return size_t(v < 0 ? 0 : v) << 20;
+    }();
+    return limit;
+}
+}  // namespace
+
+int scratch_acquire(void** out, size_t bytes, cudaStream_t stream) {
+    *out = nullptr;
+    if (bytes == 0) bytes = 256;
+    bytes = (bytes + ((size_t(1) << 20) - 1)) & ~((size_t(1) << 20) - 1);   // whole MiB: a slightly larger next call still fits
+    g_scratch_acquires.fetch_add(1, std::memory_order_relaxed);
+    int dev = 0;
+    NTB200_CUDA(cudaGetDevice(&dev));
+    const bool keep = bytes <= scratch_keep_limit();
+    void* stale = nullptr;
+    if (keep) {
+        std::lock_guard<std::mutex> lk(g_scratch_mu);
+        for (auto& b : g_scratch)
+            if (b.dev == dev && b.stream == stream && !b.busy) {
+                if (b.bytes >= bytes) {
+                    b.busy = true;
+                    b.last_use = ++g_scratch_tick;
+                    *out = b.ptr;
+                    return NTB200_OK;
+                }
+                stale = b.ptr;     // too small: replaced below (freed in stream order, after its last reader)
+                b = g_scratch.back();
+                g_scratch.pop_back();
+                break;
+            }
+    }
+    if (stale) (void)cudaFreeAsync(stale, stream);
+    keep_pool_memory();
+    g_scratch_allocs.fetch_add(1, std::memory_order_relaxed);
+    NTB200_CUDA(cudaMallocAsync(out, bytes, stream));
+    if (keep) {
+        void* evict = nullptr;
+        {
+            std::lock_guard<std::mutex> lk(g_scratch_mu);
+            if (g_scratch.size() >= kScratchCacheEntries) {   // drop the idle block that has not been used for longest
+                size_t victim = g_scratch.size();
+                for (size_t i = 0; i < g_scratch.size(); ++i)
+                    if (!g_scratch[i].busy && (victim == g_scratch.size() || g_scratch[i].last_use < g_scratch[victim].last_use)) victim = i;
+                if (victim < g_scratch.size()) {
+                    evict = g_scratch[victim].ptr;
+                    g_scratch[victim] = g_scratch.back();
+                    g_scratch.pop_back();
+                }
+            }
+            if (g_scratch.size() < kScratchCacheEntries) g_scratch.push_back({dev, stream, *out, bytes, true, ++g_scratch_tick});
+        }
+        if (evict) (void)cudaFree(evict);   // owned by another stream, which may be gone: the synchronising free is the safe one
+    }
+    return NTB200_OK;
+}
+
+void scratch_release(void* ptr, cudaStream_t stream) {
+    if (!ptr) return;
+    {
+        std::lock_guard<std::mutex> lk(g_scratch_mu);
+        for (auto& b : g_scratch)
+            if (b.ptr == ptr) {
+                b.busy = false;
+                return;
+            }
+    }
+    (void)cudaFreeAsync(ptr, stream);
 }
 
 namespace {
@@ -108,15 +195,22 @@ int run_gemm(GemmArgs g, int route, cudaStream_t stream) {
     // Float32: the exact one-chain CUDA-core kernel for small problems (and always with NTB200_FP32_MODE=ffma);
     // three-TF32-product tensor-core kernel (within 1e-5 relative Frobenius error) once the problem is large
     // enough to pay for the split pass.
-    if ((g.dtype == NTB200_I32 || g.dtype == NTB200_U32 || g.dtype == NTB200_I16 || g.dtype == NTB200_U16) && route == NTB200_ROUTE_AUTO &&
-        double(g.m) * double(g.n) * double(g.k) * double(g.batch) < 6.0e7)
+    const bool wide_int = g.dtype == NTB200_I32 || g.dtype == NTB200_U32 || g.dtype == NTB200_I16 || g.dtype == NTB200_U16;
+    if (wide_int && route == NTB200_ROUTE_AUTO && double(g.m) * double(g.n) * double(g.k) * double(g.batch) < 6.0e7)
         route = NTB200_ROUTE_SIMT;   // ten limb GEMMs and a split pass only pay off on large problems
     if (g.dtype == NTB200_F32 && route == NTB200_ROUTE_AUTO) {
         static const bool ffma_only = [] { const char* e = getenv("NTB200_FP32_MODE"); return e && std::strcmp(e, "ffma") == 0; }();
         if (ffma_only || double(g.m) * double(g.n) * double(g.k) * double(g.batch) < 6.0e7) route = NTB200_ROUTE_SIMT;
     }
+    // Callers that may not allocate: the routes that copy their operands first (Float32 hi/lo parts, integer limb
+    // planes) need scratch, so these dtypes stay on the CUDA-core kernel; the weight-streaming kernels and K slices
+    // (fp32 partial tiles) are skipped below and in launch_umma_gemm.
+    if (g.no_alloc && (g.dtype == NTB200_F32 || wide_int)) {
+        if (route == NTB200_ROUTE_TENSOR) return fail(NTB200_ERR_UNSUPPORTED, "matmult: the tcgen05 route of %s needs scratch memory", dtype_name(g.dtype));
+        route = NTB200_ROUTE_SIMT;
+    }
     // a handful of rows against a large 16-bit weight matrix is bound by reading the weights once: stream them
-    if (route == NTB200_ROUTE_AUTO && gemv_supported(g)) return launch_gemv(g, stream);
+    if (route == NTB200_ROUTE_AUTO && !g.no_alloc && gemv_supported(g)) return launch_gemv(g, stream);
     if (route != NTB200_ROUTE_SIMT) {
         const char* why = nullptr;
         if (umma_supported(g, &why)) {
@@ -178,6 +272,44 @@ int ensure(void** p, size_t* cap, size_t bytes) {
 }  // namespace
 
 int route_gemm(const GemmArgs& g, int route, cudaStream_t stream) { return run_gemm(g, route, stream); }
+
+int conv2d_forward(int dtype, const void* x, const void* w, void* out, void* workspace, int64_t batch, int64_t channels,
+                   int64_t height, int64_t width, int64_t cout, int64_t kh, int64_t kw, int64_t sh, int64_t sw, int64_t ph,
+                   int64_t pw, int64_t dh, int64_t dw, bool no_alloc, cudaStream_t stream) {
+    if (dtype_size(dtype) == 0) return fail(NTB200_ERR_UNSUPPORTED, "conv2d: unknown dtype %d", dtype);
+    if (sh < 1 || sw < 1) return fail(NTB200_ERR_INVALID_ARG, "Conv2d stride cannot be less than 1");
+    if (dh < 1 || dw < 1) return fail(NTB200_ERR_INVALID_ARG, "Conv2d dilation cannot be less than 1");
+    if (ph < 0 || pw < 0) return fail(NTB200_ERR_INVALID_ARG, "Conv2d padding cannot be less than 0");
+    if (batch < 0 || channels <= 0 || cout <= 0 || height <= 0 || width <= 0 || kh <= 0 || kw <= 0)
+        return fail(NTB200_ERR_INVALID_ARG, "conv2d: bad extent");
+    const int64_t hc = (height + 2 * ph - dh * (kh - 1) - 1) / sh + 1;
+    const int64_t wc = (width + 2 * pw - dw * (kw - 1) - 1) / sw + 1;
+    if (hc <= 0 || wc <= 0) return fail(NTB200_ERR_INVALID_ARG, "conv2d: calculated output size (%lld, %lld) must be at least one", (long long)hc, (long long)wc);
+    if (batch == 0) return NTB200_OK;
+    if (!x || !w || !out || !workspace) return fail(NTB200_ERR_INVALID_ARG, "conv2d: null pointer");
+    const int64_t L = hc * wc, ck = channels * kh * kw;
+    // 16-bit floats with stride 1 and whole 64-channel blocks: gather the GEMM's operand from a channels-last copy of
+    // the input instead of writing the column matrix (the workspace holds that copy and the reordered weights).
+    const Conv2dShape shape{dtype, batch, channels, height, width, cout, kh, kw, sh, sw, ph, pw, dh, dw, hc, wc};
+    if (conv2d_implicit_supported(shape, ntb200_conv2d_workspace_bytes(dtype, batch, channels, height, width, kh, kw, sh,
+                                                                       sw, ph, pw, dh, dw))) {
+        const int rc_implicit = launch_conv2d_implicit(shape, x, w, out, workspace, stream);
+        if (rc_implicit != NTB200_ERR_UNSUPPORTED) return rc_implicit;
+    }
+    // The column matrix is written densely ([B][ck][L]); out[b] (cout x L) = w2d (cout x ck) . col[b] (ck x L),
+    // which is the reference's matmult(col, w2d, true, true) followed by its row/col swap, with the same
+    // ascending-ck order for every output element.
+    int rc = ntb200_im2col(dtype, x, workspace, batch, channels, height, width, kh, kw, sh, sw, ph, pw, dh, dw, stream);
+    if (rc) return rc;
+    GemmArgs g{};
+    g.dtype = dtype; g.accumulate = 0; g.f16_rounding = NTB200_F16_ROUND_ONCE;
+    g.m = cout; g.n = L; g.k = ck; g.batch = batch;
+    g.a = w; g.a_rs = ck; g.a_cs = 1; g.a_bs = 0;
+    g.b = workspace; g.b_rs = L; g.b_cs = 1; g.b_bs = ck * L;
+    g.c = out; g.c_rs = L; g.c_bs = cout * L;
+    g.no_alloc = no_alloc ? 1 : 0;
+    return run_gemm(g, NTB200_ROUTE_AUTO, stream);
+}
 
 }  // namespace ntb200
 
@@ -242,6 +374,48 @@ int ntb200_free_async(void* ptr, void* stream) {
 int ntb200_pool_stats(uint64_t* bytes_in_use, uint64_t* high_water) {
     if (bytes_in_use) *bytes_in_use = g_pool_in_use.load();
     if (high_water) *high_water = g_pool_high.load();
+    return NTB200_OK;
+}
+int ntb200_scratch_stats(uint64_t* retained_bytes, uint64_t* acquisitions, uint64_t* allocations) {
+    if (retained_bytes) {
+        std::lock_guard<std::mutex> lk(g_scratch_mu);
+        uint64_t total = 0;
+        for (const auto& b : g_scratch) total += b.bytes;
+        *retained_bytes = total;
+    }
+    if (acquisitions) *acquisitions = g_scratch_acquires.load();
+    if (allocations) *allocations = g_scratch_allocs.load();
+    return NTB200_OK;
+}
+int ntb200_scratch_release_all(void) {
+    std::vector<void*> idle;
+    {
+        std::lock_guard<std::mutex> lk(g_scratch_mu);
+        for (size_t i = 0; i < g_scratch.size();)
+            if (!g_scratch[i].busy) {
+                idle.push_back(g_scratch[i].ptr);
+                g_scratch[i] = g_scratch.back();
+                g_scratch.pop_back();
+            } else {
+                ++i;
+            }
+    }
+    for (void* p : idle) NTB200_CUDA(cudaFree(p));   // waits for the work that still uses the block
+    return NTB200_OK;
+}
+int ntb200_device_pool_usage(uint64_t* used_now, uint64_t* used_high, uint64_t* reserved_now, int reset_high) {
+    int dev = 0;
+    NTB200_CUDA(cudaGetDevice(&dev));
+    cudaMemPool_t pool;
+    NTB200_CUDA(cudaDeviceGetDefaultMemPool(&pool, dev));
+    if (reset_high) {
+        unsigned long long zero = 0;
+        NTB200_CUDA(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrUsedMemHigh, &zero));
+    }
+    unsigned long long v = 0;
+    if (used_now) { NTB200_CUDA(cudaMemPoolGetAttribute(pool, cudaMemPoolAttrUsedMemCurrent, &v)); *used_now = v; }
+    if (used_high) { NTB200_CUDA(cudaMemPoolGetAttribute(pool, cudaMemPoolAttrUsedMemHigh, &v)); *used_high = v; }
+    if (reserved_now) { NTB200_CUDA(cudaMemPoolGetAttribute(pool, cudaMemPoolAttrReservedMemCurrent, &v)); *reserved_now = v; }
     return NTB200_OK;
 }
 int ntb200_memset_async(void* ptr, int value, size_t bytes, void* stream) {
@@ -417,20 +591,21 @@ int ntb200_matmult_batch(int dtype, const void* const* A, const void* const* B, 
     // Irregular pointers: device pointer tables, CUDA-core route.
     void* table = nullptr;
     const size_t tbytes = size_t(batches) * sizeof(void*);
-    NTB200_CUDA(cudaMallocAsync(&table, 3 * tbytes, s));
+    if (int rc = scratch_acquire(&table, 3 * tbytes, s)) return rc;
     char* t = static_cast<char*>(table);
     cudaError_t e = cudaMemcpyAsync(t, A, tbytes, cudaMemcpyHostToDevice, s);
     if (e == cudaSuccess) e = cudaMemcpyAsync(t + tbytes, B, tbytes, cudaMemcpyHostToDevice, s);
     if (e == cudaSuccess) e = cudaMemcpyAsync(t + 2 * tbytes, C, tbytes, cudaMemcpyHostToDevice, s);
-    if (e != cudaSuccess) { cudaFreeAsync(table, s); return cuda_fail(e, "pointer table upload"); }
-    // the host arrays may be reused by the caller as soon as we return
+    if (e != cudaSuccess) { scratch_release(table, s); return cuda_fail(e, "pointer table upload"); }
+    // the host arrays may be reused by the caller as soon as we return, so this branch waits for the upload
+    // (it therefore cannot run inside a stream capture; equally spaced pointers above never come here)
     e = cudaStreamSynchronize(s);
-    if (e != cudaSuccess) { cudaFreeAsync(table, s); return cuda_fail(e, "pointer table upload"); }
+    if (e != cudaSuccess) { scratch_release(table, s); return cuda_fail(e, "pointer table upload"); }
     g.a_ptrs = reinterpret_cast<const void* const*>(t);
     g.b_ptrs = reinterpret_cast<const void* const*>(t + tbytes);
     g.c_ptrs = reinterpret_cast<void* const*>(t + 2 * tbytes);
     int rc = run_gemm(g, NTB200_ROUTE_SIMT, s);
-    cudaFreeAsync(table, s);
+    scratch_release(table, s);
     return rc;
 }
 
@@ -525,38 +700,8 @@ size_t ntb200_conv2d_workspace_bytes(int dtype, int64_t batch, int64_t channels,
 int ntb200_conv2d(int dtype, const void* x, const void* w, void* out, void* workspace, int64_t batch, int64_t channels,
                   int64_t height, int64_t width, int64_t cout, int64_t kh, int64_t kw, int64_t sh, int64_t sw,
                   int64_t ph, int64_t pw, int64_t dh, int64_t dw, void* stream) {
-    if (dtype_size(dtype) == 0) return fail(NTB200_ERR_UNSUPPORTED, "conv2d: unknown dtype %d", dtype);
-    if (sh < 1 || sw < 1) return fail(NTB200_ERR_INVALID_ARG, "Conv2d stride cannot be less than 1");
-    if (dh < 1 || dw < 1) return fail(NTB200_ERR_INVALID_ARG, "Conv2d dilation cannot be less than 1");
-    if (ph < 0 || pw < 0) return fail(NTB200_ERR_INVALID_ARG, "Conv2d padding cannot be less than 0");
-    if (batch < 0 || channels <= 0 || cout <= 0 || height <= 0 || width <= 0 || kh <= 0 || kw <= 0)
-        return fail(NTB200_ERR_INVALID_ARG, "conv2d: bad extent");
-    const int64_t hc = (height + 2 * ph - dh * (kh - 1) - 1) / sh + 1;
-    const int64_t wc = (width + 2 * pw - dw * (kw - 1) - 1) / sw + 1;
-    if (hc <= 0 || wc <= 0) return fail(NTB200_ERR_INVALID_ARG, "conv2d: calculated output size (%lld, %lld) must be at least one", (long long)hc, (long long)wc);
-    if (batch == 0) return NTB200_OK;
-    if (!x || !w || !out || !workspace) return fail(NTB200_ERR_INVALID_ARG, "conv2d: null pointer");
-    const int64_t L = hc * wc, ck = channels * kh * kw;
-    // 16-bit floats with stride 1 and whole 64-channel blocks: gather the GEMM's operand from a channels-last copy of
-    // the input instead of writing the column matrix (the workspace holds that copy and the reordered weights).
-    const Conv2dShape shape{dtype, batch, channels, height, width, cout, kh, kw, sh, sw, ph, pw, dh, dw, hc, wc};
-    if (conv2d_implicit_supported(shape, ntb200_conv2d_workspace_bytes(dtype, batch, channels, height, width, kh, kw, sh,
-                                                                       sw, ph, pw, dh, dw))) {
-        const int rc_implicit = launch_conv2d_implicit(shape, x, w, out, workspace, static_cast<cudaStream_t>(stream));
-        if (rc_implicit != NTB200_ERR_UNSUPPORTED) return rc_implicit;
-    }
-    // The column matrix is written densely ([B][ck][L]); out[b] (cout x L) = w2d (cout x ck) . col[b] (ck x L),
-    // which is the reference's matmult(col, w2d, true, true) followed by its row/col swap, with the same
-    // ascending-ck order for every output element.
-    int rc = ntb200_im2col(dtype, x, workspace, batch, channels, height, width, kh, kw, sh, sw, ph, pw, dh, dw, stream);
-    if (rc) return rc;
-    GemmArgs g{};
-    g.dtype = dtype; g.accumulate = 0; g.f16_rounding = NTB200_F16_ROUND_ONCE;
-    g.m = cout; g.n = L; g.k = ck; g.batch = batch;
-    g.a = w; g.a_rs = ck; g.a_cs = 1; g.a_bs = 0;
-    g.b = workspace; g.b_rs = L; g.b_cs = 1; g.b_bs = ck * L;
-    g.c = out; g.c_rs = L; g.c_bs = cout * L;
-    return run_gemm(g, NTB200_ROUTE_AUTO, static_cast<cudaStream_t>(stream));
+    return conv2d_forward(dtype, x, w, out, workspace, batch, channels, height, width, cout, kh, kw, sh, sw, ph, pw, dh, dw,
+                          false, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

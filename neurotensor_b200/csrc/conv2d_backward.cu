@@ -83,7 +83,8 @@ size_t ntb200_conv2d_backward_workspace_bytes(int dtype, int64_t batch, int64_t 
     if (ho <= 0 || wo <= 0) return 0;
     const size_t col = size_t(batch) * size_t(channels * kh * kw) * size_t(ho * wo) * es;      // both general routes
     const size_t per_image = size_t(batch) * size_t(cout) * size_t(channels * kh * kw) * es;   // kernel gradient
-    size_t need = round256(col) + per_image;
+    // ... and a region of its own for the batch sum that `accumulate` adds to d_kernel afterwards
+    size_t need = round256(col) + round256(per_image) + size_t(cout) * size_t(channels * kh * kw) * es;
     if (image_as_convolution(dtype, kh, kw, sh, sw, ph, pw, dh, dw)) {
         const size_t conv_ws = ntb200_conv2d_workspace_bytes(dtype, batch, cout, ho, wo, kh, kw, 1, 1, dh * (kh - 1) - ph,
                                                              dw * (kw - 1) - pw, dh, dw);
@@ -164,8 +165,11 @@ int ntb200_conv2d_backward_kernel(int dtype, const void* x, const void* grad, vo
     if (direct) return NTB200_OK;
     // the reference's .view(batch, -1).sum(0): column sums of [B, Cout*CK]
     if (!accumulate) return ntb200_column_sum(dtype, per_image, d_kernel, batch, cout * g.ck, stream);
-    if (int rc = ntb200_column_sum(dtype, per_image, col, batch, cout * g.ck, stream)) return rc;   // col is free again
-    return ntb200_add_inplace(dtype, d_kernel, col, cout * g.ck, stream);
+    // the batch sum gets a region of its own behind the per-image gradients: it can be larger than the column matrix
+    // (a 1 x 1 output with more filters than images), which the summing blocks are still reading next door
+    void* summed = static_cast<char*>(per_image) + round256(size_t(batch) * size_t(cout) * size_t(g.ck) * es);
+    if (int rc = ntb200_column_sum(dtype, per_image, summed, batch, cout * g.ck, stream)) return rc;
+    return ntb200_add_inplace(dtype, d_kernel, summed, cout * g.ck, stream);
 }
 
 }  // extern "C"

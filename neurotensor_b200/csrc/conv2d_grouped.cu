@@ -67,8 +67,9 @@ size_t ntb200_conv2d_grouped_workspace_bytes(int dtype, int64_t batch, int64_t c
     if (groups == 1)
         return std::max(fwd, ntb200_conv2d_backward_workspace_bytes(dtype, batch, channels, height, width, cout, kh, kw, sh,
                                                                     sw, ph, pw, dh, dw));
-    // column matrix + the per-image kernel gradients [B, Cout, (C/groups)*kh*kw]
-    return round256(fwd) + size_t(batch) * size_t(cout) * size_t(channels / groups * kh * kw) * dtype_size(dtype);
+    // column matrix + the per-image kernel gradients [B, Cout, (C/groups)*kh*kw] + their batch sum (accumulate)
+    const size_t per_image = size_t(batch) * size_t(cout) * size_t(channels / groups * kh * kw) * dtype_size(dtype);
+    return round256(fwd) + round256(per_image) + size_t(cout) * size_t(channels / groups * kh * kw) * dtype_size(dtype);
 }
 
 int ntb200_conv2d_grouped(int dtype, const void* x, const void* w, void* out, void* workspace, int64_t batch,
@@ -158,8 +159,10 @@ int ntb200_conv2d_grouped_backward_kernel(int dtype, const void* x, const void* 
     }
     if (direct) return NTB200_OK;
     if (!accumulate) return ntb200_column_sum(dtype, per_image, d_kernel, batch, cout * g.ckg, stream);
-    if (int rc = ntb200_column_sum(dtype, per_image, col, batch, cout * g.ckg, stream)) return rc;
-    return ntb200_add_inplace(dtype, d_kernel, col, cout * g.ckg, stream);
+    // the batch sum has its own region behind the per-image gradients (it can be larger than the column matrix)
+    void* summed = static_cast<char*>(per_image) + round256(size_t(batch) * size_t(cout) * size_t(g.ckg) * es);
+    if (int rc = ntb200_column_sum(dtype, per_image, summed, batch, cout * g.ckg, stream)) return rc;
+    return ntb200_add_inplace(dtype, d_kernel, summed, cout * g.ckg, stream);
 }
 
 }  // extern "C"

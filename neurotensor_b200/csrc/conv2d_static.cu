@@ -6,7 +6,15 @@
 // because that call synchronises the device.  For them this file keeps ONE fixed scratch buffer inside the
 // library: a file-scope device array that every GPU loading the library holds until the process exits.
 // Nothing here, nor anything it calls, uses cudaMalloc, cudaFree, the stream-ordered pool or any other
-// allocating routine.
+// allocating routine: the GEMM under the convolution is told so (GemmArgs::no_alloc) and keeps to the routes that
+// need no scratch of their own.  Float32, Int16 and Int32 therefore run on the CUDA-core kernel whatever their size
+// (their tensor-core routes first write hi/lo or limb copies of the operands), and 16-bit problems never take K
+// slices or the weight-streaming kernels (both leave fp32 partial sums in scratch).
+//
+// The CUDA runtime creates a module's device storage when the module is first used (lazy loading, the default
+// since CUDA 12): the 32 MiB behind this array are taken at this entry point's first call on a device, or at
+// library load with CUDA_MODULE_LOADING=EAGER.  A caller that hands the whole heap to its own allocator makes
+// that first call (any valid tiny problem) beforehand, or sets the variable.
 #include <mutex>
 
 #include "internal.h"
@@ -30,6 +38,11 @@ int scratch_for_current_device(void** out) {
     if (!g_scratch_ptr[dev]) {
         void* p = nullptr;
         cudaError_t e = cudaGetSymbolAddress(&p, g_conv2d_scratch);
+        if (e == cudaErrorMemoryAllocation)
+            return ntb200::fail(NTB200_ERR_ALLOC,
+                                "conv2d_static_scratch: no device memory left for the library's built-in %zu-byte scratch array; "
+                                "make the first call on each device before the application takes the whole heap, or run with "
+                                "CUDA_MODULE_LOADING=EAGER", kScratchBytes);
         if (e != cudaSuccess) return ntb200::cuda_fail(e, "cudaGetSymbolAddress(conv2d scratch)");
         if (!p) return ntb200::fail(NTB200_ERR_CUDA, "conv2d_static_scratch: the scratch array has no device address");
         g_scratch_ptr[dev] = p;
@@ -56,6 +69,6 @@ extern "C" int ntb200_conv2d_static_scratch(int dtype, const void* x, const void
     if (int rc = scratch_for_current_device(&scratch)) return rc;
     // im2col writes every element of the column matrix it uses (zeros where a tap falls in the padding), so
     // whatever an earlier call left in the scratch never reaches the result and nothing has to be cleared.
-    return ntb200_conv2d(dtype, x, w, out, scratch, batch, channels, height, width, cout, kh, kw, sh, sw, ph, pw, dh,
-                         dw, stream);
+    return ntb200::conv2d_forward(dtype, x, w, out, scratch, batch, channels, height, width, cout, kh, kw, sh, sw, ph, pw, dh,
+                                  dw, /*no_alloc=*/true, static_cast<cudaStream_t>(stream));
 }

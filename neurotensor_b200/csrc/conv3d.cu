@@ -183,9 +183,10 @@ size_t ntb200_conv3d_workspace_bytes(int dtype, const ntb200_conv3d_geom* geom) 
     Geo3 g;
     if (es == 0 || !geom || geom->groups < 1 || geom->cout <= 0 || make_geo("conv3d", geom, &g) != NTB200_OK) return 0;
     if (geom->channels % geom->groups || geom->cout % geom->groups) return 0;
-    // column matrix + the per-image kernel gradients [B, Cout, (C/groups)*taps]
+    // column matrix + the per-image kernel gradients [B, Cout, (C/groups)*taps] + their batch sum (accumulate)
     return round256(size_t(g.batch) * size_t(g.ck) * size_t(g.L) * es) +
-           size_t(g.batch) * size_t(geom->cout) * size_t(g.ck / geom->groups) * es;
+           round256(size_t(g.batch) * size_t(geom->cout) * size_t(g.ck / geom->groups) * es) +
+           size_t(geom->cout) * size_t(g.ck / geom->groups) * es;
 }
 
 int ntb200_conv3d(int dtype, const void* x, const void* w, void* out, void* workspace, const ntb200_conv3d_geom* geom,
@@ -262,8 +263,10 @@ int ntb200_conv3d_backward_kernel(int dtype, const void* x, const void* grad, vo
     }
     if (direct) return NTB200_OK;
     if (!accumulate) return ntb200_column_sum(dtype, per_image, d_kernel, g.batch, geom->cout * ckg, stream);
-    if (int rc = ntb200_column_sum(dtype, per_image, col, g.batch, geom->cout * ckg, stream)) return rc;
-    return ntb200_add_inplace(dtype, d_kernel, col, geom->cout * ckg, stream);
+    // the batch sum has its own region behind the per-image gradients (it can be larger than the column matrix)
+    void* summed = static_cast<char*>(per_image) + round256(size_t(g.batch) * size_t(geom->cout) * size_t(ckg) * es);
+    if (int rc = ntb200_column_sum(dtype, per_image, summed, g.batch, geom->cout * ckg, stream)) return rc;
+    return ntb200_add_inplace(dtype, d_kernel, summed, geom->cout * ckg, stream);
 }
 
 }  // extern "C"

@@ -1503,8 +1503,7 @@ int launch_f32_split(const GemmArgs& g, cudaStream_t stream) {
     if (a_batch > 65535 || b_batch > 65535) return fail(NTB200_ERR_UNSUPPORTED, "tcgen05 route: batch too large for the Float32 split pass");
     const size_t a_elems = size_t(a_batch) * size_t(g.m) * size_t(kp), b_elems = size_t(b_batch) * size_t(g.n) * size_t(kp);
     float* scratch = nullptr;
-    keep_pool_memory();
-    NTB200_CUDA(cudaMallocAsync(reinterpret_cast<void**>(&scratch), 2 * (a_elems + b_elems) * sizeof(float), stream));
+    if (int rc = scratch_acquire(reinterpret_cast<void**>(&scratch), 2 * (a_elems + b_elems) * sizeof(float), stream)) return rc;
     float* a_hi = scratch;
     float* a_lo = a_hi + a_elems;
     float* b_hi = a_lo + a_elems;
@@ -1514,7 +1513,7 @@ int launch_f32_split(const GemmArgs& g, cudaStream_t stream) {
     const SplitJob ja{static_cast<const float*>(g.a), a_hi, a_lo, g.m, a_batch, g.a_bs, g.a_rs, g.a_cs, int((g.m + 31) / 32)};
     const SplitJob jb{static_cast<const float*>(g.b), b_hi, b_lo, g.n, b_batch, g.b_bs, g.b_cs, g.b_rs, int((g.n + 31) / 32)};
     if (int64_t(ja.row_blocks) + jb.row_blocks > 65535) {
-        cudaFreeAsync(scratch, stream);
+        scratch_release(scratch, stream);
         return fail(NTB200_ERR_UNSUPPORTED, "tcgen05 route: operand too tall for the Float32 split pass");
     }
     split_tf32_kernel<<<dim3(unsigned((kp + 31) / 32), unsigned(ja.row_blocks + jb.row_blocks), unsigned(std::max(a_batch, b_batch))),
@@ -1530,7 +1529,7 @@ int launch_f32_split(const GemmArgs& g, cudaStream_t stream) {
         const Side sb{b_hi, kp, 1, b_batch > 1 ? g.n * kp : 0}, sbl{b_lo, kp, 1, b_batch > 1 ? g.n * kp : 0};
         rc = launch_planned(g, pl, sa, sb, &sal, &sbl, stream);
     }
-    cudaFreeAsync(scratch, stream);
+    scratch_release(scratch, stream);
     return rc;
 }
 
@@ -1587,8 +1586,7 @@ int launch_int_limbs(const GemmArgs& g, cudaStream_t stream) {
     if (a_batch > 65535 || b_batch > 65535) return fail(NTB200_ERR_UNSUPPORTED, "tcgen05 route: batch too large for the limb split pass");
     const size_t a_bytes = size_t(a_batch) * size_t(g.m) * size_t(row_bytes), b_bytes = size_t(b_batch) * size_t(g.n) * size_t(row_bytes);
     uint8_t* scratch = nullptr;
-    keep_pool_memory();
-    NTB200_CUDA(cudaMallocAsync(reinterpret_cast<void**>(&scratch), a_bytes + b_bytes, stream));
+    if (int rc = scratch_acquire(reinterpret_cast<void**>(&scratch), a_bytes + b_bytes, stream)) return rc;
     uint8_t* a_limbs = scratch;
     uint8_t* b_limbs = scratch + a_bytes;
     const dim3 block(32, 8);
@@ -1614,7 +1612,7 @@ int launch_int_limbs(const GemmArgs& g, cudaStream_t stream) {
             rc = launch_planned(part, pl, sa, sb, nullptr, nullptr, stream);
             first = false;
         }
-    cudaFreeAsync(scratch, stream);
+    scratch_release(scratch, stream);
     return rc;
 }
 
@@ -1629,7 +1627,7 @@ int launch_int_limbs(const GemmArgs& g, cudaStream_t stream) {
 const bool g_no_splitk = [] { const char* e = getenv("NTB200_NO_SPLITK"); return e && e[0] == '1'; }();
 
 int pick_k_splits(const GemmArgs& g) {
-    if (g_no_splitk || g.batch != 1 || g.m > kBM || g.relu_out || g.mask_src || g.n_peers > 0) return 1;
+    if (g_no_splitk || g.no_alloc || g.batch != 1 || g.m > kBM || g.relu_out || g.mask_src || g.n_peers > 0) return 1;
     if (g.k % 64 != 0 || g.n % 4 != 0) return 1;
     // measured: no gain (or a loss, once the partial tiles weigh against the weights) below 4096 deep or 32 MB of weights
     if (g.k < 4096 || g.n * g.k < (int64_t(1) << 24)) return 1;
@@ -1664,7 +1662,7 @@ F16Plan plan_f16_tiles(const GemmArgs& g, int es = 2) {
     const int block_k = 128 / es;  // 8-bit operands: 128 deep K blocks, the same four MMAs and the same cycles
     const double kb = double((g.k + block_k - 1) / block_k);
     const bool fused = g.relu_out || g.mask_src || g.n_peers > 0;
-    const bool may_split = es == 2 && !g_no_splitk && g.batch == 1 && !fused && g.n % 4 == 0;   // the reduce kernel is 16-bit
+    const bool may_split = es == 2 && !g_no_splitk && !g.no_alloc && g.batch == 1 && !fused && g.n % 4 == 0;   // the reduce kernel is 16-bit
     const double dram_us = double(g.batch) * (double(g.m) * g.k + double(g.k) * g.n + double(g.m) * g.n) * es / 4.5e6;
     struct Cand { bool pair; int bn; double fixed_us, us_per_k_block; };   // launch + fill + last epilogue; main loop
     const Cand cands[] = {{true, 256, 11.0, 0.35}, {false, 256, 13.0, 0.39}, {false, 128, 10.0, 0.34}, {false, 64, 10.0, 0.30}};
@@ -1724,8 +1722,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int spli
 int launch_f16_split_k(const GemmArgs& g, const Planned& pl16, int splits, const TileChoice* choice, cudaStream_t stream) {
     const int64_t slab = g.m * g.n, kslice = g.k / splits;
     float* partial = nullptr;
-    keep_pool_memory();
-    NTB200_CUDA(cudaMallocAsync(reinterpret_cast<void**>(&partial), size_t(splits) * size_t(slab) * sizeof(float), stream));
+    if (int rc = scratch_acquire(reinterpret_cast<void**>(&partial), size_t(splits) * size_t(slab) * sizeof(float), stream)) return rc;
     GemmArgs part = g;
     part.batch = splits;
     part.k = kslice;
@@ -1752,7 +1749,7 @@ int launch_f16_split_k(const GemmArgs& g, const Planned& pl16, int splits, const
         const cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) rc = cuda_fail(e, "splitk_reduce_kernel");
     }
-    cudaFreeAsync(partial, stream);
+    scratch_release(partial, stream);
     return rc;
 }
 
@@ -1795,7 +1792,7 @@ int launch_umma_gemm(const GemmArgs& g, cudaStream_t stream) {
         }
         if (const int f = tune_int("NTB200_FORCE_SPLITS")) {
             choice = nullptr;
-            splits = (g.batch == 1 && !g.relu_out && !g.mask_src && g.n_peers == 0 && g.n % 4 == 0 && g.k % (64 * f) == 0) ? f : 1;
+            splits = (!g.no_alloc && g.batch == 1 && !g.relu_out && !g.mask_src && g.n_peers == 0 && g.n % 4 == 0 && g.k % (64 * f) == 0) ? f : 1;
         }
         if (splits > 1) return launch_f16_split_k(g, pl, splits, choice, stream);
     }

@@ -164,8 +164,7 @@ int launch_gemv_rows(const GemmArgs& g, bool kn_layout, cudaStream_t stream) {
     const long long slab = kn_layout ? kSlabKN : kSlabNK;
     const int slabs = int((g.k + slab - 1) / slab);
     float* partial = nullptr;
-    keep_pool_memory();
-    NTB200_CUDA(cudaMallocAsync(reinterpret_cast<void**>(&partial), size_t(slabs) * M * size_t(g.n) * sizeof(float), stream));
+    if (int rc = scratch_acquire(reinterpret_cast<void**>(&partial), size_t(slabs) * M * size_t(g.n) * sizeof(float), stream)) return rc;
     const T* a = static_cast<const T*>(g.a);
     const T* w = static_cast<const T*>(g.b);
     if (kn_layout)
@@ -178,7 +177,7 @@ int launch_gemv_rows(const GemmArgs& g, bool kn_layout, cudaStream_t stream) {
                                                                                g.accumulate);
     count_launch(2);
     cudaError_t e = cudaGetLastError();
-    cudaFreeAsync(partial, stream);
+    scratch_release(partial, stream);
     if (e != cudaSuccess) return cuda_fail(e, "gemv kernels");
     note_route("gemv_simt");
     return NTB200_OK;

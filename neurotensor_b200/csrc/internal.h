@@ -24,6 +24,10 @@ void count_launch(int n = 1);
 void note_route(const char* name);
 int sm_count();  // multiprocessors of the current device (cached per device)
 void keep_pool_memory();  // once per device: the stream-ordered pool retains freed blocks
+// Scratch for the library's own kernels, from a block kept per (device, stream) where one fits; `release` hands the
+// block back for the next call on that stream (the kernels already queued keep using it in stream order).
+int scratch_acquire(void** ptr, size_t bytes, cudaStream_t stream);
+void scratch_release(void* ptr, cudaStream_t stream);
 
 // A GEMM after validation: C[b] = (accumulate ? C[b] : 0) + bias + A[b].B[b]; strides in elements.
 struct GemmArgs {
@@ -47,6 +51,9 @@ struct GemmArgs {
     // peer-mapped copies of C on other GPUs that receive every finished tile as well (tcgen05 route only)
     int n_peers = 0;
     void* peer_c[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    // the caller may not allocate: only routes that need no scratch memory (no operand copies, no K slices, no
+    // weight-streaming partial sums)
+    int no_alloc = 0;
 };
 
 // tcgen05 route.  Returns NTB200_ERR_UNSUPPORTED (without touching the error text) when the operands
@@ -84,6 +91,11 @@ int launch_gemv(const GemmArgs& g, cudaStream_t stream);
 
 // CUDA-core route: every dtype, every stride pattern.
 int launch_simt_gemm(const GemmArgs& g, cudaStream_t stream);
+
+// ntb200_conv2d's body; `no_alloc` keeps its GEMM on routes that need no scratch memory.
+int conv2d_forward(int dtype, const void* x, const void* w, void* out, void* workspace, int64_t batch, int64_t channels,
+                   int64_t height, int64_t width, int64_t cout, int64_t kh, int64_t kw, int64_t sh, int64_t sw, int64_t ph,
+                   int64_t pw, int64_t dh, int64_t dw, bool no_alloc, cudaStream_t stream);
 
 // The route decision every GEMM of the library goes through (tcgen05, CUDA cores or a plain fill of C).
 int route_gemm(const GemmArgs& g, int route, cudaStream_t stream);

@@ -1,7 +1,9 @@
 """Multi-GPU partitioner for the matmult path (new: the reference has no device or process boundary).
 
-One process per GPU (torch.distributed supplies rank / world size and, where an output has to be
-reassembled, the NCCL all-gather).  Two partitionings:
+One process per GPU.  The partitioner itself lives behind the C ABI (ntb200_dist_*: shard arithmetic, buffers mapped
+into every rank, GEMMs whose epilogues gather their column blocks, a bounded flag exchange for ordering); this module
+wraps it for torch processes (torch.distributed supplies rank / world size and carries the buffer records at set-up)
+and keeps an NCCL all-gather variant as the comparison baseline.  Two partitionings:
 
   * batched matmult   -- the batch dimension is split into contiguous ranges, one per rank; items are
                          independent (nt_matmult_batch is a serial loop over items, nt_matmult.hpp:228-235), so
@@ -29,8 +31,22 @@ def column_shard(n, world, rank, align=8):
     16-byte aligned rows for 2-byte dtypes (a TMA requirement)."""
     blocks = (n + align - 1) // align
     s, c = shard_range(blocks, world, rank)
-    start = s * align
+    start = min(n, s * align)
     return start, max(0, min(n, (s + c) * align) - start)
+
+
+def conv2d_image_shard(batch, world, rank):
+    """Images of a conv2d batch owned by `rank` (contiguous range).  The convolution of an image depends on no other
+    image (functional::conv2d runs one GEMM per image, nt/functional/tensor_files/conv.cpp:69-119), so the forward pass
+    and the image gradient need no exchange with the weights replicated; only the kernel gradient, a sum over all
+    images, would need an all-reduce of the ranks' partial sums."""
+    return shard_range(batch, world, rank)
+
+
+def sharded_conv2d(x_local, w, stride=1, padding=0, dilation=1, groups=1):
+    """conv2d of this rank's images (a plain local call, no communication; weights replicated)."""
+    from . import api
+    return api.conv2d(x_local, w, stride=stride, padding=padding, dilation=dilation, groups=groups)
 
 
 def batched_matmult(a_local, b_local, transpose_a=False, transpose_b=False):
@@ -81,6 +97,115 @@ class _RawCuda:
 
     def __init__(self, ptr, shape, typestr):
         self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (int(ptr), False), "version": 3}
+
+
+def c_shard(total, world, rank, align=1):
+    """ntb200_dist_shard through the C ABI: (start, count) of `rank`'s contiguous share, in blocks of `align`."""
+    import ctypes
+    from . import _lib
+    s, c = ctypes.c_int64(), ctypes.c_int64()
+    _lib.check(_lib.lib().ntb200_dist_shard(total, world, rank, align, ctypes.byref(s), ctypes.byref(c)))
+    return s.value, c.value
+
+
+class DistComm:
+    """The library's own communicator (ntb200_dist_* in the C ABI) for the ranks of a torch.distributed group on one
+    NVLink domain.  torch.distributed is used once per buffer, at set-up, to pass the 88-byte buffer records around
+    (the all-gather callback below); data and ordering afterwards are the library's kernels alone."""
+
+    def __init__(self, group=None):
+        import ctypes
+        import torch.distributed as dist
+        from . import _lib
+        self.group = group
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+
+        def exchange(ctx, send, recv, nbytes):
+            try:
+                mine = ctypes.string_at(send, nbytes)
+                parts = [None] * self.world
+                dist.all_gather_object(parts, mine, group=group)
+                ctypes.memmove(recv, b"".join(parts), nbytes * self.world)
+                return 0
+            except Exception:                                   # the C side reports the failure
+                return 1
+
+        self._cb = _lib.ALLGATHER_FN(exchange)                  # kept alive as long as the communicator
+        self._h = ctypes.c_void_p()
+        _lib.check(_lib.lib().ntb200_dist_init(ctypes.byref(self._h), self.rank, self.world, self._cb, None))
+
+    def buffer(self, rows, cols, dtype):
+        return DistBuffer(self, rows, cols, dtype)
+
+    def barrier(self):
+        import ctypes
+        from . import _lib
+        _lib.check(_lib.lib().ntb200_dist_barrier(self._h, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+
+    def gemm_allgather(self, a, b, buf, col0, bias=None, relu=False):
+        """This rank's column block bias + a.b lands in columns [col0, col0 + n) of `buf` on EVERY rank (stored by
+        the GEMM's epilogue), then the ranks are ordered.  relu: returns the pre-activation block [m, n] and gathers
+        max(., 0); otherwise returns buf.local."""
+        import ctypes
+        from . import _lib, api
+        m, k = a.shape
+        n = b.shape[1]
+        if buf.rows != m or col0 < 0 or col0 + n > buf.cols or buf.dtype != a.dtype or b.shape[0] != k:
+            raise ValueError("gemm_allgather: block [%d x %d] at column %d does not fit a [%d x %d] buffer" % (m, n, col0, buf.rows, buf.cols))
+        d = _lib.GemmDesc()
+        d.dtype, d.route, d.accumulate, d.f16_rounding = api.dtype_code(a), _lib.ROUTE_TENSOR, 0, _lib.F16_ROUND_ONCE
+        d.m, d.n, d.k, d.batch = m, n, k, 1
+        d.a, d.a_row_stride, d.a_col_stride, d.a_batch_stride = a.data_ptr(), a.stride(0), a.stride(1), 0
+        d.b, d.b_row_stride, d.b_col_stride, d.b_batch_stride = b.data_ptr(), b.stride(0), b.stride(1), 0
+        h = None
+        if relu:
+            h = torch.empty((m, n), dtype=a.dtype, device=a.device)
+            d.c, d.c_row_stride, d.c_batch_stride = h.data_ptr(), n, 0
+        if bias is not None:
+            d.bias, d.bias_row_stride, d.bias_col_stride, d.bias_batch_stride = bias.data_ptr(), 0, bias.stride(0), 0
+        _lib.check(_lib.lib().ntb200_dist_gemm_allgather(self._h, ctypes.byref(d), buf._h, buf.cols, col0, int(relu),
+                                                         ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        return h if relu else buf.local
+
+    def allgather_columns(self, block, buf, col0):
+        import ctypes
+        from . import _lib, api
+        m, n = block.shape
+        _lib.check(_lib.lib().ntb200_dist_allgather_columns(self._h, api.dtype_code(block), block.data_ptr(), m, n, block.stride(0),
+                                                            buf._h, buf.cols, col0,
+                                                            ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        return buf.local
+
+    def close(self):
+        from . import _lib
+        if self._h is not None:
+            _lib.lib().ntb200_dist_destroy(self._h)
+            self._h = None
+
+
+class DistBuffer:
+    """A [rows, cols] matrix that exists on every rank of a DistComm and is mapped into every other rank
+    (ntb200_dist_buffer_create).  `local` is this rank's copy as a tensor; the peers' copies are only ever written
+    by this library's kernels."""
+
+    def __init__(self, comm, rows, cols, dtype):
+        import ctypes
+        from . import _lib
+        self.comm, self.rows, self.cols, self.dtype = comm, rows, cols, dtype
+        es = torch.empty((), dtype=dtype).element_size()
+        self._h = ctypes.c_void_p()
+        _lib.check(_lib.lib().ntb200_dist_buffer_create(comm._h, rows * cols * es, ctypes.byref(self._h)))
+        ptr = _lib.lib().ntb200_dist_buffer_ptr(self._h)
+        raw = torch.as_tensor(_RawCuda(ptr, (rows, cols * es), "|u1"), device="cuda")
+        self.local = raw.view(dtype)
+
+    def close(self):
+        from . import _lib
+        if self._h is not None:
+            self.local = None
+            _lib.lib().ntb200_dist_buffer_destroy(self._h)
+            self._h = None
 
 
 class PeerBuffer:
@@ -149,43 +274,42 @@ class ShardedMLP:
             return t
         return all_gather_columns(t, self.group)
 
-    def enable_fused_gather(self, batch):
+    def enable_fused_gather(self, batch, comm=None):
         """Switch the two all-gathers to the fused form: the GEMM epilogue stores its column block straight into every
-        rank's full buffer (peer stores), and one tiny NCCL all-reduce orders the ranks.  Two buffers alternate per
-        step so a fast rank never overwrites what a slower rank is still reading."""
+        rank's full buffer (stores into peer-mapped memory), and the library's flag exchange orders the ranks
+        (ntb200_dist_gemm_allgather).  Two buffers alternate per step so a fast rank never overwrites what a slower
+        rank is still reading."""
         dt = self.w2.dtype
         hidden, dout = self.w2.shape
-        self._fused = {"a": [PeerBuffer(batch, hidden, dt, self.group) for _ in range(2)],
-                       "y": [PeerBuffer(batch, dout, dt, self.group) for _ in range(2)],
-                       "flag": torch.zeros(1, device="cuda"), "parity": 0}
+        own = comm is None
+        comm = comm or DistComm(self.group)
+        self._fused = {"comm": comm, "own_comm": own, "a": [comm.buffer(batch, hidden, dt) for _ in range(2)],
+                       "y": [comm.buffer(batch, dout, dt) for _ in range(2)], "parity": 0}
 
     def close(self):
-        for bufs in (getattr(self, "_fused", None) or {}).values():
-            if isinstance(bufs, list):
-                for b in bufs:
+        f = getattr(self, "_fused", None)
+        if f:
+            for key in ("a", "y"):
+                for b in f[key]:
                     b.close()
+            if f["own_comm"]:
+                f["comm"].close()
         self._fused = None
-
-    def _rank_barrier(self):
-        import torch.distributed as dist
-        dist.all_reduce(self._fused["flag"], group=self.group)   # stream-ordered: every rank's GEMM is behind it
 
     def step_fused(self, x, target):
         """Same step with the all-gathers fused into the GEMM epilogues: layer 1 keeps its pre-activation block and
-        pushes the activation block into every rank's activation buffer (one launch), layer 2 pushes its output
-        block; one barrier after each before anybody reads a gathered buffer.  The backward is the one of step()."""
+        stores the activation block into every rank's activation buffer (one launch), layer 2 stores its output
+        block; the ranks are ordered after each before anybody reads a gathered buffer.  The backward is the one of
+        step()."""
         from . import api
         f = self._fused
         par = f["parity"]
         f["parity"] ^= 1
-        abuf, ybuf = f["a"][par], f["y"][par]
-        h_loc = api.gemm_push_relu(x, self.w1, abuf.local, self.h0, bias=self.b1, peer_bases=abuf.peer_bases)
-        self._rank_barrier()
+        comm, abuf, ybuf = f["comm"], f["a"][par], f["y"][par]
+        h_loc = comm.gemm_allgather(x, self.w1, abuf, self.h0, bias=self.b1, relu=True)
         a = abuf.local                                                         # [B, H], every rank's block
         w2_cols = self.w2[:, self.d0:self.d0 + self.dn]
-        api.gemm_push(a, w2_cols, ybuf.local, self.d0, bias=self.b2[self.d0:self.d0 + self.dn], peer_bases=ybuf.peer_bases)
-        self._rank_barrier()
-        y = ybuf.local
+        y = comm.gemm_allgather(a, w2_cols, ybuf, self.d0, bias=self.b2[self.d0:self.d0 + self.dn])
         loss, dy = api.mse(y, target)
         dy_loc = dy[:, self.d0:self.d0 + self.dn]
         gw2_loc = api.matmult(a, dy_loc, True, False)

@@ -8,7 +8,7 @@ import numpy as np
 import pytest
 import torch
 
-from gpu_util import dev, host, integers, normal
+from gpu_util import Codec, check_16bit, dev, host, integers, normal
 
 pytestmark = pytest.mark.gpu
 
@@ -358,24 +358,16 @@ def test_few_rows_stream_the_weights(api, oracle, L, m, weights_nk, bf16):
     k, n = 1544, 1160                                   # ragged against the 128 / 2048 K slabs and the column blocks
     x32, w32 = normal(rng, (m, k), np.float32, 0.5), normal(rng, (k, n), np.float32, 0.5)
     b32, c32 = normal(rng, (n,), np.float32), normal(rng, (m, n), np.float32)
-    if bf16:
-        enc = lambda v: dev(oracle.bf16_round(v), bf16=True)
-        val = lambda v: oracle.bf16_widen(oracle.bf16_round(v))
-        dec = lambda t: oracle.bf16_widen(host(t))
-    else:
-        enc = lambda v: dev(v.astype(np.float16))
-        val = lambda v: v.astype(np.float16).astype(np.float32)
-        dec = lambda t: host(t).astype(np.float32)
-    x, bias = enc(x32), enc(b32)
-    w = enc(np.ascontiguousarray(w32.T)).t() if weights_nk else enc(w32)    # [K, N] view either way
-    exact = val(x32).astype(np.float64) @ val(w32).astype(np.float64)
+    cd = Codec(oracle, bf16)
+    x, bias = cd.enc(x32), cd.enc(b32)
+    w = cd.enc(np.ascontiguousarray(w32.T)).t() if weights_nk else cd.enc(w32)    # [K, N] view either way
     got = api.linear(x, w, bias)
     assert L.last_route() == "gemv_simt"
-    assert oracle.rel_fro(dec(got), exact + val(b32)) <= 2e-3
-    out = enc(c32)
+    check_16bit(oracle, cd, cd.dec(got), x32, w32, b32, what="weight streaming, bias")
+    out = cd.enc(c32)
     api.matmult(x, w, out=out)                           # C += x . w
     assert L.last_route() == "gemv_simt"
-    assert oracle.rel_fro(dec(out), exact + val(c32)) <= 2e-3
+    check_16bit(oracle, cd, cd.dec(out), x32, w32, c32, what="weight streaming, C +=")
     # an explicit route request is honoured, and three rows are the tensor cores' again
     api.matmult(x, w, route=L.ROUTE_TENSOR)
     assert L.last_route() in ("umma_f16", "umma_bf16")
@@ -393,25 +385,20 @@ def test_few_rows_split_the_k_axis(api, oracle, L, m, n, k, weights_nk, bf16):
     rng = np.random.default_rng(97 + m)
     x32, w32 = normal(rng, (m, k), np.float32, 0.5), normal(rng, (k, n), np.float32, 0.5)
     b32, c32 = normal(rng, (n,), np.float32), normal(rng, (m, n), np.float32)
-    if bf16:
-        enc = lambda v: dev(oracle.bf16_round(v), bf16=True)
-        val = lambda v: oracle.bf16_widen(oracle.bf16_round(v))
-        dec = lambda t: oracle.bf16_widen(host(t))
-    else:
-        enc = lambda v: dev(v.astype(np.float16))
-        val = lambda v: v.astype(np.float16).astype(np.float32)
-        dec = lambda t: host(t).astype(np.float32)
-    x, bias = enc(x32), enc(b32)
-    w = enc(np.ascontiguousarray(w32.T)).t() if weights_nk else enc(w32)    # [K, N] view either way
-    exact = val(x32).astype(np.float64) @ val(w32).astype(np.float64)
+    cd = Codec(oracle, bf16)
+    x, bias = cd.enc(x32), cd.enc(b32)
+    w = cd.enc(np.ascontiguousarray(w32.T)).t() if weights_nk else cd.enc(w32)    # [K, N] view either way
+    dec = cd.dec
     split_route = "umma_bf16_splitk" if bf16 else "umma_f16_splitk"
     got = api.linear(x, w, bias)
     assert L.last_route() == split_route
-    assert oracle.rel_fro(dec(got), exact + val(b32)) <= 2e-3
-    out = enc(c32)
+    # K = 4096 / 8192: Float16 is beyond the depth at which fp32 accumulation stays within 2e-3 of the reference's
+    # per-16-k rounding; both distances are measured and reported, the bar is on the fp32-accumulate value
+    check_16bit(oracle, cd, dec(got), x32, w32, b32, what="K slices, bias")
+    out = cd.enc(c32)
     api.matmult(x, w, out=out)                           # C += x . w
     assert L.last_route() == split_route
-    assert oracle.rel_fro(dec(out), exact + val(c32)) <= 2e-3
+    check_16bit(oracle, cd, dec(out), x32, w32, c32, what="K slices, C +=")
     # the left half of the columns on its own (a strided view, possibly too small to split) gives the same sums up to
     # the order of the fp32 additions
     half = api.matmult(x, w[:, : n // 2])
@@ -558,20 +545,12 @@ def test_shallow_k_takes_the_wide_epilogue(api, oracle, L, kind, m, n, k):
     bf16 = kind == "bf16"
     a32, b32 = normal(rng, (m, k), np.float32, 0.5), normal(rng, (k, n), np.float32, 0.5)
     bias32, c32 = normal(rng, (n,), np.float32), normal(rng, (m, n), np.float32)
-    if bf16:
-        enc = lambda v: dev(oracle.bf16_round(v), bf16=True)
-        val = lambda v: oracle.bf16_widen(oracle.bf16_round(v))
-        dec = lambda t: oracle.bf16_widen(host(t))
-    else:
-        enc = lambda v: dev(v.astype(np.float16))
-        val = lambda v: v.astype(np.float16).astype(np.float32)
-        dec = lambda t: host(t).astype(np.float32)
-    exact = val(a32).astype(np.float64) @ val(b32).astype(np.float64)
-    got = api.linear(enc(a32), enc(b32), enc(bias32))
+    cd = Codec(oracle, bf16)
+    got = api.linear(cd.enc(a32), cd.enc(b32), cd.enc(bias32))
     assert L.last_route() in ("umma_f16", "umma_bf16")
-    assert oracle.rel_fro(dec(got), exact + val(bias32)) <= 2e-3
-    out = enc(c32)
-    api.matmult(enc(a32), enc(b32), out=out)
-    assert oracle.rel_fro(dec(out), exact + val(c32)) <= 2e-3
-    bt = enc(np.ascontiguousarray(b32.T)).t()            # K-major B
-    assert oracle.rel_fro(dec(api.matmult(enc(a32), bt)), exact) <= 2e-3
+    check_16bit(oracle, cd, cd.dec(got), a32, b32, bias32, what="shallow K, bias")
+    out = cd.enc(c32)
+    api.matmult(cd.enc(a32), cd.enc(b32), out=out)
+    check_16bit(oracle, cd, cd.dec(out), a32, b32, c32, what="shallow K, C +=")
+    bt = cd.enc(np.ascontiguousarray(b32.T)).t()            # K-major B
+    check_16bit(oracle, cd, cd.dec(api.matmult(cd.enc(a32), bt)), a32, b32, what="shallow K, K-major B")

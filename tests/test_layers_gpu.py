@@ -27,11 +27,11 @@ def test_linear_golden(api):
     """tests/src/linear_autograd_test.cpp:128-149 on the device."""
     x, w, b, grad = (dev(g("linear_" + n)) for n in ("input", "weight", "bias", "grad"))
     out = api.linear(x, w, b, transpose_b=True)
-    assert np.allclose(host(out), g("linear_input") @ g("linear_weight").T + g("linear_bias"), rtol=RTOL, atol=1e-6)
+    assert np.allclose(host(out), g("linear_input") @ g("linear_weight").T + g("linear_bias"), rtol=RTOL, atol=ATOL)
     dx, dw = api.matmult_backward(x, w, grad, False, True)
     assert np.allclose(host(dx), g("linear_xgrad"), rtol=RTOL, atol=ATOL)
-    assert np.allclose(host(dw).sum(axis=0), g("linear_wgrad"), rtol=RTOL, atol=1e-6)
-    assert np.allclose(host(api.column_sum(grad)), g("linear_bgrad"), rtol=RTOL, atol=1e-6)
+    assert np.allclose(host(dw).sum(axis=0), g("linear_wgrad"), rtol=RTOL, atol=ATOL)
+    assert np.allclose(host(api.column_sum(grad)), g("linear_bgrad"), rtol=RTOL, atol=ATOL)
 
 
 @pytest.mark.parametrize("ext", ["", "_batched"])
@@ -41,7 +41,7 @@ def test_conv2d_golden(api, ext):
     out = api.conv2d(x, w, stride=1, padding=1)
     exp = g("conv2d_output" + ext)
     assert tuple(out.shape) == exp.shape
-    assert np.allclose(host(out), exp, rtol=RTOL, atol=1e-6)
+    assert np.allclose(host(out), exp, rtol=RTOL, atol=ATOL)
 
 
 def test_unfold2d_golden(api):
@@ -50,7 +50,7 @@ def test_unfold2d_golden(api):
     col = api.unfold2d(x, (3, 2), dilation=(1, 2), padding=1, stride=(2, 2))
     assert np.array_equal(host(col), g("unfold_output"))
     dx = api.unfold2d_backward(dev(g("unfold_grad")), x.shape[-2:], (3, 2), dilation=(1, 2), padding=1, stride=(2, 2))
-    assert np.allclose(host(dx).reshape(g("unfold_input_grad").shape), g("unfold_input_grad"), rtol=RTOL, atol=1e-6)
+    assert np.allclose(host(dx).reshape(g("unfold_input_grad").shape), g("unfold_input_grad"), rtol=RTOL, atol=ATOL)
 
 
 @pytest.mark.parametrize("dt", [np.float32, np.float16, np.int32, np.int8])
@@ -130,9 +130,9 @@ def test_conv2d_without_column_matrix_bf16(api, oracle):
     wb = oracle.bf16_round(normal(rng, (72, 64, 3, 3), np.float32, (1.0 / (64 * 9)) ** 0.5))
     got = api.conv2d(dev(xb, bf16=True), dev(wb, bf16=True), stride=1, padding=1)
     assert _lib.last_route() == "conv2d-implicit-umma-pair"
-    # the oracle convolves the exact float32 values of the bf16 inputs; the kernel rounds its fp32 sums to bf16 once
-    exp = oracle.conv2d(oracle.bf16_widen(xb), oracle.bf16_widen(wb), stride=1, padding=1)
-    assert oracle.rel_fro(got.float().cpu().numpy(), exp) <= 6e-3
+    # the oracle runs the Float32 chain on the exactly widened inputs and rounds once to bf16, as the kernel does
+    exp = oracle.conv2d(xb, wb, stride=1, padding=1, bf16=True)
+    assert oracle.rel_fro(got.float().cpu().numpy(), oracle.bf16_widen(exp)) <= 2e-3
 
 
 def test_conv2d_errors(api):
@@ -188,7 +188,8 @@ def mlp_reference(oracle, x, w1, b1, w2, b2, target, bf16):
     da, dw2 = oracle.matmult_backward(a16, w2, dy16, bf16=bf16)
     dh16 = nar(np.where(mask, 0, wid(da)))
     dx, dw1 = oracle.matmult_backward(x, w1, dh16, bf16=bf16)
-    return dict(h=h, y=y, loss=loss, dw2=dw2, dw1=dw1, dx=dx, db2=wid(dy16).sum(0), db1=wid(dh16).sum(0))
+    return dict(h=h, y=y, loss=loss, dw2=dw2, dw1=dw1, dx=dx, da=da, a16=a16, dy16=dy16, dh16=dh16,
+                db2=wid(dy16).sum(0), db1=wid(dh16).sum(0))
 
 
 @pytest.mark.parametrize("bf16", [True, False])
@@ -219,10 +220,20 @@ def test_mlp_forward_backward(api, oracle, bf16):
     tol = 2e-3
     assert rel(h, ref["h"]) <= tol and rel(y, ref["y"]) <= tol
     assert abs(float(loss.item()) - ref["loss"]) <= 5e-3 * ref["loss"]
+    # Each backward GEMM on its own, fed the oracle's own rounded intermediates: one GEMM deep, so the 2e-3 bar applies
+    a16, dy16, dh16 = d(ref["a16"]), d(ref["dy16"]), d(ref["dh16"])
+    da_1, gw2_1 = api.matmult_backward(a16, dw2_, dy16)
+    gx_1, gw1_1 = api.matmult_backward(dx_, dw1_, dh16)
+    for got, key in ((gw2_1, "dw2"), (gw1_1, "dw1"), (gx_1, "dx"), (da_1, "da")):
+        assert rel(got, ref[key]) <= tol, (key, rel(got, ref[key]))
+    # The device's own chain end to end.  Its gradients depend on up to three GEMMs in a row (y -> dy -> dh -> dW1),
+    # each within 2e-3 of the oracle's, and dy = 2 (y - t) / n amplifies a difference in y by |y| / |y - t| (about 0.6
+    # here: y is small against the N(0,1) targets), so the chain is held to three times the single-GEMM bar.
+    chain_tol = 3 * tol
     for got, key in ((gw2, "dw2"), (gw1, "dw1"), (gx, "dx")):
-        assert rel(got, ref[key]) <= 2e-2, key
-    assert oracle.rel_fro(wid(host(gb2)), ref["db2"]) <= 2e-2
-    assert oracle.rel_fro(wid(host(gb1)), ref["db1"]) <= 2e-2
+        assert rel(got, ref[key]) <= chain_tol, (key, rel(got, ref[key]))
+    assert oracle.rel_fro(wid(host(gb2)), ref["db2"]) <= chain_tol
+    assert oracle.rel_fro(wid(host(gb1)), ref["db1"]) <= chain_tol
 
 
 def test_gemm_push_writes_every_copy(api, oracle):
@@ -291,8 +302,8 @@ def test_conv2d_backward_golden(api, ext):
     """tests/src/conv_autograd_test.cpp:249-279,313-341 (backward) on the device."""
     x, w, grad = dev(g("conv2d_input" + ext)), dev(g("conv2d_weight" + ext)), dev(g("conv2d_grad" + ext))
     dx, dw = api.conv2d_backward(x, w, grad, stride=1, padding=1)
-    assert np.allclose(host(dx), g("conv2d_xgrad" + ext), rtol=1e-4, atol=1e-6)
-    assert np.allclose(host(dw), g("conv2d_wgrad" + ext), rtol=1e-4, atol=1e-5)
+    assert np.allclose(host(dx), g("conv2d_xgrad" + ext), rtol=RTOL, atol=ATOL)
+    assert np.allclose(host(dw), g("conv2d_wgrad" + ext), rtol=RTOL, atol=ATOL)
 
 
 @pytest.mark.parametrize("m,k,n", [(256, 128, 512), (200, 96, 136), (130, 64, 72)])
@@ -377,6 +388,20 @@ def test_conv2d_backward_kernel_accumulates_and_rejects_integers(api):
     _lib.check(lib.ntb200_conv2d_backward_kernel(_lib.F32, x.data_ptr(), g.data_ptr(), acc.data_ptr(), ws.data_ptr(), 1,
                                                  3, 8, 9, 9, 6, 3, 3, 1, 1, 1, 1, 1, 1, None))
     assert torch.equal(acc, dw + 1.0)      # d_kernel += ..., as the reference does
+    # a convolution acting as a fully connected layer (1 x 1 output) with more filters than images: the batch sum
+    # [Cout*CK] is larger than the column matrix [B*CK*1], so it must not be staged in the column matrix's place
+    for groups, entry in ((1, lib.ntb200_conv2d_backward_kernel), (2, lib.ntb200_conv2d_grouped_backward_kernel)):
+        x1 = torch.randn((32, 16, 3, 3), generator=gen, device="cuda")
+        w1 = torch.randn((512, 16 // groups, 3, 3), generator=gen, device="cuda")
+        g1 = torch.randn((32, 512, 1, 1), generator=gen, device="cuda")
+        _, dw1 = api.conv2d_backward(x1, w1, g1, groups=groups)
+        need1 = lib.ntb200_conv2d_grouped_workspace_bytes(_lib.F32, 32, 16, 3, 3, 512, 3, 3, 1, 1, 0, 0, 1, 1, groups)
+        ws1 = torch.empty(need1, dtype=torch.uint8, device="cuda")
+        acc1 = torch.full_like(w1, 0.5)
+        tail = (groups, None) if groups > 1 else (None,)
+        _lib.check(entry(_lib.F32, x1.data_ptr(), g1.data_ptr(), acc1.data_ptr(), ws1.data_ptr(), 1, 32, 16, 3, 3, 512, 3, 3,
+                         1, 1, 0, 0, 1, 1, *tail))
+        assert torch.equal(acc1, dw1 + 0.5)
     xi = torch.zeros((1, 8, 9, 9), dtype=torch.int32, device="cuda")
     rc = lib.ntb200_conv2d_backward_image(_lib.I32, xi.data_ptr(), xi.data_ptr(), xi.data_ptr(), ws.data_ptr(), 1, 8, 9, 9,
                                           6, 3, 3, 1, 1, 1, 1, 1, 1, None)

@@ -95,6 +95,6 @@ def test_random_shapes_strides_and_dtypes(api, oracle, seed):
         elif kind == "f32":
             assert oracle.rel_fro(got, exp) <= 1e-5, tag
         elif kind == "bf16":
-            assert oracle.rel_fro(oracle.bf16_widen(got), oracle.bf16_widen(exp)) <= 3e-3, tag
+            assert oracle.rel_fro(oracle.bf16_widen(got), oracle.bf16_widen(exp)) <= 2e-3, tag
         else:
             assert oracle.rel_fro(got, exp) <= 2e-3, tag

@@ -65,6 +65,84 @@ def test_static_scratch_conv2d_matches_workspace_conv2d_twice():
     assert np.array_equal(got2.cpu().numpy(), exp2)
 
 
+def _pool_state(L):
+    """(bytes handed out by the device's stream-ordered pool, their high-water mark since the reset just made,
+    scratch blocks the library has handed to its own kernels so far)"""
+    lib = L.lib()
+    used, high, acq = ctypes.c_uint64(), ctypes.c_uint64(), ctypes.c_uint64()
+    L.check(lib.ntb200_device_pool_usage(ctypes.byref(used), ctypes.byref(high), None, 1))
+    L.check(lib.ntb200_scratch_stats(None, ctypes.byref(acq), None))
+    return used.value, high.value, acq.value
+
+
+def _static_only(L, code, x, w, geom):
+    lib = L.lib()
+    bsz, ch, h, wd = x.shape
+    cout, _, kh, kw = w.shape
+    sh, sw, ph, pw, dh, dw = geom
+    ho = (h + 2 * ph - dh * (kh - 1) - 1) // sh + 1
+    wo = (wd + 2 * pw - dw * (kw - 1) - 1) // sw + 1
+    need = lib.ntb200_conv2d_workspace_bytes(code, bsz, ch, h, wd, kh, kw, sh, sw, ph, pw, dh, dw)
+    assert 0 < need <= L.CONV2D_STATIC_SCRATCH_BYTES
+    got = torch.zeros((bsz, cout, ho, wo), dtype=x.dtype, device="cuda")
+    s = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    used0, _, acq0 = _pool_state(L)
+    L.check(lib.ntb200_conv2d_static_scratch(code, x.data_ptr(), w.data_ptr(), got.data_ptr(), bsz, ch, h, wd, cout,
+                                             kh, kw, sh, sw, ph, pw, dh, dw, s))
+    route = L.last_route()
+    torch.cuda.synchronize()
+    used1, high1, acq1 = ctypes.c_uint64(), ctypes.c_uint64(), ctypes.c_uint64()
+    L.check(lib.ntb200_device_pool_usage(ctypes.byref(used1), ctypes.byref(high1), None, 0))
+    L.check(lib.ntb200_scratch_stats(None, ctypes.byref(acq1), None))
+    # nothing was taken from the pool during the call, not even for a moment, and no scratch block was handed out
+    assert used1.value == used0, (used0, used1.value)
+    assert high1.value <= used0, (used0, high1.value)
+    assert acq1.value == acq0, "the call took a scratch block (%d -> %d)" % (acq0, acq1.value)
+    return got, route
+
+
+NON_ALLOCATING_ROUTES = {"simt", "umma_f16", "umma_bf16", "umma_i8", "conv2d-implicit-umma-pair"}
+
+
+def test_static_scratch_allocates_nothing_on_the_routes_that_would():
+    """Problems that fit the built-in array but whose GEMM, through ntb200_conv2d, takes a route with scratch of its
+    own (Float32 as three TF32 products, Int32 limb planes, Float16 K slices).  Through this entry point they must
+    allocate nothing, and still give the reference's result."""
+    from neurotensor_b200 import _lib as L
+    from oracle import oracle
+    rng = np.random.default_rng(77)
+    # Float32, 1.16e8 multiply-adds (the automatic route would split the operands into hi/lo copies)
+    x = torch.from_numpy(rng.standard_normal((1, 64, 56, 56)).astype(np.float32)).cuda()
+    w = torch.from_numpy((rng.standard_normal((64, 64, 3, 3)) / 24).astype(np.float32)).cuda()
+    got, route = _static_only(L, L.F32, x, w, (1, 1, 1, 1, 1, 1))
+    assert route in NON_ALLOCATING_ROUTES, route
+    assert np.array_equal(got.cpu().numpy(), oracle.conv2d(x.cpu().numpy(), w.cpu().numpy(), stride=1, padding=1))   # one chain per output: bit-exact
+    # Float32, batched: 8 x 64 x 28 x 28 against 128 filters (a 14 MB column matrix)
+    x = torch.from_numpy(rng.standard_normal((8, 64, 28, 28)).astype(np.float32)).cuda()
+    w = torch.from_numpy((rng.standard_normal((128, 64, 3, 3)) / 24).astype(np.float32)).cuda()
+    got, route = _static_only(L, L.F32, x, w, (1, 1, 1, 1, 1, 1))
+    assert route in NON_ALLOCATING_ROUTES, route
+    assert np.array_equal(got.cpu().numpy(), oracle.conv2d(x.cpu().numpy(), w.cpu().numpy(), stride=1, padding=1))
+    # Int32 above 6e7 multiply-adds (the automatic route would write limb planes)
+    xi = torch.from_numpy(rng.integers(-1000, 1000, (4, 32, 32, 32)).astype(np.int32)).cuda()
+    wi = torch.from_numpy(rng.integers(-1000, 1000, (64, 32, 3, 3)).astype(np.int32)).cuda()
+    got, route = _static_only(L, L.I32, xi, wi, (1, 1, 1, 1, 1, 1))
+    assert route in NON_ALLOCATING_ROUTES, route
+    assert np.array_equal(got.cpu().numpy(), oracle.conv2d(xi.cpu().numpy(), wi.cpu().numpy(), stride=1, padding=1))
+    # Float16, one image, stride 2 (no implicit route), deep K: the automatic route would cut K into slices
+    xh = torch.from_numpy((rng.standard_normal((1, 512, 28, 28))).astype(np.float16)).cuda()
+    wh = torch.from_numpy((rng.standard_normal((256, 512, 3, 3)) / 68).astype(np.float16)).cuda()
+    got, route = _static_only(L, L.F16, xh, wh, (2, 2, 1, 1, 1, 1))
+    assert route in NON_ALLOCATING_ROUTES, route
+    assert oracle.rel_fro(got.cpu().numpy(), oracle.conv2d(xh.cpu().numpy(), wh.cpu().numpy(), stride=2, padding=1)) <= 2e-3
+    # Float16 with two filters (the automatic route would stream the weights and leave partial sums in scratch)
+    wt = torch.from_numpy((rng.standard_normal((2, 512, 3, 3)) / 68).astype(np.float16)).cuda()
+    got, route = _static_only(L, L.F16, xh, wt, (2, 2, 1, 1, 1, 1))
+    assert route in NON_ALLOCATING_ROUTES, route
+    assert oracle.rel_fro(got.cpu().numpy(), oracle.conv2d(xh.cpu().numpy(), wt.cpu().numpy(), stride=2, padding=1)) <= 2e-3
+
+
 def test_static_scratch_refuses_what_does_not_fit():
     from neurotensor_b200 import _lib as L
     lib = L.lib()
