@@ -14,6 +14,7 @@
 #include <cstdint>
 #include <cstdlib>
 #include <cstring>
+#include <functional>
 #include <initializer_list>
 #include <memory>
 #include <numeric>
@@ -130,8 +131,14 @@ struct Storage {
             utils::check(ntb200_host_alloc(&ptr, n));
         }
     }
+    // Memory that somebody else owns (the reference's Bucket adopts an external pointer with a deleter the same way,
+    // nt/memory/bucket.cpp:149-166); `release` runs when the last tensor viewing it goes away.
+    std::function<void(void*)> release;
+    Storage(void* external, size_t n, DeviceType dev, std::function<void(void*)> deleter)
+        : ptr(external), bytes(n), device(dev), release(std::move(deleter)) {}
     ~Storage() {
         if (!ptr) return;
+        if (release) { release(ptr); return; }
         if (device == DeviceType::CUDA) ntb200_free_async(ptr, nullptr);
         else ntb200_host_free(ptr);
     }
@@ -183,6 +190,35 @@ class Tensor {
         } else {
             std::memcpy(t.data_ptr(), src, n);
         }
+        return t;
+    }
+
+    // A contiguous tensor over memory owned elsewhere; `deleter` (may be empty) runs when the last view is gone.
+    static Tensor adopt(void* ptr, SizeRef shape, DType dt, DeviceType dev = DeviceType::CUDA,
+                        std::function<void(void*)> deleter = [](void*) {}) {
+        Tensor t;
+        t.storage_ = std::make_shared<detail::Storage>(ptr, size_t(shape.multiply()) * dtype_size(dt), dev, std::move(deleter));
+        t.shape_ = std::move(shape);
+        t.strides_ = detail::contiguous_strides(t.shape_);
+        t.dtype_ = dt;
+        return t;
+    }
+    // Columns [c0, c0 + n) of a 2-D tensor: a strided view sharing the storage.
+    Tensor columns(int64_t c0, int64_t n) const {
+        utils::throw_exception(dims() == 2 && c0 >= 0 && n >= 0 && c0 + n <= shape_[1], "columns: range outside the tensor");
+        Tensor t = *this;
+        t.shape_ = SizeRef({shape_[0], n});
+        t.offset_ = offset_ + c0 * strides_[1];
+        return t;
+    }
+    // Rows [r0, r0 + n) of a tensor (first dimension): a view sharing the storage.
+    Tensor rows(int64_t r0, int64_t n) const {
+        utils::throw_exception(dims() >= 1 && r0 >= 0 && n >= 0 && r0 + n <= shape_[0], "rows: range outside the tensor");
+        Tensor t = *this;
+        std::vector<int64_t> s = shape_.Vec();
+        s[0] = n;
+        t.shape_ = SizeRef(s);
+        t.offset_ = offset_ + r0 * strides_[0];
         return t;
     }
 

@@ -7,6 +7,7 @@
 
 #include <cstdio>
 #include <iostream>
+#include <thread>
 
 static int g_failed = 0, g_run = 0;
 template <class F>
@@ -170,8 +171,8 @@ int main(int argc, char** argv) {
         REQUIRE(o.shape() == SizeRef({3, 4, 3}));
         o.backward(grad);
         REQUIRE(fn::allclose(x.grad(), fn::from_numpy(gold + "linear_xgrad.npy")));
-        REQUIRE(fn::allclose(w.grad(), fn::from_numpy(gold + "linear_wgrad.npy"), 1e-5, 1e-6));
-        REQUIRE(fn::allclose(b.grad(), fn::from_numpy(gold + "linear_bgrad.npy"), 1e-5, 1e-6));
+        REQUIRE(fn::allclose(w.grad(), fn::from_numpy(gold + "linear_wgrad.npy")));
+        REQUIRE(fn::allclose(b.grad(), fn::from_numpy(gold + "linear_bgrad.npy")));
     });
 
     for (const char* ext : {"", "_batched"}) {
@@ -182,10 +183,10 @@ int main(int argc, char** argv) {
             fn::ConvArgs args;
             args.ph = args.pw = 1;
             TensorGrad o = fn::conv2d(x, w, args);
-            REQUIRE(fn::allclose(o.detach(), fn::from_numpy(gold + "conv2d_output" + e + ".npy"), 1e-5, 1e-6));
+            REQUIRE(fn::allclose(o.detach(), fn::from_numpy(gold + "conv2d_output" + e + ".npy")));
             o.backward(fn::from_numpy(gold + "conv2d_grad" + e + ".npy"));
-            REQUIRE(fn::allclose(x.grad(), fn::from_numpy(gold + "conv2d_xgrad" + e + ".npy"), 1e-4, 1e-6));
-            REQUIRE(fn::allclose(w.grad(), fn::from_numpy(gold + "conv2d_wgrad" + e + ".npy"), 1e-4, 1e-5));
+            REQUIRE(fn::allclose(x.grad(), fn::from_numpy(gold + "conv2d_xgrad" + e + ".npy")));
+            REQUIRE(fn::allclose(w.grad(), fn::from_numpy(gold + "conv2d_wgrad" + e + ".npy")));
         });
     }
 
@@ -193,25 +194,25 @@ int main(int argc, char** argv) {
         run_test(("Conv2d Autograd test, groups = 2 (golden)" + e).c_str(), [&] {
             TensorGrad x(fn::from_numpy(gold + "conv2d_input" + e + ".npy"), true), w(fn::from_numpy(gold + "conv2d_weight" + e + ".npy"), true);
             TensorGrad o = fn::conv2d(x, w, fn::ConvArgs{}, 2);
-            REQUIRE(fn::allclose(o.detach(), fn::from_numpy(gold + "conv2d_output" + e + ".npy"), 1e-4, 1e-5));
+            REQUIRE(fn::allclose(o.detach(), fn::from_numpy(gold + "conv2d_output" + e + ".npy")));
             o.backward(fn::from_numpy(gold + "conv2d_grad" + e + ".npy"));
-            REQUIRE(fn::allclose(x.grad(), fn::from_numpy(gold + "conv2d_xgrad" + e + ".npy"), 1e-4, 1e-5));
-            REQUIRE(fn::allclose(w.grad(), fn::from_numpy(gold + "conv2d_wgrad" + e + ".npy"), 1e-4, 1e-5));
+            REQUIRE(fn::allclose(x.grad(), fn::from_numpy(gold + "conv2d_xgrad" + e + ".npy")));
+            REQUIRE(fn::allclose(w.grad(), fn::from_numpy(gold + "conv2d_wgrad" + e + ".npy")));
         });
     }
     run_test("conv1d and conv_transpose2d (golden)", [&] {
         Tensor o1 = fn::conv1d(fn::from_numpy(gold + "conv1d_input_batched.npy"), fn::from_numpy(gold + "conv1d_weight_batched.npy"), 1, 1);
-        REQUIRE(fn::allclose(o1, fn::from_numpy(gold + "conv1d_output_batched.npy"), 1e-4, 1e-5));
+        REQUIRE(fn::allclose(o1, fn::from_numpy(gold + "conv1d_output_batched.npy")));
         fn::ConvArgs a;
         a.sh = a.sw = 2; a.ph = a.pw = 1;
         Tensor o2 = fn::conv_transpose2d(fn::from_numpy(gold + "conv_transpose2d_input_batched.npy"),
                                          fn::from_numpy(gold + "conv_transpose2d_weight_batched.npy"), a, 1, 1);
-        REQUIRE(fn::allclose(o2, fn::from_numpy(gold + "conv_transpose2d_output_batched.npy"), 1e-4, 1e-5));
+        REQUIRE(fn::allclose(o2, fn::from_numpy(gold + "conv_transpose2d_output_batched.npy")));
         fn::ConvArgs b;
         b.ph = b.pw = 1;
         Tensor o3 = fn::conv_transpose2d(fn::from_numpy(gold + "conv_transpose2d_input_grouped.npy"),
                                          fn::from_numpy(gold + "conv_transpose2d_weight_grouped.npy"), b, 0, 0, 5);
-        REQUIRE(fn::allclose(o3, fn::from_numpy(gold + "conv_transpose2d_output_grouped.npy"), 1e-4, 1e-5));
+        REQUIRE(fn::allclose(o3, fn::from_numpy(gold + "conv_transpose2d_output_grouped.npy")));
     });
 
     run_test("layers::Conv2D: convolution plus per-channel bias, and the three gradients", [] {
@@ -251,7 +252,7 @@ int main(int argc, char** argv) {
         Tensor col = fn::unfold2d(x, 3, 2, args);
         REQUIRE(fn::allclose(col, fn::from_numpy(gold + "unfold_output.npy"), 0, 0));
         Tensor dx = fn::unfold2d_backward(fn::from_numpy(gold + "unfold_grad.npy"), 8, 8, 3, 2, args);
-        REQUIRE(fn::allclose(dx, fn::from_numpy(gold + "unfold_input_grad.npy"), 1e-5, 1e-6));
+        REQUIRE(fn::allclose(dx, fn::from_numpy(gold + "unfold_input_grad.npy")));
     });
 
     run_test("MLP through layers::Linear, relu and loss::MSE: forward + backward", [] {
@@ -367,6 +368,100 @@ int main(int argc, char** argv) {
         }
         REQUIRE(worst <= 1e-6);
     });
+
+    run_test("named-argument forms (nt/nt.h:812-850; conv calls as in tests/src/conv_autograd_test.cpp:140,266)", [&] {
+        Tensor a = nt::randn_seeded({4, 6}, DType::Float32, 31), b = nt::randn_seeded({5, 6}, DType::Float32, 32);
+        const auto plain = fn::matmult(a, b, false, true).to_vector<float>();
+        REQUIRE(nt::matmult(a, b, nt::transpose_b = true).to_vector<float>() == plain);
+        REQUIRE(nt::matmult(nt::other = b, nt::input = a, nt::transpose_b = true).to_vector<float>() == plain);
+        REQUIRE(nt::matmult(a, b, nullptr, false, true).to_vector<float>() == plain);
+        Tensor c = fn::zeros({4, 5});
+        Tensor r = nt::matmult(a, b, nt::out = c, nt::transpose_b = true);       // C += op(A).op(B) into the caller's tensor
+        REQUIRE(r.shares_storage_with(c) && c.to_vector<float>() == plain);
+        Tensor bias = nt::randn_seeded({5}, DType::Float32, 33);
+        REQUIRE(nt::linear(a, b, bias, nt::transpose_b = true).to_vector<float>() == fn::linear(a, b, bias, false, true).to_vector<float>());
+        REQUIRE(nt::linear(nt::input = a, nt::weight = b, nt::bias = bias, nt::transpose_b = true).shape() == SizeRef({4, 5}));
+        // the same forms on TensorGrad, with the reference's conv2d golden case written the way its test writes it
+        using namespace nt;   // stride = 1, padding = 1
+        TensorGrad x(fn::from_numpy(gold + "conv2d_input.npy"), true), w(fn::from_numpy(gold + "conv2d_weight.npy"), true);
+        TensorGrad o = nt::conv2d(x, w, stride = 1, padding = 1);
+        REQUIRE(fn::allclose(o.detach(), fn::from_numpy(gold + "conv2d_output.npy")));
+        o.backward(fn::from_numpy(gold + "conv2d_grad.npy"));
+        REQUIRE(fn::allclose(x.grad(), fn::from_numpy(gold + "conv2d_xgrad.npy")));
+        REQUIRE(fn::allclose(w.grad(), fn::from_numpy(gold + "conv2d_wgrad.npy")));
+        Tensor o1 = nt::conv1d(fn::from_numpy(gold + "conv1d_input_batched.npy"), fn::from_numpy(gold + "conv1d_weight_batched.npy"),
+                               stride = 1, padding = 1);
+        REQUIRE(fn::allclose(o1, fn::from_numpy(gold + "conv1d_output_batched.npy")));
+        TensorGrad xg(fn::from_numpy(gold + "conv2d_input_grouped.npy"), true), wg(fn::from_numpy(gold + "conv2d_weight_grouped.npy"), true);
+        REQUIRE(fn::allclose(nt::conv2d(xg, wg, stride = 1, groups = 2).detach(), fn::from_numpy(gold + "conv2d_output_grouped.npy")));
+    });
+
+    run_test("nt::distributed on one rank: shard arithmetic and a column block gathered at an offset", [&] {
+        namespace ds = nt::distributed;
+        int64_t covered = 0;
+        for (int r = 0; r < 8; ++r) {
+            auto [s0, n] = ds::shard(16384, 8, r, 8);
+            REQUIRE(s0 == covered && n == 2048);
+            covered += n;
+        }
+        REQUIRE(ds::shard(5, 2, 0).second == 3 && ds::shard(5, 2, 1).first == 3);
+        REQUIRE(throws_invalid_argument([&] { ds::shard(5, 2, 2); }));
+        ds::Communicator comm(0, 1);
+        Tensor x = nt::randn_seeded({200, 96}, DType::Float32, 41).to(DType::Float16);
+        Tensor w = nt::randn_seeded({96, 136}, DType::Float32, 42).to(DType::Float16);
+        Tensor bias = nt::randn_seeded({136}, DType::Float32, 43).to(DType::Float16);
+        ds::GatheredMatrix full(comm, 200, 400, DType::Float16);
+        Tensor pre;
+        Tensor act = ds::linear_allgather(comm, x, w, bias, full, 128, &pre);
+        Tensor expect = fn::linear(x, w, bias);
+        REQUIRE(pre.to_vector<uint16_t>() == expect.to_vector<uint16_t>());
+        REQUIRE(act.columns(128, 136).contiguous().to_vector<uint16_t>() == fn::relu(expect).to_vector<uint16_t>());
+        Tensor plain = ds::linear_allgather(comm, x, w, bias, full, 0);
+        REQUIRE(plain.columns(0, 136).contiguous().to_vector<uint16_t>() == expect.to_vector<uint16_t>());
+        comm.barrier();
+        nt::cuda::synchronize();
+    });
+
+    int n_devices = 0;
+    ntb200_device_count(&n_devices);
+    if (n_devices >= 2) {
+        run_test("nt::distributed, two ranks as two host threads on two GPUs: Linear + ReLU gathered by the GEMM epilogues", [&] {
+            namespace ds = nt::distributed;
+            ds::ThreadExchange exchange(2);
+            std::string errors[2];
+            auto worker = [&](int rank) {
+                try {
+                    nt::utils::check(ntb200_set_device(rank));
+                    ds::ThreadExchange::Rank me{&exchange, rank};
+                    ds::Communicator comm(rank, 2, ds::ThreadExchange::callback, &me);
+                    // same seeds on both ranks: replicated operands agree
+                    Tensor x = nt::randn_seeded({4096, 512}, DType::Float32, 51).to(DType::BFloat16);
+                    Tensor w = nt::randn_seeded({512, 4096}, DType::Float32, 52).to(DType::BFloat16);
+                    Tensor bias = nt::randn_seeded({4096}, DType::Float32, 53).to(DType::BFloat16);
+                    Tensor whole = fn::relu(fn::linear(x, w, bias));
+                    auto [c0, cn] = comm.shard(4096, 8);
+                    ds::GatheredMatrix bufs[2] = {ds::GatheredMatrix(comm, 4096, 4096, DType::BFloat16),
+                                                  ds::GatheredMatrix(comm, 4096, 4096, DType::BFloat16)};
+                    for (int step = 0; step < 6; ++step) {
+                        Tensor pre;
+                        Tensor act = ds::linear_allgather(comm, x, w.columns(c0, cn), bias.view({1, 4096}).columns(c0, cn), bufs[step & 1], c0, &pre);
+                        nt::cuda::synchronize();
+                        if (act.to_vector<uint16_t>() != whole.to_vector<uint16_t>()) throw std::runtime_error("gathered activation differs from the unsharded one");
+                    }
+                    comm.barrier();
+                    nt::cuda::synchronize();
+                    nt::utils::check(ntb200_check_device_status(nullptr));
+                } catch (const std::exception& e) {
+                    errors[rank] = e.what();
+                }
+            };
+            std::thread t0(worker, 0), t1(worker, 1);
+            t0.join();
+            t1.join();
+            nt::utils::check(ntb200_set_device(0));
+            REQUIRE(errors[0].empty() && errors[1].empty());
+        });
+    }
 
     nt::utils::check(ntb200_check_device_status(nullptr));
     std::printf("%d of %d cases failed\n", g_failed, g_run);

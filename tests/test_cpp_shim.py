@@ -17,7 +17,7 @@ def build_binary():
     src = os.path.join(ROOT, "tests", "cpp", "test_nt_shim.cpp")
     pkg = os.path.join(ROOT, "neurotensor_b200")
     cmd = ["g++", "-std=c++17", "-O1", "-Wall", "-Wextra", "-I", os.path.join(ROOT, "include"), "-I", pkg, src, "-o", BIN,
-           "-L", pkg, "-lntb200", "-Wl,-rpath," + pkg]
+           "-L", pkg, "-lntb200", "-Wl,-rpath," + pkg, "-pthread"]
     subprocess.check_call(cmd)
     return BIN
 

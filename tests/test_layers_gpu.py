@@ -174,9 +174,10 @@ def test_relu_mse_column_sum(api, oracle, dt):
     assert np.allclose(widen(host(cs)), xw.sum(axis=0), rtol=2e-2 if dt != "f32" else 1e-5, atol=1e-1 if dt != "f32" else 1e-4)
 
 
-def mlp_reference(oracle, x, w1, b1, w2, b2, target, bf16):
+def mlp_reference(oracle, x, w1, b1, w2, b2, target, bf16, grad_scale=1.0):
     """Linear -> ReLU -> Linear -> MSE forward and backward on the oracle (nt/nn/layers/Linear.cpp:22-24,
-    nt/nn/functional/matmult.cpp:253-273, nt/nn/Loss.cpp:49-55)."""
+    nt/nn/functional/matmult.cpp:253-273, nt/nn/Loss.cpp:49-55).  `grad_scale` (a power of two, hence exact) multiplies
+    the loss gradient before it is rounded to the 16-bit dtype."""
     wid = oracle.bf16_widen if bf16 else (lambda v: v.astype(np.float32))
     nar = oracle.bf16_round if bf16 else (lambda v: v.astype(np.float16))
     h = oracle.linear(x, w1, b1, bf16=bf16)
@@ -184,7 +185,7 @@ def mlp_reference(oracle, x, w1, b1, w2, b2, target, bf16):
     a16 = nar(a)
     y = oracle.linear(a16, w2, b2, bf16=bf16)
     loss, dy = oracle.mse(wid(y), wid(target))
-    dy16 = nar(dy)
+    dy16 = nar(dy * np.float32(grad_scale))
     da, dw2 = oracle.matmult_backward(a16, w2, dy16, bf16=bf16)
     dh16 = nar(np.where(mask, 0, wid(da)))
     dx, dw1 = oracle.matmult_backward(x, w1, dh16, bf16=bf16)
@@ -205,13 +206,20 @@ def test_mlp_forward_backward(api, oracle, bf16):
     b1 = mk(normal(rng, (H,), np.float32, 0.01))
     b2 = mk(normal(rng, (D,), np.float32, 0.01))
     t = mk(normal(rng, (B, D), np.float32))
-    ref = mlp_reference(oracle, x, w1, b1, w2, b2, t, bf16)
+    # Float16: the MSE gradient 2 (y - t) / (B D) is about 1e-5, below the smallest normal Float16 (6.1e-5), where the
+    # format keeps only a few bits and any two correct roundings differ by percents.  As Float16 training does, the
+    # gradient is scaled by a power of two (exact) before it is rounded; BFloat16 has the range and needs none.
+    grad_scale = 1.0 if bf16 else 4096.0
+    ref = mlp_reference(oracle, x, w1, b1, w2, b2, t, bf16, grad_scale)
     d = lambda v: dev(v, bf16)
     dx_, dw1_, dw2_, db1_, db2_, dt_ = d(x), d(w1), d(w2), d(b1), d(b2), d(t)
     h = api.linear(dx_, dw1_, db1_)
     a = api.relu(h)
     y = api.linear(a, dw2_, db2_)
     loss, dy = api.mse(y, dt_)
+    if grad_scale != 1.0:
+        _, dy32 = api.mse(y.float(), dt_.float())            # the Float32 gradient, scaled, then rounded once
+        dy = (dy32 * grad_scale).half()
     da, gw2 = api.matmult_backward(a, dw2_, dy)
     dh = api.relu_backward(h, da)
     gx, gw1 = api.matmult_backward(dx_, dw1_, dh)
