@@ -290,6 +290,19 @@ def main():
         target["peak"] = peaks["tflops_burst"]
         target["note"] = "20 launches after 3 warm-ups, operands (403 MB) exceed the L2"
         extras["target_8192"] = target
+        # ---- more than one GPU: the N-sharded MLP step (strong scaling) through the C-ABI partitioner
+        if world > 1:
+            from neurotensor_b200 import bench_mlp_sharded
+            rec = bench_mlp_sharded.measure(rank, world, dist, steps=20, check=True)
+            chk = rec.get("check") or {}
+            extras["mlp_n_sharded"] = {"workload": "BASELINE.json configs[3]: BFloat16 MLP 8192 x (4096 -> 16384 -> 4096), forward + backward, "
+                                                   "every GEMM split over its output columns", "scaling": "strong",
+                                       "ms_per_step": rec["ms_per_step"], "tflops": rec["tflops"], "gather": rec["gather"],
+                                       "kernels_per_step": rec["kernels_per_step_rank0"],
+                                       "matches_unsharded": bool(chk.get("bit_identical", False)),
+                                       "unsharded_ms_per_step_same_gpu": chk.get("unsharded_ms_per_step_same_gpu"),
+                                       "strong_scaling_efficiency": chk.get("strong_scaling_efficiency"), "check": chk}
+
         # ---- the same launch repeated for at least two seconds: what the GPU sustains under its power cap
         barrier()
         loop = max(50, int(2.2 / (ms_per_step * 1e-3)))
@@ -311,16 +324,6 @@ def main():
         extras["sustained"] = {"seconds": sus_ms * 1e-3, "launches": loop, "tflops_per_gpu": sus_tflops,
                                "peak": sus_peak, "frac": sus_tflops / sus_peak,
                                "peak_source": "%s (sustained bf16 cuBLAS figure)" % peaks["source"], "clocks": sus_clocks}
-        # ---- more than one GPU: the N-sharded MLP step (strong scaling) through the C-ABI partitioner
-        if world > 1:
-            from neurotensor_b200 import bench_mlp_sharded
-            rec = bench_mlp_sharded.measure(rank, world, dist, steps=10, check=True)
-            chk = rec.get("check") or {}
-            extras["mlp_n_sharded"] = {"workload": "BASELINE.json configs[3]: BFloat16 MLP 8192 x (4096 -> 16384 -> 4096), forward + backward, "
-                                                   "every GEMM split over its output columns", "scaling": "strong",
-                                       "ms_per_step": rec["ms_per_step"], "tflops": rec["tflops"], "gather": rec["gather"],
-                                       "kernels_per_step": rec["kernels_per_step_rank0"],
-                                       "matches_unsharded": bool(chk.get("bit_identical", False)), "check": chk}
 
     if rank != 0:
         if dist is not None:

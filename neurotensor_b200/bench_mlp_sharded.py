@@ -24,7 +24,7 @@ if ROOT not in sys.path:
 from neurotensor_b200 import _lib, partition  # noqa: E402
 
 
-def measure(rank, world, dist=None, steps=10, batch=8192, din=4096, hidden=16384, check=False, nccl=False, warmup=3):
+def measure(rank, world, dist=None, steps=10, batch=8192, din=4096, hidden=16384, check=False, nccl=False, warmup=3, phases=False):
     """Times the N-sharded step on the ranks of an initialised process group (dist = torch.distributed, or None for one
     rank) and returns the result record on every rank (`check` is filled on rank 0 only)."""
     B, D, H = batch, din, hidden
@@ -67,14 +67,56 @@ def measure(rank, world, dist=None, steps=10, batch=8192, din=4096, hidden=16384
     if check and rank == 0:
         ref = partition.ShardedMLP(w1, b1, w2, b2, 0, 1)
         rloss, rg = ref.step(x, t)
+        # the unsharded step timed on this rank's GPU in the state the sharded timing left it in: the denominator of
+        # the strong-scaling efficiency (the other ranks wait at the barrier below)
+        torch.cuda.synchronize()
+        u0, u1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        u0.record()
+        for _ in range(steps):
+            ref.step(x, t)
+        u1.record()
+        torch.cuda.synchronize()
+        unsharded_ms = u0.elapsed_time(u1) / steps
         d0, dn = partition.column_shard(D, world, rank)
         rel = lambda a, b: float(((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-30)).item())
         result_check = {"loss": [float(loss.item()), float(rloss.item())],
                         "dw1": rel(grads["w1"], rg["w1"][:, h0:h0 + hn]), "dw2": rel(grads["w2"], rg["w2"][:, d0:d0 + dn]),
                         "y": rel(grads["y"], rg["y"]),
+                        "unsharded_ms_per_step_same_gpu": unsharded_ms,
+                        "strong_scaling_efficiency": unsharded_ms / (world * ms),
                         "bit_identical": bool(torch.equal(grads["w1"], rg["w1"][:, h0:h0 + hn]) and
                                               torch.equal(grads["w2"], rg["w2"][:, d0:d0 + dn]) and torch.equal(grads["y"], rg["y"]))}
         del ref, rg
+    phase_ms = None
+    if phases and fused:
+        # device time of each phase of the fused step (CUDA events between the phases, averaged over the steps), and
+        # the layer-1 GEMM of the same shard shape without any peer to store to, for comparison
+        mlp.phase_events = []
+        barrier()
+        for _ in range(steps):
+            step(x, t)
+        barrier()
+        ev, mlp.phase_events = mlp.phase_events, None
+        phase_ms = {}
+        for (n0, e0_), (n1, e1_) in zip(ev[:-1], ev[1:]):
+            if n1 != "start":
+                phase_ms[n1] = phase_ms.get(n1, 0.0) + e0_.elapsed_time(e1_) / steps
+        from neurotensor_b200 import api
+        h_tmp = torch.empty((B, hn), dtype=dt, device="cuda")
+        a_tmp = torch.empty((B, hn), dtype=dt, device="cuda")
+        for _ in range(3):
+            api.gemm(x, mlp.w1, h_tmp, bias=mlp.b1, relu_out=a_tmp)
+        torch.cuda.synchronize()
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f0.record()
+        for _ in range(steps):
+            api.gemm(x, mlp.w1, h_tmp, bias=mlp.b1, relu_out=a_tmp)
+        f1.record()
+        torch.cuda.synchronize()
+        phase_ms["layer 1 GEMM + ReLU of the same shard shape, no peers (for comparison)"] = f0.elapsed_time(f1) / steps
+        es = 2
+        phase_ms["bytes stored to peers per step by layer 1 / layer 2"] = [B * hn * es * (world - 1), B * mlp.dn * es * (world - 1)]
+        del h_tmp, a_tmp
     flops = 5 * 2.0 * B * D * H
     record = {"config": "BFloat16 MLP %dx(%d->%d->%d) fwd+bwd step, N-sharded" % (B, D, H, D), "n_gpus": world,
               "ms_per_step": ms, "tflops": flops / (ms * 1e-3) / 1e12, "scaling": "strong", "steps": steps,
@@ -82,6 +124,8 @@ def measure(rank, world, dist=None, steps=10, batch=8192, din=4096, hidden=16384
               "gather": ("stores from the GEMM epilogues into peer-mapped buffers + flag exchange (ntb200_dist_gemm_allgather)" if fused
                          else ("none" if world == 1 else "NCCL all-gather + re-tile")),
               "check": result_check}
+    if phase_ms is not None:
+        record["phase_ms_rank%d" % rank] = phase_ms
     if fused:
         barrier()
         mlp.close()
@@ -97,6 +141,7 @@ def main():
     ap.add_argument("--check", action="store_true")
     ap.add_argument("--fused", action="store_true", help="(default) all-gathers fused into the GEMM epilogues: stores into peer buffers")
     ap.add_argument("--nccl", action="store_true", help="baseline: NCCL all-gather + re-tile kernel instead of the fused epilogues")
+    ap.add_argument("--phases", action="store_true", help="also time each phase of the fused step with CUDA events (rank 0 prints them)")
     args = ap.parse_args()
     rank, world, local = (int(os.environ.get(k, d)) for k, d in (("RANK", 0), ("WORLD_SIZE", 1), ("LOCAL_RANK", 0)))
     torch.cuda.set_device(local)
@@ -104,7 +149,7 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    record = measure(rank, world, dist, args.steps, args.batch, args.din, args.hidden, args.check, args.nccl)
+    record = measure(rank, world, dist, args.steps, args.batch, args.din, args.hidden, args.check, args.nccl, phases=args.phases)
     if rank == 0:
         print(json.dumps(record), flush=True)
     if dist is not None:

@@ -1032,6 +1032,217 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
     }
 }
 
+
+// ---- K slices inside a thread-block cluster ---------------------------------------------------------------------
+// Few rows against a large weight matrix are bound by reading the weights once, and a CTA streams them fastest on
+// wide tiles (bytes per issued instruction), of which a narrow output has too few to occupy every SM.  Here the S
+// CTAs of a cluster work on ONE 128 x BN output tile, each on its own slice of K: CTA r accumulates its partial tile
+// in tensor memory, spills it as fp32 into its own shared memory (over the operand ring, which is idle by then), and
+// after a cluster barrier CTA r adds columns [r BN/S, (r+1) BN/S) of all S partial tiles in slice order through
+// distributed shared memory, adds the bias and the previous C, rounds once and stores.  One launch, no partial tile
+// ever travels through HBM, and the sum order is fixed (slice 0, 1, ..., S-1), so results are reproducible.
+// Not persistent: one tile per cluster.  Roles as in umma_gemm_kernel; every wait is bounded.
+struct ClusterKParams {
+    UmmaParams u;          // geometry, operands, epilogue inputs (batch == 1)
+    int slices;            // S = cluster size
+    int blocks_per_slice;  // K blocks per slice (the last slice may have fewer, never zero)
+    int pitch;             // floats per row of a partial tile in shared memory (BN + 4)
+    int rows_live;         // rows of a tile that can hold results (min(128, m)), rounded up to 32
+    int c_wide_ok;         // C and its rows are 8-byte aligned: four results leave in one store
+};
+
+__device__ __forceinline__ float4 ld_cluster_f4(uint32_t local_addr, uint32_t cta_rank) {
+    float4 v;
+    asm volatile(
+        "{\n\t.reg .b32 remote;\n\t"
+        "mapa.shared::cluster.u32 remote, %4, %5;\n\t"
+        "ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [remote];\n\t}"
+        : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(local_addr), "r"(cta_rank) : "memory");
+    return v;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+umma_gemm_cluster_k_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const ClusterKParams cp) {
+    using T = Tile<BN, false>;
+    const UmmaParams& p = cp.u;
+    const int kStages = p.s_stages;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t ring_bytes = uint32_t(kStages) * p.s_stage_bytes + T::kABytes;
+    uint8_t* bar_gen = smem_gen + ring_bytes;
+    const uint32_t bar_base = smem_base + ring_bytes;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+    const uint32_t tfull_bar = bar_base + 8u * (2 * kStages);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_gen + 8 * (2 * kStages + 1));
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_cta_rank();
+    const int tile = blockIdx.x / cp.slices;
+    const int mi = tile / p.tiles_n, ni = tile - mi * p.tiles_n;
+    const int m0 = mi * kBM, n0 = ni * BN;
+    const int kb_begin = int(rank) * cp.blocks_per_slice;
+    const int kb_end = min(p.k_blocks, kb_begin + cp.blocks_per_slice);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        mbar_init(tfull_bar, 1);
+        *abort_flag = 0;
+        fence_barrier_init();
+        fence_proxy_async_smem();
+        tma_prefetch_desc(&tma_a);
+        tma_prefetch_desc(&tma_b);
+    }
+    if (warp == 1) {
+        tmem_alloc<1>(smem_u32(const_cast<uint32_t*>(tmem_slot)), BN);
+        tmem_relinquish<1>();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer: this slice's K blocks
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int kb = kb_begin; kb < kb_end; ++kb) {
+                if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
+                    raise_timeout(abort_flag, 0x21);
+                    ok = false;
+                    break;
+                }
+                const uint32_t a_dst = smem_base + stage * p.s_stage_bytes;
+                const uint32_t b_dst = a_dst + p.s_a_bytes;
+                const uint32_t bar = full_bar(stage);
+                mbar_expect_tx(bar, p.s_stage_tx);
+                const int k0 = kb * p.block_k;
+                if (!p.a_mn_major) {
+                    tma_load_3d(a_dst, &tma_a, bar, k0, m0, 0);
+                } else {
+                    for (int c = 0; c < p.a_chunks; ++c) tma_load_3d(a_dst + c * p.chunk_bytes, &tma_a, bar, m0 + c * p.chunk_mn, k0, 0);
+                }
+                if (!p.b_mn_major) {
+                    tma_load_3d(b_dst, &tma_b, bar, k0, n0, 0);
+                } else {
+                    for (int c = 0; c < p.b_chunks; ++c) tma_load_3d(b_dst + c * p.chunk_bytes, &tma_b, bar, n0 + c * p.chunk_mn, k0, 0);
+                }
+                if (++stage == kStages) { stage = 0; phase ^= 1u; }
+            }
+            if (ok) {   // leave no copy in flight: every stage released means every load has landed and been consumed
+                for (int s = 0; s < kStages; ++s) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { raise_timeout(abort_flag, 0x22); break; }
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int kb = kb_begin; kb < kb_end; ++kb) {
+                if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
+                    raise_timeout(abort_flag, 0x24);
+                    ok = false;
+                    break;
+                }
+                tcgen05_fence_after();
+                const uint32_t a_addr = smem_base + stage * p.s_stage_bytes;
+                const uint64_t a_desc = make_smem_desc_sw128(a_addr, p.a_lbo, 1024);
+                const uint64_t b_desc = make_smem_desc_sw128(a_addr + p.s_a_bytes, p.b_lbo, 1024);
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    umma<MmaKind::f16, 1>(tmem_base, a_desc + uint64_t(k * p.a_kstep), b_desc + uint64_t(k * p.b_kstep), p.idesc,
+                                          ((kb - kb_begin) | k) != 0);
+                umma_commit<1>(empty_bar(stage));
+                if (++stage == kStages) { stage = 0; phase ^= 1u; }
+            }
+            if (ok) umma_commit<1>(tfull_bar);   // this slice's partial tile is complete
+        }
+    } else {
+        // ------------------------------------------------------------------ spill the partial tile to shared memory
+        const int quad = warp & 3;
+        bool ok = mbar_wait(tfull_bar, 0, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+            if (lane == 0) raise_timeout(abort_flag, 0x25);
+        } else if (quad * 32 < cp.rows_live) {
+            tcgen05_fence_after();
+            // the ring is idle (every MMA has completed, so every load has been consumed): the partial tile goes there
+            float* dst = reinterpret_cast<float*>(smem_gen) + (quad * 32 + lane) * cp.pitch;
+#pragma unroll 1
+            for (int cc = 0; cc < BN / 32; ++cc) {
+                uint32_t v[32];
+                tmem_ld_32x32b_x32(tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(cc * 32), v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int q = 0; q < 8; ++q)
+                    *reinterpret_cast<float4*>(dst + cc * 32 + 4 * q) =
+                        make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]), __uint_as_float(v[4 * q + 2]), __uint_as_float(v[4 * q + 3]));
+            }
+            tcgen05_fence_before();
+        }
+    }
+
+    // ---------------------------------------------------------------------- reduce across the cluster
+    __syncwarp();
+    cluster_sync_all();   // every CTA's partial tile is in its shared memory (or its abort flag is up)
+    if (*abort_flag == 0) {
+        const int cols_mine = BN / cp.slices;               // a multiple of 4 (BN 128 / 256, S <= 8)
+        const int groups = cols_mine >> 2;
+        const int rows = min(kBM, p.m - m0);
+        const uint32_t tile_base = smem_base;
+        for (int i = threadIdx.x; i < rows * groups; i += kThreads) {
+            const int row = i / groups, gcol = (i - row * groups) * 4 + int(rank) * cols_mine;
+            const int col = n0 + gcol;
+            if (col >= p.n) continue;
+            const uint32_t addr = tile_base + uint32_t(row * cp.pitch + gcol) * 4u;
+            float4 acc = ld_cluster_f4(addr, 0);
+            for (int s = 1; s < cp.slices; ++s) {
+                const float4 v = ld_cluster_f4(addr, uint32_t(s));
+                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            }
+            float f[4] = {acc.x, acc.y, acc.z, acc.w};
+            const int grow = m0 + row;
+            uint16_t* dst = static_cast<uint16_t*>(p.c) + (long long)grow * p.c_rs + col;
+            const uint16_t* bias = static_cast<const uint16_t*>(p.bias);
+            uint32_t r[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (col + j < p.n) {
+                    if (bias) f[j] += to_float_bits16(bias[(long long)grow * p.bias_rs + (long long)(col + j) * p.bias_cs], p.out_kind);
+                    if (p.accumulate) f[j] += to_float_bits16(dst[j], p.out_kind);
+                }
+                r[j] = from_float_bits16(f[j], p.out_kind);
+            }
+            if (cp.c_wide_ok && col + 4 <= p.n) {
+                *reinterpret_cast<uint2*>(dst) = make_uint2(r[0] | (r[1] << 16), r[2] | (r[3] << 16));
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (col + j < p.n) dst[j] = uint16_t(r[j]);
+            }
+        }
+    }
+    // nobody leaves while a neighbour may still read its shared memory
+    tcgen05_fence_before();
+    cluster_sync_all();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tmem_dealloc<1>(tmem_base, BN);
+    }
+}
+
 // ---- host side ---------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -1653,6 +1864,7 @@ struct F16Plan {
     TileChoice tile;
     int splits;
     bool valid;
+    double us = 1e30;   // the model's estimate for the chosen combination
 };
 
 F16Plan plan_f16_tiles(const GemmArgs& g, int es = 2) {
@@ -1681,7 +1893,7 @@ F16Plan plan_f16_tiles(const GemmArgs& g, int es = 2) {
             if (s > 1) us += 3.0 + double(s) * double(g.m) * double(g.n) * 8.0 / 4.0e6;   // partial tiles out and back in (mostly L2)
             if (us < best_us * 0.97) {   // candidates come in order of preference: a later one has to be clearly better
                 best_us = us;
-                best = F16Plan{{c.pair, c.bn}, s, true};
+                best = F16Plan{{c.pair, c.bn}, s, true, us};
             }
         }
     }
@@ -1753,6 +1965,126 @@ int launch_f16_split_k(const GemmArgs& g, const Planned& pl16, int splits, const
     return rc;
 }
 
+
+// K slices inside a cluster (umma_gemm_cluster_k_kernel): one launch for few-row products of 16-bit floats.
+// Returns NTB200_ERR_UNSUPPORTED (nothing launched, error text untouched) when the shape does not fit the scheme.
+const bool g_no_cluster_k = [] { const char* e = getenv("NTB200_NO_CLUSTER_K"); return e && e[0] == '1'; }();
+
+template <int BN>
+int launch_cluster_k_instance(const Maps& maps, ClusterKParams cp, int a_rows_staged, int clusters, cudaStream_t stream) {
+    using T = Tile<BN, false>;
+    UmmaParams& p = cp.u;
+    p.s_a_bytes = uint32_t(a_rows_staged) * 128u;
+    p.s_stage_bytes = p.s_a_bytes + T::kBBytes;
+    p.s_stage_tx = p.s_stage_bytes;
+    p.s_stages = int(std::min<uint32_t>(uint32_t(T::kMaxStages), (T::kRingBudget - T::kABytes) / p.s_stage_bytes));
+    const uint32_t ring = uint32_t(p.s_stages) * p.s_stage_bytes + T::kABytes;
+    if (uint32_t(cp.rows_live) * uint32_t(cp.pitch) * 4u > ring) return NTB200_ERR_UNSUPPORTED;   // the partial tile lives in the ring
+    const uint32_t smem = ring + T::kBarrierBytes + 1024;
+    auto kernel = umma_gemm_cluster_k_kernel<BN>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(umma_gemm_cluster_k_kernel)");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(unsigned(clusters * cp.slices), 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = unsigned(cp.slices);
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    e = cudaLaunchKernelEx(&cfg, kernel, maps.a.map, maps.b.map, cp);
+    if (e != cudaSuccess) return cuda_fail(e, "umma_gemm_cluster_k_kernel launch");
+    count_launch();
+    return NTB200_OK;
+}
+
+// Tile width and slice count for the cluster scheme, with an estimate of its run time in microseconds (same units
+// and fitted per-K-block costs as plan_f16_tiles).  valid = false: the shape does not fit.
+struct ClusterKPlan {
+    int bn, slices;
+    double us;
+    bool valid;
+};
+
+ClusterKPlan plan_cluster_k(const GemmArgs& g, int es) {
+    ClusterKPlan best{0, 0, 1e30, false};
+    if (g_no_cluster_k || g.no_alloc || g.batch != 1 || g.relu_out || g.mask_src || g.n_peers > 0) return best;
+    if (g.k < 2048 || g.n * g.k < (int64_t(1) << 23)) return best;
+    const int block_k = 128 / es;
+    const int k_blocks = int((g.k + block_k - 1) / block_k);
+    const int sms = sm_count();
+    const int64_t tiles_m = (g.m + kBM - 1) / kBM;
+    const double dram_us = (double(g.m) * g.k + double(g.k) * g.n + double(g.m) * g.n) * es / 4.5e6;
+    // as many CTAs as fit in one wave, wide tiles first (bytes per issued instruction)
+    for (int bn : {256, 128}) {
+        if (g.n <= bn / 2) continue;
+        const int64_t tiles = tiles_m * ((g.n + bn - 1) / bn);
+        const double us_per_k_block = bn == 256 ? 0.39 : 0.34;
+        for (int sl : {8, 4, 2}) {
+            if (k_blocks / sl < 4) continue;
+            const int bps = (k_blocks + sl - 1) / sl;
+            if ((sl - 1) * bps >= k_blocks) continue;         // an empty last slice
+            const int64_t ctas = tiles * sl;
+            if (ctas > sms || ctas * 2 < sms) continue;       // one wave, and not a mostly idle GPU
+            const double us = 8.0 + std::max(double(bps) * us_per_k_block, dram_us) + 1.5;
+            if (us < best.us * 0.97) best = ClusterKPlan{bn, sl, us, true};
+        }
+    }
+    return best;
+}
+
+int launch_f16_cluster_k(const GemmArgs& g, const Planned& pl16, const ClusterKPlan& plan, cudaStream_t stream) {
+    if (!plan.valid) return NTB200_ERR_UNSUPPORTED;
+    const int es = pl16.es, block_k = 128 / es;
+    const int k_blocks = int((g.k + block_k - 1) / block_k);
+    const int bn = plan.bn, slices = plan.slices;
+    Maps maps;
+    int a_rows_staged = kBM;
+    {
+        OperandPlan probe;
+        if (plan_operand(g.a, es, pl16.dt, g.m, g.k, g.a_rs, g.a_cs, 1, 0, kBM, block_k, &probe)) return NTB200_ERR_UNSUPPORTED;
+        if (!probe.mn_major && g.m <= 64 && !g_full_a_tile) a_rows_staged = g.m <= 8 ? 8 : (g.m <= 16 ? 16 : (g.m <= 32 ? 32 : 64));
+    }
+    const int tiles_m = int((g.m + kBM - 1) / kBM);
+    if (plan_operand(g.a, es, pl16.dt, g.m, g.k, g.a_rs, g.a_cs, 1, 0, a_rows_staged, block_k, &maps.a)) return NTB200_ERR_UNSUPPORTED;
+    if (plan_operand(g.b, es, pl16.dt, g.n, g.k, g.b_cs, g.b_rs, 1, 0, bn, block_k, &maps.b)) return NTB200_ERR_UNSUPPORTED;
+    ClusterKParams cp{};
+    UmmaParams& p = cp.u;
+    p.m = int(g.m); p.n = int(g.n); p.k = int(g.k); p.batch = 1;
+    p.tiles_m = tiles_m; p.tiles_n = int((g.n + bn - 1) / bn);
+    p.k_blocks = k_blocks; p.chunk_blocks = k_blocks; p.group_m = 8; p.total_tiles = p.tiles_m * p.tiles_n;
+    p.block_k = block_k;
+    p.idesc = make_instr_desc(pl16.d_fmt, pl16.in_fmt, pl16.in_fmt, maps.a.mn_major, maps.b.mn_major, uint32_t(kBM), uint32_t(bn));
+    p.a_mn_major = maps.a.mn_major; p.b_mn_major = maps.b.mn_major;
+    p.chunk_mn = 128 / es;
+    p.chunk_bytes = uint32_t(block_k) * 128u;
+    p.a_chunks = kBM / p.chunk_mn;
+    p.b_chunks = bn / p.chunk_mn;
+    p.a_lbo = maps.a.mn_major ? p.chunk_bytes : 16u;
+    p.b_lbo = maps.b.mn_major ? p.chunk_bytes : 16u;
+    const uint32_t mn_kstep = uint32_t(32 / es) * 128u / 16u;
+    p.a_kstep = maps.a.mn_major ? mn_kstep : 2u;
+    p.b_kstep = maps.b.mn_major ? mn_kstep : 2u;
+    p.c = g.c; p.c_rs = g.c_rs; p.c_bs = g.c_bs;
+    p.bias = g.bias; p.bias_rs = g.bias_rs; p.bias_cs = g.bias_cs; p.bias_bs = g.bias_bs;
+    p.accumulate = g.accumulate;
+    p.out_kind = pl16.out_kind;
+    cp.slices = slices;
+    cp.blocks_per_slice = (k_blocks + slices - 1) / slices;
+    if ((slices - 1) * cp.blocks_per_slice >= k_blocks) return NTB200_ERR_UNSUPPORTED;   // an empty last slice
+    cp.pitch = bn + 4;
+    cp.rows_live = int(std::min<int64_t>(kBM, (g.m + 31) / 32 * 32));   // every M tile but the last is full
+    cp.c_wide_ok = (reinterpret_cast<uintptr_t>(g.c) % 8 == 0 && g.c_rs % 4 == 0) ? 1 : 0;
+    const int rc = bn == 256 ? launch_cluster_k_instance<256>(maps, cp, a_rows_staged, p.total_tiles, stream)
+                             : launch_cluster_k_instance<128>(maps, cp, a_rows_staged, p.total_tiles, stream);
+    if (rc == NTB200_OK) note_route(g.dtype == NTB200_F16 ? "umma_f16_clusterk" : "umma_bf16_clusterk");
+    return rc;
+}
+
 }  // namespace
 
 bool umma_supported(const GemmArgs& g, const char** why) {
@@ -1793,6 +2125,15 @@ int launch_umma_gemm(const GemmArgs& g, cudaStream_t stream) {
         if (const int f = tune_int("NTB200_FORCE_SPLITS")) {
             choice = nullptr;
             splits = (!g.no_alloc && g.batch == 1 && !g.relu_out && !g.mask_src && g.n_peers == 0 && g.n % 4 == 0 && g.k % (64 * f) == 0) ? f : 1;
+        }
+        if (!tune_int("NTB200_FORCE_SPLITS")) {
+            // K slices inside a cluster (one launch): always for few rows; for more rows when its estimate beats the
+            // planner's best tile kind / slice count by a margin
+            const ClusterKPlan ck = plan_cluster_k(g, es);
+            if (ck.valid && (g.m <= kBM || !plan.valid || ck.us < plan.us * 0.95)) {
+                const int rc = launch_f16_cluster_k(g, pl, ck, stream);
+                if (rc != NTB200_ERR_UNSUPPORTED) return rc;
+            }
         }
         if (splits > 1) return launch_f16_split_k(g, pl, splits, choice, stream);
     }

@@ -12,6 +12,8 @@
 
 #include <algorithm>
 
+#include <cstdlib>
+
 #include "internal.h"
 
 namespace ntb200 {
@@ -188,6 +190,8 @@ int launch_gemv_rows(const GemmArgs& g, bool kn_layout, cudaStream_t stream) {
 // One 2-D problem with one or two rows, 16-bit floats, K-contiguous A, weights contiguous along N or along K with
 // 16-byte aligned rows, plain epilogue.
 bool gemv_supported(const GemmArgs& g) {
+    static const bool disabled = [] { const char* e = getenv("NTB200_NO_GEMV"); return e && e[0] == '1'; }();   // A/B measurements
+    if (disabled) return false;
     if (g.dtype != NTB200_F16 && g.dtype != NTB200_BF16) return false;
     if (g.batch != 1 || g.m < 1 || g.m > kGemvMaxRows || g.k < 512 || g.n < 512) return false;
     if (g.a_ptrs || g.b_ptrs || g.c_ptrs || g.relu_out || g.mask_src || g.n_peers) return false;

@@ -306,19 +306,35 @@ class ShardedMLP:
         par = f["parity"]
         f["parity"] ^= 1
         comm, abuf, ybuf = f["comm"], f["a"][par], f["y"][par]
+        mark = self._mark
+        mark("start")
         h_loc = comm.gemm_allgather(x, self.w1, abuf, self.h0, bias=self.b1, relu=True)
+        mark("layer 1: GEMM + ReLU, activation block stored into every rank, flag exchange")
         a = abuf.local                                                         # [B, H], every rank's block
         w2_cols = self.w2[:, self.d0:self.d0 + self.dn]
         y = comm.gemm_allgather(a, w2_cols, ybuf, self.d0, bias=self.b2[self.d0:self.d0 + self.dn])
+        mark("layer 2: GEMM, output block stored into every rank, flag exchange")
         loss, dy = api.mse(y, target)
+        mark("MSE and its gradient")
         dy_loc = dy[:, self.d0:self.d0 + self.dn]
         gw2_loc = api.matmult(a, dy_loc, True, False)
         gb2_loc = api.column_sum(dy_loc.contiguous())
+        mark("dW2, db2")
         w2_rows = self.w2[self.h0:self.h0 + self.hn]
         dh_loc = api.matmult_relu_backward(dy, w2_rows, h_loc, True)           # ReLU mask in the epilogue
+        mark("dH with the ReLU mask")
         gw1_loc = api.matmult(x, dh_loc, True, False)
         gb1_loc = api.column_sum(dh_loc)
+        mark("dW1, db1")
         return loss, dict(w1=gw1_loc, b1=gb1_loc, w2=gw2_loc, b2=gb2_loc, y=y)
+
+    def _mark(self, name):
+        """Phase boundary of step_fused: a CUDA event when `phase_events` is a list (bench_mlp_sharded --phases)."""
+        ev = getattr(self, "phase_events", None)
+        if ev is not None:
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            ev.append((name, e))
 
     def step(self, x, target):
         from . import api

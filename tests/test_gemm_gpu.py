@@ -389,7 +389,9 @@ def test_few_rows_split_the_k_axis(api, oracle, L, m, n, k, weights_nk, bf16):
     x, bias = cd.enc(x32), cd.enc(b32)
     w = cd.enc(np.ascontiguousarray(w32.T)).t() if weights_nk else cd.enc(w32)    # [K, N] view either way
     dec = cd.dec
-    split_route = "umma_bf16_splitk" if bf16 else "umma_f16_splitk"
+    # up to 128 rows the K slices run inside a thread-block cluster (one launch, partial tiles added through
+    # distributed shared memory); more rows take the K slices as batches of the pair kernel plus a reduction kernel
+    split_route = ("umma_bf16" if bf16 else "umma_f16") + ("_clusterk" if m <= 128 else "_splitk")
     got = api.linear(x, w, bias)
     assert L.last_route() == split_route
     # K = 4096 / 8192: Float16 is beyond the depth at which fp32 accumulation stays within 2e-3 of the reference's

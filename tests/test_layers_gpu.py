@@ -234,12 +234,21 @@ def test_mlp_forward_backward(api, oracle, bf16):
     gx_1, gw1_1 = api.matmult_backward(dx_, dw1_, dh16)
     for got, key in ((gw2_1, "dw2"), (gw1_1, "dw1"), (gx_1, "dx"), (da_1, "da")):
         assert rel(got, ref[key]) <= tol, (key, rel(got, ref[key]))
-    # The device's own chain end to end.  Its gradients depend on up to three GEMMs in a row (y -> dy -> dh -> dW1),
-    # each within 2e-3 of the oracle's, and dy = 2 (y - t) / n amplifies a difference in y by |y| / |y - t| (about 0.6
-    # here: y is small against the N(0,1) targets), so the chain is held to three times the single-GEMM bar.
-    chain_tol = 3 * tol
+    # The device's own chain end to end.  Two things separate it from the oracle's chain beyond the single-GEMM bar.
+    # (1) Depth: a gradient depends on up to three GEMMs in a row (y -> dy -> dh -> dW1), each within 2e-3.
+    # (2) The ReLU mask: it is taken from the sign of h, and where |h| is below the distance between the two ways of
+    # rounding h (fp32 accumulation here, the reference's fp16 rounding every 16 k there: about 1e-3 absolute at this
+    # depth) the two chains disagree on the sign, so an element of dh is the full gradient in one chain and zero in the
+    # other.  A fraction f of disagreeing elements among the active ones moves dh, and everything computed from it, by
+    # sqrt(f) in relative Frobenius norm: f = 1e-4 already costs 1e-2.  BFloat16 has no such second rounding scheme
+    # (its oracle accumulates in fp32 like the device), so f is zero or nearly so there.  The chain is held to
+    # 3 * 2e-3 + sqrt(f), with f measured on the spot.
+    mask_dev, mask_ref = wid(host(h)) < 0, wid(ref["h"]) < 0
+    flipped = float(np.mean(mask_dev != mask_ref)) / max(1e-9, float(np.mean(~mask_ref)))
+    chain_tol = 3 * tol + np.sqrt(flipped)
+    assert flipped <= 2e-3, flipped                  # the disagreements stay rare
     for got, key in ((gw2, "dw2"), (gw1, "dw1"), (gx, "dx")):
-        assert rel(got, ref[key]) <= chain_tol, (key, rel(got, ref[key]))
+        assert rel(got, ref[key]) <= chain_tol, (key, rel(got, ref[key]), flipped)
     assert oracle.rel_fro(wid(host(gb2)), ref["db2"]) <= chain_tol
     assert oracle.rel_fro(wid(host(gb1)), ref["db1"]) <= chain_tol
 
