@@ -31,6 +31,7 @@
 
 #include <algorithm>
 #include <cstdlib>
+#include <cstring>
 #include <mutex>
 
 #include "internal.h"
@@ -1261,6 +1262,45 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
+// Encoded tensor maps of the calling thread's most recent operands.  cuTensorMapEncodeTiled costs about a
+// microsecond of host time per map and a GEMM needs three to five; a training or inference loop presents the same
+// pointers, shapes and strides again and again.  The map depends on nothing but these arguments.
+struct MapKey {
+    const void* ptr;
+    uint64_t dims[3], strides[2];
+    uint32_t box[3];
+    int32_t dt, swizzle;
+};
+CUresult encode_cached(CUtensorMap* out, CUtensorMapDataType dt, void* ptr, const cuuint64_t* dims, const cuuint64_t* strides,
+                       const cuuint32_t* box, CUtensorMapSwizzle swizzle) {
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return CUDA_ERROR_NOT_SUPPORTED;
+    constexpr int kEntries = 32;
+    struct Entry { MapKey key; CUtensorMap map; bool used; };
+    thread_local Entry cache[kEntries] = {};
+    thread_local int next = 0;
+    MapKey key;
+    std::memset(&key, 0, sizeof(key));
+    key.ptr = ptr;
+    for (int i = 0; i < 3; ++i) { key.dims[i] = dims[i]; key.box[i] = box[i]; }
+    key.strides[0] = strides[0]; key.strides[1] = strides[1];
+    key.dt = int32_t(dt); key.swizzle = int32_t(swizzle);
+    for (int i = 0; i < kEntries; ++i)
+        if (cache[i].used && std::memcmp(&cache[i].key, &key, sizeof(key)) == 0) {
+            *out = cache[i].map;
+            return CUDA_SUCCESS;
+        }
+    cuuint32_t elem_strides[3] = {1, 1, 1};
+    const CUresult r = enc(out, dt, 3, ptr, dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r == CUDA_SUCCESS) {
+        Entry& e = cache[next];
+        next = (next + 1) % kEntries;
+        e.key = key; e.map = *out; e.used = true;
+    }
+    return r;
+}
+
 struct OperandPlan {
     bool mn_major = false;
     int batch_mul = 1;
@@ -1306,12 +1346,8 @@ const char* plan_operand(const void* ptr, int es, CUtensorMapDataType dt, int64_
         box[1] = cuuint32_t(tile_mn);
     }
     box[2] = 1;
-    cuuint32_t elem_strides[3] = {1, 1, 1};
-    EncodeTiledFn enc = encode_fn();
-    if (!enc) return "cuTensorMapEncodeTiled is not available from the driver";
-    CUresult r = enc(&out->map, dt, 3, const_cast<void*>(ptr), dims, strides, box, elem_strides,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (!encode_fn()) return "cuTensorMapEncodeTiled is not available from the driver";
+    const CUresult r = encode_cached(&out->map, dt, const_cast<void*>(ptr), dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (r != CUDA_SUCCESS) return "cuTensorMapEncodeTiled rejected the operand";
     return nullptr;
 }
@@ -1401,9 +1437,7 @@ bool plan_store(void* c, CUtensorMapDataType dt, int es_bytes, int64_t m, int64_
     cuuint64_t strides[2] = {cuuint64_t(c_rs) * es, batch > 1 ? cuuint64_t(c_bs) * es : round16(cuuint64_t(c_rs) * es * cuuint64_t(m))};
     if (strides[0] >= (cuuint64_t(1) << 40) || strides[1] >= (cuuint64_t(1) << 40)) return false;
     cuuint32_t box[3] = {cuuint32_t(128 / es), 32, 1};   // 128 bytes of columns x 32 rows
-    cuuint32_t elem_strides[3] = {1, 1, 1};
-    return enc(out, dt, 3, c, dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    return encode_cached(out, dt, c, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B) == CUDA_SUCCESS;
 }
 
 template <MmaKind kKind, int BN, bool kSplit>
@@ -1418,9 +1452,17 @@ int launch_instance(const Maps& m, const UmmaParams& p_in, int grid, int a_rows_
     p.s_stage_tx = p.s_stage_bytes;
     p.s_stages = int(std::min<uint32_t>(uint32_t(T::kMaxStages), (T::kRingBudget - T::kABytes) / p.s_stage_bytes));
     const uint32_t smem = uint32_t(p.s_stages) * p.s_stage_bytes + T::kABytes + T::kBarrierBytes + 1024;
-    // the attribute is per device; setting it on every call is cheap
-    cudaError_t e = cudaFuncSetAttribute(umma_gemm_kernel<kKind, BN, kSplit>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-    if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(umma_gemm_kernel)");
+    // the attribute is per device and per instantiation: the largest size this instantiation can ask for, set once
+    static std::atomic<bool> attr_set[64];
+    int dev_i = 0;
+    (void)cudaGetDevice(&dev_i);
+    if (dev_i < 0 || dev_i >= 64) dev_i = 0;
+    if (!attr_set[dev_i].load(std::memory_order_acquire)) {
+        const uint32_t max_smem = T::kRingBudget + T::kBarrierBytes + 1024;
+        cudaError_t e = cudaFuncSetAttribute(umma_gemm_kernel<kKind, BN, kSplit>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(max_smem));
+        if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(umma_gemm_kernel)");
+        attr_set[dev_i].store(true, std::memory_order_release);
+    }
     umma_gemm_kernel<kKind, BN, kSplit><<<grid, kSplit ? kThreadsSplit : kThreads, smem, stream>>>(m.a.map, m.b.map, m.a_lo.map, m.b_lo.map, p);
     count_launch();
     NTB200_CUDA(cudaGetLastError());
