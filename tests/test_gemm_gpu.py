@@ -391,21 +391,22 @@ def test_few_rows_split_the_k_axis(api, oracle, L, m, n, k, weights_nk, bf16):
     dec = cd.dec
     # up to 128 rows the K slices run inside a thread-block cluster (one launch, partial tiles added through
     # distributed shared memory); more rows take the K slices as batches of the pair kernel plus a reduction kernel
-    split_route = ("umma_bf16" if bf16 else "umma_f16") + ("_clusterk" if m <= 128 else "_splitk")
+    base = "umma_bf16" if bf16 else "umma_f16"
+    split_routes = (base + "_clusterk",) if m <= 128 else (base + "_clusterk", base + "_splitk")   # more rows: by estimate
     got = api.linear(x, w, bias)
-    assert L.last_route() == split_route
+    assert L.last_route() in split_routes
     # K = 4096 / 8192: Float16 is beyond the depth at which fp32 accumulation stays within 2e-3 of the reference's
     # per-16-k rounding; both distances are measured and reported, the bar is on the fp32-accumulate value
     check_16bit(oracle, cd, dec(got), x32, w32, b32, what="K slices, bias")
     out = cd.enc(c32)
     api.matmult(x, w, out=out)                           # C += x . w
-    assert L.last_route() == split_route
+    assert L.last_route() in split_routes
     check_16bit(oracle, cd, dec(out), x32, w32, c32, what="K slices, C +=")
     # the left half of the columns on its own (a strided view, possibly too small to split) gives the same sums up to
     # the order of the fp32 additions
     half = api.matmult(x, w[:, : n // 2])
     both = api.matmult(x, w)
-    assert L.last_route() == split_route
+    assert L.last_route() in split_routes
     assert oracle.rel_fro(dec(both)[:, : n // 2], dec(half)) <= 1e-3
 
 
