@@ -1244,6 +1244,202 @@ umma_gemm_cluster_k_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
     }
 }
 
+// ---- K slices of CTA pairs inside one cluster ---------------------------------------------------------------------
+// A few hundred rows against a large weight matrix give fewer 256 x 256 tiles than the GPU has CTA pairs, and an SM
+// takes in operands from L2 at a fixed rate (about 64 bytes per clock), so the time of a tile is its K blocks times
+// that rate whatever else happens: the only way to finish sooner is more SMs on the same tile.  Here a cluster of
+// 2 S CTAs = S pairs computes ONE 256 x 256 tile, pair s on K slice s (tcgen05.mma.cta_group::2 exactly as in
+// umma_gemm_pair_kernel: even CTA rows 0-127, odd CTA rows 128-255, each staging its own halves of A and B).  Every
+// CTA then spills its 128 x 256 fp32 partial tile into its own shared memory (over the idle ring), and after a
+// cluster barrier the S CTAs that hold the same rows each add one S-th of the columns over all S slices, in slice
+// order, through distributed shared memory; bias and previous C are added, the sum is rounded once and stored.
+// One launch, no partial tile in HBM, reproducible sum order.  One tile per cluster (not persistent).
+template <int kDummy>
+__global__ void __launch_bounds__(kThreads, 1)
+umma_gemm_pair_cluster_k_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                                const ClusterKParams cp) {
+    constexpr int BN = 256;
+    constexpr int kStages = 6;
+    constexpr uint32_t kStageBytes = 2u * kPairOperandBytes;   // per CTA: its 128 rows of A, its 128 columns of B
+    const UmmaParams& p = cp.u;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    uint8_t* bar_gen = smem_gen + kStages * kStageBytes;
+    const uint32_t bar_base = smem_base + kStages * kStageBytes;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+    const uint32_t tfull_bar = bar_base + 8u * (2 * kStages);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_gen + 8 * (2 * kStages + 1));
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_cta_rank();
+    const uint32_t half = rank & 1u;              // 0: rows 0-127 of the tile (the pair's MMA leader), 1: rows 128-255
+    const int slice = int(rank >> 1);
+    const bool leader = half == 0;
+    const int tile = blockIdx.x / (2 * cp.slices);
+    const int mi = tile / p.tiles_n, ni = tile - mi * p.tiles_n;
+    const int m0 = mi * 256 + int(half) * 128, n0_pair = ni * BN;
+    const int kb_begin = slice * cp.blocks_per_slice;
+    const int kb_end = min(p.k_blocks, kb_begin + cp.blocks_per_slice);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        mbar_init(tfull_bar, 1);
+        *abort_flag = 0;
+        fence_barrier_init();
+        fence_proxy_async_smem();
+        tma_prefetch_desc(&tma_a);
+        tma_prefetch_desc(&tma_b);
+    }
+    if (warp == 1) {
+        tmem_alloc<2>(smem_u32(const_cast<uint32_t*>(tmem_slot)), BN);
+        tmem_relinquish<2>();
+    }
+    tcgen05_fence_before();
+    cluster_sync_all();  // barriers of every CTA are initialised before anything signals them remotely
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer (every CTA, its own halves)
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            const int n0 = n0_pair + int(half) * 128;
+            for (int kb = kb_begin; kb < kb_end; ++kb) {
+                if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
+                    raise_timeout(abort_flag, 0x31);
+                    ok = false;
+                    break;
+                }
+                const uint32_t a_dst = smem_base + stage * kStageBytes;
+                const uint32_t b_dst = a_dst + kPairOperandBytes;
+                const uint32_t bar = full_bar(stage);
+                if (leader) mbar_expect_tx(bar, 2 * kStageBytes);   // both CTAs' loads credit the even CTA's barrier
+                const int k0 = kb * p.block_k;
+                if (!p.a_mn_major) {
+                    tma_load_3d_pair(a_dst, &tma_a, bar, k0, m0, 0);
+                } else {
+                    for (int c = 0; c < p.a_chunks; ++c) tma_load_3d_pair(a_dst + c * p.chunk_bytes, &tma_a, bar, m0 + c * p.chunk_mn, k0, 0);
+                }
+                if (!p.b_mn_major) {
+                    tma_load_3d_pair(b_dst, &tma_b, bar, k0, n0, 0);
+                } else {
+                    for (int c = 0; c < p.b_chunks; ++c) tma_load_3d_pair(b_dst + c * p.chunk_bytes, &tma_b, bar, n0 + c * p.chunk_mn, k0, 0);
+                }
+                if (++stage == kStages) { stage = 0; phase ^= 1u; }
+            }
+            if (ok) {
+                for (int s = 0; s < kStages; ++s) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { raise_timeout(abort_flag, 0x32); break; }
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer (even CTA of each pair)
+        if (leader && lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            const uint16_t pair_mask = uint16_t(3u << (rank & ~1u));   // the two CTAs of this pair, by rank in the cluster
+            for (int kb = kb_begin; kb < kb_end; ++kb) {
+                if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
+                    raise_timeout(abort_flag, 0x34);
+                    ok = false;
+                    break;
+                }
+                tcgen05_fence_after();
+                const uint32_t a_addr = smem_base + stage * kStageBytes;
+                const uint64_t a_desc = make_smem_desc_sw128(a_addr, p.a_lbo, 1024);
+                const uint64_t b_desc = make_smem_desc_sw128(a_addr + kPairOperandBytes, p.b_lbo, 1024);
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    umma<MmaKind::f16, 2>(tmem_base, a_desc + uint64_t(k * p.a_kstep), b_desc + uint64_t(k * p.b_kstep), p.idesc,
+                                          ((kb - kb_begin) | k) != 0);
+                umma_commit_pair(empty_bar(stage), pair_mask);
+                if (++stage == kStages) { stage = 0; phase ^= 1u; }
+            }
+            if (ok) umma_commit_pair(tfull_bar, pair_mask);
+        }
+    } else {
+        // ------------------------------------------------------------------ spill this CTA's 128 x 256 partial tile
+        const int quad = warp & 3;
+        bool ok = mbar_wait(tfull_bar, 0, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+            if (lane == 0) raise_timeout(abort_flag, 0x35);
+        } else {
+            tcgen05_fence_after();
+            float* dst = reinterpret_cast<float*>(smem_gen) + (quad * 32 + lane) * cp.pitch;
+#pragma unroll 1
+            for (int cc = 0; cc < BN / 32; ++cc) {
+                uint32_t v[32];
+                tmem_ld_32x32b_x32(tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(cc * 32), v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int q = 0; q < 8; ++q)
+                    *reinterpret_cast<float4*>(dst + cc * 32 + 4 * q) =
+                        make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]), __uint_as_float(v[4 * q + 2]), __uint_as_float(v[4 * q + 3]));
+            }
+            tcgen05_fence_before();
+        }
+    }
+
+    // ---------------------------------------------------------------------- reduce across the slices
+    __syncwarp();
+    cluster_sync_all();
+    if (*abort_flag == 0) {
+        // the S CTAs with this row half share the tile's 256 columns: this one takes columns [slice, slice + 1) * 256 / S
+        const int cols_mine = BN / cp.slices;
+        const int groups = cols_mine >> 2;
+        const int rows = max(0, min(128, p.m - m0));
+        for (int i = threadIdx.x; i < rows * groups; i += kThreads) {
+            const int row = i / groups, gcol = (i - row * groups) * 4 + slice * cols_mine;
+            const int col = n0_pair + gcol;
+            if (col >= p.n) continue;
+            const uint32_t addr = smem_base + uint32_t(row * cp.pitch + gcol) * 4u;
+            float4 acc = ld_cluster_f4(addr, half);                         // slice 0 of this row half
+            for (int s = 1; s < cp.slices; ++s) {
+                const float4 v = ld_cluster_f4(addr, uint32_t(2 * s) + half);
+                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            }
+            float f[4] = {acc.x, acc.y, acc.z, acc.w};
+            const int grow = m0 + row;
+            uint16_t* dst = static_cast<uint16_t*>(p.c) + (long long)grow * p.c_rs + col;
+            const uint16_t* bias = static_cast<const uint16_t*>(p.bias);
+            uint32_t r[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (col + j < p.n) {
+                    if (bias) f[j] += to_float_bits16(bias[(long long)grow * p.bias_rs + (long long)(col + j) * p.bias_cs], p.out_kind);
+                    if (p.accumulate) f[j] += to_float_bits16(dst[j], p.out_kind);
+                }
+                r[j] = from_float_bits16(f[j], p.out_kind);
+            }
+            if (cp.c_wide_ok && col + 4 <= p.n) {
+                *reinterpret_cast<uint2*>(dst) = make_uint2(r[0] | (r[1] << 16), r[2] | (r[3] << 16));
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (col + j < p.n) dst[j] = uint16_t(r[j]);
+            }
+        }
+    }
+    tcgen05_fence_before();
+    cluster_sync_all();   // nobody leaves while a neighbour may still read its shared memory or signal its barriers
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tmem_dealloc<2>(tmem_base, BN);
+    }
+}
+
 // ---- host side ---------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -1488,6 +1684,27 @@ int resident_pairs_query(const void* kernel, uint32_t smem_bytes) {
         n = sm_count() / 2;
     }
     return std::min(n, sm_count() / 2);
+}
+
+// How many clusters of `cluster_size` CTAs of `kernel` the current device can hold at once (cached per call site).
+int active_clusters_query(const void* kernel, uint32_t smem_bytes, int cluster_size, int threads) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(unsigned(cluster_size * 64), 1, 1);
+    cfg.blockDim = dim3(unsigned(threads), 1, 1);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = unsigned(cluster_size);
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n <= 0) {
+        (void)cudaGetLastError();
+        return 0;
+    }
+    return n;
 }
 
 template <MmaKind kKind, bool kSplit, int kEpi = 4>
@@ -2052,6 +2269,28 @@ struct ClusterKPlan {
     bool valid;
 };
 
+int cluster_k_capacity(int bn, int slices) {
+    static std::atomic<int> cached[64][2][9];
+    int dev = 0;
+    (void)cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || slices < 1 || slices > 8) return 0;
+    const int bi = bn == 256 ? 1 : 0;
+    int v = cached[dev][bi][slices].load(std::memory_order_relaxed);
+    if (v == 0) {
+        using T256 = Tile<256, false>;
+        const uint32_t smem = T256::kRingBudget + T256::kBarrierBytes + 1024;   // the largest the kernel asks for
+        const void* kernel = bn == 256 ? reinterpret_cast<const void*>(umma_gemm_cluster_k_kernel<256>)
+                                       : reinterpret_cast<const void*>(umma_gemm_cluster_k_kernel<128>);
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return 0;
+        }
+        v = active_clusters_query(kernel, smem, slices, kThreads);
+        cached[dev][bi][slices].store(v > 0 ? v : -1, std::memory_order_relaxed);
+    }
+    return v > 0 ? v : 0;
+}
+
 ClusterKPlan plan_cluster_k(const GemmArgs& g, int es) {
     ClusterKPlan best{0, 0, 1e30, false};
     if (g_no_cluster_k || g.no_alloc || g.batch != 1 || g.relu_out || g.mask_src || g.n_peers > 0) return best;
@@ -2072,6 +2311,8 @@ ClusterKPlan plan_cluster_k(const GemmArgs& g, int es) {
             if ((sl - 1) * bps >= k_blocks) continue;         // an empty last slice
             const int64_t ctas = tiles * sl;
             if (ctas > sms || ctas * 2 < sms) continue;       // one wave, and not a mostly idle GPU
+            const int cap = cluster_k_capacity(bn, sl);       // clusters of this size the GPU holds at once (GPC boundaries)
+            if (cap > 0 && tiles > cap) continue;
             const double us = 8.0 + std::max(double(bps) * us_per_k_block, dram_us) + 1.5;
             if (us < best.us * 0.97) best = ClusterKPlan{bn, sl, us, true};
         }
@@ -2127,6 +2368,110 @@ int launch_f16_cluster_k(const GemmArgs& g, const Planned& pl16, const ClusterKP
     return rc;
 }
 
+
+constexpr uint32_t kPairClusterSmem = 6u * 2u * kPairOperandBytes + 512u + 1024u;
+
+// Clusters of S pairs that fit the device at once, S = 2 / 4 (cluster of 4 / 8 CTAs); 0 = unknown or none.
+int pair_cluster_capacity(int slices) {
+    static std::atomic<int> cached[64][5];
+    int dev = 0;
+    (void)cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || slices < 1 || slices > 4) return 0;
+    int v = cached[dev][slices].load(std::memory_order_relaxed);
+    if (v == 0) {
+        auto kernel = umma_gemm_pair_cluster_k_kernel<0>;
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kPairClusterSmem)) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return 0;
+        }
+        v = active_clusters_query(reinterpret_cast<const void*>(kernel), kPairClusterSmem, 2 * slices, kThreads);
+        cached[dev][slices].store(v > 0 ? v : -1, std::memory_order_relaxed);
+    }
+    return v > 0 ? v : 0;
+}
+
+struct PairClusterPlan {
+    int slices;
+    double us;
+    bool valid;
+};
+
+// More than 128 rows of 16-bit floats, fewer 256 x 256 tiles than half the pairs: S pairs per tile.
+PairClusterPlan plan_pair_cluster_k(const GemmArgs& g, int es) {
+    PairClusterPlan best{0, 1e30, false};
+    static const bool disabled = [] { const char* e = getenv("NTB200_NO_PAIR_CLUSTER_K"); return e && e[0] == '1'; }();
+    if (disabled || g_disable_pair || es != 2 || g.no_alloc || g.batch != 1 || g.relu_out || g.mask_src || g.n_peers > 0) return best;
+    if (g.m <= kBM || g.n <= 128) return best;
+    const int block_k = 128 / es;
+    const int k_blocks = int((g.k + block_k - 1) / block_k);
+    const int64_t tiles = ((g.m + 255) / 256) * ((g.n + 255) / 256);
+    const double dram_us = (double(g.m) * g.k + double(g.k) * g.n + double(g.m) * g.n) * es / 4.5e6;
+    for (int sl : {4, 2}) {
+        if (k_blocks / sl < 4) continue;
+        const int bps = (k_blocks + sl - 1) / sl;
+        if ((sl - 1) * bps >= k_blocks) continue;
+        const int cap = pair_cluster_capacity(sl);
+        if (cap <= 0 || tiles > cap) continue;                 // one wave only: the point is to finish a tile sooner
+        const double us = 7.0 + std::max(double(bps) * 0.29, dram_us) + 2.0;
+        if (us < best.us * 0.97) best = PairClusterPlan{sl, us, true};
+    }
+    return best;
+}
+
+int launch_f16_pair_cluster_k(const GemmArgs& g, const Planned& pl16, const PairClusterPlan& plan, cudaStream_t stream) {
+    if (!plan.valid) return NTB200_ERR_UNSUPPORTED;
+    const int es = pl16.es, block_k = 128 / es;
+    Maps maps;
+    if (plan_operand(g.a, es, pl16.dt, g.m, g.k, g.a_rs, g.a_cs, 1, 0, kBM, block_k, &maps.a)) return NTB200_ERR_UNSUPPORTED;
+    if (plan_operand(g.b, es, pl16.dt, g.n, g.k, g.b_cs, g.b_rs, 1, 0, 128, block_k, &maps.b)) return NTB200_ERR_UNSUPPORTED;
+    ClusterKParams cp{};
+    UmmaParams& p = cp.u;
+    p.m = int(g.m); p.n = int(g.n); p.k = int(g.k); p.batch = 1;
+    p.tiles_m = int((g.m + 255) / 256); p.tiles_n = int((g.n + 255) / 256);
+    p.k_blocks = int((g.k + block_k - 1) / block_k); p.chunk_blocks = p.k_blocks; p.group_m = 8;
+    p.total_tiles = p.tiles_m * p.tiles_n;
+    p.block_k = block_k;
+    p.idesc = make_instr_desc(pl16.d_fmt, pl16.in_fmt, pl16.in_fmt, maps.a.mn_major, maps.b.mn_major, 256u, 256u);
+    p.a_mn_major = maps.a.mn_major; p.b_mn_major = maps.b.mn_major;
+    p.chunk_mn = 128 / es;
+    p.chunk_bytes = uint32_t(block_k) * 128u;
+    p.a_chunks = kBM / p.chunk_mn;
+    p.b_chunks = 128 / p.chunk_mn;
+    p.a_lbo = maps.a.mn_major ? p.chunk_bytes : 16u;
+    p.b_lbo = maps.b.mn_major ? p.chunk_bytes : 16u;
+    const uint32_t mn_kstep = uint32_t(32 / es) * 128u / 16u;
+    p.a_kstep = maps.a.mn_major ? mn_kstep : 2u;
+    p.b_kstep = maps.b.mn_major ? mn_kstep : 2u;
+    p.c = g.c; p.c_rs = g.c_rs; p.c_bs = g.c_bs;
+    p.bias = g.bias; p.bias_rs = g.bias_rs; p.bias_cs = g.bias_cs; p.bias_bs = g.bias_bs;
+    p.accumulate = g.accumulate;
+    p.out_kind = pl16.out_kind;
+    cp.slices = plan.slices;
+    cp.blocks_per_slice = (p.k_blocks + plan.slices - 1) / plan.slices;
+    cp.pitch = 256 + 4;
+    cp.rows_live = 128;
+    cp.c_wide_ok = (reinterpret_cast<uintptr_t>(g.c) % 8 == 0 && g.c_rs % 4 == 0) ? 1 : 0;
+    if (uint32_t(128 * cp.pitch * 4) > 6u * 2u * kPairOperandBytes) return NTB200_ERR_UNSUPPORTED;   // the partial tile lives in the ring
+    auto kernel = umma_gemm_pair_cluster_k_kernel<0>;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(unsigned(p.total_tiles * 2 * plan.slices), 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = kPairClusterSmem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = unsigned(2 * plan.slices);
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, maps.a.map, maps.b.map, cp);
+    if (e != cudaSuccess) return cuda_fail(e, "umma_gemm_pair_cluster_k_kernel launch");
+    count_launch();
+    note_route(g.dtype == NTB200_F16 ? "umma_f16_pairclusterk" : "umma_bf16_pairclusterk");
+    return NTB200_OK;
+}
+
 }  // namespace
 
 bool umma_supported(const GemmArgs& g, const char** why) {
@@ -2171,10 +2516,20 @@ int launch_umma_gemm(const GemmArgs& g, cudaStream_t stream) {
         if (!tune_int("NTB200_FORCE_SPLITS")) {
             // K slices inside a cluster (one launch): always for few rows; for more rows when its estimate beats the
             // planner's best tile kind / slice count by a margin
-            const ClusterKPlan ck = plan_cluster_k(g, es);
-            if (ck.valid && (g.m <= kBM || !plan.valid || ck.us < plan.us * 0.95)) {
-                const int rc = launch_f16_cluster_k(g, pl, ck, stream);
-                if (rc != NTB200_ERR_UNSUPPORTED) return rc;
+            // K slices inside a cluster (one launch): single-CTA tiles for few rows; S CTA pairs per 256 x 256 tile for
+            // more rows, when that beats the planner's best tile kind / slice count
+            if (g.m <= kBM) {
+                const ClusterKPlan ck = plan_cluster_k(g, es);
+                if (ck.valid) {
+                    const int rc = launch_f16_cluster_k(g, pl, ck, stream);
+                    if (rc != NTB200_ERR_UNSUPPORTED) return rc;
+                }
+            } else {
+                const PairClusterPlan pk = plan_pair_cluster_k(g, es);
+                if (pk.valid && (!plan.valid || pk.us < plan.us)) {
+                    const int rc = launch_f16_pair_cluster_k(g, pl, pk, stream);
+                    if (rc != NTB200_ERR_UNSUPPORTED) return rc;
+                }
             }
         }
         if (splits > 1) return launch_f16_split_k(g, pl, splits, choice, stream);

@@ -392,7 +392,9 @@ def test_few_rows_split_the_k_axis(api, oracle, L, m, n, k, weights_nk, bf16):
     # up to 128 rows the K slices run inside a thread-block cluster (one launch, partial tiles added through
     # distributed shared memory); more rows take the K slices as batches of the pair kernel plus a reduction kernel
     base = "umma_bf16" if bf16 else "umma_f16"
-    split_routes = (base + "_clusterk",) if m <= 128 else (base + "_clusterk", base + "_splitk")   # more rows: by estimate
+    # up to 128 rows: S CTAs of a cluster per 128-row tile; more rows: S CTA pairs of a cluster per 256 x 256 tile, or
+    # (when the clusters would not fit in one wave) K slices as batches of the pair kernel plus a reduction kernel
+    split_routes = (base + "_clusterk",) if m <= 128 else (base + "_pairclusterk", base + "_splitk")
     got = api.linear(x, w, bias)
     assert L.last_route() in split_routes
     # K = 4096 / 8192: Float16 is beyond the depth at which fp32 accumulation stays within 2e-3 of the reference's
