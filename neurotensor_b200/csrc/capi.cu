@@ -209,8 +209,10 @@ int run_gemm(GemmArgs g, int route, cudaStream_t stream) {
         if (route == NTB200_ROUTE_TENSOR) return fail(NTB200_ERR_UNSUPPORTED, "matmult: the tcgen05 route of %s needs scratch memory", dtype_name(g.dtype));
         route = NTB200_ROUTE_SIMT;
     }
-    // a handful of rows against a large 16-bit weight matrix is bound by reading the weights once: stream them
-    if (route == NTB200_ROUTE_AUTO && !g.no_alloc && gemv_supported(g)) return launch_gemv(g, stream);
+    // one or two rows against a large 16-bit weight matrix are bound by reading the weights once: the tensor-core
+    // kernel that slices K over a cluster does that in one launch; shapes it does not take stream the weights on
+    // CUDA cores
+    if (route == NTB200_ROUTE_AUTO && !g.no_alloc && gemv_supported(g) && !umma_cluster_k_would_run(g)) return launch_gemv(g, stream);
     if (route != NTB200_ROUTE_SIMT) {
         const char* why = nullptr;
         if (umma_supported(g, &why)) {

@@ -793,7 +793,7 @@ struct PairTile {
 // kEpi = 8 (16- and 8-bit outputs through TMA stores, no second output): two epilogue warps per lane quadrant, each
 // taking 128 of the tile's 256 columns, for shallow K where the epilogue, not the main loop, bounds a tile.
 template <MmaKind kKind, bool kSplit, int kEpi = 4>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__((kSplit || kEpi == 8) ? kThreadsSplit : kThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kSplit ? kThreadsSplit : 64 + 32 * kEpi, 1)
 umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                       const __grid_constant__ CUtensorMap tma_a_lo, const __grid_constant__ CUtensorMap tma_b_lo,
                       const __grid_constant__ CUtensorMap tma_c, const __grid_constant__ CUtensorMap tma_relu,
@@ -827,7 +827,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(tfull_bar(a), 1);
-            mbar_init(tempty_bar(a), (kSplit || kEpi == 8) ? 16 : 8);   // one arrival per epilogue warp of both CTAs
+            mbar_init(tempty_bar(a), kSplit ? 16 : 2 * kEpi);   // one arrival per epilogue warp of both CTAs
         }
         *abort_flag = 0;
         fence_barrier_init();
@@ -993,7 +993,17 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
                 break;
             }
             tcgen05_fence_after();
-            if constexpr (!kSplit && kEpi == 8) {
+            if constexpr (!kSplit && kEpi == 16) {
+                const int quarter = (warp - 2) >> 2;   // four warps per lane quadrant, 64 columns (one 128-byte sub-tile) each
+                if (p.tma_store)
+                    epilogue_tile_tma<64>(p, &tma_c, &tma_relu, &tma_peers,
+                                          tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN + quarter * 64),
+                                          staging_base + uint32_t(warp - 2) * 4096u, b, mi * 256 + int(rank) * 128 + quad * 32,
+                                          lane, ni * BN + quarter * 64);
+                else
+                    epilogue_tile<64>(p, tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN + quarter * 64), b,
+                                      mi * 256 + row_in_tile, ni * BN + quarter * 64);
+            } else if constexpr (!kSplit && kEpi == 8) {
                 const int half = (warp - 2) >> 2;   // warps 2-5: columns 0-127, warps 6-9: columns 128-255
                 if (p.tma_store)
                     epilogue_tile_tma<128>(p, &tma_c, &tma_relu, &tma_peers,
@@ -1060,6 +1070,63 @@ __device__ __forceinline__ float4 ld_cluster_f4(uint32_t local_addr, uint32_t ct
         "ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [remote];\n\t}"
         : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(local_addr), "r"(cta_rank) : "memory");
     return v;
+}
+
+
+// Sum of the S partial tiles of a cluster for this CTA's share of the columns, then bias, previous C, one rounding and
+// the store.  The partial tiles sit at the same shared-memory offset (`tile_base`, row pitch cp.pitch floats) in the S
+// CTAs with ranks rank_first, rank_first + rank_stride, ...; they are added in that order.  A read of a neighbour's
+// shared memory takes several hundred cycles, so every thread first issues the reads of U items x S slices and only
+// then starts adding: the latency is paid once per batch, not once per read.
+template <int S, int U>
+__device__ __forceinline__ void cluster_reduce_store(const UmmaParams& p, const ClusterKParams& cp, uint32_t tile_base, int rows,
+                                                     int m_base, int n_base, int col_first, int cols_mine, uint32_t rank_first,
+                                                     uint32_t rank_stride) {
+    const int groups = cols_mine >> 2;
+    const int items = rows * groups;
+    for (int base = threadIdx.x; base < items; base += kThreads * U) {
+        float4 v[U][S];
+        int row[U], gcol[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int i = base + u * kThreads;
+            const bool live = i < items;
+            row[u] = live ? i / groups : 0;
+            gcol[u] = live ? (i - row[u] * groups) * 4 + col_first : col_first;
+            const uint32_t addr = tile_base + uint32_t(row[u] * cp.pitch + gcol[u]) * 4u;
+#pragma unroll
+            for (int sl = 0; sl < S; ++sl) v[u][sl] = ld_cluster_f4(addr, rank_first + uint32_t(sl) * rank_stride);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int i = base + u * kThreads;
+            const int col = n_base + gcol[u];
+            if (i >= items || col >= p.n) continue;
+            float4 acc = v[u][0];
+#pragma unroll
+            for (int sl = 1; sl < S; ++sl) { acc.x += v[u][sl].x; acc.y += v[u][sl].y; acc.z += v[u][sl].z; acc.w += v[u][sl].w; }
+            float f[4] = {acc.x, acc.y, acc.z, acc.w};
+            const int grow = m_base + row[u];
+            uint16_t* dst = static_cast<uint16_t*>(p.c) + (long long)grow * p.c_rs + col;
+            const uint16_t* bias = static_cast<const uint16_t*>(p.bias);
+            uint32_t r[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (col + j < p.n) {
+                    if (bias) f[j] += to_float_bits16(bias[(long long)grow * p.bias_rs + (long long)(col + j) * p.bias_cs], p.out_kind);
+                    if (p.accumulate) f[j] += to_float_bits16(dst[j], p.out_kind);
+                }
+                r[j] = from_float_bits16(f[j], p.out_kind);
+            }
+            if (cp.c_wide_ok && col + 4 <= p.n) {
+                *reinterpret_cast<uint2*>(dst) = make_uint2(r[0] | (r[1] << 16), r[2] | (r[3] << 16));
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (col + j < p.n) dst[j] = uint16_t(r[j]);
+            }
+        }
+    }
 }
 
 template <int BN>
@@ -1200,39 +1267,12 @@ umma_gemm_cluster_k_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
     cluster_sync_all();   // every CTA's partial tile is in its shared memory (or its abort flag is up)
     if (*abort_flag == 0) {
         const int cols_mine = BN / cp.slices;               // a multiple of 4 (BN 128 / 256, S <= 8)
-        const int groups = cols_mine >> 2;
         const int rows = min(kBM, p.m - m0);
-        const uint32_t tile_base = smem_base;
-        for (int i = threadIdx.x; i < rows * groups; i += kThreads) {
-            const int row = i / groups, gcol = (i - row * groups) * 4 + int(rank) * cols_mine;
-            const int col = n0 + gcol;
-            if (col >= p.n) continue;
-            const uint32_t addr = tile_base + uint32_t(row * cp.pitch + gcol) * 4u;
-            float4 acc = ld_cluster_f4(addr, 0);
-            for (int s = 1; s < cp.slices; ++s) {
-                const float4 v = ld_cluster_f4(addr, uint32_t(s));
-                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-            }
-            float f[4] = {acc.x, acc.y, acc.z, acc.w};
-            const int grow = m0 + row;
-            uint16_t* dst = static_cast<uint16_t*>(p.c) + (long long)grow * p.c_rs + col;
-            const uint16_t* bias = static_cast<const uint16_t*>(p.bias);
-            uint32_t r[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                if (col + j < p.n) {
-                    if (bias) f[j] += to_float_bits16(bias[(long long)grow * p.bias_rs + (long long)(col + j) * p.bias_cs], p.out_kind);
-                    if (p.accumulate) f[j] += to_float_bits16(dst[j], p.out_kind);
-                }
-                r[j] = from_float_bits16(f[j], p.out_kind);
-            }
-            if (cp.c_wide_ok && col + 4 <= p.n) {
-                *reinterpret_cast<uint2*>(dst) = make_uint2(r[0] | (r[1] << 16), r[2] | (r[3] << 16));
-            } else {
-#pragma unroll
-                for (int j = 0; j < 4; ++j)
-                    if (col + j < p.n) dst[j] = uint16_t(r[j]);
-            }
+        const int col_first = int(rank) * cols_mine;
+        switch (cp.slices) {
+            case 2: cluster_reduce_store<2, 4>(p, cp, smem_base, rows, m0, n0, col_first, cols_mine, 0u, 1u); break;
+            case 4: cluster_reduce_store<4, 4>(p, cp, smem_base, rows, m0, n0, col_first, cols_mine, 0u, 1u); break;
+            default: cluster_reduce_store<8, 2>(p, cp, smem_base, rows, m0, n0, col_first, cols_mine, 0u, 1u); break;
         }
     }
     // nobody leaves while a neighbour may still read its shared memory
@@ -1398,39 +1438,9 @@ umma_gemm_pair_cluster_k_kernel(const __grid_constant__ CUtensorMap tma_a, const
     if (*abort_flag == 0) {
         // the S CTAs with this row half share the tile's 256 columns: this one takes columns [slice, slice + 1) * 256 / S
         const int cols_mine = BN / cp.slices;
-        const int groups = cols_mine >> 2;
         const int rows = max(0, min(128, p.m - m0));
-        for (int i = threadIdx.x; i < rows * groups; i += kThreads) {
-            const int row = i / groups, gcol = (i - row * groups) * 4 + slice * cols_mine;
-            const int col = n0_pair + gcol;
-            if (col >= p.n) continue;
-            const uint32_t addr = smem_base + uint32_t(row * cp.pitch + gcol) * 4u;
-            float4 acc = ld_cluster_f4(addr, half);                         // slice 0 of this row half
-            for (int s = 1; s < cp.slices; ++s) {
-                const float4 v = ld_cluster_f4(addr, uint32_t(2 * s) + half);
-                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-            }
-            float f[4] = {acc.x, acc.y, acc.z, acc.w};
-            const int grow = m0 + row;
-            uint16_t* dst = static_cast<uint16_t*>(p.c) + (long long)grow * p.c_rs + col;
-            const uint16_t* bias = static_cast<const uint16_t*>(p.bias);
-            uint32_t r[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                if (col + j < p.n) {
-                    if (bias) f[j] += to_float_bits16(bias[(long long)grow * p.bias_rs + (long long)(col + j) * p.bias_cs], p.out_kind);
-                    if (p.accumulate) f[j] += to_float_bits16(dst[j], p.out_kind);
-                }
-                r[j] = from_float_bits16(f[j], p.out_kind);
-            }
-            if (cp.c_wide_ok && col + 4 <= p.n) {
-                *reinterpret_cast<uint2*>(dst) = make_uint2(r[0] | (r[1] << 16), r[2] | (r[3] << 16));
-            } else {
-#pragma unroll
-                for (int j = 0; j < 4; ++j)
-                    if (col + j < p.n) dst[j] = uint16_t(r[j]);
-            }
-        }
+        if (cp.slices == 2) cluster_reduce_store<2, 4>(p, cp, smem_base, rows, m0, n0_pair, slice * cols_mine, cols_mine, half, 2u);
+        else cluster_reduce_store<4, 4>(p, cp, smem_base, rows, m0, n0_pair, slice * cols_mine, cols_mine, half, 2u);
     }
     tcgen05_fence_before();
     cluster_sync_all();   // nobody leaves while a neighbour may still read its shared memory or signal its barriers
@@ -1709,10 +1719,15 @@ int active_clusters_query(const void* kernel, uint32_t smem_bytes, int cluster_s
 
 template <MmaKind kKind, bool kSplit, int kEpi = 4>
 int launch_pair_instance(const Maps& m, const UmmaParams& p, cudaStream_t stream) {
-    // Shallow K, plain TMA-store epilogue: the instantiation with eight epilogue warps
+    // Shallow K, plain TMA-store epilogue: the instantiations with eight or sixteen epilogue warps (the epilogue, not
+    // the main loop, bounds a tile, and its throughput grows with the warps that run it)
     if constexpr (!kSplit && kEpi == 4) {
-        if (p.tma_store && !p.has_relu_out && p.k_blocks <= 6 && !g_four_epilogue_warps)
+        if (p.tma_store && !p.has_relu_out && p.k_blocks <= 6 && !g_four_epilogue_warps) {
+            static const int forced = [] { const char* e = getenv("NTB200_EPILOGUE_WARPS"); return e ? atoi(e) : 0; }();
+            const int warps = forced == 8 || forced == 16 ? forced : (p.k_blocks <= 2 ? 16 : 8);   // measured: 16 warps win up to two K blocks
+            if (warps == 16) return launch_pair_instance<kKind, kSplit, 16>(m, p, stream);
             return launch_pair_instance<kKind, kSplit, 8>(m, p, stream);
+        }
     }
     constexpr uint32_t smem = PairTile<kSplit>::kSmemBytes;
     cudaError_t e = cudaFuncSetAttribute(umma_gemm_pair_kernel<kKind, kSplit, kEpi>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
@@ -1724,7 +1739,7 @@ int launch_pair_instance(const Maps& m, const UmmaParams& p, cudaStream_t stream
     if (cached[dev] == 0)
         cached[dev] = resident_pairs_query(reinterpret_cast<const void*>(umma_gemm_pair_kernel<kKind, kSplit, kEpi>), smem);
     const int pairs = std::min(p.total_tiles, cached[dev]);
-    umma_gemm_pair_kernel<kKind, kSplit, kEpi><<<2 * pairs, (kSplit || kEpi == 8) ? kThreadsSplit : kThreads, smem, stream>>>(m.a.map, m.b.map, m.a_lo.map, m.b_lo.map, m.c, m.relu, m.peers, p);
+    umma_gemm_pair_kernel<kKind, kSplit, kEpi><<<2 * pairs, kSplit ? kThreadsSplit : 64 + 32 * kEpi, smem, stream>>>(m.a.map, m.b.map, m.a_lo.map, m.b_lo.map, m.c, m.relu, m.peers, p);
     count_launch();
     NTB200_CUDA(cudaGetLastError());
     return NTB200_OK;
@@ -2473,6 +2488,12 @@ int launch_f16_pair_cluster_k(const GemmArgs& g, const Planned& pl16, const Pair
 }
 
 }  // namespace
+
+bool umma_cluster_k_would_run(const GemmArgs& g) {
+    if (g.dtype != NTB200_F16 && g.dtype != NTB200_BF16) return false;
+    if (g.m > kBM || operands_stageable(g) != nullptr) return false;
+    return plan_cluster_k(g, 2).valid;
+}
 
 bool umma_supported(const GemmArgs& g, const char** why) {
     const char* w = operands_stageable(g);

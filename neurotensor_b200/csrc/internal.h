@@ -60,6 +60,9 @@ struct GemmArgs {
 // cannot be expressed as TMA tensor maps, so the caller can route elsewhere.
 bool umma_supported(const GemmArgs& g, const char** why);
 int launch_umma_gemm(const GemmArgs& g, cudaStream_t stream);
+// Few rows of 16-bit floats against a large weight matrix: would the automatic route slice K over a thread-block
+// cluster (one launch, weights read once at close to the HBM rate)?
+bool umma_cluster_k_would_run(const GemmArgs& g);
 int read_device_status(cudaStream_t stream);
 int launch_wait_timeout_selftest(unsigned long long limit_ns, cudaStream_t stream);
 

@@ -107,7 +107,7 @@ def test_f16_tensor_core_route(api, oracle, L, ta, tb, m, k, n):
     rng = np.random.default_rng(7 + m + k + n)
     a, b = operands(rng, m, k, n, ta, tb, np.float16, 0.5)
     got = host(api.matmult(dev(a), dev(b), ta, tb, route=L.ROUTE_TENSOR))
-    assert L.last_route() == "umma_f16"
+    assert L.last_route().startswith("umma_f16")      # one-pass kernel, or K slices inside a cluster for deep, small problems
     exp = oracle.matmult(a, b, ta, tb)
     wide = (a.T if ta else a).astype(np.float32) @ (b.T if tb else b).astype(np.float32)
     assert oracle.rel_fro(got, wide) <= 5e-4, "vs fp32-accumulate"
@@ -131,7 +131,7 @@ def test_bf16_tensor_core_route(api, oracle, L, ta, tb, m, k, n):
     a32, b32 = operands(rng, m, k, n, ta, tb, np.float32)
     a, b = oracle.bf16_round(a32), oracle.bf16_round(b32)
     got = host(api.matmult(dev(a, True), dev(b, True), ta, tb, route=L.ROUTE_TENSOR))
-    assert L.last_route() == "umma_bf16"
+    assert L.last_route().startswith("umma_bf16")
     exp = oracle.matmult(a, b, ta, tb, bf16=True)
     assert oracle.rel_fro(oracle.bf16_widen(got), oracle.bf16_widen(exp)) <= F16_TOL
 
@@ -370,9 +370,9 @@ def test_few_rows_stream_the_weights(api, oracle, L, m, weights_nk, bf16):
     check_16bit(oracle, cd, cd.dec(out), x32, w32, c32, what="weight streaming, C +=")
     # an explicit route request is honoured, and three rows are the tensor cores' again
     api.matmult(x, w, route=L.ROUTE_TENSOR)
-    assert L.last_route() in ("umma_f16", "umma_bf16")
+    assert L.last_route().startswith(("umma_f16", "umma_bf16"))
     api.matmult(x[:1].repeat(3, 1), w)
-    assert L.last_route() in ("umma_f16", "umma_bf16")
+    assert L.last_route().startswith(("umma_f16", "umma_bf16"))
 
 
 @pytest.mark.gpu
@@ -552,7 +552,7 @@ def test_shallow_k_takes_the_wide_epilogue(api, oracle, L, kind, m, n, k):
     bias32, c32 = normal(rng, (n,), np.float32), normal(rng, (m, n), np.float32)
     cd = Codec(oracle, bf16)
     got = api.linear(cd.enc(a32), cd.enc(b32), cd.enc(bias32))
-    assert L.last_route() in ("umma_f16", "umma_bf16")
+    assert L.last_route().startswith(("umma_f16", "umma_bf16"))
     check_16bit(oracle, cd, cd.dec(got), a32, b32, bias32, what="shallow K, bias")
     out = cd.enc(c32)
     api.matmult(cd.enc(a32), cd.enc(b32), out=out)
