@@ -1078,10 +1078,16 @@ __device__ __forceinline__ float4 ld_cluster_f4(uint32_t local_addr, uint32_t ct
 // CTAs with ranks rank_first, rank_first + rank_stride, ...; they are added in that order.  A read of a neighbour's
 // shared memory takes several hundred cycles, so every thread first issues the reads of U items x S slices and only
 // then starts adding: the latency is paid once per batch, not once per read.
+__device__ __forceinline__ float4 ld_shared_f4(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
+    return v;
+}
+
 template <int S, int U>
 __device__ __forceinline__ void cluster_reduce_store(const UmmaParams& p, const ClusterKParams& cp, uint32_t tile_base, int rows,
                                                      int m_base, int n_base, int col_first, int cols_mine, uint32_t rank_first,
-                                                     uint32_t rank_stride) {
+                                                     uint32_t rank_stride, int my_slice) {
     const int groups = cols_mine >> 2;
     const int items = rows * groups;
     for (int base = threadIdx.x; base < items; base += kThreads * U) {
@@ -1095,7 +1101,8 @@ __device__ __forceinline__ void cluster_reduce_store(const UmmaParams& p, const 
             gcol[u] = live ? (i - row[u] * groups) * 4 + col_first : col_first;
             const uint32_t addr = tile_base + uint32_t(row[u] * cp.pitch + gcol[u]) * 4u;
 #pragma unroll
-            for (int sl = 0; sl < S; ++sl) v[u][sl] = ld_cluster_f4(addr, rank_first + uint32_t(sl) * rank_stride);
+            for (int sl = 0; sl < S; ++sl)     // this CTA's own partial is a plain shared-memory read; only the others cross the cluster
+                v[u][sl] = sl == my_slice ? ld_shared_f4(addr) : ld_cluster_f4(addr, rank_first + uint32_t(sl) * rank_stride);
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
@@ -1270,9 +1277,9 @@ umma_gemm_cluster_k_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
         const int rows = min(kBM, p.m - m0);
         const int col_first = int(rank) * cols_mine;
         switch (cp.slices) {
-            case 2: cluster_reduce_store<2, 4>(p, cp, smem_base, rows, m0, n0, col_first, cols_mine, 0u, 1u); break;
-            case 4: cluster_reduce_store<4, 4>(p, cp, smem_base, rows, m0, n0, col_first, cols_mine, 0u, 1u); break;
-            default: cluster_reduce_store<8, 2>(p, cp, smem_base, rows, m0, n0, col_first, cols_mine, 0u, 1u); break;
+            case 2: cluster_reduce_store<2, 8>(p, cp, smem_base, rows, m0, n0, col_first, cols_mine, 0u, 1u, int(rank)); break;
+            case 4: cluster_reduce_store<4, 4>(p, cp, smem_base, rows, m0, n0, col_first, cols_mine, 0u, 1u, int(rank)); break;
+            default: cluster_reduce_store<8, 2>(p, cp, smem_base, rows, m0, n0, col_first, cols_mine, 0u, 1u, int(rank)); break;
         }
     }
     // nobody leaves while a neighbour may still read its shared memory
@@ -1439,8 +1446,8 @@ umma_gemm_pair_cluster_k_kernel(const __grid_constant__ CUtensorMap tma_a, const
         // the S CTAs with this row half share the tile's 256 columns: this one takes columns [slice, slice + 1) * 256 / S
         const int cols_mine = BN / cp.slices;
         const int rows = max(0, min(128, p.m - m0));
-        if (cp.slices == 2) cluster_reduce_store<2, 4>(p, cp, smem_base, rows, m0, n0_pair, slice * cols_mine, cols_mine, half, 2u);
-        else cluster_reduce_store<4, 4>(p, cp, smem_base, rows, m0, n0_pair, slice * cols_mine, cols_mine, half, 2u);
+        if (cp.slices == 2) cluster_reduce_store<2, 8>(p, cp, smem_base, rows, m0, n0_pair, slice * cols_mine, cols_mine, half, 2u, slice);
+        else cluster_reduce_store<4, 4>(p, cp, smem_base, rows, m0, n0_pair, slice * cols_mine, cols_mine, half, 2u, slice);
     }
     tcgen05_fence_before();
     cluster_sync_all();   // nobody leaves while a neighbour may still read its shared memory or signal its barriers
