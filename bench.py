@@ -103,26 +103,41 @@ class ClockSampler(threading.Thread):
                 "reasons": sorted(self.reasons), "samples": len(s)}
 
 
+def cpu_kernel():
+    """(function(a, b_stored) -> C, kind, threads): the reference's own matmult kernel compiled from its sources
+    (oracle/_ref, built by oracle/build_ref.py where the reference tree is present and carried along otherwise) when
+    it is available, else the restatement of it in oracle/oracle.cpp.  Both use the host threads the reference would
+    (its cap is 21)."""
+    from oracle import oracle
+    oracle.build()
+    threads = oracle.default_threads()
+    try:
+        if oracle.reference_lib() is not None:
+            return (lambda a, bs: oracle.reference_matmult(a, bs, False, True)), "reference", threads
+    except OSError:
+        pass
+    return (lambda a, bs: oracle.matmult(a, bs, False, True, threads=threads)), "port", threads
+
+
 def run_reference(args, rank, world):
-    """The reference's own CPU algorithm for this path (the oracle restatement: the reference itself cannot be
-    compiled here, its simde/TBB/half submodules are empty) on the box's host cores.  One step = `sample`
-    items of the batch; thread count follows the reference's cap of 21."""
+    """The reference's own CPU implementation of this path on the box's host cores: its matmult kernel compiled from
+    its own sources (oracle/_ref; the un-vendored simde / oneTBB / half headers are replaced by stand-ins, see
+    oracle/build_ref.py), or the restatement where that library is missing.  One step = `sample` items of the batch."""
     if rank != 0:
         return
     import numpy as np
     from oracle import oracle
-    oracle.build()
-    threads = oracle.default_threads()
+    kernel, kind, threads = cpu_kernel()
     sample = 2
     rng = np.random.default_rng(3)
     a = (rng.standard_normal((sample, M, K)) * 0.1).astype(np.float16)
     bs = (rng.standard_normal((sample, N, K)) * 0.1).astype(np.float16)
     for _ in range(max(1, min(args.warmup, 2))):
-        oracle.matmult(a[:1], bs[:1], False, True, threads=threads)
+        kernel(a[:1], bs[:1])
     steps = max(1, min(args.steps, 10))
     t0 = time.perf_counter()
     for _ in range(steps):
-        oracle.matmult(a, bs, False, True, threads=threads)
+        kernel(a, bs)
     dt = (time.perf_counter() - t0) / steps
     tflops = sample * FLOPS_PER_ITEM / dt / 1e12
     line = {
@@ -130,7 +145,7 @@ def run_reference(args, rank, world):
         "steps": steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f16", "data": "synthetic",
         "config": {"workload": WORKLOAD, "sample": "%d of %d batch items per step" % (sample, BATCH)},
-        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": threads, "kind": kind,
                          "sample": "%d of %d batch items (2048^3 each) per step, %d threads of %d hardware threads"
                                    % (sample, BATCH, threads, oracle.hardware_threads())},
         "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -140,22 +155,20 @@ def run_reference(args, rank, world):
 
 def cpu_baseline():
     import numpy as np
-    from oracle import oracle
-    oracle.build()
-    threads = oracle.default_threads()
+    kernel, kind, threads = cpu_kernel()
     rng = np.random.default_rng(3)
     a = (rng.standard_normal((1, M, K)) * 0.1).astype(np.float16)
     bs = (rng.standard_normal((1, N, K)) * 0.1).astype(np.float16)
-    oracle.matmult(a, bs, False, True, threads=threads)            # warm-up (page faults, thread start)
+    kernel(a, bs)                                                  # warm-up (page faults, thread start)
     t0 = time.perf_counter()
-    oracle.matmult(a, bs, False, True, threads=threads)
+    kernel(a, bs)
     one = time.perf_counter() - t0
-    items = int(max(1, min(16, 10.0 / max(one, 1e-3))))
+    items = int(max(1, min(64, 10.0 / max(one, 1e-3))))
     t0 = time.perf_counter()
     for _ in range(items):
-        oracle.matmult(a, bs, False, True, threads=threads)
+        kernel(a, bs)
     dt = time.perf_counter() - t0
-    return {"value": items * FLOPS_PER_ITEM / dt / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+    return {"value": items * FLOPS_PER_ITEM / dt / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": kind,
             "sample": "%d of %d batch items (2048^3 each), %.1f s of CPU time on %d threads"
                       % (items, BATCH, dt, threads)}
 

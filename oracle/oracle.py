@@ -105,6 +105,46 @@ def matmult_into(a, b, c, transpose_a=False, transpose_b=False, bf16=False, thre
     return c
 
 
+_ref_lib = None
+
+
+def reference_lib():
+    """The reference's own matmult kernel compiled from its sources (oracle/build_ref.py), or None when neither the
+    reference tree nor a prebuilt oracle/_ref/libntref.so is present."""
+    global _ref_lib
+    if _ref_lib is None:
+        from . import build_ref
+        path = build_ref.build()
+        if path is None:
+            return None
+        handle = ctypes.CDLL(path)
+        handle.ntref_matmult.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p] + [ctypes.c_int64] * 4 + [ctypes.c_int] * 2
+        _ref_lib = handle
+    return _ref_lib
+
+
+def reference_matmult(a, b, transpose_a=False, transpose_b=False):
+    """C = op(A).op(B) by the REFERENCE's compiled nt_matmult<T> (2-D or batched, one item after the other as
+    nt_matmult_batch does), from a zero-filled C as functional::matmult calls it.  Uses the host threads the
+    reference would (up to 21).  No BFloat16: the reference has no such dtype."""
+    L = reference_lib()
+    if L is None:
+        raise RuntimeError("the reference's kernel is not available here (no reference tree, no prebuilt library)")
+    a, b = np.ascontiguousarray(a), np.ascontiguousarray(b)
+    batched = a.ndim == 3
+    a3, b3 = (a, b) if batched else (a[None], b[None])
+    m, k = (a3.shape[2], a3.shape[1]) if transpose_a else a3.shape[1:]
+    k2, n = (b3.shape[2], b3.shape[1]) if transpose_b else b3.shape[1:]
+    assert k == k2 and a3.shape[0] == b3.shape[0]
+    c = np.zeros((a3.shape[0], m, n), dtype=a.dtype)
+    code = _code(a, False)
+    for i in range(a3.shape[0]):
+        rc = L.ntref_matmult(code, a3[i].ctypes.data, b3[i].ctypes.data, c[i].ctypes.data, m, k, k2, n, int(transpose_a), int(transpose_b))
+        if rc:
+            raise RuntimeError("the reference kernel has no instantiation for %s" % a.dtype)
+    return c if batched else c[0]
+
+
 def matmult(a, b, transpose_a=False, transpose_b=False, bf16=False, threads=None):
     """functional::matmult: 2-D x 2-D, N-D x N-D with equal leading dims, or one operand of lower
     rank repeated over the other's batch (matmult_cpu.cpp:863-1005).  Result starts from zeros."""
