@@ -43,7 +43,11 @@ typedef enum ntb200_dtype {
      * chain.  These codes reproduce exactly that (bit for bit), on the CUDA-core route; they are NOT the mathematical
      * complex product. */
     NTB200_C64 = 11,
-    NTB200_C128 = 12
+    NTB200_C128 = 12, /* the reference's own Complex128 matmult leaves C untouched (its load / store switch has no case for
+                       * this type's tile size of 4, nt/functional/cpu/matmult/nt_matmult_macros.h:413-438); this code
+                       * computes the lane-wise product its traits define, like NTB200_C64 */
+    NTB200_C32 = 13   /* Complex32, a pair of Float16: lane-wise like the other two, fp32 within a K tile of 8, the running
+                       * sums rounded to Float16 at every tile edge (simde_traits_avx2.h:1270-1300); CUDA-core route */
 } ntb200_dtype;
 
 typedef enum ntb200_status {

@@ -9,7 +9,7 @@ import os
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libntb200.so")
 
-F32, F16, BF16, I8, I16, I32, I64, F64, U8, U16, U32, C64, C128 = range(13)
+F32, F16, BF16, I8, I16, I32, I64, F64, U8, U16, U32, C64, C128, C32 = range(14)
 ROUTE_AUTO, ROUTE_TENSOR, ROUTE_SIMT = 0, 1, 2
 F16_ROUND_ONCE, F16_ROUND_PER_KTILE = 0, 1
 OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_ALLOC, ERR_CUDA, ERR_TIMEOUT, ERR_NO_DEVICE = range(7)

@@ -25,7 +25,7 @@ _TORCH_TO_CODE = {
     torch.int16: _lib.I16, torch.int32: _lib.I32, torch.int64: _lib.I64, torch.float64: _lib.F64,
     torch.uint8: _lib.U8,
     # interleaved (re, im); the reference's componentwise semantics, see NTB200_C64 in include/ntb200.h
-    torch.complex64: _lib.C64, torch.complex128: _lib.C128,
+    torch.complex64: _lib.C64, torch.complex128: _lib.C128, torch.complex32: _lib.C32,
 }
 
 

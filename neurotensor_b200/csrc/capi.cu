@@ -41,7 +41,7 @@ int cuda_fail(cudaError_t err, const char* what) {
 
 size_t dtype_size(int dtype) {
     switch (dtype) {
-        case NTB200_F32: case NTB200_I32: case NTB200_U32: return 4;
+        case NTB200_F32: case NTB200_I32: case NTB200_U32: case NTB200_C32: return 4;
         case NTB200_F16: case NTB200_BF16: case NTB200_I16: case NTB200_U16: return 2;
         case NTB200_I8: case NTB200_U8: return 1;
         case NTB200_I64: case NTB200_F64: case NTB200_C64: return 8;
@@ -52,8 +52,8 @@ size_t dtype_size(int dtype) {
 
 const char* dtype_name(int dtype) {
     static const char* names[] = {"Float32", "Float16", "BFloat16", "int8", "int16", "int32",
-                                  "int64",   "Float64", "uint8",    "uint16", "uint32", "Complex64", "Complex128"};
-    return (dtype >= 0 && dtype <= NTB200_C128) ? names[dtype] : "unknown";
+                                  "int64",   "Float64", "uint8",    "uint16", "uint32", "Complex64", "Complex128", "Complex32"};
+    return (dtype >= 0 && dtype <= NTB200_C32) ? names[dtype] : "unknown";
 }
 
 void count_launch(int n) { g_launches.fetch_add(uint64_t(n), std::memory_order_relaxed); }
@@ -188,7 +188,7 @@ int run_gemm(GemmArgs g, int route, cudaStream_t stream) {
         return launch_fill_c(g, stream);
     }
     // Complex64 / Complex128: the reference's componentwise chains, CUDA-core route only.
-    if (g.dtype == NTB200_C64 || g.dtype == NTB200_C128) {
+    if (g.dtype == NTB200_C64 || g.dtype == NTB200_C128 || g.dtype == NTB200_C32) {
         if (route == NTB200_ROUTE_TENSOR) return fail(NTB200_ERR_UNSUPPORTED, "matmult: complex dtypes run on the CUDA-core route only");
         route = NTB200_ROUTE_SIMT;
     }

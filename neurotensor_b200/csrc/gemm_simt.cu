@@ -81,6 +81,19 @@ template <> struct Num<Cplx<double>> {
     static __device__ __forceinline__ Acc fma(Acc a, Acc b, Acc c) { return Acc(::fma(a.re, b.re, c.re), ::fma(a.im, b.im, c.im)); }
     static __device__ __forceinline__ Acc round_tile(Acc v) { return v; }
 };
+// Complex32 (a pair of Float16): the reference's traits widen the interleaved halves to floats, multiply lane by lane
+// and round the running sums back to Float16 whenever its K tile ends, every 8 k-steps for this type
+// (simde_traits_avx2.h:1270-1300: pack size 4, so a tile is 8 wide; load = cvtph_ps, store = cvtps_ph).
+struct CplxH {
+    __half re, im;
+};
+template <> struct Num<CplxH> {
+    using Acc = Cplx<float>;
+    static __device__ __forceinline__ Acc widen(CplxH v) { return Acc(__half2float(v.re), __half2float(v.im)); }
+    static __device__ __forceinline__ CplxH narrow(Acc v) { CplxH r; r.re = __float2half_rn(v.re); r.im = __float2half_rn(v.im); return r; }
+    static __device__ __forceinline__ Acc fma(Acc a, Acc b, Acc c) { return Acc(fmaf(a.re, b.re, c.re), fmaf(a.im, b.im, c.im)); }
+    static __device__ __forceinline__ Acc round_tile(Acc v) { return Acc(__half2float(__float2half_rn(v.re)), __half2float(__float2half_rn(v.im))); }
+};
 template <class U, class A> struct IntNum {
     using Acc = A;
     static __device__ __forceinline__ Acc widen(U v) { return Acc(v); }
@@ -293,7 +306,8 @@ SimtParams to_params(const GemmArgs& g) {
     const bool a_ok = (g.a_cs == 1 && g.a_rs != 1) ? m4(g.a_rs) : (g.a_rs == 1 && m4(g.a_cs));
     const bool b_ok = (g.b_rs == 1 && g.b_cs != 1) ? m4(g.b_cs) : (g.b_cs == 1 && m4(g.b_rs));
     p.vec_ok = (dtype_size(g.dtype) == 4 && !g.a_ptrs && al16(g.a) && al16(g.b) && a_ok && b_ok && m4(g.a_bs) && m4(g.b_bs)) ? 1 : 0;
-    p.round_per_ktile = (g.dtype == NTB200_F16 && g.f16_rounding == NTB200_F16_ROUND_PER_KTILE) ? 1 : 0;
+    // Complex32 always rounds at the reference's K-tile edges (the kernel's K block for this type is the reference's tile, 8)
+    p.round_per_ktile = ((g.dtype == NTB200_F16 && g.f16_rounding == NTB200_F16_ROUND_PER_KTILE) || g.dtype == NTB200_C32) ? 1 : 0;
     return p;
 }
 
@@ -342,6 +356,7 @@ int dispatch(const GemmArgs& g, cudaStream_t stream, bool fill_only) {
         case NTB200_I64: return launch_typed<unsigned long long>(g, stream, fill_only);
         case NTB200_C64: return launch_typed<Cplx<float>>(g, stream, fill_only);
         case NTB200_C128: return launch_typed<Cplx<double>>(g, stream, fill_only);
+        case NTB200_C32: return launch_typed<CplxH>(g, stream, fill_only);
     }
     return fail(NTB200_ERR_UNSUPPORTED, "unknown dtype %d", g.dtype);
 }

@@ -55,6 +55,9 @@ _NT_MATMULT_DECLARE_STATIC_BLOCK_(uint8_t)
 _NT_MATMULT_DECLARE_STATIC_BLOCK_(int16_t)
 _NT_MATMULT_DECLARE_STATIC_BLOCK_(int32_t)
 _NT_MATMULT_DECLARE_STATIC_BLOCK_(int64_t)
+_NT_MATMULT_DECLARE_STATIC_BLOCK_(complex_32)
+_NT_MATMULT_DECLARE_STATIC_BLOCK_(complex_64)
+_NT_MATMULT_DECLARE_STATIC_BLOCK_(complex_128)
 }
 using namespace nt::functional::cpu;
 extern "C" int ntref_matmult(int code, const void* A, const void* B, void* C, int64_t ar, int64_t ac, int64_t br, int64_t bc, int ta, int tb) {
@@ -67,6 +70,9 @@ extern "C" int ntref_matmult(int code, const void* A, const void* B, void* C, in
         case 6: nt_matmult<int64_t>((const int64_t*)A, (const int64_t*)B, (int64_t*)C, ar, ac, br, bc, ta, tb); return 0;
         case 7: nt_matmult<double>((const double*)A, (const double*)B, (double*)C, ar, ac, br, bc, ta, tb); return 0;
         case 8: nt_matmult<uint8_t>((const uint8_t*)A, (const uint8_t*)B, (uint8_t*)C, ar, ac, br, bc, ta, tb); return 0;
+        case 11: nt_matmult<nt::complex_64>((const nt::complex_64*)A, (const nt::complex_64*)B, (nt::complex_64*)C, ar, ac, br, bc, ta, tb); return 0;
+        case 12: nt_matmult<nt::complex_128>((const nt::complex_128*)A, (const nt::complex_128*)B, (nt::complex_128*)C, ar, ac, br, bc, ta, tb); return 0;
+        case 13: nt_matmult<nt::complex_32>((const nt::complex_32*)A, (const nt::complex_32*)B, (nt::complex_32*)C, ar, ac, br, bc, ta, tb); return 0;
     }
     return 1;
 }

@@ -39,7 +39,8 @@
 
 namespace {
 
-enum DType : int { F32 = 0, F16 = 1, BF16 = 2, I8 = 3, I16 = 4, I32 = 5, I64 = 6, F64 = 7, U8 = 8, U16 = 9, U32 = 10 };
+enum DType : int { F32 = 0, F16 = 1, BF16 = 2, I8 = 3, I16 = 4, I32 = 5, I64 = 6, F64 = 7, U8 = 8, U16 = 9, U32 = 10,
+                   F16_TILE8 = 100 /* one lane of Complex32: Float16 with a K tile of 8 */ };
 
 inline float half_to_float(uint16_t h) { return _cvtsh_ss(h); }
 inline uint16_t float_to_half(float f) { return _cvtss_sh(f, _MM_FROUND_TO_NEAREST_INT); }
@@ -69,7 +70,7 @@ void parallel_rows(int64_t n, int nthreads, F&& f) {
 }
 
 // ---- floating point (fp32 chain) -------------------------------------------------------------
-enum class FloatKind { f32, f16, bf16 };
+enum class FloatKind { f32, f16, bf16, f16_tile8 };
 
 template <FloatKind KIND>
 struct FloatIO;
@@ -79,6 +80,7 @@ struct FloatIO<FloatKind::f32> {
     static float widen(T v) { return v; }
     static T narrow(float v) { return v; }
     static constexpr bool round_each_tile = false;
+    static constexpr int tile = 16;
 };
 template <>
 struct FloatIO<FloatKind::f16> {
@@ -86,6 +88,17 @@ struct FloatIO<FloatKind::f16> {
     static float widen(T v) { return half_to_float(v); }
     static T narrow(float v) { return float_to_half(v); }
     static constexpr bool round_each_tile = true;   // C tile is stored as fp16 after every K tile
+    static constexpr int tile = 16;
+};
+// One lane of a Complex32 matmult: Float16 values, but the reference's K tile for complex_32 is 8 wide (pack size 4,
+// nt/mp/simde_traits/simde_traits_avx2.h:1273-1275), so the running sum is rounded to Float16 every 8 k-steps.
+template <>
+struct FloatIO<FloatKind::f16_tile8> {
+    using T = uint16_t;
+    static float widen(T v) { return half_to_float(v); }
+    static T narrow(float v) { return float_to_half(v); }
+    static constexpr bool round_each_tile = true;
+    static constexpr int tile = 8;
 };
 template <>
 struct FloatIO<FloatKind::bf16> {
@@ -93,6 +106,7 @@ struct FloatIO<FloatKind::bf16> {
     static float widen(T v) { return bf16_to_float(v); }
     static T narrow(float v) { return float_to_bf16(v); }
     static constexpr bool round_each_tile = false;
+    static constexpr int tile = 16;
 };
 
 inline __m256 round_through_half(__m256 v) {
@@ -105,7 +119,7 @@ template <FloatKind KIND>
 void float_rows(const float* Ap, const float* Bp, typename FloatIO<KIND>::T* C, int64_t N, int64_t K,
                 int64_t Kp, int64_t Np, int64_t r0, int64_t r1) {
     using IO = FloatIO<KIND>;
-    constexpr int TILE = 16, MR = 4;
+    constexpr int TILE = IO::tile, MR = 4;
     (void)K;
     for (int64_t j0 = 0; j0 < Np; j0 += 16) {
         const int64_t jn = std::min<int64_t>(16, N - j0);
@@ -228,6 +242,7 @@ int dispatch(int dtype, const void* A, const void* B, void* C, int64_t M, int64_
         case F32: float_gemm<FloatKind::f32>(A, B, C, M, K, N, ta, tb, nthreads); return 0;
         case F16: float_gemm<FloatKind::f16>(A, B, C, M, K, N, ta, tb, nthreads); return 0;
         case BF16: float_gemm<FloatKind::bf16>(A, B, C, M, K, N, ta, tb, nthreads); return 0;
+        case F16_TILE8: float_gemm<FloatKind::f16_tile8>(A, B, C, M, K, N, ta, tb, nthreads); return 0;
         case F64:
             double_gemm(static_cast<const double*>(A), static_cast<const double*>(B), static_cast<double*>(C), M, K, N,
                         ta, tb, nthreads);
@@ -243,7 +258,7 @@ int dispatch(int dtype, const void* A, const void* B, void* C, int64_t M, int64_
 int elem_size(int dtype) {
     switch (dtype) {
         case F32: case I32: case U32: return 4;
-        case F16: case BF16: case I16: case U16: return 2;
+        case F16: case BF16: case I16: case U16: case F16_TILE8: return 2;
         case I8: case U8: return 1;
         case I64: case F64: return 8;
     }

@@ -80,11 +80,28 @@ def bf16_widen(bits):
     return (np.ascontiguousarray(bits, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
 
 
+F16_TILE8 = 100   # one lane of a Complex32 product: Float16 rounded every 8 k-steps
+
+
 def _code(arr, bf16):
+    if bf16 == "c32-lane":
+        assert arr.dtype == np.float16
+        return F16_TILE8
     if bf16:
         assert arr.dtype == np.uint16, "bf16 operands are passed as uint16 bit patterns"
         return BF16
     return _NP_TO_CODE[arr.dtype]
+
+
+def matmult_complex32(a, b, transpose_a=False, transpose_b=False, threads=None):
+    """Complex32 matmult as the reference computes it.  Operands are float16 arrays whose last axis holds (re, im).
+    The reference's traits for complex_32 are the float lane operations on the widened interleaved halves
+    (nt/mp/simde_traits/simde_traits_avx2.h:1270-1400), so real parts meet real parts and imaginary parts imaginary
+    parts, each an fp32 chain rounded to Float16 at the type's K-tile edges, every 8 k-steps."""
+    assert a.dtype == np.float16 and b.dtype == np.float16 and a.shape[-1] == 2 and b.shape[-1] == 2
+    re = matmult(np.ascontiguousarray(a[..., 0]), np.ascontiguousarray(b[..., 0]), transpose_a, transpose_b, "c32-lane", threads)
+    im = matmult(np.ascontiguousarray(a[..., 1]), np.ascontiguousarray(b[..., 1]), transpose_a, transpose_b, "c32-lane", threads)
+    return np.stack([re, im], axis=-1)
 
 
 def matmult_into(a, b, c, transpose_a=False, transpose_b=False, bf16=False, threads=None):

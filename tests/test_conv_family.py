@@ -9,7 +9,7 @@ import pytest
 
 from conftest import REF_GOLDEN
 
-RTOL, ATOL = 1e-4, 1e-5
+RTOL, ATOL = 1e-5, 1e-8   # nt::allclose defaults (nt/functional/tensor_files/compare.h:34), as the reference's tests use them
 
 
 def g(name):

@@ -175,6 +175,32 @@ def test_unaligned_fp16_falls_to_cuda_cores_not_cpu(api, oracle, L):
         api.matmult(dev(a), dev(b), route=L.ROUTE_TENSOR)
 
 
+def test_complex32_matmult(api, oracle, L):
+    """Complex32 (pairs of Float16): lane-wise like Complex64, the running sums rounded to Float16 at the edges of the
+    reference's K tile for this type, every 8 k-steps.  Bit for bit against the oracle (which is pinned on the compiled
+    reference kernel for this type): 2-D, batched against a 2-D operand, both transposed views, C +=."""
+    rng = np.random.default_rng(109)
+    pairs = lambda shape: normal(rng, shape + (2,), np.float16, 0.5)
+    as_c32 = lambda arr: torch.view_as_complex(torch.from_numpy(arr).cuda())
+    back = lambda t: torch.view_as_real(t).cpu().numpy()
+    a, b = pairs((3, 70, 45)), pairs((45, 133))
+    got = api.matmult(as_c32(a), as_c32(b))
+    assert L.last_route() == "simt" and got.dtype == torch.complex32
+    assert np.array_equal(back(got), oracle.matmult_complex32(a, b))
+    bt, at = pairs((133, 45)), pairs((3, 45, 70))
+    assert np.array_equal(back(api.matmult(as_c32(a), as_c32(bt), transpose_b=True)), oracle.matmult_complex32(a, bt, transpose_b=True))
+    assert np.array_equal(back(api.matmult(as_c32(at), as_c32(b), transpose_a=True)), oracle.matmult_complex32(at, b, transpose_a=True))
+    # fp32 lanes rounded once would differ: the tile-edge rounding is really there
+    once = np.stack([(a[0, ..., i].astype(np.float32) @ b[..., i].astype(np.float32)).astype(np.float16) for i in (0, 1)], axis=-1)
+    assert not np.array_equal(back(got)[0], once)
+    c0 = pairs((70, 133))
+    out = as_c32(c0.copy())
+    api.matmult(as_c32(a[0]), as_c32(b), out=out)
+    exp = np.stack([oracle.matmult_into(np.ascontiguousarray(a[0, ..., i]), np.ascontiguousarray(b[..., i]), np.ascontiguousarray(c0[..., i]),
+                                        bf16="c32-lane") for i in (0, 1)], axis=-1)
+    assert np.array_equal(back(out), exp)
+
+
 def test_transposed_view_is_not_copied(api, oracle, L):
     """b.transpose(-1,-2) is a stride swap (the reference flips the flag, matmult_cpu.cpp:268-273)."""
     rng = np.random.default_rng(31)
@@ -528,6 +554,32 @@ def test_complex_matmult_is_the_references_lanewise_product(api, oracle, L, np_d
     assert np.array_equal(host(out).real, exp_re) and np.array_equal(host(out).imag, exp_im)
     with pytest.raises(L.Ntb200Error):
         api.matmult(dev(a), dev(b), route=L.ROUTE_TENSOR)
+
+
+def test_complex32_matmult(api, oracle, L):
+    """Complex32 (pairs of Float16): lane-wise like Complex64, the running sums rounded to Float16 at the edges of the
+    reference's K tile for this type, every 8 k-steps.  Bit for bit against the oracle (which is pinned on the compiled
+    reference kernel for this type): 2-D, batched against a 2-D operand, both transposed views, C +=."""
+    rng = np.random.default_rng(109)
+    pairs = lambda shape: normal(rng, shape + (2,), np.float16, 0.5)
+    as_c32 = lambda arr: torch.view_as_complex(torch.from_numpy(arr).cuda())
+    back = lambda t: torch.view_as_real(t).cpu().numpy()
+    a, b = pairs((3, 70, 45)), pairs((45, 133))
+    got = api.matmult(as_c32(a), as_c32(b))
+    assert L.last_route() == "simt" and got.dtype == torch.complex32
+    assert np.array_equal(back(got), oracle.matmult_complex32(a, b))
+    bt, at = pairs((133, 45)), pairs((3, 45, 70))
+    assert np.array_equal(back(api.matmult(as_c32(a), as_c32(bt), transpose_b=True)), oracle.matmult_complex32(a, bt, transpose_b=True))
+    assert np.array_equal(back(api.matmult(as_c32(at), as_c32(b), transpose_a=True)), oracle.matmult_complex32(at, b, transpose_a=True))
+    # fp32 lanes rounded once would differ: the tile-edge rounding is really there
+    once = np.stack([(a[0, ..., i].astype(np.float32) @ b[..., i].astype(np.float32)).astype(np.float16) for i in (0, 1)], axis=-1)
+    assert not np.array_equal(back(got)[0], once)
+    c0 = pairs((70, 133))
+    out = as_c32(c0.copy())
+    api.matmult(as_c32(a[0]), as_c32(b), out=out)
+    exp = np.stack([oracle.matmult_into(np.ascontiguousarray(a[0, ..., i]), np.ascontiguousarray(b[..., i]), np.ascontiguousarray(c0[..., i]),
+                                        bf16="c32-lane") for i in (0, 1)], axis=-1)
+    assert np.array_equal(back(out), exp)
 
 
 @pytest.mark.gpu

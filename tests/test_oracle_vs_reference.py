@@ -60,6 +60,34 @@ def test_oracle_equals_the_reference_kernel_bit_for_bit(oracle, dtype, ta, tb):
         assert oracle.matmult(a, b, ta, tb).tobytes() == want0.tobytes()
 
 
+def test_complex_types_on_the_reference_kernel(oracle):
+    """Complex64 and Complex32: the reference multiplies real parts with real parts and imaginary parts with imaginary
+    parts (its traits are the lane operations on interleaved data), Complex32 rounding to Float16 every 8 k-steps; the
+    oracle reproduces both bit for bit.  Complex128: the reference's kernel returns with C untouched -- the switch that
+    loads and stores the C tile has cases for tile sizes 64, 32, 16 and 8 only (nt_matmult_macros.h:413-438) and this
+    type's tile is 4 wide -- so functional::matmult of two Complex128 tensors is all zeros there.  That is recorded
+    here as a fact about the reference; the library computes the lane-wise product its traits define, like Complex64."""
+    rng = np.random.default_rng(13)
+    for m, k, n in SHAPES[:6]:
+        for ta in (False, True):
+            for tb in (False, True):
+                sa, sb = ((k, m) if ta else (m, k)), ((n, k) if tb else (k, n))
+                a = (rng.standard_normal(sa) + 1j * rng.standard_normal(sa)).astype(np.complex64)
+                b = (rng.standard_normal(sb) + 1j * rng.standard_normal(sb)).astype(np.complex64)
+                c = np.zeros((m, n), np.complex64)
+                assert REF.ntref_matmult(11, a.ctypes.data, b.ctypes.data, c.ctypes.data, m, k, k, n, int(ta), int(tb)) == 0
+                assert oracle.matmult(a, b, ta, tb).tobytes() == c.tobytes()
+                ah, bh = rng.standard_normal(sa + (2,)).astype(np.float16), rng.standard_normal(sb + (2,)).astype(np.float16)
+                ch = np.zeros((m, n, 2), np.float16)
+                assert REF.ntref_matmult(13, ah.ctypes.data, bh.ctypes.data, ch.ctypes.data, m, k, k, n, int(ta), int(tb)) == 0
+                assert oracle.matmult_complex32(ah, bh, ta, tb).tobytes() == ch.tobytes()
+    a = (rng.standard_normal((8, 8)) + 1j * rng.standard_normal((8, 8))).astype(np.complex128)
+    c0 = np.full((8, 8), 1 + 2j, np.complex128)
+    c = c0.copy()
+    assert REF.ntref_matmult(12, a.ctypes.data, a.ctypes.data, c.ctypes.data, 8, 8, 8, 8, 0, 0) == 0
+    assert np.array_equal(c, c0)            # untouched: no tile-size-4 case in the reference's load / store switch
+
+
 def test_float16_rounds_the_running_sum_every_16_k(oracle):
     """The property the Float16 parity bars rest on, seen on the reference kernel itself: its result differs from an
     fp32-accumulate-and-round-once product, by the amounts the oracle predicts."""
