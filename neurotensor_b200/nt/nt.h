@@ -77,7 +77,7 @@ decltype(auto) pick(Default&& def, std::tuple<A...>& args) {
     } else if constexpr (Pos < leading_positional<A...>()) {
         return as_lvalue(std::get<Pos>(args));
     } else {
-        return std::forward<Default>(def);
+        return std::decay_t<Default>(std::forward<Default>(def));   // by value: the default is a temporary of the caller
     }
 }
 template <class Tag, size_t Pos, class... A>

@@ -317,7 +317,7 @@ int main(int argc, char** argv) {
         TensorGrad x(nt::randn_seeded({256, 256}, DType::BFloat16, 7), false);
         Tensor target = nt::randn_seeded({256, 256}, DType::BFloat16, 8);
         TensorGrad y = l2(fn::relu(l1(x)));
-        REQUIRE(std::string(ntb200_last_gemm_route()) == "umma_bf16");
+        REQUIRE(std::string(ntb200_last_gemm_route()).rfind("umma_bf16", 0) == 0);   // any of the tensor-core routes
         nt::ScalarGrad loss = nt::loss::MSE(y, target);
         REQUIRE(std::isfinite(loss.item()) && loss.item() > 0);
         loss.backward();
