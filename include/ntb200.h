@@ -344,6 +344,32 @@ int ntb200_conv3d_backward_image(int dtype, const void* grad, const void* w, voi
 int ntb200_conv3d_backward_kernel(int dtype, const void* x, const void* grad, void* d_kernel, void* workspace,
                                   int accumulate, const ntb200_conv3d_geom* geom, void* stream);
 
+/* ---- convnd ---------------------------------------------------------------------------------------------
+ * functional::convnd / conv_transposend / unfoldnd for any number N of spatial dimensions
+ * (nt/functional/tensor_files/conv.cpp:177-262 and :747-860; nt/functional/cpu/unfoldnd.cpp,
+ * unfoldnd_backward.cpp), 1 <= N <= NTB200_CONVND_MAX_DIMS.  x is [B, C, size_0 .. size_{N-1}], w is
+ * [Cout, C/groups, kernel_0 .. kernel_{N-1}]; the arrays hold one entry per spatial dimension, outermost
+ * first, entries past dims are ignored.  The column matrix is col[b][(c, k_0 .. k_{N-1})][(o_0 .. o_{N-1})],
+ * both index groups flattened row-major - for N = 1, 2, 3 exactly the layouts of unfold1d/2d/3d, which is what
+ * the reference's own tests assert of unfoldnd (tests/src/col_im_tests.cpp:47-83).  One workspace size serves
+ * the three calls.  conv_transposend(x, w) is ntb200_convnd_backward_image with x in the place of grad.
+ * This struct is frozen: new inputs get new entry points. */
+#define NTB200_CONVND_MAX_DIMS 8
+typedef struct ntb200_convnd_geom {
+    int64_t dims, batch, channels, cout, groups;
+    int64_t size[NTB200_CONVND_MAX_DIMS], kernel[NTB200_CONVND_MAX_DIMS], stride[NTB200_CONVND_MAX_DIMS],
+            padding[NTB200_CONVND_MAX_DIMS], dilation[NTB200_CONVND_MAX_DIMS];
+} ntb200_convnd_geom;
+int ntb200_im2colnd(int dtype, const void* im, void* col, const ntb200_convnd_geom* geom, void* stream);
+int ntb200_col2imnd(int dtype, const void* col, void* im, const ntb200_convnd_geom* geom, void* stream);
+size_t ntb200_convnd_workspace_bytes(int dtype, const ntb200_convnd_geom* geom);
+int ntb200_convnd(int dtype, const void* x, const void* w, void* out, void* workspace, const ntb200_convnd_geom* geom,
+                  void* stream);
+int ntb200_convnd_backward_image(int dtype, const void* grad, const void* w, void* d_image, void* workspace,
+                                 const ntb200_convnd_geom* geom, void* stream);
+int ntb200_convnd_backward_kernel(int dtype, const void* x, const void* grad, void* d_kernel, void* workspace,
+                                  int accumulate, const ntb200_convnd_geom* geom, void* stream);
+
 /* ntb200_conv2d for callers that cannot allocate device memory.  No counterpart in the reference, which
  * allocates its column matrix on the CPU heap as it goes.  Some users of this library cannot do the
  * device-side equivalent: their application has given the whole device heap to its own allocator, so a

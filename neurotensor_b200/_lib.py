@@ -36,6 +36,13 @@ class Conv3dGeom(ctypes.Structure):
                [(n, ctypes.c_int64 * 3) for n in ("kernel", "stride", "padding", "dilation")]
 
 
+class ConvNdGeom(ctypes.Structure):
+    """ntb200_convnd_geom: arrays hold one entry per spatial dimension, outermost first."""
+    MAX_DIMS = 8
+    _fields_ = [(n, ctypes.c_int64) for n in ("dims", "batch", "channels", "cout", "groups")] + \
+               [(n, ctypes.c_int64 * 8) for n in ("size", "kernel", "stride", "padding", "dilation")]
+
+
 class GemmEpilogue(ctypes.Structure):
     _fields_ = [("relu_out", _vp), ("relu_mask_src", _vp)]
 
@@ -106,6 +113,12 @@ SIGNATURES = {
     "ntb200_conv2d_grouped_backward_kernel": (_ci, [_ci, _vp, _vp, _vp, _vp, _ci] + [_i64] * 14 + [_vp]),
     "ntb200_im2col3d": (_ci, [_ci, _vp, _vp, ctypes.POINTER(Conv3dGeom), _vp]),
     "ntb200_col2im3d": (_ci, [_ci, _vp, _vp, ctypes.POINTER(Conv3dGeom), _vp]),
+    "ntb200_im2colnd": (_ci, [_ci, _vp, _vp, ctypes.POINTER(ConvNdGeom), _vp]),
+    "ntb200_col2imnd": (_ci, [_ci, _vp, _vp, ctypes.POINTER(ConvNdGeom), _vp]),
+    "ntb200_convnd_workspace_bytes": (_sz, [_ci, ctypes.POINTER(ConvNdGeom)]),
+    "ntb200_convnd": (_ci, [_ci, _vp, _vp, _vp, _vp, ctypes.POINTER(ConvNdGeom), _vp]),
+    "ntb200_convnd_backward_image": (_ci, [_ci, _vp, _vp, _vp, _vp, ctypes.POINTER(ConvNdGeom), _vp]),
+    "ntb200_convnd_backward_kernel": (_ci, [_ci, _vp, _vp, _vp, _vp, _ci, ctypes.POINTER(ConvNdGeom), _vp]),
     "ntb200_conv3d_workspace_bytes": (_sz, [_ci, ctypes.POINTER(Conv3dGeom)]),
     "ntb200_conv3d": (_ci, [_ci, _vp, _vp, _vp, _vp, ctypes.POINTER(Conv3dGeom), _vp]),
     "ntb200_conv3d_backward_image": (_ci, [_ci, _vp, _vp, _vp, _vp, ctypes.POINTER(Conv3dGeom), _vp]),

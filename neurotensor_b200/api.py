@@ -671,6 +671,174 @@ def conv_transpose3d_backward(x, w, grad, stride=1, padding=0, output_padding=0,
     return dx.reshape(x.shape), dw_.reshape(w.shape)
 
 
+def _ntuple(v, n):
+    t = tuple(v) if isinstance(v, (tuple, list)) else (v,) * n
+    if len(t) != n:
+        raise ValueError("Error, expected a single value or %d values (one per dimension), got %d" % (n, len(t)))
+    return t
+
+
+def _geomn(dim, bsz, ch, size, cout, groups, k, s, p, d):
+    if dim > _lib.ConvNdGeom.MAX_DIMS:
+        raise ValueError("convnd: at most %d spatial dimensions (got %d)" % (_lib.ConvNdGeom.MAX_DIMS, dim))
+    g = _lib.ConvNdGeom()
+    g.dims, g.batch, g.channels, g.cout, g.groups = dim, bsz, ch, cout, groups
+    for arr, val in ((g.size, size), (g.kernel, k), (g.stride, s), (g.padding, p), (g.dilation, d)):
+        for i in range(dim):
+            arr[i] = val[i]
+    return g
+
+
+def _convnd_setup(x, w, dim, stride, padding, dilation, what="conv"):
+    _require_cuda(x, w)
+    if dim <= 0:
+        raise ValueError("Error, cannot do a dynamic ConvND where N < 0 got (N = %d)" % dim)
+    if x.dim() < dim + 1:
+        raise ValueError("Expected to get a %dD or greater tensor as the input for a %dd convolution, but got %dD" % (dim + 1, dim, x.dim()))
+    if w.dim() not in (dim + 1, dim + 2):
+        raise ValueError("Expected to get a %dD or %dD tensor as the kernel for a %dd convolution, but got %dD" % (dim + 1, dim + 2, dim, w.dim()))
+    if x.dtype != w.dtype:
+        raise ValueError("Expected both kernel and image to have the same dtype for %s%dd but got %s and %s" % (what, dim, w.dtype, x.dtype))
+    wn = (w.unsqueeze(0) if w.dim() == dim + 1 else w).contiguous()
+    xn = (x.unsqueeze(0) if x.dim() == dim + 1 else x.reshape((-1,) + tuple(x.shape[-(dim + 1):]))).contiguous()
+    s, p, d = _ntuple(stride, dim), _ntuple(padding, dim), _ntuple(dilation, dim)
+    if min(s) < 1:
+        raise ValueError("Conv%dD stride cannot be less than 1" % dim)
+    if min(d) < 1:
+        raise ValueError("Conv%dD dilation cannot be less than 1" % dim)
+    if min(p) < 0:
+        raise ValueError("Conv%dD padding cannot be less than 0" % dim)
+    return xn, wn, s, p, d
+
+
+def _outn(size, k, s, p, d):
+    return tuple((size[i] + 2 * p[i] - d[i] * (k[i] - 1) - 1) // s[i] + 1 for i in range(len(size)))
+
+
+def _workspace_nd(code, geom, device):
+    return torch.empty(max(1, lib().ntb200_convnd_workspace_bytes(code, ctypes.byref(geom))), dtype=torch.uint8, device=device)
+
+
+def unfoldnd(x, dim, kernel_size, dilation=1, padding=0, stride=1):
+    """functional::unfoldnd with transpose_out (colim_transform.h:106; cpu/unfoldnd.cpp): x [B, C, size...] ->
+    col [B, C*prod(kernel), prod(out)], rows ordered (c, k_0 .. k_{N-1}), columns (o_0 .. o_{N-1})."""
+    _require_cuda(x)
+    xn = x.contiguous()
+    k, s, p, d = _ntuple(kernel_size, dim), _ntuple(stride, dim), _ntuple(padding, dim), _ntuple(dilation, dim)
+    bsz, ch = xn.shape[:2]
+    size = tuple(xn.shape[2:])
+    on = _outn(size, k, s, p, d)
+    if min(on) <= 0:
+        raise ValueError("unfoldnd: calculated output size %s must be at least one" % (on,))
+    geom = _geomn(dim, bsz, ch, size, 1, 1, k, s, p, d)
+    taps = 1
+    for v in k:
+        taps *= v
+    L = 1
+    for v in on:
+        L *= v
+    col = torch.empty((bsz, ch * taps, L), dtype=x.dtype, device=x.device)
+    check(lib().ntb200_im2colnd(dtype_code(x), xn.data_ptr(), col.data_ptr(), ctypes.byref(geom), _stream()))
+    return col
+
+
+def unfoldnd_backward(dcol, dim, output_size, kernel_size, dilation=1, padding=0, stride=1):
+    """functional::unfoldnd_backward (colim_transform.h:112): the adjoint of unfoldnd -> [B, C, size...]."""
+    _require_cuda(dcol)
+    k, s, p, d = _ntuple(kernel_size, dim), _ntuple(stride, dim), _ntuple(padding, dim), _ntuple(dilation, dim)
+    size = _ntuple(output_size, dim)
+    taps = 1
+    for v in k:
+        taps *= v
+    bsz, ch = dcol.shape[0], dcol.shape[1] // taps
+    geom = _geomn(dim, bsz, ch, size, 1, 1, k, s, p, d)
+    im = torch.empty((bsz, ch) + size, dtype=dcol.dtype, device=dcol.device)
+    check(lib().ntb200_col2imnd(dtype_code(dcol), dcol.contiguous().data_ptr(), im.data_ptr(), ctypes.byref(geom), _stream()))
+    return im
+
+
+def convnd(x, w, dim, stride=1, padding=0, dilation=1, groups=1):
+    """functional::convnd (conv.cpp:177-262) -> [B, Cout, out_0 .. out_{N-1}]; w is [Cout, C/groups, k_0 .. k_{N-1}]."""
+    xn, wn, s, p, d = _convnd_setup(x, w, dim, stride, padding, dilation)
+    bsz, ch = xn.shape[:2]
+    cout, k = wn.shape[0], tuple(wn.shape[2:])
+    if groups < 1 or ch % groups:
+        raise ValueError("Expected image channels to be divisible by groups in Conv%dd but got %d %% %d != 0" % (dim, ch, groups))
+    if wn.shape[1] * groups != ch:
+        raise ValueError("Expected kernel rows times groups to be equal to rows of image Conv%dd but got %d * %d != %d"
+                         % (dim, wn.shape[1], groups, ch))
+    size = tuple(xn.shape[2:])
+    on = _outn(size, k, s, p, d)
+    if min(on) <= 0:
+        raise ValueError("conv%dd: calculated output size %s must be at least one" % (dim, on))
+    geom = _geomn(dim, bsz, ch, size, cout, groups, k, s, p, d)
+    code = dtype_code(x)
+    ws = _workspace_nd(code, geom, x.device)
+    out = torch.empty((bsz, cout) + on, dtype=x.dtype, device=x.device)
+    check(lib().ntb200_convnd(code, xn.data_ptr(), wn.data_ptr(), out.data_ptr(), ws.data_ptr(), ctypes.byref(geom), _stream()))
+    return out
+
+
+def convnd_backward(x, w, grad, dim, stride=1, padding=0, dilation=1, groups=1):
+    """conv_dimage / conv_dkernel for any dimension (conv.cpp:378-410, 501-560) -> (d_image, d_kernel)."""
+    xn, wn, s, p, d = _convnd_setup(x, w, dim, stride, padding, dilation)
+    _require_cuda(grad)
+    bsz, ch = xn.shape[:2]
+    cout, k = wn.shape[0], tuple(wn.shape[2:])
+    geom = _geomn(dim, bsz, ch, tuple(xn.shape[2:]), cout, groups, k, s, p, d)
+    code = dtype_code(x)
+    g = grad.contiguous()
+    ws = _workspace_nd(code, geom, x.device)
+    dx, dw_ = torch.empty_like(xn), torch.empty_like(wn)
+    check(lib().ntb200_convnd_backward_image(code, g.data_ptr(), wn.data_ptr(), dx.data_ptr(), ws.data_ptr(), ctypes.byref(geom),
+                                             _stream()))
+    check(lib().ntb200_convnd_backward_kernel(code, xn.data_ptr(), g.data_ptr(), dw_.data_ptr(), ws.data_ptr(), 0,
+                                              ctypes.byref(geom), _stream()))
+    return dx.reshape(x.shape), dw_.reshape(w.shape)
+
+
+def _transposen_geom(xn, wn, dim, s, p, opad, d, groups):
+    if xn.shape[1] != wn.shape[0]:
+        raise ValueError("Expected image channels to be the same as the kernel batches for conv_transpose%dd but got %s and %s"
+                         % (dim, tuple(xn.shape), tuple(wn.shape)))
+    if any(opad[i] < 0 or opad[i] >= s[i] for i in range(dim)):
+        raise ValueError("conv_transpose%dd: output_padding must be at least 0 and smaller than the stride" % dim)
+    k = tuple(wn.shape[2:])
+    outn = tuple((xn.shape[2 + i] - 1) * s[i] - 2 * p[i] + d[i] * (k[i] - 1) + 1 + opad[i] for i in range(dim))
+    return k, outn, wn.shape[1] * groups
+
+
+def conv_transposend(x, w, dim, stride=1, padding=0, output_padding=0, dilation=1, groups=1):
+    """functional::conv_transposend (conv.cpp:747-860): x [B, Cin, size...], w [Cin, Cout/groups, k...] ->
+    [B, Cout, out...], evaluated as the image gradient of the convolution with the same kernel."""
+    xn, wn, s, p, d = _convnd_setup(x, w, dim, stride, padding, dilation, "conv transpose")
+    k, outn, cout = _transposen_geom(xn, wn, dim, s, p, _ntuple(output_padding, dim), d, groups)
+    bsz, cin = xn.shape[:2]
+    geom = _geomn(dim, bsz, cout, outn, cin, groups, k, s, p, d)
+    code = dtype_code(x)
+    ws = _workspace_nd(code, geom, x.device)
+    out = torch.empty((bsz, cout) + outn, dtype=x.dtype, device=x.device)
+    check(lib().ntb200_convnd_backward_image(code, xn.data_ptr(), wn.data_ptr(), out.data_ptr(), ws.data_ptr(), ctypes.byref(geom),
+                                             _stream()))
+    return out
+
+
+def conv_transposend_backward(x, w, grad, dim, stride=1, padding=0, output_padding=0, dilation=1, groups=1):
+    xn, wn, s, p, d = _convnd_setup(x, w, dim, stride, padding, dilation, "conv transpose")
+    _require_cuda(grad)
+    k, outn, cout = _transposen_geom(xn, wn, dim, s, p, _ntuple(output_padding, dim), d, groups)
+    bsz, cin = xn.shape[:2]
+    geom = _geomn(dim, bsz, cout, outn, cin, groups, k, s, p, d)
+    code = dtype_code(x)
+    g = grad.contiguous()
+    ws = _workspace_nd(code, geom, x.device)
+    dx, dw_ = torch.empty_like(xn), torch.empty_like(wn)
+    check(lib().ntb200_convnd(code, g.data_ptr(), wn.data_ptr(), dx.data_ptr(), ws.data_ptr(), ctypes.byref(geom), _stream()))
+    check(lib().ntb200_convnd_backward_kernel(code, g.data_ptr(), xn.data_ptr(), dw_.data_ptr(), ws.data_ptr(), 0,
+                                              ctypes.byref(geom), _stream()))
+    return dx.reshape(x.shape), dw_.reshape(w.shape)
+
+
 def relu(x):
     _require_cuda(x)
     x = x.contiguous()

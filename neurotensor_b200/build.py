@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT_DIR = os.path.join(HERE, "_build")
 LIB = os.path.join(HERE, "libntb200.so")
-SOURCES = ["capi.cu", "gemm_umma.cu", "gemm_simt.cu", "aux_kernels.cu", "conv2d_static.cu", "conv2d_implicit.cu", "conv2d_backward.cu", "optimizer_kernels.cu", "conv2d_grouped.cu", "conv3d.cu", "gemv.cu", "dist.cu"]
+SOURCES = ["capi.cu", "gemm_umma.cu", "gemm_simt.cu", "aux_kernels.cu", "conv2d_static.cu", "conv2d_implicit.cu", "conv2d_backward.cu", "optimizer_kernels.cu", "conv2d_grouped.cu", "conv3d.cu", "convnd.cu", "gemv.cu", "dist.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
          "--expt-relaxed-constexpr"]

@@ -140,7 +140,8 @@ using namespace ntb200;
         case 1: { using T = uint8_t; CALL; break; }                    \
         case 2: { using T = uint16_t; CALL; break; }                   \
         case 4: { using T = uint32_t; CALL; break; }                   \
-        default: { using T = unsigned long long; CALL; break; }        \
+        case 8: { using T = unsigned long long; CALL; break; }         \
+        default: return fail(NTB200_ERR_UNSUPPORTED, "column matrix: elements of 1, 2, 4 or 8 bytes (got %d)", int(es)); \
     }
 
 extern "C" {

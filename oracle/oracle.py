@@ -442,6 +442,101 @@ def conv_transpose3d_backward(x, w, grad, stride=1, padding=0, output_padding=0,
     return dx, dw
 
 
+def _ntuple(v, n):
+    return tuple(v) if isinstance(v, (tuple, list)) else (v,) * n
+
+
+def unfoldnd(x, dim, kernel_size, dilation=1, padding=0, stride=1):
+    """unfoldnd with transpose_out (cpu/unfoldnd.cpp:327-420): col[b][(c, k_0..k_{N-1})][(o_0..o_{N-1})] =
+    x[b][c][o_i*s_i - p_i + k_i*d_i ...], zero outside the image; in 1, 2 and 3 dimensions the layouts of
+    unfold1d / unfold2d / unfold3d (the reference asserts this in tests/src/col_im_tests.cpp:47-83)."""
+    k, d, p, s = _ntuple(kernel_size, dim), _ntuple(dilation, dim), _ntuple(padding, dim), _ntuple(stride, dim)
+    b, c = x.shape[:2]
+    size = x.shape[2:]
+    o = tuple(conv_out_size(size[i], k[i], s[i], p[i], d[i]) for i in range(dim))
+    xp = np.zeros((b, c) + tuple(size[i] + 2 * p[i] for i in range(dim)), dtype=x.dtype)
+    xp[(slice(None), slice(None)) + tuple(slice(p[i], p[i] + size[i]) for i in range(dim))] = x
+    col = np.empty((b, c) + k + o, dtype=x.dtype)
+    for tap in np.ndindex(*k):
+        src = tuple(slice(tap[i] * d[i], tap[i] * d[i] + (o[i] - 1) * s[i] + 1, s[i]) for i in range(dim))
+        col[(slice(None), slice(None)) + tap] = xp[(slice(None), slice(None)) + src]
+    return col.reshape(b, c * int(np.prod(k)), int(np.prod(o)))
+
+
+def unfoldnd_backward(dcol, dim, out_size, kernel_size, dilation=1, padding=0, stride=1):
+    """unfoldnd_backward (cpu/unfoldnd_backward.cpp:323-420): the adjoint of unfoldnd, accumulated in Float32."""
+    k, d, p, s = _ntuple(kernel_size, dim), _ntuple(dilation, dim), _ntuple(padding, dim), _ntuple(stride, dim)
+    size = tuple(out_size)
+    b = dcol.shape[0]
+    c = dcol.shape[1] // int(np.prod(k))
+    o = tuple(conv_out_size(size[i], k[i], s[i], p[i], d[i]) for i in range(dim))
+    dn = dcol.reshape((b, c) + k + o).astype(np.float32)
+    xp = np.zeros((b, c) + tuple(size[i] + 2 * p[i] for i in range(dim)), dtype=np.float32)
+    for tap in np.ndindex(*k):
+        dst = tuple(slice(tap[i] * d[i], tap[i] * d[i] + (o[i] - 1) * s[i] + 1, s[i]) for i in range(dim))
+        xp[(slice(None), slice(None)) + dst] += dn[(slice(None), slice(None)) + tap]
+    return xp[(slice(None), slice(None)) + tuple(slice(p[i], p[i] + size[i]) for i in range(dim))].astype(dcol.dtype)
+
+
+def convnd(x, w, dim, stride=1, padding=0, dilation=1, groups=1, threads=None):
+    """functional::convnd (conv.cpp:177-262): unfoldnd, then matmult(col, w2d, true, true) and the row/col swap,
+    group by group."""
+    xn = x.reshape((-1,) + x.shape[-(dim + 1):])
+    k = tuple(w.shape[-dim:])
+    s, p, d = _ntuple(stride, dim), _ntuple(padding, dim), _ntuple(dilation, dim)
+    o = tuple(conv_out_size(xn.shape[2 + i], k[i], s[i], p[i], d[i]) for i in range(dim))
+    col = unfoldnd(xn, dim, k, d, p, s)
+    cout = w.shape[0]
+    ckg, coutg = col.shape[1] // groups, cout // groups
+    outs = []
+    for g in range(groups):
+        col_g = np.ascontiguousarray(col[:, g * ckg:(g + 1) * ckg])
+        w2d = np.ascontiguousarray(w[g * coutg:(g + 1) * coutg].reshape(coutg, -1))
+        outs.append(matmult(col_g, w2d, True, True, threads=threads).transpose(0, 2, 1))
+    return np.ascontiguousarray(np.concatenate(outs, axis=1)).reshape((xn.shape[0], cout) + o)
+
+
+def convnd_backward(x, w, grad, dim, stride=1, padding=0, dilation=1, groups=1, threads=None):
+    """conv_dimage / conv_dkernel, general dimension (conv.cpp:378-410, 501-560), Float32."""
+    xn = x.reshape((-1,) + x.shape[-(dim + 1):])
+    k = tuple(w.shape[-dim:])
+    s, p, d = _ntuple(stride, dim), _ntuple(padding, dim), _ntuple(dilation, dim)
+    bsz, cout = xn.shape[0], w.shape[0]
+    col = unfoldnd(xn, dim, k, d, p, s)
+    g3 = np.ascontiguousarray(grad.reshape(bsz, cout, -1))
+    ckg, coutg = col.shape[1] // groups, cout // groups
+    dcol = np.empty_like(col)
+    dw = np.empty((cout, ckg), dtype=np.float32)
+    for g in range(groups):
+        w2d = np.ascontiguousarray(w[g * coutg:(g + 1) * coutg].reshape(coutg, -1))
+        gg = np.ascontiguousarray(g3[:, g * coutg:(g + 1) * coutg])
+        dcol[:, g * ckg:(g + 1) * ckg] = matmult(w2d, gg, True, False, threads=threads)
+        col_g = np.ascontiguousarray(col[:, g * ckg:(g + 1) * ckg])
+        dw[g * coutg:(g + 1) * coutg] = matmult(gg, col_g, False, True, threads=threads).sum(axis=0, dtype=np.float32)
+    dx = unfoldnd_backward(dcol, dim, xn.shape[2:], k, d, p, s).reshape(x.shape)
+    return dx, dw.reshape(w.shape)
+
+
+def conv_transposend(x, w, dim, stride=1, padding=0, output_padding=0, dilation=1, groups=1, threads=None):
+    """functional::conv_transposend (conv.cpp:747-860): dilate the input by the stride, pad the end by
+    output_padding, convolve with stride 1 and padding d*(k-1) - p by the channel-swapped, flipped kernel."""
+    s, p, op, d = _ntuple(stride, dim), _ntuple(padding, dim), _ntuple(output_padding, dim), _ntuple(dilation, dim)
+    xn = x.reshape((-1,) + x.shape[-(dim + 1):])
+    bsz, cin = xn.shape[:2]
+    k = tuple(w.shape[-dim:])
+    ext = tuple((xn.shape[2 + i] - 1) * s[i] + 1 + op[i] for i in range(dim))
+    xd = np.zeros((bsz, cin) + ext, dtype=x.dtype)
+    xd[(slice(None), slice(None)) + tuple(slice(0, (xn.shape[2 + i] - 1) * s[i] + 1, s[i]) for i in range(dim))] = xn
+    cing, coutg = cin // groups, w.shape[1]
+    wf = np.empty((coutg * groups, cing) + k, dtype=w.dtype)
+    flip = (slice(None), slice(None)) + (slice(None, None, -1),) * dim
+    for g in range(groups):
+        blk = w[g * cing:(g + 1) * cing]
+        wf[g * coutg:(g + 1) * coutg] = np.swapaxes(blk, 0, 1)[flip]
+    pad = tuple(d[i] * (k[i] - 1) - p[i] for i in range(dim))
+    return convnd(xd, np.ascontiguousarray(wf), dim, 1, pad, d, groups=groups, threads=threads)
+
+
 def conv1d(x, w, stride=1, padding=0, dilation=1, groups=1, threads=None):
     """functional::conv1d (conv.cpp:13-67): unfold1d + matmult, i.e. the one-row case of conv2d."""
     x3 = x.reshape((-1,) + x.shape[-2:])

@@ -196,3 +196,136 @@ def test_grouped_errors(api):
         api.conv2d(x, torch.zeros((4, 3, 3, 3), device="cuda"), groups=3)       # kernel channels * groups != channels
     with pytest.raises(ValueError):
         api.conv_transpose2d(x, torch.zeros((6, 2, 3, 3), device="cuda"), stride=1, output_padding=1)
+
+
+# ---------------------------------------------------------------------------------------------- convnd
+def _direct_convnd(x, w, dim, s, p, d, groups):
+    """Definition of the N-D cross-correlation, summed in float64 tap by tap: the check of the column-matrix chain."""
+    b, c = x.shape[:2]
+    cout, cg = w.shape[:2]
+    k = w.shape[2:]
+    size = x.shape[2:]
+    o = tuple((size[i] + 2 * p[i] - d[i] * (k[i] - 1) - 1) // s[i] + 1 for i in range(dim))
+    xp = np.zeros((b, c) + tuple(size[i] + 2 * p[i] for i in range(dim)))
+    xp[(slice(None), slice(None)) + tuple(slice(p[i], p[i] + size[i]) for i in range(dim))] = x
+    out = np.zeros((b, cout) + o)
+    coutg = cout // groups
+    for gi in range(groups):
+        for tap in np.ndindex(*k):
+            src = tuple(slice(tap[i] * d[i], tap[i] * d[i] + (o[i] - 1) * s[i] + 1, s[i]) for i in range(dim))
+            patch = xp[(slice(None), slice(gi * cg, (gi + 1) * cg)) + src]            # [b, cg, o...]
+            wt = w[(slice(gi * coutg, (gi + 1) * coutg), slice(None)) + tap]          # [coutg, cg]
+            out[:, gi * coutg:(gi + 1) * coutg] += np.einsum("bc...,oc->bo...", patch, wt.astype(np.float64))
+    return out
+
+
+CONVND_4D = [  # shapes of the reference's own ConvND (N = 4) cases, tests/src/conv_autograd_test.cpp:502-545, spatial extent reduced
+    ((1, 3, 6, 6, 6, 6), (4, 3, 3, 3, 3, 3), dict(stride=1, padding=1, groups=1)),
+    ((1, 4, 5, 5, 5, 5), (4, 2, 3, 3, 3, 3), dict(stride=1, padding=0, groups=2)),
+    ((3, 4, 5, 5, 5, 5), (4, 2, 3, 3, 3, 3), dict(stride=1, padding=0, groups=2)),
+    ((2, 2, 6, 5, 7, 6), (6, 1, 2, 3, 2, 3), dict(stride=(1, 2, 1, 2), padding=(1, 0, 2, 1), dilation=(2, 1, 1, 2), groups=2)),
+]
+
+
+def test_oracle_convnd_equals_the_fixed_rank_oracles(oracle):
+    """unfoldnd in 1, 2 and 3 dimensions is unfold1d / 2d / 3d (the reference's own assertion,
+    tests/src/col_im_tests.cpp:47-83), so convnd there must equal the golden-pinned conv1d / conv2d / conv3d."""
+    rng = np.random.default_rng(3)
+    x3 = rng.standard_normal((2, 4, 7, 6, 5)).astype(np.float32)
+    w3 = rng.standard_normal((6, 2, 3, 2, 3)).astype(np.float32)
+    kw = dict(stride=(1, 2, 1), padding=(1, 0, 2), dilation=(1, 1, 2), groups=2)
+    assert np.array_equal(oracle.convnd(x3, w3, 3, **kw), oracle.conv3d(x3, w3, **kw))
+    g3 = rng.standard_normal(oracle.conv3d(x3, w3, **kw).shape).astype(np.float32)
+    for a, b in zip(oracle.convnd_backward(x3, w3, g3, 3, **kw), oracle.conv3d_backward(x3, w3, g3, **kw)):
+        assert np.array_equal(a, b)
+    x2 = rng.standard_normal((2, 3, 9, 8)).astype(np.float32)
+    w2 = rng.standard_normal((4, 3, 3, 3)).astype(np.float32)
+    assert np.array_equal(oracle.convnd(x2, w2, 2, 2, 1, 1), oracle.conv2d(x2, w2, 2, 1, 1))
+    x1 = rng.standard_normal((2, 4, 19)).astype(np.float32)
+    w1 = rng.standard_normal((6, 2, 3)).astype(np.float32)
+    assert np.array_equal(oracle.convnd(x1, w1, 1, 2, 1, 1, groups=2).reshape(2, 6, -1), oracle.conv1d(x1, w1, 2, 1, 1, groups=2).reshape(2, 6, -1))
+    xt = rng.standard_normal((2, 4, 3, 4, 3)).astype(np.float32)
+    wt = rng.standard_normal((4, 3, 2, 3, 2)).astype(np.float32)
+    kt = dict(stride=(2, 1, 2), padding=(0, 1, 0), output_padding=(1, 0, 1), dilation=1, groups=2)
+    assert np.array_equal(oracle.conv_transposend(xt, wt, 3, **kt), oracle.conv_transpose3d(xt, wt, **kt))
+
+
+@pytest.mark.parametrize("xs,ws,kw", CONVND_4D)
+def test_oracle_convnd_4d_against_the_definition(oracle, xs, ws, kw):
+    rng = np.random.default_rng(5)
+    x = rng.uniform(0, 3, xs).astype(np.float32)
+    w = rng.uniform(0, 3, ws).astype(np.float32)
+    t = lambda v: tuple(v) if isinstance(v, tuple) else (v,) * 4
+    exp = _direct_convnd(x, w, 4, t(kw["stride"]), t(kw["padding"]), t(kw.get("dilation", 1)), kw["groups"])
+    got = oracle.convnd(x, w, 4, **kw)
+    assert got.shape == exp.shape and np.allclose(got, exp, rtol=1e-5, atol=1e-5)
+    # the adjoint identities <conv(x), g> = <x, d_image> = <w, d_kernel> hold for the backward chain
+    grad = rng.uniform(0, 1, got.shape).astype(np.float32)
+    dx, dw = oracle.convnd_backward(x, w, grad, 4, **kw)
+    lhs = float(np.sum(got.astype(np.float64) * grad))
+    assert abs(float(np.sum(x.astype(np.float64) * dx)) - lhs) <= 1e-4 * abs(lhs)
+    assert abs(float(np.sum(w.astype(np.float64) * dw)) - lhs) <= 1e-4 * abs(lhs)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("xs,ws,kw", CONVND_4D + [((1, 3, 16, 16, 16, 16), (4, 3, 3, 3, 3, 3), dict(stride=1, padding=1, groups=1))])
+def test_convnd_4d(api, oracle, xs, ws, kw):
+    """convnd with N = 4 (the reference's ConvND cases, the first at its full 16^4 extent) against the oracle at the
+    reference's allclose tolerance, forward and both gradients."""
+    from gpu_util import dev, host
+    rng = np.random.default_rng(7)
+    x = rng.uniform(0, 3, xs).astype(np.float32)
+    w = rng.uniform(0, 3, ws).astype(np.float32)
+    exp = oracle.convnd(x, w, 4, **kw)
+    got = host(api.convnd(dev(x), dev(w), 4, **kw))
+    assert close(got, exp)
+    grad = rng.uniform(0, 1, exp.shape).astype(np.float32)
+    edx, edw = oracle.convnd_backward(x, w, grad, 4, **kw)
+    dx, dw = api.convnd_backward(dev(x), dev(w), dev(grad), 4, **kw)
+    assert close(host(dx), edx) and np.allclose(host(dw), edw, rtol=RTOL, atol=1e-8 * max(1.0, float(np.abs(edw).max())))
+
+
+@pytest.mark.gpu
+def test_convnd_equals_fixed_rank_calls_and_unfoldnd_is_a_gather(api, oracle):
+    """N = 1, 2, 3 give what conv1d / conv2d / conv3d give (tests/src/col_im_tests.cpp:47-117 assert this of unfoldnd),
+    unfoldnd is bit-exact for any geometry, integer images included, and conv_transposend equals conv_transpose3d."""
+    import torch
+    from gpu_util import dev, host, normal
+    rng = np.random.default_rng(11)
+    x3 = normal(rng, (2, 4, 7, 6, 5), np.float32)
+    w3 = normal(rng, (6, 2, 3, 2, 3), np.float32)
+    kw = dict(stride=(1, 2, 1), padding=(1, 0, 2), dilation=(1, 1, 2), groups=2)
+    a, b = host(api.convnd(dev(x3), dev(w3), 3, **kw)), host(api.conv3d(dev(x3), dev(w3), **kw))
+    assert close(a, b) and close(a, oracle.conv3d(x3, w3, **kw))
+    x2 = normal(rng, (2, 3, 9, 8), np.float32)
+    w2 = normal(rng, (4, 3, 3, 3), np.float32)
+    assert close(host(api.convnd(dev(x2), dev(w2), 2, 2, 1, 1)), oracle.conv2d(x2, w2, 2, 1, 1))
+    x1 = normal(rng, (2, 4, 19), np.float32)
+    w1 = normal(rng, (6, 2, 3), np.float32)
+    assert close(host(api.convnd(dev(x1), dev(w1), 1, 2, 1, 1, groups=2)), oracle.conv1d(x1, w1, 2, 1, 1, groups=2).reshape(2, 6, -1))
+    # unfoldnd: a pure gather, any element size
+    x4 = rng.integers(-100, 100, (1, 2, 6, 6, 6, 6)).astype(np.int32)
+    k4, d4, p4, s4 = (3, 3, 3, 3), 1, (1, 1, 1, 1), (1, 1, 2, 2)   # tests/src/col_im_autograd_test.cpp:183-190
+    exp = oracle.unfoldnd(x4, 4, k4, d4, p4, s4)
+    assert np.array_equal(host(api.unfoldnd(dev(x4), 4, k4, d4, p4, s4)), exp)
+    xf = x4.astype(np.float32)
+    col = api.unfoldnd(dev(xf), 4, k4, d4, p4, s4)
+    back = host(api.unfoldnd_backward(col, 4, (6, 6, 6, 6), k4, d4, p4, s4))
+    assert np.array_equal(back, oracle.unfoldnd_backward(exp.astype(np.float32), 4, (6, 6, 6, 6), k4, d4, p4, s4))   # small integers: exact
+    xt = normal(rng, (2, 4, 3, 4, 3), np.float32)
+    wt = normal(rng, (4, 3, 2, 3, 2), np.float32)
+    kt = dict(stride=(2, 1, 2), padding=(0, 1, 0), output_padding=(1, 0, 1), dilation=1, groups=2)
+    got = host(api.conv_transposend(dev(xt), dev(wt), 3, **kt))
+    assert close(got, oracle.conv_transpose3d(xt, wt, **kt))
+    gt = normal(rng, got.shape, np.float32)
+    edx, edw = oracle.conv_transpose3d_backward(xt, wt, gt, **kt)
+    dx, dw = api.conv_transposend_backward(dev(xt), dev(wt), dev(gt), 3, **kt)
+    assert close(host(dx), edx) and np.allclose(host(dw), edw, rtol=1e-5, atol=1e-6)
+    with pytest.raises(ValueError):
+        api.convnd(dev(x3), dev(w3), 0)
+    with pytest.raises(ValueError):
+        api.convnd(dev(x3), dev(w3), 3, stride=0)
+    xh = normal(rng, (2, 16, 4, 5, 4, 5), np.float16)
+    wh = normal(rng, (24, 16, 3, 3, 3, 3), np.float16, (1.0 / (16 * 81)) ** 0.5)
+    goth = host(api.convnd(dev(xh), dev(wh), 4, stride=1, padding=1))
+    assert oracle.rel_fro(goth, oracle.convnd(xh.astype(np.float32), wh.astype(np.float32), 4, 1, 1, 1)) <= 2e-3
