@@ -306,6 +306,8 @@ def main():
         # ---- more than one GPU: the N-sharded MLP step (strong scaling) through the C-ABI partitioner
         if world > 1:
             from neurotensor_b200 import bench_mlp_sharded
+            # measure() agrees between the ranks on every failure it can meet (peer mapping, a flag exchange that
+            # ran out of time) and then times the NCCL gather instead, saying so in the record
             rec = bench_mlp_sharded.measure(rank, world, dist, steps=20, check=True)
             chk = rec.get("check") or {}
             extras["mlp_n_sharded"] = {"workload": "BASELINE.json configs[3]: BFloat16 MLP 8192 x (4096 -> 16384 -> 4096), forward + backward, "
@@ -315,6 +317,8 @@ def main():
                                        "matches_unsharded": bool(chk.get("bit_identical", False)),
                                        "unsharded_ms_per_step_same_gpu": chk.get("unsharded_ms_per_step_same_gpu"),
                                        "strong_scaling_efficiency": chk.get("strong_scaling_efficiency"), "check": chk}
+            if rec.get("fused_gather_unavailable"):
+                extras["mlp_n_sharded"]["fused_gather_unavailable"] = rec["fused_gather_unavailable"]
 
         # ---- the same launch repeated for at least two seconds: what the GPU sustains under its power cap
         barrier()

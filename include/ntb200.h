@@ -195,6 +195,9 @@ int ntb200_peer_release(void* ptr);
  *   ntb200_dist_init             collective over all ranks, with the rank's device current; `exchange` gathers
  *                                `bytes` bytes of every rank, rank-major, into `recv` and returns 0 (may be NULL for one rank).
  *   ntb200_dist_buffer_create    collective: `bytes` on every rank, each block mapped into every rank (zero-filled).
+ *                                Two calls of `exchange`: the 88-byte records, then one status word per rank, so a
+ *                                rank that cannot allocate or map makes the call fail on EVERY rank (nobody is left
+ *                                waiting in a later collective); ntb200_dist_init creates one small buffer this way.
  *   ntb200_dist_gemm_allgather   this rank's column block of C = bias + A.B goes to columns [col0, col0 + n) of the
  *                                gathered [m, gathered_row_stride] matrix in EVERY rank's buffer, stored by the GEMM's
  *                                epilogue, followed by ntb200_dist_barrier on the same stream: when work queued after

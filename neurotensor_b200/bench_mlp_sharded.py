@@ -42,13 +42,38 @@ def measure(rank, world, dist=None, steps=10, batch=8192, din=4096, hidden=16384
             dist.barrier()
         torch.cuda.synchronize()
 
+    def all_ranks(ok):
+        """True when `ok` holds on every rank (one all-reduce, so the ranks take the same branch afterwards)."""
+        if dist is None:
+            return bool(ok)
+        flag = torch.tensor([1 if ok else 0], device="cuda", dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        return bool(flag.item())
+
     fused = (not nccl) and world > 1
+    fused_error = None
     if fused:
-        mlp.enable_fused_gather(B)
+        # peer mappings are made rank by rank; a rank that cannot map a peer must not leave the others waiting in the
+        # first exchange, so the outcome is agreed on and every rank falls back to the NCCL gather together
+        try:
+            mlp.enable_fused_gather(B)
+        except Exception as exc:   # noqa: BLE001 - reported in the record
+            fused_error = "%s: %s" % (type(exc).__name__, exc)
+        if not all_ranks(fused_error is None):
+            fused_error = fused_error or "another rank could not map its peers"
+            fused = False
     step = mlp.step_fused if fused else mlp.step
     for _ in range(warmup):
         loss, grads = step(x, t)
     barrier()
+    if fused and not all_ranks(_lib.lib().ntb200_check_device_status(None) == 0):
+        # a bounded wait of the flag exchange ran out on some rank during the warm-up: time the NCCL gather instead
+        fused_error = "flag exchange timed out during the warm-up: " + _lib.last_error()
+        fused = False
+        step = mlp.step
+        for _ in range(warmup):
+            loss, grads = step(x, t)
+        barrier()
     l0 = _lib.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -124,11 +149,12 @@ def measure(rank, world, dist=None, steps=10, batch=8192, din=4096, hidden=16384
               "gather": ("stores from the GEMM epilogues into peer-mapped buffers + flag exchange (ntb200_dist_gemm_allgather)" if fused
                          else ("none" if world == 1 else "NCCL all-gather + re-tile")),
               "check": result_check}
+    if fused_error:
+        record["fused_gather_unavailable"] = fused_error
     if phase_ms is not None:
         record["phase_ms_rank%d" % rank] = phase_ms
-    if fused:
-        barrier()
-        mlp.close()
+    barrier()
+    mlp.close()
     return record
 
 

@@ -165,13 +165,17 @@ int ntb200_dist_buffer_create(ntb200_dist_comm* comm, size_t bytes, ntb200_dist_
     ntb200_dist_buffer* b = new ntb200_dist_buffer();
     b->comm = comm;
     b->bytes = bytes;
+    // Every rank makes the same two exchanges whatever happens to it: a rank that cannot allocate or cannot map a peer
+    // says so in the second one, and then all ranks fail together instead of one leaving the others in a collective.
     void* local = nullptr;
     cudaError_t e = cudaMalloc(&local, bytes);
     if (e == cudaSuccess) e = cudaMemset(local, 0, bytes);
+    int rc = NTB200_OK;
     if (e != cudaSuccess) {
         if (local) cudaFree(local);
-        delete b;
-        return cuda_fail(e, "dist_buffer_create: cudaMalloc");
+        local = nullptr;
+        rc = cuda_fail(e, "dist_buffer_create: cudaMalloc");
+        if (comm->world == 1) { delete b; return rc; }
     }
     b->base[comm->rank] = local;
     if (comm->world == 1) { *out = b; return NTB200_OK; }
@@ -181,19 +185,22 @@ int ntb200_dist_buffer_create(ntb200_dist_comm* comm, size_t bytes, ntb200_dist_
     mine.address = reinterpret_cast<uint64_t>(local);
     cudaIpcMemHandle_t h;
     static_assert(sizeof(h) == 64, "IPC handle size");
-    e = cudaIpcGetMemHandle(&h, local);
-    if (e == cudaSuccess) std::memcpy(mine.ipc, &h, 64);
-    else (void)cudaGetLastError();                       // ranks inside one process do not need the handle
+    if (local) {
+        e = cudaIpcGetMemHandle(&h, local);
+        if (e == cudaSuccess) std::memcpy(mine.ipc, &h, 64);
+        else (void)cudaGetLastError();                   // ranks inside one process do not need the handle
+    }
     std::vector<BufferBlob> all(size_t(comm->world));
-    int rc = comm->exchange(comm->ctx, &mine, all.data(), sizeof(BufferBlob));
-    if (rc != 0) {
-        cudaFree(local);
+    const int xrc = comm->exchange(comm->ctx, &mine, all.data(), sizeof(BufferBlob));
+    if (xrc != 0) {                                      // the transport itself failed: nothing more can be agreed on
+        if (local) cudaFree(local);
         delete b;
-        return fail(NTB200_ERR_INVALID_ARG, "dist_buffer_create: the all-gather callback failed with %d", rc);
+        return fail(NTB200_ERR_INVALID_ARG, "dist_buffer_create: the all-gather callback failed with %d", xrc);
     }
     for (int r = 0; r < comm->world && rc == NTB200_OK; ++r) {
         if (r == comm->rank) continue;
         const BufferBlob& o = all[size_t(r)];
+        if (o.address == 0) break;                       // that rank has no block; it reports the failure below
         if (o.pid == mine.pid) {                         // a thread of this process: plain peer access
             if (o.device != comm->device) {
                 e = cudaDeviceEnablePeerAccess(o.device, 0);
@@ -211,12 +218,19 @@ int ntb200_dist_buffer_create(ntb200_dist_comm* comm, size_t bytes, ntb200_dist_
             b->ipc[r] = true;
         }
     }
-    if (rc != NTB200_OK) {
+    int32_t status = rc, statuses[kMaxRanks] = {0, 0, 0, 0, 0, 0, 0, 0};
+    const int yrc = comm->exchange(comm->ctx, &status, statuses, sizeof(int32_t));
+    int failed_rank = -1;
+    for (int r = 0; r < comm->world && failed_rank < 0; ++r)
+        if (statuses[r] != NTB200_OK) failed_rank = r;
+    if (rc != NTB200_OK || yrc != 0 || failed_rank >= 0) {
         for (int r = 0; r < comm->world; ++r)
             if (b->ipc[r] && b->base[r]) cudaIpcCloseMemHandle(b->base[r]);
-        cudaFree(local);
+        if (local) cudaFree(local);
         delete b;
-        return rc;
+        if (rc != NTB200_OK) return rc;                  // this rank's own error text stands
+        if (yrc != 0) return fail(NTB200_ERR_INVALID_ARG, "dist_buffer_create: the all-gather callback failed with %d", yrc);
+        return fail(statuses[failed_rank], "dist_buffer_create: rank %d could not allocate or map its peers", failed_rank);
     }
     *out = b;
     return NTB200_OK;

@@ -402,10 +402,17 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, uint32_t tmem
 // read with the thread's own 16-byte loads); the fused ReLU output is a second sub-tile and a second store.
 // `staging` is this warp's 16 KB = four 4 KB sub-tile buffers; a buffer is rewritten only after the store that
 // last used it has finished reading it.
-template <int BN>
+// `extra.apply<parity>(v, cc)` may change the 32 accumulator values of chunk cc before they are converted (K slices of a
+// cluster add the other slices' partial sums there; parity = cc & 1, a constant, for hooks that keep one register set
+// per parity); the default does nothing.
+struct NoExtra {
+    template <int kParity> __device__ __forceinline__ void apply(uint32_t (&)[32], int) const {}
+};
+
+template <int BN, class Extra = NoExtra>
 __device__ __forceinline__ void epilogue_tile_tma(const UmmaParams& p, const CUtensorMap* tma_c, const CUtensorMap* tma_relu,
                                                   const PeerMaps* peers, uint32_t tmem_acc, uint32_t staging, int b, int row0,
-                                                  int lane, int n0) {
+                                                  int lane, int n0, const Extra extra = Extra()) {
     const int row = row0 + lane;
     const bool row_ok = row < p.m;
     const bool i8 = p.out_kind == kOutI8;
@@ -544,10 +551,14 @@ __device__ __forceinline__ void epilogue_tile_tma(const UmmaParams& p, const CUt
         if (n0 + cc * 32 >= p.n) break;  // uniform across the CTA
         tmem_ld_wait();
         tmem_ld_32x32b_x32(tmem_acc + uint32_t((cc + 1) * 32), vb);
+        extra.template apply<0>(va, cc);
         process(va, cc);
         tmem_ld_wait();
         if (cc + 2 < kChunks) tmem_ld_32x32b_x32(tmem_acc + uint32_t((cc + 2) * 32), va);
-        if (n0 + (cc + 1) * 32 < p.n) process(vb, cc + 1);
+        if (n0 + (cc + 1) * 32 < p.n) {
+            extra.template apply<1>(vb, cc + 1);
+            process(vb, cc + 1);
+        }
     }
     tmem_ld_wait();
 }
@@ -1060,6 +1071,8 @@ struct ClusterKParams {
     int pitch;             // floats per row of a partial tile in shared memory (BN + 4)
     int rows_live;         // rows of a tile that can hold results (min(128, m)), rounded up to 32
     int c_wide_ok;         // C and its rows are 8-byte aligned: four results leave in one store
+    float* exchange;       // pair clusters: scratch the partial tiles cross the K slices through (L2-resident); null = distributed shared memory
+    int c_tma_ok;          // pair clusters: C can be written by TMA stores (16-byte aligned rows), see plan_store
 };
 
 __device__ __forceinline__ float4 ld_cluster_f4(uint32_t local_addr, uint32_t cta_rank) {
@@ -1090,12 +1103,13 @@ __device__ __forceinline__ void cluster_reduce_store(const UmmaParams& p, const 
                                                      uint32_t rank_stride, int my_slice) {
     const int groups = cols_mine >> 2;
     const int items = rows * groups;
-    for (int base = threadIdx.x; base < items; base += kThreads * U) {
+    const int threads = int(blockDim.x);
+    for (int base = threadIdx.x; base < items; base += threads * U) {
         float4 v[U][S];
         int row[U], gcol[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            const int i = base + u * kThreads;
+            const int i = base + u * threads;
             const bool live = i < items;
             row[u] = live ? i / groups : 0;
             gcol[u] = live ? (i - row[u] * groups) * 4 + col_first : col_first;
@@ -1106,7 +1120,7 @@ __device__ __forceinline__ void cluster_reduce_store(const UmmaParams& p, const 
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            const int i = base + u * kThreads;
+            const int i = base + u * threads;
             const int col = n_base + gcol[u];
             if (i >= items || col >= p.n) continue;
             float4 acc = v[u][0];
@@ -1291,6 +1305,80 @@ umma_gemm_cluster_k_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
     }
 }
 
+// Pair clusters, exchange through L2: the epilogue warp of lane quadrant `quad` adds, for the 32-column chunks this CTA
+// owns, its own partial (tensor memory) and the partials the other S - 1 slices left in scratch, in slice order, and
+// writes the sums into the staged tile in shared memory (row pitch cp.pitch floats).  A scratch region holds one CTA's
+// 128 x 256 partial as [quad][chunk][piece][lane] float4: the thread that owns a row writes and reads 16-byte pieces
+// that neighbour its warp's other lanes, so every warp access covers whole 512-byte runs.
+constexpr int kExchangeRegion = 4 * 8 * 8 * 32;   // float4 per CTA
+
+template <int S>
+__device__ __forceinline__ void pair_cluster_sum_chunks(const ClusterKParams& cp, uint32_t tmem_base, float* staged, int quad, int lane,
+                                                        int tile, int slice, uint32_t half) {
+    constexpr int kChunks = 8 / S;
+    const float4* regions = reinterpret_cast<const float4*>(cp.exchange) + size_t(tile) * (2 * S) * kExchangeRegion;
+    float* dst = staged + (quad * 32 + lane) * cp.pitch;
+#pragma unroll
+    for (int i = 0; i < kChunks; ++i) {
+        const int cc = slice * kChunks + i;
+        float4 r[S][8];
+#pragma unroll
+        for (int sl = 0; sl < S; ++sl) {
+            if (sl == slice) continue;
+            const float4* src = regions + size_t(2 * sl + int(half)) * kExchangeRegion + ((quad * 8 + cc) * 8) * 32 + lane;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) r[sl][q] = __ldcg(src + q * 32);
+        }
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(cc * 32), v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const float4 own = make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]), __uint_as_float(v[4 * q + 2]),
+                                           __uint_as_float(v[4 * q + 3]));
+            float4 acc = slice == 0 ? own : r[0][q];
+#pragma unroll
+            for (int sl = 1; sl < S; ++sl) {
+                const float4 t = sl == slice ? own : r[sl][q];
+                acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
+            }
+            *reinterpret_cast<float4*>(dst + cc * 32 + 4 * q) = acc;
+        }
+    }
+}
+
+
+// The same sum as pair_cluster_sum_chunks, as the hook of epilogue_tile_tma: the chunk's own partial arrives in `v`
+// (tensor memory), the other slices' partials are read from scratch, and the slice-ordered sum replaces `v`.
+template <int S>
+struct ExchangeAdd {
+    const float4* regions;   // the 2 S regions of this tile
+    int quad, lane, slice, half, chunk0;
+    template <int kParity> __device__ __forceinline__ void apply(uint32_t (&v)[32], int cc) const {
+        float4 r[S][8];
+#pragma unroll
+        for (int sl = 0; sl < S; ++sl) {
+            if (sl == slice) continue;
+            const float4* src = regions + size_t(2 * sl + half) * kExchangeRegion + ((quad * 8 + chunk0 + cc) * 8) * 32 + lane;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) r[sl][q] = __ldcg(src + q * 32);
+        }
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const float4 own = make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]), __uint_as_float(v[4 * q + 2]),
+                                           __uint_as_float(v[4 * q + 3]));
+            float4 acc = slice == 0 ? own : r[0][q];
+#pragma unroll
+            for (int sl = 1; sl < S; ++sl) {
+                const float4 t = sl == slice ? own : r[sl][q];
+                acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
+            }
+            v[4 * q] = __float_as_uint(acc.x); v[4 * q + 1] = __float_as_uint(acc.y);
+            v[4 * q + 2] = __float_as_uint(acc.z); v[4 * q + 3] = __float_as_uint(acc.w);
+        }
+    }
+};
+
 // ---- K slices of CTA pairs inside one cluster ---------------------------------------------------------------------
 // A few hundred rows against a large weight matrix give fewer 256 x 256 tiles than the GPU has CTA pairs, and an SM
 // takes in operands from L2 at a fixed rate (about 64 bytes per clock), so the time of a tile is its K blocks times
@@ -1301,10 +1389,37 @@ umma_gemm_cluster_k_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
 // cluster barrier the S CTAs that hold the same rows each add one S-th of the columns over all S slices, in slice
 // order, through distributed shared memory; bias and previous C are added, the sum is rounded once and stored.
 // One launch, no partial tile in HBM, reproducible sum order.  One tile per cluster (not persistent).
+// Two slices, two chunks per warp: the other slice's partials of both chunks are requested before the first
+// tensor-memory load is waited for, so the L2 latency is paid once (set r[parity][piece] with load()).
+struct ExchangePair {
+    float4 r[2][8];
+    int slice;
+    __device__ __forceinline__ void load(const float4* regions, int quad, int lane, int half, int chunk0) {
+        const float4* src = regions + size_t(2 * (slice ^ 1) + half) * kExchangeRegion + ((quad * 8 + chunk0) * 8) * 32 + lane;
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+            for (int q = 0; q < 8; ++q) r[c][q] = __ldcg(src + (c * 8 + q) * 32);
+    }
+    template <int kParity> __device__ __forceinline__ void apply(uint32_t (&v)[32], int) const {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const float4 own = make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]), __uint_as_float(v[4 * q + 2]),
+                                           __uint_as_float(v[4 * q + 3]));
+            const float4 oth = r[kParity][q];
+            const float4 first = slice == 0 ? own : oth, second = slice == 0 ? oth : own;   // slice order: 0 then 1
+            v[4 * q] = __float_as_uint(first.x + second.x); v[4 * q + 1] = __float_as_uint(first.y + second.y);
+            v[4 * q + 2] = __float_as_uint(first.z + second.z); v[4 * q + 3] = __float_as_uint(first.w + second.w);
+        }
+    }
+};
+
+constexpr int kPairClusterThreads = 256;   // eight warps, two per lane quadrant; lane 0 of warps 0 and 1 feed and issue the main loop first
+
 template <int kDummy>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kPairClusterThreads, 1)
 umma_gemm_pair_cluster_k_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                                const ClusterKParams cp) {
+                                const __grid_constant__ CUtensorMap tma_c, const ClusterKParams cp) {
     constexpr int BN = 256;
     constexpr int kStages = 6;
     constexpr uint32_t kStageBytes = 2u * kPairOperandBytes;   // per CTA: its 128 rows of A, its 128 columns of B
@@ -1342,6 +1457,7 @@ umma_gemm_pair_cluster_k_kernel(const __grid_constant__ CUtensorMap tma_a, const
         fence_proxy_async_smem();
         tma_prefetch_desc(&tma_a);
         tma_prefetch_desc(&tma_b);
+        if (cp.c_tma_ok) tma_prefetch_desc(&tma_c);
     }
     if (warp == 1) {
         tmem_alloc<2>(smem_u32(const_cast<uint32_t*>(tmem_slot)), BN);
@@ -1415,25 +1531,47 @@ umma_gemm_pair_cluster_k_kernel(const __grid_constant__ CUtensorMap tma_a, const
             }
             if (ok) umma_commit_pair(tfull_bar, pair_mask);
         }
-    } else {
-        // ------------------------------------------------------------------ spill this CTA's 128 x 256 partial tile
-        const int quad = warp & 3;
+    }
+    __syncwarp();   // the other lanes of the producer and MMA warps wait here, without issuing, until their lane 0 is done
+    {
+        // ------------------------------------------------------------------ all eight warps: this CTA's 128 x 256 partial tile
+        // (one tile per cluster, so the epilogue never overlaps a main loop and the two role warps can join it)
+        const int quad = warp & 3, part = warp >> 2;   // two warps per lane quadrant
         bool ok = mbar_wait(tfull_bar, 0, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) {
             if (lane == 0) raise_timeout(abort_flag, 0x35);
         } else {
             tcgen05_fence_after();
-            float* dst = reinterpret_cast<float*>(smem_gen) + (quad * 32 + lane) * cp.pitch;
+            if (cp.exchange) {
+                // the chunks other slices own leave for their owners through L2 (coalesced 16-byte pieces, see above)
+                float4* mine = reinterpret_cast<float4*>(cp.exchange) + (size_t(blockIdx.x) * 4 + quad) * (8 * 8 * 32) + lane;
+                const int chunks_per_slice = 8 / cp.slices;
+                int turn = 0;
 #pragma unroll 1
-            for (int cc = 0; cc < BN / 32; ++cc) {
-                uint32_t v[32];
-                tmem_ld_32x32b_x32(tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(cc * 32), v);
-                tmem_ld_wait();
+                for (int cc = 0; cc < BN / 32; ++cc) {
+                    if (cc / chunks_per_slice == slice) continue;
+                    if ((turn++ & 1) != part) continue;           // the quadrant's two warps take the foreign chunks in turn
+                    uint32_t v[32];
+                    tmem_ld_32x32b_x32(tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(cc * 32), v);
+                    tmem_ld_wait();
 #pragma unroll
-                for (int q = 0; q < 8; ++q)
-                    *reinterpret_cast<float4*>(dst + cc * 32 + 4 * q) =
-                        make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]), __uint_as_float(v[4 * q + 2]), __uint_as_float(v[4 * q + 3]));
+                    for (int q = 0; q < 8; ++q)
+                        __stcg(mine + (cc * 8 + q) * 32,
+                               make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]), __uint_as_float(v[4 * q + 2]), __uint_as_float(v[4 * q + 3])));
+                }
+            } else {
+                float* dst = reinterpret_cast<float*>(smem_gen) + (quad * 32 + lane) * cp.pitch;
+#pragma unroll 1
+                for (int cc = part; cc < BN / 32; cc += 2) {
+                    uint32_t v[32];
+                    tmem_ld_32x32b_x32(tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(cc * 32), v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int q = 0; q < 8; ++q)
+                        *reinterpret_cast<float4*>(dst + cc * 32 + 4 * q) =
+                            make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]), __uint_as_float(v[4 * q + 2]), __uint_as_float(v[4 * q + 3]));
+                }
             }
             tcgen05_fence_before();
         }
@@ -1446,8 +1584,44 @@ umma_gemm_pair_cluster_k_kernel(const __grid_constant__ CUtensorMap tma_a, const
         // the S CTAs with this row half share the tile's 256 columns: this one takes columns [slice, slice + 1) * 256 / S
         const int cols_mine = BN / cp.slices;
         const int rows = max(0, min(128, p.m - m0));
-        if (cp.slices == 2) cluster_reduce_store<2, 8>(p, cp, smem_base, rows, m0, n0_pair, slice * cols_mine, cols_mine, half, 2u, slice);
-        else cluster_reduce_store<4, 4>(p, cp, smem_base, rows, m0, n0_pair, slice * cols_mine, cols_mine, half, 2u, slice);
+        if (cp.exchange && cp.c_tma_ok) {
+            // sums are formed in registers, converted, staged 32 rows x 128 bytes at a time over the idle ring and leave
+            // as TMA stores (whole 128-byte row segments): no copy-out pass
+            {
+                tcgen05_fence_after();
+                const int quad = warp & 3, part = warp >> 2;
+                const float4* regions = reinterpret_cast<const float4*>(cp.exchange) + size_t(tile) * (2 * cp.slices) * kExchangeRegion;
+                const uint32_t staging = smem_base + uint32_t(warp) * 4096u;    // one 32-row x 128-byte sub-tile per warp
+                if (cp.slices == 2) {      // 128 columns: each of the quadrant's two warps takes 64 of them (two chunks)
+                    const int col = slice * cols_mine + part * 64;
+                    ExchangePair ex;
+                    ex.slice = slice;
+                    ex.load(regions, quad, lane, int(half), col / 32);
+                    epilogue_tile_tma<64>(p, &tma_c, &tma_c, nullptr, tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(col), staging, 0,
+                                          m0 + quad * 32, lane, n0_pair + col, ex);
+                } else if (part == 0) {   // 64 columns = one sub-tile: one warp per quadrant
+                    const int col = slice * cols_mine;
+                    epilogue_tile_tma<64>(p, &tma_c, &tma_c, nullptr, tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(col), staging, 0,
+                                          m0 + quad * 32, lane, n0_pair + col, ExchangeAdd<4>{regions, quad, lane, slice, int(half), slice * 2});
+                }
+                if (lane == 0) tma_store_wait_all();
+                tcgen05_fence_before();
+            }
+        } else if (cp.exchange) {
+            if (warp < 4) {
+                tcgen05_fence_after();
+                if (cp.slices == 2) pair_cluster_sum_chunks<2>(cp, tmem_base, reinterpret_cast<float*>(smem_gen), warp & 3, lane, tile, slice, half);
+                else pair_cluster_sum_chunks<4>(cp, tmem_base, reinterpret_cast<float*>(smem_gen), warp & 3, lane, tile, slice, half);
+                tcgen05_fence_before();
+            }
+            __syncthreads();
+            // the staged sums leave with bias, previous C and one rounding, coalesced along the rows
+            cluster_reduce_store<1, 8>(p, cp, smem_base, rows, m0, n0_pair, slice * cols_mine, cols_mine, 0u, 0u, 0);
+        } else if (cp.slices == 2) {
+            cluster_reduce_store<2, 8>(p, cp, smem_base, rows, m0, n0_pair, slice * cols_mine, cols_mine, half, 2u, slice);
+        } else {
+            cluster_reduce_store<4, 4>(p, cp, smem_base, rows, m0, n0_pair, slice * cols_mine, cols_mine, half, 2u, slice);
+        }
     }
     tcgen05_fence_before();
     cluster_sync_all();   // nobody leaves while a neighbour may still read its shared memory or signal its barriers
@@ -2406,7 +2580,7 @@ int pair_cluster_capacity(int slices) {
             (void)cudaGetLastError();
             return 0;
         }
-        v = active_clusters_query(reinterpret_cast<const void*>(kernel), kPairClusterSmem, 2 * slices, kThreads);
+        v = active_clusters_query(reinterpret_cast<const void*>(kernel), kPairClusterSmem, 2 * slices, kPairClusterThreads);
         cached[dev][slices].store(v > 0 ? v : -1, std::memory_order_relaxed);
     }
     return v > 0 ? v : 0;
@@ -2474,10 +2648,22 @@ int launch_f16_pair_cluster_k(const GemmArgs& g, const Planned& pl16, const Pair
     cp.rows_live = 128;
     cp.c_wide_ok = (reinterpret_cast<uintptr_t>(g.c) % 8 == 0 && g.c_rs % 4 == 0) ? 1 : 0;
     if (uint32_t(128 * cp.pitch * 4) > 6u * 2u * kPairOperandBytes) return NTB200_ERR_UNSUPPORTED;   // the partial tile lives in the ring
+    // The partial tiles cross the slices through scratch that stays in L2 (128 KB per CTA, at most one wave of CTAs);
+    // NTB200_PAIR_CLUSTER_DSMEM=1 keeps the exchange through distributed shared memory instead.
+    static const bool dsmem = [] { const char* e = getenv("NTB200_PAIR_CLUSTER_DSMEM"); return e && e[0] == '1'; }();
+    void* exchange = nullptr;
+    if (!dsmem) {
+        const size_t bytes = size_t(p.total_tiles) * 2 * plan.slices * kExchangeRegion * sizeof(float4);
+        if (scratch_acquire(&exchange, bytes, stream) != NTB200_OK) exchange = nullptr;   // the distributed-shared-memory exchange needs none
+    }
+    cp.exchange = static_cast<float*>(exchange);
+    CUtensorMap map_c = maps.a.map;   // a valid map either way; used only when c_tma_ok
+    static const bool copy_out = [] { const char* e = getenv("NTB200_PAIR_CLUSTER_COPY_OUT"); return e && e[0] == '1'; }();
+    cp.c_tma_ok = (exchange && !copy_out && !g_direct_stores && plan_store(g.c, pl16.dt, 2, g.m, g.n, 1, g.c_rs, g.c_bs, &map_c)) ? 1 : 0;
     auto kernel = umma_gemm_pair_cluster_k_kernel<0>;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(unsigned(p.total_tiles * 2 * plan.slices), 1, 1);
-    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.blockDim = dim3(kPairClusterThreads, 1, 1);
     cfg.dynamicSmemBytes = kPairClusterSmem;
     cfg.stream = stream;
     cudaLaunchAttribute attr;
@@ -2487,7 +2673,8 @@ int launch_f16_pair_cluster_k(const GemmArgs& g, const Planned& pl16, const Pair
     attr.val.clusterDim.z = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, maps.a.map, maps.b.map, cp);
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, maps.a.map, maps.b.map, map_c, cp);
+    if (exchange) scratch_release(exchange, stream);
     if (e != cudaSuccess) return cuda_fail(e, "umma_gemm_pair_cluster_k_kernel launch");
     count_launch();
     note_route(g.dtype == NTB200_F16 ? "umma_f16_pairclusterk" : "umma_bf16_pairclusterk");
