@@ -8,6 +8,8 @@
 // shared-memory reads are conflict-free; K is consumed in blocks staged through double-buffered shared
 // memory with the next block prefetched into registers.  No split-K: the k order of every output is
 // ascending, so Float32 results do not depend on the launch geometry.
+#include <cstdlib>
+
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -106,6 +108,8 @@ template <> struct Num<uint16_t> : IntNum<uint16_t, uint32_t> {};
 template <> struct Num<uint32_t> : IntNum<uint32_t, uint32_t> {};
 template <> struct Num<unsigned long long> : IntNum<unsigned long long, unsigned long long> {};
 
+// One CTA per SM by register count (231 registers for Float32).  Holding a thread to 128 registers
+// (__launch_bounds__(256, 2), two CTAs per SM) was measured and is slower: 41.7 against 45.7 TFLOP/s at 4096^3.
 template <class T>
 __global__ void __launch_bounds__(kThreads)
 simt_gemm_kernel(const SimtParams p) {

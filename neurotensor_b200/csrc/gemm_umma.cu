@@ -111,11 +111,33 @@ __device__ __forceinline__ void raise_timeout(volatile uint32_t* abort_flag, uns
     atomicExch(&g_device_status, 0x100u | where);
 }
 
+// n / d for 0 <= n < 2^22 and d >= 1 through the Float32 reciprocal (both are exact as floats, the quotient is off by
+// less than one, one correction step): a quarter of the instructions of an integer division.  Every role of every
+// CTA runs the tile scheduler once per tile, and for tiles with one or two K blocks it was a fifth of the tile's time.
+__device__ __forceinline__ int small_div(int n, int d) {
+    int q = __float2int_rz(__fdividef(__int2float_rn(n), __int2float_rn(d)));
+    const int r = n - q * d;
+    if (r < 0) --q;
+    else if (r >= d) ++q;
+    return q;
+}
+
 __device__ __forceinline__ void tile_coords(const UmmaParams& p, int t, int& b, int& mi, int& ni) {
     const int per_batch = p.tiles_m * p.tiles_n;
+    const int group = p.group_m * p.tiles_n;
+    if (p.total_tiles < (1 << 22)) {
+        b = small_div(t, per_batch);
+        const int r = t - b * per_batch;
+        const int g = small_div(r, group);
+        const int first_m = g * p.group_m;
+        const int gm = min(p.group_m, p.tiles_m - first_m);
+        const int w = r - g * group;
+        ni = small_div(w, gm);
+        mi = first_m + (w - ni * gm);
+        return;
+    }
     b = t / per_batch;
     const int r = t - b * per_batch;
-    const int group = p.group_m * p.tiles_n;
     const int g = r / group;
     const int first_m = g * p.group_m;
     const int gm = min(p.group_m, p.tiles_m - first_m);
@@ -495,8 +517,13 @@ __device__ __forceinline__ void epilogue_tile_tma(const UmmaParams& p, const CUt
                         }
                 }
             }
+            if (p.out_kind == kOutF16) {   // decided once per chunk, not once per pair of values
 #pragma unroll
-            for (int q = 0; q < 16; ++q) w[q] = pack2_bits16(f[2 * q], f[2 * q + 1], p.out_kind);
+                for (int q = 0; q < 16; ++q) w[q] = pack2_bits16(f[2 * q], f[2 * q + 1], kOutF16);
+            } else {
+#pragma unroll
+                for (int q = 0; q < 16; ++q) w[q] = pack2_bits16(f[2 * q], f[2 * q + 1], kOutBF16);
+            }
         }
         const uint32_t row_c = staging + uint32_t(buf_c) * 4096u + uint32_t(lane) * 128u;
         for (int q = 0; q < pieces; ++q) {

@@ -42,6 +42,47 @@ template <> struct Fmt<__nv_bfloat16> {
     static float from_double(double x) { return __bfloat162float(__double2bfloat16(x)); }
 };
 
+// Division and square root for the 16-bit formats.  The sequence to reproduce is the correctly rounded Float32 result,
+// then one rounding to the 16-bit format.  The hardware approximations (two ulps for the division, one for the root)
+// give the same 16-bit value unless the approximate result lies within a few Float32 ulps of a rounding boundary of
+// the 16-bit format (the low kLowBits bits of the Float32 pattern equal to a one followed by zeros); only then, and
+// for results the narrow format holds as subnormals, overflows or NaNs, is the exact instruction issued.  About one
+// element in two thousand (Float16) to ten thousand (BFloat16) takes the exact path; the result is the same always.
+template <typename T> struct Narrow;
+template <> struct Narrow<__half> {
+    static constexpr uint32_t kLowBits = 13;
+    static __device__ __forceinline__ bool plain(float q) { const float a = fabsf(q); return a >= 6.103515625e-05f && a < 65504.f; }   // normal Float16, no overflow
+};
+template <> struct Narrow<__nv_bfloat16> {
+    static constexpr uint32_t kLowBits = 16;
+    static __device__ __forceinline__ bool plain(float q) { const float a = fabsf(q); return a >= 1.17549435e-38f && a < 3.3e38f; }
+};
+template <typename T>
+__device__ __forceinline__ bool far_from_boundary(float q) {
+    constexpr uint32_t mask = (1u << Narrow<T>::kLowBits) - 1u, tie = 1u << (Narrow<T>::kLowBits - 1);
+    const uint32_t low = __float_as_uint(q) & mask;
+    const uint32_t dist = low > tie ? low - tie : tie - low;
+    return dist > 4u && Narrow<T>::plain(q);
+}
+template <typename T>
+__device__ __forceinline__ float div_rounded(float num, float den) {
+    if constexpr (sizeof(T) == 2) {
+        const float a = fabsf(den);
+        const float q = __fdividef(num, den);
+        if (a > 1e-30f && a < 1e30f && far_from_boundary<T>(q)) return Fmt<T>::round(q);
+    }
+    return Fmt<T>::round(__fdiv_rn(num, den));
+}
+template <typename T>
+__device__ __forceinline__ float sqrt_rounded(float x) {
+    if constexpr (sizeof(T) == 2) {
+        float r;
+        asm("sqrt.approx.f32 %0, %1;" : "=f"(r) : "f"(x));
+        if (x > 1e-30f && x < 1e30f && far_from_boundary<T>(r)) return Fmt<T>::round(r);
+    }
+    return Fmt<T>::round(__fsqrt_rn(x));
+}
+
 // std::clamp as the reference's clamp_ applies it (nt/functional/cpu/min_max.cpp:66-101): a NaN stays a NaN
 __device__ __forceinline__ float clip10(float x) { return x < -10.f ? -10.f : (10.f < x ? 10.f : x); }
 
@@ -93,11 +134,11 @@ __device__ __forceinline__ void adam_one(float& p, float g, float& m, float& v, 
     vi = F::round(__fmul_rn(vi, g2));
     m = mi;
     v = vi;
-    const float m_hat = k.corr1 == 1.f ? mi : F::round(__fdiv_rn(mi, k.corr1));
-    const float v_hat = k.corr2 == 1.f ? vi : F::round(__fdiv_rn(vi, k.corr2));
+    const float m_hat = k.corr1 == 1.f ? mi : div_rounded<T>(mi, k.corr1);
+    const float v_hat = k.corr2 == 1.f ? vi : div_rounded<T>(vi, k.corr2);
     const float num = F::round(__fmul_rn(k.lr, m_hat));
-    const float den = F::round(__fadd_rn(F::round(__fsqrt_rn(v_hat)), k.eps));
-    const float u = clip10(F::round(__fdiv_rn(num, den)));
+    const float den = F::round(__fadd_rn(sqrt_rounded<T>(v_hat), k.eps));
+    const float u = clip10(div_rounded<T>(num, den));
     p = F::round(__fsub_rn(p, u));
 }
 

@@ -89,7 +89,7 @@ def test_optimizer_steps_bf16_and_errors(oracle):
     import torch
     from gpu_util import dev, host
     from neurotensor_b200 import _lib, api
-    p, g, m, v = (oracle.bf16_round(x) for x in _inputs(11, 4096, np.float32))      # bf16 bit patterns
+    p, g, m, v = (oracle.bf16_round(x) for x in _inputs(11, 2 ** 18 + 5, np.float32))      # bf16 bit patterns
     pb, gb, mb, vb = (dev(x, bf16=True) for x in (p, g, m, v))
     p32, g32, m32, v32 = (oracle.bf16_widen(x) for x in (p, g, m, v))
     api.adam_step(pb, gb, mb, vb, lr=0.01)
