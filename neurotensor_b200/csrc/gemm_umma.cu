@@ -590,6 +590,45 @@ __device__ __forceinline__ void epilogue_tile_tma(const UmmaParams& p, const CUt
     tmem_ld_wait();
 }
 
+// The same for the commonest case and one 64-column sub-tile: a 16-bit C with nothing fused (no bias, previous C,
+// mask, second output or peer copy).  Used by the sixteen-warp instantiation, whose 96 registers per thread do not
+// hold two chunks in flight without spilling: one chunk at a time (the quadrant's other warps cover the tensor-memory
+// latency), no run-time choices inside the chunk, one TMA store.
+__device__ __forceinline__ void epilogue_plain64(const UmmaParams& p, const CUtensorMap* tma_c, uint32_t tmem_acc, uint32_t staging,
+                                                 int b, int row0, int lane, int n0) {
+    if (n0 >= p.n) return;   // uniform across the CTA
+    if (lane == 0) tma_store_wait_read();
+    __syncwarp();
+    const uint32_t row_c = staging + uint32_t(lane) * 128u;
+#pragma unroll
+    for (int cc = 0; cc < 2; ++cc) {
+        if (n0 + cc * 32 >= p.n) break;   // C ends inside the sub-tile: the store clips the rest
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tmem_acc + uint32_t(cc * 32), v);
+        tmem_ld_wait();
+        uint32_t w[16];
+        if (p.out_kind == kOutF16) {
+#pragma unroll
+            for (int q = 0; q < 16; ++q) w[q] = pack2_bits16(__uint_as_float(v[2 * q]), __uint_as_float(v[2 * q + 1]), kOutF16);
+        } else {
+#pragma unroll
+            for (int q = 0; q < 16; ++q) w[q] = pack2_bits16(__uint_as_float(v[2 * q]), __uint_as_float(v[2 * q + 1]), kOutBF16);
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const uint32_t chunk = uint32_t(cc * 4 + q) ^ uint32_t(lane & 7);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_c + (chunk << 4)), "r"(w[4 * q]), "r"(w[4 * q + 1]),
+                         "r"(w[4 * q + 2]), "r"(w[4 * q + 3]) : "memory");
+        }
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+        tma_store_3d(tma_c, staging, n0, row0, b);
+        tma_store_commit();
+    }
+}
+
 template <MmaKind kKind, int BN, bool kSplit>
 __global__ void __launch_bounds__(kSplit ? kThreadsSplit : kThreads, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
@@ -1033,7 +1072,13 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
             tcgen05_fence_after();
             if constexpr (!kSplit && kEpi == 16) {
                 const int quarter = (warp - 2) >> 2;   // four warps per lane quadrant, 64 columns (one 128-byte sub-tile) each
-                if (p.tma_store)
+                const bool plain = p.tma_store && !p.bias && !p.accumulate && !p.has_mask && !p.has_relu_out && p.n_peers == 0 &&
+                                   p.out_kind != kOutI8;
+                if (plain)
+                    epilogue_plain64(p, &tma_c, tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN + quarter * 64),
+                                     staging_base + uint32_t(warp - 2) * 4096u, b, mi * 256 + int(rank) * 128 + quad * 32, lane,
+                                     ni * BN + quarter * 64);
+                else if (p.tma_store)
                     epilogue_tile_tma<64>(p, &tma_c, &tma_relu, &tma_peers,
                                           tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN + quarter * 64),
                                           staging_base + uint32_t(warp - 2) * 4096u, b, mi * 256 + int(rank) * 128 + quad * 32,

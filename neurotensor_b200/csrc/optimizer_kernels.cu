@@ -43,42 +43,40 @@ template <> struct Fmt<__nv_bfloat16> {
 };
 
 // Division and square root for the 16-bit formats.  The sequence to reproduce is the correctly rounded Float32 result,
-// then one rounding to the 16-bit format.  The hardware approximations (two ulps for the division, one for the root)
-// give the same 16-bit value unless the approximate result lies within a few Float32 ulps of a rounding boundary of
-// the 16-bit format (the low kLowBits bits of the Float32 pattern equal to a one followed by zeros); only then, and
-// for results the narrow format holds as subnormals, overflows or NaNs, is the exact instruction issued.  About one
-// element in two thousand (Float16) to ten thousand (BFloat16) takes the exact path; the result is the same always.
-template <typename T> struct Narrow;
-template <> struct Narrow<__half> {
-    static constexpr uint32_t kLowBits = 13;
-    static __device__ __forceinline__ bool plain(float q) { const float a = fabsf(q); return a >= 6.103515625e-05f && a < 65504.f; }   // normal Float16, no overflow
-};
-template <> struct Narrow<__nv_bfloat16> {
-    static constexpr uint32_t kLowBits = 16;
-    static __device__ __forceinline__ bool plain(float q) { const float a = fabsf(q); return a >= 1.17549435e-38f && a < 3.3e38f; }
-};
+// then one rounding to the 16-bit format (which, Float32 having more than twice the 16-bit formats' precision plus
+// two bits, is the correctly rounded 16-bit result of the operation).  The hardware approximations are within two
+// ulps (division) and one ulp (root) of the exact Float32 result, so whenever the approximation moved four ulps down
+// and four ulps up rounds to one and the same 16-bit value, that value is the answer: rounding is monotonic and the
+// exact result lies in between.  Otherwise (the approximation sits next to a rounding boundary of the narrow format:
+// one element in a few thousand; or it is a NaN, or so small that the approximation itself may flush) the exact
+// instruction is issued.  The result is the same always; subnormal 16-bit results take the fast path too.
 template <typename T>
-__device__ __forceinline__ bool far_from_boundary(float q) {
-    constexpr uint32_t mask = (1u << Narrow<T>::kLowBits) - 1u, tie = 1u << (Narrow<T>::kLowBits - 1);
-    const uint32_t low = __float_as_uint(q) & mask;
-    const uint32_t dist = low > tie ? low - tie : tie - low;
-    return dist > 4u && Narrow<T>::plain(q);
+__device__ __forceinline__ bool settled(float q, float& rounded) {
+    const uint32_t bits = __float_as_uint(q);
+    const float lo = Fmt<T>::round(__uint_as_float(bits - 4u)), hi = Fmt<T>::round(__uint_as_float(bits + 4u));
+    rounded = hi;
+    return lo == hi && fabsf(q) > 1e-36f;   // false for NaNs; an approximation of a Float32 subnormal is not trusted
 }
 template <typename T>
 __device__ __forceinline__ float div_rounded(float num, float den) {
     if constexpr (sizeof(T) == 2) {
         const float a = fabsf(den);
-        const float q = __fdividef(num, den);
-        if (a > 1e-30f && a < 1e30f && far_from_boundary<T>(q)) return Fmt<T>::round(q);
+        if (a > 1e-30f && a < 1e30f) {
+            if (num == 0.f) return __fdiv_rn(num, den) ;            // a signed zero: exact and cheap enough
+            float r;
+            if (settled<T>(__fdividef(num, den), r)) return r;
+        }
     }
     return Fmt<T>::round(__fdiv_rn(num, den));
 }
 template <typename T>
 __device__ __forceinline__ float sqrt_rounded(float x) {
     if constexpr (sizeof(T) == 2) {
-        float r;
-        asm("sqrt.approx.f32 %0, %1;" : "=f"(r) : "f"(x));
-        if (x > 1e-30f && x < 1e30f && far_from_boundary<T>(r)) return Fmt<T>::round(r);
+        if (x > 1e-30f && x < 1e30f) {
+            float q, r;
+            asm("sqrt.approx.f32 %0, %1;" : "=f"(q) : "f"(x));
+            if (settled<T>(q, r)) return r;
+        }
     }
     return Fmt<T>::round(__fsqrt_rn(x));
 }
@@ -142,6 +140,48 @@ __device__ __forceinline__ void adam_one(float& p, float g, float& m, float& v, 
     p = F::round(__fsub_rn(p, u));
 }
 
+// Eight 16-bit elements at once.  Every product and sum of the update is one correctly rounded operation in the
+// tensor's own format, which is exactly what the packed hardware instructions deliver (the _rn forms are never
+// contracted into an FMA); only the root and the two divisions go through Float32, lane by lane.
+template <typename T> struct Packed;
+template <> struct Packed<__half> {
+    using T2 = __half2;
+    static __device__ __forceinline__ T2 make(float x) { return __float2half2_rn(x); }
+    static __device__ __forceinline__ float lo(T2 v) { return __low2float(v); }
+    static __device__ __forceinline__ float hi(T2 v) { return __high2float(v); }
+    static __device__ __forceinline__ T2 pack(float a, float b) { return __floats2half2_rn(a, b); }
+};
+template <> struct Packed<__nv_bfloat16> {
+    using T2 = __nv_bfloat162;
+    static __device__ __forceinline__ T2 make(float x) { return __float2bfloat162_rn(x); }
+    static __device__ __forceinline__ float lo(T2 v) { return __low2float(v); }
+    static __device__ __forceinline__ float hi(T2 v) { return __high2float(v); }
+    static __device__ __forceinline__ T2 pack(float a, float b) { return __floats2bfloat162_rn(a, b); }
+};
+
+template <typename T>
+__device__ __forceinline__ void adam_pair(typename Packed<T>::T2& p, typename Packed<T>::T2 g, typename Packed<T>::T2& m,
+                                          typename Packed<T>::T2& v, const AdamScalars& k) {
+    using P = Packed<T>;
+    using T2 = typename P::T2;
+    T2 mi = __hmul2_rn(m, P::make(k.beta1));
+    mi = __hadd2_rn(mi, P::make(k.one_minus_beta1));
+    mi = __hmul2_rn(mi, g);
+    const T2 g2 = __hmul2_rn(g, g);
+    T2 vi = __hmul2_rn(v, P::make(k.beta2));
+    vi = __hadd2_rn(vi, P::make(k.one_minus_beta2));
+    vi = __hmul2_rn(vi, g2);
+    m = mi;
+    v = vi;
+    const T2 m_hat = k.corr1 == 1.f ? mi : P::pack(div_rounded<T>(P::lo(mi), k.corr1), div_rounded<T>(P::hi(mi), k.corr1));
+    const T2 v_hat = k.corr2 == 1.f ? vi : P::pack(div_rounded<T>(P::lo(vi), k.corr2), div_rounded<T>(P::hi(vi), k.corr2));
+    const T2 num = __hmul2_rn(P::make(k.lr), m_hat);
+    const T2 root = P::pack(sqrt_rounded<T>(P::lo(v_hat)), sqrt_rounded<T>(P::hi(v_hat)));
+    const T2 den = __hadd2_rn(root, P::make(k.eps));
+    const T2 u = P::pack(clip10(div_rounded<T>(P::lo(num), P::lo(den))), clip10(div_rounded<T>(P::hi(num), P::hi(den))));
+    p = __hsub2_rn(p, u);
+}
+
 template <typename T>
 __global__ void adam_step_kernel(T* __restrict__ param, const T* __restrict__ grad, T* __restrict__ m, T* __restrict__ v,
                                  long long n, AdamScalars k, int vec) {
@@ -155,13 +195,23 @@ __global__ void adam_step_kernel(T* __restrict__ param, const T* __restrict__ gr
         g.raw = reinterpret_cast<const uint4*>(grad)[i];
         mm.raw = reinterpret_cast<const uint4*>(m)[i];
         vv.raw = reinterpret_cast<const uint4*>(v)[i];
+        if constexpr (sizeof(T) == 2) {
+            using T2 = typename Packed<T>::T2;
+            T2* p2 = reinterpret_cast<T2*>(&p.raw);
+            T2* m2 = reinterpret_cast<T2*>(&mm.raw);
+            T2* v2 = reinterpret_cast<T2*>(&vv.raw);
+            const T2* g2 = reinterpret_cast<const T2*>(&g.raw);
 #pragma unroll
-        for (int j = 0; j < kN; ++j) {
-            float pj = F::load(&p.e[j]), mj = F::load(&mm.e[j]), vj = F::load(&vv.e[j]);
-            adam_one<T>(pj, F::load(&g.e[j]), mj, vj, k);
-            F::store(&p.e[j], pj);
-            F::store(&mm.e[j], mj);
-            F::store(&vv.e[j], vj);
+            for (int j = 0; j < kN / 2; ++j) adam_pair<T>(p2[j], g2[j], m2[j], v2[j], k);
+        } else {
+#pragma unroll
+            for (int j = 0; j < kN; ++j) {
+                float pj = F::load(&p.e[j]), mj = F::load(&mm.e[j]), vj = F::load(&vv.e[j]);
+                adam_one<T>(pj, F::load(&g.e[j]), mj, vj, k);
+                F::store(&p.e[j], pj);
+                F::store(&mm.e[j], mj);
+                F::store(&vv.e[j], vj);
+            }
         }
         reinterpret_cast<uint4*>(param)[i] = p.raw;
         reinterpret_cast<uint4*>(m)[i] = mm.raw;
