@@ -77,6 +77,7 @@ struct UmmaParams {
     int has_relu_out, has_mask;
     int shift;                   // kOutU32 / kOutU16: the s32 accumulator is shifted left by this much before it is added
     int tma_store;               // pair kernel, 16-bit outputs: tiles leave through shared memory and TMA stores
+    int lean_ok;                 // pair kernel: a C with nothing fused may take the lean epilogue
     int peers_relu;              // TMA-store epilogue: the peer copies receive the fused ReLU output instead of C
     // Stage geometry of the single-CTA kernel (run-time: a problem with few rows stages only those rows of A and
     // spends the shared memory on more stages instead; the unused rows of the 128-row MMA operand alias whatever follows
@@ -590,42 +591,69 @@ __device__ __forceinline__ void epilogue_tile_tma(const UmmaParams& p, const CUt
     tmem_ld_wait();
 }
 
-// The same for the commonest case and one 64-column sub-tile: a 16-bit C with nothing fused (no bias, previous C,
-// mask, second output or peer copy).  Used by the sixteen-warp instantiation, whose 96 registers per thread do not
-// hold two chunks in flight without spilling: one chunk at a time (the quadrant's other warps cover the tensor-memory
-// latency), no run-time choices inside the chunk, one TMA store.
-__device__ __forceinline__ void epilogue_plain64(const UmmaParams& p, const CUtensorMap* tma_c, uint32_t tmem_acc, uint32_t staging,
-                                                 int b, int row0, int lane, int n0) {
+// The same for the commonest case: a 16-bit C with nothing fused (no bias, previous C, mask, second output or peer
+// copy), NSUB sub-tiles of 64 columns.  Nothing is decided per value and little per chunk, so the warp issues a
+// fraction of the instructions of the general epilogue.  kDouble keeps the next chunk's tensor-memory load in flight
+// during the conversion (two register sets); the sixteen-warp instantiation, whose 96 registers per thread do not
+// hold two chunks without spilling, takes one chunk at a time and lets the quadrant's other warps cover the latency.
+// `staging` is NSUB x 4 KB; a sub-tile is handed to its TMA store as soon as its two chunks are staged.
+template <int NSUB, bool kDouble>
+__device__ __forceinline__ void epilogue_plain(const UmmaParams& p, const CUtensorMap* tma_c, uint32_t tmem_acc, uint32_t staging,
+                                               int b, int row0, int lane, int n0) {
     if (n0 >= p.n) return;   // uniform across the CTA
     if (lane == 0) tma_store_wait_read();
     __syncwarp();
-    const uint32_t row_c = staging + uint32_t(lane) * 128u;
-#pragma unroll
-    for (int cc = 0; cc < 2; ++cc) {
-        if (n0 + cc * 32 >= p.n) break;   // C ends inside the sub-tile: the store clips the rest
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(tmem_acc + uint32_t(cc * 32), v);
-        tmem_ld_wait();
+    constexpr int kChunks = 2 * NSUB;
+    const bool f16 = p.out_kind == kOutF16;
+    auto emit = [&](const uint32_t (&v)[32], int cc) {
         uint32_t w[16];
-        if (p.out_kind == kOutF16) {
+        if (f16) {
 #pragma unroll
             for (int q = 0; q < 16; ++q) w[q] = pack2_bits16(__uint_as_float(v[2 * q]), __uint_as_float(v[2 * q + 1]), kOutF16);
         } else {
 #pragma unroll
             for (int q = 0; q < 16; ++q) w[q] = pack2_bits16(__uint_as_float(v[2 * q]), __uint_as_float(v[2 * q + 1]), kOutBF16);
         }
+        const uint32_t sub = staging + uint32_t(cc >> 1) * 4096u;
+        const uint32_t row_c = sub + uint32_t(lane) * 128u;
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-            const uint32_t chunk = uint32_t(cc * 4 + q) ^ uint32_t(lane & 7);
+            const uint32_t chunk = uint32_t((cc & 1) * 4 + q) ^ uint32_t(lane & 7);
             asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_c + (chunk << 4)), "r"(w[4 * q]), "r"(w[4 * q + 1]),
                          "r"(w[4 * q + 2]), "r"(w[4 * q + 3]) : "memory");
         }
-    }
-    fence_proxy_async_smem();
-    __syncwarp();
-    if (lane == 0) {
-        tma_store_3d(tma_c, staging, n0, row0, b);
-        tma_store_commit();
+        if ((cc & 1) || n0 + (cc + 1) * 32 >= p.n) {   // the sub-tile is complete, or C ends inside it (the store clips)
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                tma_store_3d(tma_c, sub, n0 + (cc >> 1) * 64, row0, b);
+                tma_store_commit();
+            }
+        }
+    };
+    if constexpr (!kDouble) {
+#pragma unroll
+        for (int cc = 0; cc < kChunks; ++cc) {
+            if (n0 + cc * 32 >= p.n) break;
+            uint32_t v[32];
+            tmem_ld_32x32b_x32(tmem_acc + uint32_t(cc * 32), v);
+            tmem_ld_wait();
+            emit(v, cc);
+        }
+    } else {
+        uint32_t va[32], vb[32];
+        tmem_ld_32x32b_x32(tmem_acc, va);
+#pragma unroll
+        for (int cc = 0; cc < kChunks; cc += 2) {
+            if (n0 + cc * 32 >= p.n) break;
+            tmem_ld_wait();
+            tmem_ld_32x32b_x32(tmem_acc + uint32_t((cc + 1) * 32), vb);   // past the last column of C: never used
+            emit(va, cc);
+            tmem_ld_wait();
+            if (cc + 2 < kChunks) tmem_ld_32x32b_x32(tmem_acc + uint32_t((cc + 2) * 32), va);
+            if (n0 + (cc + 1) * 32 < p.n) emit(vb, cc + 1);
+        }
+        tmem_ld_wait();
     }
 }
 
@@ -1070,14 +1098,15 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
                 break;
             }
             tcgen05_fence_after();
+            // a 16-bit C with nothing fused takes the lean epilogue (NTB200_GENERAL_EPILOGUE=1 sets p.lean_ok to 0)
+            const bool plain = p.tma_store && p.lean_ok && !p.bias && !p.accumulate && !p.has_mask && !p.has_relu_out &&
+                               p.n_peers == 0 && p.out_kind != kOutI8;
             if constexpr (!kSplit && kEpi == 16) {
                 const int quarter = (warp - 2) >> 2;   // four warps per lane quadrant, 64 columns (one 128-byte sub-tile) each
-                const bool plain = p.tma_store && !p.bias && !p.accumulate && !p.has_mask && !p.has_relu_out && p.n_peers == 0 &&
-                                   p.out_kind != kOutI8;
                 if (plain)
-                    epilogue_plain64(p, &tma_c, tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN + quarter * 64),
-                                     staging_base + uint32_t(warp - 2) * 4096u, b, mi * 256 + int(rank) * 128 + quad * 32, lane,
-                                     ni * BN + quarter * 64);
+                    epilogue_plain<1, false>(p, &tma_c, tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN + quarter * 64),
+                                             staging_base + uint32_t(warp - 2) * 4096u, b, mi * 256 + int(rank) * 128 + quad * 32, lane,
+                                             ni * BN + quarter * 64);
                 else if (p.tma_store)
                     epilogue_tile_tma<64>(p, &tma_c, &tma_relu, &tma_peers,
                                           tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN + quarter * 64),
@@ -1088,7 +1117,11 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
                                       mi * 256 + row_in_tile, ni * BN + quarter * 64);
             } else if constexpr (!kSplit && kEpi == 8) {
                 const int half = (warp - 2) >> 2;   // warps 2-5: columns 0-127, warps 6-9: columns 128-255
-                if (p.tma_store)
+                if (plain)
+                    epilogue_plain<2, true>(p, &tma_c, tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN + half * 128),
+                                            staging_base + uint32_t(warp - 2) * 8192u, b, mi * 256 + int(rank) * 128 + quad * 32, lane,
+                                            ni * BN + half * 128);
+                else if (p.tma_store)
                     epilogue_tile_tma<128>(p, &tma_c, &tma_relu, &tma_peers,
                                            tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN + half * 128),
                                            staging_base + uint32_t(warp - 2) * 8192u, b, mi * 256 + int(rank) * 128 + quad * 32,
@@ -1097,7 +1130,11 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
                     epilogue_tile<128>(p, tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN + half * 128), b,
                                        mi * 256 + row_in_tile, ni * BN + half * 128);
             } else if constexpr (!kSplit) {
-                if (p.tma_store)
+                if (plain)
+                    epilogue_plain<BN / 64, true>(p, &tma_c, tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN),
+                                                  staging_base + uint32_t(quad) * 16384u, b, mi * 256 + int(rank) * 128 + quad * 32, lane,
+                                                  ni * BN);
+                else if (p.tma_store)
                     epilogue_tile_tma<BN>(p, &tma_c, &tma_relu, &tma_peers, tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN),
                                           staging_base + uint32_t(quad) * 16384u, b, mi * 256 + int(rank) * 128 + quad * 32,
                                           lane, ni * BN);
@@ -2207,6 +2244,8 @@ int launch_planned(const GemmArgs& g, const Planned& pl, const Side& a, const Si
         p.peers_relu = peers_relu ? 1 : 0;
         if (ok && g.mask_src) ok = reinterpret_cast<uintptr_t>(g.mask_src) % 16 == 0;
         p.tma_store = ok ? 1 : 0;
+        static const bool general_only = [] { const char* e = getenv("NTB200_GENERAL_EPILOGUE"); return e && e[0] == '1'; }();
+        p.lean_ok = general_only ? 0 : 1;
     }
     if (!p.tma_store && g.relu_out && ((g.relu_rs && g.relu_rs != g.c_rs) || g.peers_get_relu))
         return fail(NTB200_ERR_UNSUPPORTED,
