@@ -387,7 +387,7 @@ int ntb200_convnd_backward_kernel(int dtype, const void* x, const void* grad, vo
  *   - A problem whose column matrix (ntb200_conv2d_workspace_bytes) is larger than the array is refused with
  *     NTB200_ERR_INVALID_ARG and a message naming both sizes; nothing is launched.
  *   - The first call on each device looks up the array's device address (one cudaGetSymbolAddress with that
- *     device current); make that first call before starting any stream capture.  With CUDA's lazy module loading
+ *     device current).  With CUDA's lazy module loading
  *     (the default) the runtime also creates the array's 32 MiB of device storage at that moment, which fails with
  *     NTB200_ERR_ALLOC if the application has already taken the whole heap: make the first call (any tiny valid
  *     problem) before that, or run with CUDA_MODULE_LOADING=EAGER so the storage exists from library load on.
