@@ -404,7 +404,10 @@ def test_few_rows_stream_the_weights(api, oracle, L, m, weights_nk, bf16):
 @pytest.mark.gpu
 @pytest.mark.parametrize("bf16", [False, True])
 @pytest.mark.parametrize("m,n,k,weights_nk", [(3, 4096, 4096, False), (16, 4100, 4096, True), (100, 4096, 8192, False),
-                                              (128, 8192, 4096, True), (256, 2048, 8192, False), (300, 2048, 8192, True)])
+                                              (128, 8192, 4096, True), (256, 2048, 8192, False), (300, 2048, 8192, True),
+                                              (512, 4096, 4096, False),     # two pairs per tile (S = 2)
+                                              (300, 2052, 8192, True),      # rows of C not 16-byte aligned: no TMA store, copy-out pass
+                                              (260, 2050, 4096, True)])     # rows of C not 8-byte aligned: scalar stores
 def test_few_rows_split_the_k_axis(api, oracle, L, m, n, k, weights_nk, bf16):
     """A few rows (or a few hundred against a deep, narrow weight matrix) of 16-bit floats: K is cut into slices that run
     side by side as fp32 partial tiles, and a second kernel adds them, the bias and the previous C and rounds once."""
@@ -436,6 +439,37 @@ def test_few_rows_split_the_k_axis(api, oracle, L, m, n, k, weights_nk, bf16):
     both = api.matmult(x, w)
     assert L.last_route() in split_routes
     assert oracle.rel_fro(dec(both)[:, : n // 2], dec(half)) <= 1e-3
+
+
+@pytest.mark.gpu
+def test_pair_cluster_exchange_variants_agree_bit_for_bit():
+    """The K slices of a pair cluster are summed in slice order whichever way the partial tiles travel (L2 scratch and
+    TMA stores, L2 scratch and the copy-out pass, distributed shared memory): the three give identical bits.  The
+    switches are read once per process, so each variant runs in a process of its own."""
+    import os
+    import subprocess
+    import sys
+    from conftest import ROOT
+    code = (
+        "import sys, torch, hashlib\n"
+        "sys.path.insert(0, %r)\n"
+        "from neurotensor_b200 import _lib, api\n"
+        "g = torch.Generator(device='cuda').manual_seed(5)\n"
+        "out = []\n"
+        "for (m, k, n) in ((512, 4096, 4096), (300, 8192, 2048)):\n"
+        "    a = (torch.randn((m, k), generator=g, device='cuda') * 0.5).half()\n"
+        "    b = (torch.randn((k, n), generator=g, device='cuda') * 0.5).half()\n"
+        "    bias = torch.randn((n,), generator=g, device='cuda').half()\n"
+        "    c = api.linear(a, b, bias)\n"
+        "    assert _lib.last_route() == 'umma_f16_pairclusterk', _lib.last_route()\n"
+        "    out.append(hashlib.sha256(c.cpu().numpy().tobytes()).hexdigest())\n"
+        "print(' '.join(out))\n" % ROOT)
+    digests = {}
+    for name, env in (("l2+tma", {}), ("l2+copy-out", {"NTB200_PAIR_CLUSTER_COPY_OUT": "1"}), ("dsmem", {"NTB200_PAIR_CLUSTER_DSMEM": "1"})):
+        r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600, env=dict(os.environ, **env))
+        assert r.returncode == 0, name + ": " + r.stderr[-2000:]
+        digests[name] = r.stdout.strip().splitlines()[-1]
+    assert len(set(digests.values())) == 1, digests
 
 
 def test_pinned_host_buffers_from_the_library(api, oracle, L):
