@@ -108,8 +108,10 @@ template <> struct Num<uint16_t> : IntNum<uint16_t, uint32_t> {};
 template <> struct Num<uint32_t> : IntNum<uint32_t, uint32_t> {};
 template <> struct Num<unsigned long long> : IntNum<unsigned long long, unsigned long long> {};
 
-// One CTA per SM by register count (231 registers for Float32).  Holding a thread to 128 registers
-// (__launch_bounds__(256, 2), two CTAs per SM) was measured and is slower: 41.7 against 45.7 TFLOP/s at 4096^3.
+// One CTA per SM by register count (231 registers for Float32).  More warps per SM do not help: holding a thread to
+// 128 registers (__launch_bounds__(256, 2), two CTAs per SM, a few spills) gave 41.7 against 45.7 TFLOP/s at 4096^3,
+// and a Float32-only variant with 64 x 128 tiles, 128 threads and three CTAs per SM at 168 registers (twelve warps,
+// no spills, same chains) gave 43.3 against 44.9 (30.4 against 38.4 at 2048^3).
 template <class T>
 __global__ void __launch_bounds__(kThreads)
 simt_gemm_kernel(const SimtParams p) {
