@@ -316,7 +316,9 @@ def main():
                                        "kernels_per_step": rec["kernels_per_step_rank0"],
                                        "matches_unsharded": bool(chk.get("bit_identical", False)),
                                        "unsharded_ms_per_step_same_gpu": chk.get("unsharded_ms_per_step_same_gpu"),
-                                       "strong_scaling_efficiency": chk.get("strong_scaling_efficiency"), "check": chk}
+                                       "strong_scaling_efficiency": chk.get("strong_scaling_efficiency"), "check": chk,
+                                       "forward_schedule": rec.get("forward_schedule"),
+                                       "forward_schedule_trial_ms": rec.get("forward_schedule_trial_ms")}
             if rec.get("fused_gather_unavailable"):
                 extras["mlp_n_sharded"]["fused_gather_unavailable"] = rec["fused_gather_unavailable"]
 

@@ -227,6 +227,11 @@ int ntb200_dist_barrier(ntb200_dist_comm* comm, void* stream);
 int ntb200_dist_set_barrier_limit_ms(ntb200_dist_comm* comm, unsigned int limit_ms);
 int ntb200_dist_gemm_allgather(ntb200_dist_comm* comm, const ntb200_gemm_desc* desc, ntb200_dist_buffer* gathered,
                                int64_t gathered_row_stride, int64_t col0, int relu, void* stream);
+/* The same with the block placed at row `row0` of the gathered matrix: row blocks of one matrix can be gathered
+ * one after the other, or at the same time on two streams - each stream then needs a communicator of its own (its
+ * own flags), while `gathered` may have been created by either. */
+int ntb200_dist_gemm_allgather_at(ntb200_dist_comm* comm, const ntb200_gemm_desc* desc, ntb200_dist_buffer* gathered,
+                                  int64_t gathered_row_stride, int64_t row0, int64_t col0, int relu, void* stream);
 int ntb200_dist_allgather_columns(ntb200_dist_comm* comm, int dtype, const void* block, int64_t rows, int64_t cols,
                                   int64_t block_row_stride, ntb200_dist_buffer* gathered, int64_t gathered_row_stride,
                                   int64_t col0, void* stream);

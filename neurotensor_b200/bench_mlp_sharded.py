@@ -24,7 +24,8 @@ if ROOT not in sys.path:
 from neurotensor_b200 import _lib, partition  # noqa: E402
 
 
-def measure(rank, world, dist=None, steps=10, batch=8192, din=4096, hidden=16384, check=False, nccl=False, warmup=3, phases=False):
+def measure(rank, world, dist=None, steps=10, batch=8192, din=4096, hidden=16384, check=False, nccl=False, warmup=3, phases=False,
+            schedule="auto"):
     """Times the N-sharded step on the ranks of an initialised process group (dist = torch.distributed, or None for one
     rank) and returns the result record on every rank (`check` is filled on rank 0 only)."""
     B, D, H = batch, din, hidden
@@ -63,6 +64,32 @@ def measure(rank, world, dist=None, steps=10, batch=8192, din=4096, hidden=16384
             fused_error = fused_error or "another rank could not map its peers"
             fused = False
     step = mlp.step_fused if fused else mlp.step
+    schedule_ms = None
+    if fused and schedule != "plain":
+        # two forward schedules give the same bits: one row block, or two row blocks on two streams so that the
+        # gather of one overlaps the math of the other.  Which is faster depends on how long the gather is against the
+        # math (i.e. on the number of ranks): both are timed for a few steps and every rank takes the faster one (the
+        # times are maxima over the ranks, so the choice is the same everywhere).
+        if schedule == "pipelined":
+            step = mlp.step_fused_pipelined
+        else:
+            schedule_ms = {}
+            for name, fn in (("plain", mlp.step_fused), ("pipelined", mlp.step_fused_pipelined)):
+                for _ in range(2):
+                    fn(x, t)
+                barrier()
+                a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a0.record()
+                for _ in range(5):
+                    fn(x, t)
+                a1.record()
+                barrier()
+                tt = torch.tensor([a0.elapsed_time(a1) / 5], device="cuda")
+                if dist is not None:
+                    dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+                schedule_ms[name] = float(tt.item())
+            if schedule_ms["pipelined"] < schedule_ms["plain"]:
+                step = mlp.step_fused_pipelined
     for _ in range(warmup):
         loss, grads = step(x, t)
     barrier()
@@ -149,6 +176,10 @@ def measure(rank, world, dist=None, steps=10, batch=8192, din=4096, hidden=16384
               "gather": ("stores from the GEMM epilogues into peer-mapped buffers + flag exchange (ntb200_dist_gemm_allgather)" if fused
                          else ("none" if world == 1 else "NCCL all-gather + re-tile")),
               "check": result_check}
+    if fused:
+        record["forward_schedule"] = "two row blocks on two streams" if step == mlp.step_fused_pipelined else "one row block"
+        if schedule_ms:
+            record["forward_schedule_trial_ms"] = schedule_ms
     if fused_error:
         record["fused_gather_unavailable"] = fused_error
     if phase_ms is not None:
@@ -168,6 +199,8 @@ def main():
     ap.add_argument("--fused", action="store_true", help="(default) all-gathers fused into the GEMM epilogues: stores into peer buffers")
     ap.add_argument("--nccl", action="store_true", help="baseline: NCCL all-gather + re-tile kernel instead of the fused epilogues")
     ap.add_argument("--phases", action="store_true", help="also time each phase of the fused step with CUDA events (rank 0 prints them)")
+    ap.add_argument("--schedule", default="auto", choices=["auto", "plain", "pipelined"],
+                    help="forward pass of the fused step: one row block, two row blocks on two streams, or whichever a short trial finds faster")
     args = ap.parse_args()
     rank, world, local = (int(os.environ.get(k, d)) for k, d in (("RANK", 0), ("WORLD_SIZE", 1), ("LOCAL_RANK", 0)))
     torch.cuda.set_device(local)
@@ -175,7 +208,7 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    record = measure(rank, world, dist, args.steps, args.batch, args.din, args.hidden, args.check, args.nccl, phases=args.phases)
+    record = measure(rank, world, dist, args.steps, args.batch, args.din, args.hidden, args.check, args.nccl, phases=args.phases, schedule=args.schedule)
     if rank == 0:
         print(json.dumps(record), flush=True)
     if dist is not None:

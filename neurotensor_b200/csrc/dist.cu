@@ -307,9 +307,20 @@ int ntb200_dist_barrier(ntb200_dist_comm* c, void* stream) {
 
 int ntb200_dist_gemm_allgather(ntb200_dist_comm* c, const ntb200_gemm_desc* desc, ntb200_dist_buffer* gathered,
                                int64_t gathered_row_stride, int64_t col0, int relu, void* stream) {
+    if (gathered && gathered->comm != c)
+        return fail(NTB200_ERR_INVALID_ARG, "dist_gemm_allgather: the buffer belongs to another communicator");
+    return ntb200_dist_gemm_allgather_at(c, desc, gathered, gathered_row_stride, 0, col0, relu, stream);
+}
+
+int ntb200_dist_gemm_allgather_at(ntb200_dist_comm* c, const ntb200_gemm_desc* desc, ntb200_dist_buffer* gathered,
+                                  int64_t gathered_row_stride, int64_t row0, int64_t col0, int relu, void* stream) {
     if (int rc = check_comm(c, "dist_gemm_allgather")) return rc;
     if (!desc || !gathered) return fail(NTB200_ERR_INVALID_ARG, "dist_gemm_allgather: null pointer");
-    if (gathered->comm != c) return fail(NTB200_ERR_INVALID_ARG, "dist_gemm_allgather: the buffer belongs to another communicator");
+    // the buffer may come from another communicator of the same ranks (row blocks of one matrix gathered on two
+    // streams need two sets of flags, i.e. two communicators, and one buffer)
+    if (!gathered->comm || gathered->comm->world != c->world || gathered->comm->rank != c->rank)
+        return fail(NTB200_ERR_INVALID_ARG, "dist_gemm_allgather: the buffer belongs to a communicator of other ranks");
+    if (row0 < 0) return fail(NTB200_ERR_INVALID_ARG, "dist_gemm_allgather: negative row offset");
     const size_t es = dtype_size(desc->dtype);
     if (desc->dtype != NTB200_F16 && desc->dtype != NTB200_BF16)
         return fail(NTB200_ERR_UNSUPPORTED, "dist_gemm_allgather: Float16 / BFloat16 (got %s)", dtype_name(desc->dtype));
@@ -317,14 +328,15 @@ int ntb200_dist_gemm_allgather(ntb200_dist_comm* c, const ntb200_gemm_desc* desc
     if (col0 < 0 || gathered_row_stride < col0 + desc->n)
         return fail(NTB200_ERR_INVALID_ARG, "dist_gemm_allgather: columns [%lld, %lld) do not fit rows of %lld", (long long)col0,
                     (long long)(col0 + desc->n), (long long)gathered_row_stride);
-    if (size_t(desc->m) * size_t(gathered_row_stride) * es > gathered->bytes)
-        return fail(NTB200_ERR_INVALID_ARG, "dist_gemm_allgather: %lld rows of %lld elements do not fit the %zu-byte buffer", (long long)desc->m,
-                    (long long)gathered_row_stride, gathered->bytes);
+    if (size_t(row0 + desc->m) * size_t(gathered_row_stride) * es > gathered->bytes)
+        return fail(NTB200_ERR_INVALID_ARG, "dist_gemm_allgather: rows [%lld, %lld) of %lld elements do not fit the %zu-byte buffer",
+                    (long long)row0, (long long)(row0 + desc->m), (long long)gathered_row_stride, gathered->bytes);
+    const size_t block_offset = (size_t(row0) * size_t(gathered_row_stride) + size_t(col0)) * es;
     void* peers[kMaxRanks];
     int n_peers = 0;
     for (int r = 0; r < c->world; ++r)
-        if (r != c->rank) peers[n_peers++] = static_cast<char*>(gathered->base[r]) + size_t(col0) * es;
-    void* local_block = static_cast<char*>(gathered->base[c->rank]) + size_t(col0) * es;
+        if (r != c->rank) peers[n_peers++] = static_cast<char*>(gathered->base[r]) + block_offset;
+    void* local_block = static_cast<char*>(gathered->base[c->rank]) + block_offset;
     int rc;
     if (relu) {
         // desc->c keeps the pre-activation block; the activation goes into every rank's gathered buffer
@@ -349,7 +361,7 @@ int ntb200_dist_gemm_allgather(ntb200_dist_comm* c, const ntb200_gemm_desc* desc
             ntb200_gemm_desc d = *desc;
             d.route = NTB200_ROUTE_AUTO;
             if ((rc = ntb200_gemm(&d, stream))) return rc;
-            for (int r = 0; r < c->world; ++r) t.base[t.count++] = static_cast<char*>(gathered->base[r]) + size_t(col0) * es;
+            for (int r = 0; r < c->world; ++r) t.base[t.count++] = static_cast<char*>(gathered->base[r]) + block_offset;
             if (desc->dtype == NTB200_BF16)
                 push_relu16_kernel<true><<<blocks, 256, 0, s>>>(static_cast<const unsigned short*>(desc->c), desc->c_row_stride, t, dst_rb, desc->m, desc->n);
             else
@@ -362,7 +374,7 @@ int ntb200_dist_gemm_allgather(ntb200_dist_comm* c, const ntb200_gemm_desc* desc
             d.route = NTB200_ROUTE_AUTO;
             if ((rc = ntb200_gemm(&d, stream))) return rc;
             for (int r = 0; r < c->world; ++r)
-                if (r != c->rank) t.base[t.count++] = static_cast<char*>(gathered->base[r]) + size_t(col0) * es;
+                if (r != c->rank) t.base[t.count++] = static_cast<char*>(gathered->base[r]) + block_offset;
             if (t.count > 0)
                 push_block_bytes_kernel<<<blocks, 256, 0, s>>>(static_cast<const char*>(local_block), dst_rb, t, dst_rb, desc->m, desc->n * (long long)es);
         }

@@ -82,6 +82,30 @@ for m, k, n in ((256, 128, 512), (4096, 512, 4096)):               # copy-kernel
     for b_ in bufs:
         b_.close()
 _lib.check(L.ntb200_check_device_status(None))
+# two row blocks of one gathered matrix on two streams, each with its own communicator (its own flags), into a buffer
+# that belongs to the first: ntb200_dist_gemm_allgather_at
+comm2 = partition.DistComm()
+side = torch.cuda.Stream()
+m, k, n = 4096, 512, 4096
+x, w, b = rn((m, k)), rn((k, n), k ** -0.5), rn((n,), 0.1)
+full = api.linear(x, w, b)
+c0, cn = partition.c_shard(n, world, rank, 8)
+bufs = [comm.buffer(m, n, torch.bfloat16) for _ in range(2)]
+for step in range(10):
+    buf = bufs[step & 1]
+    h = torch.empty((m, cn), dtype=torch.bfloat16, device="cuda")
+    main = torch.cuda.current_stream()
+    side.wait_stream(main)
+    comm.gemm_allgather(x[:1920], w[:, c0:c0 + cn], buf, c0, bias=b[c0:c0 + cn], relu=True, row0=0, h_out=h[:1920])
+    with torch.cuda.stream(side):
+        comm2.gemm_allgather(x[1920:], w[:, c0:c0 + cn], buf, c0, bias=b[c0:c0 + cn], relu=True, row0=1920, h_out=h[1920:])
+    main.wait_stream(side)
+    assert torch.equal(h, full[:, c0:c0 + cn]) and torch.equal(buf.local, torch.clamp(full, min=0)), ("row blocks", step)
+torch.cuda.synchronize()
+for b_ in bufs:
+    b_.close()
+comm2.close()
+_lib.check(L.ntb200_check_device_status(None))
 # a barrier whose peer stays away: rank 0 gives up after 100 ms and says so; rank 1 arrives late and completes at
 # once against the count rank 0 left behind; afterwards the two are in step again
 _lib.check(L.ntb200_dist_set_barrier_limit_ms(comm._h, 100))
