@@ -1,7 +1,7 @@
 """Builds oracle/_ref/libntref.so: the REFERENCE's own matmult kernel sources, compiled here, as a second opinion on
 the restatement in oracle.cpp.  Test infrastructure only (tests/ and the CPU-baseline leg of bench.py may load it).
 
-    python oracle/build_ref.py [reference root, default /root/reference]
+    python oracle/build_ref.py [reference root]        (default: $NT_REFERENCE_ROOT, else the checkout beside this repository)
 
 What is compiled: the reference's nt_matmult<T> template (nt/functional/cpu/matmult/nt_matmult.hpp: packing, K-tile
 loop, tile schedule), its microkernel (nt_matmult_simde.hpp) and its per-dtype SIMD traits
@@ -22,6 +22,8 @@ import re
 import shutil
 import subprocess
 import sys
+
+DEFAULT_REFERENCE = os.environ.get("NT_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
@@ -168,7 +170,8 @@ static inline __m128 ntref_x_mm_round_ps(__m128 v, int mode) { (void)mode; retur
     return "\n".join(out) + "\n"
 
 
-def build(reference="/root/reference", force=False):
+def build(reference=None, force=False):
+    reference = reference or DEFAULT_REFERENCE
     if not os.path.isdir(os.path.join(reference, "nt")):
         return LIB if os.path.exists(LIB) else None
     if os.path.exists(LIB) and not force:
@@ -198,4 +201,4 @@ def build(reference="/root/reference", force=False):
 
 
 if __name__ == "__main__":
-    print(build(sys.argv[1] if len(sys.argv) > 1 else "/root/reference", force=True))
+    print(build(sys.argv[1] if len(sys.argv) > 1 else None, force=True))
