@@ -1285,6 +1285,28 @@ umma_gemm_cluster_k_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
     const int kb_begin = int(rank) * cp.blocks_per_slice;
     const int kb_end = min(p.k_blocks, kb_begin + cp.blocks_per_slice);
 
+    // One K block into one stage (thread 0 only: it is the producer, before and after the block-wide barrier).
+    auto load_stage = [&](int kb, int stage) {
+        const uint32_t a_dst = smem_base + stage * p.s_stage_bytes;
+        const uint32_t b_dst = a_dst + p.s_a_bytes;
+        const uint32_t bar = full_bar(stage);
+        mbar_expect_tx(bar, p.s_stage_tx);
+        const int k0 = kb * p.block_k;
+        if (!p.a_mn_major) {
+            tma_load_3d(a_dst, &tma_a, bar, k0, m0, 0);
+        } else {
+            for (int c = 0; c < p.a_chunks; ++c) tma_load_3d(a_dst + c * p.chunk_bytes, &tma_a, bar, m0 + c * p.chunk_mn, k0, 0);
+        }
+        if (!p.b_mn_major) {
+            tma_load_3d(b_dst, &tma_b, bar, k0, n0, 0);
+        } else {
+            for (int c = 0; c < p.b_chunks; ++c) tma_load_3d(b_dst + c * p.chunk_bytes, &tma_b, bar, n0 + c * p.chunk_mn, k0, 0);
+        }
+    };
+    // The first loads leave before the tensor-memory allocation and the block-wide barrier: every barrier they use is
+    // this CTA's own and was initialised by this very thread, the ring is empty, and the weights' first bytes are what
+    // the kernel waits for longest.
+    int prefilled = 0;
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
             mbar_init(full_bar(s), 1);
@@ -1294,8 +1316,8 @@ umma_gemm_cluster_k_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
         *abort_flag = 0;
         fence_barrier_init();
         fence_proxy_async_smem();
-        tma_prefetch_desc(&tma_a);
-        tma_prefetch_desc(&tma_b);
+        prefilled = min(min(4, kStages), kb_end - kb_begin);
+        for (int i = 0; i < prefilled; ++i) load_stage(kb_begin + i, i);
     }
     if (warp == 1) {
         tmem_alloc<1>(smem_u32(const_cast<uint32_t*>(tmem_slot)), BN);
@@ -1309,30 +1331,16 @@ umma_gemm_cluster_k_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer: this slice's K blocks
         if (lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0;
+            int stage = prefilled == kStages ? 0 : prefilled;       // the stages filled before the barrier come first
+            uint32_t phase = prefilled == kStages ? 1u : 0u;
             bool ok = true;
-            for (int kb = kb_begin; kb < kb_end; ++kb) {
+            for (int kb = kb_begin + prefilled; kb < kb_end; ++kb) {
                 if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
                     raise_timeout(abort_flag, 0x21);
                     ok = false;
                     break;
                 }
-                const uint32_t a_dst = smem_base + stage * p.s_stage_bytes;
-                const uint32_t b_dst = a_dst + p.s_a_bytes;
-                const uint32_t bar = full_bar(stage);
-                mbar_expect_tx(bar, p.s_stage_tx);
-                const int k0 = kb * p.block_k;
-                if (!p.a_mn_major) {
-                    tma_load_3d(a_dst, &tma_a, bar, k0, m0, 0);
-                } else {
-                    for (int c = 0; c < p.a_chunks; ++c) tma_load_3d(a_dst + c * p.chunk_bytes, &tma_a, bar, m0 + c * p.chunk_mn, k0, 0);
-                }
-                if (!p.b_mn_major) {
-                    tma_load_3d(b_dst, &tma_b, bar, k0, n0, 0);
-                } else {
-                    for (int c = 0; c < p.b_chunks; ++c) tma_load_3d(b_dst + c * p.chunk_bytes, &tma_b, bar, n0 + c * p.chunk_mn, k0, 0);
-                }
+                load_stage(kb, stage);
                 if (++stage == kStages) { stage = 0; phase ^= 1u; }
             }
             if (ok) {   // leave no copy in flight: every stage released means every load has landed and been consumed
@@ -1367,9 +1375,15 @@ umma_gemm_cluster_k_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
             }
             if (ok) umma_commit<1>(tfull_bar);   // this slice's partial tile is complete
         }
-    } else {
+    }
+    __syncwarp();   // the other lanes of the producer and MMA warps wait here until their lane 0 is through its loop
+    {
         // ------------------------------------------------------------------ spill the partial tile to shared memory
+        // A warp reads the 32 tensor-memory lanes of quadrant warp % 4, so rows 0-63 have two warps each (0 and 4, 1
+        // and 5: the producer and MMA warps are free by now) and share their chunks; with few rows, where only the
+        // first quadrants hold results, that halves the longest serial piece of the kernel's tail.
         const int quad = warp & 3;
+        const int part = warp >> 2, parts = quad < 2 ? 2 : 1;
         bool ok = mbar_wait(tfull_bar, 0, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) {
@@ -1379,7 +1393,7 @@ umma_gemm_cluster_k_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
             // the ring is idle (every MMA has completed, so every load has been consumed): the partial tile goes there
             float* dst = reinterpret_cast<float*>(smem_gen) + (quad * 32 + lane) * cp.pitch;
 #pragma unroll 1
-            for (int cc = 0; cc < BN / 32; ++cc) {
+            for (int cc = part; cc < BN / 32; cc += parts) {
                 uint32_t v[32];
                 tmem_ld_32x32b_x32(tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(cc * 32), v);
                 tmem_ld_wait();
