@@ -70,11 +70,13 @@ def measure(rank, world, dist=None, steps=10, batch=8192, din=4096, hidden=16384
         # gather of one overlaps the math of the other.  Which is faster depends on how long the gather is against the
         # math (i.e. on the number of ranks): both are timed for a few steps and every rank takes the faster one (the
         # times are maxima over the ranks, so the choice is the same everywhere).
-        if schedule == "pipelined":
-            step = mlp.step_fused_pipelined
+        four = lambda a, b: mlp.step_fused_pipelined(a, b, 4)
+        variants = {"plain": mlp.step_fused, "pipelined": mlp.step_fused_pipelined, "pipelined4": four}
+        if schedule in ("pipelined", "pipelined4"):
+            step = variants[schedule]
         else:
             schedule_ms = {}
-            for name, fn in (("plain", mlp.step_fused), ("pipelined", mlp.step_fused_pipelined)):
+            for name, fn in variants.items():
                 for _ in range(2):
                     fn(x, t)
                 barrier()
@@ -88,8 +90,7 @@ def measure(rank, world, dist=None, steps=10, batch=8192, din=4096, hidden=16384
                 if dist is not None:
                     dist.all_reduce(tt, op=dist.ReduceOp.MAX)
                 schedule_ms[name] = float(tt.item())
-            if schedule_ms["pipelined"] < schedule_ms["plain"]:
-                step = mlp.step_fused_pipelined
+            step = variants[min(schedule_ms, key=schedule_ms.get)]
     for _ in range(warmup):
         loss, grads = step(x, t)
     barrier()
@@ -177,7 +178,8 @@ def measure(rank, world, dist=None, steps=10, batch=8192, din=4096, hidden=16384
                          else ("none" if world == 1 else "NCCL all-gather + re-tile")),
               "check": result_check}
     if fused:
-        record["forward_schedule"] = "two row blocks on two streams" if step == mlp.step_fused_pipelined else "one row block"
+        record["forward_schedule"] = ("one row block" if step == mlp.step_fused else
+                                      "two row blocks on two streams" if step == mlp.step_fused_pipelined else "four row blocks on four streams")
         if schedule_ms:
             record["forward_schedule_trial_ms"] = schedule_ms
     if fused_error:
@@ -199,7 +201,7 @@ def main():
     ap.add_argument("--fused", action="store_true", help="(default) all-gathers fused into the GEMM epilogues: stores into peer buffers")
     ap.add_argument("--nccl", action="store_true", help="baseline: NCCL all-gather + re-tile kernel instead of the fused epilogues")
     ap.add_argument("--phases", action="store_true", help="also time each phase of the fused step with CUDA events (rank 0 prints them)")
-    ap.add_argument("--schedule", default="auto", choices=["auto", "plain", "pipelined"],
+    ap.add_argument("--schedule", default="auto", choices=["auto", "plain", "pipelined", "pipelined4"],
                     help="forward pass of the fused step: one row block, two row blocks on two streams, or whichever a short trial finds faster")
     args = ap.parse_args()
     rank, world, local = (int(os.environ.get(k, d)) for k, d in (("RANK", 0), ("WORLD_SIZE", 1), ("LOCAL_RANK", 0)))

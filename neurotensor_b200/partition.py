@@ -287,7 +287,8 @@ class ShardedMLP:
         own = comm is None
         comm = comm or DistComm(self.group)
         # a second communicator (its own flags) and a side stream for the second row block of step_fused_pipelined
-        self._fused = {"comm": comm, "own_comm": own, "comm2": DistComm(self.group), "side": torch.cuda.Stream(),
+        self._fused = {"comm": comm, "own_comm": own, "more_comms": [DistComm(self.group) for _ in range(3)],
+                       "side": [torch.cuda.Stream() for _ in range(3)],
                        "a": [comm.buffer(batch, hidden, dt) for _ in range(2)],
                        "y": [comm.buffer(batch, dout, dt) for _ in range(2)], "parity": 0}
 
@@ -297,45 +298,47 @@ class ShardedMLP:
             for key in ("a", "y"):
                 for b in f[key]:
                     b.close()
-            f["comm2"].close()
+            for c in f["more_comms"]:
+                c.close()
             if f["own_comm"]:
                 f["comm"].close()
         self._fused = None
 
-    def step_fused_pipelined(self, x, target):
-        """step_fused with the forward pass in two row blocks on two streams: while the first block's activations cross
-        NVLink the second block is being computed, and layer 2 of the first block runs while the second block's
-        activations travel.  Rows are independent, so every result is bit for bit the one of step_fused; the backward
-        pass (which contracts over all rows) is unchanged.  It pays when the gather is longer than the math, i.e. from
-        about four GPUs on (at eight, a rank receives 235 MB of activations per step against 0.13 ms of layer-1 math)."""
+    def step_fused_pipelined(self, x, target, nblocks=2):
+        """step_fused with the forward pass in `nblocks` (2 or 4) row blocks, each on a stream of its own: while one
+        block's activations cross NVLink the next block is being computed, and layer 2 of a block runs while the later
+        blocks' activations travel.  Rows are independent, so every result is bit for bit the one of step_fused; the
+        backward pass (which contracts over all rows) is unchanged.  It pays when the gather is longer than the math,
+        i.e. from about four GPUs on (at eight, a rank receives 235 MB of activations per step against 0.13 ms of
+        layer-1 math).  Every stream has a communicator (flags) of its own; all write into one gathered buffer."""
         from . import api
         f = self._fused
         par = f["parity"]
         f["parity"] ^= 1
-        abuf, ybuf, side = f["a"][par], f["y"][par], f["side"]
-        comms = (f["comm"], f["comm2"])
+        abuf, ybuf = f["a"][par], f["y"][par]
+        nblocks = max(1, min(int(nblocks), 1 + len(f["more_comms"])))
+        comms = [f["comm"]] + f["more_comms"][:nblocks - 1]
         main = torch.cuda.current_stream()
+        streams = [main] + f["side"][:nblocks - 1]
         rows = x.shape[0]
-        half = (rows // 2 + 127) // 128 * 128
-        blocks = ((0, half), (half, rows - half))
+        per = (-(-rows // nblocks) + 127) // 128 * 128
+        blocks = [(r0, min(per, rows - r0)) for r0 in range(0, rows, per)]
         h_loc = torch.empty((rows, self.hn), dtype=x.dtype, device=x.device)
         w2_cols = self.w2[:, self.d0:self.d0 + self.dn]
         b2_cols = self.b2[self.d0:self.d0 + self.dn]
         mark = self._mark
         mark("start")
-        side.wait_stream(main)
+        for st in streams[1:]:
+            st.wait_stream(main)
         for i, (r0, nr) in enumerate(blocks):
-            if nr <= 0:
-                continue
-            with torch.cuda.stream(main if i == 0 else side):
+            with torch.cuda.stream(streams[i]):
                 comms[i].gemm_allgather(x[r0:r0 + nr], self.w1, abuf, self.h0, bias=self.b1, relu=True, row0=r0, h_out=h_loc[r0:r0 + nr])
         for i, (r0, nr) in enumerate(blocks):
-            if nr <= 0:
-                continue
-            with torch.cuda.stream(main if i == 0 else side):
+            with torch.cuda.stream(streams[i]):
                 comms[i].gemm_allgather(abuf.local[r0:r0 + nr], w2_cols, ybuf, self.d0, bias=b2_cols, row0=r0)
-        main.wait_stream(side)
-        mark("forward: two row blocks on two streams, both layers, gathers and flag exchanges")
+        for st in streams[1:]:
+            main.wait_stream(st)
+        mark("forward: %d row blocks on %d streams, both layers, gathers and flag exchanges" % (len(blocks), len(blocks)))
         a, y = abuf.local, ybuf.local
         loss, dy = api.mse(y, target)
         mark("MSE and its gradient")
