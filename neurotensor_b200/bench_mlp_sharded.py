@@ -76,7 +76,7 @@ def measure(rank, world, dist=None, steps=10, batch=8192, din=4096, hidden=16384
             step = variants[schedule]
         else:
             schedule_ms = {}
-            for name, fn in variants.items():
+            for name, fn in list(variants.items())[:2]:   # four blocks lost on two and on eight GPUs: on request only
                 for _ in range(2):
                     fn(x, t)
                 barrier()

@@ -106,15 +106,18 @@ class GatheredMatrix {
 // This rank's column block  bias + x . w_cols  lands in columns [col0, col0 + n) of `out` on every rank; on return
 // (in stream order) `out.local()` holds every rank's block.  With `pre_activation` the block itself is kept there
 // ([m, n], for the ReLU backward mask) and `out` receives max(block, 0): Linear + ReLU of a column-sharded layer.
+// `row0`: the block goes to rows [row0, row0 + m) of the gathered matrix (row blocks of one matrix gathered one after
+// the other; `out` may have been created through another communicator of the same ranks).
 inline Tensor linear_allgather(Communicator& comm, const Tensor& x, const Tensor& w_cols, const Tensor& bias_cols, GatheredMatrix& out,
-                               int64_t col0, Tensor* pre_activation = nullptr) {
+                               int64_t col0, Tensor* pre_activation = nullptr, int64_t row0 = 0) {
     utils::throw_exception(!x.is_null() && !w_cols.is_null(), "linear_allgather got a null tensor");
     utils::throw_exception(x.dims() == 2 && w_cols.dims() == 2, "linear_allgather takes 2-D operands");
     utils::throw_exception(x.dtype() == w_cols.dtype(), "Expected both tensors to have the same dtype for matmult");
     utils::throw_exception(x.shape()[1] == w_cols.shape()[0], "Expected second tensor rows to be ", x.shape()[1], " when it was ",
                            w_cols.shape()[0]);
     const int64_t m = x.shape()[0], k = x.shape()[1], n = w_cols.shape()[1];
-    utils::throw_exception(m == out.rows() && col0 >= 0 && col0 + n <= out.cols(), "linear_allgather: the column block does not fit the gathered matrix");
+    utils::throw_exception(row0 >= 0 && row0 + m <= out.rows() && col0 >= 0 && col0 + n <= out.cols(),
+                           "linear_allgather: the block does not fit the gathered matrix");
     ntb200_gemm_desc d{};
     d.dtype = dtype_code(x.dtype());
     d.route = NTB200_ROUTE_TENSOR;
@@ -129,7 +132,7 @@ inline Tensor linear_allgather(Communicator& comm, const Tensor& x, const Tensor
         *pre_activation = Tensor(SizeRef({m, n}), x.dtype());
         d.c = pre_activation->data_ptr(); d.c_row_stride = n;
     }
-    utils::check(ntb200_dist_gemm_allgather(comm.handle(), &d, out.handle(), out.cols(), col0, pre_activation ? 1 : 0, nullptr));
+    utils::check(ntb200_dist_gemm_allgather_at(comm.handle(), &d, out.handle(), out.cols(), row0, col0, pre_activation ? 1 : 0, nullptr));
     return out.local();
 }
 

@@ -418,6 +418,13 @@ int main(int argc, char** argv) {
         REQUIRE(act.columns(128, 136).contiguous().to_vector<uint16_t>() == fn::relu(expect).to_vector<uint16_t>());
         Tensor plain = ds::linear_allgather(comm, x, w, bias, full, 0);
         REQUIRE(plain.columns(0, 136).contiguous().to_vector<uint16_t>() == expect.to_vector<uint16_t>());
+        // two row blocks of the same product, the second through another communicator, give the same matrix
+        ds::Communicator comm2(0, 1);
+        ds::GatheredMatrix blocks(comm, 200, 136, DType::Float16);
+        ds::linear_allgather(comm, x.rows(0, 128), w, bias, blocks, 0, nullptr, 0);
+        Tensor both = ds::linear_allgather(comm2, x.rows(128, 72), w, bias, blocks, 0, nullptr, 128);
+        REQUIRE(both.contiguous().to_vector<uint16_t>() == expect.to_vector<uint16_t>());
+        REQUIRE(throws_invalid_argument([&] { ds::linear_allgather(comm, x, w, bias, blocks, 0, nullptr, 8); }));
         comm.barrier();
         nt::cuda::synchronize();
     });
