@@ -305,22 +305,26 @@ def main():
         extras["target_8192"] = target
         # ---- more than one GPU: the N-sharded MLP step (strong scaling) through the C-ABI partitioner
         if world > 1:
-            from neurotensor_b200 import bench_mlp_sharded
-            # measure() agrees between the ranks on every failure it can meet (peer mapping, a flag exchange that
-            # ran out of time) and then times the NCCL gather instead, saying so in the record
-            rec = bench_mlp_sharded.measure(rank, world, dist, steps=20, check=True)
-            chk = rec.get("check") or {}
-            extras["mlp_n_sharded"] = {"workload": "BASELINE.json configs[3]: BFloat16 MLP 8192 x (4096 -> 16384 -> 4096), forward + backward, "
-                                                   "every GEMM split over its output columns", "scaling": "strong",
-                                       "ms_per_step": rec["ms_per_step"], "tflops": rec["tflops"], "gather": rec["gather"],
-                                       "kernels_per_step": rec["kernels_per_step_rank0"],
-                                       "matches_unsharded": bool(chk.get("bit_identical", False)),
-                                       "unsharded_ms_per_step_same_gpu": chk.get("unsharded_ms_per_step_same_gpu"),
-                                       "strong_scaling_efficiency": chk.get("strong_scaling_efficiency"), "check": chk,
-                                       "forward_schedule": rec.get("forward_schedule"),
-                                       "forward_schedule_trial_ms": rec.get("forward_schedule_trial_ms")}
-            if rec.get("fused_gather_unavailable"):
-                extras["mlp_n_sharded"]["fused_gather_unavailable"] = rec["fused_gather_unavailable"]
+            try:
+                from neurotensor_b200 import bench_mlp_sharded
+                # measure() agrees between the ranks on every failure it can meet (peer mapping, a flag exchange that
+                # ran out of time) and then times the NCCL gather instead, saying so in the record
+                rec = bench_mlp_sharded.measure(rank, world, dist, steps=20, check=True)
+                chk = rec.get("check") or {}
+                extras["mlp_n_sharded"] = {"workload": "BASELINE.json configs[3]: BFloat16 MLP 8192 x (4096 -> 16384 -> 4096), forward + backward, "
+                                                       "every GEMM split over its output columns", "scaling": "strong",
+                                           "ms_per_step": rec["ms_per_step"], "tflops": rec["tflops"], "gather": rec["gather"],
+                                           "kernels_per_step": rec["kernels_per_step_rank0"],
+                                           "matches_unsharded": bool(chk.get("bit_identical", False)),
+                                           "unsharded_ms_per_step_same_gpu": chk.get("unsharded_ms_per_step_same_gpu"),
+                                           "strong_scaling_efficiency": chk.get("strong_scaling_efficiency"), "check": chk,
+                                           "forward_schedule": rec.get("forward_schedule"),
+                                           "forward_schedule_trial_ms": rec.get("forward_schedule_trial_ms")}
+                if rec.get("fused_gather_unavailable"):
+                    extras["mlp_n_sharded"]["fused_gather_unavailable"] = rec["fused_gather_unavailable"]
+            except Exception as exc:   # noqa: BLE001 - a failure every rank meets alike must not cost the headline line
+                extras["mlp_n_sharded"] = {"error": "%s: %s" % (type(exc).__name__, exc)}
+                torch.cuda.synchronize()
 
         # ---- the same launch repeated for at least two seconds: what the GPU sustains under its power cap
         barrier()
