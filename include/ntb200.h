@@ -232,6 +232,11 @@ int ntb200_dist_gemm_allgather(ntb200_dist_comm* comm, const ntb200_gemm_desc* d
  * own flags), while `gathered` may have been created by either. */
 int ntb200_dist_gemm_allgather_at(ntb200_dist_comm* comm, const ntb200_gemm_desc* desc, ntb200_dist_buffer* gathered,
                                   int64_t gathered_row_stride, int64_t row0, int64_t col0, int relu, void* stream);
+/* The same without the closing flag exchange: the block is on its way to every rank when the call returns (in stream
+ * order), and nothing may read the other ranks' blocks before an ntb200_dist_barrier on the same communicator.  For
+ * callers with work that needs only this rank's own block in the meantime. */
+int ntb200_dist_gemm_push_at(ntb200_dist_comm* comm, const ntb200_gemm_desc* desc, ntb200_dist_buffer* gathered,
+                             int64_t gathered_row_stride, int64_t row0, int64_t col0, int relu, void* stream);
 int ntb200_dist_allgather_columns(ntb200_dist_comm* comm, int dtype, const void* block, int64_t rows, int64_t cols,
                                   int64_t block_row_stride, ntb200_dist_buffer* gathered, int64_t gathered_row_stride,
                                   int64_t col0, void* stream);
@@ -410,6 +415,11 @@ int ntb200_relu(int dtype, const void* x, void* y, int64_t n, void* stream);
 int ntb200_relu_backward(int dtype, const void* x, const void* grad_out, void* grad_in, int64_t n, void* stream);
 /* loss::MSE (nt/nn/Loss.cpp:49-55): *loss (float, device) = sum((o-t)^2)/n ; grad = 2(o-t)/n in `dtype`. */
 int ntb200_mse(int dtype, const void* out, const void* target, void* grad, float* loss, int64_t n, void* stream);
+/* The gradient alone for a [rows, cols] block of a larger matrix (row strides in elements; n_total = the element count
+ * of the whole matrix the loss is taken over): the same values ntb200_mse writes there.  A rank that owns a column
+ * block of the output can start on its weight gradient before the other ranks' blocks have arrived. */
+int ntb200_mse_grad_block(int dtype, const void* out, int64_t out_row_stride, const void* target, int64_t target_row_stride,
+                          void* grad, int64_t grad_row_stride, int64_t rows, int64_t cols, int64_t n_total, void* stream);
 /* Bias gradient: column sums of grad[rows, cols] -> out[cols], the broadcast-reduce that
  * Tensor::operator+= / sum_as performs for dBias (nt/functional/tensor_files/operators.cpp:178-186). */
 int ntb200_column_sum(int dtype, const void* grad, void* out, int64_t rows, int64_t cols, void* stream);

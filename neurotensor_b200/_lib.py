@@ -96,6 +96,8 @@ SIGNATURES = {
     "ntb200_dist_set_barrier_limit_ms": (_ci, [_vp, ctypes.c_uint]),
     "ntb200_dist_gemm_allgather": (_ci, [_vp, ctypes.POINTER(GemmDesc), _vp, _i64, _i64, _ci, _vp]),
     "ntb200_dist_gemm_allgather_at": (_ci, [_vp, ctypes.POINTER(GemmDesc), _vp, _i64, _i64, _i64, _ci, _vp]),
+    "ntb200_dist_gemm_push_at": (_ci, [_vp, ctypes.POINTER(GemmDesc), _vp, _i64, _i64, _i64, _ci, _vp]),
+    "ntb200_mse_grad_block": (_ci, [_ci, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _vp]),
     "ntb200_dist_allgather_columns": (_ci, [_vp, _ci, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _vp]),
     "ntb200_matmult": (_ci, [_ci, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _ci, _ci, _vp]),
     "ntb200_matmult_batch": (_ci, [_ci, ctypes.POINTER(_vp), ctypes.POINTER(_vp), ctypes.POINTER(_vp), _i64, _i64,

@@ -911,6 +911,21 @@ def mse(out, target, want_grad=True):
     return loss, grad
 
 
+
+def mse_grad_block(out_block, target_block, numel_total):
+    """The gradient loss::MSE gives for a [rows, cols] block (views with unit column stride) of a matrix of
+    `numel_total` elements: the values mse() writes at those positions, as a contiguous [rows, cols] tensor."""
+    _require_cuda(out_block, target_block)
+    if out_block.dim() != 2 or out_block.shape != target_block.shape or out_block.stride(1) != 1 or target_block.stride(1) != 1:
+        raise ValueError("mse_grad_block takes two [rows, cols] blocks of the same shape with unit column stride")
+    if out_block.dtype != target_block.dtype:
+        raise ValueError("Expected both tensors to have the same dtype for MSE")
+    rows, cols = out_block.shape
+    grad = torch.empty((rows, cols), dtype=out_block.dtype, device=out_block.device)
+    check(lib().ntb200_mse_grad_block(dtype_code(out_block), out_block.data_ptr(), out_block.stride(0), target_block.data_ptr(),
+                                      target_block.stride(0), grad.data_ptr(), cols, rows, cols, int(numel_total), _stream()))
+    return grad
+
 def column_sum(grad):
     g2 = grad.reshape(-1, grad.shape[-1]).contiguous()
     out = torch.empty(g2.shape[1], dtype=grad.dtype, device=grad.device)

@@ -71,12 +71,13 @@ def measure(rank, world, dist=None, steps=10, batch=8192, din=4096, hidden=16384
         # math (i.e. on the number of ranks): both are timed for a few steps and every rank takes the faster one (the
         # times are maxima over the ranks, so the choice is the same everywhere).
         four = lambda a, b: mlp.step_fused_pipelined(a, b, 4)
-        variants = {"plain": mlp.step_fused, "pipelined": mlp.step_fused_pipelined, "pipelined4": four}
-        if schedule in ("pipelined", "pipelined4"):
+        early = lambda a, b: mlp.step_fused_pipelined(a, b, 2, True)
+        variants = {"plain": mlp.step_fused, "pipelined": mlp.step_fused_pipelined, "pipelined_dw2": early, "pipelined4": four}
+        if schedule in ("pipelined", "pipelined4", "pipelined_dw2"):
             step = variants[schedule]
         else:
             schedule_ms = {}
-            for name, fn in list(variants.items())[:2]:   # four blocks lost on two and on eight GPUs: on request only
+            for name, fn in list(variants.items())[:3]:   # four blocks lost on two and on eight GPUs: on request only
                 for _ in range(2):
                     fn(x, t)
                 barrier()
@@ -179,7 +180,9 @@ def measure(rank, world, dist=None, steps=10, batch=8192, din=4096, hidden=16384
               "check": result_check}
     if fused:
         record["forward_schedule"] = ("one row block" if step == mlp.step_fused else
-                                      "two row blocks on two streams" if step == mlp.step_fused_pipelined else "four row blocks on four streams")
+                                      "two row blocks on two streams" if step == mlp.step_fused_pipelined else
+                                      "two row blocks on two streams, dW2 alongside the output gather" if step is early else
+                                      "four row blocks on four streams")
         if schedule_ms:
             record["forward_schedule_trial_ms"] = schedule_ms
     if fused_error:
@@ -201,7 +204,7 @@ def main():
     ap.add_argument("--fused", action="store_true", help="(default) all-gathers fused into the GEMM epilogues: stores into peer buffers")
     ap.add_argument("--nccl", action="store_true", help="baseline: NCCL all-gather + re-tile kernel instead of the fused epilogues")
     ap.add_argument("--phases", action="store_true", help="also time each phase of the fused step with CUDA events (rank 0 prints them)")
-    ap.add_argument("--schedule", default="auto", choices=["auto", "plain", "pipelined", "pipelined4"],
+    ap.add_argument("--schedule", default="auto", choices=["auto", "plain", "pipelined", "pipelined_dw2", "pipelined4"],
                     help="forward pass of the fused step: one row block, two row blocks on two streams, or whichever a short trial finds faster")
     args = ap.parse_args()
     rank, world, local = (int(os.environ.get(k, d)) for k, d in (("RANK", 0), ("WORLD_SIZE", 1), ("LOCAL_RANK", 0)))

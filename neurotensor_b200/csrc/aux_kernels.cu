@@ -276,6 +276,19 @@ __global__ void mse_kernel(const T* __restrict__ o, const T* __restrict__ t, T* 
     }
 }
 
+// The gradient of mse_kernel alone, for a [rows, cols] block of a larger matrix (row strides in elements): the same
+// expression, with the element count of the WHOLE matrix the loss is taken over.
+template <class T>
+__global__ void mse_grad_block_kernel(const T* __restrict__ o, long long o_rs, const T* __restrict__ t, long long t_rs,
+                                      T* __restrict__ grad, long long g_rs, long long rows, long long cols, float inv_n) {
+    const long long total = rows * cols;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / cols, c = i - r * cols;
+        const float d = F<T>::ld(o[r * o_rs + c]) - F<T>::ld(t[r * t_rs + c]);
+        grad[r * g_rs + c] = F<T>::st(2.f * d * inv_n);
+    }
+}
+
 // out[c] = sum_r grad[r][c]; block = 32 columns x 32 row lanes, one block per 32 columns.
 template <class T>
 __global__ void column_sum_kernel(const T* __restrict__ g, T* __restrict__ out, long long rows, long long cols) {
@@ -538,6 +551,23 @@ int ntb200_mse(int dtype, const void* out, const void* target, void* grad, float
     const int blocks = grid_for(n, 2048);
     const float inv_n = 1.0f / float(n);
     NTB200_FLOAT_SWITCH(dtype, (mse_kernel<T><<<blocks, 256, 0, s>>>((const T*)out, (const T*)target, (T*)grad, loss, n, inv_n)));
+    count_launch();
+    NTB200_CUDA(cudaGetLastError());
+    return NTB200_OK;
+}
+
+int ntb200_mse_grad_block(int dtype, const void* out, int64_t out_row_stride, const void* target, int64_t target_row_stride,
+                          void* grad, int64_t grad_row_stride, int64_t rows, int64_t cols, int64_t n_total, void* stream) {
+    if (rows < 0 || cols < 0 || n_total <= 0) return fail(NTB200_ERR_INVALID_ARG, "mse_grad_block: bad size");
+    if (rows == 0 || cols == 0) return NTB200_OK;
+    if (!out || !target || !grad) return fail(NTB200_ERR_INVALID_ARG, "mse_grad_block: null pointer");
+    if (out_row_stride < cols || target_row_stride < cols || grad_row_stride < cols)
+        return fail(NTB200_ERR_INVALID_ARG, "mse_grad_block: a row stride is shorter than the block's rows");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int blocks = grid_for(rows * cols, 2048);
+    const float inv_n = 1.0f / float(n_total);
+    NTB200_FLOAT_SWITCH(dtype, (mse_grad_block_kernel<T><<<blocks, 256, 0, s>>>((const T*)out, out_row_stride, (const T*)target, target_row_stride,
+                                                                               (T*)grad, grad_row_stride, rows, cols, inv_n)));
     count_launch();
     NTB200_CUDA(cudaGetLastError());
     return NTB200_OK;

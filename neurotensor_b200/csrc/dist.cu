@@ -314,6 +314,12 @@ int ntb200_dist_gemm_allgather(ntb200_dist_comm* c, const ntb200_gemm_desc* desc
 
 int ntb200_dist_gemm_allgather_at(ntb200_dist_comm* c, const ntb200_gemm_desc* desc, ntb200_dist_buffer* gathered,
                                   int64_t gathered_row_stride, int64_t row0, int64_t col0, int relu, void* stream) {
+    if (int rc = ntb200_dist_gemm_push_at(c, desc, gathered, gathered_row_stride, row0, col0, relu, stream)) return rc;
+    return ntb200_dist_barrier(c, stream);
+}
+
+int ntb200_dist_gemm_push_at(ntb200_dist_comm* c, const ntb200_gemm_desc* desc, ntb200_dist_buffer* gathered,
+                             int64_t gathered_row_stride, int64_t row0, int64_t col0, int relu, void* stream) {
     if (int rc = check_comm(c, "dist_gemm_allgather")) return rc;
     if (!desc || !gathered) return fail(NTB200_ERR_INVALID_ARG, "dist_gemm_allgather: null pointer");
     // the buffer may come from another communicator of the same ranks (row blocks of one matrix gathered on two
@@ -382,8 +388,7 @@ int ntb200_dist_gemm_allgather_at(ntb200_dist_comm* c, const ntb200_gemm_desc* d
         NTB200_CUDA(cudaGetLastError());
         rc = NTB200_OK;
     }
-    if (rc) return rc;
-    return ntb200_dist_barrier(c, stream);
+    return rc;
 }
 
 int ntb200_dist_allgather_columns(ntb200_dist_comm* c, int dtype, const void* block, int64_t rows, int64_t cols,

@@ -143,7 +143,7 @@ class DistComm:
         from . import _lib
         _lib.check(_lib.lib().ntb200_dist_barrier(self._h, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
 
-    def gemm_allgather(self, a, b, buf, col0, bias=None, relu=False, row0=0, h_out=None):
+    def gemm_allgather(self, a, b, buf, col0, bias=None, relu=False, row0=0, h_out=None, barrier=True):
         """This rank's column block bias + a.b lands in rows [row0, row0 + m), columns [col0, col0 + n) of `buf` on EVERY
         rank (stored by the GEMM's epilogue), then the ranks are ordered.  relu: returns the pre-activation block [m, n]
         (written into `h_out` when given) and gathers max(., 0); otherwise returns the rows of buf.local it wrote.
@@ -167,8 +167,11 @@ class DistComm:
             d.c, d.c_row_stride, d.c_batch_stride = h.data_ptr(), h.stride(0), 0
         if bias is not None:
             d.bias, d.bias_row_stride, d.bias_col_stride, d.bias_batch_stride = bias.data_ptr(), 0, bias.stride(0), 0
-        _lib.check(_lib.lib().ntb200_dist_gemm_allgather_at(self._h, ctypes.byref(d), buf._h, buf.cols, row0, col0, int(relu),
-                                                            ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        # barrier=False: no closing flag exchange; the caller orders the ranks (self.barrier()) before anything reads the
+        # other ranks' blocks
+        entry = _lib.lib().ntb200_dist_gemm_allgather_at if barrier else _lib.lib().ntb200_dist_gemm_push_at
+        _lib.check(entry(self._h, ctypes.byref(d), buf._h, buf.cols, row0, col0, int(relu),
+                         ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
         return h if relu else buf.local[row0:row0 + m]
 
     def allgather_columns(self, block, buf, col0):
@@ -304,13 +307,16 @@ class ShardedMLP:
                 f["comm"].close()
         self._fused = None
 
-    def step_fused_pipelined(self, x, target, nblocks=2):
+    def step_fused_pipelined(self, x, target, nblocks=2, early_dw2=False):
         """step_fused with the forward pass in `nblocks` (2 or 4) row blocks, each on a stream of its own: while one
         block's activations cross NVLink the next block is being computed, and layer 2 of a block runs while the later
         blocks' activations travel.  Rows are independent, so every result is bit for bit the one of step_fused; the
         backward pass (which contracts over all rows) is unchanged.  It pays when the gather is longer than the math,
         i.e. from about four GPUs on (at eight, a rank receives 235 MB of activations per step against 0.13 ms of
-        layer-1 math).  Every stream has a communicator (flags) of its own; all write into one gathered buffer."""
+        layer-1 math).  Every stream has a communicator (flags) of its own; all write into one gathered buffer.
+        early_dw2: the gradient of W2's columns needs only this rank's own block of the output (and the gathered
+        activations), so it starts as soon as layer 2 has been computed here, on a stream of its own, while the other
+        ranks' output blocks are still on the links; its operand is the same gradient block, element for element."""
         from . import api
         f = self._fused
         par = f["parity"]
@@ -333,18 +339,36 @@ class ShardedMLP:
         for i, (r0, nr) in enumerate(blocks):
             with torch.cuda.stream(streams[i]):
                 comms[i].gemm_allgather(x[r0:r0 + nr], self.w1, abuf, self.h0, bias=self.b1, relu=True, row0=r0, h_out=h_loc[r0:r0 + nr])
-        for i, (r0, nr) in enumerate(blocks):
-            with torch.cuda.stream(streams[i]):
-                comms[i].gemm_allgather(abuf.local[r0:r0 + nr], w2_cols, ybuf, self.d0, bias=b2_cols, row0=r0)
+        a, y = abuf.local, ybuf.local
+        gw2_loc = gb2_loc = None
+        if early_dw2:
+            bw = f["side"][-1]
+            for i, (r0, nr) in enumerate(blocks):
+                with torch.cuda.stream(streams[i]):
+                    comms[i].gemm_allgather(a[r0:r0 + nr], w2_cols, ybuf, self.d0, bias=b2_cols, row0=r0, barrier=False)
+                bw.wait_stream(streams[i])              # this rank's rows of its own output block are complete
+            with torch.cuda.stream(bw):
+                dy_blk = api.mse_grad_block(y[:, self.d0:self.d0 + self.dn], target[:, self.d0:self.d0 + self.dn], y.numel())
+                gw2_loc = api.matmult(a, dy_blk, True, False)
+                gb2_loc = api.column_sum(dy_blk)
+            for i in range(len(blocks)):
+                with torch.cuda.stream(streams[i]):
+                    comms[i].barrier()
+            main.wait_stream(bw)
+        else:
+            for i, (r0, nr) in enumerate(blocks):
+                with torch.cuda.stream(streams[i]):
+                    comms[i].gemm_allgather(a[r0:r0 + nr], w2_cols, ybuf, self.d0, bias=b2_cols, row0=r0)
         for st in streams[1:]:
             main.wait_stream(st)
-        mark("forward: %d row blocks on %d streams, both layers, gathers and flag exchanges" % (len(blocks), len(blocks)))
-        a, y = abuf.local, ybuf.local
+        mark("forward: %d row blocks on %d streams, both layers, gathers and flag exchanges%s"
+             % (len(blocks), len(blocks), " (dW2, db2 alongside the output gather)" if early_dw2 else ""))
         loss, dy = api.mse(y, target)
         mark("MSE and its gradient")
-        dy_loc = dy[:, self.d0:self.d0 + self.dn]
-        gw2_loc = api.matmult(a, dy_loc, True, False)
-        gb2_loc = api.column_sum(dy_loc.contiguous())
+        if gw2_loc is None:
+            dy_loc = dy[:, self.d0:self.d0 + self.dn]
+            gw2_loc = api.matmult(a, dy_loc, True, False)
+            gb2_loc = api.column_sum(dy_loc.contiguous())
         mark("dW2, db2")
         w2_rows = self.w2[self.h0:self.h0 + self.hn]
         dh_loc = api.matmult_relu_backward(dy, w2_rows, h_loc, True)           # ReLU mask in the epilogue
