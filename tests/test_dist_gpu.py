@@ -101,6 +101,14 @@ for step in range(10):
         comm2.gemm_allgather(x[1920:], w[:, c0:c0 + cn], buf, c0, bias=b[c0:c0 + cn], relu=True, row0=1920, h_out=h[1920:])
     main.wait_stream(side)
     assert torch.equal(h, full[:, c0:c0 + cn]) and torch.equal(buf.local, torch.clamp(full, min=0)), ("row blocks", step)
+    # the gather without its closing flag exchange: the own block is there at once (in stream order), everybody's after
+    # a barrier of the same communicator
+    comm.barrier()          # every rank is through comparing this buffer
+    got = comm.gemm_allgather(x, w[:, c0:c0 + cn], buf, c0, bias=b[c0:c0 + cn], barrier=False)
+    assert torch.equal(got[:, c0:c0 + cn], full[:, c0:c0 + cn]), ("own block", step)
+    comm.barrier()
+    assert torch.equal(buf.local, full), ("after the barrier", step)
+    comm.barrier()          # nobody overwrites the buffer (next step) while a slower rank still compares it
 torch.cuda.synchronize()
 for b_ in bufs:
     b_.close()

@@ -172,6 +172,12 @@ def test_relu_mse_column_sum(api, oracle, dt):
     assert np.allclose(widen(host(grad)), egrad, rtol=tol, atol=1e-6)
     cs = api.column_sum(dx)
     assert np.allclose(widen(host(cs)), xw.sum(axis=0), rtol=2e-2 if dt != "f32" else 1e-5, atol=1e-1 if dt != "f32" else 1e-4)
+    # the gradient of a column block alone (strided views into the two matrices): the very values mse() writes there
+    import torch
+    blk = api.mse_grad_block(dx[:, 24:90], dt_[:, 24:90], dx.numel())
+    assert blk.is_contiguous() and torch.equal(blk, grad[:, 24:90])
+    with pytest.raises(ValueError):
+        api.mse_grad_block(dx[:, 24:90], dt_[:, 24:80], dx.numel())
 
 
 def mlp_reference(oracle, x, w1, b1, w2, b2, target, bf16, grad_scale=1.0):
