@@ -2028,9 +2028,15 @@ int launch_pair_instance(const Maps& m, const UmmaParams& p, cudaStream_t stream
     if constexpr (!kSplit && kEpi == 4) {
         if (p.tma_store && !p.has_relu_out && p.k_blocks <= 6 && !g_four_epilogue_warps) {
             static const int forced = [] { const char* e = getenv("NTB200_EPILOGUE_WARPS"); return e ? atoi(e) : 0; }();
-            const int warps = forced == 8 || forced == 16 ? forced : (p.k_blocks <= 2 ? 16 : 8);   // measured: 16 warps win up to two K blocks
+            // A C with nothing fused leaves through the lean epilogue, and with it four warps (two chunks in flight, no
+            // register pressure) are as fast as eight and faster than sixteen at every depth: [8192, k]^T x [k, 8192] at
+            // k = 16 / 128 / 256 / 384 takes 0.0255 / 0.0282 / 0.0414 / 0.0541 ms on four warps against 0.0279 / 0.0357 /
+            // 0.0491 / 0.0622 ms on sixteen and 0.0258 / 0.0308 / 0.0448 / 0.0571 ms on eight.  The wider instantiations
+            // remain for the general epilogue (bias, previous C, mask), whose chunks are several times as long.
+            const bool plain = p.lean_ok && !p.bias && !p.accumulate && !p.has_mask && p.n_peers == 0 && p.out_kind != kOutI8;
+            const int warps = forced == 8 || forced == 16 ? forced : (plain ? 4 : (p.k_blocks <= 2 ? 16 : 8));   // general epilogue: 16 warps win up to two K blocks
             if (warps == 16) return launch_pair_instance<kKind, kSplit, 16>(m, p, stream);
-            return launch_pair_instance<kKind, kSplit, 8>(m, p, stream);
+            if (warps == 8) return launch_pair_instance<kKind, kSplit, 8>(m, p, stream);
         }
     }
     constexpr uint32_t smem = PairTile<kSplit>::kSmemBytes;
